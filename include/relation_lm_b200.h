@@ -1,0 +1,192 @@
+/*
+ * relation_lm_b200 — C ABI of the B200 (sm_100a) implementation of Relation
+ * LM's routed selection-and-reduction path.
+ *
+ * Every entry point mirrors one operator of the reference project (path and
+ * line of the Python/Triton operator it replaces are cited per function; paths
+ * are relative to the reference project root).  A binding passes raw device
+ * pointers, sizes and a CUDA stream; nothing here depends on PyTorch.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless stated otherwise.  Tensors are
+ *     row-major contiguous unless a stride argument says otherwise.
+ *   - Float tensors carry an rlm_dtype code and are up-cast to fp32 on load;
+ *     all arithmetic is fp32.  Tensors read by bulk (TMA) copies — key caches,
+ *     block statistics, the partner-anchor cache — must be 16-byte aligned.
+ *   - `position` is a device int64 scalar shared by the whole batch (the
+ *     reference reads it on the device so that a captured CUDA graph sees new
+ *     positions).  The *_rows variants take per-row int32 sequence and
+ *     position arrays instead (`position` may then be NULL).
+ *   - Calls validate their arguments on the host and return a negative
+ *     rlm_status WITHOUT launching when something is wrong.  They never
+ *     allocate, never synchronise and never throw.  Work is enqueued on
+ *     `stream` (a cudaStream_t passed as void*).
+ *   - `status` (optional, may be NULL) is a device int32 word.  A kernel that
+ *     detects a device-side problem (bounded wait expired, position outside
+ *     the cache) ORs an RLM_DEV_* bit into it and returns early; it never
+ *     traps.  The caller zeroes and reads it.
+ */
+#ifndef RELATION_LM_B200_H
+#define RELATION_LM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RLM_ABI_VERSION 1
+
+typedef enum { RLM_F32 = 0, RLM_BF16 = 1, RLM_F16 = 2 } rlm_dtype;
+
+typedef enum {
+    RLM_OK = 0,
+    RLM_ERR_NULL = -1,        /* a required pointer is NULL */
+    RLM_ERR_SHAPE = -2,       /* unsupported or inconsistent sizes */
+    RLM_ERR_DTYPE = -3,       /* unknown dtype code */
+    RLM_ERR_ALIGN = -4,       /* a bulk-copied tensor is not 16-byte aligned */
+    RLM_ERR_SMEM = -5,        /* the per-row working set exceeds shared memory */
+    RLM_ERR_LAUNCH = -6,      /* the CUDA runtime refused the launch */
+    RLM_ERR_UNSUPPORTED = -7  /* valid request this build does not implement */
+} rlm_status;
+
+#define RLM_DEV_TIMEOUT 1      /* a bounded wait on a bulk copy expired */
+#define RLM_DEV_POSITION 2     /* position / row index outside the caches */
+
+/* Library identity.  rlm_last_error() returns a host string describing the
+ * last non-zero status returned on the calling thread. */
+int rlm_abi_version(void);
+const char* rlm_last_error(void);
+/* Number of kernels this library has launched since it was loaded (host counter). */
+int64_t rlm_launch_count(void);
+
+/*
+ * Fused anchor + partner selection for the current position.
+ * Replaces relation_lm::relation_select_packed
+ * (src/relation_lm/kernels/relation_select.py:311-382, kernel :9-308).
+ *
+ *   anchor_query [N,64], anchor_router_query [N,64], partner_base [N,128]   query_dtype
+ *   anchor_keys, partner_keys [B,T,64]; partner_anchor_cache [B,T,128]      key_dtype
+ *   *_mean, *_std [B,NB,4,16]                                               stats_dtype
+ *   *_gamma [4], *_bias [4,buckets]                                         param_dtype
+ *   out_anchor [N] i32, out_anchor_score [N] f32,
+ *   out_partner [N,k_out] i32, out_partner_score [N,k_out] f32
+ * Decode form: row_batch = row_position = NULL, N == B, row i uses sequence i
+ * at *position.  Rows form: row i uses sequence row_batch[i] at row_position[i].
+ * block_size is T / NB.  strict_valid selects the strict remote-block rule
+ * (blocks must end before the local window); 0 is the compatibility rule.
+ * Empty partner slots carry score -inf and index t - local_window + 1.
+ */
+int rlm_relation_select_packed(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma,
+    const void* anchor_bias, const void* partner_base, const void* partner_anchor_cache,
+    const void* partner_keys, const void* partner_mean, const void* partner_std,
+    const void* partner_gamma, const void* partner_bias, const int64_t* position,
+    const int32_t* row_batch, const int32_t* row_position,
+    int32_t* out_anchor, float* out_anchor_score, int32_t* out_partner, float* out_partner_score,
+    int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
+    int local_window, int top_blocks, int k_out, int strict_valid,
+    int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
+    int32_t* status, void* stream);
+
+/*
+ * Anchor half alone.  Replaces relationlex::anchor_select
+ * (src/relation_lm/kernels/triton_select.py:255-295, kernel :9-120).
+ */
+int rlm_anchor_select(
+    const void* anchor_query, const void* anchor_keys, const void* router_query,
+    const void* block_mean, const void* block_std, const void* gamma, const void* bias,
+    const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
+    int32_t* out_index, float* out_score,
+    int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
+    int local_window, int top_blocks, int strict_valid,
+    int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
+    int32_t* status, void* stream);
+
+/*
+ * Partner half alone, exact and router queries precomputed by the caller.
+ * Replaces relationlex::partner_topk
+ * (src/relation_lm/kernels/triton_select.py:298-346, kernel :123-252).
+ * anchor_index [N] i32 is excluded from the candidates.
+ */
+int rlm_partner_topk(
+    const void* partner_query, const void* partner_keys, const void* router_query,
+    const void* block_mean, const void* block_std, const void* gamma, const void* bias,
+    const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
+    const int32_t* anchor_index, int32_t* out_index, float* out_score,
+    int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
+    int local_window, int top_blocks, int k_out, int strict_valid,
+    int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
+    int32_t* status, void* stream);
+
+/*
+ * Router state update for the current position.  Replaces
+ * relation_lm::router_cache_update
+ * (src/relation_lm/kernels/router_cache.py:175-241, kernel :9-172).
+ *   anchor_raw, partner_raw [B,64] with row strides in ELEMENTS (views of the
+ *   packed projection)                                   raw_dtype
+ *   four caches [B,T,64]                                 cache_dtype (mutated at row t)
+ *   four stats  [B,NB,4,16]                              stats_dtype (mutated at block t/block_size)
+ *   conv weights [64,3]                                  weight_dtype
+ *   out [B,2,64] f32: the convolved anchor and partner router keys.
+ */
+int rlm_router_cache_update(
+    const void* anchor_raw, int64_t anchor_raw_stride, const void* partner_raw,
+    int64_t partner_raw_stride, void* anchor_raw_cache, void* partner_raw_cache,
+    void* anchor_conv_cache, void* partner_conv_cache, void* anchor_mean, void* anchor_std,
+    void* partner_mean, void* partner_std, const void* anchor_conv_weight,
+    const void* partner_conv_weight, const int64_t* position, float* out,
+    int batch, int max_t, int n_blocks, int block_size,
+    int raw_dtype, int cache_dtype, int stats_dtype, int weight_dtype,
+    int32_t* status, void* stream);
+
+/*
+ * Factorised first relation-MLP layer over gathered rows.  Replaces
+ * relation_lm::relation_hidden_cached
+ * (src/relation_lm/kernels/relation_reduce.py:149-183, kernel :72-146).
+ *   expanded_cache [B,T,2H], operand_cache [B,T,R]       cache_dtype
+ *   anchor_index [N] i32, partner_index [N,K] i32
+ *   product_weight [H,R]                                 weight_dtype
+ *   out [N,K,H] f32
+ * row_batch == NULL: row i gathers from sequence i.  Indices outside [0,T)
+ * (empty partner slots) are clamped; their output is masked by the reduce op.
+ */
+int rlm_relation_hidden_cached(
+    const void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
+    const int32_t* partner_index, const void* product_weight, const int32_t* row_batch,
+    float* out, int n_rows, int n_seq, int max_t, int relation_dim, int hidden_dim, int k_out,
+    int cache_dtype, int weight_dtype, int32_t* status, void* stream);
+
+/*
+ * Same, and first computes the current position's expanded row from
+ * operand_cache[b, t], stores it into expanded_cache[b, t] and uses the fresh
+ * values wherever an index equals t.  Replaces
+ * relation_lm::relation_hidden_cache_update
+ * (src/relation_lm/kernels/relation_reduce.py:312-357, kernel :186-309).
+ *   anchor_weight, partner_weight, product_weight [H,R]; first_bias [H]   weight_dtype
+ */
+int rlm_relation_hidden_cache_update(
+    void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
+    const int32_t* partner_index, const void* anchor_weight, const void* partner_weight,
+    const void* product_weight, const void* first_bias, const int64_t* position, float* out,
+    int batch, int max_t, int relation_dim, int hidden_dim, int k_out,
+    int cache_dtype, int weight_dtype, int32_t* status, void* stream);
+
+/*
+ * Per-partner LayerNorm, active-K softmax and weighted sum.  Replaces
+ * relation_lm::relation_norm_reduce
+ * (src/relation_lm/kernels/relation_reduce.py:420-450, kernel :360-417).
+ *   raw [N,K,D] raw_dtype; partner_scores [N,K] f32; norm_weight, norm_bias [D] param_dtype
+ *   out [N,D] f32.  row_position == NULL: all rows use *position.
+ */
+int rlm_relation_norm_reduce(
+    const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
+    const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
+    int n_rows, int k_out, int dim, int raw_dtype, int param_dtype,
+    int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RELATION_LM_B200_H */

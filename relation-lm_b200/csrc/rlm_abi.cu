@@ -1,0 +1,49 @@
+// Library identity, error reporting and launch bookkeeping.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "rlm_common.cuh"
+
+namespace rlm {
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<int64_t> g_launches{0};
+std::mutex g_attr_mutex;
+std::set<std::pair<const void*, int>> g_attr_done;
+}  // namespace
+
+void set_error(const char* message) {
+    std::snprintf(g_error, sizeof(g_error), "%s", message ? message : "");
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int check_launch(const char* kernel_name) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return RLM_OK;
+    char buffer[400];
+    std::snprintf(buffer, sizeof(buffer), "%s: %s", kernel_name, cudaGetErrorString(e));
+    set_error(buffer);
+    return RLM_ERR_LAUNCH;
+}
+
+int allow_large_smem(const void* kernel, int bytes) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) { set_error("cudaGetDevice failed"); return RLM_ERR_LAUNCH; }
+    std::lock_guard<std::mutex> lock(g_attr_mutex);
+    auto key = std::make_pair(kernel, device);
+    if (g_attr_done.count(key)) return RLM_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return RLM_ERR_LAUNCH; }
+    g_attr_done.insert(key);
+    return RLM_OK;
+}
+}  // namespace rlm
+
+extern "C" int rlm_abi_version(void) { return RLM_ABI_VERSION; }
+extern "C" const char* rlm_last_error(void) { return rlm::g_error; }
+extern "C" int64_t rlm_launch_count(void) { return rlm::g_launches.load(std::memory_order_relaxed); }

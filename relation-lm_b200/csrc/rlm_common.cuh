@@ -1,0 +1,218 @@
+// Shared device/host helpers for the relation_lm_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/relation_lm_b200.h"
+
+namespace rlm {
+
+// ------------------------------------------------------------------ host side
+
+void set_error(const char* message);          // remembered per thread for rlm_last_error()
+void count_launch();                          // bumps rlm_launch_count()
+int check_launch(const char* kernel_name);    // cudaGetLastError -> rlm_status
+// Opts a kernel into `bytes` of dynamic shared memory, once per device.
+int allow_large_smem(const void* kernel, int bytes);
+
+inline bool valid_dtype(int d) { return d == RLM_F32 || d == RLM_BF16 || d == RLM_F16; }
+inline int dtype_size(int d) { return d == RLM_F32 ? 4 : 2; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------ device side
+
+constexpr float kNegInf = -__builtin_huge_valf();
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+
+// One element of a tensor whose dtype is only known at run time (small tensors).
+__device__ __forceinline__ float load_scalar(const void* base, int64_t index, int dtype) {
+    if (dtype == RLM_F32) return static_cast<const float*>(base)[index];
+    if (dtype == RLM_BF16)
+        return bf16_bits_to_float(static_cast<const uint16_t*>(base)[index]);
+    return __half2float(static_cast<const __half*>(base)[index]);
+}
+
+__device__ __forceinline__ void store_scalar(void* base, int64_t index, int dtype, float v) {
+    if (dtype == RLM_F32) static_cast<float*>(base)[index] = v;
+    else if (dtype == RLM_BF16) static_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(v);
+    else static_cast<__half*>(base)[index] = __float2half_rn(v);
+}
+
+// Eight consecutive elements starting at element index `first` (a multiple of
+// 8) of a row that starts at `row` (16-byte aligned; shared or global).
+__device__ __forceinline__ void load8(const void* row, int first, int dtype, float (&f)[8]) {
+    if (dtype == RLM_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(row) + first);
+        float4 a = p[0], b = p[1];
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        uint4 v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(row) + first);
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (dtype == RLM_BF16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                f[2 * i] = __uint_as_float(w[i] << 16);
+                f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __half2 h = *reinterpret_cast<__half2*>(&w[i]);
+                float2 p = __half22float2(h);
+                f[2 * i] = p.x;
+                f[2 * i + 1] = p.y;
+            }
+        }
+    }
+}
+
+// ---- canonical fp32 arithmetic: every operation that can move a selected
+// index is spelled with an explicit rounding so that no contraction or
+// reassociation can differ between builds.  exp/log are plain-fp32
+// Cody-Waite/polynomial evaluations (not the hardware approximations), which
+// makes block scores reproducible bit for bit by a CPU following the same steps.
+
+__device__ __forceinline__ float canon_exp(float x) {
+    if (x != x) return x;
+    if (x < -86.0f) return 0.0f;
+    if (x > 88.0f) return __int_as_float(0x7f800000);
+    const float magic = 12582912.0f;  // 1.5 * 2^23
+    float kf = __fsub_rn(__fmaf_rn(x, 1.44269502f, magic), magic);
+    float r = __fmaf_rn(kf, -0.693145752f, x);
+    r = __fmaf_rn(kf, -1.42860677e-06f, r);
+    float p = 1.98412701e-04f;
+    p = __fmaf_rn(p, r, 1.38888892e-03f);
+    p = __fmaf_rn(p, r, 8.33333377e-03f);
+    p = __fmaf_rn(p, r, 4.16666679e-02f);
+    p = __fmaf_rn(p, r, 1.66666672e-01f);
+    p = __fmaf_rn(p, r, 0.5f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    int k = static_cast<int>(kf);
+    return __int_as_float(__float_as_int(p) + k * (1 << 23));
+}
+
+__device__ __forceinline__ float canon_log(float y) {
+    if (y != y || y < 0.0f) return __int_as_float(0x7fc00000);
+    if (y == 0.0f) return kNegInf;
+    if (y == __int_as_float(0x7f800000)) return y;
+    int bits = __float_as_int(y);
+    int e = (bits - 0x3f3504f3) >> 23;
+    float m = __int_as_float(bits - e * (1 << 23));
+    float f = __fsub_rn(m, 1.0f);
+    float z = __fdiv_rn(f, __fadd_rn(2.0f, f));
+    float w = __fmul_rn(z, z);
+    float p = 9.09090936e-02f;
+    p = __fmaf_rn(p, w, 1.11111112e-01f);
+    p = __fmaf_rn(p, w, 1.42857149e-01f);
+    p = __fmaf_rn(p, w, 0.2f);
+    p = __fmaf_rn(p, w, 3.33333343e-01f);
+    p = __fmul_rn(p, w);
+    float z2 = __fadd_rn(z, z);
+    float lm = __fmaf_rn(z2, p, z2);
+    float ef = static_cast<float>(e);
+    float r = __fmaf_rn(ef, 1.42860677e-06f, lm);
+    return __fmaf_rn(ef, 0.693145752f, r);
+}
+
+// acc = 0; acc = fma(a[i], b[i], acc) for ascending i.
+__device__ __forceinline__ float seg8(const float (&a)[8], const float (&b)[8]) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = __fmaf_rn(a[i], b[i], acc);
+    return acc;
+}
+
+// ---- mbarrier + bulk (TMA, untiled) copies
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Orders earlier generic-proxy accesses to shared memory before later
+// async-proxy (bulk copy) accesses to the same locations.
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up after about one second and reports false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t deadline = global_timer_ns() + 1000000000ull;
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() > deadline) return false;
+    }
+}
+
+// Global -> shared bulk copy; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// ---- warp helpers
+
+// (value, index) arg-max over the warp; ties keep the lowest index.  All lanes
+// receive the result.
+__device__ __forceinline__ void warp_argmax_low(float& v, int& idx) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, s);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, s);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    return v;
+}
+
+}  // namespace rlm

@@ -1,0 +1,182 @@
+"""Relation-reduce tail: factorised first relation-MLP layer and fused norm + reduction.
+
+Operator names, schemas and helper names follow the reference project's
+``src/relation_lm/kernels/relation_reduce.py`` (``factor_relation_first_layer``
+:23-57, ``recommended_relation_cache_mode`` :60-69, ``relation_hidden_cached``
+:149-183, ``relation_hidden_cache_update`` :312-357, ``relation_norm_reduce``
+:420-450).  The operators launch sm_100a kernels through the C ABI.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from relation_lm.kernels import _abi
+
+
+@dataclass(frozen=True)
+class FactorizedRelationWeights:
+    """The first relation-MLP layer rewritten as per-token contributions."""
+
+    anchor_weight: Tensor
+    partner_weight: Tensor
+    product_weight: Tensor
+    first_bias: Tensor
+    expanded_weight: Tensor
+    expanded_bias: Tensor
+
+
+def factor_relation_first_layer(first_weight: Tensor, first_bias: Tensor,
+                                relation_dim: int) -> FactorizedRelationWeights:
+    """Rewrite ``W [a, p, a*p, a-p] + b`` as ``(W_a+W_d) a + (W_p-W_d) p + W_m (a*p) + b``.
+
+    ``expanded_weight`` stacks the anchor and partner matrices so one projection of a cached
+    operand yields both of its contributions; ``expanded_bias`` carries ``b`` on the anchor half
+    only, so the bias enters each relation exactly once.
+    """
+    relation_dim = int(relation_dim)
+    if first_weight.dim() != 2 or first_bias.dim() != 1:
+        raise ValueError("first_weight must be 2D and first_bias must be 1D")
+    if first_weight.size(1) != 4 * relation_dim:
+        raise ValueError("first_weight input dimension must equal 4 * relation_dim")
+    w_a, w_p, w_m, w_d = first_weight.split(relation_dim, dim=1)
+    anchor_weight = (w_a + w_d).contiguous()
+    partner_weight = (w_p - w_d).contiguous()
+    return FactorizedRelationWeights(
+        anchor_weight=anchor_weight,
+        partner_weight=partner_weight,
+        product_weight=w_m.contiguous(),
+        first_bias=first_bias.contiguous(),
+        expanded_weight=torch.cat((anchor_weight, partner_weight), dim=0).contiguous(),
+        expanded_bias=torch.cat((first_bias, torch.zeros_like(first_bias)), dim=0).contiguous(),
+    )
+
+
+def recommended_relation_cache_mode(batch_size: int) -> str:
+    """``"fused_update"`` for a single sequence, ``"separate_update"`` for larger batches."""
+    if batch_size < 1:
+        raise ValueError("batch_size must be positive")
+    return "fused_update" if batch_size == 1 else "separate_update"
+
+
+def _check_indices(anchor_index: Tensor, partner_index: Tensor, rows: int) -> None:
+    if anchor_index.dtype != torch.int32 or partner_index.dtype != torch.int32:
+        raise ValueError("anchor_index and partner_index must be int32")
+    if anchor_index.numel() != rows or partner_index.dim() != 2 or partner_index.size(0) != rows:
+        raise ValueError("anchor_index must be [B] and partner_index [B, K]")
+
+
+@torch.library.custom_op("relation_lm::relation_hidden_cached", mutates_args=(),
+                         device_types="cuda")
+def relation_hidden_cached(
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    product_weight: Tensor,
+) -> Tensor:
+    """``gelu((o[p] * o[a]) W_m^T + E[a, :H] + E[p, H:])`` for every partner slot, ``[B, K, H]`` fp32."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, product_weight=product_weight)
+    batch, max_t, rdim = operand_cache.shape
+    hdim, k_out = product_weight.size(0), partner_index.size(1)
+    _check_indices(anchor_index, partner_index, batch)
+    if expanded_cache.shape != (batch, max_t, 2 * hdim) or product_weight.size(1) != rdim:
+        raise ValueError("expanded_cache must be [B, T, 2H] and product_weight [H, R]")
+    out = torch.empty((batch, k_out, hdim), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cached(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(product_weight), None, _abi.ptr(out), batch, batch,
+            max_t, rdim, hdim, k_out, _abi.same_dtype("cache", expanded_cache, operand_cache),
+            _abi.code(product_weight), _abi.ptr(_abi.status_tensor(device)),
+            _abi.stream_ptr(device)))
+    return out
+
+
+@relation_hidden_cached.register_fake
+def _(expanded_cache, operand_cache, anchor_index, partner_index, product_weight):
+    return operand_cache.new_empty(
+        (operand_cache.size(0), partner_index.size(1), product_weight.size(0)), dtype=torch.float32)
+
+
+@torch.library.custom_op("relation_lm::relation_hidden_cache_update",
+                         mutates_args=("expanded_cache",), device_types="cuda")
+def relation_hidden_cache_update(
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    anchor_weight: Tensor,
+    partner_weight: Tensor,
+    product_weight: Tensor,
+    first_bias: Tensor,
+    position: Tensor,
+) -> Tensor:
+    """As ``relation_hidden_cached``, after computing and storing ``expanded_cache[:, position]``."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, anchor_weight=anchor_weight, partner_weight=partner_weight,
+        product_weight=product_weight, first_bias=first_bias)
+    _abi.require_position(position, device)
+    batch, max_t, rdim = operand_cache.shape
+    hdim, k_out = product_weight.size(0), partner_index.size(1)
+    _check_indices(anchor_index, partner_index, batch)
+    if expanded_cache.shape != (batch, max_t, 2 * hdim) or product_weight.size(1) != rdim \
+            or anchor_weight.shape != product_weight.shape or partner_weight.shape != product_weight.shape \
+            or first_bias.numel() != hdim:
+        raise ValueError("expected expanded_cache [B, T, 2H], weights [H, R] and first_bias [H]")
+    out = torch.empty((batch, k_out, hdim), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cache_update(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(anchor_weight), _abi.ptr(partner_weight),
+            _abi.ptr(product_weight), _abi.ptr(first_bias), _abi.ptr(position), _abi.ptr(out),
+            batch, max_t, rdim, hdim, k_out,
+            _abi.same_dtype("cache", expanded_cache, operand_cache),
+            _abi.same_dtype("weight", anchor_weight, partner_weight, product_weight, first_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@relation_hidden_cache_update.register_fake
+def _(expanded_cache, operand_cache, anchor_index, partner_index, anchor_weight, partner_weight,
+      product_weight, first_bias, position):
+    return operand_cache.new_empty(
+        (operand_cache.size(0), partner_index.size(1), product_weight.size(0)), dtype=torch.float32)
+
+
+@torch.library.custom_op("relation_lm::relation_norm_reduce", mutates_args=(),
+                         device_types="cuda")
+def relation_norm_reduce(
+    raw: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+) -> Tensor:
+    """LayerNorm of each partner's relation vector, softmax over the active partner slots
+    (``k < clamp(ceil(log2(position + 2)), 1, K)`` and a finite score) and their weighted sum."""
+    device = _abi.require_cuda_contiguous(raw=raw, partner_scores=partner_scores,
+                                          norm_weight=norm_weight, norm_bias=norm_bias)
+    _abi.require_position(position, device)
+    batch, k_out, dim = raw.shape
+    if partner_scores.shape != (batch, k_out) or partner_scores.dtype != torch.float32:
+        raise ValueError("partner_scores must be float32 [B, K]")
+    out = torch.empty((batch, dim), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_norm_reduce(
+            _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
+            _abi.ptr(position), None, float(norm_eps), _abi.ptr(out), batch, k_out, dim,
+            _abi.code(raw), _abi.same_dtype("norm parameter", norm_weight, norm_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@relation_norm_reduce.register_fake
+def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps):
+    return raw.new_empty((raw.size(0), raw.size(2)), dtype=torch.float32)

@@ -1,0 +1,75 @@
+"""``relation_lm::router_cache_update`` — stateful router-key update for one position.
+
+Same operator name, schema and mutated arguments as the reference project's
+``src/relation_lm/kernels/router_cache.py:175-241``; one launch of the sm_100a
+kernel ``router_cache_update_kernel`` through the C ABI.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from relation_lm.kernels import _abi
+
+_MUTATED = ("anchor_raw_cache", "partner_raw_cache", "anchor_conv_cache", "partner_conv_cache",
+            "anchor_mean", "anchor_std", "partner_mean", "partner_std")
+
+
+@torch.library.custom_op("relation_lm::router_cache_update", mutates_args=_MUTATED,
+                         device_types="cuda")
+def router_cache_update(
+    anchor_raw: Tensor,
+    partner_raw: Tensor,
+    anchor_raw_cache: Tensor,
+    partner_raw_cache: Tensor,
+    anchor_conv_cache: Tensor,
+    partner_conv_cache: Tensor,
+    anchor_mean: Tensor,
+    anchor_std: Tensor,
+    partner_mean: Tensor,
+    partner_std: Tensor,
+    anchor_conv_weight: Tensor,
+    partner_conv_weight: Tensor,
+    position: Tensor,
+    block_size: int,
+) -> Tensor:
+    """Write raw and causally convolved router keys at ``position`` and refresh that block's
+    mean / biased std for both streams.  ``anchor_raw`` / ``partner_raw`` may be column slices
+    of a wider packed projection (row stride is honoured, inner stride must be 1).
+    Returns the convolved keys ``[B, 2, 64]`` in fp32."""
+    device = _abi.require_cuda_contiguous(
+        anchor_raw_cache=anchor_raw_cache, partner_raw_cache=partner_raw_cache,
+        anchor_conv_cache=anchor_conv_cache, partner_conv_cache=partner_conv_cache,
+        anchor_mean=anchor_mean, anchor_std=anchor_std, partner_mean=partner_mean,
+        partner_std=partner_std, anchor_conv_weight=anchor_conv_weight,
+        partner_conv_weight=partner_conv_weight)
+    for name, raw in (("anchor_raw", anchor_raw), ("partner_raw", partner_raw)):
+        if raw.device != device or raw.dim() != 2 or raw.size(1) != 64 or raw.stride(1) != 1:
+            raise ValueError(f"{name} must be a [B, 64] CUDA tensor with unit inner stride")
+    _abi.require_position(position, device)
+    batch = anchor_raw.size(0)
+    if anchor_raw_cache.size(2) != 64 or anchor_mean[0, 0].numel() != 64:
+        raise ValueError("this build supports router width 64")
+    out = torch.empty((batch, 2, 64), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_router_cache_update(
+            _abi.ptr(anchor_raw), anchor_raw.stride(0), _abi.ptr(partner_raw), partner_raw.stride(0),
+            _abi.ptr(anchor_raw_cache), _abi.ptr(partner_raw_cache), _abi.ptr(anchor_conv_cache),
+            _abi.ptr(partner_conv_cache), _abi.ptr(anchor_mean), _abi.ptr(anchor_std),
+            _abi.ptr(partner_mean), _abi.ptr(partner_std), _abi.ptr(anchor_conv_weight),
+            _abi.ptr(partner_conv_weight), _abi.ptr(position), _abi.ptr(out), batch,
+            anchor_raw_cache.size(1), anchor_mean.size(1), int(block_size),
+            _abi.same_dtype("raw key", anchor_raw, partner_raw),
+            _abi.same_dtype("router cache", anchor_raw_cache, partner_raw_cache,
+                            anchor_conv_cache, partner_conv_cache),
+            _abi.same_dtype("block statistics", anchor_mean, anchor_std, partner_mean, partner_std),
+            _abi.same_dtype("conv weight", anchor_conv_weight, partner_conv_weight),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@router_cache_update.register_fake
+def _(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache, anchor_conv_cache,
+      partner_conv_cache, anchor_mean, anchor_std, partner_mean, partner_std,
+      anchor_conv_weight, partner_conv_weight, position, block_size):
+    return anchor_raw.new_empty((anchor_raw.size(0), 2, anchor_raw.size(1)), dtype=torch.float32)
