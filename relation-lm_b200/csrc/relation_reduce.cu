@@ -10,7 +10,6 @@
 namespace rlm {
 namespace {
 
-constexpr int kMaxSmem = 232448;
 
 // ------------------------------------------------------------------ hidden
 
@@ -197,14 +196,14 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         return RLM_ERR_ALIGN;
     }
     int smem_bytes = hidden_smem_bytes(update, a.rdim);
-    if (smem_bytes > kMaxSmem) {
+    if (smem_bytes > kSmemDynamicLimit) {
         set_error("relation_hidden: relation_dim too large for the staged weight tiles");
         return RLM_ERR_SMEM;
     }
     const void* fn = update ? reinterpret_cast<const void*>(relation_hidden_kernel<true>)
                             : reinterpret_cast<const void*>(relation_hidden_kernel<false>);
     if (smem_bytes > 48 * 1024) {
-        int rc = allow_large_smem(fn, kMaxSmem);
+        int rc = allow_large_smem(fn, kSmemPerCta);
         if (rc != RLM_OK) return rc;
     }
     int tiles = (a.hdim + kHT - 1) / kHT;

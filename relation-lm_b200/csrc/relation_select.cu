@@ -21,7 +21,6 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kD = 64;        // exact-score width == router heads * head width
 constexpr int kHeads = 4;
-constexpr int kMaxSmem = 232448;  // 227 KB per CTA on sm_100
 
 enum Mode { kPacked = 0, kAnchorOnly = 1, kPartnerOnly = 2 };
 
@@ -475,11 +474,11 @@ int launch(SelectArgs& a, void* stream) {
     a.block_size = a.max_t / a.n_blocks;
     Plan plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
                           dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode);
-    if (plan.total > kMaxSmem) {
+    if (plan.total > kSmemDynamicLimit) {
         set_error("relation_select: block statistics + local window + remote blocks exceed 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
-    int rc = allow_large_smem(reinterpret_cast<const void*>(relation_select_kernel), kMaxSmem);
+    int rc = allow_large_smem(reinterpret_cast<const void*>(relation_select_kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     relation_select_kernel<<<a.n_rows, kThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(a);
     count_launch();

@@ -32,13 +32,27 @@ int check_launch(const char* kernel_name) {
 }
 
 int allow_large_smem(const void* kernel, int bytes) {
+    // `bytes` is the per-CTA total the hardware offers; static shared memory of the kernel
+    // counts against it, so the dynamic limit is the remainder.
     int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess) { set_error("cudaGetDevice failed"); return RLM_ERR_LAUNCH; }
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaGetDevice failed");
+        return RLM_ERR_LAUNCH;
+    }
     std::lock_guard<std::mutex> lock(g_attr_mutex);
     auto key = std::make_pair(kernel, device);
     if (g_attr_done.count(key)) return RLM_OK;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) { set_error(cudaGetErrorString(e)); return RLM_ERR_LAUNCH; }
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bytes - static_cast<int>(attr.sharedSizeBytes));
+    if (e != cudaSuccess) {
+        cudaGetLastError();   // do not leave the error for the next launch check
+        set_error(cudaGetErrorString(e));
+        return RLM_ERR_LAUNCH;
+    }
     g_attr_done.insert(key);
     return RLM_OK;
 }

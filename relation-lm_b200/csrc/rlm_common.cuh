@@ -18,6 +18,11 @@ int check_launch(const char* kernel_name);    // cudaGetLastError -> rlm_status
 // Opts a kernel into `bytes` of dynamic shared memory, once per device.
 int allow_large_smem(const void* kernel, int bytes);
 
+// Shared memory one CTA may use on sm_100 (227 KB) and the part of it the kernels here
+// request dynamically (the rest covers their small static allocations).
+constexpr int kSmemPerCta = 232448;
+constexpr int kSmemDynamicLimit = kSmemPerCta - 1024;
+
 inline bool valid_dtype(int d) { return d == RLM_F32 || d == RLM_BF16 || d == RLM_F16; }
 inline int dtype_size(int d) { return d == RLM_F32 ? 4 : 2; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

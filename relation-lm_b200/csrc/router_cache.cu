@@ -17,7 +17,6 @@ namespace {
 
 constexpr int kD = 64;
 constexpr int kThreads = 2 * kD;
-constexpr int kMaxSmem = 232448;
 
 struct RouterArgs {
     const void* raw[2];
@@ -137,12 +136,12 @@ extern "C" int rlm_router_cache_update(
         return RLM_ERR_ALIGN;
     }
     const int smem_bytes = 2 * block_size * kD * dtype_size(cache_dtype);
-    if (smem_bytes > kMaxSmem) {
+    if (smem_bytes > kSmemDynamicLimit) {
         set_error("router_cache_update: block tile exceeds 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
     if (smem_bytes > 48 * 1024) {
-        int rc = allow_large_smem(reinterpret_cast<const void*>(router_cache_update_kernel), kMaxSmem);
+        int rc = allow_large_smem(reinterpret_cast<const void*>(router_cache_update_kernel), kSmemPerCta);
         if (rc != RLM_OK) return rc;
     }
     RouterArgs a{};

@@ -1,0 +1,163 @@
+"""GPU parity of the relation-reduce tail vs the CPU oracle and the reference kernels' golden
+outputs.  Tolerances: 2e-5 max-abs for fp32 inputs, 1e-2 relative for bf16 inputs."""
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import cases
+import oracle
+from gpu_util import assert_status_clear, position_tensor, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+FP32_ATOL = 2.0e-5
+
+
+def _names(kind):
+    return [n for n, c in cases.all_cases().items() if c["kind"] == kind]
+
+
+def _close(got, want, low):
+    got, want = got.float().cpu(), want.float()
+    if low:
+        assert torch.allclose(got, want, atol=1e-2, rtol=1e-2), (got - want).abs().max()
+    else:
+        assert torch.allclose(got, want, atol=FP32_ATOL, rtol=1e-5), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("name", _names("reduce"))
+def test_hidden_kernels_match_golden_and_oracle(golden, name):
+    from relation_lm.kernels.relation_reduce import (factor_relation_first_layer,
+                                                     relation_hidden_cache_update,
+                                                     relation_hidden_cached)
+
+    entry = golden[name]
+    case, ref = entry["case"], entry["outputs"]
+    x = cases.make_inputs(case)
+    assert cases.checksum(x) == entry["input_sha256"]
+    low = case["dtype"] != "fp32"
+    factors = factor_relation_first_layer(x["first_weight"], x["first_bias"], case["relation_dim"])
+    expanded = F.linear(x["operand_cache"].float(), factors.expanded_weight.float(),
+                        factors.expanded_bias.float()).to(x["operand_cache"].dtype)
+    xg = to_cuda(x)
+    fg = factor_relation_first_layer(xg["first_weight"], xg["first_bias"], case["relation_dim"])
+    hidden = relation_hidden_cached(expanded.cuda(), xg["operand_cache"], xg["anchor_index"],
+                                    xg["partner_index"], fg.product_weight)
+    want, _ = oracle.relation_hidden(expanded, x["operand_cache"], x["anchor_index"],
+                                     x["partner_index"], factors.product_weight)
+    _close(hidden, want, low)
+    _close(hidden, ref["hidden_cached"], low)
+    t = case["position"]
+    mutable = expanded.clone()
+    mutable[:, t].zero_()
+    mg = mutable.cuda()
+    updated = relation_hidden_cache_update(
+        mg, xg["operand_cache"], xg["anchor_index"], xg["partner_index"], fg.anchor_weight,
+        fg.partner_weight, fg.product_weight, fg.first_bias, position_tensor(t))
+    want_u, want_cache = oracle.relation_hidden(
+        mutable, x["operand_cache"], x["anchor_index"], x["partner_index"], factors.product_weight,
+        factors.anchor_weight, factors.partner_weight, factors.first_bias, position=t)
+    _close(updated, want_u, low)
+    _close(updated, ref["hidden_updated"], low)
+    _close(mg[:, t], want_cache[:, t], low)
+    _close(mg[:, t], ref["expanded_row"], low)
+    rest = mg.float().cpu()
+    rest[:, t] = 0
+    assert torch.equal(rest, mutable.float())          # only the current row is written
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("batch", [1, 8])
+@pytest.mark.parametrize("k_out", [5, 8])
+def test_reduce_tail_like_the_reference_test(batch, k_out):
+    """Context 512, relation_dim 128, hidden 2304, output 576 (the reference's fixture,
+    tests/test_relation_reduce_gpu.py:46-160): factorised kernels vs the unfactorised layer."""
+    from relation_lm.kernels.relation_reduce import (factor_relation_first_layer,
+                                                     relation_hidden_cache_update,
+                                                     relation_hidden_cached, relation_norm_reduce)
+
+    g = torch.Generator().manual_seed(20260818 + batch)
+    T, R, H, D = 512, 128, 2304, 576
+    operand = torch.randn(batch, T, R, generator=g)
+    w1, b1 = torch.randn(H, 4 * R, generator=g) * 0.02, torch.randn(H, generator=g) * 0.01
+    anchor_index = torch.randint(0, T, (batch,), generator=g, dtype=torch.int32)
+    partner_index = torch.randint(0, T, (batch, k_out), generator=g, dtype=torch.int32)
+    anchor_index[0] = T - 1
+    partner_index[:, 0] = T - 1
+    rows = torch.arange(batch)
+    a = operand[rows, anchor_index.long()][:, None].expand(-1, k_out, -1)
+    p = operand[rows[:, None], partner_index.long()]
+    reference_hidden = F.gelu(F.linear(torch.cat((a, p, a * p, a - p), -1).double(), w1.double(), b1.double())).float()
+    factors = factor_relation_first_layer(w1.cuda(), b1.cuda(), R)
+    expanded = F.linear(operand.cuda(), factors.expanded_weight, factors.expanded_bias)
+    hidden = relation_hidden_cached(expanded, operand.cuda(), anchor_index.cuda(),
+                                    partner_index.cuda(), factors.product_weight)
+    assert torch.allclose(hidden.cpu(), reference_hidden, atol=2e-4, rtol=2e-5)
+    mutable = expanded.clone()
+    mutable[:, T - 1].zero_()
+    updated = relation_hidden_cache_update(
+        mutable, operand.cuda(), anchor_index.cuda(), partner_index.cuda(), factors.anchor_weight,
+        factors.partner_weight, factors.product_weight, factors.first_bias, position_tensor(T - 1))
+    assert torch.allclose(updated.cpu(), reference_hidden, atol=2e-4, rtol=2e-5)
+    assert torch.allclose(mutable[:, T - 1], expanded[:, T - 1], atol=2e-4, rtol=2e-5)
+
+    w2, b2 = torch.randn(D, H, generator=g) * 0.02, torch.randn(D, generator=g) * 0.01
+    gamma, beta = torch.randn(D, generator=g) * 0.05 + 1.0, torch.randn(D, generator=g) * 0.01
+    raw = F.linear(hidden.cpu(), w2, b2)
+    scores = torch.randn(batch, k_out, generator=g)
+    scores[:, -1] = -torch.inf
+    context = relation_norm_reduce(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(),
+                                   position_tensor(T - 1), 1e-5)
+    want = oracle.relation_norm_reduce(raw, scores, gamma, beta, T - 1, 1e-5)
+    assert torch.allclose(context.cpu(), want, atol=FP32_ATOL, rtol=1e-5)
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("name", _names("norm_reduce"))
+def test_norm_reduce_matches_golden_and_oracle(golden, name):
+    from relation_lm.kernels.relation_reduce import relation_norm_reduce
+
+    entry = golden[name]
+    case = entry["case"]
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    for t, ref in entry["outputs"].items():
+        got = relation_norm_reduce(xg["raw"], xg["scores"], xg["norm_weight"], xg["norm_bias"],
+                                   position_tensor(t), case["eps"])
+        want = oracle.relation_norm_reduce(x["raw"], x["scores"], x["norm_weight"], x["norm_bias"],
+                                           t, case["eps"])
+        assert torch.allclose(got.cpu(), want, atol=FP32_ATOL, rtol=1e-5), (name, t)
+        assert torch.allclose(got.cpu(), ref, atol=FP32_ATOL, rtol=1e-5), (name, t)
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_reduce_tail_low_precision_inputs(dtype):
+    """bf16 / fp16 caches and weights at the 512-wide decode shape (hidden 2048), sentinel
+    (negative) partner indices included: within 1e-2 relative of the oracle."""
+    from relation_lm.kernels.relation_reduce import (factor_relation_first_layer,
+                                                     relation_hidden_cached, relation_norm_reduce)
+
+    g = torch.Generator().manual_seed(5150)
+    B, T, R, H, D, K = 8, 512, 128, 2048, 512, 8
+    operand = torch.randn(B, T, R, generator=g).to(dtype)
+    w1, b1 = (torch.randn(H, 4 * R, generator=g) * 0.02).to(dtype), (torch.randn(H, generator=g) * 0.01).to(dtype)
+    factors = factor_relation_first_layer(w1, b1, R)
+    expanded = F.linear(operand.float(), factors.expanded_weight.float(), factors.expanded_bias.float()).to(dtype)
+    anchor_index = torch.randint(0, T, (B,), generator=g, dtype=torch.int32)
+    partner_index = torch.randint(0, T, (B, K), generator=g, dtype=torch.int32)
+    partner_index[:, -1] = -26          # the empty-slot sentinel must not fault
+    hidden = relation_hidden_cached(expanded.cuda(), operand.cuda(), anchor_index.cuda(),
+                                    partner_index.cuda(), factors.product_weight.cuda())
+    want, _ = oracle.relation_hidden(expanded, operand, anchor_index, partner_index, factors.product_weight)
+    assert torch.allclose(hidden.cpu(), want, atol=1e-2, rtol=1e-2)
+    raw = (torch.randn(B, K, D, generator=g)).to(dtype)
+    scores = torch.randn(B, K, generator=g)
+    scores[:, -1] = -torch.inf
+    gamma, beta = torch.ones(D).to(dtype), torch.zeros(D).to(dtype)
+    got = relation_norm_reduce(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(), position_tensor(300), 1e-5)
+    want = oracle.relation_norm_reduce(raw, scores, gamma, beta, 300, 1e-5)
+    assert torch.allclose(got.cpu(), want, atol=1e-2, rtol=1e-2)
+    assert_status_clear()

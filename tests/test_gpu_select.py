@@ -1,0 +1,188 @@
+"""GPU parity of the selectors: CUDA kernels vs the CPU oracle (bit-exact indices AND scores)
+and vs the reference kernels' golden outputs (indices exact, scores within 4e-6)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import cases
+import oracle
+from gpu_util import (assert_scores_equal, assert_status_clear, position_tensor, select_args,
+                      to_cuda)
+
+pytestmark = pytest.mark.gpu
+
+
+def _select_cases():
+    return [n for n, c in cases.all_cases().items() if c["kind"] == "select"]
+
+
+def _policy(case):
+    return case["local_window"], case["top_blocks"], case["k_out"], case["strict_valid"]
+
+
+@pytest.mark.parametrize("name", _select_cases())
+def test_packed_select_matches_golden_and_oracle(golden, name):
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    entry = golden[name]
+    case = entry["case"]
+    x = cases.make_inputs(case)
+    assert cases.checksum(x) == entry["input_sha256"]
+    xg = to_cuda(x)
+    for t, ref in entry["outputs"].items():
+        a, a_s, p, p_s = relation_select_packed(*select_args(xg), position_tensor(t), *_policy(case))
+        oa, oa_s, op, op_s, _ = oracle.relation_select(*select_args(x), t, *_policy(case))
+        assert torch.equal(a.cpu(), oa) and torch.equal(p.cpu(), op), (name, t)
+        assert_scores_equal(a_s, oa_s)
+        assert_scores_equal(p_s, op_s)
+        assert torch.equal(a.cpu(), ref["anchor"]) and torch.equal(p.cpu(), ref["partner"]), (name, t)
+        finite = torch.isfinite(ref["partner_score"])
+        assert torch.allclose(p_s.cpu()[finite], ref["partner_score"][finite], atol=4e-6, rtol=1e-6)
+        assert torch.allclose(a_s.cpu(), ref["anchor_score"], atol=4e-6, rtol=1e-6)
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("name", ["select_reftest", "select_c128_strict", "select_top4_k5",
+                                  "select_bf16", "select_ties_compat"])
+def test_two_operator_path_equals_packed(golden, name):
+    """The reference's own GPU test (tests/test_relation_select_gpu.py:33-87): packed == two-op."""
+    from relation_lm.kernels.relation_select import relation_select_packed
+    from relation_lm.kernels.triton_select import anchor_select, partner_topk
+
+    case = golden[name]["case"]
+    xg = to_cuda(cases.make_inputs(case))
+    L, top, k, strict = _policy(case)
+    batch = torch.arange(case["batch"], device="cuda")
+    for t in case["positions"]:
+        pos = position_tensor(t)
+        anchor, anchor_score = anchor_select(*select_args(xg)[:7], pos, L, top, strict)
+        contribution = xg["partner_anchor_cache"][batch, anchor.long()].float()
+        base = xg["partner_base"].float()
+        partner, partner_score = partner_topk(
+            (base[:, :64] + contribution[:, :64]).contiguous(), xg["partner_keys"],
+            (base[:, 64:] + contribution[:, 64:]).contiguous(), xg["partner_mean"],
+            xg["partner_std"], xg["partner_gamma"], xg["partner_bias"], pos, anchor, L, top, k, strict)
+        fused = relation_select_packed(*select_args(xg), pos, L, top, k, strict)
+        assert torch.equal(anchor, fused[0]) and torch.equal(partner, fused[2])
+        assert torch.equal(anchor_score, fused[1]) and torch.equal(partner_score, fused[3])
+    assert_status_clear()
+
+
+SHAPES = [
+    # batch, context, blocks, window, top, k, dtype
+    (8, 512, 16, 64, 2, 8, "bf16"),      # ctx-512 decode, block 32
+    (8, 512, 64, 16, 2, 8, "fp32"),      # the reference's published policy (block 8, window 16)
+    (16, 2048, 32, 128, 2, 8, "bf16"),   # 12-layer decode shape, block 64
+    (4, 4096, 64, 128, 4, 8, "bf16"),    # long-context shape, 4 remote blocks
+    (4, 2048, 64, 64, 3, 4, "fp16"),     # multi-anchor shape: 3 remote blocks, 4 partners
+    (3, 4096, 64, 128, 4, 8, "fp32"),    # largest shared-memory footprint
+]
+
+
+@pytest.mark.parametrize("strict", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_packed_select_matches_oracle_at_baseline_shapes(shape, strict):
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    B, T, NB, L, top, K, dtype = shape
+    case = {"kind": "select", "seed": 7000 + T + NB + top, "batch": B, "context": T, "blocks": NB,
+            "local_window": L, "top_blocks": top, "k_out": K, "strict_valid": strict, "dtype": dtype}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    bs = T // NB
+    for t in sorted({0, 1, L - 2, L - 1, L, bs - 1, bs, 2 * bs - 1, L + bs, T // 2 + 3, T - 1}):
+        a, a_s, p, p_s = relation_select_packed(*select_args(xg), position_tensor(t), L, top, K, strict)
+        oa, oa_s, op, op_s, _ = oracle.relation_select(*select_args(x), t, L, top, K, strict)
+        assert torch.equal(a.cpu(), oa), (shape, t)
+        assert torch.equal(p.cpu(), op), (shape, t)
+        assert_scores_equal(a_s, oa_s)
+        assert_scores_equal(p_s, op_s)
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("strict", [False, True])
+def test_rows_form_equals_decode_form_at_every_position(strict):
+    """Per-row positions: every t of a context-128 sequence in one launch (fp32, block 16)."""
+    from relation_lm.kernels.relation_select import relation_select_packed_rows
+
+    B, T, NB, L, top, K = 2, 128, 8, 32, 2, 8
+    case = {"kind": "select", "seed": 7100, "batch": B, "rows": B * T, "context": T, "blocks": NB,
+            "local_window": L, "top_blocks": top, "k_out": K, "strict_valid": strict}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(T)
+    row_pos = torch.arange(T, dtype=torch.int32).repeat(B)
+    got = relation_select_packed_rows(*select_args(xg), row_batch.cuda(), row_pos.cuda(), L, top, K, strict)
+    want = oracle.relation_select(*select_args(x), 0, L, top, K, strict, row_batch=row_batch, row_pos=row_pos)
+    assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[2].cpu(), want[2])
+    assert_scores_equal(got[1], want[1])
+    assert_scores_equal(got[3], want[3])
+    # size-independent properties: causal, anchor excluded, partners distinct where valid
+    anchor, partner, score = got[0].cpu(), got[2].cpu(), got[3].cpu()
+    assert torch.all(anchor <= row_pos) and torch.all(anchor >= 0)
+    valid = torch.isfinite(score)
+    assert torch.all((partner <= row_pos[:, None]) | ~valid)
+    assert torch.all((partner != anchor[:, None]) | ~valid)
+    assert torch.all(partner[~valid] == (row_pos[:, None].expand_as(partner)[~valid] - L + 1))
+    assert torch.all(score[:, :-1] >= score[:, 1:])
+    for r in range(0, B * T, 17):
+        live = partner[r][valid[r]]
+        assert live.unique().numel() == live.numel()
+    assert_status_clear()
+
+
+def test_full_window_selection_is_dense_argmax_and_topk():
+    """With the window covering the whole history and no remote blocks the routed selection
+    must equal dense argmax / top-k of causal scores (the reference's dense models,
+    src/relation_lm/models/relation_lm.py:158-167)."""
+    from relation_lm.kernels.relation_select import relation_select_packed_rows
+
+    B, T, NB, K = 2, 64, 8, 8
+    case = {"kind": "select", "seed": 7200, "batch": B, "rows": B * T, "context": T, "blocks": NB,
+            "local_window": T, "top_blocks": 0, "k_out": K, "strict_valid": False}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(T)
+    row_pos = torch.arange(T, dtype=torch.int32).repeat(B)
+    a, _, p, p_s = [v.cpu() for v in relation_select_packed_rows(
+        *select_args(xg), row_batch.cuda(), row_pos.cuda(), T, 0, K, False)]
+    future = torch.triu(torch.ones(T, T, dtype=torch.bool), diagonal=1)
+    aq = x["anchor_query"].view(B, T, 64)
+    dense = (torch.einsum("btd,bsd->bts", aq.double(), x["anchor_keys"].double()) * 0.125)
+    dense = dense.masked_fill(future[None], -torch.inf)
+    assert torch.equal(a.view(B, T).long(), dense.argmax(-1))
+    v = x["partner_base"].view(B, T, 128) + x["partner_anchor_cache"][
+        torch.arange(B)[:, None], a.view(B, T).long()]
+    pd = torch.einsum("btd,bsd->bts", v[..., :64].double(), x["partner_keys"].double()) * 0.125
+    pd = pd.masked_fill(future[None], -torch.inf).scatter(2, a.view(B, T, 1).long(), -torch.inf)
+    top_scores, top_index = pd.topk(K, dim=-1)
+    finite = torch.isfinite(top_scores)
+    assert torch.equal(p.view(B, T, K).long()[finite], top_index[finite])
+    assert torch.equal(torch.isfinite(p_s.view(B, T, K)), finite)
+
+
+def test_argument_validation():
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    case = cases.all_cases()["select_top1_k4"]
+    xg = to_cuda(cases.make_inputs(case))
+    args = select_args(xg)
+    pos = position_tensor(5)
+    with pytest.raises(ValueError):       # position on the host
+        relation_select_packed(*args, torch.tensor(5), 16, 1, 4, False)
+    with pytest.raises(ValueError):       # mixed cache dtypes
+        bad = list(args)
+        bad[1] = bad[1].half()
+        relation_select_packed(*bad, pos, 16, 1, 4, False)
+    with pytest.raises(ValueError):       # non-contiguous keys
+        bad = list(args)
+        bad[1] = bad[1].transpose(0, 1).contiguous().transpose(0, 1)
+        relation_select_packed(*bad, pos, 16, 1, 4, False)
+    with pytest.raises(ValueError):       # working set beyond shared memory
+        relation_select_packed(*args, pos, 16, 1000, 4, False)
+    # a position outside the cache is reported through the status word, never a fault
+    from relation_lm.kernels import _abi
+    relation_select_packed(*args, position_tensor(case["context"] + 3), 16, 1, 4, False)
+    assert _abi.read_status() == 2
+    assert _abi.read_status() == 0
