@@ -1,0 +1,438 @@
+#!/usr/bin/env python3
+"""Benchmark of the routed selection-and-reduction path: ctx-512, K=8 stateful decode.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode position for a batch of sequences (one pass of the hot path:
+packed projection -> cache append / router update -> per layer select -> relation hidden ->
+second MLP layer -> norm-reduce -> heads).  Workload = BASELINE config 2: 6 relation layers,
+d_model 512, vocab 16000 + 256 boundary ids, context 512 (448-token prefix, then generated
+positions), block 32, local window 64, 2 remote blocks, 1 anchor, K = 8, bf16, batch 8 per
+GPU.  Token ids are bounded Zipf(s = 1.1) over the vocabulary, boundary ids uniform; weights
+are seeded random init.  These synthetic inputs stand in for the reference's private
+checkpoint and validation text.
+
+Prints ONE JSON line (rank 0).  ``value`` = tokens/s over all GPUs with every input resident
+in HBM, each step's CUDA-event time summed, the L2 flushed between steps.  ``e2e`` = the same
+metric through the host API: token ids copied from pinned host memory and the greedy next
+token read back every step.  ``roofline`` describes the library kernel with the largest
+share of a step; ``cpu_baseline`` is the CPU port of the same step timed on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "relation-lm_b200"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+PREFIX = 448
+METRIC = "relation decode tokens/s at ctx512 K=8"
+UNIT = "tokens/s"
+
+
+def zipf_tokens(batch: int, length: int, vocab: int, seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    weights = torch.arange(1, vocab + 1, dtype=torch.float64).pow(-1.1)
+    return torch.multinomial(weights / weights.sum(), batch * length, replacement=True,
+                             generator=g).view(batch, length)
+
+
+def make_model(workload: str):
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+
+    if workload == "cfg5":
+        cfg = RoutedRelationConfig(d_model=768, layers=12, max_context=2048, block_size=64,
+                                   local_window=128, top_blocks=2)
+        seed = 1005
+    else:
+        cfg = RoutedRelationConfig()
+        seed = 1002
+    return RoutedRelationLM(cfg, seed=seed), seed
+
+
+# ---------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[list[str]] = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 7:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[3:7]) if v == "Active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(self.samples[0][1]) if self.samples else None,
+                "samples": len(self.samples), "reasons": reasons}
+
+
+# ---------------------------------------------------------------------------- CPU arm
+
+
+def cpu_decode_rate(workload: str, batch: int, steps: int, warmup: int, threads: int):
+    """The CPU port of the decode step on the host cores, from a synthetic state at the end
+    of the prefix (cache contents do not change the work done)."""
+    import oracle
+    from oracle.decode_port import OracleDecoder
+
+    threads = threads or (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    oracle.set_threads(threads)
+    model, seed = make_model(workload)
+    cfg = model.config
+    prefix = cfg.max_context - 64
+    dec = OracleDecoder(model, batch, torch.float32)
+    g = torch.Generator().manual_seed(seed)
+    for t in (dec.anchor_keys, dec.partner_keys, dec.operand_cache, dec.partner_anchor_cache,
+              dec.expanded_cache, *dec.router_caches):
+        t[:, :, :prefix].normal_(generator=g)
+    for i, s in enumerate(dec.router_stats):
+        s[:, :, :prefix // cfg.block_size].normal_(generator=g)
+        if i % 2 == 1:
+            s.abs_()
+    dec.position = prefix
+    tokens = zipf_tokens(batch, warmup + steps, cfg.vocab_size, seed)
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (batch, warmup + steps), generator=g)
+    for i in range(warmup):
+        dec.step(tokens[:, i], bounds[:, i])
+    start = time.perf_counter()
+    for i in range(warmup, warmup + steps):
+        if dec.position >= cfg.max_context:
+            dec.position = prefix
+        dec.step(tokens[:, i], bounds[:, i])
+    elapsed = time.perf_counter() - start
+    return batch * steps / elapsed, elapsed, threads
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    value, elapsed, threads = cpu_decode_rate(args.workload, args.batch, steps, args.warmup, 0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": elapsed / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args.workload, args.batch, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{steps} decode positions of batch {args.batch} from a synthetic "
+                                   "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships no CPU-runnable sparse decode (its kernels are Triton-only and its "
+                "decode driver is not public); this arm times the CPU restatement of the same step",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(workload: str, batch: int, n_gpus: int) -> dict:
+    if workload == "cfg5":
+        return {"workload": "cfg5 batch-sharded stateful decode: 12 layers, d_model 768, ctx 2048, "
+                            "block 64, window 128, 2 remote blocks, 1 anchor, K=8",
+                "batch_per_gpu": batch, "global_batch": batch * n_gpus, "l2": "flushed between steps"}
+    return {"workload": "cfg2 routed stateful decode: 6 layers, d_model 512, ctx 512 (448 prefix), "
+                        "block 32, window 64, 2 remote blocks, 1 anchor, K=8",
+            "batch_per_gpu": batch, "global_batch": batch * n_gpus, "l2": "flushed between steps"}
+
+
+# ---------------------------------------------------------------------------- GPU arm
+
+
+def kernel_table(dec, graph_iters: int = 20):
+    """Average launch duration of each library kernel on the decoder's own state, captured in
+    CUDA graphs (one launch per layer per graph, so consecutive launches touch different
+    caches), with the algorithmic bytes of SURVEY's per-row formulas."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cache_update, relation_norm_reduce
+    from relation_lm.kernels.relation_select import relation_select_packed
+    from relation_lm.kernels.router_cache import sparse_cache_append
+
+    cfg, w, B = dec.config, dec.w, dec.batch
+    L, K, H, R, d = cfg.layers, cfg.k_max, cfg.hidden_dim, cfg.relation_dim, cfg.d_model
+    dev = dec.device
+    e = dec.anchor_keys.element_size()
+    pos = torch.tensor(cfg.max_context - 1, device=dev, dtype=torch.int64)
+    packed = torch.randn(B, L * (384 + R), device=dev).to(dec.dtype)
+    q = torch.randn(B, 256, device=dev).to(dec.dtype)
+    anchor = torch.randint(0, cfg.max_context, (B,), device=dev, dtype=torch.int32)
+    partner = torch.randint(0, cfg.max_context, (B, K), device=dev, dtype=torch.int32)
+    scores = torch.randn(B, K, device=dev)
+    raw = torch.randn(L, B, K, d, device=dev).to(dec.dtype)
+
+    def select(l):
+        relation_select_packed(q[:, 0:64], dec.anchor_keys[l], q[:, 64:128], dec.router_stats[0][l],
+                               dec.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l],
+                               q[:, 128:256], dec.partner_anchor_cache[l], dec.partner_keys[l],
+                               dec.router_stats[2][l], dec.router_stats[3][l], w["partner_gamma"][l],
+                               w["partner_bias"][l], pos, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+
+    def hidden(l):
+        relation_hidden_cache_update(dec.expanded_cache[l], dec.operand_cache[l], anchor, partner,
+                                     w["anchor_weight"][l], w["partner_weight"][l],
+                                     w["product_weight"][l], w["first_bias"][l], pos)
+
+    def reduce(l):
+        relation_norm_reduce(raw[l], scores, w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps)
+
+    def append(_):
+        sparse_cache_append(packed, dec.anchor_keys, dec.partner_keys, dec.operand_cache,
+                            dec.partner_anchor_cache, *dec.router_caches, *dec.router_stats,
+                            w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+
+    cand = cfg.local_window + cfg.top_blocks * cfg.block_size
+    nb = cfg.max_context // cfg.block_size
+    bytes_per_launch = {
+        "relation_select_kernel": B * (e * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K),
+        "relation_hidden_kernel<update>": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + 4 * K * H) + e * 3 * H * R + B * e * (R + 2 * H),
+        "relation_norm_reduce_kernel": B * (e * K * d + 4 * K + 4 * d) + 4 * 2 * d,
+        "router_cache_update_kernel(all layers)": L * B * (e * 64 * (2 + 4 + 4 + 2 * cfg.block_size + 4) + 2 * 64 * 4 + 2 * e * (256 + R)),
+    }
+    table = {}
+    for name, fn, per_graph in (("relation_select_kernel", select, L),
+                                ("relation_hidden_kernel<update>", hidden, L),
+                                ("relation_norm_reduce_kernel", reduce, L),
+                                ("router_cache_update_kernel(all layers)", append, 1)):
+        for l in range(per_graph):
+            fn(l)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for l in range(per_graph):
+                    fn(l)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(graph_iters):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(end) * 1e3 / (graph_iters * per_graph)
+        launches_per_step = per_graph
+        table[name] = {"us_per_launch": us, "launches_per_step": launches_per_step,
+                       "us_per_step": us * launches_per_step, "bytes_per_launch": bytes_per_launch[name],
+                       "gb_per_s": bytes_per_launch[name] / us / 1e3}
+    return table
+
+
+def run_ours(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the library has no CPU fallback)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+    from relation_lm.kernels import _abi
+
+    model, seed = make_model(args.workload)
+    cfg = model.config
+    B, T = args.batch, cfg.max_context
+    prefix = T - 64
+    dec = StatefulDecoder(model, B, device, torch.bfloat16)
+    tokens = zipf_tokens(B, T, cfg.vocab_size, seed + rank).to(device)
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (B, T),
+                           generator=torch.Generator().manual_seed(seed + 77 + rank)).to(device)
+
+    launches_before = _abi.launch_count()
+    dec.step(tokens[:, 0], bounds[:, 0])
+    kernels_per_step = _abi.launch_count() - launches_before
+    dec.reset()
+    dec.capture()
+    # prefix: PREFIX positions through the captured step
+    for t in range(prefix):
+        dec.static_tokens.copy_(tokens[:, t])
+        dec.static_boundaries.copy_(bounds[:, t])
+        dec.replay()
+    torch.cuda.synchronize()
+    assert int(dec.position.item()) == prefix
+    assert _abi.read_status() == 0, "a kernel reported a device-side error during the prefix"
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def run_steps(count: int, timed: bool):
+        events = []
+        for i in range(count):
+            t = prefix + (int(run_steps.done) % 64)
+            if t == prefix and run_steps.done:
+                dec.position.fill_(prefix)
+            dec.static_tokens.copy_(tokens[:, t])
+            dec.static_boundaries.copy_(bounds[:, t])
+            flush.zero_()
+            if timed:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                dec.replay()
+                e.record()
+                events.append((s, e))
+            else:
+                dec.replay()
+            run_steps.done += 1
+        return events
+
+    run_steps.done = 0
+    run_steps(args.warmup, False)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    events = run_steps(args.steps, True)
+    barrier()
+    total_ms = sum(s.elapsed_time(e) for s, e in events)
+
+    # the same steps without the L2 flush (weights stay L2-resident between positions)
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dec.position.fill_(prefix)
+    s.record()
+    for i in range(min(args.steps, 64)):
+        dec.replay()
+    e.record()
+    torch.cuda.synchronize()
+    warm_ms = s.elapsed_time(e) / min(args.steps, 64)
+
+    # end to end: host token ids in, greedy token out, every step
+    host_in = torch.zeros(2, B, dtype=torch.int64).pin_memory()
+    host_out = torch.zeros(B, dtype=torch.int64).pin_memory()
+    host_in[0].copy_(tokens[:, prefix].cpu())
+    dec.position.fill_(prefix)
+    stream = torch.cuda.current_stream(device)
+    e2e_steps = min(args.steps, 64)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        dec.static_tokens.copy_(host_in[0], non_blocking=True)
+        dec.static_boundaries.copy_(host_in[1], non_blocking=True)
+        dec.replay()
+        host_out.copy_(dec.static_next, non_blocking=True)
+        stream.synchronize()
+        host_in[0].copy_(host_out)                      # greedy feedback through the host
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    assert _abi.read_status() == 0, "a kernel reported a device-side error"
+
+    times = torch.tensor([total_ms, e2e_s * 1e3, warm_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, warm_ms = [float(v) for v in times.tolist()]
+
+    if rank == 0:
+        table = kernel_table(dec)
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        dominant = max(table, key=lambda k: table[k]["us_per_step"])
+        dom = table[dominant]
+        lib_us = sum(v["us_per_step"] for v in table.values())
+        threads = os.cpu_count() or 1
+        cpu_steps = 6
+        cpu_value, cpu_elapsed, cpu_threads = cpu_decode_rate(args.workload, B, cpu_steps, 1, threads)
+        line = {
+            "metric": METRIC, "value": world * B * args.steps / (total_ms / 1e3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {**workload_config(args.workload, B, world),
+                       "parameters": model.parameter_count(), "state_bytes_per_gpu": dec.state_bytes()},
+            "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": 2 * B * 8, "d2h_bytes_per_step": B * 8,
+                    "steps": e2e_steps},
+            "gpu_launches": kernels_per_step * args.steps,
+            "l2_warm": {"ms_per_step": warm_ms, "value": world * B / (warm_ms / 1e3), "unit": UNIT,
+                        "note": "same steps back to back without the L2 flush"},
+            "clocks": clocks,
+            "roofline": {"kernel": dominant, "bound": "hbm", "achieved": dom["gb_per_s"], "peak": peak,
+                         "unit": "GB/s", "frac": dom["gb_per_s"] / peak,
+                         "peak_source": "measured" if peaks else "fallback",
+                         "traffic": None, "us_per_launch": dom["us_per_launch"],
+                         "share_of_library_time": dom["us_per_step"] / lib_us,
+                         "note": "batch-8 decode launches move < 1 MB each and are latency-bound"},
+            "kernels": table,
+            "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cpu_threads, "kind": "port",
+                             "sample": f"{cpu_steps} decode positions of batch {B} from a synthetic "
+                                       "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--workload", choices=("cfg2", "cfg5"), default="cfg2")
+    parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
+    args = parser.parse_args()
+    if args.batch is None:
+        args.batch = 8 if args.workload == "cfg2" else 256 // max(1, args.gpus)
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,8 @@ int64_t rlm_launch_count(void);
  * (src/relation_lm/kernels/relation_select.py:311-382, kernel :9-308).
  *
  *   anchor_query [N,64], anchor_router_query [N,64], partner_base [N,128]   query_dtype
+ *     (unit inner stride; row strides in ELEMENTS are passed, so the three may be column
+ *     slices of one query-side projection)
  *   anchor_keys, partner_keys [B,T,64]; partner_anchor_cache [B,T,128]      key_dtype
  *   *_mean, *_std [B,NB,4,16]                                               stats_dtype
  *   *_gamma [4], *_bias [4,buckets]                                         param_dtype
@@ -85,6 +87,7 @@ int rlm_relation_select_packed(
     const void* partner_gamma, const void* partner_bias, const int64_t* position,
     const int32_t* row_batch, const int32_t* row_position,
     int32_t* out_anchor, float* out_anchor_score, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
     int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
     int local_window, int top_blocks, int k_out, int strict_valid,
     int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
@@ -185,6 +188,28 @@ int rlm_relation_norm_reduce(
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
     int n_rows, int k_out, int dim, int raw_dtype, int param_dtype,
     int32_t* status, void* stream);
+
+/*
+ * Decode-state append for every layer of a stack in one launch (extension).  Does what a
+ * reference decode step does per layer after PackedSparseCacheProjection.project
+ * (src/relation_lm/inference/packed_cache.py:52-57): writes the four token features into
+ * row t of their caches and runs router_cache_update
+ * (src/relation_lm/kernels/router_cache.py:175-241) on the two router slices.
+ *   packed [B, layers*(384+R)] packed_dtype, row stride in elements; per layer the columns are
+ *     anchor_key 64 | partner_key 64 | operand R | partner_anchor 128 | anchor_router 64 | partner_router 64
+ *   anchor_keys, partner_keys [layers,B,T,64]; operand_cache [layers,B,T,R];
+ *   partner_anchor_cache [layers,B,T,128]; router caches [layers,B,T,64]      cache_dtype
+ *   stats [layers,B,NB,4,16] stats_dtype; conv weights [layers,64,3] weight_dtype
+ *   out [layers,B,2,64] f32 or NULL.
+ */
+int rlm_sparse_cache_append(
+    const void* packed, int64_t packed_row_stride, int relation_dim, void* anchor_keys,
+    void* partner_keys, void* operand_cache, void* partner_anchor_cache, void* anchor_raw_cache,
+    void* partner_raw_cache, void* anchor_conv_cache, void* partner_conv_cache, void* anchor_mean,
+    void* anchor_std, void* partner_mean, void* partner_std, const void* anchor_conv_weight,
+    const void* partner_conv_weight, const int64_t* position, float* out, int layers, int batch,
+    int max_t, int n_blocks, int block_size, int packed_dtype, int cache_dtype, int stats_dtype,
+    int weight_dtype, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -145,10 +145,12 @@ def block_scores(mean, std, rq, gamma, bias, position, max_t, local_window, stri
 def router_cache_update(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache,
                         anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std,
                         partner_mean, partner_std, anchor_conv_weight, partner_conv_weight,
-                        position, block_size):
-    """Returns (out, new_state dict); inputs are not modified.
+                        position, block_size, inplace=False, cache_dtype=None, stats_dtype=None):
+    """Returns (out, new_state dict).
 
-    Stores are rounded to the dtype of the cache / stats tensors passed in.
+    Stores are rounded to the dtype of the cache / stats tensors passed in (or to
+    ``cache_dtype`` / ``stats_dtype`` when given).  With ``inplace=True`` the eight state
+    tensors must be fp32 contiguous CPU tensors and are updated where they lie.
     """
     batch, max_t = anchor_raw_cache.shape[0], anchor_raw_cache.shape[1]
     nb = anchor_mean.shape[1]
@@ -156,15 +158,21 @@ def router_cache_update(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_c
              "anchor_mean", "anchor_std", "partner_mean", "partner_std")
     tensors = (anchor_raw_cache, partner_raw_cache, anchor_conv_cache, partner_conv_cache,
                anchor_mean, anchor_std, partner_mean, partner_std)
-    state = [_f32(x).copy() for x in tensors]
+    if inplace:
+        if any(t.dtype != torch.float32 or not t.is_contiguous() for t in tensors):
+            raise ValueError("inplace update needs fp32 contiguous state")
+        state = [t.numpy() for t in tensors]
+    else:
+        state = [_f32(x).copy() for x in tensors]
     araw, praw = _f32(anchor_raw), _f32(partner_raw)
     aw, pw = _f32(anchor_conv_weight), _f32(partner_conv_weight)
     out = np.empty((batch, 2, 64), np.float32)
     rc = lib().orc_router_cache_update(
         batch, max_t, nb, int(block_size), int(position), _p(araw),
         ctypes.c_int64(araw.shape[1]), _p(praw), ctypes.c_int64(praw.shape[1]),
-        *[_p(a) for a in state], _p(aw), _p(pw), DTYPE_CODE[anchor_raw_cache.dtype],
-        DTYPE_CODE[anchor_mean.dtype], _p(out))
+        *[_p(a) for a in state], _p(aw), _p(pw),
+        DTYPE_CODE[cache_dtype or anchor_raw_cache.dtype],
+        DTYPE_CODE[stats_dtype or anchor_mean.dtype], _p(out))
     _check(rc, "router_cache_update")
     new_state = {n: torch.from_numpy(a).reshape(t.shape) for n, a, t in zip(names, state, tensors)}
     return torch.from_numpy(out), new_state
@@ -172,17 +180,23 @@ def router_cache_update(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_c
 
 def relation_hidden(expanded_cache, operand_cache, anchor_index, partner_index, product_weight,
                     anchor_weight=None, partner_weight=None, first_bias=None, position=None,
-                    row_batch=None, row_pos=None):
+                    row_batch=None, row_pos=None, inplace=False, cache_dtype=None):
     """``relation_hidden_cached`` (no weights/position) or ``relation_hidden_cache_update``.
 
-    Returns (hidden ``[N, K, H]``, expanded cache after the update).
+    Returns (hidden ``[N, K, H]``, expanded cache after the update).  With ``inplace=True`` the
+    expanded cache must be an fp32 contiguous CPU tensor and is updated where it lies.
     """
     update = anchor_weight is not None
     n, k_out = partner_index.shape
     n_seq, max_t, rdim = operand_cache.shape
     hdim = product_weight.shape[0]
     rb, rp = _rows(n, position if position is not None else 0, row_batch, row_pos)
-    ex = _f32(expanded_cache).copy()
+    if inplace:
+        if expanded_cache.dtype != torch.float32 or not expanded_cache.is_contiguous():
+            raise ValueError("inplace update needs an fp32 contiguous expanded cache")
+        ex = expanded_cache.numpy()
+    else:
+        ex = _f32(expanded_cache).copy()
     op = _f32(operand_cache)
     ai, pi = _i32(anchor_index), _i32(partner_index)
     wm = _f32(product_weight)
@@ -192,7 +206,8 @@ def relation_hidden(expanded_cache, operand_cache, anchor_index, partner_index, 
     out = np.empty((n, k_out, hdim), np.float32)
     rc = lib().orc_relation_hidden(n, n_seq, max_t, rdim, hdim, k_out, _p(rb), _p(rp), _p(ex),
                                    _p(op), _p(ai), _p(pi), _p(wa), _p(wp), _p(wm), _p(fb),
-                                   int(update), DTYPE_CODE[expanded_cache.dtype], _p(out))
+                                   int(update), DTYPE_CODE[cache_dtype or expanded_cache.dtype],
+                                   _p(out))
     _check(rc, "relation_hidden")
     return torch.from_numpy(out), torch.from_numpy(ex).reshape(expanded_cache.shape)
 
@@ -202,7 +217,7 @@ def relation_norm_reduce(raw, partner_scores, norm_weight, norm_bias, position, 
     n, k_out, dim = raw.shape
     if k_out > 64:
         raise ValueError("oracle supports at most 64 partner slots")
-    _, rp = _rows(n, position, None if row_pos is None else torch.zeros(n), row_pos)
+    rp = _i32(torch.full((n,), int(position), dtype=torch.int32) if row_pos is None else row_pos)
     arrs = [_f32(x) for x in (raw, partner_scores, norm_weight, norm_bias)]
     out = np.empty((n, dim), np.float32)
     rc = lib().orc_relation_norm_reduce(n, k_out, dim, _p(rp), *[_p(a) for a in arrs],

@@ -49,6 +49,7 @@ struct SelectArgs {
     int32_t* out_partner;
     float* out_partner_score;
     int32_t* status;
+    int64_t aq_stride, arq_stride, pbase_stride, prq_stride;   // query row strides, elements
     int n_rows, n_seq, max_t, n_blocks, block_size, buckets;
     int local_window, top_blocks, k_out, strict_valid;
     int query_dtype, key_dtype, stats_dtype, param_dtype;
@@ -267,12 +268,12 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     }
     // Small operands through ordinary loads while the bulk copies fly.
     if (do_anchor) {
-        if (tid < kD) aq[tid] = load_scalar(a.anchor_query, static_cast<int64_t>(row) * kD + tid, a.query_dtype);
-        else if (tid < 2 * kD) arq[tid - kD] = load_scalar(a.anchor_router_query, static_cast<int64_t>(row) * kD + tid - kD, a.query_dtype);
+        if (tid < kD) aq[tid] = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) arq[tid - kD] = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
     }
     if (a.mode == kPartnerOnly) {
-        if (tid < kD) pq[tid] = load_scalar(a.partner_base, static_cast<int64_t>(row) * kD + tid, a.query_dtype);
-        else if (tid < 2 * kD) prq[tid - kD] = load_scalar(a.partner_router_query, static_cast<int64_t>(row) * kD + tid - kD, a.query_dtype);
+        if (tid < kD) pq[tid] = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) prq[tid - kD] = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
     }
     if (tid >= 2 * kD && tid < 2 * kD + 8) {
         int h = (tid - 2 * kD) & 3;
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             return;
         }
         if (tid < 2 * kD) {
-            float base = load_scalar(a.partner_base, static_cast<int64_t>(row) * 2 * kD + tid, a.query_dtype);
+            float base = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
             float add = load_scalar(smem + p.pa_row, tid, a.key_dtype);
             pq[tid] = __fadd_rn(base, add);   // pq[64..127] is prq
         }
@@ -495,11 +496,14 @@ extern "C" int rlm_relation_select_packed(
     const void* partner_keys, const void* partner_mean, const void* partner_std,
     const void* partner_gamma, const void* partner_bias, const int64_t* position,
     const int32_t* row_batch, const int32_t* row_position, int32_t* out_anchor,
-    float* out_anchor_score, int32_t* out_partner, float* out_partner_score, int n_rows, int n_seq,
+    float* out_anchor_score, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
+    int n_rows, int n_seq,
     int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out,
     int strict_valid, int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
     int32_t* status, void* stream) {
     rlm::SelectArgs a{};
+    a.aq_stride = anchor_query_stride; a.arq_stride = anchor_router_query_stride; a.pbase_stride = partner_base_stride;
     a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = anchor_router_query;
     a.anchor_mean = anchor_mean; a.anchor_std = anchor_std; a.anchor_gamma = anchor_gamma; a.anchor_bias = anchor_bias;
     a.partner_base = partner_base; a.partner_anchor_cache = partner_anchor_cache; a.partner_keys = partner_keys;
@@ -522,6 +526,7 @@ extern "C" int rlm_anchor_select(
     int buckets, int local_window, int top_blocks, int strict_valid, int query_dtype,
     int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream) {
     rlm::SelectArgs a{};
+    a.aq_stride = 64; a.arq_stride = 64;
     a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = router_query;
     a.anchor_mean = block_mean; a.anchor_std = block_std; a.anchor_gamma = gamma; a.anchor_bias = bias;
     a.position = position; a.row_batch = row_batch; a.row_position = row_position;
@@ -542,6 +547,7 @@ extern "C" int rlm_partner_topk(
     int strict_valid, int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
     int32_t* status, void* stream) {
     rlm::SelectArgs a{};
+    a.pbase_stride = 64; a.prq_stride = 64;
     a.partner_base = partner_query; a.partner_router_query = router_query; a.partner_keys = partner_keys;
     a.partner_mean = block_mean; a.partner_std = block_std; a.partner_gamma = gamma; a.partner_bias = bias;
     a.position = position; a.row_batch = row_batch; a.row_position = row_position;

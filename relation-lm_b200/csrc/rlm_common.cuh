@@ -174,21 +174,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait: gives up after about one second and reports false.
+// Bounded wait: gives up after about 2^31 SM cycles (roughly a second) and reports false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t deadline = global_timer_ns() + 1000000000ull;
+    const long long start = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() > deadline) return false;
+        if (clock64() - start > (1ll << 31)) return false;
     }
 }
 

@@ -1,0 +1,132 @@
+"""Stateful sparse decode: one new position per call, all history in caches.
+
+The step is the composition the reference's decode operators were written for (its own
+driver is not public; the order follows docs/architecture.md:26-40 and
+docs/benchmarks.md:87-113 of the reference project):
+
+1. embed the new token, ``memory = LayerNorm(x)``; one packed projection of ``memory`` for
+   every layer (packed_cache.py:52-57) followed by ``sparse_cache_append`` (token-cache rows
+   + ``router_cache_update`` of all layers, one launch);
+2. per layer: ``LayerNorm(hidden)`` -> one 256-wide query-side projection ->
+   ``relation_select_packed`` -> ``relation_hidden_cache_update`` -> second relation-MLP layer
+   -> ``relation_norm_reduce`` -> ``hidden += sigmoid(mix) * context``;
+3. final LayerNorm, tied token head, boundary head.
+
+Every state tensor is allocated once and mutated in place; ``position`` lives on the device
+and is advanced there, so a captured CUDA graph of ``step`` replays for successive positions.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from relation_lm.inference.routed_model import RoutedRelationLM
+from relation_lm.kernels.relation_reduce import relation_hidden_cache_update, relation_norm_reduce
+from relation_lm.kernels.relation_select import relation_select_packed
+from relation_lm.kernels.router_cache import sparse_cache_append
+
+
+class StatefulDecoder:
+    def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
+                 dtype: torch.dtype = torch.bfloat16) -> None:
+        cfg = model.config
+        self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
+        self.w = model.decode_weights(self.device, dtype)
+        self.input_scale = float(model.input_scale)
+        L, B, T, R, H = cfg.layers, self.batch, cfg.max_context, cfg.relation_dim, cfg.hidden_dim
+        nb = T // cfg.block_size
+
+        def zeros(*shape, dt=dtype):
+            return torch.zeros(*shape, device=self.device, dtype=dt)
+
+        self.anchor_keys = zeros(L, B, T, 64)
+        self.partner_keys = zeros(L, B, T, 64)
+        self.operand_cache = zeros(L, B, T, R)
+        self.partner_anchor_cache = zeros(L, B, T, 128)
+        self.expanded_cache = zeros(L, B, T, 2 * H)
+        self.router_caches = [zeros(L, B, T, 64) for _ in range(4)]   # raw a, raw p, conv a, conv p
+        self.router_stats = [zeros(L, B, nb, 4, 16) for _ in range(4)]  # mean a, std a, mean p, std p
+        self.position = torch.zeros((), device=self.device, dtype=torch.int64)
+        self.last_selection: list[tuple[Tensor, Tensor]] = []
+        self._graph = None
+
+    # ------------------------------------------------------------------ state
+    def reset(self) -> None:
+        for t in (self.anchor_keys, self.partner_keys, self.operand_cache, self.partner_anchor_cache,
+                  self.expanded_cache, *self.router_caches, *self.router_stats):
+            t.zero_()
+        self.position.zero_()
+
+    def state_bytes(self) -> int:
+        tensors = (self.anchor_keys, self.partner_keys, self.operand_cache, self.partner_anchor_cache,
+                   self.expanded_cache, *self.router_caches, *self.router_stats)
+        return sum(t.numel() * t.element_size() for t in tensors)
+
+    # ------------------------------------------------------------------ one position
+    def step(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool = False):
+        """Consume one token per sequence at the current position; returns (token logits
+        ``[B, V]``, boundary logits ``[B, Vb]``) and advances the position."""
+        cfg, w = self.config, self.w
+        pos = self.position
+        x = (F.embedding(tokens, w["token_embedding"]) + F.embedding(boundaries, w["boundary_embedding"])).float()
+        x = x * self.input_scale + w["position_embedding"].index_select(0, pos.view(1))
+        memory = F.layer_norm(x, (cfg.d_model,), w["memory_norm_w"], w["memory_norm_b"], cfg.norm_eps).to(self.dtype)
+        hidden = x
+        packed = F.linear(memory, w["w_packed"])                      # [B, layers * 512]
+        sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
+                            self.partner_anchor_cache, *self.router_caches, *self.router_stats,
+                            w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+        if keep_selection:
+            self.last_selection = []
+        B, K = self.batch, cfg.k_max
+        for l in range(cfg.layers):
+            normalized = F.layer_norm(hidden, (cfg.d_model,), w["input_norm_w"][l], w["input_norm_b"][l],
+                                      cfg.norm_eps).to(self.dtype)
+            q = F.linear(normalized, w["w_query"][l])                 # [B, 256]
+            anchor, _, partner, partner_score = relation_select_packed(
+                q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
+                self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
+                self.partner_anchor_cache[l], self.partner_keys[l], self.router_stats[2][l],
+                self.router_stats[3][l], w["partner_gamma"][l], w["partner_bias"][l], pos,
+                cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+            relation_hidden = relation_hidden_cache_update(
+                self.expanded_cache[l], self.operand_cache[l], anchor, partner, w["anchor_weight"][l],
+                w["partner_weight"][l], w["product_weight"][l], w["first_bias"][l], pos)
+            raw = F.linear(relation_hidden.to(self.dtype), w["w2"][l], w["b2"][l])      # [B, K, d]
+            context = relation_norm_reduce(raw, partner_score, w["relation_norm_w"][l],
+                                           w["relation_norm_b"][l], pos, cfg.norm_eps)
+            hidden = torch.addcmul(hidden, context, w["mix"][l])
+            if keep_selection:
+                self.last_selection.append((anchor, partner))
+        final = F.layer_norm(hidden, (cfg.d_model,), w["final_norm_w"], w["final_norm_b"], cfg.norm_eps).to(self.dtype)
+        token_logits = F.linear(final, w["token_embedding"])
+        boundary_logits = F.linear(final, w["boundary_w"], w["boundary_b"])
+        pos.add_(1)
+        return token_logits, boundary_logits
+
+    # ------------------------------------------------------------------ CUDA graph
+    def capture(self) -> None:
+        """Capture one ``step`` into a CUDA graph with static input / output buffers.  State and
+        position are left exactly as they were."""
+        B = self.batch
+        self.static_tokens = torch.zeros(B, device=self.device, dtype=torch.int64)
+        self.static_boundaries = torch.zeros(B, device=self.device, dtype=torch.int64)
+        saved = int(self.position.item())
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):                                   # warm-up outside capture
+                self.step(self.static_tokens, self.static_boundaries)
+                self.position.fill_(saved)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                self.static_token_logits, self.static_boundary_logits = self.step(
+                    self.static_tokens, self.static_boundaries)
+                self.static_next = self.static_token_logits.argmax(-1)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.position.fill_(saved)
+        self._graph = graph
+
+    def replay(self) -> None:
+        self._graph.replay()

@@ -14,13 +14,14 @@ _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
 # name -> argument types, in the order of include/relation_lm_b200.h
 PROTOTYPES = {
-    "rlm_relation_select_packed": [_P] * 21 + [_I] * 13 + [_P, _P],
+    "rlm_relation_select_packed": [_P] * 21 + [_L] * 3 + [_I] * 13 + [_P, _P],
     "rlm_anchor_select": [_P] * 12 + [_I] * 12 + [_P, _P],
     "rlm_partner_topk": [_P] * 13 + [_I] * 13 + [_P, _P],
     "rlm_router_cache_update": [_P, _L, _P, _L] + [_P] * 12 + [_I] * 8 + [_P, _P],
     "rlm_relation_hidden_cached": [_P] * 7 + [_I] * 8 + [_P, _P],
     "rlm_relation_hidden_cache_update": [_P] * 10 + [_I] * 7 + [_P, _P],
     "rlm_relation_norm_reduce": [_P] * 6 + [_F, _P] + [_I] * 5 + [_P, _P],
+    "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
 }
 
 
@@ -96,6 +97,21 @@ def same_dtype(name: str, *tensors: torch.Tensor) -> int:
     if any(t.dtype != first for t in tensors):
         raise ValueError(f"{name} tensors must share one dtype, got {[t.dtype for t in tensors]}")
     return code(tensors[0])
+
+
+def require_cuda_rows(**tensors: torch.Tensor) -> torch.device:
+    """2-D CUDA tensors whose rows are dense (unit inner stride); the row stride is free."""
+    device = None
+    for name, t in tensors.items():
+        if not t.is_cuda:
+            raise NotImplementedError(
+                f"{name} is on {t.device}: relation_lm operators run on CUDA devices only")
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be 2-D with unit inner stride")
+        if device is not None and t.device != device:
+            raise ValueError(f"{name} is on {t.device}, expected {device}")
+        device = t.device
+    return device
 
 
 def require_cuda_contiguous(**tensors: torch.Tensor) -> torch.device:

@@ -19,10 +19,12 @@ def _select(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, a
             anchor_gamma, anchor_bias, partner_base, partner_anchor_cache, partner_keys,
             partner_block_mean, partner_block_std, partner_gamma, partner_bias, position,
             row_batch, row_position, local_window, top_blocks, k_out, strict_valid):
+    _abi.require_cuda_rows(anchor_query=anchor_query, anchor_router_query=anchor_router_query,
+                           partner_base=partner_base)
     device = _abi.require_cuda_contiguous(
-        anchor_query=anchor_query, anchor_keys=anchor_keys, anchor_router_query=anchor_router_query,
+        anchor_keys=anchor_keys,
         anchor_block_mean=anchor_block_mean, anchor_block_std=anchor_block_std,
-        anchor_gamma=anchor_gamma, anchor_bias=anchor_bias, partner_base=partner_base,
+        anchor_gamma=anchor_gamma, anchor_bias=anchor_bias,
         partner_anchor_cache=partner_anchor_cache, partner_keys=partner_keys,
         partner_block_mean=partner_block_mean, partner_block_std=partner_block_std,
         partner_gamma=partner_gamma, partner_bias=partner_bias, row_batch=row_batch,
@@ -53,6 +55,7 @@ def _select(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, a
             _abi.ptr(partner_gamma), _abi.ptr(partner_bias), _abi.ptr(position),
             _abi.ptr(row_batch), _abi.ptr(row_position), _abi.ptr(out_anchor),
             _abi.ptr(out_anchor_score), _abi.ptr(out_partner), _abi.ptr(out_partner_score),
+            anchor_query.stride(0), anchor_router_query.stride(0), partner_base.stride(0),
             rows, n_seq, max_t, n_blocks, anchor_bias.size(1), int(local_window), int(top_blocks),
             int(k_out), int(bool(strict_valid)), query_dtype, key_dtype, stats_dtype, param_dtype,
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))

@@ -73,3 +73,67 @@ def _(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache, anchor_conv_
       partner_conv_cache, anchor_mean, anchor_std, partner_mean, partner_std,
       anchor_conv_weight, partner_conv_weight, position, block_size):
     return anchor_raw.new_empty((anchor_raw.size(0), 2, anchor_raw.size(1)), dtype=torch.float32)
+
+
+_APPEND_MUTATED = ("anchor_keys", "partner_keys", "operand_cache", "partner_anchor_cache") + _MUTATED
+
+
+@torch.library.custom_op("relation_lm::sparse_cache_append", mutates_args=_APPEND_MUTATED,
+                         device_types="cuda")
+def sparse_cache_append(
+    packed: Tensor,
+    anchor_keys: Tensor,
+    partner_keys: Tensor,
+    operand_cache: Tensor,
+    partner_anchor_cache: Tensor,
+    anchor_raw_cache: Tensor,
+    partner_raw_cache: Tensor,
+    anchor_conv_cache: Tensor,
+    partner_conv_cache: Tensor,
+    anchor_mean: Tensor,
+    anchor_std: Tensor,
+    partner_mean: Tensor,
+    partner_std: Tensor,
+    anchor_conv_weight: Tensor,
+    partner_conv_weight: Tensor,
+    position: Tensor,
+    block_size: int,
+) -> None:
+    """All layers of a stack at once: write the packed projection's token features into row
+    ``position`` of their caches and update both router streams (extension of
+    ``router_cache_update``; every cache carries a leading layer dimension and ``packed`` is
+    ``[B, layers * (384 + R)]`` in the packed column order)."""
+    device = _abi.require_cuda_contiguous(
+        anchor_keys=anchor_keys, partner_keys=partner_keys, operand_cache=operand_cache,
+        partner_anchor_cache=partner_anchor_cache, anchor_raw_cache=anchor_raw_cache,
+        partner_raw_cache=partner_raw_cache, anchor_conv_cache=anchor_conv_cache,
+        partner_conv_cache=partner_conv_cache, anchor_mean=anchor_mean, anchor_std=anchor_std,
+        partner_mean=partner_mean, partner_std=partner_std, anchor_conv_weight=anchor_conv_weight,
+        partner_conv_weight=partner_conv_weight)
+    _abi.require_cuda_rows(packed=packed)
+    _abi.require_position(position, device)
+    layers, batch, max_t, rdim = operand_cache.shape
+    if packed.shape != (batch, layers * (384 + rdim)) or anchor_keys.shape != (layers, batch, max_t, 64) \
+            or partner_anchor_cache.shape != (layers, batch, max_t, 128) \
+            or anchor_raw_cache.shape != (layers, batch, max_t, 64) or anchor_mean.size(0) != layers:
+        raise ValueError("caches must be [layers, B, T, width] and packed [B, layers * (384 + R)]")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_sparse_cache_append(
+            _abi.ptr(packed), packed.stride(0), rdim, _abi.ptr(anchor_keys), _abi.ptr(partner_keys),
+            _abi.ptr(operand_cache), _abi.ptr(partner_anchor_cache), _abi.ptr(anchor_raw_cache),
+            _abi.ptr(partner_raw_cache), _abi.ptr(anchor_conv_cache), _abi.ptr(partner_conv_cache),
+            _abi.ptr(anchor_mean), _abi.ptr(anchor_std), _abi.ptr(partner_mean), _abi.ptr(partner_std),
+            _abi.ptr(anchor_conv_weight), _abi.ptr(partner_conv_weight), _abi.ptr(position), None,
+            layers, batch, max_t, anchor_mean.size(2), int(block_size), _abi.code(packed),
+            _abi.same_dtype("cache", anchor_keys, partner_keys, operand_cache, partner_anchor_cache,
+                            anchor_raw_cache, partner_raw_cache, anchor_conv_cache, partner_conv_cache),
+            _abi.same_dtype("block statistics", anchor_mean, anchor_std, partner_mean, partner_std),
+            _abi.same_dtype("conv weight", anchor_conv_weight, partner_conv_weight),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@sparse_cache_append.register_fake
+def _(packed, anchor_keys, partner_keys, operand_cache, partner_anchor_cache, anchor_raw_cache,
+      partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std,
+      partner_mean, partner_std, anchor_conv_weight, partner_conv_weight, position, block_size):
+    return None

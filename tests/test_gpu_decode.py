@@ -1,0 +1,97 @@
+"""The stateful decode step on the GPU vs its CPU port (oracle kernels + fp32 matmuls).
+
+fp32 model: selected indices must be identical at every layer and position and logits agree
+to 2e-3 (the two paths differ only in GEMM accumulation order).  bf16 model: GEMM outputs are
+rounded to bf16 on both sides, so rare near-tie selections may differ; reduced states must
+stay within 1e-2 relative where the selections agree.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from gpu_util import assert_status_clear
+
+pytestmark = pytest.mark.gpu
+
+
+def _small_model(seed=3, **kw):
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+
+    cfg = RoutedRelationConfig(vocab_size=500, boundary_vocab_size=16, d_model=128, layers=3,
+                               max_context=96, block_size=8, local_window=16, top_blocks=2, **kw)
+    return RoutedRelationLM(cfg, seed=seed)
+
+
+@pytest.mark.parametrize("strict", [False, True])
+def test_fp32_decode_matches_cpu_port(strict):
+    from oracle.decode_port import OracleDecoder
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(strict_valid=strict)
+    B, steps = 3, 96
+    gpu = StatefulDecoder(model, B, "cuda", torch.float32)
+    cpu = OracleDecoder(model, B, torch.float32)
+    g = torch.Generator().manual_seed(11)
+    tokens = torch.randint(0, 500, (B, steps), generator=g)
+    bounds = torch.randint(0, 16, (B, steps), generator=g)
+    for t in range(steps):
+        tl, bl = gpu.step(tokens[:, t].cuda(), bounds[:, t].cuda(), keep_selection=True)
+        ctl, cbl = cpu.step(tokens[:, t], bounds[:, t])
+        for layer, ((ga, gp), (ca, cp)) in enumerate(zip(gpu.last_selection, cpu.last_selection)):
+            assert torch.equal(ga.cpu(), ca), (t, layer)
+            assert torch.equal(gp.cpu(), cp), (t, layer)
+        assert torch.allclose(tl.cpu(), ctl, atol=2e-3, rtol=1e-4), (t, (tl.cpu() - ctl).abs().max())
+        assert torch.allclose(bl.cpu(), cbl, atol=2e-3, rtol=1e-4)
+    for name in ("anchor_keys", "partner_keys", "operand_cache", "partner_anchor_cache", "expanded_cache"):
+        assert torch.allclose(getattr(gpu, name).cpu(), getattr(cpu, name), atol=2e-5, rtol=1e-5), name
+    for mine, theirs in zip(gpu.router_caches + gpu.router_stats, cpu.router_caches + cpu.router_stats):
+        assert torch.allclose(mine.cpu(), theirs, atol=2e-5, rtol=1e-5)
+    assert_status_clear()
+
+
+def test_graph_replay_equals_eager_steps():
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=5)
+    B, steps = 2, 40
+    g = torch.Generator().manual_seed(12)
+    tokens = torch.randint(0, 500, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, 16, (B, steps), generator=g).cuda()
+    eager = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    graphed = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    graphed.capture()
+    for t in range(steps):
+        tl, _ = eager.step(tokens[:, t], bounds[:, t])
+        graphed.static_tokens.copy_(tokens[:, t])
+        graphed.static_boundaries.copy_(bounds[:, t])
+        graphed.replay()
+        assert torch.equal(tl, graphed.static_token_logits), t
+    assert int(graphed.position.item()) == steps
+    assert torch.equal(eager.expanded_cache, graphed.expanded_cache)
+    assert_status_clear()
+
+
+def test_bf16_decode_tracks_cpu_port():
+    from oracle.decode_port import OracleDecoder
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=9)
+    B, steps = 4, 64
+    gpu = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    cpu = OracleDecoder(model, B, torch.bfloat16)
+    g = torch.Generator().manual_seed(13)
+    tokens = torch.randint(0, 500, (B, steps), generator=g)
+    bounds = torch.randint(0, 16, (B, steps), generator=g)
+    same = total = 0
+    for t in range(steps):
+        tl, _ = gpu.step(tokens[:, t].cuda(), bounds[:, t].cuda(), keep_selection=True)
+        ctl, _ = cpu.step(tokens[:, t], bounds[:, t])
+        (ga, gp), (ca, cp) = gpu.last_selection[0], cpu.last_selection[0]
+        same += int((ga.cpu() == ca).sum()) + int((gp.cpu() == cp).sum())
+        total += ga.numel() + gp.numel()
+        assert torch.isfinite(tl).all()
+        cos = torch.nn.functional.cosine_similarity(tl.float().cpu().flatten(), ctl.flatten(), dim=0)
+        assert cos > 0.98, (t, float(cos))
+    assert same / total > 0.97, same / total
+    assert_status_clear()
