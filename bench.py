@@ -275,7 +275,7 @@ def run_ours(args) -> None:
     model, seed = make_model(args.workload)
     cfg = model.config
     B, T = args.batch, cfg.max_context
-    prefix = T - 64
+    prefix = T - 64 if args.prefix is None else args.prefix
     dec = StatefulDecoder(model, B, device, torch.bfloat16)
     tokens = zipf_tokens(B, T, cfg.vocab_size, seed + rank).to(device)
     bounds = torch.randint(0, cfg.boundary_vocab_size, (B, T),
@@ -416,6 +416,59 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_kernel_case(args) -> None:
+    """A handful of eager launches of one kernel on caches of several layers (hundreds of MB,
+    so consecutive launches do not hit L2), at the d_model-768 / ctx-2048 / block-64 decode shape."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached, relation_norm_reduce
+    from relation_lm.kernels.relation_select import relation_select_packed
+    from relation_lm.kernels.router_cache import router_cache_update
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    B, T, bs, L, TOP, K, H, R, d = args.rows, 2048, 64, 128, 2, 8, 3072, 128, 768
+    nb, sets = T // bs, 4
+    rn = lambda *s: torch.randn(*s, device=dev).bfloat16()  # noqa: E731
+    pos = torch.tensor(T - 1, device=dev)
+    events = []
+    for i in range(sets + 2):
+        if args.kernel_case == "select":
+            if i == 0:
+                S = [(rn(B, T, 64), rn(B, T, 64), rn(B, T, 128), rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs(),
+                      rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs()) for _ in range(sets)]
+                q, g, bias = rn(B, 256), torch.randn(4, device=dev), torch.randn(4, 16, device=dev)
+            ak, pk, pac, am, as_, pm, ps = S[i % sets]
+            fn = lambda: relation_select_packed(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:],  # noqa: E731
+                                                pac, pk, pm, ps, g, bias, pos, L, TOP, K, False)
+        elif args.kernel_case == "hidden":
+            if i == 0:
+                S = [(rn(B, T, 2 * H), rn(B, T, R)) for _ in range(2)]
+                wm = rn(H, R) * 0.02
+                ai = torch.randint(0, T, (B,), device=dev, dtype=torch.int32)
+                pi = torch.randint(0, T, (B, K), device=dev, dtype=torch.int32)
+            ex, op = S[i % 2]
+            fn = lambda: relation_hidden_cached(ex, op, ai, pi, wm)  # noqa: E731
+        elif args.kernel_case == "norm":
+            if i == 0:
+                S = [rn(B, K, d) for _ in range(sets)]
+                sc, gm, bt = torch.randn(B, K, device=dev), torch.ones(d, device=dev), torch.zeros(d, device=dev)
+            raw = S[i % sets]
+            fn = lambda: relation_norm_reduce(raw, sc, gm, bt, pos, 1e-5)  # noqa: E731
+        else:
+            if i == 0:
+                S = [([rn(B, T, 64) for _ in range(4)], [rn(B, nb, 4, 16) for _ in range(4)]) for _ in range(sets)]
+                packed, wc = rn(B, 512), torch.randn(64, 3, device=dev) * 0.1
+            caches, stats = S[i % sets]
+            fn = lambda: router_cache_update(packed[:, 384:448], packed[:, 448:512], *caches, *stats, wc, wc, pos, bs)  # noqa: E731
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        events.append((s, e))
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_case": args.kernel_case, "rows": B,
+                      "us": [round(s.elapsed_time(e) * 1e3, 2) for s, e in events]}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -424,7 +477,16 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=("cfg2", "cfg5"), default="cfg2")
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
+    parser.add_argument("--prefix", type=int, default=None,
+                        help="prefix length (default: context - 64); shorter only for profiling runs")
+    parser.add_argument("--kernel-case", choices=("select", "hidden", "norm", "router"), default=None,
+                        help="launch one library kernel a few times at --rows rows of the 12-layer "
+                             "decode shape and exit (for profiler captures)")
+    parser.add_argument("--rows", type=int, default=256)
     args = parser.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args)
+        return
     if args.batch is None:
         args.batch = 8 if args.workload == "cfg2" else 256 // max(1, args.gpus)
     args.warmup = max(args.warmup, 3)
