@@ -33,8 +33,7 @@
  *   head dot      (head_dim 16) segment(2h) + segment(2h+1).
  *   head score    ((mdot + softplus(gamma_h) * sdot) * 0.25) + bias[h][bucket],
  *                 each operation rounded separately.
- *   block score   acc = s_0; for h = 1..3: m = max(acc, s_h);
- *                 acc = m + log(exp(acc - m) + exp(s_h - m)).
+ *   block score   m = max_h s_h; m + log((e_0 + e_1) + (e_2 + e_3)), e_h = exp(s_h - m).
  *
  * All array arguments are fp32 (callers up-cast bf16/fp16 caches exactly, as
  * the kernels do on load) and row-major contiguous.
@@ -137,7 +136,7 @@ static void block_scores(const float* mean, const float* std, const float* rq,
         int bk = bucket_of(t, end, buckets);
         const float* m = mean + (size_t)n * ORC_D;
         const float* s = std + (size_t)n * ORC_D;
-        float acc = 0.0f;
+        float sh[ORC_HEADS];
         for (int h = 0; h < ORC_HEADS; ++h) {
             int o = h * ORC_HEAD_D;
             float md = seg8(m + o, rq + o) + seg8(m + o + 8, rq + o + 8);
@@ -145,16 +144,15 @@ static void block_scores(const float* mean, const float* std, const float* rq,
             float t1 = sp[h] * sd;
             float t2 = md + t1;
             float t3 = t2 * 0.25f;
-            float sh = t3 + bias[h * buckets + bk];
-            if (h == 0) {
-                acc = sh;
-            } else {
-                float mx = fmaxf(acc, sh);
-                float ea = orc_expf(acc - mx);
-                float eb = orc_expf(sh - mx);
-                acc = mx + orc_logf(ea + eb);
-            }
+            sh[h] = t3 + bias[h * buckets + bk];
         }
+        /* log-sum-exp over the heads in the max-shifted form of torch.logsumexp
+         * (routing/block_router.py:99; the Triton kernels fold the heads pairwise,
+         * relation_select.py:97-103, which agrees to rounding). */
+        float mx = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+        float e0 = orc_expf(sh[0] - mx), e1 = orc_expf(sh[1] - mx);
+        float e2 = orc_expf(sh[2] - mx), e3 = orc_expf(sh[3] - mx);
+        float acc = mx + orc_logf((e0 + e1) + (e2 + e3));
         out[n] = acc;
     }
 }

@@ -8,12 +8,25 @@
 #include "rlm_common.cuh"
 
 namespace rlm {
+#ifdef RLM_TRACE
+__device__ long long g_trace_reduce[64 * 32];
+#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x + blockIdx.y * gridDim.x < 64) g_trace_reduce[(blockIdx.x + blockIdx.y * gridDim.x) * 32 + (i)] = clock64(); } while (0)
+#else
+#define RLM_PROBE(i) do { } while (0)
+#endif
 namespace {
 
 
 // ------------------------------------------------------------------ hidden
+//
+// Tile = kRB sequences (kRB*K relation rows) x kHT hidden columns per CTA pass.  The weight
+// tiles of the CTA's hidden columns are staged once (fp32, padded rows); a CTA then walks
+// its share of sequence groups.  Per group: the gathered operand rows are multiplied into
+// the product matrix in shared memory, and every thread accumulates an NR x 2 register tile
+// (NR relation rows, two hidden columns) over the relation dimension with float4 reads.
 
-constexpr int kHT = 64;            // hidden columns per CTA
+constexpr int kHT = 32;            // hidden columns per CTA
+constexpr int kRB = 4;             // sequences per tile
 constexpr int kHiddenThreads = 128;
 constexpr int kMaxK = 16;          // partner slots per row
 constexpr int kPad = 4;            // row padding (floats) of staged weight tiles: conflict-free float4 reads
@@ -39,7 +52,7 @@ __device__ __forceinline__ void stage_weight_tile(const void* weight, int dtype,
                                                   int rdim, float* dst) {
     const int segs = rdim / 8;
     for (int i = threadIdx.x; i < kHT * segs; i += kHiddenThreads) {
-        int r = i / segs, sgm = i % segs;
+        int r = i / segs, sgm = i - r * segs;
         float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (h0 + r < hdim) {
             const char* row = static_cast<const char*>(weight) +
@@ -56,21 +69,32 @@ __device__ __forceinline__ float gelu_erf(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
 
-template <bool kUpdate>
+__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc);
+    return fmaf(a.w, b.w, acc);
+}
+
+// NR = relation rows per thread: the tile's kRB*K rows are dealt to 8 thread rows.
+template <bool kUpdate, int NR>
 __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const HiddenArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x;
     const int R = a.rdim, H = a.hdim, K = a.k_out;
     const int stride = R + kPad;
+    const int tile_rows = kRB * K;
     float* wm = reinterpret_cast<float*>(smem);
     float* wa = wm + kHT * stride;                        // only when kUpdate
     float* wp = wa + (kUpdate ? kHT * stride : 0);
-    float* prod = wp + (kUpdate ? kHT * stride : 0);      // [K][R]
-    float* cur = prod + kMaxK * R;                        // [R] current operand (kUpdate)
-    float* fresh = cur + R;                               // [2][kHT] (kUpdate)
-    __shared__ int idx[kMaxK + 1];
+    float* prod = wp + (kUpdate ? kHT * stride : 0);      // [8 * NR][R]
+    float* cur = prod + 8 * NR * R;                       // [kRB][R] current operands (kUpdate)
+    float* fresh = cur + (kUpdate ? kRB * R : 0);         // [kRB][2][kHT] (kUpdate)
+    __shared__ int idx[kRB][kMaxK + 1];
+    __shared__ int seq[kRB];
 
-    const int h0 = blockIdx.y * kHT;
+    RLM_PROBE(0);
+    const int h0 = blockIdx.x * kHT;
     int t = -1;
     if (kUpdate) {
         t = static_cast<int>(*a.position);
@@ -84,90 +108,164 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         stage_weight_tile(a.anchor_weight, a.weight_dtype, h0, H, R, wa);
         stage_weight_tile(a.partner_weight, a.weight_dtype, h0, H, R, wp);
     }
-    const int h = tid % kHT, g = tid / kHT;        // two thread groups split the partner slots
-    const int per = (K + 1) / 2;
-    const int k_lo = g * per, k_hi = min(K, k_lo + per);
-    const bool h_ok = h0 + h < H;
+    RLM_PROBE(1);
+    const int tx = tid & 15, ty = tid >> 4;              // hidden columns {tx, tx+16}; rows {ty + 8 i}
     const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
+    const int segs = R / 8;
+    const int groups = (a.n_rows + kRB - 1) / kRB;
 
-    for (int row = blockIdx.x; row < a.n_rows; row += gridDim.x) {
-        __syncthreads();   // previous row's reads of prod/idx/fresh are done; weights are staged
-        const int b = a.row_batch ? a.row_batch[row] : row;
-        if (b < 0 || b >= a.n_seq) {
-            if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
-            continue;
-        }
-        if (tid <= K) {
-            int v = tid == 0 ? a.anchor_index[row] : a.partner_index[static_cast<size_t>(row) * K + tid - 1];
-            idx[tid] = min(max(v, 0), a.max_t - 1);
-        }
-        __syncthreads();
-        const char* operand = static_cast<const char*>(a.operand_cache) + static_cast<size_t>(b) * a.max_t * R * cs;
-        for (int i = tid; i < K * R; i += kHiddenThreads) {
-            int k = i / R, r = i % R;
-            float oa = load_scalar(operand, static_cast<int64_t>(idx[0]) * R + r, a.cache_dtype);
-            float op = load_scalar(operand, static_cast<int64_t>(idx[k + 1]) * R + r, a.cache_dtype);
-            prod[k * R + r] = op * oa;
-        }
-        if (kUpdate)
-            for (int r = tid; r < R; r += kHiddenThreads)
-                cur[r] = load_scalar(operand, static_cast<int64_t>(t) * R + r, a.cache_dtype);
-        __syncthreads();
-
-        char* expanded = static_cast<char*>(a.expanded_cache) + static_cast<size_t>(b) * a.max_t * 2 * H * cs;
-        if (kUpdate) {
-            // group 0: anchor half (+ bias); group 1: partner half of the current expanded row
-            const float* w = (g == 0 ? wa : wp) + h * stride;
-            float acc = 0.0f;
-            for (int r = 0; r < R; r += 4) {
-                float4 wv = *reinterpret_cast<const float4*>(w + r);
-                float4 ov = *reinterpret_cast<const float4*>(cur + r);
-                acc = fmaf(wv.x, ov.x, acc); acc = fmaf(wv.y, ov.y, acc);
-                acc = fmaf(wv.z, ov.z, acc); acc = fmaf(wv.w, ov.w, acc);
+    for (int group = blockIdx.y; group < groups; group += gridDim.y) {
+        __syncthreads();   // previous group's reads are done; weight tiles are staged
+        const int row0 = group * kRB;
+        if (tid < kRB * (K + 1)) {
+            int rb = tid / (K + 1), j = tid - rb * (K + 1), row = row0 + rb;
+            int v = 0;
+            if (row < a.n_rows)
+                v = j == 0 ? a.anchor_index[row] : a.partner_index[static_cast<size_t>(row) * K + j - 1];
+            idx[rb][j] = min(max(v, 0), a.max_t - 1);
+            if (j == 0) {
+                int b = row < a.n_rows ? (a.row_batch ? a.row_batch[row] : row) : -1;
+                if (row < a.n_rows && (b < 0 || b >= a.n_seq)) {
+                    if (a.status) atomicOr(a.status, RLM_DEV_POSITION);
+                    b = -1;
+                }
+                seq[rb] = b;
             }
-            if (g == 0 && h_ok) acc += load_scalar(a.first_bias, h0 + h, a.weight_dtype);
-            fresh[g * kHT + h] = acc;
-            if (h_ok)
-                store_scalar(expanded, static_cast<int64_t>(t) * 2 * H + g * H + h0 + h, a.cache_dtype, acc);
+        }
+        __syncthreads();
+        RLM_PROBE(2);
+        // product matrix: prod[rb*K + k][:] = operand[p_k] * operand[anchor]
+        for (int i = tid; i < 8 * NR * segs; i += kHiddenThreads) {
+            int prow = i / segs, sgm = i - prow * segs;
+            int rb = prow / K, k = prow - rb * K;
+            float4 lo = make_float4(0, 0, 0, 0), hi = lo;
+            if (prow < tile_rows && seq[rb] >= 0) {
+                const char* operand = static_cast<const char*>(a.operand_cache) +
+                                      static_cast<size_t>(seq[rb]) * a.max_t * R * cs;
+                float oa[8], op[8];
+                load8(operand + static_cast<size_t>(idx[rb][0]) * R * cs, 8 * sgm, a.cache_dtype, oa);
+                load8(operand + static_cast<size_t>(idx[rb][k + 1]) * R * cs, 8 * sgm, a.cache_dtype, op);
+                lo = make_float4(op[0] * oa[0], op[1] * oa[1], op[2] * oa[2], op[3] * oa[3]);
+                hi = make_float4(op[4] * oa[4], op[5] * oa[5], op[6] * oa[6], op[7] * oa[7]);
+            }
+            float4* d = reinterpret_cast<float4*>(prod + prow * R + 8 * sgm);
+            d[0] = lo;
+            d[1] = hi;
+        }
+        if (kUpdate) {
+            for (int i = tid; i < kRB * segs; i += kHiddenThreads) {
+                int rb = i / segs, sgm = i - rb * segs;
+                float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (seq[rb] >= 0)
+                    load8(static_cast<const char*>(a.operand_cache) +
+                              (static_cast<size_t>(seq[rb]) * a.max_t + t) * R * cs,
+                          8 * sgm, a.cache_dtype, o);
+                float4* d = reinterpret_cast<float4*>(cur + rb * R + 8 * sgm);
+                d[0] = make_float4(o[0], o[1], o[2], o[3]);
+                d[1] = make_float4(o[4], o[5], o[6], o[7]);
+            }
+        }
+        __syncthreads();
+        RLM_PROBE(3);
+
+        if (kUpdate) {
+            // current expanded rows: thread row ty -> (sequence ty/2, anchor or partner half)
+            const int rb = ty >> 1, half = ty & 1;
+            const float* w0 = (half ? wp : wa) + tx * stride;
+            const float* w1 = w0 + 16 * stride;
+            const float* c = cur + rb * R;
+            float f0 = 0.0f, f1 = 0.0f;
+            for (int r = 0; r < R; r += 4) {
+                float4 cv = *reinterpret_cast<const float4*>(c + r);
+                f0 = dot4(*reinterpret_cast<const float4*>(w0 + r), cv, f0);
+                f1 = dot4(*reinterpret_cast<const float4*>(w1 + r), cv, f1);
+            }
+            if (half == 0) {
+                if (h0 + tx < H) f0 += load_scalar(a.first_bias, h0 + tx, a.weight_dtype);
+                if (h0 + tx + 16 < H) f1 += load_scalar(a.first_bias, h0 + tx + 16, a.weight_dtype);
+            }
+            fresh[(rb * 2 + half) * kHT + tx] = f0;
+            fresh[(rb * 2 + half) * kHT + tx + 16] = f1;
+            if (seq[rb] >= 0) {
+                const int64_t base = (static_cast<int64_t>(seq[rb]) * a.max_t + t) * 2 * H + half * H + h0;
+                if (h0 + tx < H) store_scalar(a.expanded_cache, base + tx, a.cache_dtype, f0);
+                if (h0 + tx + 16 < H) store_scalar(a.expanded_cache, base + tx + 16, a.cache_dtype, f1);
+            }
             __syncthreads();
         }
-        float acc[(kMaxK + 1) / 2];
+
+        RLM_PROBE(4);
+        float acc[NR][2];
 #pragma unroll
-        for (int i = 0; i < (kMaxK + 1) / 2; ++i) acc[i] = 0.0f;
-        const float* w = wm + h * stride;
+        for (int i = 0; i < NR; ++i) acc[i][0] = acc[i][1] = 0.0f;
+        const float* w0 = wm + tx * stride;
+        const float* w1 = w0 + 16 * stride;
+        const float* p0 = prod + ty * R;
+#pragma unroll 2
         for (int r = 0; r < R; r += 4) {
-            float4 wv = *reinterpret_cast<const float4*>(w + r);
+            float4 a0 = *reinterpret_cast<const float4*>(w0 + r);
+            float4 a1 = *reinterpret_cast<const float4*>(w1 + r);
 #pragma unroll
-            for (int i = 0; i < (kMaxK + 1) / 2; ++i) {
-                if (k_lo + i < k_hi) {
-                    float4 pv = *reinterpret_cast<const float4*>(prod + (k_lo + i) * R + r);
-                    acc[i] = fmaf(wv.x, pv.x, acc[i]); acc[i] = fmaf(wv.y, pv.y, acc[i]);
-                    acc[i] = fmaf(wv.z, pv.z, acc[i]); acc[i] = fmaf(wv.w, pv.w, acc[i]);
-                }
+            for (int i = 0; i < NR; ++i) {
+                float4 pv = *reinterpret_cast<const float4*>(p0 + i * 8 * R + r);
+                acc[i][0] = dot4(a0, pv, acc[i][0]);
+                acc[i][1] = dot4(a1, pv, acc[i][1]);
             }
         }
-        if (h_ok) {
-            const int ai = idx[0];
-            float base_a = (kUpdate && ai == t) ? fresh[h]
-                                                 : load_scalar(expanded, static_cast<int64_t>(ai) * 2 * H + h0 + h, a.cache_dtype);
+        RLM_PROBE(5);
 #pragma unroll
-            for (int i = 0; i < (kMaxK + 1) / 2; ++i) {
-                int k = k_lo + i;
-                if (k < k_hi) {
-                    const int pi = idx[k + 1];
-                    float base_p = (kUpdate && pi == t) ? fresh[kHT + h]
-                                                         : load_scalar(expanded, static_cast<int64_t>(pi) * 2 * H + H + h0 + h, a.cache_dtype);
-                    float x = acc[i] + (base_a + base_p);
-                    a.out[(static_cast<size_t>(row) * K + k) * H + h0 + h] = gelu_erf(x);
-                }
+        for (int i = 0; i < NR; ++i) {
+            const int prow = ty + 8 * i;
+            if (prow >= tile_rows) continue;
+            const int rb = prow / K, k = prow - rb * K, row = row0 + rb;
+            if (row >= a.n_rows || seq[rb] < 0) continue;
+            const int64_t ebase = static_cast<int64_t>(seq[rb]) * a.max_t * 2 * H;
+            const int ai = idx[rb][0], pi = idx[rb][k + 1];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int hh = tx + 16 * j;
+                if (h0 + hh >= H) continue;
+                float base_a = (kUpdate && ai == t)
+                                   ? fresh[(rb * 2) * kHT + hh]
+                                   : load_scalar(a.expanded_cache, ebase + static_cast<int64_t>(ai) * 2 * H + h0 + hh, a.cache_dtype);
+                float base_p = (kUpdate && pi == t)
+                                   ? fresh[(rb * 2 + 1) * kHT + hh]
+                                   : load_scalar(a.expanded_cache, ebase + static_cast<int64_t>(pi) * 2 * H + H + h0 + hh, a.cache_dtype);
+                a.out[(static_cast<size_t>(row) * K + k) * H + h0 + hh] = gelu_erf(acc[i][j] + (base_a + base_p));
             }
         }
+        RLM_PROBE(6);
     }
 }
 
-int hidden_smem_bytes(bool update, int rdim) {
+int hidden_smem_bytes(bool update, int rdim, int nr) {
     int tiles = update ? 3 : 1;
-    return (tiles * kHT * (rdim + kPad) + kMaxK * rdim + rdim + 2 * kHT) * 4;
+    int floats = tiles * kHT * (rdim + kPad) + 8 * nr * rdim;
+    if (update) floats += kRB * rdim + kRB * 2 * kHT;
+    return floats * 4;
+}
+
+template <bool kUpdate, int NR>
+int launch_hidden_as(const HiddenArgs& a, void* stream) {
+    const int smem_bytes = hidden_smem_bytes(kUpdate, a.rdim, NR);
+    if (smem_bytes > kSmemDynamicLimit) {
+        set_error("relation_hidden: relation_dim too large for the staged weight tiles");
+        return RLM_ERR_SMEM;
+    }
+    auto kernel = relation_hidden_kernel<kUpdate, NR>;
+    if (smem_bytes > 48 * 1024) {
+        int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+        if (rc != RLM_OK) return rc;
+    }
+    const int tiles = (a.hdim + kHT - 1) / kHT;
+    const int groups = (a.n_rows + kRB - 1) / kRB;
+    // a few CTAs per SM; beyond that a CTA keeps its weight tiles and walks several groups
+    int gy = (148 * 6 + tiles - 1) / tiles;
+    if (gy > groups) gy = groups;
+    dim3 grid(tiles, gy);
+    kernel<<<grid, kHiddenThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    count_launch();
+    return check_launch("relation_hidden_kernel");
 }
 
 int launch_hidden(HiddenArgs& a, bool update, void* stream) {
@@ -191,32 +289,14 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         set_error("relation_hidden: unknown dtype code");
         return RLM_ERR_DTYPE;
     }
-    if (!aligned16(a.product_weight) || (update && (!aligned16(a.anchor_weight) || !aligned16(a.partner_weight)))) {
-        set_error("relation_hidden: weight matrices must be 16-byte aligned");
+    if (!aligned16(a.product_weight) || !aligned16(a.operand_cache) ||
+        (update && (!aligned16(a.anchor_weight) || !aligned16(a.partner_weight)))) {
+        set_error("relation_hidden: weight matrices and the operand cache must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
-    int smem_bytes = hidden_smem_bytes(update, a.rdim);
-    if (smem_bytes > kSmemDynamicLimit) {
-        set_error("relation_hidden: relation_dim too large for the staged weight tiles");
-        return RLM_ERR_SMEM;
-    }
-    const void* fn = update ? reinterpret_cast<const void*>(relation_hidden_kernel<true>)
-                            : reinterpret_cast<const void*>(relation_hidden_kernel<false>);
-    if (smem_bytes > 48 * 1024) {
-        int rc = allow_large_smem(fn, kSmemPerCta);
-        if (rc != RLM_OK) return rc;
-    }
-    int tiles = (a.hdim + kHT - 1) / kHT;
-    // enough CTAs to fill the machine a few times over; more rows per CTA amortise the weight tile
-    int want = (148 * 4 + tiles - 1) / tiles;
-    int gx = a.n_rows < want ? a.n_rows : want;
-    dim3 grid(gx, tiles);
-    if (update)
-        relation_hidden_kernel<true><<<grid, kHiddenThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
-    else
-        relation_hidden_kernel<false><<<grid, kHiddenThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
-    count_launch();
-    return check_launch("relation_hidden_kernel");
+    const bool wide = kRB * a.k_out > 32;      // more than 4 relation rows per thread
+    if (update) return wide ? launch_hidden_as<true, 8>(a, stream) : launch_hidden_as<true, 4>(a, stream);
+    return wide ? launch_hidden_as<false, 8>(a, stream) : launch_hidden_as<false, 4>(a, stream);
 }
 
 // ------------------------------------------------------------------ norm + reduce
@@ -243,13 +323,35 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = a.k_out, D = a.dim;
-    const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
-    int k_limit = 32 - __clz(max(t, 0) + 1);   // ceil(log2(t + 2))
-    k_limit = min(max(k_limit, 1), K);
+    const int per = (D + 31) / 32;
 
-    // softmax weights over the active slots (every warp computes them redundantly)
+    // Every load that does not depend on another is issued first: position, scores, this
+    // warp's first partner row and the affine parameters.  (raw is dense [N, K, D], so the
+    // row of an inactive slot is readable; it is simply not accumulated.)
+    const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
     float s0 = lane < K ? a.scores[static_cast<size_t>(row) * K + lane] : kNegInf;
     float s1 = lane + 32 < K ? a.scores[static_cast<size_t>(row) * K + lane + 32] : kNegInf;
+    float x[kMaxPerLane];
+    if (warp < K) {
+        const int64_t base = (static_cast<int64_t>(row) * K + warp) * D;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) {
+            int c = lane + 32 * i;
+            x[i] = (i < per && c < D) ? load_scalar(a.raw, base + c, a.raw_dtype) : 0.0f;
+        }
+    }
+    float gm[kMaxPerLane], bt[kMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        int c = lane + 32 * i;
+        bool in = i < per && c < D;
+        gm[i] = in ? load_scalar(a.weight, c, a.param_dtype) : 0.0f;
+        bt[i] = in ? load_scalar(a.bias, c, a.param_dtype) : 0.0f;
+    }
+
+    // softmax weights over the active slots (every warp computes them redundantly)
+    int k_limit = 32 - __clz(max(t, 0) + 1);   // ceil(log2(t + 2))
+    k_limit = min(max(k_limit, 1), K);
     bool a0 = lane < K && lane < k_limit && s0 > -1.0e30f;
     bool a1 = lane + 32 < K && lane + 32 < k_limit && s1 > -1.0e30f;
     float f0 = a0 ? s0 : -1.0e4f, f1 = a1 ? s1 : -1.0e4f;
@@ -260,22 +362,23 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
     float den = fmaxf(warp_sum(e0 + e1), 1.0e-9f);
     float w0 = e0 / den, w1 = e1 / den;
 
-    const int per = (D + 31) / 32;
     float y[kMaxPerLane];
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) y[i] = 0.0f;
     for (int k = warp; k < K; k += kNormWarps) {
         float wk = __shfl_sync(0xffffffffu, k < 32 ? w0 : w1, k & 31);
-        if (wk == 0.0f) continue;   // inactive slot: contributes nothing, its row is not read
-        const int64_t base = (static_cast<int64_t>(row) * K + k) * D;
-        float x[kMaxPerLane];
+        if (k != warp && wk != 0.0f) {
+            const int64_t base = (static_cast<int64_t>(row) * K + k) * D;
+#pragma unroll
+            for (int i = 0; i < kMaxPerLane; ++i) {
+                int c = lane + 32 * i;
+                x[i] = (i < per && c < D) ? load_scalar(a.raw, base + c, a.raw_dtype) : 0.0f;
+            }
+        }
+        if (wk == 0.0f) continue;   // inactive slot contributes nothing
         float sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-            int c = lane + 32 * i;
-            x[i] = (i < per && c < D) ? load_scalar(a.raw, base + c, a.raw_dtype) : 0.0f;
-            sum += x[i];
-        }
+        for (int i = 0; i < kMaxPerLane; ++i) sum += x[i];
         const float mean = warp_sum(sum) / static_cast<float>(D);
         float sq = 0.0f;
 #pragma unroll
@@ -287,14 +390,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
         }
         const float inv = rsqrtf(warp_sum(sq) / static_cast<float>(D) + a.eps);
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-            int c = lane + 32 * i;
-            if (i < per && c < D) {
-                float gm = load_scalar(a.weight, c, a.param_dtype);
-                float bt = load_scalar(a.bias, c, a.param_dtype);
-                y[i] = fmaf(wk, fmaf(x[i] * inv, gm, bt), y[i]);
-            }
-        }
+        for (int i = 0; i < kMaxPerLane; ++i) y[i] = fmaf(wk, fmaf(x[i] * inv, gm[i], bt[i]), y[i]);
     }
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
@@ -372,3 +468,9 @@ extern "C" int rlm_relation_norm_reduce(
     count_launch();
     return check_launch("relation_norm_reduce_kernel");
 }
+
+#ifdef RLM_TRACE
+extern "C" int rlm_debug_trace_reduce(long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_reduce, sizeof(long long) * 64 * 32));
+}
+#endif

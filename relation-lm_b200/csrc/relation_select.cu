@@ -15,14 +15,35 @@
 #include "rlm_common.cuh"
 
 namespace rlm {
+#ifdef RLM_TRACE
+// Phase timestamps for working builds (never compiled into the shipped library).
+__device__ long long g_trace[64 * 32];
+#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x < 64) g_trace[blockIdx.x * 32 + (i)] = clock64(); } while (0)
+#else
+#define RLM_PROBE(i) do { } while (0)
+#endif
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kD = 64;        // exact-score width == router heads * head width
-constexpr int kHeads = 4;
 
 enum Mode { kPacked = 0, kAnchorOnly = 1, kPartnerOnly = 2 };
+
+// Shared-memory plan (byte offsets from the dynamic shared base).
+struct Plan {
+    int a_mean, a_std, p_mean, p_std;   // [NB,64] stats elements
+    int a_local, p_local;               // [L,64] key elements
+    int remote;                         // [TOP*BS,64] key elements (anchor phase, then partner phase)
+    int pa_row;                         // [128] key elements
+    int queries;                        // f32: aq[64] arq[64] pq[64] prq[64]
+    int params;                         // f32: softplus(gamma) a[4] p[4], bias a[4*buckets] p[4*buckets]
+    int block_scores;                   // f32 [NB]
+    int cand;                           // f32 [L + TOP*BS]
+    int sel;                            // int [3*TOP]: block, usable, valid row count
+    int bars;                           // 5 mbarriers
+    int total;
+};
 
 struct SelectArgs {
     const void* anchor_query;
@@ -54,21 +75,7 @@ struct SelectArgs {
     int local_window, top_blocks, k_out, strict_valid;
     int query_dtype, key_dtype, stats_dtype, param_dtype;
     int mode;
-};
-
-// Shared-memory plan (byte offsets from the dynamic shared base).
-struct Plan {
-    int a_mean, a_std, p_mean, p_std;   // [NB,64] stats elements
-    int a_local, p_local;               // [L,64] key elements
-    int remote;                         // [TOP*BS,64] key elements (anchor phase, then partner phase)
-    int pa_row;                         // [128] key elements
-    int queries;                        // f32: aq[64] arq[64] pq[64] prq[64]
-    int params;                         // f32: softplus(gamma) a[4] p[4], bias a[4*buckets] p[4*buckets]
-    int block_scores;                   // f32 [NB]
-    int cand;                           // f32 [L + TOP*BS]
-    int sel;                            // int [3*TOP]: block, usable, valid row count
-    int bars;                           // 5 mbarriers
-    int total;
+    Plan plan;
 };
 
 __host__ __device__ inline int align16(int x) { return (x + 15) & ~15; }
@@ -89,8 +96,8 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     p.remote = off; off += top * bs * kD * key_size;
     p.pa_row = off; off += 2 * kD * key_size;
     p.queries = off; off += 4 * kD * 4;
-    p.params = off; off += align16((8 + 8 * buckets) * 4);
-    p.block_scores = off; off += align16(nb * 4);
+    p.params = off; off += align16(8 * buckets * 4);
+    p.block_scores = off; off += align16(((nb + 3) & ~3) * 4);
     p.cand = off; off += align16((local + top * bs) * 4);
     p.sel = off; off += align16(3 * (top > 0 ? top : 1) * 4);
     p.bars = off; off += 5 * 8;
@@ -98,51 +105,85 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     return p;
 }
 
-// Scores `n_rows` staged key rows against the query held in shared memory
-// (f32 [64]).  Row r of `rows` is candidate slot `slot0 + r`; rows at or past
-// `n_valid`, and the row whose position equals `exclude`, score -inf.
-__device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
-                                           int n_valid_first, int n_valid_end, int pos0,
-                                           int exclude, const float* query, float* cand,
-                                           int slot0) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Scores staged key rows against the query held in shared memory (f32 [64]) with the
+// `nw` warps of a group (this warp is number `wi`).  Two layouts:
+//   local window (sel == nullptr): row r is position pos0 + r, valid from `first_valid` on;
+//   remote blocks (sel != nullptr): row r belongs to the block of rank r / bs at offset
+//     o = r % bs, position sel[3 rank] * bs + o, valid while o < sel[3 rank + 2].
+// The row at position `exclude` scores -inf.  With `cand` the scores go to candidate slots
+// slot0 + r; in every case the warp's best (score, lowest position on ties) is folded into
+// (best_key, best_pos), identical in all lanes.
+__device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
+                                        const int* sel, int bs, int first_valid, int pos0,
+                                        int exclude, const float* query, float* cand, int slot0,
+                                        int wi, int nw, uint32_t& best_key, int& best_pos) {
+    const int lane = threadIdx.x & 31;
     const int j = lane & 7, sub = lane >> 3;
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
     float q[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) q[i] = query[8 * j + i];
-    for (int base = warp * 4; base < n_rows; base += 4 * kWarps) {
-        int r = base + sub;
-        bool valid = r < n_rows && r >= n_valid_first && r < n_valid_end && (pos0 + r) != exclude;
-        float acc = 0.0f;
-        if (valid) {
-            float k[8];
-            load8(rows + static_cast<size_t>(r) * row_bytes, 8 * j, key_dtype, k);
-            acc = seg8(k, q);
+    uint32_t my_key = 0;
+    int my_pos = 0x7fffffff;
+    // two independent row groups per iteration keep two fma chains in flight
+    for (int base = wi * 8; base < n_rows; base += 8 * nw) {
+        int r[2] = {base + sub, base + 4 + sub};
+        int pos[2];
+        bool valid[2];
+        float acc[2] = {0.0f, 0.0f};
+        float k[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (sel) {
+                int rank = r[u] / bs, o = r[u] - rank * bs;
+                bool in = r[u] < n_rows;
+                pos[u] = in ? sel[3 * rank] * bs + o : -1;
+                valid[u] = in && o < sel[3 * rank + 2];
+            } else {
+                pos[u] = pos0 + r[u];
+                valid[u] = r[u] < n_rows && r[u] >= first_valid;
+            }
+            valid[u] = valid[u] && pos[u] != exclude;
+            if (valid[u]) load8(rows + static_cast<size_t>(r[u]) * row_bytes, 8 * j, key_dtype, k[u]);
         }
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
-        if (j == 0 && r < n_rows) cand[slot0 + r] = valid ? __fmul_rn(acc, 0.125f) : kNegInf;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (valid[u]) acc[u] = seg8(k[u], q);
+#pragma unroll
+        for (int sft = 1; sft <= 4; sft <<= 1) {
+            acc[0] = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], sft));
+            acc[1] = __fadd_rn(acc[1], __shfl_xor_sync(0xffffffffu, acc[1], sft));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            float sc = valid[u] ? __fmul_rn(acc[u], 0.125f) : kNegInf;
+            if (cand && j == 0 && r[u] < n_rows) cand[slot0 + r[u]] = sc;
+            uint32_t key = float_key(sc);
+            if (valid[u] && (key > my_key || my_pos == 0x7fffffff)) { my_key = key; my_pos = pos[u]; }
+        }
+    }
+    warp_argmax_key(my_key, my_pos);
+    if (my_pos != 0x7fffffff &&
+        (my_key > best_key || best_pos == 0x7fffffff || (my_key == best_key && my_pos < best_pos))) {
+        best_key = my_key;
+        best_pos = my_pos;
     }
 }
 
-// Block scores of the first `n_complete` blocks (the others are not eligible).
-__device__ __forceinline__ void score_blocks(const unsigned char* mean, const unsigned char* stdv,
-                                             int stats_dtype, int nb, int n_complete, int bs,
-                                             int t, int ls, int strict, int buckets,
-                                             const float* rq, const float* softplus,
-                                             const float* bias, float* out) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Block scores of the first `n_complete` blocks with the `nw` warps of a group; the other
+// entries of `out` (up to the next multiple of four) are set to -inf.
+__device__ __noinline__ void score_blocks(const unsigned char* mean, const unsigned char* stdv,
+                                          int stats_dtype, int nb, int n_complete, int bs, int t,
+                                          int ls, int strict, int buckets, const float* rq,
+                                          float sp, const float* bias, float* out, int wi, int nw) {
+    const int lane = threadIdx.x & 31;
     const int j = lane & 7, sub = lane >> 3, head = j >> 1;
     const int row_bytes = kD * (stats_dtype == RLM_F32 ? 4 : 2);
     float q[8], aq[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { q[i] = rq[8 * j + i]; aq[i] = fabsf(q[i]); }
-    const float sp = softplus[head];
-    for (int n = threadIdx.x; n < nb; n += kThreads)
-        if (n >= n_complete) out[n] = kNegInf;
-    for (int base = warp * 4; base < n_complete; base += 4 * kWarps) {
+    for (int n = n_complete + wi * 32 + lane; n < ((nb + 3) & ~3); n += 32 * nw) out[n] = kNegInf;
+    for (int base = wi * 4; base < n_complete; base += 4 * nw) {
         int n = base + sub;
         bool live = n < n_complete;
         float md = 0.0f, sd = 0.0f;
@@ -162,15 +203,14 @@ __device__ __forceinline__ void score_blocks(const unsigned char* mean, const un
         if (bucket > buckets - 1) bucket = buckets - 1;
         float sh = __fadd_rn(__fmul_rn(__fadd_rn(md, __fmul_rn(sp, sd)), 0.25f),
                              live ? bias[head * buckets + bucket] : 0.0f);
-        const int g = lane & ~7;
-        float acc = __shfl_sync(0xffffffffu, sh, g);
-#pragma unroll
-        for (int h = 1; h < kHeads; ++h) {
-            float s = __shfl_sync(0xffffffffu, sh, g + 2 * h);
-            float mx = fmaxf(acc, s);
-            acc = __fadd_rn(mx, canon_log(__fadd_rn(canon_exp(__fsub_rn(acc, mx)),
-                                                    canon_exp(__fsub_rn(s, mx)))));
-        }
+        // log-sum-exp over the four heads, max-shifted: every lane evaluates the exponential
+        // of its own head, the sum is (e0 + e1) + (e2 + e3) through two xor shuffles.
+        float mx = fmaxf(sh, __shfl_xor_sync(0xffffffffu, sh, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        float e = canon_exp(__fsub_rn(sh, mx));
+        e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, 2));
+        e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, 4));
+        float acc = __fadd_rn(mx, canon_log(e));
         if (j == 0 && live) {
             bool eligible = !strict || end < ls;
             out[n] = eligible ? acc : kNegInf;
@@ -178,52 +218,98 @@ __device__ __forceinline__ void score_blocks(const unsigned char* mean, const un
     }
 }
 
-// Warp 0: pick `top` blocks by descending score (ties: lowest index), record
-// (block, usable, number of rows before the local window) per rank.
-__device__ __forceinline__ void pick_blocks(float* scores, int nb, int top, int bs, int ls,
-                                            int* sel) {
+// Warp 0: rank the block scores by counting (descending score, ties to the lowest index)
+// and record (block, usable, rows before the local window) for ranks below `top`.  Ranks of
+// blocks that are not usable (-inf) never matter: they contribute no candidates.  `scores`
+// is padded with -inf to a multiple of four.
+__device__ __noinline__ void pick_blocks(const float* scores, int nb, int top, int bs, int ls,
+                                         int* sel) {
     const int lane = threadIdx.x & 31;
-    for (int r = 0; r < top; ++r) {
-        float bv = kNegInf;
-        int bi = 0x7fffffff;
-        for (int n = lane; n < nb; n += 32) {
-            float v = scores[n];
-            if (v > bv || bi == 0x7fffffff) { bv = v; bi = n; }
+    for (int r = lane; r < top; r += 32) { sel[3 * r] = 0; sel[3 * r + 1] = 0; sel[3 * r + 2] = 0; }
+    __syncwarp();
+    const float4* s4 = reinterpret_cast<const float4*>(scores);
+    const int groups = (nb + 3) >> 2;
+    for (int n = lane; n < nb; n += 32) {
+        const float mine = scores[n];
+        if (!(mine > -1.0e30f)) continue;
+        int rank = 0;
+        for (int g = 0; g < groups; ++g) {
+            float4 o = s4[g];
+            const int m = g << 2;
+            rank += (o.x > mine || (o.x == mine && m < n)) + (o.y > mine || (o.y == mine && m + 1 < n)) +
+                    (o.z > mine || (o.z == mine && m + 2 < n)) + (o.w > mine || (o.w == mine && m + 3 < n));
         }
-        warp_argmax_low(bv, bi);
-        if (bi == 0x7fffffff) bi = 0;
-        if (lane == 0) {
-            int usable = bv > -1.0e30f;
-            int rows = ls - bi * bs;
+        if (rank < top) {
+            int rows = ls - n * bs;
             rows = rows < 0 ? 0 : (rows > bs ? bs : rows);
-            sel[3 * r] = bi;
-            sel[3 * r + 1] = usable;
-            sel[3 * r + 2] = usable ? rows : 0;
-            scores[bi] = kNegInf;
+            sel[3 * rank] = n;
+            sel[3 * rank + 1] = 1;
+            sel[3 * rank + 2] = rows;
         }
-        __syncwarp();
     }
+    __syncwarp();
+}
+
+__device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned char* dst,
+                                             const int* sel, int top, int bs, size_t key_row,
+                                             size_t seq_keys, uint32_t bar) {
+    uint32_t total = 0;
+    for (int r = 0; r < top; ++r) total += static_cast<uint32_t>(sel[3 * r + 2] * key_row);
+    mbar_expect_tx(bar, total);
+    for (int r = 0; r < top; ++r)
+        if (sel[3 * r + 2] > 0)
+            bulk_g2s(smem_u32(dst) + static_cast<uint32_t>(r * bs * key_row),
+                     keys + seq_keys + static_cast<size_t>(sel[3 * r]) * bs * key_row,
+                     static_cast<uint32_t>(sel[3 * r + 2] * key_row), bar);
 }
 
 __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint32_t warp_key[2 * kWarps];
+    __shared__ int warp_pos[2 * kWarps];
+    RLM_PROBE(0);
     const int row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool do_anchor = a.mode != kPartnerOnly, do_partner = a.mode != kAnchorOnly;
+    const int buckets4 = 4 * a.buckets;
+
+    // Loads that depend on nothing go first: this thread's query element, the router
+    // parameters of its head and its slice of the two bias tables.
+    float qv = 0.0f;
+    if (a.mode == kPacked) {
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
+        else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, a.query_dtype);
+    } else if (a.mode == kAnchorOnly) {
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
+    } else {
+        if (tid < kD) qv = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
+    }
+    const int my_head = (lane & 7) >> 1;
+    float ga = 0.0f, gp = 0.0f, ba = 0.0f, bp_ = 0.0f;
+    if (do_anchor) ga = load_scalar(a.anchor_gamma, my_head, a.param_dtype);
+    if (do_partner) gp = load_scalar(a.partner_gamma, my_head, a.param_dtype);
+    if (tid < buckets4) {
+        if (do_anchor) ba = load_scalar(a.anchor_bias, tid, a.param_dtype);
+        if (do_partner) bp_ = load_scalar(a.partner_bias, tid, a.param_dtype);
+    }
     const int b = a.row_batch ? a.row_batch[row] : row;
     const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
     if (b < 0 || b >= a.n_seq || t < 0 || t >= a.max_t) {
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
         return;
     }
+    RLM_PROBE(1);
     const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks;
     const int ks = a.key_dtype == RLM_F32 ? 4 : 2, ss = a.stats_dtype == RLM_F32 ? 4 : 2;
-    const Plan p = make_plan(nb, bs, L, top, a.buckets, ks, ss, a.mode);
-    const bool do_anchor = a.mode != kPartnerOnly, do_partner = a.mode != kAnchorOnly;
+    const Plan& p = a.plan;
 
     float* queries = reinterpret_cast<float*>(smem + p.queries);
     float* aq = queries, *arq = queries + kD, *pq = queries + 2 * kD, *prq = queries + 3 * kD;
     float* params = reinterpret_cast<float*>(smem + p.params);
-    float* sp_a = params, *sp_p = params + 4, *bias_a = params + 8, *bias_p = bias_a + 4 * a.buckets;
+    float* bias_a = params, *bias_p = params + buckets4;
     float* bscore = reinterpret_cast<float*>(smem + p.block_scores);
     float* cand = reinterpret_cast<float*>(smem + p.cand);
     int* sel = reinterpret_cast<int*>(smem + p.sel);
@@ -238,14 +324,14 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     const size_t key_row = static_cast<size_t>(kD) * ks, stat_row = static_cast<size_t>(kD) * ss;
     const size_t seq_keys = static_cast<size_t>(b) * a.max_t * key_row;
     const size_t seq_stats = static_cast<size_t>(b) * nb * stat_row;
+    const int cap = L + top * bs, cap4 = (cap + 3) & ~3;
 
     if (tid == 0) {
+        // the issuing thread initialises the barriers itself; the others first touch them
+        // after the block-wide barrier below
         for (int i = 0; i < 5; ++i) mbar_init(bars + 8 * i, 1);
         fence_barrier_init();
-    }
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t sbytes = static_cast<uint32_t>(n_complete * stat_row);
+        const uint32_t sbytes = top > 0 ? static_cast<uint32_t>(n_complete * stat_row) : 0u;
         const uint32_t lbytes = static_cast<uint32_t>(n_local * key_row);
         const size_t loff = seq_keys + static_cast<size_t>(ls) * key_row;
         const uint32_t ldst = static_cast<uint32_t>(first_local * key_row);
@@ -266,29 +352,27 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             bulk_g2s(smem_u32(smem + p.p_local) + ldst, static_cast<const char*>(a.partner_keys) + loff, lbytes, bar_p);
         }
     }
-    // Small operands through ordinary loads while the bulk copies fly.
-    if (do_anchor) {
-        if (tid < kD) aq[tid] = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) arq[tid - kD] = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
-    }
-    if (a.mode == kPartnerOnly) {
-        if (tid < kD) pq[tid] = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) prq[tid - kD] = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
-    }
-    if (tid >= 2 * kD && tid < 2 * kD + 8) {
-        int h = (tid - 2 * kD) & 3;
-        bool partner_side = tid - 2 * kD >= 4;
-        const void* g = partner_side ? a.partner_gamma : a.anchor_gamma;
-        if (g) {
-            float gamma = load_scalar(g, h, a.param_dtype);
-            (partner_side ? sp_p : sp_a)[h] = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
-        }
-    }
-    for (int i = tid; i < 4 * a.buckets; i += kThreads) {
+    // queries[0..255]: packed = aq | arq | partner base (exact 64 | router 64);
+    // partner-only = (unused 128) | pq | prq; anchor-only = aq | arq
+    if (a.mode == kPartnerOnly) { if (tid < 2 * kD) queries[2 * kD + tid] = qv; }
+    else if (a.mode == kPacked || tid < 2 * kD) queries[tid] = qv;
+    if (tid < buckets4) { bias_a[tid] = ba; bias_p[tid] = bp_; }
+    for (int i = tid + kThreads; i < buckets4; i += kThreads) {      // bias tables wider than the CTA
         if (do_anchor) bias_a[i] = load_scalar(a.anchor_bias, i, a.param_dtype);
         if (do_partner) bias_p[i] = load_scalar(a.partner_bias, i, a.param_dtype);
     }
+    if (tid < cap4 - cap) cand[cap + tid] = kNegInf;   // padding slots never win a comparison
+    // softplus of this lane's head, evaluated while the bulk copies fly
+    const float sp_a = canon_log(__fadd_rn(1.0f, canon_exp(ga)));
+    const float sp_p = canon_log(__fadd_rn(1.0f, canon_exp(gp)));
+    RLM_PROBE(2);
     __syncthreads();
+    RLM_PROBE(3);
+
+    // With remote blocks, half of the warps score blocks while the other half scores the
+    // local window; without, everybody scores rows.
+    const bool split = top > 0;
+    const int row_wi = split ? warp - kWarps / 2 : warp, row_nw = split ? kWarps / 2 : kWarps;
 
     int anchor_pos = 0;
     if (do_anchor) {
@@ -297,63 +381,56 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
-        score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
-                     a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore);
-        score_rows(smem + p.a_local, a.key_dtype, L, first_local, L, t - L + 1, -1, aq, cand, 0);
+        RLM_PROBE(4);
+        uint32_t bk = 0;
+        int bp = 0x7fffffff;
+        if (split && warp < kWarps / 2)
+            score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
+                         a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, kWarps / 2);
+        else
+            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, aq,
+                       nullptr, 0, row_wi, row_nw, bk, bp);
+        if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
-        if (warp == 0) {
-            pick_blocks(bscore, nb, top, bs, ls, sel);
-            if (lane == 0 && top > 0) {
-                fence_proxy_async();
-                uint32_t total = 0;
-                for (int r = 0; r < top; ++r) total += static_cast<uint32_t>(sel[3 * r + 2] * key_row);
-                mbar_expect_tx(bar_ra, total);
-                for (int r = 0; r < top; ++r)
-                    if (sel[3 * r + 2] > 0)
-                        bulk_g2s(smem_u32(smem + p.remote) + static_cast<uint32_t>(r * bs * key_row),
-                                 static_cast<const char*>(a.anchor_keys) + seq_keys + static_cast<size_t>(sel[3 * r]) * bs * key_row,
-                                 static_cast<uint32_t>(sel[3 * r + 2] * key_row), bar_ra);
-            }
-        }
-        __syncthreads();
+        RLM_PROBE(6);
         if (top > 0) {
+            if (warp == 0) {
+                pick_blocks(bscore, nb, top, bs, ls, sel);
+                RLM_PROBE(7);
+                if (lane == 0)
+                    issue_remote(static_cast<const unsigned char*>(a.anchor_keys), smem + p.remote, sel,
+                                 top, bs, key_row, seq_keys, bar_ra);
+                RLM_PROBE(8);
+            }
+            __syncthreads();
+            RLM_PROBE(9);
             ok = mbar_wait(bar_ra, 0);
             if (__syncthreads_or(!ok)) {
                 if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
                 return;
             }
-            for (int r = 0; r < top; ++r)
-                score_rows(smem + p.remote + static_cast<size_t>(r) * bs * key_row, a.key_dtype, bs, 0,
-                           sel[3 * r + 2], sel[3 * r] * bs, -1, aq, cand, L + r * bs);
+            RLM_PROBE(10);
+            bk = 0;
+            bp = 0x7fffffff;
+            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, aq, nullptr, 0, warp,
+                       kWarps, bk, bp);
+            if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             __syncthreads();
+            RLM_PROBE(11);
         }
-        // Every warp reduces redundantly so that all threads know the anchor.
-        float best = kNegInf;
-        int best_c = 0x7fffffff;
-        for (int c = lane; c < L; c += 32) {
-            float v = cand[c];
-            if (v > best || best_c == 0x7fffffff) { best = v; best_c = c; }
-        }
-        warp_argmax_low(best, best_c);
-        anchor_pos = t - L + 1 + best_c;
-        for (int r = 0; r < top; ++r) {
-            float cv = kNegInf;
-            int co = 0x7fffffff;
-            for (int o = lane; o < bs; o += 32) {
-                float v = cand[L + r * bs + o];
-                if (v > cv || co == 0x7fffffff) { cv = v; co = o; }
-            }
-            warp_argmax_low(cv, co);
-            if (co == 0x7fffffff) co = 0;
-            int cpos = sel[3 * r] * bs + co;
-            if (cv > best || (cv == best && cpos < anchor_pos)) { best = cv; anchor_pos = cpos; }
-        }
+        // Highest score wins; equal scores go to the lowest position (the reference's
+        // left-most local arg-max followed by its "equal and earlier" merge rule).
+        const int entries = top > 0 ? 2 * kWarps : kWarps;
+        uint32_t best_key = lane < entries ? warp_key[lane] : 0u;
+        anchor_pos = lane < entries ? warp_pos[lane] : 0x7fffffff;
+        if (anchor_pos == 0x7fffffff) best_key = 0u;
+        warp_argmax_key(best_key, anchor_pos);
         if (tid == 0) {
             a.out_anchor[row] = anchor_pos;
-            a.out_anchor_score[row] = best;
+            a.out_anchor_score[row] = key_float(best_key);
         }
         if (!do_partner) return;
-        __syncthreads();   // all reads of cand / sel / remote are done before they are reused
+        RLM_PROBE(12);
         if (tid == 0) {
             mbar_expect_tx(bar_row, static_cast<uint32_t>(2 * key_row));
             bulk_g2s(smem_u32(smem + p.pa_row),
@@ -365,10 +442,10 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
+        RLM_PROBE(13);
         if (tid < 2 * kD) {
-            float base = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
             float add = load_scalar(smem + p.pa_row, tid, a.key_dtype);
-            pq[tid] = __fadd_rn(base, add);   // pq[64..127] is prq
+            pq[tid] = __fadd_rn(pq[tid], add);   // pq[64..127] is prq
         }
     } else {
         anchor_pos = a.anchor_index_in[row];
@@ -379,57 +456,85 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
         return;
     }
-    score_blocks(smem + p.p_mean, smem + p.p_std, a.stats_dtype, nb, n_complete, bs, t, ls,
-                 a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore);
+    RLM_PROBE(14);
+    uint32_t dk = 0;
+    int dp = 0x7fffffff;
+    if (split && warp < kWarps / 2)
+        score_blocks(smem + p.p_mean, smem + p.p_std, a.stats_dtype, nb, n_complete, bs, t, ls,
+                     a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, kWarps / 2);
+    else
+        score_rows(smem + p.p_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
+                   pq, cand, 0, row_wi, row_nw, dk, dp);
     __syncthreads();
-    if (warp == 0) {
-        pick_blocks(bscore, nb, top, bs, ls, sel);
-        if (lane == 0 && top > 0) {
-            fence_proxy_async();
-            uint32_t total = 0;
-            for (int r = 0; r < top; ++r) total += static_cast<uint32_t>(sel[3 * r + 2] * key_row);
-            mbar_expect_tx(bar_rp, total);
-            for (int r = 0; r < top; ++r)
-                if (sel[3 * r + 2] > 0)
-                    bulk_g2s(smem_u32(smem + p.remote) + static_cast<uint32_t>(r * bs * key_row),
-                             static_cast<const char*>(a.partner_keys) + seq_keys + static_cast<size_t>(sel[3 * r]) * bs * key_row,
-                             static_cast<uint32_t>(sel[3 * r + 2] * key_row), bar_rp);
-        }
-    }
-    score_rows(smem + p.p_local, a.key_dtype, L, first_local, L, t - L + 1, anchor_pos, pq, cand, 0);
-    __syncthreads();
+    RLM_PROBE(15);
     if (top > 0) {
+        if (warp == 0) {
+            pick_blocks(bscore, nb, top, bs, ls, sel);
+            RLM_PROBE(16);
+            if (lane == 0) {
+                fence_proxy_async();   // the anchor phase read this buffer through the generic proxy
+                issue_remote(static_cast<const unsigned char*>(a.partner_keys), smem + p.remote, sel, top,
+                             bs, key_row, seq_keys, bar_rp);
+            }
+            RLM_PROBE(17);
+        }
+        __syncthreads();
         bool ok = mbar_wait(bar_rp, 0);
         if (__syncthreads_or(!ok)) {
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
-        for (int r = 0; r < top; ++r)
-            score_rows(smem + p.remote + static_cast<size_t>(r) * bs * key_row, a.key_dtype, bs, 0,
-                       sel[3 * r + 2], sel[3 * r] * bs, anchor_pos, pq, cand, L + r * bs);
+        RLM_PROBE(19);
+        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, pq, cand, L, warp,
+                   kWarps, dk, dp);
         __syncthreads();
+        RLM_PROBE(20);
     }
-    if (warp == 0) {
-        const int cap = L + top * bs;
-        for (int k = 0; k < a.k_out; ++k) {
-            float bv = kNegInf;
-            int bc = 0x7fffffff;
-            for (int c = lane; c < cap; c += 32) {
-                float v = cand[c];
-                if (v > bv || bc == 0x7fffffff) { bv = v; bc = c; }
+    // Exact top-K by rank counting: a candidate's output slot is the number of candidates
+    // that beat it (higher score, or equal score in an earlier slot).  `parts` adjacent
+    // threads share one candidate and scan interleaved groups of four slots.  Slots past the
+    // valid candidates carry score -inf and the position of candidate slot 0.
+    const int K = a.k_out;
+    int parts = 1;
+    while (parts < 8 && parts * 2 * cap <= kThreads) parts *= 2;
+    const float4* cand4 = reinterpret_cast<const float4*>(cand);
+    const int part = tid & (parts - 1);
+    const int n_groups = cap4 >> 2;
+    for (int c0 = 0; c0 < cap; c0 += kThreads / parts) {
+        const int c = c0 + tid / parts;
+        const bool live = c < cap;
+        const float mine = live ? cand[c] : 0.0f;
+        int rank = 0;
+        if (live) {
+            const int home = c >> 2;                       // group of four that holds slot c
+            for (int g = part; g < n_groups; g += parts) {
+                float4 o = cand4[g];
+                if (g < home)                               // earlier slots win ties
+                    rank += (o.x >= mine) + (o.y >= mine) + (o.z >= mine) + (o.w >= mine);
+                else if (g > home)                          // later slots lose ties
+                    rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
+                else {
+                    const int m0 = g << 2;
+                    rank += (o.x > mine || (o.x == mine && m0 < c)) + (o.y > mine || (o.y == mine && m0 + 1 < c)) +
+                            (o.z > mine || (o.z == mine && m0 + 2 < c)) + (o.w > mine || (o.w == mine && m0 + 3 < c));
+                }
             }
-            warp_argmax_low(bv, bc);
-            if (lane == 0) {
-                int pos;
-                if (bc < L) pos = t - L + 1 + bc;
-                else { int r = (bc - L) / bs; pos = sel[3 * r] * bs + (bc - L - r * bs); }
-                a.out_partner[static_cast<size_t>(row) * a.k_out + k] = pos;
-                a.out_partner_score[static_cast<size_t>(row) * a.k_out + k] = bv;
-                cand[bc] = kNegInf;
-            }
-            __syncwarp();
+        }
+        for (int sft = 1; sft < parts; sft <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, sft);
+        if (live && part == 0 && rank < K) {
+            int pos;
+            if (!(mine > kNegInf)) pos = t - L + 1;
+            else if (c < L) pos = t - L + 1 + c;
+            else { int r = (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
+            a.out_partner[static_cast<size_t>(row) * K + rank] = pos;
+            a.out_partner_score[static_cast<size_t>(row) * K + rank] = mine;
         }
     }
+    for (int k = cap + tid; k < K; k += kThreads) {
+        a.out_partner[static_cast<size_t>(row) * K + k] = t - L + 1;
+        a.out_partner_score[static_cast<size_t>(row) * K + k] = kNegInf;
+    }
+    RLM_PROBE(21);
 }
 
 int launch(SelectArgs& a, void* stream) {
@@ -473,8 +578,9 @@ int launch(SelectArgs& a, void* stream) {
             return RLM_ERR_ALIGN;
         }
     a.block_size = a.max_t / a.n_blocks;
-    Plan plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
-                          dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode);
+    a.plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
+                       dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode);
+    const Plan& plan = a.plan;
     if (plan.total > kSmemDynamicLimit) {
         set_error("relation_select: block statistics + local window + remote blocks exceed 227 KB of shared memory");
         return RLM_ERR_SMEM;
@@ -558,3 +664,9 @@ extern "C" int rlm_partner_topk(
     a.mode = rlm::kPartnerOnly;
     return rlm::launch(a, stream);
 }
+
+#ifdef RLM_TRACE
+extern "C" int rlm_debug_trace(long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace, sizeof(long long) * 64 * 32));
+}
+#endif

@@ -197,15 +197,24 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 
 // ---- warp helpers
 
-// (value, index) arg-max over the warp; ties keep the lowest index.  All lanes
-// receive the result.
-__device__ __forceinline__ void warp_argmax_low(float& v, int& idx) {
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, v, s);
-        int oi = __shfl_xor_sync(0xffffffffu, idx, s);
-        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
-    }
+// Order-preserving map of a float onto an unsigned key (larger float <=> larger key).
+__device__ __forceinline__ uint32_t float_key(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float key_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Arg-max over the warp of (key, slot) pairs with two redux instructions: the largest key
+// wins, ties go to the lowest slot.  Lanes without a candidate pass slot = 0x7fffffff and
+// key = 0.  All lanes receive the result.
+__device__ __forceinline__ void warp_argmax_key(uint32_t& key, int& slot) {
+    const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+    const uint32_t mine = key == best ? static_cast<uint32_t>(slot) : 0x7fffffffu;
+    slot = static_cast<int>(__reduce_min_sync(0xffffffffu, mine));
+    key = best;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
