@@ -21,13 +21,18 @@ namespace {
 //
 // Tile = kRB sequences (kRB*K relation rows) x kHT hidden columns per CTA pass.  The weight
 // tiles of the CTA's hidden columns are staged once (fp32, padded rows); a CTA then walks
-// its share of sequence groups.  Per group: the gathered operand rows are multiplied into
-// the product matrix in shared memory, and every thread accumulates an NR x 2 register tile
-// (NR relation rows, two hidden columns) over the relation dimension with float4 reads.
+// its share of sequence groups.  Per group the gathered operand rows are multiplied into the
+// product matrix in shared memory.  The 512 threads form four groups of 128 that each take a
+// quarter of the relation dimension (sixteen warps per CTA hide the shared-memory latency);
+// inside a group a thread accumulates an NR x 2 register tile (NR relation rows, two hidden
+// columns) with float4 reads.  Partial sums meet in shared memory; the epilogue (expanded-cache
+// terms, GELU, store) is spread over all threads, two adjacent hidden columns per thread.
 
 constexpr int kHT = 32;            // hidden columns per CTA
 constexpr int kRB = 4;             // sequences per tile
-constexpr int kHiddenThreads = 128;
+constexpr int kSplit = 4;          // thread groups along the relation dimension
+constexpr int kGroupThreads = 128;
+constexpr int kHiddenThreads = kSplit * kGroupThreads;
 constexpr int kMaxK = 16;          // partner slots per row
 constexpr int kPad = 4;            // row padding (floats) of staged weight tiles: conflict-free float4 reads
 
@@ -48,23 +53,6 @@ struct HiddenArgs {
     int cache_dtype, weight_dtype;
 };
 
-__device__ __forceinline__ void stage_weight_tile(const void* weight, int dtype, int h0, int hdim,
-                                                  int rdim, float* dst) {
-    const int segs = rdim / 8;
-    for (int i = threadIdx.x; i < kHT * segs; i += kHiddenThreads) {
-        int r = i / segs, sgm = i - r * segs;
-        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (h0 + r < hdim) {
-            const char* row = static_cast<const char*>(weight) +
-                              static_cast<size_t>(h0 + r) * rdim * (dtype == RLM_F32 ? 4 : 2);
-            load8(row, 8 * sgm, dtype, f);
-        }
-        float4* d = reinterpret_cast<float4*>(dst + r * (rdim + kPad) + 8 * sgm);
-        d[0] = make_float4(f[0], f[1], f[2], f[3]);
-        d[1] = make_float4(f[4], f[5], f[6], f[7]);
-    }
-}
-
 __device__ __forceinline__ float gelu_erf(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
@@ -76,6 +64,11 @@ __device__ __forceinline__ float dot4(const float4& a, const float4& b, float ac
     return fmaf(a.w, b.w, acc);
 }
 
+__device__ __forceinline__ void store8(float* dst, const float (&f)[8]) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 // NR = relation rows per thread: the tile's kRB*K rows are dealt to 8 thread rows.
 template <bool kUpdate, int NR>
 __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const HiddenArgs a) {
@@ -84,17 +77,47 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
     const int R = a.rdim, H = a.hdim, K = a.k_out;
     const int stride = R + kPad;
     const int tile_rows = kRB * K;
+    constexpr int kRows = 8 * NR;                          // rows of the product matrix
     float* wm = reinterpret_cast<float*>(smem);
     float* wa = wm + kHT * stride;                        // only when kUpdate
     float* wp = wa + (kUpdate ? kHT * stride : 0);
-    float* prod = wp + (kUpdate ? kHT * stride : 0);      // [8 * NR][R]
-    float* cur = prod + 8 * NR * R;                       // [kRB][R] current operands (kUpdate)
-    float* fresh = cur + (kUpdate ? kRB * R : 0);         // [kRB][2][kHT] (kUpdate)
+    float* prod = wp + (kUpdate ? kHT * stride : 0);      // [kRows][R]
+    float* red = prod + kRows * R;                        // [kSplit][kRows][kHT] partial sums
+    float* cur = red + kSplit * kRows * kHT;              // [kRB][R] current operands (kUpdate)
+    float* red2 = cur + (kUpdate ? kRB * R : 0);          // [kSplit][kRB][2][kHT] (kUpdate)
     __shared__ int idx[kRB][kMaxK + 1];
     __shared__ int seq[kRB];
 
     RLM_PROBE(0);
     const int h0 = blockIdx.x * kHT;
+    const int ws = a.weight_dtype == RLM_F32 ? 4 : 2;
+    const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
+    const int segs = R / 8;
+    // weight tiles: every load of this thread is issued before the first conversion
+    for (int i = tid; i < kHT * segs; i += kHiddenThreads) {
+        const int r = i / segs, sgm = i - r * segs;
+        Raw8 rm, ra, rp;
+        rm.lo = rm.hi = make_uint4(0, 0, 0, 0);
+        ra = rm;
+        rp = rm;
+        if (h0 + r < H) {
+            const size_t off = static_cast<size_t>(h0 + r) * R * ws;
+            rm = load8_raw(static_cast<const char*>(a.product_weight) + off, 8 * sgm, a.weight_dtype);
+            if (kUpdate) {
+                ra = load8_raw(static_cast<const char*>(a.anchor_weight) + off, 8 * sgm, a.weight_dtype);
+                rp = load8_raw(static_cast<const char*>(a.partner_weight) + off, 8 * sgm, a.weight_dtype);
+            }
+        }
+        float f[8];
+        convert8(rm, a.weight_dtype, f);
+        store8(wm + r * stride + 8 * sgm, f);
+        if (kUpdate) {
+            convert8(ra, a.weight_dtype, f);
+            store8(wa + r * stride + 8 * sgm, f);
+            convert8(rp, a.weight_dtype, f);
+            store8(wp + r * stride + 8 * sgm, f);
+        }
+    }
     int t = -1;
     if (kUpdate) {
         t = static_cast<int>(*a.position);
@@ -103,15 +126,11 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             return;
         }
     }
-    stage_weight_tile(a.product_weight, a.weight_dtype, h0, H, R, wm);
-    if (kUpdate) {
-        stage_weight_tile(a.anchor_weight, a.weight_dtype, h0, H, R, wa);
-        stage_weight_tile(a.partner_weight, a.weight_dtype, h0, H, R, wp);
-    }
     RLM_PROBE(1);
-    const int tx = tid & 15, ty = tid >> 4;              // hidden columns {tx, tx+16}; rows {ty + 8 i}
-    const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
-    const int segs = R / 8;
+    const int rq = tid / kGroupThreads, t7 = tid - rq * kGroupThreads;
+    const int tx = t7 & 15, ty = t7 >> 4;                // hidden columns {tx, tx+16}; rows {ty + 8 i}
+    const int steps = R / 4;                              // float4 steps along the relation dimension
+    const int r_lo = 4 * (rq * steps / kSplit), r_hi = 4 * ((rq + 1) * steps / kSplit);
     const int groups = (a.n_rows + kRB - 1) / kRB;
 
     for (int group = blockIdx.y; group < groups; group += gridDim.y) {
@@ -135,39 +154,96 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         __syncthreads();
         RLM_PROBE(2);
         // product matrix: prod[rb*K + k][:] = operand[p_k] * operand[anchor]
-        for (int i = tid; i < 8 * NR * segs; i += kHiddenThreads) {
-            int prow = i / segs, sgm = i - prow * segs;
-            int rb = prow / K, k = prow - rb * K;
-            float4 lo = make_float4(0, 0, 0, 0), hi = lo;
+        for (int i = tid; i < kRows * segs; i += kHiddenThreads) {
+            const int prow = i / segs, sgm = i - prow * segs;
+            const int rb = prow / K, k = prow - rb * K;
+            float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (prow < tile_rows && seq[rb] >= 0) {
                 const char* operand = static_cast<const char*>(a.operand_cache) +
                                       static_cast<size_t>(seq[rb]) * a.max_t * R * cs;
+                Raw8 ra = load8_raw(operand + static_cast<size_t>(idx[rb][0]) * R * cs, 8 * sgm, a.cache_dtype);
+                Raw8 rp = load8_raw(operand + static_cast<size_t>(idx[rb][k + 1]) * R * cs, 8 * sgm, a.cache_dtype);
                 float oa[8], op[8];
-                load8(operand + static_cast<size_t>(idx[rb][0]) * R * cs, 8 * sgm, a.cache_dtype, oa);
-                load8(operand + static_cast<size_t>(idx[rb][k + 1]) * R * cs, 8 * sgm, a.cache_dtype, op);
-                lo = make_float4(op[0] * oa[0], op[1] * oa[1], op[2] * oa[2], op[3] * oa[3]);
-                hi = make_float4(op[4] * oa[4], op[5] * oa[5], op[6] * oa[6], op[7] * oa[7]);
+                convert8(ra, a.cache_dtype, oa);
+                convert8(rp, a.cache_dtype, op);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = op[e] * oa[e];
             }
-            float4* d = reinterpret_cast<float4*>(prod + prow * R + 8 * sgm);
-            d[0] = lo;
-            d[1] = hi;
+            store8(prod + prow * R + 8 * sgm, f);
         }
         if (kUpdate) {
             for (int i = tid; i < kRB * segs; i += kHiddenThreads) {
-                int rb = i / segs, sgm = i - rb * segs;
+                const int rb = i / segs, sgm = i - rb * segs;
                 float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 if (seq[rb] >= 0)
                     load8(static_cast<const char*>(a.operand_cache) +
                               (static_cast<size_t>(seq[rb]) * a.max_t + t) * R * cs,
                           8 * sgm, a.cache_dtype, o);
-                float4* d = reinterpret_cast<float4*>(cur + rb * R + 8 * sgm);
-                d[0] = make_float4(o[0], o[1], o[2], o[3]);
-                d[1] = make_float4(o[4], o[5], o[6], o[7]);
+                store8(cur + rb * R + 8 * sgm, o);
+            }
+        }
+        // expanded-cache terms of this thread's epilogue outputs, requested before the
+        // arithmetic so that their latency is hidden; pair q covers hidden columns 2q, 2q+1
+        constexpr int kPairs = kRows * (kHT / 2) / kHiddenThreads;
+        float2 base_a[kPairs], base_p[kPairs];
+        int out_row[kPairs], out_k[kPairs];
+        bool sub_a[kPairs], sub_p[kPairs];
+#pragma unroll
+        for (int e = 0; e < kPairs; ++e) {
+            const int o = tid + e * kHiddenThreads;
+            const int prow = o / (kHT / 2), hh = 2 * (o - prow * (kHT / 2));
+            const int rb = prow / K, k = prow - rb * K;
+            const bool live = prow < tile_rows && row0 + rb < a.n_rows && seq[rb < kRB ? rb : 0] >= 0 &&
+                              h0 + hh < H;
+            out_row[e] = live ? row0 + rb : -1;
+            out_k[e] = k;
+            base_a[e] = base_p[e] = make_float2(0.0f, 0.0f);
+            sub_a[e] = sub_p[e] = false;
+            if (!live) continue;
+            const int64_t ebase = static_cast<int64_t>(seq[rb]) * a.max_t * 2 * H;
+            const int ai = idx[rb][0], pi = idx[rb][k + 1];
+            sub_a[e] = kUpdate && ai == t;
+            sub_p[e] = kUpdate && pi == t;
+            const bool two = h0 + hh + 1 < H;
+            if (!sub_a[e]) {
+                const int64_t at = ebase + static_cast<int64_t>(ai) * 2 * H + h0 + hh;
+                base_a[e].x = load_scalar(a.expanded_cache, at, a.cache_dtype);
+                if (two) base_a[e].y = load_scalar(a.expanded_cache, at + 1, a.cache_dtype);
+            }
+            if (!sub_p[e]) {
+                const int64_t at = ebase + static_cast<int64_t>(pi) * 2 * H + H + h0 + hh;
+                base_p[e].x = load_scalar(a.expanded_cache, at, a.cache_dtype);
+                if (two) base_p[e].y = load_scalar(a.expanded_cache, at + 1, a.cache_dtype);
             }
         }
         __syncthreads();
         RLM_PROBE(3);
 
+        // partial sums over this group's quarter of the relation dimension
+        float acc[NR][2];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) acc[i][0] = acc[i][1] = 0.0f;
+        {
+            const float* w0 = wm + tx * stride;
+            const float* w1 = w0 + 16 * stride;
+            const float* p0 = prod + ty * R;
+#pragma unroll 2
+            for (int r = r_lo; r < r_hi; r += 4) {
+                float4 a0 = *reinterpret_cast<const float4*>(w0 + r);
+                float4 a1 = *reinterpret_cast<const float4*>(w1 + r);
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    float4 pv = *reinterpret_cast<const float4*>(p0 + i * 8 * R + r);
+                    acc[i][0] = dot4(a0, pv, acc[i][0]);
+                    acc[i][1] = dot4(a1, pv, acc[i][1]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                red[(rq * kRows + ty + 8 * i) * kHT + tx] = acc[i][0];
+                red[(rq * kRows + ty + 8 * i) * kHT + tx + 16] = acc[i][1];
+            }
+        }
         if (kUpdate) {
             // current expanded rows: thread row ty -> (sequence ty/2, anchor or partner half)
             const int rb = ty >> 1, half = ty & 1;
@@ -175,73 +251,71 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             const float* w1 = w0 + 16 * stride;
             const float* c = cur + rb * R;
             float f0 = 0.0f, f1 = 0.0f;
-            for (int r = 0; r < R; r += 4) {
+            for (int r = r_lo; r < r_hi; r += 4) {
                 float4 cv = *reinterpret_cast<const float4*>(c + r);
                 f0 = dot4(*reinterpret_cast<const float4*>(w0 + r), cv, f0);
                 f1 = dot4(*reinterpret_cast<const float4*>(w1 + r), cv, f1);
             }
-            if (half == 0) {
-                if (h0 + tx < H) f0 += load_scalar(a.first_bias, h0 + tx, a.weight_dtype);
-                if (h0 + tx + 16 < H) f1 += load_scalar(a.first_bias, h0 + tx + 16, a.weight_dtype);
-            }
-            fresh[(rb * 2 + half) * kHT + tx] = f0;
-            fresh[(rb * 2 + half) * kHT + tx + 16] = f1;
-            if (seq[rb] >= 0) {
-                const int64_t base = (static_cast<int64_t>(seq[rb]) * a.max_t + t) * 2 * H + half * H + h0;
-                if (h0 + tx < H) store_scalar(a.expanded_cache, base + tx, a.cache_dtype, f0);
-                if (h0 + tx + 16 < H) store_scalar(a.expanded_cache, base + tx + 16, a.cache_dtype, f1);
-            }
-            __syncthreads();
+            red2[((rq * kRB + rb) * 2 + half) * kHT + tx] = f0;
+            red2[((rq * kRB + rb) * 2 + half) * kHT + tx + 16] = f1;
         }
-
+        __syncthreads();
         RLM_PROBE(4);
-        float acc[NR][2];
+
+        if (kUpdate && tid < kRB * 2 * (kHT / 2)) {
+            // fresh expanded rows -> cache row t (rounded to the cache dtype)
+            const int pair = tid % (kHT / 2), rh = tid / (kHT / 2);      // rh = rb * 2 + half
+            const int rb = rh >> 1, half = rh & 1, hh = 2 * pair;
+            if (seq[rb] >= 0) {
 #pragma unroll
-        for (int i = 0; i < NR; ++i) acc[i][0] = acc[i][1] = 0.0f;
-        const float* w0 = wm + tx * stride;
-        const float* w1 = w0 + 16 * stride;
-        const float* p0 = prod + ty * R;
-#pragma unroll 2
-        for (int r = 0; r < R; r += 4) {
-            float4 a0 = *reinterpret_cast<const float4*>(w0 + r);
-            float4 a1 = *reinterpret_cast<const float4*>(w1 + r);
+                for (int j = 0; j < 2; ++j) {
+                    if (h0 + hh + j >= H) continue;
+                    float v = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                float4 pv = *reinterpret_cast<const float4*>(p0 + i * 8 * R + r);
-                acc[i][0] = dot4(a0, pv, acc[i][0]);
-                acc[i][1] = dot4(a1, pv, acc[i][1]);
+                    for (int q = 0; q < kSplit; ++q) v += red2[((q * kRB + rb) * 2 + half) * kHT + hh + j];
+                    if (half == 0) v += load_scalar(a.first_bias, h0 + hh + j, a.weight_dtype);
+                    store_scalar(a.expanded_cache,
+                                 (static_cast<int64_t>(seq[rb]) * a.max_t + t) * 2 * H + half * H + h0 + hh + j,
+                                 a.cache_dtype, v);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kPairs; ++e) {
+            if (out_row[e] < 0) continue;
+            const int o = tid + e * kHiddenThreads;
+            const int prow = o / (kHT / 2), hh = 2 * (o - prow * (kHT / 2));
+            const int rb = prow / K;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (h0 + hh + j >= H) continue;
+                float v = 0.0f;
+#pragma unroll
+                for (int q = 0; q < kSplit; ++q) v += red[(q * kRows + prow) * kHT + hh + j];
+                float ba = j == 0 ? base_a[e].x : base_a[e].y;
+                float bp = j == 0 ? base_p[e].x : base_p[e].y;
+                if (kUpdate && (sub_a[e] || sub_p[e])) {
+                    float fa = 0.0f, fp = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < kSplit; ++q) {
+                        fa += red2[((q * kRB + rb) * 2 + 0) * kHT + hh + j];
+                        fp += red2[((q * kRB + rb) * 2 + 1) * kHT + hh + j];
+                    }
+                    if (sub_a[e]) ba = fa + load_scalar(a.first_bias, h0 + hh + j, a.weight_dtype);
+                    if (sub_p[e]) bp = fp;
+                }
+                a.out[(static_cast<size_t>(out_row[e]) * K + out_k[e]) * H + h0 + hh + j] =
+                    gelu_erf(v + (ba + bp));
             }
         }
         RLM_PROBE(5);
-#pragma unroll
-        for (int i = 0; i < NR; ++i) {
-            const int prow = ty + 8 * i;
-            if (prow >= tile_rows) continue;
-            const int rb = prow / K, k = prow - rb * K, row = row0 + rb;
-            if (row >= a.n_rows || seq[rb] < 0) continue;
-            const int64_t ebase = static_cast<int64_t>(seq[rb]) * a.max_t * 2 * H;
-            const int ai = idx[rb][0], pi = idx[rb][k + 1];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int hh = tx + 16 * j;
-                if (h0 + hh >= H) continue;
-                float base_a = (kUpdate && ai == t)
-                                   ? fresh[(rb * 2) * kHT + hh]
-                                   : load_scalar(a.expanded_cache, ebase + static_cast<int64_t>(ai) * 2 * H + h0 + hh, a.cache_dtype);
-                float base_p = (kUpdate && pi == t)
-                                   ? fresh[(rb * 2 + 1) * kHT + hh]
-                                   : load_scalar(a.expanded_cache, ebase + static_cast<int64_t>(pi) * 2 * H + H + h0 + hh, a.cache_dtype);
-                a.out[(static_cast<size_t>(row) * K + k) * H + h0 + hh] = gelu_erf(acc[i][j] + (base_a + base_p));
-            }
-        }
-        RLM_PROBE(6);
     }
 }
 
 int hidden_smem_bytes(bool update, int rdim, int nr) {
     int tiles = update ? 3 : 1;
-    int floats = tiles * kHT * (rdim + kPad) + 8 * nr * rdim;
-    if (update) floats += kRB * rdim + kRB * 2 * kHT;
+    int floats = tiles * kHT * (rdim + kPad) + 8 * nr * rdim + kSplit * 8 * nr * kHT;
+    if (update) floats += kRB * rdim + kSplit * kRB * 2 * kHT;
     return floats * 4;
 }
 
@@ -260,7 +334,7 @@ int launch_hidden_as(const HiddenArgs& a, void* stream) {
     const int tiles = (a.hdim + kHT - 1) / kHT;
     const int groups = (a.n_rows + kRB - 1) / kRB;
     // a few CTAs per SM; beyond that a CTA keeps its weight tiles and walks several groups
-    int gy = (148 * 6 + tiles - 1) / tiles;
+    int gy = (148 * 4 + tiles - 1) / tiles;
     if (gy > groups) gy = groups;
     dim3 grid(tiles, gy);
     kernel<<<grid, kHiddenThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
@@ -276,9 +350,9 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         set_error("relation_hidden: NULL pointer");
         return RLM_ERR_NULL;
     }
-    if (a.n_rows < 0 || a.n_seq < 1 || a.max_t < 1 || a.rdim < 8 || a.rdim % 8 != 0 || a.hdim < 1 ||
+    if (a.n_rows < 0 || a.n_seq < 1 || a.max_t < 1 || a.rdim < 16 || a.rdim % 16 != 0 || a.hdim < 1 ||
         a.k_out < 1 || a.k_out > kMaxK) {
-        set_error("relation_hidden: need relation_dim a multiple of 8, 1 <= K <= 16 and positive sizes");
+        set_error("relation_hidden: need relation_dim a multiple of 16, 1 <= K <= 16 and positive sizes");
         return RLM_ERR_SHAPE;
     }
     if (!a.row_batch && a.n_rows != a.n_seq) {

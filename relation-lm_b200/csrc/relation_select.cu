@@ -26,6 +26,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+constexpr int kMaxKOut = 32;  // partner slots per query
 constexpr int kD = 64;        // exact-score width == router heads * head width
 
 enum Mode { kPacked = 0, kAnchorOnly = 1, kPartnerOnly = 2 };
@@ -267,6 +268,8 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
+    __shared__ uint32_t surv_key[kWarps * kMaxKOut];
+    __shared__ int surv_slot[kWarps * kMaxKOut];
     RLM_PROBE(0);
     const int row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -495,6 +498,59 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     // threads share one candidate and scan interleaved groups of four slots.  Slots past the
     // valid candidates carry score -inf and the position of candidate slot 0.
     const int K = a.k_out;
+    if (cap > 128) {
+        // Large candidate sets: tournament.  Each warp extracts the top K of the slots it
+        // owns (K rounds of redux arg-max, knocking winners out of the table); warp 0 then
+        // extracts the top K of the 8 K survivors.  Any global top-K candidate is among the
+        // top K of its own warp, and (score, lowest slot) ordering is kept at both levels.
+        for (int r = 0; r < K; ++r) {
+            uint32_t bk = 0;
+            int bc = 0x7fffffff;
+            for (int c = warp * 32 + lane; c < cap; c += kThreads) {
+                uint32_t key = float_key(cand[c]);
+                if (key > bk || bc == 0x7fffffff) { bk = key; bc = c; }
+            }
+            warp_argmax_key(bk, bc);
+            if (lane == 0) {
+                surv_key[warp * kMaxKOut + r] = bc == 0x7fffffff ? 0u : bk;
+                surv_slot[warp * kMaxKOut + r] = bc;
+                if (bc != 0x7fffffff) cand[bc] = __uint_as_float(0xffffffffu);   // below every score: key 0
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int r = 0; r < K; ++r) {
+                uint32_t bk = 0;
+                int bc = 0x7fffffff, bi = -1;
+                for (int i = lane; i < kWarps * K; i += 32) {
+                    const int e = (i / K) * kMaxKOut + (i - (i / K) * K);
+                    uint32_t key = surv_key[e];
+                    int c = surv_slot[e];
+                    if (key != 0u && (key > bk || (key == bk && c < bc) || bc == 0x7fffffff)) { bk = key; bc = c; bi = e; }
+                }
+                const int mine = bc;
+                warp_argmax_key(bk, bc);
+                if (bc != 0x7fffffff && mine == bc && bi >= 0) surv_key[bi] = 0u;
+                if (lane == 0) {
+                    const float sc = bc == 0x7fffffff ? kNegInf : key_float(bk);
+                    int pos;
+                    if (!(sc > kNegInf)) pos = t - L + 1;
+                    else if (bc < L) pos = t - L + 1 + bc;
+                    else { int rr = (bc - L) / bs; pos = sel[3 * rr] * bs + (bc - L - rr * bs); }
+                    a.out_partner[static_cast<size_t>(row) * K + r] = pos;
+                    a.out_partner_score[static_cast<size_t>(row) * K + r] = sc;
+                }
+                __syncwarp();
+            }
+        }
+        RLM_PROBE(21);
+        return;
+    }
+    // Small candidate sets: exact top-K by rank counting.  A candidate's output slot is the
+    // number of candidates that beat it (higher score, or equal score in an earlier slot).
+    // `parts` adjacent threads share one candidate and scan interleaved groups of four slots.
+    // Slots past the valid candidates carry score -inf and the position of candidate slot 0.
     int parts = 1;
     while (parts < 8 && parts * 2 * cap <= kThreads) parts *= 2;
     const float4* cand4 = reinterpret_cast<const float4*>(cand);
@@ -544,8 +600,8 @@ int launch(SelectArgs& a, void* stream) {
         set_error("relation_select: sizes must be positive and T a multiple of the block count");
         return RLM_ERR_SHAPE;
     }
-    if (a.mode != kAnchorOnly && a.k_out < 1) {
-        set_error("relation_select: k_out must be at least 1");
+    if (a.mode != kAnchorOnly && (a.k_out < 1 || a.k_out > kMaxKOut)) {
+        set_error("relation_select: k_out must be between 1 and 32");
         return RLM_ERR_SHAPE;
     }
     if (!valid_dtype(a.query_dtype) || !valid_dtype(a.key_dtype) || !valid_dtype(a.stats_dtype) ||

@@ -78,6 +78,49 @@ __device__ __forceinline__ void load8(const void* row, int first, int dtype, flo
     }
 }
 
+// Split form of load8 for software pipelining: fetch the raw bytes of eight elements now,
+// convert them later (after more loads have been issued).
+struct Raw8 { uint4 lo, hi; };
+
+__device__ __forceinline__ Raw8 load8_raw(const void* row, int first, int dtype) {
+    Raw8 r;
+    if (dtype == RLM_F32) {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(row) + first);
+        r.lo = p[0];
+        r.hi = p[1];
+    } else {
+        r.lo = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(row) + first);
+        r.hi = make_uint4(0, 0, 0, 0);
+    }
+    return r;
+}
+
+__device__ __forceinline__ void convert8(const Raw8& r, int dtype, float (&f)[8]) {
+    if (dtype == RLM_F32) {
+        f[0] = __uint_as_float(r.lo.x); f[1] = __uint_as_float(r.lo.y);
+        f[2] = __uint_as_float(r.lo.z); f[3] = __uint_as_float(r.lo.w);
+        f[4] = __uint_as_float(r.hi.x); f[5] = __uint_as_float(r.hi.y);
+        f[6] = __uint_as_float(r.hi.z); f[7] = __uint_as_float(r.hi.w);
+    } else {
+        uint32_t w[4] = {r.lo.x, r.lo.y, r.lo.z, r.lo.w};
+        if (dtype == RLM_BF16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                f[2 * i] = __uint_as_float(w[i] << 16);
+                f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __half2 h = *reinterpret_cast<__half2*>(&w[i]);
+                float2 p = __half22float2(h);
+                f[2 * i] = p.x;
+                f[2 * i + 1] = p.y;
+            }
+        }
+    }
+}
+
 // ---- canonical fp32 arithmetic: every operation that can move a selected
 // index is spelled with an explicit rounding so that no contraction or
 // reassociation can differ between builds.  exp/log are plain-fp32
