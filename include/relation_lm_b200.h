@@ -190,6 +190,19 @@ int rlm_relation_norm_reduce(
     int32_t* status, void* stream);
 
 /*
+ * Packed sparse-cache projection on the tensor cores (tcgen05, TMEM accumulator, TMA loads):
+ * out[rows, n_out] = x[rows, d_in] . weight[n_out, d_in]^T.  Replaces the F.linear inside
+ * PackedSparseCacheProjection.project (src/relation_lm/inference/packed_cache.py:52-57); the
+ * caller splits the packed columns.  Also used for the query-side router projections.
+ *   x [rows, d_in] with a row stride in ELEMENTS (multiple of 8), weight [n_out, d_in]:
+ *   bfloat16 or float16 (in_dtype); out [rows, n_out] contiguous, any rlm_dtype (out_dtype).
+ *   d_in a multiple of 8, n_out a multiple of 32; fp32 operands return RLM_ERR_UNSUPPORTED.
+ */
+int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight, void* out,
+                          int rows, int d_in, int n_out, int in_dtype, int out_dtype,
+                          int32_t* status, void* stream);
+
+/*
  * Decode-state append for every layer of a stack in one launch (extension).  Does what a
  * reference decode step does per layer after PackedSparseCacheProjection.project
  * (src/relation_lm/inference/packed_cache.py:52-57): writes the four token features into

@@ -1,0 +1,278 @@
+// Packed sparse-cache / router projection on the 5th-generation tensor cores (sm_100a):
+//   out[M, N] = x[M, K] . w[N, K]^T      bf16 or fp16 operands, fp32 accumulation in TMEM.
+//
+// One CTA per 128 x BN output tile.  A single producer thread streams 128 x 64 tiles of x
+// and BN x 64 tiles of w into a 4-stage shared-memory ring with tiled TMA loads
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast); a single thread issues
+// tcgen05.mma (UMMA 128 x BN x 16, both operands K-major from shared memory) and releases
+// ring stages with tcgen05.commit; the four warps then read the accumulator with
+// tcgen05.ld, convert and store.  Rows past M are zero-filled by TMA and not stored.
+// Every wait is bounded; on expiry the kernel sets RLM_DEV_TIMEOUT, frees its TMEM and returns.
+//
+// Replaces the F.linear of src/relation_lm/inference/packed_cache.py:52-57 of the reference
+// project (and serves the query-side router projections, which have the same shape).
+
+#include <cuda.h>
+
+#include "rlm_common.cuh"
+
+namespace rlm {
+namespace {
+
+constexpr int kBM = 128;       // rows per tile == TMEM lanes
+constexpr int kBK = 64;        // K elements per stage: 128 bytes, one swizzle atom
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 128;
+
+struct GemmArgs {
+    void* out;
+    int32_t* status;
+    int m, n, k;
+    int out_dtype;
+    uint32_t idesc;
+};
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading byte offset
+// unused (1), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(addr));
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
+    const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+    const GemmArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * kStages + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+
+    constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2;
+    // the ring must start on a 1024-byte boundary for the 128-byte swizzle
+    unsigned char* ring = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t ring_addr = smem_u32(ring);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kBM;
+    const int k_iters = (a.k + kBK - 1) / kBK;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * kStages);
+
+    if (tid == 0) {
+        for (int i = 0; i < 2 * kStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        fence_barrier_init();
+        failed = 0;
+    }
+    if (warp == 1) {   // one warp owns the TMEM allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (tid == 0) {
+        // producer: fill the ring
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % kStages;
+            if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
+            mbar_expect_tx(full(s), kABytes + kBBytes);
+            tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, it * kBK, m0, full(s));
+            tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, it * kBK, n0, full(s));
+        }
+    } else if (tid == 32) {
+        // tensor-core issue: four UMMA K-steps of 16 per stage
+        bool ok = true;
+        for (int it = 0; it < k_iters && ok; ++it) {
+            const int s = it % kStages;
+            ok = mbar_wait(full(s), (it / kStages) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes));
+            const uint64_t db = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes) + kABytes);
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)      // +32 bytes along K inside the swizzle atom
+                umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, a.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(empty(s));                       // stage reusable once these MMAs retire
+        }
+        if (!ok) failed = 1;
+        umma_commit(acc_full);                           // accumulator complete (or abandoned)
+    }
+    __syncwarp();
+
+    // epilogue: warp w reads TMEM lanes 32w .. 32w+31 (one output row per thread)
+    bool ready = mbar_wait(acc_full, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+    if (!__syncthreads_or(!ready)) {
+        const int row = m0 + warp * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < a.m) {
+                const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
+                if (a.out_dtype == RLM_F32) {
+                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        o[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                           __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                } else {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+                        if (a.out_dtype == RLM_BF16) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                            packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(lo, hi);
+                            packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    uint4* o = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + at);
+                    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        }
+    } else if (tid == 0 && a.status) {
+        atomicOr(a.status, RLM_DEV_TIMEOUT);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+// [rows, cols] row-major 16-bit matrix, box = box_rows x 64 columns, 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t row_stride_elems,
+              int box_rows, int dtype) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_elems) * 2};
+    cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMapDataType dt = dtype == RLM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a, void* stream) {
+    const int smem_bytes = kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+    auto kernel = packed_projection_kernel<BN>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    dim3 grid(a.n / BN, (a.m + kBM - 1) / kBM);
+    kernel<<<grid, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mx, mw, a);
+    count_launch();
+    return check_launch("packed_projection_kernel");
+}
+
+}  // namespace
+}  // namespace rlm
+
+extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
+                                     void* out, int rows, int d_in, int n_out, int in_dtype,
+                                     int out_dtype, int32_t* status, void* stream) {
+    using namespace rlm;
+    if (rows == 0) return RLM_OK;
+    if (!x || !weight || !out) { set_error("packed_projection: NULL pointer"); return RLM_ERR_NULL; }
+    if (rows < 0 || d_in < 8 || d_in % 8 != 0 || n_out < 32 || n_out % 32 != 0 || x_row_stride < d_in ||
+        x_row_stride % 8 != 0) {
+        set_error("packed_projection: need d_in and the row stride multiples of 8 and n_out a multiple of 32");
+        return RLM_ERR_SHAPE;
+    }
+    if ((in_dtype != RLM_BF16 && in_dtype != RLM_F16) || !valid_dtype(out_dtype)) {
+        set_error("packed_projection: operands must be bfloat16 or float16 (fp32 inputs are not a tensor-core format here)");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(out)) {
+        set_error("packed_projection: tensors must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    // few rows: narrow tiles so that more CTAs share the weight read; many rows: wide tiles
+    const int bn = (rows <= 128 || n_out % 128 != 0) ? (n_out % 64 == 0 && rows > 32 ? 64 : 32) : 128;
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, rows, d_in, x_row_stride, kBM, in_dtype) ||
+        !make_map(&mw, weight, n_out, d_in, d_in, bn, in_dtype)) {
+        set_error("packed_projection: cuTensorMapEncodeTiled failed");
+        return RLM_ERR_LAUNCH;
+    }
+    GemmArgs a{};
+    a.out = out; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
+    const uint32_t fmt = in_dtype == RLM_BF16 ? 1u : 0u;
+    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+              (static_cast<uint32_t>(kBM >> 4) << 24);
+    if (bn == 32) return launch_gemm<32>(mx, mw, a, stream);
+    if (bn == 64) return launch_gemm<64>(mx, mw, a, stream);
+    return launch_gemm<128>(mx, mw, a, stream);
+}

@@ -54,7 +54,18 @@ class PackedSparseCacheProjection:
         one packed result (so the router slices keep the packed row stride)."""
         if memory.size(-1) != self.input_width:
             raise ValueError("memory width does not match packed projection input")
-        packed = F.linear(memory, self.weight)
+        if memory.is_cuda and memory.dtype in (torch.bfloat16, torch.float16) \
+                and self.weight.dtype == memory.dtype and self.output_width % 32 == 0 \
+                and self.input_width % 8 == 0:
+            # tensor-core kernel of this library (tcgen05); fp32 operands use the library GEMM
+            from relation_lm.kernels.packed_projection import packed_projection
+
+            rows = memory.reshape(-1, self.input_width) if memory.dim() != 2 else memory
+            if rows.stride(-1) != 1 or rows.stride(0) % 8 != 0:
+                rows = rows.contiguous()
+            packed = packed_projection(rows, self.weight).view(*memory.shape[:-1], self.output_width)
+        else:
+            packed = F.linear(memory, self.weight)
         return packed.split(self.split_sizes, dim=-1)
 
     def project_dict(self, memory: Tensor) -> dict[str, Tensor]:

@@ -21,6 +21,7 @@ PROTOTYPES = {
     "rlm_relation_hidden_cached": [_P] * 7 + [_I] * 8 + [_P, _P],
     "rlm_relation_hidden_cache_update": [_P] * 10 + [_I] * 7 + [_P, _P],
     "rlm_relation_norm_reduce": [_P] * 6 + [_F, _P] + [_I] * 5 + [_P, _P],
+    "rlm_packed_projection": [_P, _L, _P, _P] + [_I] * 5 + [_P, _P],
     "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
 }
 

@@ -1,0 +1,58 @@
+"""The tcgen05 packed projection vs an fp64-accumulated product of the same bf16/fp16 operands.
+
+Products of 16-bit operands are exact in fp32, so the only differences are the fp32
+accumulation order and the final rounding to the output dtype: tolerance 1e-2 relative
+(bf16 / fp16 outputs), as for every reduced-precision state of this path.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from gpu_util import assert_status_clear
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,d_in,n_out", [(1, 512, 512), (8, 512, 3072), (8, 576, 512),
+                                             (100, 768, 512), (128, 512, 96), (200, 512, 512),
+                                             (1000, 576, 1024), (256, 768, 6144)])
+def test_packed_projection_matches_oracle(rows, d_in, n_out, dtype):
+    from relation_lm.kernels.packed_projection import packed_projection
+
+    g = torch.Generator().manual_seed(rows * 7 + d_in + n_out)
+    x = torch.randn(rows, d_in, generator=g).to(dtype)
+    w = (torch.randn(n_out, d_in, generator=g) * 0.05).to(dtype)
+    got = packed_projection(x.cuda(), w.cuda()).float().cpu()
+    want = oracle.linear(x, w)
+    assert torch.allclose(got, want, atol=1e-2, rtol=1e-2), (got - want).abs().max()
+    assert_status_clear()
+
+
+def test_strided_rows_and_six_way_split_like_the_reference_test():
+    """tests/test_packed_cache_projection.py of the reference: packed == six separate linears."""
+    from relation_lm.inference import pack_sparse_cache_projection_weights
+
+    g = torch.Generator().manual_seed(20260822)
+    widths = (64, 64, 128, 128, 64, 64)
+    weights = tuple((torch.randn(w, 576, generator=g) * 0.02).bfloat16().cuda() for w in widths)
+    projection = pack_sparse_cache_projection_weights(weights)
+    wide = torch.randn(8, 1152, generator=g).bfloat16().cuda()
+    memory = wide[:, :576]                                   # row stride 1152
+    parts = projection.project(memory)
+    assert [p.size(-1) for p in parts] == list(widths)
+    assert parts[4].stride(0) == 512                         # router slices stay views of the packed result
+    for part, weight in zip(parts, weights, strict=True):
+        want = F.linear(memory.float(), weight.float())
+        assert torch.allclose(part.float(), want, atol=1e-2, rtol=1e-2)
+    assert_status_clear()
+
+
+def test_projection_rejects_fp32_operands():
+    from relation_lm.kernels.packed_projection import packed_projection
+
+    with pytest.raises(ValueError):
+        packed_projection(torch.randn(4, 512, device="cuda"), torch.randn(512, 512, device="cuda"))
