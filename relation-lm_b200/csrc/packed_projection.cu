@@ -2,7 +2,7 @@
 //   out[M, N] = x[M, K] . w[N, K]^T      bf16 or fp16 operands, fp32 accumulation in TMEM.
 //
 // One CTA per 128 x BN output tile.  A single producer thread streams 128 x 64 tiles of x
-// and BN x 64 tiles of w into a 4-stage shared-memory ring with tiled TMA loads
+// and BN x 64 tiles of w into a 3- or 8-stage shared-memory ring with tiled TMA loads
 // (cp.async.bulk.tensor, 128-byte swizzle, no multicast); a single thread issues
 // tcgen05.mma (UMMA 128 x BN x 16, both operands K-major from shared memory) and releases
 // ring stages with tcgen05.commit; the four warps then read the accumulator with
@@ -21,8 +21,12 @@ namespace {
 
 constexpr int kBM = 128;       // rows per tile == TMEM lanes
 constexpr int kBK = 64;        // K elements per stage: 128 bytes, one swizzle atom
-constexpr int kStages = 4;
 constexpr int kGemmThreads = 128;
+
+// Ring depth: wide tiles use three stages (96 KB) so that two CTAs share an SM and one CTA's
+// epilogue overlaps the other's main loop; narrow tiles (few rows, latency-bound) use eight so
+// that a whole K = 512 reduction is requested at once.
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 128 ? 3 : 8; }
 
 struct GemmArgs {
     void* out;
@@ -30,6 +34,7 @@ struct GemmArgs {
     int m, n, k;
     int out_dtype;
     uint32_t idesc;
+    uint32_t a_bytes;      // bytes one x tile load delivers (box rows x 128)
 };
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
@@ -83,10 +88,11 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
     const GemmArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * kStages + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
+    constexpr int kStages = stages_for(BN);
     constexpr int kTmemCols = BN < 32 ? 32 : BN;
     constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2;
     // the ring must start on a 1024-byte boundary for the 128-byte swizzle
@@ -102,6 +108,8 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     const uint32_t acc_full = bar0 + 8u * (2 * kStages);
 
     if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         for (int i = 0; i < 2 * kStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
         fence_barrier_init();
         failed = 0;
@@ -121,7 +129,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
         for (int it = 0; it < k_iters; ++it) {
             const int s = it % kStages;
             if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
-            mbar_expect_tx(full(s), kABytes + kBBytes);
+            mbar_expect_tx(full(s), a.a_bytes + kBBytes);
             tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, it * kBK, m0, full(s));
             tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, it * kBK, n0, full(s));
         }
@@ -227,7 +235,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ro
 
 template <int BN>
 int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a, void* stream) {
-    const int smem_bytes = kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+    const int smem_bytes = stages_for(BN) * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
     auto kernel = packed_projection_kernel<BN>;
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
@@ -259,16 +267,23 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
         set_error("packed_projection: tensors must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
-    // few rows: narrow tiles so that more CTAs share the weight read; many rows: wide tiles
-    const int bn = (rows <= 128 || n_out % 128 != 0) ? (n_out % 64 == 0 && rows > 32 ? 64 : 32) : 128;
+    // Tile width: with few rows the weight read dominates, so pick the widest tile that still
+    // gives about one CTA per SM; with many rows use wide tiles.
+    int bn = 128;
+    if (n_out % 128 != 0 || (rows <= 128 && n_out / 128 < 100)) bn = 64;
+    if (n_out % 64 != 0 || (rows <= 128 && n_out / 64 < 100 && bn == 64)) bn = 32;
+    // x tile: the box holds only the rows that exist (a multiple of 8, at most 128); the MMA
+    // reads 128 rows of the stage, the rest is never stored
+    const int box_rows = rows >= kBM ? kBM : ((rows + 7) / 8) * 8;
     CUtensorMap mx, mw;
-    if (!make_map(&mx, x, rows, d_in, x_row_stride, kBM, in_dtype) ||
+    if (!make_map(&mx, x, rows, d_in, x_row_stride, box_rows, in_dtype) ||
         !make_map(&mw, weight, n_out, d_in, d_in, bn, in_dtype)) {
         set_error("packed_projection: cuTensorMapEncodeTiled failed");
         return RLM_ERR_LAUNCH;
     }
     GemmArgs a{};
     a.out = out; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
+    a.a_bytes = static_cast<uint32_t>(box_rows) * kBK * 2;
     const uint32_t fmt = in_dtype == RLM_BF16 ? 1u : 0u;
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
               (static_cast<uint32_t>(kBM >> 4) << 24);
