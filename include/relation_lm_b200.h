@@ -151,15 +151,16 @@ int rlm_router_cache_update(
  *   expanded_cache [B,T,2H], operand_cache [B,T,R]       cache_dtype
  *   anchor_index [N] i32, partner_index [N,K] i32
  *   product_weight [H,R]                                 weight_dtype
- *   out [N,K,H] f32
+ *   out [N,K,H] out_dtype (the reference operator returns fp32; a 16-bit output feeds the
+ *   second MLP layer's GEMM without a cast kernel)
  * row_batch == NULL: row i gathers from sequence i.  Indices outside [0,T)
  * (empty partner slots) are clamped; their output is masked by the reduce op.
  */
 int rlm_relation_hidden_cached(
     const void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
     const int32_t* partner_index, const void* product_weight, const int32_t* row_batch,
-    float* out, int n_rows, int n_seq, int max_t, int relation_dim, int hidden_dim, int k_out,
-    int cache_dtype, int weight_dtype, int32_t* status, void* stream);
+    void* out, int n_rows, int n_seq, int max_t, int relation_dim, int hidden_dim, int k_out,
+    int cache_dtype, int weight_dtype, int out_dtype, int32_t* status, void* stream);
 
 /*
  * Same, and first computes the current position's expanded row from
@@ -172,20 +173,24 @@ int rlm_relation_hidden_cached(
 int rlm_relation_hidden_cache_update(
     void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
     const int32_t* partner_index, const void* anchor_weight, const void* partner_weight,
-    const void* product_weight, const void* first_bias, const int64_t* position, float* out,
+    const void* product_weight, const void* first_bias, const int64_t* position, void* out,
     int batch, int max_t, int relation_dim, int hidden_dim, int k_out,
-    int cache_dtype, int weight_dtype, int32_t* status, void* stream);
+    int cache_dtype, int weight_dtype, int out_dtype, int32_t* status, void* stream);
 
 /*
  * Per-partner LayerNorm, active-K softmax and weighted sum.  Replaces
  * relation_lm::relation_norm_reduce
  * (src/relation_lm/kernels/relation_reduce.py:420-450, kernel :360-417).
  *   raw [N,K,D] raw_dtype; partner_scores [N,K] f32; norm_weight, norm_bias [D] param_dtype
- *   out [N,D] f32.  row_position == NULL: all rows use *position.
+ *   out [N,D] f32 (may be NULL when residual is given).  row_position == NULL: all rows use
+ *   *position.  residual (optional, [N,D] f32, updated in place): residual += (*mix) * context,
+ *   the `hidden + sigmoid(mix_logit) * context` of the reference's relation layer
+ *   (src/relation_lm/models/stacked_relation.py:124) with mix a device fp32 scalar.
  */
 int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
+    float* residual, const float* mix,
     int n_rows, int k_out, int dim, int raw_dtype, int param_dtype,
     int32_t* status, void* stream);
 
@@ -201,6 +206,19 @@ int rlm_relation_norm_reduce(
 int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight, void* out,
                           int rows, int d_in, int n_out, int in_dtype, int out_dtype,
                           int32_t* status, void* stream);
+
+/*
+ * LayerNorm fused into the projection, for decode batches (extension):
+ * out[rows, n_out] = LayerNorm(x; gamma, beta, eps) . weight[n_out, d_in]^T with the normalised
+ * rows rounded to the weight dtype, as the reference's `layer_norm(...)` followed by `F.linear`
+ * on a low-precision model does.  gamma = beta = NULL skips the normalisation (plain cast).
+ *   x [rows, d_in] fp32, row stride in ELEMENTS; rows <= 128; d_in a multiple of 64 up to 1024;
+ *   weight bfloat16 / float16 [n_out, d_in]; n_out a multiple of 32; out contiguous, any dtype.
+ */
+int rlm_norm_projection(const float* x, int64_t x_row_stride, const float* gamma,
+                        const float* beta, float eps, const void* weight, void* out, int rows,
+                        int d_in, int n_out, int weight_dtype, int out_dtype, int32_t* status,
+                        void* stream);
 
 /*
  * Decode-state append for every layer of a stack in one launch (extension).  Does what a
@@ -223,6 +241,19 @@ int rlm_sparse_cache_append(
     const void* partner_conv_weight, const int64_t* position, float* out, int layers, int batch,
     int max_t, int n_blocks, int block_size, int packed_dtype, int cache_dtype, int stats_dtype,
     int weight_dtype, int32_t* status, void* stream);
+
+/*
+ * Input embedding of one decode position (extension; the reference computes it for whole
+ * sequences, src/relation_lm/models/relation_lm.py:130-131):
+ * out[b] = (token_table[tokens[b]] + boundary_table[boundaries[b]]) * scale + position_table[*position]
+ *   tokens, boundaries [B] int64; tables [V, d] / [Vb, d] table_dtype; position_table [T, d] f32;
+ *   out [B, d] f32.  Ids outside the tables set RLM_DEV_POSITION and leave the row unwritten.
+ */
+int rlm_decode_embed(const int64_t* tokens, const int64_t* boundaries, const void* token_table,
+                     const void* boundary_table, const float* position_table,
+                     const int64_t* position, float scale, float* out, int batch, int d_model,
+                     int vocab, int boundary_vocab, int max_t, int table_dtype, int32_t* status,
+                     void* stream);
 
 #ifdef __cplusplus
 }

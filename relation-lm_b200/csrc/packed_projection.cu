@@ -201,6 +201,210 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
                      ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+// ------------------------------------------------------------------ LayerNorm + projection
+//
+// out = LayerNorm(x) . w^T for at most 128 fp32 rows (decode batches): every CTA normalises
+// the rows itself (a few KB), writes them as 16-bit values straight into the swizzled
+// K-major layout the tensor core reads, and streams only its BN x K slice of w with TMA.
+// The x tile of K-block kb starts kb * a_stride bytes into the A region, a_stride covering
+// just the row groups that exist; the MMA reads 128 rows from there, rows that do not exist
+// land in accumulator lanes that are never stored.
+
+struct NormGemmArgs {
+    const float* x;
+    const float* gamma;
+    const float* beta;
+    void* out;
+    int32_t* status;
+    int64_t x_stride;
+    float eps;
+    int m, n, k;
+    int w_dtype, out_dtype;
+    uint32_t idesc;
+    uint32_t a_stride;     // bytes between consecutive K-blocks of the x tile
+    uint32_t a_bytes;      // size of the A region (multiple of 1024)
+};
+
+constexpr int kNormMaxPerLane = 4;     // 16-byte chunks per lane: d_in <= 1024
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
+    const __grid_constant__ CUtensorMap map_w, const NormGemmArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+
+    constexpr int kStages = 8;
+    constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kBBytes = BN * kBK * 2;
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* a_tile = base;
+    const uint32_t a_addr = smem_u32(a_tile);
+    const uint32_t ring_addr = a_addr + a.a_bytes;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN;
+    const int k_iters = (a.k + kBK - 1) / kBK;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * kStages);
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        for (int i = 0; i < 2 * kStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        fence_barrier_init();
+        failed = 0;
+        // the weight slice does not depend on the normalisation: request it first
+        for (int it = 0; it < k_iters && it < kStages; ++it) {
+            mbar_expect_tx(full(it), kBBytes);
+            tma_load_2d(ring_addr + it * kBBytes, &map_w, it * kBK, n0, full(it));
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    // LayerNorm of the rows, one warp per row, lane l owns the 16-byte chunks l, l+32, ...
+    const int chunks = a.k / 8;
+    for (int r = warp; r < a.m; r += kGemmThreads / 32) {
+        const float* row = a.x + r * a.x_stride;
+        float v[kNormMaxPerLane][8];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kNormMaxPerLane; ++i) {
+            const int c = lane + 32 * i;
+            if (c < chunks) {
+                const float4 lo = *reinterpret_cast<const float4*>(row + 8 * c);
+                const float4 hi = *reinterpret_cast<const float4*>(row + 8 * c + 4);
+                v[i][0] = lo.x; v[i][1] = lo.y; v[i][2] = lo.z; v[i][3] = lo.w;
+                v[i][4] = hi.x; v[i][5] = hi.y; v[i][6] = hi.z; v[i][7] = hi.w;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum += v[i][e];
+            }
+        }
+        float mean = 0.0f, inv = 1.0f;
+        if (a.gamma) {
+            mean = warp_sum(sum) / static_cast<float>(a.k);
+            float sq = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kNormMaxPerLane; ++i)
+                if (lane + 32 * i < chunks)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) { float d = v[i][e] - mean; sq = fmaf(d, d, sq); }
+            inv = rsqrtf(warp_sum(sq) / static_cast<float>(a.k) + a.eps);
+        }
+#pragma unroll
+        for (int i = 0; i < kNormMaxPerLane; ++i) {
+            const int c = lane + 32 * i;
+            if (c >= chunks) continue;
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+                float y0 = (v[i][e] - mean) * inv, y1 = (v[i][e + 1] - mean) * inv;
+                if (a.gamma) {
+                    y0 = fmaf(y0, a.gamma[8 * c + e], a.beta[8 * c + e]);
+                    y1 = fmaf(y1, a.gamma[8 * c + e + 1], a.beta[8 * c + e + 1]);
+                }
+                if (a.w_dtype == RLM_BF16) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                    packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                } else {
+                    __half2 h = __floats2half2_rn(y0, y1);
+                    packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            // K-major, 128-byte swizzle: 16-byte chunk index xor (row mod 8)
+            const int kb = c >> 3, c16 = c & 7;
+            unsigned char* dst = a_tile + kb * a.a_stride + (r >> 3) * 1024 + (r & 7) * 128 +
+                                 ((c16 ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+    fence_proxy_async();     // generic-proxy writes of the x tile -> visible to the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (tid == 0) {
+        for (int it = kStages; it < k_iters; ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
+            mbar_expect_tx(full(s), kBBytes);
+            tma_load_2d(ring_addr + s * kBBytes, &map_w, it * kBK, n0, full(s));
+        }
+    } else if (tid == 32) {
+        bool ok = true;
+        for (int it = 0; it < k_iters && ok; ++it) {
+            const int s = it % kStages;
+            ok = mbar_wait(full(s), (it / kStages) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = smem_desc_sw128(a_addr + it * a.a_stride);
+            const uint64_t db = smem_desc_sw128(ring_addr + s * kBBytes);
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)
+                umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, a.idesc, (it > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(empty(s));
+        }
+        if (!ok) failed = 1;
+        umma_commit(acc_full);
+    }
+    __syncwarp();
+
+    bool ready = mbar_wait(acc_full, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+    if (!__syncthreads_or(!ready)) {
+        const int row = warp * 32 + lane;
+        if (warp * 32 < a.m) {      // warps whose 32 rows do not exist skip the read-back
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < a.m) {
+                    const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
+                    if (a.out_dtype == RLM_F32) {
+                        float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            o[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                               __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    } else {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+                            if (a.out_dtype == RLM_BF16) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                                packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                            } else {
+                                __half2 h = __floats2half2_rn(lo, hi);
+                                packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        }
+                        uint4* o = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + at);
+                        o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                }
+            }
+        }
+    } else if (tid == 0 && a.status) {
+        atomicOr(a.status, RLM_DEV_TIMEOUT);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -245,8 +449,67 @@ int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a,
     return check_launch("packed_projection_kernel");
 }
 
+template <int BN>
+int launch_norm_gemm(const CUtensorMap& mw, const NormGemmArgs& a, void* stream) {
+    const int smem_bytes = static_cast<int>(a.a_bytes) + 8 * BN * kBK * 2 + 1024;
+    if (smem_bytes > kSmemDynamicLimit) {
+        set_error("norm_projection: rows x d_in too large for the shared-memory x tile");
+        return RLM_ERR_SMEM;
+    }
+    auto kernel = norm_projection_kernel<BN>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    kernel<<<a.n / BN, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mw, a);
+    count_launch();
+    return check_launch("norm_projection_kernel");
+}
+
 }  // namespace
 }  // namespace rlm
+
+extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const float* gamma,
+                                   const float* beta, float eps, const void* weight, void* out,
+                                   int rows, int d_in, int n_out, int weight_dtype, int out_dtype,
+                                   int32_t* status, void* stream) {
+    using namespace rlm;
+    if (rows == 0) return RLM_OK;
+    if (!x || !weight || !out || ((gamma == nullptr) != (beta == nullptr))) {
+        set_error("norm_projection: NULL pointer (gamma and beta go together)");
+        return RLM_ERR_NULL;
+    }
+    if (rows < 0 || rows > kBM || d_in < 64 || d_in % 64 != 0 || d_in > 256 * kNormMaxPerLane ||
+        n_out < 32 || n_out % 32 != 0 || x_row_stride < d_in || x_row_stride % 4 != 0) {
+        set_error("norm_projection: need rows <= 128, d_in a multiple of 64 up to 1024, n_out a multiple of 32");
+        return RLM_ERR_SHAPE;
+    }
+    if ((weight_dtype != RLM_BF16 && weight_dtype != RLM_F16) || !valid_dtype(out_dtype)) {
+        set_error("norm_projection: weights must be bfloat16 or float16");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || (gamma && (!aligned16(gamma) || !aligned16(beta)))) {
+        set_error("norm_projection: tensors must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    int bn = 128;
+    if (n_out % 128 != 0 || n_out / 128 < 100) bn = 64;
+    if (n_out % 64 != 0 || (n_out / 64 < 100 && bn == 64)) bn = 32;
+    CUtensorMap mw;
+    if (!make_map(&mw, weight, n_out, d_in, d_in, bn, weight_dtype)) {
+        set_error("norm_projection: cuTensorMapEncodeTiled failed");
+        return RLM_ERR_LAUNCH;
+    }
+    NormGemmArgs a{};
+    a.x = x; a.gamma = gamma; a.beta = beta; a.out = out; a.status = status; a.x_stride = x_row_stride;
+    a.eps = eps; a.m = rows; a.n = n_out; a.k = d_in; a.w_dtype = weight_dtype; a.out_dtype = out_dtype;
+    const uint32_t fmt = weight_dtype == RLM_BF16 ? 1u : 0u;
+    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+              (static_cast<uint32_t>(kBM >> 4) << 24);
+    a.a_stride = static_cast<uint32_t>((rows + 7) / 8) * 1024u;
+    a.a_bytes = (static_cast<uint32_t>(d_in / kBK) - 1u) * a.a_stride + kBM * kBK * 2;
+    if (bn == 32) return launch_norm_gemm<32>(mw, a, stream);
+    if (bn == 64) return launch_norm_gemm<64>(mw, a, stream);
+    return launch_norm_gemm<128>(mw, a, stream);
+}
 
 extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
                                      void* out, int rows, int d_in, int n_out, int in_dtype,

@@ -47,10 +47,10 @@ struct HiddenArgs {
     const void* first_bias;
     const int64_t* position;
     const int32_t* row_batch;
-    float* out;
+    void* out;
     int32_t* status;
     int n_rows, n_seq, max_t, rdim, hdim, k_out;
-    int cache_dtype, weight_dtype;
+    int cache_dtype, weight_dtype, out_dtype;
 };
 
 __device__ __forceinline__ float gelu_erf(float x) {
@@ -304,8 +304,8 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
                     if (sub_a[e]) ba = fa + load_scalar(a.first_bias, h0 + hh + j, a.weight_dtype);
                     if (sub_p[e]) bp = fp;
                 }
-                a.out[(static_cast<size_t>(out_row[e]) * K + out_k[e]) * H + h0 + hh + j] =
-                    gelu_erf(v + (ba + bp));
+                store_scalar(a.out, (static_cast<int64_t>(out_row[e]) * K + out_k[e]) * H + h0 + hh + j,
+                             a.out_dtype, gelu_erf(v + (ba + bp)));
             }
         }
         RLM_PROBE(5);
@@ -359,7 +359,7 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         set_error("relation_hidden: without row_batch the rows must equal the sequences");
         return RLM_ERR_SHAPE;
     }
-    if (!valid_dtype(a.cache_dtype) || !valid_dtype(a.weight_dtype)) {
+    if (!valid_dtype(a.cache_dtype) || !valid_dtype(a.weight_dtype) || !valid_dtype(a.out_dtype)) {
         set_error("relation_hidden: unknown dtype code");
         return RLM_ERR_DTYPE;
     }
@@ -387,7 +387,9 @@ struct NormArgs {
     const void* bias;
     const int64_t* position;
     const int32_t* row_position;
-    float* out;
+    float* out;               // context [N, D], or NULL when only the residual is wanted
+    float* residual;          // optional [N, D] fp32: residual += (*mix) * context
+    const float* mix;
     int32_t* status;
     float eps;
     int n_rows, k_out, dim, raw_dtype, param_dtype;
@@ -476,7 +478,11 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
         float total = 0.0f;
 #pragma unroll
         for (int w = 0; w < kNormWarps; ++w) total += partial[w * D + c];
-        a.out[static_cast<size_t>(row) * D + c] = total;
+        if (a.out) a.out[static_cast<size_t>(row) * D + c] = total;
+        if (a.residual) {
+            const size_t at = static_cast<size_t>(row) * D + c;
+            a.residual[at] = fmaf(*a.mix, total, a.residual[at]);
+        }
     }
 }
 
@@ -485,24 +491,24 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 
 extern "C" int rlm_relation_hidden_cached(
     const void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
-    const int32_t* partner_index, const void* product_weight, const int32_t* row_batch, float* out,
+    const int32_t* partner_index, const void* product_weight, const int32_t* row_batch, void* out,
     int n_rows, int n_seq, int max_t, int relation_dim, int hidden_dim, int k_out, int cache_dtype,
-    int weight_dtype, int32_t* status, void* stream) {
+    int weight_dtype, int out_dtype, int32_t* status, void* stream) {
     rlm::HiddenArgs a{};
     a.expanded_cache = const_cast<void*>(expanded_cache); a.operand_cache = operand_cache;
     a.anchor_index = anchor_index; a.partner_index = partner_index; a.product_weight = product_weight;
     a.row_batch = row_batch; a.out = out; a.status = status;
     a.n_rows = n_rows; a.n_seq = n_seq; a.max_t = max_t; a.rdim = relation_dim; a.hdim = hidden_dim;
-    a.k_out = k_out; a.cache_dtype = cache_dtype; a.weight_dtype = weight_dtype;
+    a.k_out = k_out; a.cache_dtype = cache_dtype; a.weight_dtype = weight_dtype; a.out_dtype = out_dtype;
     return rlm::launch_hidden(a, false, stream);
 }
 
 extern "C" int rlm_relation_hidden_cache_update(
     void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
     const int32_t* partner_index, const void* anchor_weight, const void* partner_weight,
-    const void* product_weight, const void* first_bias, const int64_t* position, float* out,
+    const void* product_weight, const void* first_bias, const int64_t* position, void* out,
     int batch, int max_t, int relation_dim, int hidden_dim, int k_out, int cache_dtype,
-    int weight_dtype, int32_t* status, void* stream) {
+    int weight_dtype, int out_dtype, int32_t* status, void* stream) {
     rlm::HiddenArgs a{};
     a.expanded_cache = expanded_cache; a.operand_cache = operand_cache;
     a.anchor_index = anchor_index; a.partner_index = partner_index;
@@ -510,17 +516,19 @@ extern "C" int rlm_relation_hidden_cache_update(
     a.product_weight = product_weight; a.first_bias = first_bias; a.position = position;
     a.out = out; a.status = status;
     a.n_rows = batch; a.n_seq = batch; a.max_t = max_t; a.rdim = relation_dim; a.hdim = hidden_dim;
-    a.k_out = k_out; a.cache_dtype = cache_dtype; a.weight_dtype = weight_dtype;
+    a.k_out = k_out; a.cache_dtype = cache_dtype; a.weight_dtype = weight_dtype; a.out_dtype = out_dtype;
     return rlm::launch_hidden(a, true, stream);
 }
 
 extern "C" int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
-    const int64_t* position, const int32_t* row_position, float norm_eps, float* out, int n_rows,
+    const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
+    float* residual, const float* mix, int n_rows,
     int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
     using namespace rlm;
     if (n_rows == 0) return RLM_OK;
-    if (!raw || !partner_scores || !norm_weight || !norm_bias || !out || (!position && !row_position)) {
+    if (!raw || !partner_scores || !norm_weight || !norm_bias || (!out && !residual) ||
+        (residual && !mix) || (!position && !row_position)) {
         set_error("relation_norm_reduce: NULL pointer");
         return RLM_ERR_NULL;
     }
@@ -535,6 +543,7 @@ extern "C" int rlm_relation_norm_reduce(
     NormArgs a{};
     a.raw = raw; a.scores = partner_scores; a.weight = norm_weight; a.bias = norm_bias;
     a.position = position; a.row_position = row_position; a.out = out; a.status = status;
+    a.residual = residual; a.mix = mix;
     a.eps = norm_eps; a.n_rows = n_rows; a.k_out = k_out; a.dim = dim;
     a.raw_dtype = raw_dtype; a.param_dtype = param_dtype;
     int smem_bytes = kNormWarps * dim * 4;

@@ -22,7 +22,11 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from relation_lm.inference.routed_model import RoutedRelationLM
-from relation_lm.kernels.relation_reduce import relation_hidden_cache_update, relation_norm_reduce
+from relation_lm.kernels.packed_projection import decode_embed, norm_projection
+from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update,
+                                                 relation_hidden_cache_update_out,
+                                                 relation_norm_reduce,
+                                                 relation_norm_reduce_residual)
 from relation_lm.kernels.relation_select import relation_select_packed
 from relation_lm.kernels.router_cache import sparse_cache_append
 
@@ -50,6 +54,16 @@ class StatefulDecoder:
         self.position = torch.zeros((), device=self.device, dtype=torch.int64)
         self.last_selection: list[tuple[Tensor, Tensor]] = []
         self._graph = None
+        # Low-precision decode batches take the fused path: LayerNorm folded into the tcgen05
+        # projections, 16-bit relation hidden states, residual update inside norm-reduce.
+        self.fused = (dtype in (torch.bfloat16, torch.float16) and self.batch <= 128
+                      and cfg.d_model % 64 == 0 and cfg.d_model <= 1024)
+        if self.fused:
+            self.relation_hidden = zeros(B, cfg.k_max, H)
+            self.head_weight = torch.cat((self.w["token_embedding"], self.w["boundary_w"]), 0).contiguous()
+            pad = (-self.head_weight.size(0)) % 32
+            if pad:
+                self.head_weight = torch.cat((self.head_weight, zeros(pad, cfg.d_model)), 0).contiguous()
 
     # ------------------------------------------------------------------ state
     def reset(self) -> None:
@@ -67,6 +81,8 @@ class StatefulDecoder:
     def step(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool = False):
         """Consume one token per sequence at the current position; returns (token logits
         ``[B, V]``, boundary logits ``[B, Vb]``) and advances the position."""
+        if self.fused:
+            return self._step_fused(tokens, boundaries, keep_selection)
         cfg, w = self.config, self.w
         pos = self.position
         x = (F.embedding(tokens, w["token_embedding"]) + F.embedding(boundaries, w["boundary_embedding"])).float()
@@ -102,6 +118,45 @@ class StatefulDecoder:
         final = F.layer_norm(hidden, (cfg.d_model,), w["final_norm_w"], w["final_norm_b"], cfg.norm_eps).to(self.dtype)
         token_logits = F.linear(final, w["token_embedding"])
         boundary_logits = F.linear(final, w["boundary_w"], w["boundary_b"])
+        pos.add_(1)
+        return token_logits, boundary_logits
+
+    def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool):
+        """The same step with the elementwise glue folded into the library's kernels:
+        5 launches per layer (norm+query projection, select, relation hidden, second MLP layer
+        GEMM, norm-reduce+residual)."""
+        cfg, w = self.config, self.w
+        pos = self.position
+        tokens, boundaries = tokens.contiguous(), boundaries.contiguous()
+        hidden = decode_embed(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
+                              w["position_embedding"], pos, self.input_scale)
+        packed = norm_projection(hidden, w["memory_norm_w"], w["memory_norm_b"], w["w_packed"], cfg.norm_eps)
+        sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
+                            self.partner_anchor_cache, *self.router_caches, *self.router_stats,
+                            w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+        if keep_selection:
+            self.last_selection = []
+        K = cfg.k_max
+        for l in range(cfg.layers):
+            q = norm_projection(hidden, w["input_norm_w"][l], w["input_norm_b"][l], w["w_query"][l], cfg.norm_eps)
+            anchor, _, partner, partner_score = relation_select_packed(
+                q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
+                self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
+                self.partner_anchor_cache[l], self.partner_keys[l], self.router_stats[2][l],
+                self.router_stats[3][l], w["partner_gamma"][l], w["partner_bias"][l], pos,
+                cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+            relation_hidden_cache_update_out(
+                self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
+                w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
+                w["first_bias"][l], pos)
+            raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])                # [B, K, d]
+            relation_norm_reduce_residual(raw, partner_score, w["relation_norm_w"][l],
+                                          w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l])
+            if keep_selection:
+                self.last_selection.append((anchor, partner))
+        logits = norm_projection(hidden, w["final_norm_w"], w["final_norm_b"], self.head_weight, cfg.norm_eps)
+        token_logits = logits[:, :cfg.vocab_size]
+        boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size] + w["boundary_b"]
         pos.add_(1)
         return token_logits, boundary_logits
 

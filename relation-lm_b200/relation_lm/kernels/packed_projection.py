@@ -37,3 +37,57 @@ def packed_projection(x: Tensor, weight: Tensor) -> Tensor:
 @packed_projection.register_fake
 def _(x, weight):
     return x.new_empty((x.size(0), weight.size(0)))
+
+
+@torch.library.custom_op("relation_lm::norm_projection", mutates_args=(), device_types="cuda")
+def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: Tensor,
+                    norm_eps: float) -> Tensor:
+    """``layer_norm(x) @ weight.T`` in one launch for at most 128 fp32 rows: the rows are
+    normalised in fp32, rounded to the weight dtype and multiplied on the tensor cores."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(norm_weight=norm_weight, norm_bias=norm_bias, weight=weight)
+    if x.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_bias.dtype != torch.float32:
+        raise ValueError("norm_projection takes fp32 rows and fp32 LayerNorm parameters")
+    if weight.dim() != 2 or weight.size(1) != x.size(1) or norm_weight.numel() != x.size(1):
+        raise ValueError("weight must be [n_out, d_in] and the norm parameters [d_in]")
+    rows, d_in = x.shape
+    out = torch.empty((rows, weight.size(0)), device=device, dtype=weight.dtype)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_norm_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(norm_weight), _abi.ptr(norm_bias), float(norm_eps),
+            _abi.ptr(weight), _abi.ptr(out), rows, d_in, weight.size(0), _abi.code(weight),
+            _abi.code(out), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@norm_projection.register_fake
+def _(x, norm_weight, norm_bias, weight, norm_eps):
+    return x.new_empty((x.size(0), weight.size(0)), dtype=weight.dtype)
+
+
+@torch.library.custom_op("relation_lm::decode_embed", mutates_args=(), device_types="cuda")
+def decode_embed(tokens: Tensor, boundaries: Tensor, token_table: Tensor, boundary_table: Tensor,
+                 position_table: Tensor, position: Tensor, scale: float) -> Tensor:
+    """``(token_table[tokens] + boundary_table[boundaries]) * scale + position_table[position]``
+    for one decode position, ``[B, d]`` fp32."""
+    device = _abi.require_cuda_contiguous(tokens=tokens, boundaries=boundaries,
+                                          token_table=token_table, boundary_table=boundary_table,
+                                          position_table=position_table)
+    _abi.require_position(position, device)
+    if tokens.dtype != torch.int64 or boundaries.dtype != torch.int64 or position_table.dtype != torch.float32:
+        raise ValueError("ids must be int64 and the position table float32")
+    batch, d_model = tokens.numel(), token_table.size(1)
+    out = torch.empty((batch, d_model), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_decode_embed(
+            _abi.ptr(tokens), _abi.ptr(boundaries), _abi.ptr(token_table), _abi.ptr(boundary_table),
+            _abi.ptr(position_table), _abi.ptr(position), float(scale), _abi.ptr(out), batch, d_model,
+            token_table.size(0), boundary_table.size(0), position_table.size(0),
+            _abi.same_dtype("embedding table", token_table, boundary_table),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@decode_embed.register_fake
+def _(tokens, boundaries, token_table, boundary_table, position_table, position, scale):
+    return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)

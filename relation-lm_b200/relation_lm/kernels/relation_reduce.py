@@ -92,7 +92,7 @@ def relation_hidden_cached(
             _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
             _abi.ptr(partner_index), _abi.ptr(product_weight), None, _abi.ptr(out), batch, batch,
             max_t, rdim, hdim, k_out, _abi.same_dtype("cache", expanded_cache, operand_cache),
-            _abi.code(product_weight), _abi.ptr(_abi.status_tensor(device)),
+            _abi.code(product_weight), _abi.code(out), _abi.ptr(_abi.status_tensor(device)),
             _abi.stream_ptr(device)))
     return out
 
@@ -138,7 +138,7 @@ def relation_hidden_cache_update(
             batch, max_t, rdim, hdim, k_out,
             _abi.same_dtype("cache", expanded_cache, operand_cache),
             _abi.same_dtype("weight", anchor_weight, partner_weight, product_weight, first_bias),
-            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+            _abi.code(out), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
     return out
 
 
@@ -171,7 +171,7 @@ def relation_norm_reduce(
     with _abi.device_guard(device):
         _abi.check(_abi.LIB.rlm_relation_norm_reduce(
             _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
-            _abi.ptr(position), None, float(norm_eps), _abi.ptr(out), batch, k_out, dim,
+            _abi.ptr(position), None, float(norm_eps), _abi.ptr(out), None, None, batch, k_out, dim,
             _abi.code(raw), _abi.same_dtype("norm parameter", norm_weight, norm_bias),
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
     return out
@@ -180,3 +180,91 @@ def relation_norm_reduce(
 @relation_norm_reduce.register_fake
 def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps):
     return raw.new_empty((raw.size(0), raw.size(2)), dtype=torch.float32)
+
+
+def _hidden_update_into(out, expanded_cache, operand_cache, anchor_index, partner_index,
+                        anchor_weight, partner_weight, product_weight, first_bias, position):
+    device = _abi.require_cuda_contiguous(
+        out=out, expanded_cache=expanded_cache, operand_cache=operand_cache,
+        anchor_index=anchor_index, partner_index=partner_index, anchor_weight=anchor_weight,
+        partner_weight=partner_weight, product_weight=product_weight, first_bias=first_bias)
+    _abi.require_position(position, device)
+    batch, max_t, rdim = operand_cache.shape
+    hdim, k_out = product_weight.size(0), partner_index.size(1)
+    _check_indices(anchor_index, partner_index, batch)
+    if out.shape != (batch, k_out, hdim) or expanded_cache.shape != (batch, max_t, 2 * hdim):
+        raise ValueError("expected out [B, K, H] and expanded_cache [B, T, 2H]")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cache_update(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(anchor_weight), _abi.ptr(partner_weight),
+            _abi.ptr(product_weight), _abi.ptr(first_bias), _abi.ptr(position), _abi.ptr(out),
+            batch, max_t, rdim, hdim, k_out,
+            _abi.same_dtype("cache", expanded_cache, operand_cache),
+            _abi.same_dtype("weight", anchor_weight, partner_weight, product_weight, first_bias),
+            _abi.code(out), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@torch.library.custom_op("relation_lm::relation_hidden_cache_update_out",
+                         mutates_args=("out", "expanded_cache"), device_types="cuda")
+def relation_hidden_cache_update_out(
+    out: Tensor,
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    anchor_weight: Tensor,
+    partner_weight: Tensor,
+    product_weight: Tensor,
+    first_bias: Tensor,
+    position: Tensor,
+) -> None:
+    """``relation_hidden_cache_update`` writing into a caller-owned ``out [B, K, H]`` of any
+    float dtype (extension: a 16-bit ``out`` feeds the second MLP layer without a cast)."""
+    _hidden_update_into(out, expanded_cache, operand_cache, anchor_index, partner_index,
+                        anchor_weight, partner_weight, product_weight, first_bias, position)
+
+
+@relation_hidden_cache_update_out.register_fake
+def _(out, expanded_cache, operand_cache, anchor_index, partner_index, anchor_weight,
+      partner_weight, product_weight, first_bias, position):
+    return None
+
+
+@torch.library.custom_op("relation_lm::relation_norm_reduce_residual", mutates_args=("hidden",),
+                         device_types="cuda")
+def relation_norm_reduce_residual(
+    raw: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+    hidden: Tensor,
+    mix: Tensor,
+) -> None:
+    """``relation_norm_reduce`` fused with the layer's residual update (extension):
+    ``hidden += mix * context`` in place, ``hidden [B, D]`` fp32, ``mix`` a 0-d fp32 tensor
+    holding ``sigmoid(mix_logit)``."""
+    device = _abi.require_cuda_contiguous(raw=raw, partner_scores=partner_scores,
+                                          norm_weight=norm_weight, norm_bias=norm_bias,
+                                          hidden=hidden, mix=mix)
+    _abi.require_position(position, device)
+    batch, k_out, dim = raw.shape
+    if partner_scores.shape != (batch, k_out) or partner_scores.dtype != torch.float32:
+        raise ValueError("partner_scores must be float32 [B, K]")
+    if hidden.shape != (batch, dim) or hidden.dtype != torch.float32 or mix.dtype != torch.float32 \
+            or mix.numel() != 1:
+        raise ValueError("hidden must be float32 [B, D] and mix a one-element float32 tensor")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_norm_reduce(
+            _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
+            _abi.ptr(position), None, float(norm_eps), None, _abi.ptr(hidden), _abi.ptr(mix),
+            batch, k_out, dim, _abi.code(raw),
+            _abi.same_dtype("norm parameter", norm_weight, norm_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_norm_reduce_residual.register_fake
+def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, mix):
+    return None

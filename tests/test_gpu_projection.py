@@ -56,3 +56,30 @@ def test_projection_rejects_fp32_operands():
 
     with pytest.raises(ValueError):
         packed_projection(torch.randn(4, 512, device="cuda"), torch.randn(512, 512, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,d_in,n_out", [(1, 512, 256), (8, 512, 3072), (8, 512, 16256), (5, 576, 512),
+                                             (33, 768, 256), (100, 512, 512), (64, 1024, 96), (128, 512, 64)])
+def test_norm_projection_matches_layer_norm_then_linear(rows, d_in, n_out, dtype):
+    from relation_lm.kernels.packed_projection import norm_projection
+
+    g = torch.Generator().manual_seed(rows * 13 + d_in + n_out)
+    wide = torch.randn(rows, d_in + 64, generator=g) * 3 + 0.5
+    x = wide[:, :d_in]                                        # strided rows
+    gamma = torch.rand(d_in, generator=g) + 0.5
+    beta = torch.randn(d_in, generator=g) * 0.1
+    w = (torch.randn(n_out, d_in, generator=g) * 0.05).to(dtype)
+    got = norm_projection(wide.cuda()[:, :d_in], gamma.cuda(), beta.cuda(), w.cuda(), 1e-5).float().cpu()
+    normalized = F.layer_norm(x, (d_in,), gamma, beta, 1e-5).to(dtype)
+    want = oracle.linear(normalized, w)
+    assert torch.allclose(got, want, atol=2e-2, rtol=1e-2), (got - want).abs().max()
+    assert_status_clear()
+
+
+def test_norm_projection_rejects_a_tile_beyond_shared_memory():
+    from relation_lm.kernels.packed_projection import norm_projection
+
+    with pytest.raises(ValueError):
+        norm_projection(torch.randn(128, 1024, device="cuda"), torch.ones(1024, device="cuda"),
+                        torch.zeros(1024, device="cuda"), torch.randn(96, 1024, device="cuda").bfloat16(), 1e-5)
