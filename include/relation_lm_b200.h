@@ -243,6 +243,28 @@ int rlm_sparse_cache_append(
     int weight_dtype, int32_t* status, void* stream);
 
 /*
+ * Fused relation tail (extension): second relation-MLP layer + relation_norm_reduce + residual.
+ * Does in one launch what a reference decode step does with F.linear(hidden, W2, b2)
+ * (benchmarks/benchmark_relation_reduce.py:63) followed by relation_lm::relation_norm_reduce
+ * (src/relation_lm/kernels/relation_reduce.py:420-450) and `hidden + sigmoid(mix) * context`
+ * (src/relation_lm/models/stacked_relation.py:124).
+ *   relation_hidden [B, K, H] and second_weight [d, H], second_bias [d]: bfloat16 or float16 (dtype)
+ *   partner_scores [B, K] f32; norm_weight, norm_bias [d] f32; position device int64
+ *   residual [B, d] f32 (optional, += (*mix) * context), context [B, d] f32 (optional output)
+ *   scratch: caller-owned device memory of at least rlm_relation_tail_scratch_bytes() bytes,
+ *   ZERO before the first call; the kernel leaves it zero again, so one buffer serves every
+ *   call that is ordered on a stream.  Calls that overlap on the GPU need separate buffers.
+ *   K must divide 128; d a multiple of 64 up to 1024; H a multiple of 8.
+ */
+int64_t rlm_relation_tail_scratch_bytes(int batch, int k_out, int d_model);
+int rlm_relation_tail(const void* relation_hidden, const void* second_weight,
+                      const void* second_bias, const float* partner_scores,
+                      const float* norm_weight, const float* norm_bias, const int64_t* position,
+                      float norm_eps, float* residual, const float* mix, float* context,
+                      void* scratch, int64_t scratch_bytes, int batch, int k_out, int d_model,
+                      int hidden_dim, int dtype, int32_t* status, void* stream);
+
+/*
  * Input embedding of one decode position (extension; the reference computes it for whole
  * sequences, src/relation_lm/models/relation_lm.py:130-131):
  * out[b] = (token_table[tokens[b]] + boundary_table[boundaries[b]]) * scale + position_table[*position]

@@ -12,15 +12,11 @@
 // Replaces the F.linear of src/relation_lm/inference/packed_cache.py:52-57 of the reference
 // project (and serves the query-side router projections, which have the same shape).
 
-#include <cuda.h>
-
-#include "rlm_common.cuh"
+#include "rlm_tcgen05.cuh"
 
 namespace rlm {
 namespace {
 
-constexpr int kBM = 128;       // rows per tile == TMEM lanes
-constexpr int kBK = 64;        // K elements per stage: 128 bytes, one swizzle atom
 constexpr int kGemmThreads = 128;
 
 // Ring depth: wide tiles use three stages (96 KB) so that two CTAs share an SM and one CTA's
@@ -36,52 +32,6 @@ struct GemmArgs {
     uint32_t idesc;
     uint32_t a_bytes;      // bytes one x tile load delivers (box rows x 128)
 };
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
-// 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading byte offset
-// unused (1), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                         uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(addr));
-}
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
@@ -403,38 +353,6 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"(kTmemCols) : "memory");
-}
-
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiled>(p);
-    }();
-    return fn;
-}
-
-// [rows, cols] row-major 16-bit matrix, box = box_rows x 64 columns, 128-byte swizzle, zero fill.
-bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t row_stride_elems,
-              int box_rows, int dtype) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_elems) * 2};
-    cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(box_rows)};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMapDataType dt = dtype == RLM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN>

@@ -26,14 +26,14 @@ from relation_lm.kernels.packed_projection import decode_embed, norm_projection
 from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update,
                                                  relation_hidden_cache_update_out,
                                                  relation_norm_reduce,
-                                                 relation_norm_reduce_residual)
+                                                 relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
 from relation_lm.kernels.router_cache import sparse_cache_append
 
 
 class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
-                 dtype: torch.dtype = torch.bfloat16) -> None:
+                 dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False) -> None:
         cfg = model.config
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
         self.w = model.decode_weights(self.device, dtype)
@@ -58,6 +58,9 @@ class StatefulDecoder:
         # projections, 16-bit relation hidden states, residual update inside norm-reduce.
         self.fused = (dtype in (torch.bfloat16, torch.float16) and self.batch <= 128
                       and cfg.d_model % 64 == 0 and cfg.d_model <= 1024)
+        # The single-launch tail (second MLP layer + norm-reduce + residual) is optional: at
+        # decode batch sizes its one-CTA finalisation costs more than the launch it saves.
+        self.fused_tail = fused_tail and self.fused and 128 % cfg.k_max == 0 and cfg.k_max <= 32
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.head_weight = torch.cat((self.w["token_embedding"], self.w["boundary_w"]), 0).contiguous()
@@ -123,8 +126,8 @@ class StatefulDecoder:
 
     def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool):
         """The same step with the elementwise glue folded into the library's kernels:
-        5 launches per layer (norm+query projection, select, relation hidden, second MLP layer
-        GEMM, norm-reduce+residual)."""
+        5 launches per layer (norm + query projection, select, relation hidden, second MLP layer
+        GEMM, norm-reduce + residual), or 4 with the fused tail."""
         cfg, w = self.config, self.w
         pos = self.position
         tokens, boundaries = tokens.contiguous(), boundaries.contiguous()
@@ -149,9 +152,14 @@ class StatefulDecoder:
                 self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
                 w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
                 w["first_bias"][l], pos)
-            raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])                # [B, K, d]
-            relation_norm_reduce_residual(raw, partner_score, w["relation_norm_w"][l],
-                                          w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l])
+            if self.fused_tail:
+                relation_tail(self.relation_hidden, w["w2"][l], w["b2"][l], partner_score,
+                              w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,
+                              hidden, w["mix"][l])
+            else:
+                raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])            # [B, K, d]
+                relation_norm_reduce_residual(raw, partner_score, w["relation_norm_w"][l],
+                                              w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l])
             if keep_selection:
                 self.last_selection.append((anchor, partner))
         logits = norm_projection(hidden, w["final_norm_w"], w["final_norm_b"], self.head_weight, cfg.norm_eps)

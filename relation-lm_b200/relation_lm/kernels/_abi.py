@@ -23,6 +23,7 @@ PROTOTYPES = {
     "rlm_relation_norm_reduce": [_P] * 6 + [_F, _P, _P, _P] + [_I] * 5 + [_P, _P],
     "rlm_packed_projection": [_P, _L, _P, _P] + [_I] * 5 + [_P, _P],
     "rlm_norm_projection": [_P, _L, _P, _P, _F, _P, _P] + [_I] * 5 + [_P, _P],
+    "rlm_relation_tail": [_P] * 7 + [_F] + [_P] * 4 + [_L] + [_I] * 5 + [_P, _P],
     "rlm_decode_embed": [_P] * 6 + [_F, _P] + [_I] * 6 + [_P, _P],
     "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
 }
@@ -41,6 +42,8 @@ def _load() -> ctypes.CDLL:
     lib.rlm_abi_version.restype = ctypes.c_int
     lib.rlm_last_error.restype = ctypes.c_char_p
     lib.rlm_launch_count.restype = ctypes.c_int64
+    lib.rlm_relation_tail_scratch_bytes.argtypes = [_I, _I, _I]
+    lib.rlm_relation_tail_scratch_bytes.restype = ctypes.c_int64
     if lib.rlm_abi_version() != 1:
         raise ImportError("librelation_lm_b200.so has an unexpected ABI version")
     return lib

@@ -268,3 +268,66 @@ def relation_norm_reduce_residual(
 @relation_norm_reduce_residual.register_fake
 def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, mix):
     return None
+
+
+_TAIL_SCRATCH: dict[tuple[int, int], Tensor] = {}
+
+
+def _tail_scratch(device: torch.device, nbytes: int) -> Tensor:
+    """Zero-initialised per-device scratch of the fused tail; grown on demand, reused after."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    buf = _TAIL_SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _TAIL_SCRATCH[key] = buf
+    return buf
+
+
+@torch.library.custom_op("relation_lm::relation_tail", mutates_args=("hidden",), device_types="cuda")
+def relation_tail(
+    relation_hidden: Tensor,
+    second_weight: Tensor,
+    second_bias: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+    hidden: Tensor,
+    mix: Tensor,
+) -> None:
+    """Second relation-MLP layer, ``relation_norm_reduce`` and the residual update in one launch
+    (extension): ``hidden += mix * norm_reduce(relation_hidden @ W2.T + b2, scores)``.
+    ``relation_hidden [B, K, H]``, ``second_weight [d, H]`` and ``second_bias [d]`` share
+    bfloat16 or float16; ``hidden [B, d]`` and the norm parameters are fp32.  The split-K
+    partial sums meet in a per-device scratch buffer that is allocated once (first call on a
+    device, before any stream capture) and left zero by every launch."""
+    device = _abi.require_cuda_contiguous(
+        relation_hidden=relation_hidden, second_weight=second_weight, second_bias=second_bias,
+        partner_scores=partner_scores, norm_weight=norm_weight, norm_bias=norm_bias,
+        hidden=hidden, mix=mix)
+    _abi.require_position(position, device)
+    batch, k_out, hdim = relation_hidden.shape
+    dim = second_weight.size(0)
+    if second_weight.shape != (dim, hdim) or second_bias.numel() != dim or hidden.shape != (batch, dim):
+        raise ValueError("expected second_weight [d, H], second_bias [d] and hidden [B, d]")
+    if partner_scores.shape != (batch, k_out) or partner_scores.dtype != torch.float32 \
+            or hidden.dtype != torch.float32 or mix.dtype != torch.float32 \
+            or norm_weight.dtype != torch.float32 or norm_bias.dtype != torch.float32:
+        raise ValueError("scores, hidden, mix and the norm parameters must be float32")
+    need = int(_abi.LIB.rlm_relation_tail_scratch_bytes(batch, k_out, dim))
+    scratch = _tail_scratch(device, need)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_tail(
+            _abi.ptr(relation_hidden), _abi.ptr(second_weight), _abi.ptr(second_bias),
+            _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias), _abi.ptr(position),
+            float(norm_eps), _abi.ptr(hidden), _abi.ptr(mix), None, _abi.ptr(scratch), scratch.numel(),
+            batch, k_out, dim, hdim,
+            _abi.same_dtype("relation MLP", relation_hidden, second_weight, second_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_tail.register_fake
+def _(relation_hidden, second_weight, second_bias, partner_scores, norm_weight, norm_bias, position,
+      norm_eps, hidden, mix):
+    return None

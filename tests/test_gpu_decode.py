@@ -95,3 +95,24 @@ def test_bf16_decode_tracks_cpu_port():
         assert cos > 0.98, (t, float(cos))
     assert same / total > 0.97, same / total
     assert_status_clear()
+
+
+def test_fused_tail_decode_tracks_default_path():
+    """The single-launch tail sums its split-K partials with atomics (order not fixed), so the
+    decode is compared by tolerance with the default path."""
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=21)
+    B, steps = 2, 24
+    g = torch.Generator().manual_seed(14)
+    tokens = torch.randint(0, 500, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, 16, (B, steps), generator=g).cuda()
+    plain = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    fused = StatefulDecoder(model, B, "cuda", torch.bfloat16, fused_tail=True)
+    assert fused.fused_tail
+    for t in range(steps):
+        a, _ = plain.step(tokens[:, t], bounds[:, t])
+        b, _ = fused.step(tokens[:, t], bounds[:, t])
+        cos = torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0)
+        assert cos > 0.995, (t, float(cos))
+    assert_status_clear()
