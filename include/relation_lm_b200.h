@@ -265,6 +265,38 @@ int rlm_relation_tail(const void* relation_hidden, const void* second_weight,
                       int hidden_dim, int dtype, int32_t* status, void* stream);
 
 /*
+ * rlm_relation_tail for callers that cannot hand over scratch memory.  This entry point has no
+ * counterpart in the reference project.
+ *
+ * Who needs it: hosts that are not allowed to allocate device memory once they are running —
+ * a serving process that gave all device memory to its own pool at start-up, a plug-in loaded
+ * into an engine that owns the allocator, or a latency-critical thread for which the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree is unacceptable.  Such a caller has
+ * nowhere to get the split-K accumulator that rlm_relation_tail asks for, so the library keeps
+ * one inside its own image: a fixed device array of 512 KB + 256 bytes that every GPU holds
+ * from the moment the library is loaded on it until the process ends.
+ *
+ * Same arguments and results as rlm_relation_tail without `scratch` / `scratch_bytes`.
+ *   - Limit: batch * k_out <= 128 and d_model <= 1024; anything larger is rejected with
+ *     RLM_ERR_SHAPE before any work is enqueued.
+ *   - The function allocates nothing and frees nothing (no cudaMalloc, no cudaFree, no library
+ *     routine that allocates).  The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress) and remembers it; make that first call with the device current and
+ *     before any stream capture begins.
+ *   - All calls on one device share the one array, and it still holds what the previous call
+ *     left; each call clears the part it uses on `stream` before launching.  Two calls that can
+ *     run at the same time on one GPU (different streams without an ordering between them)
+ *     would corrupt each other's sums: order them.
+ */
+int rlm_relation_tail_static(const void* relation_hidden, const void* second_weight,
+                             const void* second_bias, const float* partner_scores,
+                             const float* norm_weight, const float* norm_bias,
+                             const int64_t* position, float norm_eps, float* residual,
+                             const float* mix, float* context, int batch, int k_out,
+                             int d_model, int hidden_dim, int dtype, int32_t* status,
+                             void* stream);
+
+/*
  * Input embedding of one decode position (extension; the reference computes it for whole
  * sequences, src/relation_lm/models/relation_lm.py:130-131):
  * out[b] = (token_table[tokens[b]] + boundary_table[boundaries[b]]) * scale + position_table[*position]

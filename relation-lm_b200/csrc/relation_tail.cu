@@ -16,6 +16,8 @@
 // reference project; the GEMM replaces the F.linear its callers run between the two
 // operators (benchmarks/benchmark_relation_reduce.py:63).
 
+#include <mutex>
+
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
@@ -314,6 +316,45 @@ int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hi
     return check_launch("relation_tail_kernel");
 }
 
+// ------------------------------------------------------------------ built-in scratch
+//
+// Scratch for callers that may not allocate device memory themselves.  It is part of the
+// library image, so every GPU that loads the library carries these bytes until the process
+// exits.  Limits: one 128-row tile (batch * k_out <= 128) and d_model <= 1024.
+constexpr int kStaticRows = kBM;
+constexpr int kStaticDim = 1024;
+constexpr size_t kStaticAccBytes = static_cast<size_t>(kStaticRows) * kStaticDim * sizeof(float);
+constexpr size_t kStaticScratchBytes = kStaticAccBytes + 256;        // + the arrival counter
+
+static __device__ __align__(256) unsigned char g_tail_scratch[kStaticScratchBytes];
+
+// Device address of g_tail_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use; the address is asked for
+// once per device (with that device current) and remembered.
+int static_scratch_address(void** out) {
+    static std::mutex guard;
+    static void* address[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        cudaGetLastError();
+        set_error("relation_tail_static: cannot identify the current device");
+        return RLM_ERR_LAUNCH;
+    }
+    std::lock_guard<std::mutex> lock(guard);
+    if (!address[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_tail_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            set_error(e != cudaSuccess ? cudaGetErrorString(e) : "relation_tail_static: no address for the built-in scratch");
+            return RLM_ERR_LAUNCH;
+        }
+        address[device] = p;
+    }
+    *out = address[device];
+    return RLM_OK;
+}
+
 }  // namespace
 }  // namespace rlm
 
@@ -362,3 +403,48 @@ extern "C" int rlm_debug_trace_tail(long long* host) {
     return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_tail, sizeof(long long) * 16));
 }
 #endif
+
+// The fused relation tail for callers that cannot provide scratch memory: identical
+// arithmetic to rlm_relation_tail, with the split-K accumulator in the library's built-in
+// device array instead of a caller buffer.  Nothing is allocated, here or in anything this
+// function calls.
+extern "C" int rlm_relation_tail_static(const void* relation_hidden, const void* second_weight,
+                                        const void* second_bias, const float* partner_scores,
+                                        const float* norm_weight, const float* norm_bias,
+                                        const int64_t* position, float norm_eps, float* residual,
+                                        const float* mix, float* context, int batch, int k_out,
+                                        int d_model, int hidden_dim, int dtype, int32_t* status,
+                                        void* stream) {
+    using namespace rlm;
+    if (batch == 0) return RLM_OK;
+    if (!relation_hidden || !second_weight || !second_bias || !partner_scores || !norm_weight ||
+        !norm_bias || !position || (!residual && !context) || (residual && !mix)) {
+        set_error("relation_tail_static: NULL pointer");
+        return RLM_ERR_NULL;
+    }
+    if (batch < 0 || k_out < 1 || static_cast<int64_t>(batch) * k_out > kStaticRows || d_model > kStaticDim) {
+        set_error("relation_tail_static: the built-in scratch holds batch * k_out <= 128 rows of d_model <= 1024; "
+                  "use rlm_relation_tail with a caller buffer for larger problems");
+        return RLM_ERR_SHAPE;
+    }
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != RLM_OK) return rc;
+    // The array keeps whatever the previous call left.  A completed call leaves zeros, but a call
+    // that was cut short would not, so the part this call uses is cleared on the stream first.
+    const size_t acc_bytes = static_cast<size_t>(kStaticRows) * d_model * sizeof(float);
+    if (cudaMemsetAsync(scratch, 0, acc_bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess ||
+        cudaMemsetAsync(static_cast<char*>(scratch) + kStaticAccBytes, 0, 256, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("relation_tail_static: clearing the built-in scratch failed");
+        return RLM_ERR_LAUNCH;
+    }
+    TailArgs a{};
+    a.bias2 = second_bias; a.scores = partner_scores; a.norm_w = norm_weight; a.norm_b = norm_bias;
+    a.position = position; a.residual = residual; a.mix = mix; a.context = context;
+    a.scratch = static_cast<float*>(scratch);
+    a.counters = reinterpret_cast<int*>(static_cast<char*>(scratch) + kStaticAccBytes);
+    a.status = status; a.eps = norm_eps; a.batch = batch; a.k_out = k_out; a.d = d_model; a.h = hidden_dim;
+    a.w_dtype = dtype;
+    return launch_relation_tail(relation_hidden, second_weight, a, dtype, stream);
+}
