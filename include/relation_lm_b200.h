@@ -96,11 +96,16 @@ int rlm_relation_select_packed(
 /*
  * Anchor half alone.  Replaces relationlex::anchor_select
  * (src/relation_lm/kernels/triton_select.py:255-295, kernel :9-120).
+ * exclude_index (optional, [N, exclude_count] i32, at most 8 per row, entries < 0 unused) bars
+ * positions from the candidates: the distinct-anchor rule of multi-anchor selection
+ * (src/relation_lm/models/multi_relation_blocks.py:86-95).  A row whose candidates are all
+ * barred returns index 0 with score -inf.
  */
 int rlm_anchor_select(
     const void* anchor_query, const void* anchor_keys, const void* router_query,
     const void* block_mean, const void* block_std, const void* gamma, const void* bias,
     const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
+    const int32_t* exclude_index, int exclude_count,
     int32_t* out_index, float* out_score,
     int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
     int local_window, int top_blocks, int strict_valid,
@@ -111,13 +116,16 @@ int rlm_anchor_select(
  * Partner half alone, exact and router queries precomputed by the caller.
  * Replaces relationlex::partner_topk
  * (src/relation_lm/kernels/triton_select.py:298-346, kernel :123-252).
- * anchor_index [N] i32 is excluded from the candidates.
+ * anchor_index [N] i32 is excluded from the candidates, and so are the positions of
+ * exclude_index (as for rlm_anchor_select): the "no anchor of any slot is a partner" rule of
+ * multi-anchor selection (src/relation_lm/models/multi_relation_blocks.py:133-139).
  */
 int rlm_partner_topk(
     const void* partner_query, const void* partner_keys, const void* router_query,
     const void* block_mean, const void* block_std, const void* gamma, const void* bias,
     const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
-    const int32_t* anchor_index, int32_t* out_index, float* out_score,
+    const int32_t* anchor_index, const int32_t* exclude_index, int exclude_count,
+    int32_t* out_index, float* out_score,
     int n_rows, int n_seq, int max_t, int n_blocks, int buckets,
     int local_window, int top_blocks, int k_out, int strict_valid,
     int query_dtype, int key_dtype, int stats_dtype, int param_dtype,

@@ -100,32 +100,41 @@ def relation_select(aq, ak, arq, amean, astd, agamma, abias, pbase, pac, pk, pme
             torch.from_numpy(ops), (int(scored[0]), int(scored[1])))
 
 
+def _exclusions(exclude_index):
+    if exclude_index is None or exclude_index.shape[1] == 0:
+        return None, 0
+    arr = _i32(exclude_index)
+    return arr, arr.shape[1]
+
+
 def anchor_select(aq, ak, rq, mean, std, gamma, bias, position, local_window, top_blocks,
-                  strict_valid, row_batch=None, row_pos=None):
+                  strict_valid, row_batch=None, row_pos=None, exclude_index=None):
     n = aq.shape[0]
     rb, rp = _rows(n, position, row_batch, row_pos)
     arrs = [_f32(x) for x in (aq, ak, rq, mean, std, gamma, bias)]
+    ex, n_ex = _exclusions(exclude_index)
     oi = np.empty(n, np.int32)
     osc = np.empty(n, np.float32)
     rc = lib().orc_anchor_select(n, ak.shape[0], ak.shape[1], mean.shape[1], bias.shape[1],
                                  _p(rb), _p(rp), *[_p(a) for a in arrs], int(local_window),
-                                 int(top_blocks), int(bool(strict_valid)), _p(oi), _p(osc))
+                                 int(top_blocks), int(bool(strict_valid)), _p(ex), n_ex, _p(oi), _p(osc))
     _check(rc, "anchor_select")
     return torch.from_numpy(oi), torch.from_numpy(osc)
 
 
 def partner_topk(pq, pk, rq, mean, std, gamma, bias, position, anchor_index, local_window,
-                 top_blocks, k_out, strict_valid, row_batch=None, row_pos=None):
+                 top_blocks, k_out, strict_valid, row_batch=None, row_pos=None, exclude_index=None):
     n = pq.shape[0]
     rb, rp = _rows(n, position, row_batch, row_pos)
     arrs = [_f32(x) for x in (pq, pk, rq, mean, std, gamma, bias)]
     anchor = _i32(anchor_index)
+    ex, n_ex = _exclusions(exclude_index)
     oi = np.empty((n, k_out), np.int32)
     osc = np.empty((n, k_out), np.float32)
     rc = lib().orc_partner_topk(n, pk.shape[0], pk.shape[1], mean.shape[1], bias.shape[1],
                                 _p(rb), _p(rp), *[_p(a) for a in arrs], _p(anchor),
                                 int(local_window), int(top_blocks), int(k_out),
-                                int(bool(strict_valid)), _p(oi), _p(osc))
+                                int(bool(strict_valid)), _p(ex), n_ex, _p(oi), _p(osc))
     _check(rc, "partner_topk")
     return torch.from_numpy(oi), torch.from_numpy(osc)
 

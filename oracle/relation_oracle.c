@@ -168,9 +168,17 @@ static inline int argmax_left(const float* v, int n, float* best) {
 }
 
 /* Anchor selection for one query (relation_select.py:108-163). */
+static inline int barred(int p, const int32_t* excl, int n_excl) {
+    for (int i = 0; i < n_excl; ++i)
+        if (excl[i] == p) return 1;
+    return 0;
+}
+
+/* excl[0 .. n_excl): positions that may not be chosen (distinct anchors of a multi-anchor
+ * layer, src/relation_lm/models/multi_relation_blocks.py:86-95); empty for the reference ops. */
 static void anchor_one(const float* aq, const float* ak_seq, const float* bsc_in, int nb, int bs,
-                       int t, int local, int top, int* out_idx, float* out_score,
-                       int64_t* scored, float* work) {
+                       int t, int local, int top, const int32_t* excl, int n_excl, int* out_idx,
+                       float* out_score, int64_t* scored, float* work) {
     int ls = t - local + 1;
     if (ls < 0) ls = 0;
     float best = -INFINITY;
@@ -179,7 +187,7 @@ static void anchor_one(const float* aq, const float* ak_seq, const float* bsc_in
     for (int c = 0; c < local; ++c) {
         int p = t - local + 1 + c;
         float sc = -INFINITY;
-        if (p >= 0 && p <= t) { sc = dot64(ak_seq + (size_t)p * ORC_D, aq) * 0.125f; ++*scored; }
+        if (p >= 0 && p <= t && !barred(p, excl, n_excl)) { sc = dot64(ak_seq + (size_t)p * ORC_D, aq) * 0.125f; ++*scored; }
         if (first || sc > best) { best = sc; best_pos = p; first = 0; }
     }
     memcpy(work, bsc_in, sizeof(float) * (size_t)nb);
@@ -193,20 +201,22 @@ static void anchor_one(const float* aq, const float* ak_seq, const float* bsc_in
         for (int o = 0; o < bs; ++o) {
             int p = bi * bs + o;
             float sc = -INFINITY;
-            if (usable && p <= t && p < ls) { sc = dot64(ak_seq + (size_t)p * ORC_D, aq) * 0.125f; ++*scored; }
+            if (usable && p <= t && p < ls && !barred(p, excl, n_excl)) { sc = dot64(ak_seq + (size_t)p * ORC_D, aq) * 0.125f; ++*scored; }
             if (cfirst || sc > cs) { cs = sc; cpos = p; cfirst = 0; }
         }
         if (cs > best || (cs == best && cpos < best_pos)) { best = cs; best_pos = cpos; }
         work[bi] = -INFINITY;
     }
+    if (!(best > -INFINITY)) best_pos = 0;      /* every candidate was barred */
     *out_idx = best_pos;
     *out_score = best;
 }
 
 /* Partner top-K for one query (relation_select.py:229-308). */
 static void partner_one(const float* pq, const float* pk_seq, const float* bsc_in, int nb, int bs,
-                        int t, int local, int top, int k_out, int anchor, int* out_idx,
-                        float* out_score, int64_t* scored, float* work, float* cs, int* cp) {
+                        int t, int local, int top, int k_out, int anchor, const int32_t* excl,
+                        int n_excl, int* out_idx, float* out_score, int64_t* scored, float* work,
+                        float* cs, int* cp) {
     int ls = t - local + 1;
     if (ls < 0) ls = 0;
     int cap = local + top * bs;
@@ -214,7 +224,7 @@ static void partner_one(const float* pq, const float* pk_seq, const float* bsc_i
     for (int c = 0; c < local; ++c) {
         int p = t - local + 1 + c;
         cp[c] = p;
-        int valid = p >= 0 && p <= t && p != anchor;
+        int valid = p >= 0 && p <= t && p != anchor && !barred(p, excl, n_excl);
         cs[c] = -INFINITY;
         if (valid) { cs[c] = dot64(pk_seq + (size_t)p * ORC_D, pq) * 0.125f; ++*scored; }
     }
@@ -227,7 +237,7 @@ static void partner_one(const float* pq, const float* pk_seq, const float* bsc_i
             int c = local + r * bs + o;
             int p = bi * bs + o;
             cp[c] = p;
-            int valid = usable && p <= t && p < ls && p != anchor;
+            int valid = usable && p <= t && p < ls && p != anchor && !barred(p, excl, n_excl);
             cs[c] = -INFINITY;
             if (valid) { cs[c] = dot64(pk_seq + (size_t)p * ORC_D, pq) * 0.125f; ++*scored; }
         }
@@ -278,7 +288,7 @@ int orc_relation_select(int n_rows, int n_seq, int max_t, int nb, int buckets,
             block_scores(amean + so, astd + so, arq + (size_t)i * ORC_D, agamma, abias, nb, bs,
                          buckets, t, local, strict, bsc);
             int anchor;
-            anchor_one(aq + (size_t)i * ORC_D, ak_seq, bsc, nb, bs, t, local, top, &anchor,
+            anchor_one(aq + (size_t)i * ORC_D, ak_seq, bsc, nb, bs, t, local, top, NULL, 0, &anchor,
                        out_anchor_score + i, &sa, work);
             out_anchor[i] = anchor;
             float v[2 * ORC_D];
@@ -287,7 +297,7 @@ int orc_relation_select(int n_rows, int n_seq, int max_t, int nb, int buckets,
             for (int c = 0; c < 2 * ORC_D; ++c) v[c] = base[c] + row[c];
             block_scores(pmean + so, pstd + so, v + ORC_D, pgamma, pbias, nb, bs, buckets, t,
                          local, strict, bsc);
-            partner_one(v, pk_seq, bsc, nb, bs, t, local, top, k_out, anchor,
+            partner_one(v, pk_seq, bsc, nb, bs, t, local, top, k_out, anchor, NULL, 0,
                         out_partner + (size_t)i * k_out, out_partner_score + (size_t)i * k_out,
                         &spn, work, cs, cp);
         }
@@ -302,7 +312,7 @@ int orc_anchor_select(int n_rows, int n_seq, int max_t, int nb, int buckets,
                       const int32_t* row_batch, const int32_t* row_pos, const float* aq,
                       const float* ak, const float* rq, const float* mean, const float* std,
                       const float* gamma, const float* bias, int local, int top, int strict,
-                      int32_t* out_idx, float* out_score) {
+                      const int32_t* exclude, int n_excl, int32_t* out_idx, float* out_score) {
     if (nb <= 0 || max_t % nb != 0 || local < 1 || top < 0) return -1;
     int bs = max_t / nb;
     int bad = 0;
@@ -319,7 +329,8 @@ int orc_anchor_select(int n_rows, int n_seq, int max_t, int nb, int buckets,
                          t, local, strict, bsc);
             int anchor;
             anchor_one(aq + (size_t)i * ORC_D, ak + (size_t)b * max_t * ORC_D, bsc, nb, bs, t,
-                       local, top, &anchor, out_score + i, &dummy, bsc + nb);
+                       local, top, exclude ? exclude + (size_t)i * n_excl : NULL, exclude ? n_excl : 0,
+                       &anchor, out_score + i, &dummy, bsc + nb);
             out_idx[i] = anchor;
         }
         free(bsc);
@@ -332,7 +343,8 @@ int orc_partner_topk(int n_rows, int n_seq, int max_t, int nb, int buckets,
                      const int32_t* row_batch, const int32_t* row_pos, const float* pq,
                      const float* pk, const float* rq, const float* mean, const float* std,
                      const float* gamma, const float* bias, const int32_t* anchor, int local,
-                     int top, int k_out, int strict, int32_t* out_idx, float* out_score) {
+                     int top, int k_out, int strict, const int32_t* exclude, int n_excl,
+                     int32_t* out_idx, float* out_score) {
     if (nb <= 0 || max_t % nb != 0 || local < 1 || top < 0 || k_out < 1) return -1;
     int bs = max_t / nb;
     int cap = local + top * bs;
@@ -351,7 +363,8 @@ int orc_partner_topk(int n_rows, int n_seq, int max_t, int nb, int buckets,
             block_scores(mean + so, std + so, rq + (size_t)i * ORC_D, gamma, bias, nb, bs, buckets,
                          t, local, strict, bsc);
             partner_one(pq + (size_t)i * ORC_D, pk + (size_t)b * max_t * ORC_D, bsc, nb, bs, t,
-                        local, top, k_out, anchor[i], out_idx + (size_t)i * k_out,
+                        local, top, k_out, anchor[i], exclude ? exclude + (size_t)i * n_excl : NULL,
+                        exclude ? n_excl : 0, out_idx + (size_t)i * k_out,
                         out_score + (size_t)i * k_out, &dummy, bsc + nb, cs, cp);
         }
         free(bsc); free(cs); free(cp);

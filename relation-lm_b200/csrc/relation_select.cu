@@ -27,6 +27,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxKOut = 32;  // partner slots per query
+constexpr int kMaxExclude = 8; // extra excluded positions per query (multi-anchor selection)
 constexpr int kD = 64;        // exact-score width == router heads * head width
 
 enum Mode { kPacked = 0, kAnchorOnly = 1, kPartnerOnly = 2 };
@@ -66,6 +67,8 @@ struct SelectArgs {
     const int32_t* row_batch;
     const int32_t* row_position;
     const int32_t* anchor_index_in;      // partner-only
+    const int32_t* exclude_list;         // optional [N, exclude_count]: positions barred as candidates (< 0: unused entry)
+    int exclude_count;
     int32_t* out_anchor;
     float* out_anchor_score;
     int32_t* out_partner;
@@ -111,13 +114,14 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
 //   local window (sel == nullptr): row r is position pos0 + r, valid from `first_valid` on;
 //   remote blocks (sel != nullptr): row r belongs to the block of rank r / bs at offset
 //     o = r % bs, position sel[3 rank] * bs + o, valid while o < sel[3 rank + 2].
-// The row at position `exclude` scores -inf.  With `cand` the scores go to candidate slots
+// The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand` the scores go to candidate slots
 // slot0 + r; in every case the warp's best (score, lowest position on ties) is folded into
 // (best_key, best_pos), identical in all lanes.
 __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
                                         const int* sel, int bs, int first_valid, int pos0,
-                                        int exclude, const float* query, float* cand, int slot0,
-                                        int wi, int nw, uint32_t& best_key, int& best_pos) {
+                                        int exclude, const int* excl, int n_excl, const float* query,
+                                        float* cand, int slot0, int wi, int nw, uint32_t& best_key,
+                                        int& best_pos) {
     const int lane = threadIdx.x & 31;
     const int j = lane & 7, sub = lane >> 3;
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
@@ -145,6 +149,7 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
                 valid[u] = r[u] < n_rows && r[u] >= first_valid;
             }
             valid[u] = valid[u] && pos[u] != exclude;
+            for (int x = 0; x < n_excl; ++x) valid[u] = valid[u] && pos[u] != excl[x];
             if (valid[u]) load8(rows + static_cast<size_t>(r[u]) * row_bytes, 8 * j, key_dtype, k[u]);
         }
 #pragma unroll
@@ -268,6 +273,7 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
+    __shared__ int excl_s[kMaxExclude];
     __shared__ uint32_t surv_key[kWarps * kMaxKOut];
     __shared__ int surv_slot[kWarps * kMaxKOut];
     RLM_PROBE(0);
@@ -365,6 +371,8 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
         if (do_partner) bias_p[i] = load_scalar(a.partner_bias, i, a.param_dtype);
     }
     if (tid < cap4 - cap) cand[cap + tid] = kNegInf;   // padding slots never win a comparison
+    const int n_excl = a.exclude_list ? a.exclude_count : 0;
+    if (tid < n_excl) excl_s[tid] = a.exclude_list[static_cast<size_t>(row) * n_excl + tid];
     // softplus of this lane's head, evaluated while the bulk copies fly
     const float sp_a = canon_log(__fadd_rn(1.0f, canon_exp(ga)));
     const float sp_p = canon_log(__fadd_rn(1.0f, canon_exp(gp)));
@@ -391,8 +399,8 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
                          a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, kWarps / 2);
         else
-            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, aq,
-                       nullptr, 0, row_wi, row_nw, bk, bp);
+            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
+                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
         RLM_PROBE(6);
@@ -415,8 +423,8 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             RLM_PROBE(10);
             bk = 0;
             bp = 0x7fffffff;
-            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, aq, nullptr, 0, warp,
-                       kWarps, bk, bp);
+            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+                       nullptr, 0, warp, kWarps, bk, bp);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             __syncthreads();
             RLM_PROBE(11);
@@ -428,6 +436,10 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
         anchor_pos = lane < entries ? warp_pos[lane] : 0x7fffffff;
         if (anchor_pos == 0x7fffffff) best_key = 0u;
         warp_argmax_key(best_key, anchor_pos);
+        if (anchor_pos == 0x7fffffff) {   // every candidate was excluded
+            anchor_pos = 0;
+            best_key = float_key(kNegInf);
+        }
         if (tid == 0) {
             a.out_anchor[row] = anchor_pos;
             a.out_anchor_score[row] = key_float(best_key);
@@ -467,7 +479,7 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
                      a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, kWarps / 2);
     else
         score_rows(smem + p.p_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
-                   pq, cand, 0, row_wi, row_nw, dk, dp);
+                   excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp);
     __syncthreads();
     RLM_PROBE(15);
     if (top > 0) {
@@ -488,8 +500,8 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             return;
         }
         RLM_PROBE(19);
-        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, pq, cand, L, warp,
-                   kWarps, dk, dp);
+        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+                   cand, L, warp, kWarps, dk, dp);
         __syncthreads();
         RLM_PROBE(20);
     }
@@ -609,6 +621,10 @@ int launch(SelectArgs& a, void* stream) {
         set_error("relation_select: unknown dtype code");
         return RLM_ERR_DTYPE;
     }
+    if (a.exclude_list && (a.exclude_count < 0 || a.exclude_count > kMaxExclude)) {
+        set_error("relation_select: at most 8 excluded positions per query");
+        return RLM_ERR_SHAPE;
+    }
     if (!a.position && !a.row_position) {
         set_error("relation_select: either position or row_position is required");
         return RLM_ERR_NULL;
@@ -684,10 +700,12 @@ extern "C" int rlm_anchor_select(
     const void* anchor_query, const void* anchor_keys, const void* router_query,
     const void* block_mean, const void* block_std, const void* gamma, const void* bias,
     const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
+    const int32_t* exclude_index, int exclude_count,
     int32_t* out_index, float* out_score, int n_rows, int n_seq, int max_t, int n_blocks,
     int buckets, int local_window, int top_blocks, int strict_valid, int query_dtype,
     int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream) {
     rlm::SelectArgs a{};
+    a.exclude_list = exclude_index; a.exclude_count = exclude_count;
     a.aq_stride = 64; a.arq_stride = 64;
     a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = router_query;
     a.anchor_mean = block_mean; a.anchor_std = block_std; a.anchor_gamma = gamma; a.anchor_bias = bias;
@@ -704,11 +722,13 @@ extern "C" int rlm_partner_topk(
     const void* partner_query, const void* partner_keys, const void* router_query,
     const void* block_mean, const void* block_std, const void* gamma, const void* bias,
     const int64_t* position, const int32_t* row_batch, const int32_t* row_position,
-    const int32_t* anchor_index, int32_t* out_index, float* out_score, int n_rows, int n_seq,
+    const int32_t* anchor_index, const int32_t* exclude_index, int exclude_count,
+    int32_t* out_index, float* out_score, int n_rows, int n_seq,
     int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out,
     int strict_valid, int query_dtype, int key_dtype, int stats_dtype, int param_dtype,
     int32_t* status, void* stream) {
     rlm::SelectArgs a{};
+    a.exclude_list = exclude_index; a.exclude_count = exclude_count;
     a.pbase_stride = 64; a.prq_stride = 64;
     a.partner_base = partner_query; a.partner_router_query = router_query; a.partner_keys = partner_keys;
     a.partner_mean = block_mean; a.partner_std = block_std; a.partner_gamma = gamma; a.partner_bias = bias;

@@ -15,8 +15,8 @@ _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 # name -> argument types, in the order of include/relation_lm_b200.h
 PROTOTYPES = {
     "rlm_relation_select_packed": [_P] * 21 + [_L] * 3 + [_I] * 13 + [_P, _P],
-    "rlm_anchor_select": [_P] * 12 + [_I] * 12 + [_P, _P],
-    "rlm_partner_topk": [_P] * 13 + [_I] * 13 + [_P, _P],
+    "rlm_anchor_select": [_P] * 11 + [_I] + [_P] * 2 + [_I] * 12 + [_P, _P],
+    "rlm_partner_topk": [_P] * 12 + [_I] + [_P] * 2 + [_I] * 13 + [_P, _P],
     "rlm_router_cache_update": [_P, _L, _P, _L] + [_P] * 12 + [_I] * 8 + [_P, _P],
     "rlm_relation_hidden_cached": [_P] * 7 + [_I] * 9 + [_P, _P],
     "rlm_relation_hidden_cache_update": [_P] * 10 + [_I] * 8 + [_P, _P],

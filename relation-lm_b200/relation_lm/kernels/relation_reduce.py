@@ -331,3 +331,79 @@ def relation_tail(
 def _(relation_hidden, second_weight, second_bias, partner_scores, norm_weight, norm_bias, position,
       norm_eps, hidden, mix):
     return None
+
+
+@torch.library.custom_op("relation_lm::relation_hidden_cached_rows", mutates_args=(),
+                         device_types="cuda")
+def relation_hidden_cached_rows(
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    product_weight: Tensor,
+    row_batch: Tensor,
+) -> Tensor:
+    """Per-row form of ``relation_hidden_cached`` (extension, prefill): query row ``i`` gathers
+    from sequence ``row_batch[i]`` of caches ``[B, T, ...]``; ``anchor_index [N]``,
+    ``partner_index [N, K]``; returns ``[N, K, H]`` fp32."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, product_weight=product_weight, row_batch=row_batch)
+    n_seq, max_t, rdim = operand_cache.shape
+    rows, k_out = partner_index.shape
+    hdim = product_weight.size(0)
+    _check_indices(anchor_index, partner_index, rows)
+    if row_batch.dtype != torch.int32 or row_batch.numel() != rows:
+        raise ValueError("row_batch must be int32 with one entry per query row")
+    if expanded_cache.shape != (n_seq, max_t, 2 * hdim) or product_weight.size(1) != rdim:
+        raise ValueError("expanded_cache must be [B, T, 2H] and product_weight [H, R]")
+    out = torch.empty((rows, k_out, hdim), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cached(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(product_weight), _abi.ptr(row_batch), _abi.ptr(out),
+            rows, n_seq, max_t, rdim, hdim, k_out,
+            _abi.same_dtype("cache", expanded_cache, operand_cache), _abi.code(product_weight),
+            _abi.code(out), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@relation_hidden_cached_rows.register_fake
+def _(expanded_cache, operand_cache, anchor_index, partner_index, product_weight, row_batch):
+    return operand_cache.new_empty(
+        (partner_index.size(0), partner_index.size(1), product_weight.size(0)), dtype=torch.float32)
+
+
+@torch.library.custom_op("relation_lm::relation_norm_reduce_rows", mutates_args=(),
+                         device_types="cuda")
+def relation_norm_reduce_rows(
+    raw: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    row_position: Tensor,
+    norm_eps: float,
+) -> Tensor:
+    """Per-row form of ``relation_norm_reduce`` (extension, prefill): row ``i`` uses the active-K
+    limit of position ``row_position[i]``."""
+    device = _abi.require_cuda_contiguous(raw=raw, partner_scores=partner_scores,
+                                          norm_weight=norm_weight, norm_bias=norm_bias,
+                                          row_position=row_position)
+    rows, k_out, dim = raw.shape
+    if partner_scores.shape != (rows, k_out) or partner_scores.dtype != torch.float32:
+        raise ValueError("partner_scores must be float32 [N, K]")
+    if row_position.dtype != torch.int32 or row_position.numel() != rows:
+        raise ValueError("row_position must be int32 with one entry per row")
+    out = torch.empty((rows, dim), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_norm_reduce(
+            _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
+            None, _abi.ptr(row_position), float(norm_eps), _abi.ptr(out), None, None, rows, k_out,
+            dim, _abi.code(raw), _abi.same_dtype("norm parameter", norm_weight, norm_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@relation_norm_reduce_rows.register_fake
+def _(raw, partner_scores, norm_weight, norm_bias, row_position, norm_eps):
+    return raw.new_empty((raw.size(0), raw.size(2)), dtype=torch.float32)

@@ -128,9 +128,16 @@ def packed_inputs(case) -> dict:
     return {"memory": rn(rows, d), "weights": [rn(w, d) * 0.02 for w in widths]}
 
 
+def multi_anchor_inputs(case) -> dict[str, torch.Tensor]:
+    g = _gen(case["seed"])
+    B, T, d = case["batch"], case["context"], case["d_model"]
+    return {"hidden": torch.randn(B, T, d, generator=g), "memory": torch.randn(B, T, d, generator=g)}
+
+
 _BUILDERS = {"select": select_inputs, "router": router_inputs,
              "router_sequence": router_sequence_inputs, "reduce": reduce_inputs,
-             "norm_reduce": norm_reduce_inputs, "packed": packed_inputs}
+             "norm_reduce": norm_reduce_inputs, "packed": packed_inputs,
+             "multi_anchor": multi_anchor_inputs}
 
 
 def make_inputs(case):
@@ -213,6 +220,8 @@ def all_cases() -> dict[str, dict]:
         c[f"norm_reduce_b{batch}_k{k}_d{dim}"] = {
             "kind": "norm_reduce", "seed": 4000 + i, "batch": batch, "k_out": k, "dim": dim,
             "eps": 1.0e-5, "positions": [0, 1, 2, 5, 6, 30, 511], "all_inactive": i == 1}
+    c["multi_anchor_dense"] = {"kind": "multi_anchor", "seed": 6000, "batch": 2, "context": 24,
+                               "d_model": 48, "anchors": 4, "partners": 4}
     c["packed_d576"] = {"kind": "packed", "seed": 5000, "rows": 8, "d_model": 576}
     c["packed_d512"] = {"kind": "packed", "seed": 5001, "rows": 3, "d_model": 512}
     return c

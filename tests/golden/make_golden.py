@@ -224,8 +224,36 @@ def run_packed(case, x):
             "names": list(projection.names), "split_sizes": list(projection.split_sizes)}
 
 
+def run_multi_anchor(case, x):
+    """The reference's dense multi-anchor block (models/multi_relation_blocks.py): its per-slot
+    queries / keys are stored as the selector inputs, its indices as the expected result."""
+    from relation_lm.models.multi_relation_blocks import (MultiAnchorRelationBlock,
+                                                          MultiRelationBlockConfig)
+
+    torch.manual_seed(case["seed"])
+    cfg = MultiRelationBlockConfig(d_model=case["d_model"], gate_dim=64, relation_dim=16,
+                                   anchors_per_block=case["anchors"],
+                                   partners_per_anchor=case["partners"])
+    block = MultiAnchorRelationBlock(cfg).eval()
+    B, T, h, g = case["batch"], case["context"], case["anchors"], 64
+    hidden, memory = x["hidden"], x["memory"]
+    with torch.no_grad():
+        _, info = block(hidden, memory)
+        normalized = block.input_norm(hidden)
+        anchor_q = block.anchor_query(normalized).view(B, T, h, g)
+        anchor_k = block.anchor_key(memory).view(B, T, h, g)
+        anchor = block._gather(memory, info["anchor_index"]) * info["anchor_active"][..., None]
+        partner_input = torch.cat((normalized[:, :, None].expand(-1, -1, h, -1), anchor), dim=-1)
+        partner_q = torch.stack([layer(partner_input[:, :, i]) for i, layer in enumerate(block.partner_query)], dim=2)
+        partner_k = block.partner_key(memory).view(B, T, h, g)
+    return {"anchor_q": anchor_q, "anchor_k": anchor_k, "partner_q": partner_q, "partner_k": partner_k,
+            "anchor_index": info["anchor_index"].to(torch.int32), "anchor_active": info["anchor_active"],
+            "partner_index": info["partner_index"].to(torch.int32), "partner_active": info["partner_active"]}
+
+
 RUNNERS = {"select": run_select, "router": run_router, "router_sequence": run_router_sequence,
-           "reduce": run_reduce, "norm_reduce": run_norm_reduce, "packed": run_packed}
+           "reduce": run_reduce, "norm_reduce": run_norm_reduce, "packed": run_packed,
+           "multi_anchor": run_multi_anchor}
 
 
 def main() -> None:

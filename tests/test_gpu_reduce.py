@@ -161,3 +161,34 @@ def test_reduce_tail_low_precision_inputs(dtype):
     want = oracle.relation_norm_reduce(raw, scores, gamma, beta, 300, 1e-5)
     assert torch.allclose(got.cpu(), want, atol=1e-2, rtol=1e-2)
     assert_status_clear()
+
+
+def test_per_row_forms_match_the_oracle():
+    """Prefill forms: rows carry their own sequence index / position (long-context shape:
+    block 64 is irrelevant here; d_model 512, hidden 2048, bf16 caches)."""
+    from relation_lm.kernels.relation_reduce import (relation_hidden_cached_rows,
+                                                     relation_norm_reduce_rows)
+
+    g = torch.Generator().manual_seed(6060)
+    B, T, R, H, D, K, N = 3, 256, 128, 2048, 512, 8, 200
+    dtype = torch.bfloat16
+    operand = torch.randn(B, T, R, generator=g).to(dtype)
+    expanded = (torch.randn(B, T, 2 * H, generator=g) * 0.3).to(dtype)
+    wm = (torch.randn(H, R, generator=g) * 0.02).to(dtype)
+    row_batch = torch.randint(0, B, (N,), generator=g, dtype=torch.int32)
+    row_pos = torch.randint(0, T, (N,), generator=g, dtype=torch.int32)
+    anchor = (torch.rand(N, generator=g) * (row_pos + 1)).to(torch.int32)
+    partner = (torch.rand(N, K, generator=g) * (row_pos[:, None] + 1)).to(torch.int32)
+    hidden = relation_hidden_cached_rows(expanded.cuda(), operand.cuda(), anchor.cuda(), partner.cuda(),
+                                         wm.cuda(), row_batch.cuda())
+    want, _ = oracle.relation_hidden(expanded, operand, anchor, partner, wm, row_batch=row_batch,
+                                     row_pos=row_pos)
+    assert torch.allclose(hidden.cpu(), want, atol=1e-2, rtol=1e-2)
+    raw = torch.randn(N, K, D, generator=g)
+    scores = torch.randn(N, K, generator=g)
+    scores[::3, -2:] = -torch.inf
+    gamma, beta = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    ctx = relation_norm_reduce_rows(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(), row_pos.cuda(), 1e-5)
+    want_ctx = oracle.relation_norm_reduce(raw, scores, gamma, beta, 0, 1e-5, row_pos=row_pos)
+    assert torch.allclose(ctx.cpu(), want_ctx, atol=FP32_ATOL, rtol=1e-5)
+    assert_status_clear()

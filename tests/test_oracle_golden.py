@@ -191,3 +191,51 @@ def test_canonical_exp_log_accuracy():
         got, want = lib.orc_logf(vf), float(torch.tensor(vf, dtype=torch.float64).log())
         assert abs(got - want) <= 4e-7 * max(abs(want), 1e-1), v
     assert lib.orc_logf(1.0) == 0.0
+
+
+def _multi_anchor_rows(ref):
+    B, T, h, _ = ref["anchor_q"].shape
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(T)
+    row_pos = torch.arange(T, dtype=torch.int32).repeat(B)
+    return B, T, h, row_batch, row_pos
+
+
+def multi_anchor_dense_check(ref, anchor_rows, partner_rows):
+    """Full-window routed selection per slot must reproduce the reference's dense multi-anchor
+    block: distinct anchors slot by slot, partners with every active anchor barred."""
+    B, T, h, row_batch, row_pos = _multi_anchor_rows(ref)
+    N, nb, K = B * T, 3, ref["partner_index"].shape[-1]
+    stats = torch.zeros(B, nb, 4, 16)
+    gamma, bias, rq = torch.zeros(4), torch.zeros(4, 16), torch.zeros(N, 64)
+    active = ref["anchor_active"].reshape(N, h)
+    anchors = torch.full((N, h), -1, dtype=torch.int32)
+    for s in range(h):
+        idx, _ = anchor_rows(ref["anchor_q"][:, :, s].reshape(N, 64).contiguous(),
+                             ref["anchor_k"][:, :, s].contiguous(), rq, stats, stats, gamma, bias,
+                             row_batch, row_pos, anchors.clone(), T, 0, False)
+        idx = torch.where(active[:, s], idx, torch.zeros_like(idx))
+        assert torch.equal(idx, ref["anchor_index"].reshape(N, h)[:, s]), s
+        anchors[:, s] = torch.where(active[:, s], idx, torch.full_like(idx, -1))
+    for s in range(h):
+        pidx, pscore = partner_rows(ref["partner_q"][:, :, s].reshape(N, 64).contiguous(),
+                                    ref["partner_k"][:, :, s].contiguous(), rq, stats, stats, gamma,
+                                    bias, row_batch, row_pos, anchors[:, s].contiguous(), anchors, T, 0, K, False)
+        want_active = ref["partner_active"].reshape(N, h, K)[:, s] & active[:, s, None]
+        got_active = torch.isfinite(pscore) & active[:, s, None]
+        assert torch.equal(got_active, want_active), s
+        want = ref["partner_index"].reshape(N, h, K)[:, s]
+        assert torch.equal(pidx[want_active], want[want_active]), s
+
+
+def test_multi_anchor_rules_match_the_dense_reference_block(golden):
+    ref = golden["multi_anchor_dense"]["outputs"]
+
+    def anchor_rows(aq, ak, rq, mean, std, gamma, bias, rb, rp, excl, L, top, strict):
+        return oracle.anchor_select(aq, ak, rq, mean, std, gamma, bias, 0, L, top, strict,
+                                    row_batch=rb, row_pos=rp, exclude_index=excl)
+
+    def partner_rows(pq, pk, rq, mean, std, gamma, bias, rb, rp, anchor, excl, L, top, K, strict):
+        return oracle.partner_topk(pq, pk, rq, mean, std, gamma, bias, 0, anchor, L, top, K, strict,
+                                   row_batch=rb, row_pos=rp, exclude_index=excl)
+
+    multi_anchor_dense_check(ref, anchor_rows, partner_rows)
