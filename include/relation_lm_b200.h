@@ -203,6 +203,23 @@ int rlm_relation_norm_reduce(
     int32_t* status, void* stream);
 
 /*
+ * Prefill of the router state (extension): raw and convolved router keys and the block
+ * statistics of positions [0, length) of ZERO-INITIALISED caches in one launch, leaving the
+ * state that `length` successive rlm_router_cache_update calls would leave (including the
+ * zero-padded statistics of a trailing partial block; the full-sequence form is
+ * DistilledBlockRouter.block_statistics(_causal_conv(keys)), src/relation_lm/routing/block_router.py:51-68).
+ *   anchor_raw, partner_raw: [B, length, 64] views with row and batch strides in ELEMENTS.
+ */
+int rlm_router_cache_prefill(
+    const void* anchor_raw, int64_t anchor_row_stride, int64_t anchor_batch_stride,
+    const void* partner_raw, int64_t partner_row_stride, int64_t partner_batch_stride,
+    void* anchor_raw_cache, void* partner_raw_cache, void* anchor_conv_cache,
+    void* partner_conv_cache, void* anchor_mean, void* anchor_std, void* partner_mean,
+    void* partner_std, const void* anchor_conv_weight, const void* partner_conv_weight, int length,
+    int batch, int max_t, int n_blocks, int block_size, int raw_dtype, int cache_dtype,
+    int stats_dtype, int weight_dtype, void* stream);
+
+/*
  * Packed sparse-cache projection on the tensor cores (tcgen05, TMEM accumulator, TMA loads):
  * out[rows, n_out] = x[rows, d_in] . weight[n_out, d_in]^T.  Replaces the F.linear inside
  * PackedSparseCacheProjection.project (src/relation_lm/inference/packed_cache.py:52-57); the

@@ -135,6 +135,86 @@ __global__ void __launch_bounds__(kThreads) router_cache_update_kernel(const Rou
     router_update(a, b, layer, smem, bar, t);
 }
 
+// Prefill: conv + statistics of positions [0, length) of zero-initialised caches in one launch,
+// leaving exactly the state that `length` successive single-position updates would leave.
+// One CTA per (sequence, block); a thread owns one (stream, channel) and walks the block's rows
+// in ascending order.  A single-position update reads earlier rows of the block back from the
+// cache (rounded to the cache dtype) and uses the un-rounded value only for its own row, so
+// the statistics of a block are those computed at its last filled position: rounded values
+// for the rows before it, the fp32 value for that row, zeros (the fresh cache) after it.
+struct PrefillArgs {
+    const void* raw[2];
+    int64_t raw_row_stride[2], raw_batch_stride[2];   // elements
+    void* raw_cache[2];
+    void* conv_cache[2];
+    void* mean[2];
+    void* stdv[2];
+    const void* weight[2];
+    int batch, max_t, n_blocks, block_size, length;
+    int raw_dtype, cache_dtype, stats_dtype, weight_dtype;
+};
+
+__device__ __forceinline__ float round_to(float v, int dtype) {
+    if (dtype == RLM_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    if (dtype == RLM_F16) return __half2float(__float2half_rn(v));
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads) router_cache_prefill_kernel(const PrefillArgs a) {
+    const int b = blockIdx.x, blk = blockIdx.y, tid = threadIdx.x;
+    const int s = tid / kD, c = tid % kD;
+    const int bs = a.block_size, start = blk * bs;
+    const int last = min(start + bs, a.length) - 1;        // last filled position of the block
+    if (last < start) return;
+    const float w0 = load_scalar(a.weight[s], c * 3 + 0, a.weight_dtype);
+    const float w1 = load_scalar(a.weight[s], c * 3 + 1, a.weight_dtype);
+    const float w2 = load_scalar(a.weight[s], c * 3 + 2, a.weight_dtype);
+    const int64_t src = b * a.raw_batch_stride[s] + c;
+    auto raw_at = [&](int p) {      // as the raw cache holds it: rounded to the cache dtype
+        return round_to(load_scalar(a.raw[s], src + p * a.raw_row_stride[s], a.raw_dtype), a.cache_dtype);
+    };
+    auto conv_at = [&](int p, float cur, float prev1, float prev2) {
+        float v = __fmul_rn(cur, w2);
+        v = __fadd_rn(v, __fmul_rn(__fmul_rn(prev1, w1), p >= 1 ? 1.0f : 0.0f));
+        v = __fadd_rn(v, __fmul_rn(__fmul_rn(prev2, w0), p >= 2 ? 1.0f : 0.0f));
+        return v;
+    };
+    const int64_t cache_row0 = (static_cast<int64_t>(b) * a.max_t + start) * kD + c;
+    float sum = 0.0f;
+    float prev1 = start >= 1 ? raw_at(start - 1) : 0.0f, prev2 = start >= 2 ? raw_at(start - 2) : 0.0f;
+    for (int p = start; p <= last; ++p) {
+        // the update convolves the un-rounded incoming key with the cached (rounded) history
+        const float cur = load_scalar(a.raw[s], src + p * a.raw_row_stride[s], a.raw_dtype);
+        const float conv = conv_at(p, cur, prev1, prev2);
+        store_scalar(a.raw_cache[s], cache_row0 + static_cast<int64_t>(p - start) * kD, a.cache_dtype, cur);
+        store_scalar(a.conv_cache[s], cache_row0 + static_cast<int64_t>(p - start) * kD, a.cache_dtype, conv);
+        sum = __fadd_rn(sum, p == last ? conv : round_to(conv, a.cache_dtype));
+        prev2 = prev1;
+        prev1 = round_to(cur, a.cache_dtype);
+    }
+    for (int p = last + 1; p < start + bs; ++p) sum = __fadd_rn(sum, 0.0f);
+    const float mean = __fdiv_rn(sum, static_cast<float>(bs));
+    float acc = 0.0f;
+    prev1 = start >= 1 ? raw_at(start - 1) : 0.0f;
+    prev2 = start >= 2 ? raw_at(start - 2) : 0.0f;
+    for (int p = start; p < start + bs; ++p) {
+        float x = 0.0f;
+        if (p <= last) {
+            const float cur = load_scalar(a.raw[s], src + p * a.raw_row_stride[s], a.raw_dtype);
+            const float conv = conv_at(p, cur, prev1, prev2);
+            x = p == last ? conv : round_to(conv, a.cache_dtype);
+            prev2 = prev1;
+            prev1 = round_to(cur, a.cache_dtype);
+        }
+        const float d = __fsub_rn(x, mean);
+        acc = __fmaf_rn(d, d, acc);
+    }
+    const float sd = __fsqrt_rn(__fdiv_rn(acc, static_cast<float>(bs)));
+    const int64_t stat = (static_cast<int64_t>(b) * a.n_blocks + blk) * kD + c;
+    store_scalar(a.mean[s], stat, a.stats_dtype, mean);
+    store_scalar(a.stdv[s], stat, a.stats_dtype, sd);
+}
+
 int validate_and_launch(RouterArgs& a, void* stream, const char* who) {
     if (a.batch == 0 || a.layers == 0) return RLM_OK;
     if (a.batch < 0 || a.layers < 0 || a.max_t < 1 || a.n_blocks < 1 || a.block_size < 1 ||
@@ -236,4 +316,47 @@ extern "C" int rlm_sparse_cache_append(
     a.raw_dtype = packed_dtype; a.cache_dtype = cache_dtype; a.stats_dtype = stats_dtype;
     a.weight_dtype = weight_dtype;
     return validate_and_launch(a, stream, "sparse_cache_append");
+}
+
+extern "C" int rlm_router_cache_prefill(
+    const void* anchor_raw, int64_t anchor_row_stride, int64_t anchor_batch_stride,
+    const void* partner_raw, int64_t partner_row_stride, int64_t partner_batch_stride,
+    void* anchor_raw_cache, void* partner_raw_cache, void* anchor_conv_cache,
+    void* partner_conv_cache, void* anchor_mean, void* anchor_std, void* partner_mean,
+    void* partner_std, const void* anchor_conv_weight, const void* partner_conv_weight, int length,
+    int batch, int max_t, int n_blocks, int block_size, int raw_dtype, int cache_dtype,
+    int stats_dtype, int weight_dtype, void* stream) {
+    using namespace rlm;
+    if (batch == 0 || length == 0) return RLM_OK;
+    const void* need[] = {anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache,
+                          anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std,
+                          partner_mean, partner_std, anchor_conv_weight, partner_conv_weight};
+    for (const void* q : need)
+        if (!q) { set_error("router_cache_prefill: NULL pointer"); return RLM_ERR_NULL; }
+    if (batch < 0 || length < 0 || length > max_t || n_blocks < 1 || block_size < 1 ||
+        static_cast<int64_t>(n_blocks) * block_size > max_t ||
+        (length + block_size - 1) / block_size > n_blocks) {
+        set_error("router_cache_prefill: need length <= T and n_blocks * block_size <= T covering it");
+        return RLM_ERR_SHAPE;
+    }
+    if (!valid_dtype(raw_dtype) || !valid_dtype(cache_dtype) || !valid_dtype(stats_dtype) ||
+        !valid_dtype(weight_dtype)) {
+        set_error("router_cache_prefill: unknown dtype code");
+        return RLM_ERR_DTYPE;
+    }
+    PrefillArgs a{};
+    a.raw[0] = anchor_raw; a.raw[1] = partner_raw;
+    a.raw_row_stride[0] = anchor_row_stride; a.raw_row_stride[1] = partner_row_stride;
+    a.raw_batch_stride[0] = anchor_batch_stride; a.raw_batch_stride[1] = partner_batch_stride;
+    a.raw_cache[0] = anchor_raw_cache; a.raw_cache[1] = partner_raw_cache;
+    a.conv_cache[0] = anchor_conv_cache; a.conv_cache[1] = partner_conv_cache;
+    a.mean[0] = anchor_mean; a.mean[1] = partner_mean;
+    a.stdv[0] = anchor_std; a.stdv[1] = partner_std;
+    a.weight[0] = anchor_conv_weight; a.weight[1] = partner_conv_weight;
+    a.batch = batch; a.max_t = max_t; a.n_blocks = n_blocks; a.block_size = block_size; a.length = length;
+    a.raw_dtype = raw_dtype; a.cache_dtype = cache_dtype; a.stats_dtype = stats_dtype; a.weight_dtype = weight_dtype;
+    dim3 grid(batch, (length + block_size - 1) / block_size);
+    router_cache_prefill_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    count_launch();
+    return check_launch("router_cache_prefill_kernel");
 }

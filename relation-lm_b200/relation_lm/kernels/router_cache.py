@@ -137,3 +137,58 @@ def _(packed, anchor_keys, partner_keys, operand_cache, partner_anchor_cache, an
       partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std,
       partner_mean, partner_std, anchor_conv_weight, partner_conv_weight, position, block_size):
     return None
+
+
+@torch.library.custom_op("relation_lm::router_cache_prefill", mutates_args=_MUTATED,
+                         device_types="cuda")
+def router_cache_prefill(
+    anchor_raw: Tensor,
+    partner_raw: Tensor,
+    anchor_raw_cache: Tensor,
+    partner_raw_cache: Tensor,
+    anchor_conv_cache: Tensor,
+    partner_conv_cache: Tensor,
+    anchor_mean: Tensor,
+    anchor_std: Tensor,
+    partner_mean: Tensor,
+    partner_std: Tensor,
+    anchor_conv_weight: Tensor,
+    partner_conv_weight: Tensor,
+    block_size: int,
+) -> None:
+    """Fill zero-initialised router caches and block statistics for a whole prefix
+    ``anchor_raw, partner_raw [B, length, 64]`` in one launch (extension); the state equals that
+    of ``length`` successive ``router_cache_update`` calls."""
+    device = _abi.require_cuda_contiguous(
+        anchor_raw_cache=anchor_raw_cache, partner_raw_cache=partner_raw_cache,
+        anchor_conv_cache=anchor_conv_cache, partner_conv_cache=partner_conv_cache,
+        anchor_mean=anchor_mean, anchor_std=anchor_std, partner_mean=partner_mean,
+        partner_std=partner_std, anchor_conv_weight=anchor_conv_weight,
+        partner_conv_weight=partner_conv_weight)
+    for name, raw in (("anchor_raw", anchor_raw), ("partner_raw", partner_raw)):
+        if raw.device != device or raw.dim() != 3 or raw.size(2) != 64 or raw.stride(2) != 1:
+            raise ValueError(f"{name} must be a [B, length, 64] CUDA tensor with unit inner stride")
+    batch, length = anchor_raw.size(0), anchor_raw.size(1)
+    if partner_raw.shape != anchor_raw.shape:
+        raise ValueError("anchor_raw and partner_raw must have the same shape")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_router_cache_prefill(
+            _abi.ptr(anchor_raw), anchor_raw.stride(1), anchor_raw.stride(0), _abi.ptr(partner_raw),
+            partner_raw.stride(1), partner_raw.stride(0), _abi.ptr(anchor_raw_cache),
+            _abi.ptr(partner_raw_cache), _abi.ptr(anchor_conv_cache), _abi.ptr(partner_conv_cache),
+            _abi.ptr(anchor_mean), _abi.ptr(anchor_std), _abi.ptr(partner_mean), _abi.ptr(partner_std),
+            _abi.ptr(anchor_conv_weight), _abi.ptr(partner_conv_weight), length, batch,
+            anchor_raw_cache.size(1), anchor_mean.size(1), int(block_size),
+            _abi.same_dtype("raw key", anchor_raw, partner_raw),
+            _abi.same_dtype("router cache", anchor_raw_cache, partner_raw_cache,
+                            anchor_conv_cache, partner_conv_cache),
+            _abi.same_dtype("block statistics", anchor_mean, anchor_std, partner_mean, partner_std),
+            _abi.same_dtype("conv weight", anchor_conv_weight, partner_conv_weight),
+            _abi.stream_ptr(device)))
+
+
+@router_cache_prefill.register_fake
+def _(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache, anchor_conv_cache,
+      partner_conv_cache, anchor_mean, anchor_std, partner_mean, partner_std,
+      anchor_conv_weight, partner_conv_weight, block_size):
+    return None

@@ -140,3 +140,27 @@ def test_router_update_validation():
         _run(bad, 8, 8)
     _run(xg, 4096, 8)                                      # position outside the cache
     assert _abi.read_status() == 2
+
+
+@pytest.mark.parametrize("dtype,length", [("fp32", 96), ("fp32", 77), ("bf16", 128), ("bf16", 45)])
+def test_prefill_equals_sequential_updates(dtype, length):
+    """One prefill launch == `length` oracle updates from a zero state, bit for bit, including a
+    trailing partial block; the keys come as strided slices of a packed projection."""
+    from relation_lm.kernels.router_cache import router_cache_prefill
+
+    B, T, bs = 2, 128, 32
+    td = {"fp32": torch.float32, "bf16": torch.bfloat16}[dtype]
+    g = torch.Generator().manual_seed(900 + length)
+    packed = torch.randn(B, length, 512, generator=g).to(td)
+    w_a, w_p = torch.randn(64, 3, generator=g) * 0.1, torch.randn(64, 3, generator=g) * 0.1
+    host = {n: torch.zeros(B, T, 64, dtype=td) for n in STATE[:4]}
+    host.update({n: torch.zeros(B, T // bs, 4, 16, dtype=td) for n in STATE[4:]})
+    dev = to_cuda(host)
+    pg = packed.cuda()
+    router_cache_prefill(pg[:, :, 384:448], pg[:, :, 448:512], *[dev[n] for n in STATE], w_a.cuda(), w_p.cuda(), bs)
+    for t in range(length):
+        _, new = oracle.router_cache_update(packed[:, t, 384:448], packed[:, t, 448:512],
+                                            *[host[n] for n in STATE], w_a, w_p, t, bs)
+        host = {n: new[n].to(td) for n in STATE}
+    for n in STATE:
+        assert torch.equal(dev[n].cpu(), host[n]), n
