@@ -27,6 +27,10 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxKOut = 32;  // partner slots per query
+#ifndef RLM_FILTER_MIN_CAP
+#define RLM_FILTER_MIN_CAP 129
+#endif
+constexpr int kFilterMinCap = RLM_FILTER_MIN_CAP;  // smallest candidate count that takes the threshold filter
 constexpr int kMaxExclude = 8; // extra excluded positions per query (multi-anchor selection)
 constexpr int kD = 64;        // exact-score width == router heads * head width
 
@@ -276,6 +280,9 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     __shared__ int excl_s[kMaxExclude];
     __shared__ uint32_t surv_key[kWarps * kMaxKOut];
     __shared__ int surv_slot[kWarps * kMaxKOut];
+    __shared__ uint32_t group_max[2 * kWarps];
+    __shared__ int short_count;
+    if (threadIdx.x == 0) short_count = 0;
     RLM_PROBE(0);
     const int row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -510,6 +517,64 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     // threads share one candidate and scan interleaved groups of four slots.  Slots past the
     // valid candidates carry score -inf and the position of candidate slot 0.
     const int K = a.k_out;
+    // Threshold filter: the K-th largest of the sixteen half-warp maxima is a lower bound of
+    // the K-th largest score, so only candidates at or above it can be selected.  They are
+    // compacted into a short list and ranked exactly there; when the list is long (many equal
+    // or -inf scores) the general paths below take over with the score table untouched.
+    if (cap >= kFilterMinCap && K <= 2 * kWarps && cap > 16 * (K - 1)) {
+        uint32_t kmax = 0;
+        for (int c = tid; c < cap; c += kThreads) kmax = max(kmax, float_key(cand[c] + 0.0f));
+#pragma unroll
+        for (int s = 8; s > 0; s >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, s));
+        if ((lane & 15) == 0) group_max[tid >> 4] = kmax;
+        __syncthreads();
+        const uint32_t g = group_max[lane & 15];
+        int grank = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t o = __shfl_sync(0xffffffffu, g, j);
+            grank += (o > g) || (o == g && j < (lane & 15));
+        }
+        const unsigned holder = __ballot_sync(0xffffffffu, grank == K - 1) & 0xffffu;
+        const uint32_t tau = __shfl_sync(0xffffffffu, g, __ffs(holder) - 1);
+        for (int c0 = 0; c0 < cap; c0 += kThreads) {
+            const int c = c0 + tid;
+            const uint32_t key = c < cap ? float_key(cand[c] + 0.0f) : 0u;
+            const bool pass = c < cap && key >= tau;
+            const unsigned m = __ballot_sync(0xffffffffu, pass);
+            int base = 0;
+            if (lane == 0 && m) base = atomicAdd(&short_count, __popc(m));
+            base = __shfl_sync(0xffffffffu, base, 0);
+            const int at = base + __popc(m & ((1u << lane) - 1u));
+            if (pass && at < kWarps * kMaxKOut) { surv_key[at] = key; surv_slot[at] = c; }
+        }
+        __syncthreads();
+        const int n = short_count;
+        if (tau > float_key(kNegInf) && n <= kThreads / 4) {
+            const int i = tid >> 2, part = tid & 3;
+            int rank = 0, c = 0;
+            uint32_t key = 0;
+            if (i < n) {
+                key = surv_key[i];
+                c = surv_slot[i];
+                for (int j = part; j < n; j += 4) {
+                    const uint32_t ok = surv_key[j];
+                    rank += (ok > key) || (ok == key && surv_slot[j] < c);
+                }
+            }
+            rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+            rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+            if (i < n && part == 0 && rank < K) {
+                int pos;
+                if (c < L) pos = t - L + 1 + c;
+                else { int r = (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
+                a.out_partner[static_cast<size_t>(row) * K + rank] = pos;
+                a.out_partner_score[static_cast<size_t>(row) * K + rank] = cand[c];
+            }
+            RLM_PROBE(21);
+            return;
+        }
+    }
     if (cap > 128) {
         // Large candidate sets: tournament.  Each warp extracts the top K of the slots it
         // owns (K rounds of redux arg-max, knocking winners out of the table); warp 0 then
