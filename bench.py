@@ -40,6 +40,11 @@ import torch  # noqa: E402
 PREFIX = 448
 METRIC = "relation decode tokens/s at ctx512 K=8"
 UNIT = "tokens/s"
+CPU_SAMPLE_BATCH = 8   # the CPU arm keeps fp32 caches on the host: it decodes at most this many sequences
+
+
+def log(message: str) -> None:
+    print(f"[bench {time.strftime('%H:%M:%S')}] {message}", file=sys.stderr, flush=True)
 
 
 def zipf_tokens(batch: int, length: int, vocab: int, seed: int) -> torch.Tensor:
@@ -148,7 +153,8 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     steps = max(1, args.steps)
-    value, elapsed, threads = cpu_decode_rate(args.workload, args.batch, steps, args.warmup, 0)
+    cpu_batch = min(args.batch, CPU_SAMPLE_BATCH)
+    value, elapsed, threads = cpu_decode_rate(args.workload, cpu_batch, steps, args.warmup, 0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": elapsed / steps * 1e3,
@@ -156,7 +162,7 @@ def run_reference(args) -> None:
         "data": "synthetic",
         "config": workload_config(args.workload, args.batch, 1),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{steps} decode positions of batch {args.batch} from a synthetic "
+                         "sample": f"{steps} decode positions of {cpu_batch} of the {args.batch} sequences from a synthetic "
                                    "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference ships no CPU-runnable sparse decode (its kernels are Triton-only and its "
@@ -292,6 +298,7 @@ def run_ours(args) -> None:
     bounds = torch.randint(0, cfg.boundary_vocab_size, (B, T),
                            generator=torch.Generator().manual_seed(seed + 77 + rank)).to(device)
 
+    log(f"state allocated: {dec.state_bytes() / 1e9:.1f} GB")
     launches_before = _abi.launch_count()
     dec.step(tokens[:, 0], bounds[:, 0])
     kernels_per_step = _abi.launch_count() - launches_before
@@ -303,6 +310,7 @@ def run_ours(args) -> None:
         dec.static_boundaries.copy_(bounds[:, t])
         dec.replay()
     torch.cuda.synchronize()
+    log(f"prefix of {prefix} positions done")
     assert int(dec.position.item()) == prefix
     assert _abi.read_status() == 0, "a kernel reported a device-side error during the prefix"
 
@@ -382,7 +390,9 @@ def run_ours(args) -> None:
     total_ms, e2e_ms, warm_ms = [float(v) for v in times.tolist()]
 
     if rank == 0:
+        log(f"timed region done: {total_ms / args.steps:.3f} ms/step")
         table = kernel_table(dec)
+        log("kernel table done")
         peaks = {}
         try:
             peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -394,7 +404,9 @@ def run_ours(args) -> None:
         lib_us = sum(v["us_per_step"] for v in table.values())
         threads = os.cpu_count() or 1
         cpu_steps = 6
-        cpu_value, cpu_elapsed, cpu_threads = cpu_decode_rate(args.workload, B, cpu_steps, 1, threads)
+        cpu_batch = min(B, CPU_SAMPLE_BATCH)
+        log(f"cpu baseline: {cpu_steps} positions of {cpu_batch} sequences on {threads} threads")
+        cpu_value, cpu_elapsed, cpu_threads = cpu_decode_rate(args.workload, cpu_batch, cpu_steps, 1, threads)
         line = {
             "metric": METRIC, "value": world * B * args.steps / (total_ms / 1e3), "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -417,7 +429,7 @@ def run_ours(args) -> None:
                          "note": "batch-8 decode launches move < 1 MB each and are latency-bound"},
             "kernels": table,
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cpu_threads, "kind": "port",
-                             "sample": f"{cpu_steps} decode positions of batch {B} from a synthetic "
+                             "sample": f"{cpu_steps} decode positions of {cpu_batch} of the {B} sequences from a synthetic "
                                        "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
         }
         print(json.dumps(line), flush=True)

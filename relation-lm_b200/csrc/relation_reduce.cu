@@ -8,6 +8,15 @@
 #include "rlm_common.cuh"
 
 namespace rlm {
+// tensor-core form for launches with many relation rows (relation_hidden_tc.cu)
+bool hidden_tc_applicable(bool update, int n_rows, int rdim, int hdim, int k_out, int cache_dtype,
+                          int weight_dtype, const void* expanded_cache, const void* out, int out_dtype);
+int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cache,
+                     const int32_t* anchor_index, const int32_t* partner_index,
+                     const void* anchor_weight, const void* partner_weight, const void* product_weight,
+                     const void* first_bias, const int64_t* position, const int32_t* row_batch, void* out,
+                     int n_rows, int n_seq, int max_t, int rdim, int hdim, int k_out, int dtype,
+                     int out_dtype, int32_t* status, void* stream);
 #ifdef RLM_TRACE
 __device__ long long g_trace_reduce[64 * 32];
 #define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x + blockIdx.y * gridDim.x < 64) g_trace_reduce[(blockIdx.x + blockIdx.y * gridDim.x) * 32 + (i)] = clock64(); } while (0)
@@ -368,6 +377,12 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         set_error("relation_hidden: weight matrices and the operand cache must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
+    if (hidden_tc_applicable(update, a.n_rows, a.rdim, a.hdim, a.k_out, a.cache_dtype, a.weight_dtype,
+                             a.expanded_cache, a.out, a.out_dtype))
+        return launch_hidden_tc(update, a.expanded_cache, a.operand_cache, a.anchor_index, a.partner_index,
+                                a.anchor_weight, a.partner_weight, a.product_weight, a.first_bias,
+                                a.position, a.row_batch, a.out, a.n_rows, a.n_seq, a.max_t, a.rdim, a.hdim,
+                                a.k_out, a.cache_dtype, a.out_dtype, a.status, stream);
     const bool wide = kRB * a.k_out > 32;      // more than 4 relation rows per thread
     if (update) return wide ? launch_hidden_as<true, 8>(a, stream) : launch_hidden_as<true, 4>(a, stream);
     return wide ? launch_hidden_as<false, 8>(a, stream) : launch_hidden_as<false, 4>(a, stream);

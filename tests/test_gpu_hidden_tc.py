@@ -1,0 +1,86 @@
+"""GPU parity of the tensor-core form of the relation-hidden kernels (launches with at least
+256 (row, partner) pairs and 16-bit caches) against the CPU oracle, through the C ABI.
+Tolerance: 1e-2 relative / absolute, the 16-bit bound of the path."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import oracle
+from gpu_util import assert_status_clear, position_tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, B, T, R, H, K, dtype, t):
+    g = torch.Generator().manual_seed(seed)
+    operand = torch.randn(B, T, R, generator=g).to(dtype)
+    expanded = (torch.randn(B, T, 2 * H, generator=g) * 0.3).to(dtype)
+    wm, wa, wp = [(torch.randn(H, R, generator=g) * 0.05).to(dtype) for _ in range(3)]
+    bias = (torch.randn(H, generator=g) * 0.1).to(dtype)
+    anchor = torch.randint(0, t + 1, (B,), generator=g, dtype=torch.int32)
+    partner = torch.randint(0, t + 1, (B, K), generator=g, dtype=torch.int32)
+    anchor[::3] = t                      # rows whose anchor is the position being written
+    partner[1::4, 0] = t                 # rows with a partner at the position being written
+    partner[:, -1] = t - 1000            # empty-slot sentinel (negative): clamped, never faults
+    return operand, expanded, wm, wa, wp, bias, anchor, partner
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,K,H,R", [(64, 8, 256, 128), (70, 8, 384, 128), (80, 5, 256, 64),
+                                     (100, 4, 128, 128), (32, 16, 256, 128)])
+def test_update_form_matches_the_oracle(B, K, H, R, dtype):
+    """Hidden rows and the freshly written expanded-cache row, ragged last tiles (rows not a
+    multiple of 128 / K, K not a divisor of 128) included."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cache_update
+
+    T, t = 96, 77
+    operand, expanded, wm, wa, wp, bias, anchor, partner = _case(9000 + B + K, B, T, R, H, K, dtype, t)
+    cache = expanded.cuda().clone()
+    got = relation_hidden_cache_update(cache, operand.cuda(), anchor.cuda(), partner.cuda(), wa.cuda(),
+                                       wp.cuda(), wm.cuda(), bias.cuda(), position_tensor(t))
+    want, want_cache = oracle.relation_hidden(expanded, operand, anchor, partner, wm, wa, wp, bias, position=t)
+    assert torch.allclose(got.cpu(), want, atol=1e-2, rtol=1e-2), (got.cpu() - want).abs().max()
+    assert torch.allclose(cache.float().cpu(), want_cache.float(), atol=1e-2, rtol=1e-2)
+    untouched = torch.ones(T, dtype=torch.bool)
+    untouched[t] = False
+    assert torch.equal(cache.cpu()[:, untouched], expanded[:, untouched])
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_cached_form_and_low_precision_output(out_dtype):
+    from relation_lm.kernels.relation_reduce import relation_hidden_cache_update_out, relation_hidden_cached
+
+    B, T, R, H, K, t = 48, 64, 128, 512, 8, 40
+    dtype = torch.bfloat16
+    operand, expanded, wm, wa, wp, bias, anchor, partner = _case(9100, B, T, R, H, K, dtype, t)
+    want, _ = oracle.relation_hidden(expanded, operand, anchor, partner, wm)
+    if out_dtype == torch.float32:
+        got = relation_hidden_cached(expanded.cuda(), operand.cuda(), anchor.cuda(), partner.cuda(), wm.cuda())
+    else:
+        want, _ = oracle.relation_hidden(expanded, operand, anchor, partner, wm, wa, wp, bias, position=t)
+        got = torch.empty(B, K, H, device="cuda", dtype=out_dtype)
+        relation_hidden_cache_update_out(got, expanded.cuda().clone(), operand.cuda(), anchor.cuda(),
+                                         partner.cuda(), wa.cuda(), wp.cuda(), wm.cuda(), bias.cuda(),
+                                         position_tensor(t))
+    assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), (got.float().cpu() - want).abs().max()
+    assert_status_clear()
+
+
+def test_same_results_as_the_small_launch_form():
+    """The same rows through the tensor-core form (one launch of 64 sequences) and through the
+    CUDA-core form (launches of 8 sequences) agree within the 16-bit bound."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows
+
+    B, T, R, H, K, t = 64, 64, 128, 256, 8, 63
+    dtype = torch.bfloat16
+    operand, expanded, wm, _, _, _, anchor, partner = _case(9200, B, T, R, H, K, dtype, t)
+    ex, op, wm_d = expanded.cuda(), operand.cuda(), wm.cuda()
+    rows = torch.arange(B, dtype=torch.int32)
+    big = relation_hidden_cached_rows(ex, op, anchor.cuda(), partner.cuda(), wm_d, rows.cuda())
+    parts = [relation_hidden_cached_rows(ex, op, anchor[i:i + 8].cuda(), partner[i:i + 8].cuda(), wm_d,
+                                         rows[i:i + 8].cuda()) for i in range(0, B, 8)]
+    small = torch.cat(parts)
+    assert torch.allclose(big, small, atol=1e-2, rtol=1e-2), (big - small).abs().max()
+    assert_status_clear()
