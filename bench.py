@@ -188,7 +188,9 @@ def kernel_table(dec, graph_iters: int = 20):
     """Average launch duration of each library kernel on the decoder's own state, captured in
     CUDA graphs (one launch per layer per graph, so consecutive launches touch different
     caches), with the algorithmic bytes of SURVEY's per-row formulas."""
-    from relation_lm.kernels.relation_reduce import relation_hidden_cache_update, relation_norm_reduce
+    from relation_lm.kernels.packed_projection import norm_projection
+    from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update_out,
+                                                     relation_norm_reduce_residual)
     from relation_lm.kernels.relation_select import relation_select_packed
     from relation_lm.kernels.router_cache import sparse_cache_append
 
@@ -203,6 +205,8 @@ def kernel_table(dec, graph_iters: int = 20):
     partner = torch.randint(0, cfg.max_context, (B, K), device=dev, dtype=torch.int32)
     scores = torch.randn(B, K, device=dev)
     raw = torch.randn(L, B, K, d, device=dev).to(dec.dtype)
+    hidden_out = torch.empty(B, K, H, device=dev, dtype=dec.dtype)
+    residual = torch.randn(B, d, device=dev)
 
     def select(l):
         relation_select_packed(q[:, 0:64], dec.anchor_keys[l], q[:, 64:128], dec.router_stats[0][l],
@@ -212,12 +216,16 @@ def kernel_table(dec, graph_iters: int = 20):
                                w["partner_bias"][l], pos, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
 
     def hidden(l):
-        relation_hidden_cache_update(dec.expanded_cache[l], dec.operand_cache[l], anchor, partner,
-                                     w["anchor_weight"][l], w["partner_weight"][l],
-                                     w["product_weight"][l], w["first_bias"][l], pos)
+        relation_hidden_cache_update_out(hidden_out, dec.expanded_cache[l], dec.operand_cache[l], anchor,
+                                         partner, w["anchor_weight"][l], w["partner_weight"][l],
+                                         w["product_weight"][l], w["first_bias"][l], pos)
 
     def reduce(l):
-        relation_norm_reduce(raw[l], scores, w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps)
+        relation_norm_reduce_residual(raw[l], scores, w["relation_norm_w"][l], w["relation_norm_b"][l], pos,
+                                      cfg.norm_eps, residual, w["mix"][l])
+
+    def query(l):
+        norm_projection(residual, w["input_norm_w"][l], w["input_norm_b"][l], w["w_query"][l], cfg.norm_eps)
 
     def append(_):
         sparse_cache_append(packed, dec.anchor_keys, dec.partner_keys, dec.operand_cache,
@@ -228,14 +236,16 @@ def kernel_table(dec, graph_iters: int = 20):
     nb = cfg.max_context // cfg.block_size
     bytes_per_launch = {
         "relation_select_kernel": B * (e * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K),
-        "relation_hidden_kernel<update>": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + 4 * K * H) + e * 3 * H * R + B * e * (R + 2 * H),
-        "relation_norm_reduce_kernel": B * (e * K * d + 4 * K + 4 * d) + 4 * 2 * d,
+        "relation_hidden_kernel<update>": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + e * K * H) + e * 3 * H * R + B * e * (R + 2 * H),
+        "relation_norm_reduce_kernel": B * (e * K * d + 4 * K + 4 * d + 8 * d) + 4 * 3 * d,
+        "norm_projection_kernel(query)": B * (4 * d + e * 256) + e * 256 * d + 8 * d,
         "router_cache_update_kernel(all layers)": L * B * (e * 64 * (2 + 4 + 4 + 2 * cfg.block_size + 4) + 2 * 64 * 4 + 2 * e * (256 + R)),
     }
     table = {}
     for name, fn, per_graph in (("relation_select_kernel", select, L),
                                 ("relation_hidden_kernel<update>", hidden, L),
                                 ("relation_norm_reduce_kernel", reduce, L),
+                                ("norm_projection_kernel(query)", query, L),
                                 ("router_cache_update_kernel(all layers)", append, 1)):
         for l in range(per_graph):
             fn(l)

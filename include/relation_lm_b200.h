@@ -237,13 +237,25 @@ int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weigh
  * out[rows, n_out] = LayerNorm(x; gamma, beta, eps) . weight[n_out, d_in]^T with the normalised
  * rows rounded to the weight dtype, as the reference's `layer_norm(...)` followed by `F.linear`
  * on a low-precision model does.  gamma = beta = NULL skips the normalisation (plain cast).
- *   x [rows, d_in] fp32, row stride in ELEMENTS; rows <= 128; d_in a multiple of 64 up to 1024;
+ *   x [rows, d_in] fp32, row stride in ELEMENTS (row tiles of 128); d_in a multiple of 64 up to 1024;
  *   weight bfloat16 / float16 [n_out, d_in]; n_out a multiple of 32; out contiguous, any dtype.
  */
 int rlm_norm_projection(const float* x, int64_t x_row_stride, const float* gamma,
                         const float* beta, float eps, const void* weight, void* out, int rows,
                         int d_in, int n_out, int weight_dtype, int out_dtype, int32_t* status,
                         void* stream);
+
+/*
+ * LayerNorm of fp32 rows into a 16-bit matrix (extension): the first half of
+ * rlm_norm_projection for batches beyond one row tile, where normalising once and streaming
+ * the result through rlm_packed_projection beats normalising per output-column tile.  Same
+ * arithmetic as rlm_norm_projection; gamma = beta = NULL gives a plain cast.  No reference
+ * counterpart beyond `layer_norm(...).to(dtype)` in the model code.
+ *   x [rows, d_in] fp32, row stride in ELEMENTS; d_in a multiple of 8 up to 1024;
+ *   out [rows, d_in] contiguous bfloat16 / float16.
+ */
+int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const float* gamma, const float* beta,
+                        float eps, void* out, int rows, int d_in, int out_dtype, void* stream);
 
 /*
  * Decode-state append for every layer of a stack in one launch (extension).  Does what a

@@ -153,8 +153,8 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
 
 // ------------------------------------------------------------------ LayerNorm + projection
 //
-// out = LayerNorm(x) . w^T for at most 128 fp32 rows (decode batches): every CTA normalises
-// the rows itself (a few KB), writes them as 16-bit values straight into the swizzled
+// out = LayerNorm(x) . w^T for fp32 rows (decode batches): every CTA normalises the (at most
+// 128) rows of its tile itself (a few KB), writes them as 16-bit values straight into the swizzled
 // K-major layout the tensor core reads, and streams only its BN x K slice of w with TMA.
 // The x tile of K-block kb starts kb * a_stride bytes into the A region, a_stride covering
 // just the row groups that exist; the MMA reads 128 rows from there, rows that do not exist
@@ -173,6 +173,7 @@ struct NormGemmArgs {
     uint32_t idesc;
     uint32_t a_stride;     // bytes between consecutive K-blocks of the x tile
     uint32_t a_bytes;      // size of the A region (multiple of 1024)
+    int tile_rows;         // rows per CTA (multiple of 8, at most 128)
 };
 
 constexpr int kNormMaxPerLane = 4;     // 16-byte chunks per lane: d_in <= 1024
@@ -194,7 +195,8 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
     const uint32_t a_addr = smem_u32(a_tile);
     const uint32_t ring_addr = a_addr + a.a_bytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * a.tile_rows;
+    const int m_here = min(a.m - m0, a.tile_rows);
     const int k_iters = (a.k + kBK - 1) / kBK;
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
@@ -220,8 +222,8 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
 
     // LayerNorm of the rows, one warp per row, lane l owns the 16-byte chunks l, l+32, ...
     const int chunks = a.k / 8;
-    for (int r = warp; r < a.m; r += kGemmThreads / 32) {
-        const float* row = a.x + r * a.x_stride;
+    for (int r = warp; r < m_here; r += kGemmThreads / 32) {
+        const float* row = a.x + (m0 + r) * a.x_stride;
         float v[kNormMaxPerLane][8];
         float sum = 0.0f;
 #pragma unroll
@@ -311,14 +313,14 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
     if (!__syncthreads_or(!ready)) {
         const int row = warp * 32 + lane;
-        if (warp * 32 < a.m) {      // warps whose 32 rows do not exist skip the read-back
+        if (warp * 32 < m_here) {   // warps whose 32 rows do not exist skip the read-back
 #pragma unroll
             for (int c = 0; c < BN; c += 16) {
                 uint32_t v[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < a.m) {
-                    const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
+                if (row < m_here) {
+                    const size_t at = static_cast<size_t>(m0 + row) * a.n + n0 + c;
                     if (a.out_dtype == RLM_F32) {
                         float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
 #pragma unroll
@@ -355,6 +357,79 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
                      ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+// ------------------------------------------------------------------ LayerNorm -> 16-bit rows
+//
+// For batches beyond one row tile the normalisation is done once (one warp per row) into a
+// 16-bit matrix that packed_projection_kernel then streams with TMA, instead of once per
+// output-column tile.  Arithmetic identical to the fused kernel above.
+constexpr int kCastThreads = 256;
+
+struct NormCastArgs {
+    const float* x;
+    const float* gamma;
+    const float* beta;
+    void* out;
+    int64_t x_stride;
+    float eps;
+    int m, k, out_dtype;
+};
+
+__global__ void __launch_bounds__(kCastThreads) layer_norm_cast_kernel(const NormCastArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (kCastThreads / 32) + (threadIdx.x >> 5);
+    if (r >= a.m) return;
+    const int chunks = a.k / 8;
+    const float* row = a.x + r * a.x_stride;
+    float v[kNormMaxPerLane][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            const float4 lo = *reinterpret_cast<const float4*>(row + 8 * c);
+            const float4 hi = *reinterpret_cast<const float4*>(row + 8 * c + 4);
+            v[i][0] = lo.x; v[i][1] = lo.y; v[i][2] = lo.z; v[i][3] = lo.w;
+            v[i][4] = hi.x; v[i][5] = hi.y; v[i][6] = hi.z; v[i][7] = hi.w;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum += v[i][e];
+        }
+    }
+    float mean = 0.0f, inv = 1.0f;
+    if (a.gamma) {
+        mean = warp_sum(sum) / static_cast<float>(a.k);
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kNormMaxPerLane; ++i)
+            if (lane + 32 * i < chunks)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { float d = v[i][e] - mean; sq = fmaf(d, d, sq); }
+        inv = rsqrtf(warp_sum(sq) / static_cast<float>(a.k) + a.eps);
+    }
+#pragma unroll
+    for (int i = 0; i < kNormMaxPerLane; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= chunks) continue;
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+            float y0 = (v[i][e] - mean) * inv, y1 = (v[i][e + 1] - mean) * inv;
+            if (a.gamma) {
+                y0 = fmaf(y0, a.gamma[8 * c + e], a.beta[8 * c + e]);
+                y1 = fmaf(y1, a.gamma[8 * c + e + 1], a.beta[8 * c + e + 1]);
+            }
+            if (a.out_dtype == RLM_BF16) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+                __half2 h = __floats2half2_rn(y0, y1);
+                packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+        *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + static_cast<size_t>(r) * a.k + 8 * c) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+}
+
 template <int BN>
 int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a, void* stream) {
     const int smem_bytes = stages_for(BN) * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
@@ -377,7 +452,8 @@ int launch_norm_gemm(const CUtensorMap& mw, const NormGemmArgs& a, void* stream)
     auto kernel = norm_projection_kernel<BN>;
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
-    kernel<<<a.n / BN, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mw, a);
+    dim3 grid(a.n / BN, (a.m + a.tile_rows - 1) / a.tile_rows);
+    kernel<<<grid, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mw, a);
     count_launch();
     return check_launch("norm_projection_kernel");
 }
@@ -395,9 +471,9 @@ extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const f
         set_error("norm_projection: NULL pointer (gamma and beta go together)");
         return RLM_ERR_NULL;
     }
-    if (rows < 0 || rows > kBM || d_in < 64 || d_in % 64 != 0 || d_in > 256 * kNormMaxPerLane ||
+    if (rows < 0 || d_in < 64 || d_in % 64 != 0 || d_in > 256 * kNormMaxPerLane ||
         n_out < 32 || n_out % 32 != 0 || x_row_stride < d_in || x_row_stride % 4 != 0) {
-        set_error("norm_projection: need rows <= 128, d_in a multiple of 64 up to 1024, n_out a multiple of 32");
+        set_error("norm_projection: need d_in a multiple of 64 up to 1024 and n_out a multiple of 32");
         return RLM_ERR_SHAPE;
     }
     if ((weight_dtype != RLM_BF16 && weight_dtype != RLM_F16) || !valid_dtype(out_dtype)) {
@@ -408,9 +484,10 @@ extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const f
         set_error("norm_projection: tensors must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
+    const int m_tiles = (rows + kBM - 1) / kBM, tile_rows = rows < kBM ? rows : kBM;
     int bn = 128;
-    if (n_out % 128 != 0 || n_out / 128 < 100) bn = 64;
-    if (n_out % 64 != 0 || (n_out / 64 < 100 && bn == 64)) bn = 32;
+    if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
+    if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
     CUtensorMap mw;
     if (!make_map(&mw, weight, n_out, d_in, d_in, bn, weight_dtype)) {
         set_error("norm_projection: cuTensorMapEncodeTiled failed");
@@ -422,11 +499,49 @@ extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const f
     const uint32_t fmt = weight_dtype == RLM_BF16 ? 1u : 0u;
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
               (static_cast<uint32_t>(kBM >> 4) << 24);
-    a.a_stride = static_cast<uint32_t>((rows + 7) / 8) * 1024u;
-    a.a_bytes = (static_cast<uint32_t>(d_in / kBK) - 1u) * a.a_stride + kBM * kBK * 2;
+    // rows per CTA: as many as the shared memory left by the weight ring holds
+    a.tile_rows = ((tile_rows + 7) / 8) * 8;
+    for (;;) {
+        a.a_stride = static_cast<uint32_t>(a.tile_rows / 8) * 1024u;
+        a.a_bytes = (static_cast<uint32_t>(d_in / kBK) - 1u) * a.a_stride + kBM * kBK * 2;
+        if (static_cast<int>(a.a_bytes) + 8 * bn * kBK * 2 + 1024 <= kSmemDynamicLimit || a.tile_rows <= 8)
+            break;
+        a.tile_rows -= 8;
+    }
     if (bn == 32) return launch_norm_gemm<32>(mw, a, stream);
     if (bn == 64) return launch_norm_gemm<64>(mw, a, stream);
     return launch_norm_gemm<128>(mw, a, stream);
+}
+
+extern "C" int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const float* gamma,
+                                   const float* beta, float eps, void* out, int rows, int d_in,
+                                   int out_dtype, void* stream) {
+    using namespace rlm;
+    if (rows == 0) return RLM_OK;
+    if (!x || !out || ((gamma == nullptr) != (beta == nullptr))) {
+        set_error("layer_norm_cast: NULL pointer (gamma and beta go together)");
+        return RLM_ERR_NULL;
+    }
+    if (rows < 0 || d_in < 8 || d_in % 8 != 0 || d_in > 256 * kNormMaxPerLane || x_row_stride < d_in ||
+        x_row_stride % 4 != 0) {
+        set_error("layer_norm_cast: need d_in a multiple of 8 up to 1024");
+        return RLM_ERR_SHAPE;
+    }
+    if (out_dtype != RLM_BF16 && out_dtype != RLM_F16) {
+        set_error("layer_norm_cast: the output must be bfloat16 or float16");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(x) || !aligned16(out) || (gamma && (!aligned16(gamma) || !aligned16(beta)))) {
+        set_error("layer_norm_cast: tensors must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    NormCastArgs a{};
+    a.x = x; a.gamma = gamma; a.beta = beta; a.out = out; a.x_stride = x_row_stride; a.eps = eps;
+    a.m = rows; a.k = d_in; a.out_dtype = out_dtype;
+    const int per_cta = kCastThreads / 32;
+    layer_norm_cast_kernel<<<(rows + per_cta - 1) / per_cta, kCastThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    count_launch();
+    return check_launch("layer_norm_cast_kernel");
 }
 
 extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
@@ -450,9 +565,10 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     }
     // Tile width: with few rows the weight read dominates, so pick the widest tile that still
     // gives about one CTA per SM; with many rows use wide tiles.
+    const int m_tiles = (rows + kBM - 1) / kBM;
     int bn = 128;
-    if (n_out % 128 != 0 || (rows <= 128 && n_out / 128 < 100)) bn = 64;
-    if (n_out % 64 != 0 || (rows <= 128 && n_out / 64 < 100 && bn == 64)) bn = 32;
+    if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
+    if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
     // x tile: the box holds only the rows that exist (a multiple of 8, at most 128); the MMA
     // reads 128 rows of the stage, the rest is never stored
     const int box_rows = rows >= kBM ? kBM : ((rows + 7) / 8) * 8;

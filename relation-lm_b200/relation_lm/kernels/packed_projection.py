@@ -13,6 +13,8 @@ from torch import Tensor
 
 from relation_lm.kernels import _abi
 
+_ROW_TILE = 128    # rows one CTA of the fused LayerNorm + projection kernel normalises
+
 
 @torch.library.custom_op("relation_lm::packed_projection", mutates_args=(), device_types="cuda")
 def packed_projection(x: Tensor, weight: Tensor) -> Tensor:
@@ -42,8 +44,8 @@ def _(x, weight):
 @torch.library.custom_op("relation_lm::norm_projection", mutates_args=(), device_types="cuda")
 def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: Tensor,
                     norm_eps: float) -> Tensor:
-    """``layer_norm(x) @ weight.T`` in one launch for at most 128 fp32 rows: the rows are
-    normalised in fp32, rounded to the weight dtype and multiplied on the tensor cores."""
+    """``layer_norm(x) @ weight.T`` in one launch for fp32 rows: the rows are normalised in
+    fp32, rounded to the weight dtype and multiplied on the tensor cores."""
     device = _abi.require_cuda_rows(x=x)
     _abi.require_cuda_contiguous(norm_weight=norm_weight, norm_bias=norm_bias, weight=weight)
     if x.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_bias.dtype != torch.float32:
@@ -51,6 +53,14 @@ def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: T
     if weight.dim() != 2 or weight.size(1) != x.size(1) or norm_weight.numel() != x.size(1):
         raise ValueError("weight must be [n_out, d_in] and the norm parameters [d_in]")
     rows, d_in = x.shape
+    if rows > _ROW_TILE:
+        # beyond one row tile: normalise once into a 16-bit matrix, then the TMA-fed GEMM
+        normalized = torch.empty((rows, d_in), device=device, dtype=weight.dtype)
+        with _abi.device_guard(device):
+            _abi.check(_abi.LIB.rlm_layer_norm_cast(
+                _abi.ptr(x), x.stride(0), _abi.ptr(norm_weight), _abi.ptr(norm_bias), float(norm_eps),
+                _abi.ptr(normalized), rows, d_in, _abi.code(normalized), _abi.stream_ptr(device)))
+        return packed_projection(normalized, weight)
     out = torch.empty((rows, weight.size(0)), device=device, dtype=weight.dtype)
     with _abi.device_guard(device):
         _abi.check(_abi.LIB.rlm_norm_projection(
