@@ -452,13 +452,14 @@ def run_ours(args) -> None:
 def run_kernel_case(args) -> None:
     """A handful of eager launches of one kernel on caches of several layers (hundreds of MB,
     so consecutive launches do not hit L2), at the d_model-768 / ctx-2048 / block-64 decode shape."""
-    from relation_lm.kernels.relation_reduce import relation_hidden_cached, relation_norm_reduce
+    from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update_out, relation_hidden_cached,
+                                                     relation_norm_reduce)
     from relation_lm.kernels.relation_select import relation_select_packed
     from relation_lm.kernels.router_cache import router_cache_update
 
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
-    B, T, bs, L, TOP, K, H, R, d = args.rows, 2048, 64, 128, 2, 8, 3072, 128, 768
+    B, T, bs, L, TOP, K, H, R, d = args.rows, args.ctx, 64, 128, 2, 8, 3072, 128, 768
     nb, sets = T // bs, 4
     rn = lambda *s: torch.randn(*s, device=dev).bfloat16()  # noqa: E731
     pos = torch.tensor(T - 1, device=dev)
@@ -480,6 +481,15 @@ def run_kernel_case(args) -> None:
                 pi = torch.randint(0, T, (B, K), device=dev, dtype=torch.int32)
             ex, op = S[i % 2]
             fn = lambda: relation_hidden_cached(ex, op, ai, pi, wm)  # noqa: E731
+        elif args.kernel_case == "hidden_update":
+            if i == 0:
+                S = [(rn(B, T, 2 * H), rn(B, T, R)) for _ in range(2)]
+                wm, wa, wp, b1 = rn(H, R) * 0.02, rn(H, R) * 0.02, rn(H, R) * 0.02, rn(H) * 0.01
+                ai = torch.randint(0, T, (B,), device=dev, dtype=torch.int32)
+                pi = torch.randint(0, T, (B, K), device=dev, dtype=torch.int32)
+                hidden_out = torch.empty(B, K, H, device=dev, dtype=torch.bfloat16)
+            ex, op = S[i % 2]
+            fn = lambda: relation_hidden_cache_update_out(hidden_out, ex, op, ai, pi, wa, wp, wm, b1, pos)  # noqa: E731
         elif args.kernel_case == "norm":
             if i == 0:
                 S = [rn(B, K, d) for _ in range(sets)]
@@ -512,10 +522,12 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
-    parser.add_argument("--kernel-case", choices=("select", "hidden", "norm", "router"), default=None,
+    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "norm", "router"), default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")
     parser.add_argument("--rows", type=int, default=256)
+    parser.add_argument("--ctx", type=int, default=2048,
+                        help="cache length of --kernel-case runs (shorter caches keep profiler captures small)")
     args = parser.parse_args()
     if args.kernel_case:
         run_kernel_case(args)

@@ -4,56 +4,96 @@
 //   out[row, k, h] = gelu( product_weight[h, :] . (operand[a] * operand[p_k])
 //                          + expanded[a, h] + expanded[p_k, H + h] )
 //
-// with a = anchor_index[row], p_k = partner_index[row, k], and, in the update form, the
-// expanded row of the current position computed here first
-// (expanded[t, :H] = anchor_weight . operand[t] + bias, expanded[t, H:] = partner_weight . operand[t]),
-// written to the cache and used un-rounded by the rows that selected position t.
+// with a = anchor_index[row], p_k = partner_index[row, k].  The update form first writes the
+// expanded row of the current position,
+//   expanded[t, :H] = anchor_weight . operand[t] + bias,  expanded[t, H:] = partner_weight . operand[t],
+// with a kernel of its own (expanded_row_update_kernel) and then runs the gather kernel, which
+// therefore reads position t like any other row (rounded to the cache dtype).
 //
-// One CTA per tile of 128 (row, partner) pairs x 128 hidden columns:
-//   * the three 128 x R weight tiles arrive by tiled TMA loads (128-byte swizzle, no multicast);
-//   * all threads gather the operand rows, multiply them in fp32 and write the 16-bit products
-//     straight into the swizzled K-major layout the tensor core reads (A tile, 128 x R);
-//   * one thread issues tcgen05.mma: pairs x weight^T into 128 TMEM columns and, in the update
-//     form, weight x current-operands^T (hidden columns on the TMEM lanes, the tile's sequences
-//     on 16..32 columns) for the two fresh half rows;
+// relation_hidden_tc_kernel, one CTA per tile of 128 (row, partner) pairs x 128 hidden columns:
+//   * the 128 x R product-weight tile arrives by tiled TMA loads (128-byte swizzle, no multicast);
+//   * all threads copy the partner operand rows asynchronously (cp.async) straight into the
+//     swizzled K-major layout the tensor core reads (A tile, 128 x R) and multiply them there,
+//     in fp32, with the anchor operand chunks they hold in registers;
+//   * one thread issues tcgen05.mma (pairs x weight^T into 128 TMEM columns);
+//   * once the MMA has consumed the tiles, all threads gather the two expanded-cache terms of
+//     every pair into the same shared memory as 16-byte asynchronous copies (cp.async), two
+//     256-byte tile rows per warp instruction;
 //   * the epilogue reads TMEM with tcgen05.ld; every thread owns one pair row and 64 hidden
-//     columns, adds the two gathered expanded-cache terms (requested before the MMA wait),
-//     applies GELU and stores.
-// Every wait is bounded; on expiry the kernel sets RLM_DEV_TIMEOUT, frees its TMEM and returns.
+//     columns, adds the staged terms, applies GELU and writes 16-bit results over the staged
+//     partner term; the rows then leave with coalesced 16-byte stores (fp32 results are stored
+//     directly).
+//     Three CTAs share an SM so that one tile's gathers overlap another's arithmetic.
+// expanded_row_update_kernel, one CTA per 128 hidden columns of one half and up to 64 sequences:
+//   weight tile (TMA) x current-operand rows^T, hidden columns on the TMEM lanes and sequences on
+//   the TMEM columns, so that a warp's stores of one sequence are contiguous in the cache row.
+// Every wait is bounded; on expiry a kernel sets RLM_DEV_TIMEOUT, frees its TMEM and returns.
 //
 // Semantics follow src/relation_lm/kernels/relation_reduce.py:72-146 and 186-309 of the
 // reference project; the products are rounded to the cache dtype before the tensor-core
-// contraction (the reference contracts fp32 products), which the 16-bit tolerance covers.
+// contraction and GELU uses a 1.5e-7 polynomial erfc on the hardware reciprocal and exponential
+// (the reference contracts fp32 products and calls erf), which the 16-bit tolerance of this path covers.
 
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
+#ifdef RLM_TRACE
+// Phase timestamps for working builds (never compiled into the shipped library).
+__device__ long long g_trace_tc[64 * 32];
+__device__ unsigned long long g_span_tc[1024 * 3];
+__device__ __forceinline__ unsigned long long tc_globaltimer() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ unsigned tc_smid() { unsigned s; asm volatile("mov.u32 %0, %smid;" : "=r"(s)); return s; }
+#define RLM_TC_PROBE(i) do { if (threadIdx.x == 0) { const int blk_ = blockIdx.x + blockIdx.y * gridDim.x; if (blk_ < 64) g_trace_tc[blk_ * 32 + (i)] = clock64(); if (blk_ < 1024 && ((i) == 0 || (i) == 8)) { g_span_tc[blk_ * 3 + ((i) ? 1 : 0)] = tc_globaltimer(); g_span_tc[blk_ * 3 + 2] = tc_smid(); } } } while (0)
+#else
+#define RLM_TC_PROBE(i) do { } while (0)
+#endif
 namespace {
 
 constexpr int kTcThreads = 256;
 constexpr int kTcBN = 128;          // hidden columns per tile
-constexpr int kTcMaxFresh = 32;     // sequences per tile in the update form (128 / K, K >= 4)
+constexpr int kUpdThreads = 128;
+constexpr int kUpdMaxSeq = 64;      // sequences per CTA of the update kernel
 
 struct HiddenTcArgs {
-    void* expanded_cache;
+    const void* expanded_cache;
     const void* operand_cache;
     const int32_t* anchor_index;
     const int32_t* partner_index;
-    const void* first_bias;
-    const int64_t* position;
     const int32_t* row_batch;
     void* out;
     int32_t* status;
     int n_rows, n_seq, max_t, rdim, hdim, k_out;
     int dtype, out_dtype;
     int rows_per_tile;      // 128 / K
-    int n_fresh;            // rows_per_tile rounded up to 16 (update form)
-    int tmem_cols;
-    uint32_t idesc_main, idesc_fresh;
+    int inv_k16;            // ceil(65536 / K): r / K == (r * inv_k16) >> 16 for r < 256
+    uint32_t idesc;
 };
 
-__device__ __forceinline__ float gelu_erf_tc(float x) {
-    return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+struct RowUpdateArgs {
+    void* expanded_cache;
+    const void* operand_cache;
+    const void* first_bias;
+    const int64_t* position;
+    int32_t* status;
+    int n_seq, max_t, rdim, hdim, dtype;
+};
+
+// GELU(x) = x * Phi(x) with Phi(x) = 1 - erfc(|x| / sqrt 2) / 2 mirrored for x < 0, erfc from the
+// Abramowitz & Stegun 7.1.26 polynomial (absolute error below 1.5e-7) on the hardware
+// reciprocal and exponential: about a third of the instructions of erff, enough for 16-bit
+// outputs.  The polynomial coefficients carry the factor 1/2.
+__device__ __forceinline__ float gelu_tc(float x) {
+    const float z = fabsf(x) * 0.70710678118654752f;
+    float t, e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * z * -1.4426950408889634f));
+    float p = 0.5307027145f;
+    p = fmaf(p, t, -0.7265760135f);
+    p = fmaf(p, t, 0.7107068705f);
+    p = fmaf(p, t, -0.142248368f);
+    p = fmaf(p, t, 0.127414796f);
+    const float h = p * t * e;                 // erfc(z) / 2
+    return x * (x >= 0.0f ? 1.0f - h : h);
 }
 
 __device__ __forceinline__ void unpack8(const uint4& raw, int dtype, float (&f)[8]) {
@@ -79,10 +119,27 @@ __device__ __forceinline__ uint32_t swizzled(int r, int c, uint32_t kblock_bytes
            static_cast<uint32_t>(r & 7) * 128u + static_cast<uint32_t>(((c & 7) ^ (r & 7)) << 4);
 }
 
-template <bool kUpdate>
-__global__ void __launch_bounds__(kTcThreads) relation_hidden_tc_kernel(
-    const __grid_constant__ CUtensorMap map_wm, const __grid_constant__ CUtensorMap map_wa,
-    const __grid_constant__ CUtensorMap map_wp, const HiddenTcArgs a) {
+// ------------------------------------------------------------------ gather + product GEMM + GELU
+
+constexpr uint32_t kRowBytes = kTcBN * 2;            // one tile row of a 16-bit matrix
+constexpr uint32_t kRowStride = kRowBytes + 16;      // padded: conflict-free 16-byte row accesses
+
+// Shared-memory plan of the gather kernel (bytes past the 1024-aligned base): the A and weight
+// tiles first; once the MMA has consumed them the same bytes hold the gathered expanded-cache
+// rows (anchor terms, then partner terms), which the epilogue overwrites with its results.
+struct GatherPlan { uint32_t partner_rows, total; };
+
+__host__ __device__ inline GatherPlan gather_plan(int rdim, int rows_per_tile) {
+    GatherPlan p;
+    const uint32_t tile_bytes = static_cast<uint32_t>(rdim / kBK) * kBM * 128u;
+    p.partner_rows = static_cast<uint32_t>(rows_per_tile) * kRowStride;
+    const uint32_t staged = p.partner_rows + kBM * kRowStride;
+    p.total = 2 * tile_bytes > staged ? 2 * tile_bytes : staged;
+    return p;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
+    const __grid_constant__ CUtensorMap map_wm, const HiddenTcArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ uint32_t tmem_base_slot;
@@ -90,55 +147,36 @@ __global__ void __launch_bounds__(kTcThreads) relation_hidden_tc_kernel(
     __shared__ int idx_s[2 * kBM];      // [rows_per_tile][K + 1]
     __shared__ int seq_s[kBM];
 
+    RLM_TC_PROBE(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int R = a.rdim, H = a.hdim, K = a.k_out, RPT = a.rows_per_tile;
     const int kblocks = R / kBK, chunks = R / 8;
     const int h0 = blockIdx.x * kTcBN, row0 = blockIdx.y * RPT;
     const int tile_pairs = RPT * K;
 
-    int t = -1;
-    if (kUpdate) {
-        t = static_cast<int>(*a.position);
-        if (t < 0 || t >= a.max_t) {
-            if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
-            return;
-        }
-    }
-
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const GatherPlan plan = gather_plan(R, RPT);
     const uint32_t tile_bytes = static_cast<uint32_t>(kblocks) * kBM * 128u;   // one 128 x R tile
     unsigned char* a_tile = base;
     unsigned char* wm_tile = a_tile + tile_bytes;
-    unsigned char* wa_tile = wm_tile + tile_bytes;                              // kUpdate only
-    unsigned char* wp_tile = wa_tile + (kUpdate ? tile_bytes : 0u);
-    unsigned char* cur_tile = wp_tile + (kUpdate ? tile_bytes : 0u);            // [kblocks][n_fresh][128 B]
-    const uint32_t cur_kblock = static_cast<uint32_t>(a.n_fresh) * 128u;
-    float* fresh_s = reinterpret_cast<float*>(cur_tile + (kUpdate ? kblocks * cur_kblock : 0u));  // [2][RPT][128]
+    unsigned char* g_anchor = base;                        // after the MMA: [RPT][kRowStride] expanded[a, h0 ..]
+    unsigned char* g_partner = base + plan.partner_rows;   // [128][kRowStride] expanded[p, H + h0 ..], then results
 
     const uint32_t bar_w = smem_u32(&bars[0]), bar_acc = smem_u32(&bars[1]);
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wm) : "memory");
-        if (kUpdate) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wa) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wp) : "memory");
-        }
         mbar_init(bar_w, 1);
         mbar_init(bar_acc, 1);
         fence_barrier_init();
         failed = 0;
-        mbar_expect_tx(bar_w, (kUpdate ? 3u : 1u) * tile_bytes);
-        for (int kb = 0; kb < kblocks; ++kb) {
+        mbar_expect_tx(bar_w, tile_bytes);
+        for (int kb = 0; kb < kblocks; ++kb)
             tma_load_2d(smem_u32(wm_tile) + kb * kBM * 128u, &map_wm, kb * kBK, h0, bar_w);
-            if (kUpdate) {
-                tma_load_2d(smem_u32(wa_tile) + kb * kBM * 128u, &map_wa, kb * kBK, h0, bar_w);
-                tma_load_2d(smem_u32(wp_tile) + kb * kBM * 128u, &map_wp, kb * kBK, h0, bar_w);
-            }
-        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_slot)), "r"(a.tmem_cols) : "memory");
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTcBN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
 
@@ -158,63 +196,58 @@ __global__ void __launch_bounds__(kTcThreads) relation_hidden_tc_kernel(
             seq_s[rb] = b;
         }
     }
-    __syncthreads();
+    __syncthreads();      // also publishes the barrier initialisation
+    RLM_TC_PROBE(1);
 
-    // A tile: products of the gathered operand rows, four 16-byte chunks per thread in flight
+    // A tile: the partner operand rows go straight to their swizzled places in the A tile as
+    // 16-byte asynchronous copies while the anchor chunks they are multiplied with wait in
+    // registers; once this thread's copies have landed it multiplies them in place (fp32).
+    // A thread keeps one chunk column and walks the pair rows, eight rows per round.
     const size_t op_row = static_cast<size_t>(R) * 2;
-    const int items = kBM * chunks;
-    for (int i0 = tid; i0 < items; i0 += 4 * kTcThreads) {
-        uint4 ra[4], rp[4];
-        bool live[4];
+    {
+        constexpr int kRound = 8;
+        const int rows_per_pass = kTcThreads / chunks;
+        const int bc = tid % chunks, r_first = tid / chunks;
+        for (int r0 = r_first < rows_per_pass ? r_first : kBM; r0 < kBM; r0 += kRound * rows_per_pass) {
+            uint4 anchor_chunk[kRound];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * kTcThreads;
-            const int r = i / chunks, c = i - r * chunks;
-            const int rb = r / K, k = r - rb * K;
-            live[u] = i < items && r < tile_pairs && seq_s[rb < RPT ? rb : 0] >= 0;
-            if (live[u]) {
-                const char* operand = static_cast<const char*>(a.operand_cache) +
-                                      static_cast<size_t>(seq_s[rb]) * a.max_t * op_row;
-                ra[u] = *reinterpret_cast<const uint4*>(operand + idx_s[rb * (K + 1)] * op_row + 16 * c);
-                rp[u] = *reinterpret_cast<const uint4*>(operand + idx_s[rb * (K + 1) + k + 1] * op_row + 16 * c);
+            for (int u = 0; u < kRound; ++u) {
+                const int r = r0 + u * rows_per_pass;
+                anchor_chunk[u] = make_uint4(0, 0, 0, 0);
+                if (r >= kBM) continue;
+                const int rb = (r * a.inv_k16) >> 16, k = r - rb * K;
+                const uint32_t dst = smem_u32(a_tile) + swizzled(r, bc, kBM * 128u);
+                if (r < tile_pairs && seq_s[rb < RPT ? rb : 0] >= 0) {
+                    const char* operand = static_cast<const char*>(a.operand_cache) +
+                                          static_cast<size_t>(seq_s[rb]) * a.max_t * op_row + 16 * bc;
+                    cp_async16(dst, operand + idx_s[rb * (K + 1) + k + 1] * op_row);
+                    anchor_chunk[u] = *reinterpret_cast<const uint4*>(operand + idx_s[rb * (K + 1)] * op_row);
+                } else {
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+                }
             }
-        }
+            cp_async_commit();
+            cp_async_wait_all();
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * kTcThreads;
-            if (i >= items) continue;
-            const int r = i / chunks, c = i - r * chunks;
-            uint4 packed = make_uint4(0, 0, 0, 0);
-            if (live[u]) {
+            for (int u = 0; u < kRound; ++u) {
+                const int r = r0 + u * rows_per_pass;
+                if (r >= kBM) continue;
+                uint4* cell = reinterpret_cast<uint4*>(a_tile + swizzled(r, bc, kBM * 128u));
                 float fa[8], fp[8];
-                unpack8(ra[u], a.dtype, fa);
-                unpack8(rp[u], a.dtype, fp);
-                packed.x = pack2(fp[0] * fa[0], fp[1] * fa[1], a.dtype);
-                packed.y = pack2(fp[2] * fa[2], fp[3] * fa[3], a.dtype);
-                packed.z = pack2(fp[4] * fa[4], fp[5] * fa[5], a.dtype);
-                packed.w = pack2(fp[6] * fa[6], fp[7] * fa[7], a.dtype);
+                unpack8(anchor_chunk[u], a.dtype, fa);
+                unpack8(*cell, a.dtype, fp);
+                *cell = make_uint4(pack2(fp[0] * fa[0], fp[1] * fa[1], a.dtype), pack2(fp[2] * fa[2], fp[3] * fa[3], a.dtype),
+                                   pack2(fp[4] * fa[4], fp[5] * fa[5], a.dtype), pack2(fp[6] * fa[6], fp[7] * fa[7], a.dtype));
             }
-            *reinterpret_cast<uint4*>(a_tile + swizzled(r, c, kBM * 128u)) = packed;
         }
     }
-    if (kUpdate) {
-        // current operand rows of the tile's sequences (zero rows up to n_fresh)
-        for (int i = tid; i < a.n_fresh * chunks; i += kTcThreads) {
-            const int j = i / chunks, c = i - j * chunks;
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (j < RPT && seq_s[j] >= 0)
-                raw = *reinterpret_cast<const uint4*>(
-                    static_cast<const char*>(a.operand_cache) +
-                    (static_cast<size_t>(seq_s[j]) * a.max_t + t) * op_row + 16 * c);
-            *reinterpret_cast<uint4*>(cur_tile + swizzled(j, c, cur_kblock)) = raw;
-        }
-    }
-    fence_proxy_async();     // generic-proxy writes of the tiles -> visible to the tensor core
+    RLM_TC_PROBE(2);
+    fence_proxy_async();     // generic-proxy writes of the tile -> visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    RLM_TC_PROBE(3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tmem_fresh = tmem_base + kTcBN;      // anchor half, then partner half n_fresh further
 
     if (tid == 0) {
         bool ok = mbar_wait(bar_w, 0);
@@ -225,113 +258,223 @@ __global__ void __launch_bounds__(kTcThreads) relation_hidden_tc_kernel(
                 const uint64_t db = smem_desc_sw128(smem_u32(wm_tile) + kb * kBM * 128u);
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk)
-                    umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, a.idesc_main, (kb > 0 || kk > 0) ? 1u : 0u);
-            }
-            if (kUpdate) {
-                for (int half = 0; half < 2; ++half)
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        const uint64_t dw = smem_desc_sw128(smem_u32(half ? wp_tile : wa_tile) + kb * kBM * 128u);
-                        const uint64_t dc = smem_desc_sw128(smem_u32(cur_tile) + kb * cur_kblock);
-#pragma unroll
-                        for (int kk = 0; kk < kBK / 16; ++kk)
-                            umma_f16(tmem_fresh + half * a.n_fresh, dw + 2 * kk, dc + 2 * kk, a.idesc_fresh,
-                                     (kb > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, a.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
         } else {
             failed = 1;
         }
-        umma_commit(bar_acc);     // accumulators complete (or abandoned)
+        umma_commit(bar_acc);     // accumulator complete (or abandoned)
     }
     __syncwarp();
-
-    // This thread's epilogue share: pair row `pr`, hidden columns [h0 + 64 ch, h0 + 64 ch + 64).
-    // The expanded-cache terms are requested now and consumed after the MMA wait.
-    const int pr = 32 * (warp & 3) + lane, ch = warp >> 2;
-    const int rb = pr / K, k = pr - rb * K;
-    const bool pair_live = pr < tile_pairs && row0 + rb < a.n_rows && seq_s[rb < RPT ? rb : 0] >= 0;
-    bool sub_a = false, sub_p = false;
-    uint4 ea[8], ep[8];
-    if (pair_live) {
-        const int ai = idx_s[rb * (K + 1)], pi = idx_s[rb * (K + 1) + k + 1];
-        sub_a = kUpdate && ai == t;
-        sub_p = kUpdate && pi == t;
-        const char* ex = static_cast<const char*>(a.expanded_cache) +
-                         static_cast<size_t>(seq_s[rb]) * a.max_t * 2 * H * 2;
-        const uint4* pa = reinterpret_cast<const uint4*>(ex + (static_cast<size_t>(ai) * 2 * H + h0 + 64 * ch) * 2);
-        const uint4* pp = reinterpret_cast<const uint4*>(ex + (static_cast<size_t>(pi) * 2 * H + H + h0 + 64 * ch) * 2);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            ea[i] = sub_a ? make_uint4(0, 0, 0, 0) : pa[i];
-            ep[i] = sub_p ? make_uint4(0, 0, 0, 0) : pp[i];
-        }
-    }
+    RLM_TC_PROBE(4);
 
     bool ready = mbar_wait(bar_acc, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+    RLM_TC_PROBE(5);
+    const bool staged = a.out_dtype != RLM_F32;
     if (!__syncthreads_or(!ready)) {
-        const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-        if (kUpdate) {
-            // fresh half rows: this thread owns hidden column h0 + hc of half `ch`
-            const int hc = 32 * (warp & 3) + lane;
-            const float bias = ch == 0 ? load_scalar(a.first_bias, h0 + hc, a.dtype) : 0.0f;
-            for (int c = 0; c < a.n_fresh; c += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_fresh + ch * a.n_fresh + lane_base + c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int s = c + j;
-                    if (s >= RPT || seq_s[s] < 0) continue;
-                    const float val = __uint_as_float(v[j]) + bias;
-                    fresh_s[(ch * RPT + s) * kTcBN + hc] = val;
-                    store_scalar(a.expanded_cache,
-                                 (static_cast<int64_t>(seq_s[s]) * a.max_t + t) * 2 * H + ch * H + h0 + hc,
-                                 a.dtype, val);
-                }
+    // The operand tiles are consumed: all threads request the expanded-cache segments of the
+        // epilogue into the same bytes as 16-byte asynchronous copies (a warp covers two 256-byte
+        // tile rows per instruction): row j < RPT of the staging area is the anchor term of
+        // sequence j, row RPT + r the partner term of pair r.
+            {
+            const int c = tid & 15, n_rows_staged = RPT + tile_pairs;
+            for (int g = tid >> 4; g < n_rows_staged; g += kTcThreads / 16) {
+                const int r = g - RPT;
+                const int rb = g < RPT ? g : (r * a.inv_k16) >> 16;
+                if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
+                const int at = g < RPT ? idx_s[rb * (K + 1)] : idx_s[rb * (K + 1) + (r - rb * K) + 1];
+                const char* src = static_cast<const char*>(a.expanded_cache) +
+                                  ((static_cast<size_t>(seq_s[rb]) * a.max_t + at) * 2 * H + (g < RPT ? 0 : H) + h0) * 2;
+                // the partner rows follow the anchor rows in shared memory
+                cp_async16(smem_u32(g_anchor) + g * kRowStride + 16 * c, src + 16 * c);
             }
-            __syncthreads();
+            cp_async_commit();
         }
+        cp_async_wait_all();
+        __syncthreads();
+        RLM_TC_PROBE(6);
+        // This thread's share: pair row `pr`, hidden columns [h0 + 64 ch, h0 + 64 ch + 64).
+        const int pr = 32 * (warp & 3) + lane, ch = warp >> 2;
+        const int prb = (pr * a.inv_k16) >> 16;
+        const bool pair_live = pr < tile_pairs && row0 + prb < a.n_rows && seq_s[prb < RPT ? prb : 0] >= 0;
+        const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+        const unsigned char* ga = g_anchor + (prb < RPT ? prb : 0) * kRowStride + 128 * ch;
+        const unsigned char* gp = g_partner + pr * kRowStride + 128 * ch;
+        unsigned char* so = g_partner + pr * kRowStride + 128 * ch;      // results replace the partner term
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             uint32_t v[16];
             tmem_ld16(tmem_base + lane_base + 64 * ch + 16 * q, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (!pair_live) continue;
-            float fa[16], fp[16];
-            {
-                float lo[8], hi[8];
-                unpack8(ea[2 * q], a.dtype, lo);
-                unpack8(ea[2 * q + 1], a.dtype, hi);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { fa[i] = lo[i]; fa[8 + i] = hi[i]; }
-                unpack8(ep[2 * q], a.dtype, lo);
-                unpack8(ep[2 * q + 1], a.dtype, hi);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { fp[i] = lo[i]; fp[8 + i] = hi[i]; }
-            }
-            if (kUpdate && (sub_a || sub_p)) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (sub_a) fa[i] = fresh_s[(0 * RPT + rb) * kTcBN + 64 * ch + 16 * q + i];
-                    if (sub_p) fp[i] = fresh_s[(1 * RPT + rb) * kTcBN + 64 * ch + 16 * q + i];
-                }
-            }
             float y[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = gelu_erf_tc(__uint_as_float(v[i]) + (fa[i] + fp[i]));
-            const size_t at = (static_cast<size_t>(row0) * K + pr) * H + h0 + 64 * ch + 16 * q;
-            if (a.out_dtype == RLM_F32) {
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                float fa[8], fp[8];
+                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), a.dtype, fa);
+                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), a.dtype, fp);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    y[8 * hlf + i] = gelu_tc(__uint_as_float(v[8 * hlf + i]) + (fa[i] + fp[i]));
+            }
+            if (!staged) {
+                const size_t at = (static_cast<size_t>(row0) * K + pr) * H + h0 + 64 * ch + 16 * q;
                 float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) o[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
             } else {
-                uint4* o = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + at);
+                uint4* o = reinterpret_cast<uint4*>(so + 32 * q);
                 o[0] = make_uint4(pack2(y[0], y[1], a.out_dtype), pack2(y[2], y[3], a.out_dtype),
                                   pack2(y[4], y[5], a.out_dtype), pack2(y[6], y[7], a.out_dtype));
                 o[1] = make_uint4(pack2(y[8], y[9], a.out_dtype), pack2(y[10], y[11], a.out_dtype),
                                   pack2(y[12], y[13], a.out_dtype), pack2(y[14], y[15], a.out_dtype));
+            }
+        }
+        if (staged) {
+            // 16-bit outputs leave row by row: a warp stores two 256-byte pair rows per instruction
+            __syncthreads();
+            const int c = tid & 15;
+            for (int r = tid >> 4; r < tile_pairs; r += kTcThreads / 16) {
+                const int rb = (r * a.inv_k16) >> 16;
+                if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
+                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) +
+                                          (static_cast<size_t>(row0) * K + r) * H + h0 + 8 * c) =
+                    *reinterpret_cast<const uint4*>(g_partner + r * kRowStride + 16 * c);
+            }
+        }
+    } else if (tid == 0 && a.status) {
+        atomicOr(a.status, RLM_DEV_TIMEOUT);
+    }
+    RLM_TC_PROBE(7);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"(kTcBN) : "memory");
+    RLM_TC_PROBE(8);
+}
+
+// ------------------------------------------------------------------ expanded row of position t
+
+// grid (H / 128, 2 halves, sequence groups of up to 64).  `n_cols` = sequences of the group
+// rounded up to 16 = MMA N = TMEM columns in use; `tmem_cols` the power of two allocated.
+__global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
+    const __grid_constant__ CUtensorMap map_wa, const __grid_constant__ CUtensorMap map_wp,
+    const RowUpdateArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int R = a.rdim, H = a.hdim;
+    const int kblocks = R / kBK, chunks = R / 8;
+    const int h0 = blockIdx.x * kTcBN, half = blockIdx.y, s0 = blockIdx.z * kUpdMaxSeq;
+    const int n_here = min(a.n_seq - s0, kUpdMaxSeq);
+    const int n_cols = (n_here + 15) & ~15;
+    int tmem_cols = 32;
+    while (tmem_cols < n_cols) tmem_cols *= 2;
+    const uint32_t fmt = a.dtype == RLM_BF16 ? 1u : 0u;
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(n_cols >> 3) << 17) |
+                           (static_cast<uint32_t>(kBM >> 4) << 24);
+
+    const int t = static_cast<int>(*a.position);
+    if (t < 0 || t >= a.max_t) {
+        if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
+        return;
+    }
+
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t w_bytes = static_cast<uint32_t>(kblocks) * kBM * 128u;
+    unsigned char* w_tile = base;
+    unsigned char* cur_tile = base + w_bytes;                 // [kblocks][n_cols][128 B]
+    const uint32_t cur_kblock = static_cast<uint32_t>(n_cols) * 128u;
+
+    const uint32_t bar_w = smem_u32(&bars[0]), bar_acc = smem_u32(&bars[1]);
+    if (tid == 0) {
+        const CUtensorMap* map = half ? &map_wp : &map_wa;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+        mbar_init(bar_w, 1);
+        mbar_init(bar_acc, 1);
+        fence_barrier_init();
+        failed = 0;
+        mbar_expect_tx(bar_w, w_bytes);
+        for (int kb = 0; kb < kblocks; ++kb)
+            tma_load_2d(smem_u32(w_tile) + kb * kBM * 128u, map, kb * kBK, h0, bar_w);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // current operand rows of the group's sequences (zero rows up to n_cols), copied
+    // asynchronously straight to their swizzled places
+    const size_t op_row = static_cast<size_t>(R) * 2;
+    const int items = n_cols * chunks;
+    for (int i = tid; i < items; i += kUpdThreads) {
+        const int j = i / chunks, c = i - j * chunks;
+        const uint32_t dst = smem_u32(cur_tile) + swizzled(j, c, cur_kblock);
+        if (j < n_here)
+            cp_async16(dst, static_cast<const char*>(a.operand_cache) +
+                                (static_cast<size_t>(s0 + j) * a.max_t + t) * op_row + 16 * c);
+        else
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+    }
+    cp_async_commit();
+    cp_async_wait_all();
+    fence_proxy_async();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (tid == 0) {
+        bool ok = mbar_wait(bar_w, 0);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const uint64_t dw = smem_desc_sw128(smem_u32(w_tile) + kb * kBM * 128u);
+                const uint64_t dc = smem_desc_sw128(smem_u32(cur_tile) + kb * cur_kblock);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; ++kk)
+                    umma_f16(tmem_base, dw + 2 * kk, dc + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+        } else {
+            failed = 1;
+        }
+        umma_commit(bar_acc);
+    }
+    __syncwarp();
+
+    bool ready = mbar_wait(bar_acc, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+    if (!__syncthreads_or(!ready)) {
+        // this thread owns hidden column h0 + tid of the half: one 2-byte store per sequence,
+        // a warp's 32 stores of one sequence are 64 contiguous bytes of its cache row
+        const float bias = half == 0 ? load_scalar(a.first_bias, h0 + tid, a.dtype) : 0.0f;
+        const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
+        uint16_t* cache = static_cast<uint16_t*>(a.expanded_cache);
+        for (int c = 0; c < n_cols; c += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + lane_base + c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (c + j >= n_here) continue;
+                const float val = __uint_as_float(v[j]) + bias;
+                uint16_t bits;
+                if (a.dtype == RLM_BF16) {
+                    __nv_bfloat16 hv = __float2bfloat16_rn(val);
+                    bits = *reinterpret_cast<uint16_t*>(&hv);
+                } else {
+                    __half hv = __float2half_rn(val);
+                    bits = *reinterpret_cast<uint16_t*>(&hv);
+                }
+                cache[(static_cast<size_t>(s0 + c + j) * a.max_t + t) * 2 * H + half * H + h0 + tid] = bits;
             }
         }
     } else if (tid == 0 && a.status) {
@@ -341,25 +484,28 @@ __global__ void __launch_bounds__(kTcThreads) relation_hidden_tc_kernel(
     __syncthreads();
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+                     ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+}
+
+size_t gather_smem_bytes(int rdim, int k_out) { return 1024 + gather_plan(rdim, kBM / k_out).total; }
+
+size_t update_smem_bytes(int rdim, int n_seq) {
+    const int n_cols = ((n_seq < kUpdMaxSeq ? n_seq : kUpdMaxSeq) + 15) & ~15;
+    return 1024 + static_cast<size_t>(rdim / kBK) * (kBM + n_cols) * 128;
 }
 
 }  // namespace
 
 // Whether the tensor-core form applies; the callers fall back to the CUDA-core kernel otherwise.
 bool hidden_tc_applicable(bool update, int n_rows, int rdim, int hdim, int k_out, int cache_dtype,
-                          int weight_dtype, const void* expanded_cache, const void* out, int out_dtype) {
+                          int weight_dtype, const void* expanded_cache, const void* out) {
     if (cache_dtype != weight_dtype || (cache_dtype != RLM_BF16 && cache_dtype != RLM_F16)) return false;
     if (rdim % kBK != 0 || hdim % kTcBN != 0 || k_out < 1 || k_out > 16) return false;
     if (static_cast<long long>(n_rows) * k_out < 256) return false;    // small launches: latency-bound form
-    if (update && kBM / k_out > kTcMaxFresh) return false;
     if (!aligned16(expanded_cache) || !aligned16(out)) return false;
-    (void)out_dtype;
-    const int kblocks = rdim / kBK;
-    const int rpt = kBM / k_out, n_fresh = (rpt + 15) & ~15;
-    size_t bytes = 1024 + static_cast<size_t>(update ? 4 : 2) * kblocks * kBM * 128;
-    if (update) bytes += static_cast<size_t>(kblocks) * n_fresh * 128 + static_cast<size_t>(2) * rpt * kTcBN * 4;
-    return bytes <= static_cast<size_t>(kSmemDynamicLimit);
+    if (gather_smem_bytes(rdim, k_out) > static_cast<size_t>(kSmemDynamicLimit)) return false;
+    if (update && update_smem_bytes(rdim, n_rows) > static_cast<size_t>(kSmemDynamicLimit)) return false;
+    return true;
 }
 
 int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cache,
@@ -368,49 +514,57 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
                      const void* first_bias, const int64_t* position, const int32_t* row_batch, void* out,
                      int n_rows, int n_seq, int max_t, int rdim, int hdim, int k_out, int dtype,
                      int out_dtype, int32_t* status, void* stream) {
+    const uint32_t fmt = dtype == RLM_BF16 ? 1u : 0u;
+    if (update) {
+        RowUpdateArgs u{};
+        u.expanded_cache = expanded_cache; u.operand_cache = operand_cache; u.first_bias = first_bias;
+        u.position = position; u.status = status; u.n_seq = n_seq; u.max_t = max_t; u.rdim = rdim;
+        u.hdim = hdim; u.dtype = dtype;
+        CUtensorMap ma, mp;
+        if (!make_map(&ma, anchor_weight, hdim, rdim, rdim, kTcBN, dtype) ||
+            !make_map(&mp, partner_weight, hdim, rdim, rdim, kTcBN, dtype)) {
+            set_error("relation_hidden: cuTensorMapEncodeTiled failed");
+            return RLM_ERR_LAUNCH;
+        }
+        auto kernel = expanded_row_update_kernel;
+        int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+        if (rc != RLM_OK) return rc;
+        dim3 grid(hdim / kTcBN, 2, (n_seq + kUpdMaxSeq - 1) / kUpdMaxSeq);
+        kernel<<<grid, kUpdThreads, update_smem_bytes(rdim, n_seq), static_cast<cudaStream_t>(stream)>>>(ma, mp, u);
+        count_launch();
+        rc = check_launch("expanded_row_update_kernel");
+        if (rc != RLM_OK) return rc;
+    }
     HiddenTcArgs a{};
     a.expanded_cache = expanded_cache; a.operand_cache = operand_cache; a.anchor_index = anchor_index;
-    a.partner_index = partner_index; a.first_bias = first_bias; a.position = position;
-    a.row_batch = row_batch; a.out = out; a.status = status;
+    a.partner_index = partner_index; a.row_batch = row_batch; a.out = out; a.status = status;
     a.n_rows = n_rows; a.n_seq = n_seq; a.max_t = max_t; a.rdim = rdim; a.hdim = hdim; a.k_out = k_out;
     a.dtype = dtype; a.out_dtype = out_dtype;
     a.rows_per_tile = kBM / k_out;
-    a.n_fresh = update ? (a.rows_per_tile + 15) & ~15 : 0;
-    int cols = kTcBN + 2 * a.n_fresh;
-    a.tmem_cols = 32;
-    while (a.tmem_cols < cols) a.tmem_cols *= 2;
-    const uint32_t fmt = dtype == RLM_BF16 ? 1u : 0u;
-    a.idesc_main = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
-                   (static_cast<uint32_t>(kBM >> 4) << 24);
-    a.idesc_fresh = (1u << 4) | (fmt << 7) | (fmt << 10) |
-                    (static_cast<uint32_t>((update ? a.n_fresh : 16) >> 3) << 17) |
-                    (static_cast<uint32_t>(kBM >> 4) << 24);
-    CUtensorMap mm, ma, mp;
-    if (!make_map(&mm, product_weight, hdim, rdim, rdim, kTcBN, dtype) ||
-        !make_map(&ma, update ? anchor_weight : product_weight, hdim, rdim, rdim, kTcBN, dtype) ||
-        !make_map(&mp, update ? partner_weight : product_weight, hdim, rdim, rdim, kTcBN, dtype)) {
+    a.inv_k16 = (65536 + k_out - 1) / k_out;
+    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
+              (static_cast<uint32_t>(kBM >> 4) << 24);
+    CUtensorMap mm;
+    if (!make_map(&mm, product_weight, hdim, rdim, rdim, kTcBN, dtype)) {
         set_error("relation_hidden: cuTensorMapEncodeTiled failed");
         return RLM_ERR_LAUNCH;
     }
-    const int kblocks = rdim / kBK;
-    size_t bytes = 1024 + static_cast<size_t>(update ? 4 : 2) * kblocks * kBM * 128;
-    if (update)
-        bytes += static_cast<size_t>(kblocks) * a.n_fresh * 128 + static_cast<size_t>(2) * a.rows_per_tile * kTcBN * 4;
+    auto kernel = relation_hidden_tc_kernel;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
     dim3 grid(hdim / kTcBN, (n_rows + a.rows_per_tile - 1) / a.rows_per_tile);
-    int rc;
-    if (update) {
-        auto kernel = relation_hidden_tc_kernel<true>;
-        rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
-        if (rc != RLM_OK) return rc;
-        kernel<<<grid, kTcThreads, bytes, static_cast<cudaStream_t>(stream)>>>(mm, ma, mp, a);
-    } else {
-        auto kernel = relation_hidden_tc_kernel<false>;
-        rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
-        if (rc != RLM_OK) return rc;
-        kernel<<<grid, kTcThreads, bytes, static_cast<cudaStream_t>(stream)>>>(mm, ma, mp, a);
-    }
+    kernel<<<grid, kTcThreads, gather_smem_bytes(rdim, k_out), static_cast<cudaStream_t>(stream)>>>(mm, a);
     count_launch();
     return check_launch("relation_hidden_tc_kernel");
 }
 
 }  // namespace rlm
+
+#ifdef RLM_TRACE
+extern "C" int rlm_debug_span_tc(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_span_tc, sizeof(unsigned long long) * 1024 * 3));
+}
+extern "C" int rlm_debug_trace_tc(long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_tc, sizeof(long long) * 64 * 32));
+}
+#endif

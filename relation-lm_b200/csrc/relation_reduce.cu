@@ -10,7 +10,7 @@
 namespace rlm {
 // tensor-core form for launches with many relation rows (relation_hidden_tc.cu)
 bool hidden_tc_applicable(bool update, int n_rows, int rdim, int hdim, int k_out, int cache_dtype,
-                          int weight_dtype, const void* expanded_cache, const void* out, int out_dtype);
+                          int weight_dtype, const void* expanded_cache, const void* out);
 int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cache,
                      const int32_t* anchor_index, const int32_t* partner_index,
                      const void* anchor_weight, const void* partner_weight, const void* product_weight,
@@ -378,7 +378,7 @@ int launch_hidden(HiddenArgs& a, bool update, void* stream) {
         return RLM_ERR_ALIGN;
     }
     if (hidden_tc_applicable(update, a.n_rows, a.rdim, a.hdim, a.k_out, a.cache_dtype, a.weight_dtype,
-                             a.expanded_cache, a.out, a.out_dtype))
+                             a.expanded_cache, a.out))
         return launch_hidden_tc(update, a.expanded_cache, a.operand_cache, a.anchor_index, a.partner_index,
                                 a.anchor_weight, a.partner_weight, a.product_weight, a.first_bias,
                                 a.position, a.row_batch, a.out, a.n_rows, a.n_seq, a.max_t, a.rdim, a.hdim,
