@@ -501,6 +501,107 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
     }
 }
 
+// Vector form for feature widths that are a multiple of 8 (16-byte aligned rows): a lane owns
+// the 8-column chunks lane, lane + 32, ... (kVecChunks of them, at most four: dim <= 1024), so a partner row is
+// fetched with a few 16-byte loads per lane instead of one scalar load per column.
+template <int kVecChunks>
+__global__ void __launch_bounds__(kNormThreads, 2) relation_norm_reduce_vec_kernel(const NormArgs a) {
+    extern __shared__ __align__(16) float partial[];   // [warps][dim]
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = a.k_out, D = a.dim;
+    const int chunks = D / 8;
+    const size_t raw_elem = a.raw_dtype == RLM_F32 ? 4 : 2;
+
+    // loads that depend on nothing first: position, scores, this warp's first partner row, affine
+    const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
+    float s0 = lane < K ? a.scores[static_cast<size_t>(row) * K + lane] : kNegInf;
+    float s1 = lane + 32 < K ? a.scores[static_cast<size_t>(row) * K + lane + 32] : kNegInf;
+    float x[kVecChunks][8];
+    const char* raw_row = static_cast<const char*>(a.raw) + static_cast<size_t>(row) * K * D * raw_elem;
+    if (warp < K) {
+#pragma unroll
+        for (int i = 0; i < kVecChunks; ++i)
+            if (lane + 32 * i < chunks) load8(raw_row + static_cast<size_t>(warp) * D * raw_elem, 8 * (lane + 32 * i), a.raw_dtype, x[i]);
+    }
+
+    int k_limit = 32 - __clz(max(t, 0) + 1);   // ceil(log2(t + 2))
+    k_limit = min(max(k_limit, 1), K);
+    bool a0 = lane < K && lane < k_limit && s0 > -1.0e30f;
+    bool a1 = lane + 32 < K && lane + 32 < k_limit && s1 > -1.0e30f;
+    float f0 = a0 ? s0 : -1.0e4f, f1 = a1 ? s1 : -1.0e4f;
+    float mx = fmaxf(f0, f1);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    float e0 = a0 ? expf(f0 - mx) : 0.0f, e1 = a1 ? expf(f1 - mx) : 0.0f;
+    float den = fmaxf(warp_sum(e0 + e1), 1.0e-9f);
+    float w0 = e0 / den, w1 = e1 / den;
+
+    float y[kVecChunks][8];
+#pragma unroll
+    for (int i = 0; i < kVecChunks; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[i][e] = 0.0f;
+    for (int k = warp; k < K; k += kNormWarps) {
+        float wk = __shfl_sync(0xffffffffu, k < 32 ? w0 : w1, k & 31);
+        if (k != warp && wk != 0.0f) {
+#pragma unroll
+            for (int i = 0; i < kVecChunks; ++i)
+                if (lane + 32 * i < chunks) load8(raw_row + static_cast<size_t>(k) * D * raw_elem, 8 * (lane + 32 * i), a.raw_dtype, x[i]);
+        }
+        if (wk == 0.0f) continue;   // inactive slot contributes nothing
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kVecChunks; ++i)
+            if (lane + 32 * i < chunks)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum += x[i][e];
+        const float mean = warp_sum(sum) / static_cast<float>(D);
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kVecChunks; ++i)
+            if (lane + 32 * i < chunks)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { x[i][e] -= mean; sq = fmaf(x[i][e], x[i][e], sq); }
+        const float inv = rsqrtf(warp_sum(sq) / static_cast<float>(D) + a.eps);
+#pragma unroll
+        for (int i = 0; i < kVecChunks; ++i)
+            if (lane + 32 * i < chunks) {
+                float gm[8], bt[8];       // cache-resident affine parameters, read where they are used
+                load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm);
+                load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[i][e] = fmaf(wk, fmaf(x[i][e] * inv, gm[e], bt[e]), y[i][e]);
+            }
+    }
+#pragma unroll
+    for (int i = 0; i < kVecChunks; ++i)
+        if (lane + 32 * i < chunks) {
+            float4* dst = reinterpret_cast<float4*>(partial + warp * D + 8 * (lane + 32 * i));
+            dst[0] = make_float4(y[i][0], y[i][1], y[i][2], y[i][3]);
+            dst[1] = make_float4(y[i][4], y[i][5], y[i][6], y[i][7]);
+        }
+    __syncthreads();
+    const float mix = a.residual ? *a.mix : 0.0f;
+    for (int c = 4 * tid; c < D; c += 4 * kNormThreads) {
+        float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const int used = K < kNormWarps ? K : kNormWarps;      // warps beyond K hold zeros they never wrote
+#pragma unroll
+        for (int w = 0; w < kNormWarps; ++w) {
+            if (w >= used) break;
+            const float4 v = *reinterpret_cast<const float4*>(partial + w * D + c);
+            total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+        }
+        const size_t at = static_cast<size_t>(row) * D + c;
+        if (a.out) *reinterpret_cast<float4*>(a.out + at) = total;
+        if (a.residual) {
+            float4 r = *reinterpret_cast<float4*>(a.residual + at);
+            r.x = fmaf(mix, total.x, r.x); r.y = fmaf(mix, total.y, r.y);
+            r.z = fmaf(mix, total.z, r.z); r.w = fmaf(mix, total.w, r.w);
+            *reinterpret_cast<float4*>(a.residual + at) = r;
+        }
+    }
+}
+
 }  // namespace
 }  // namespace rlm
 
@@ -562,7 +663,16 @@ extern "C" int rlm_relation_norm_reduce(
     a.eps = norm_eps; a.n_rows = n_rows; a.k_out = k_out; a.dim = dim;
     a.raw_dtype = raw_dtype; a.param_dtype = param_dtype;
     int smem_bytes = kNormWarps * dim * 4;
-    relation_norm_reduce_kernel<<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    const bool vec = dim % 8 == 0 && aligned16(raw) && aligned16(norm_weight) && aligned16(norm_bias) &&
+                     (!out || aligned16(out)) && (!residual || aligned16(residual));
+    if (vec && dim <= 512)
+        relation_norm_reduce_vec_kernel<2><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    else if (vec && dim <= 768)
+        relation_norm_reduce_vec_kernel<3><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    else if (vec)
+        relation_norm_reduce_vec_kernel<4><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    else
+        relation_norm_reduce_kernel<<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
     count_launch();
     return check_launch("relation_norm_reduce_kernel");
 }
