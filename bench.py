@@ -490,6 +490,13 @@ def run_kernel_case(args) -> None:
                 hidden_out = torch.empty(B, K, H, device=dev, dtype=torch.bfloat16)
             ex, op = S[i % 2]
             fn = lambda: relation_hidden_cache_update_out(hidden_out, ex, op, ai, pi, wa, wp, wm, b1, pos)  # noqa: E731
+        elif args.kernel_case == "projection":
+            if i == 0:
+                from relation_lm.kernels.packed_projection import packed_projection
+                S = [rn(B, d) for _ in range(sets)]
+                w_packed = rn(12 * (384 + R), d) * 0.02          # the 12-layer packed projection matrix
+            x = S[i % sets]
+            fn = lambda: packed_projection(x, w_packed)  # noqa: E731
         elif args.kernel_case == "norm":
             if i == 0:
                 S = [rn(B, K, d) for _ in range(sets)]
@@ -522,7 +529,8 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
-    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "norm", "router"), default=None,
+    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "router"),
+                        default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")
     parser.add_argument("--rows", type=int, default=256)

@@ -138,6 +138,9 @@ __host__ __device__ inline GatherPlan gather_plan(int rdim, int rows_per_tile) {
     return p;
 }
 
+// kDt: dtype of the caches and weights, kOut: dtype of the output (compile-time, so that the
+// conversions carry no branches).
+template <int kDt, int kOut>
 __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
     const __grid_constant__ CUtensorMap map_wm, const HiddenTcArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -181,6 +184,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
     }
 
     // gathered indices of the tile's sequences
+#pragma unroll 1
     for (int i = tid; i < RPT * (K + 1); i += kTcThreads) {
         const int rb = i / (K + 1), j = i - rb * (K + 1), row = row0 + rb;
         int v = 0;
@@ -234,10 +238,10 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
                 if (r >= kBM) continue;
                 uint4* cell = reinterpret_cast<uint4*>(a_tile + swizzled(r, bc, kBM * 128u));
                 float fa[8], fp[8];
-                unpack8(anchor_chunk[u], a.dtype, fa);
-                unpack8(*cell, a.dtype, fp);
-                *cell = make_uint4(pack2(fp[0] * fa[0], fp[1] * fa[1], a.dtype), pack2(fp[2] * fa[2], fp[3] * fa[3], a.dtype),
-                                   pack2(fp[4] * fa[4], fp[5] * fa[5], a.dtype), pack2(fp[6] * fa[6], fp[7] * fa[7], a.dtype));
+                unpack8(anchor_chunk[u], kDt, fa);
+                unpack8(*cell, kDt, fp);
+                *cell = make_uint4(pack2(fp[0] * fa[0], fp[1] * fa[1], kDt), pack2(fp[2] * fa[2], fp[3] * fa[3], kDt),
+                                   pack2(fp[4] * fa[4], fp[5] * fa[5], kDt), pack2(fp[6] * fa[6], fp[7] * fa[7], kDt));
             }
         }
     }
@@ -272,7 +276,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
     RLM_TC_PROBE(5);
-    const bool staged = a.out_dtype != RLM_F32;
+    const bool staged = kOut != RLM_F32;
     if (!__syncthreads_or(!ready)) {
     // The operand tiles are consumed: all threads request the expanded-cache segments of the
         // epilogue into the same bytes as 16-byte asynchronous copies (a warp covers two 256-byte
@@ -280,6 +284,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         // sequence j, row RPT + r the partner term of pair r.
             {
             const int c = tid & 15, n_rows_staged = RPT + tile_pairs;
+#pragma unroll 1
             for (int g = tid >> 4; g < n_rows_staged; g += kTcThreads / 16) {
                 const int r = g - RPT;
                 const int rb = g < RPT ? g : (r * a.inv_k16) >> 16;
@@ -303,7 +308,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         const unsigned char* ga = g_anchor + (prb < RPT ? prb : 0) * kRowStride + 128 * ch;
         const unsigned char* gp = g_partner + pr * kRowStride + 128 * ch;
         unsigned char* so = g_partner + pr * kRowStride + 128 * ch;      // results replace the partner term
-#pragma unroll
+#pragma unroll 1      // the body is large and runs once per warp: keep the instruction footprint small
         for (int q = 0; q < 4; ++q) {
             uint32_t v[16];
             tmem_ld16(tmem_base + lane_base + 64 * ch + 16 * q, v);
@@ -313,8 +318,8 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
                 float fa[8], fp[8];
-                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), a.dtype, fa);
-                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), a.dtype, fp);
+                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
+                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     y[8 * hlf + i] = gelu_tc(__uint_as_float(v[8 * hlf + i]) + (fa[i] + fp[i]));
@@ -326,16 +331,17 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
                 for (int i = 0; i < 4; ++i) o[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
             } else {
                 uint4* o = reinterpret_cast<uint4*>(so + 32 * q);
-                o[0] = make_uint4(pack2(y[0], y[1], a.out_dtype), pack2(y[2], y[3], a.out_dtype),
-                                  pack2(y[4], y[5], a.out_dtype), pack2(y[6], y[7], a.out_dtype));
-                o[1] = make_uint4(pack2(y[8], y[9], a.out_dtype), pack2(y[10], y[11], a.out_dtype),
-                                  pack2(y[12], y[13], a.out_dtype), pack2(y[14], y[15], a.out_dtype));
+                o[0] = make_uint4(pack2(y[0], y[1], kOut), pack2(y[2], y[3], kOut),
+                                  pack2(y[4], y[5], kOut), pack2(y[6], y[7], kOut));
+                o[1] = make_uint4(pack2(y[8], y[9], kOut), pack2(y[10], y[11], kOut),
+                                  pack2(y[12], y[13], kOut), pack2(y[14], y[15], kOut));
             }
         }
         if (staged) {
             // 16-bit outputs leave row by row: a warp stores two 256-byte pair rows per instruction
             __syncthreads();
             const int c = tid & 15;
+#pragma unroll 2
             for (int r = tid >> 4; r < tile_pairs; r += kTcThreads / 16) {
                 const int rb = (r * a.inv_k16) >> 16;
                 if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
@@ -549,7 +555,16 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
         set_error("relation_hidden: cuTensorMapEncodeTiled failed");
         return RLM_ERR_LAUNCH;
     }
-    auto kernel = relation_hidden_tc_kernel;
+    using Kernel = void (*)(const CUtensorMap, const HiddenTcArgs);
+    Kernel kernel = nullptr;
+    if (dtype == RLM_BF16)
+        kernel = out_dtype == RLM_F32 ? relation_hidden_tc_kernel<RLM_BF16, RLM_F32>
+               : out_dtype == RLM_BF16 ? relation_hidden_tc_kernel<RLM_BF16, RLM_BF16>
+                                       : relation_hidden_tc_kernel<RLM_BF16, RLM_F16>;
+    else
+        kernel = out_dtype == RLM_F32 ? relation_hidden_tc_kernel<RLM_F16, RLM_F32>
+               : out_dtype == RLM_BF16 ? relation_hidden_tc_kernel<RLM_F16, RLM_BF16>
+                                       : relation_hidden_tc_kernel<RLM_F16, RLM_F16>;
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     dim3 grid(hdim / kTcBN, (n_rows + a.rows_per_tile - 1) / a.rows_per_tile);
