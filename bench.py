@@ -81,10 +81,14 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 3.0               # nvidia-smi needs a moment before its first line
+            while not self.samples and time.time() < deadline:
+                time.sleep(0.01)
+            self.samples.clear()                        # keep only what is sampled from here on
         except OSError:
             self.proc = None
 
@@ -181,6 +185,32 @@ def workload_config(workload: str, batch: int, n_gpus: int) -> dict:
             "batch_per_gpu": batch, "global_batch": batch * n_gpus, "l2": "flushed between steps"}
 
 
+# ---------------------------------------------------------------------------- rank sharding
+
+
+def rank_inputs(cfg, seed: int, batch: int, rank: int):
+    """The token / boundary ids of this rank's sequences: every rank decodes its own `batch`
+    sequences (weak scaling), drawn from a rank-specific seed."""
+    tokens = zipf_tokens(batch, cfg.max_context, cfg.vocab_size, seed + rank)
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (batch, cfg.max_context),
+                           generator=torch.Generator().manual_seed(seed + 77 + rank))
+    return tokens, bounds
+
+
+def max_over_ranks(values, world: int, device) -> list[float]:
+    """Element-wise maximum of per-rank timings (the slowest rank defines the job's time)."""
+    times = torch.tensor(list(values), device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    return [float(v) for v in times.tolist()]
+
+
+def job_rate(world: int, batch_per_rank: int, steps: int, max_ms: float) -> float:
+    """Whole-job tokens/s: the positions all ranks decoded divided by the slowest rank's time."""
+    return world * batch_per_rank * steps / (max_ms / 1e3)
+
+
 # ---------------------------------------------------------------------------- GPU arm
 
 
@@ -273,6 +303,49 @@ def kernel_table(dec, graph_iters: int = 20):
     return table
 
 
+def select_rows256(device, graph_iters: int = 10):
+    """The selector at the row count where bandwidth starts to matter: 256 rows of the 12-layer
+    decode shape (ctx 2048, block 64, window 128, 2 remote blocks, K 8, bf16), three cache sets of
+    268 MB so that consecutive launches miss L2, timed inside a captured graph."""
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    B, T, bs, L, TOP, K = 256, 2048, 64, 128, 2, 8
+    nb, sets = T // bs, 3
+    rn = lambda *shape: torch.randn(*shape, device=device).bfloat16()  # noqa: E731
+    S = [(rn(B, T, 64), rn(B, T, 64), rn(B, T, 128), rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs(),
+          rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs()) for _ in range(sets)]
+    q, g, bias = rn(B, 256), torch.randn(4, device=device), torch.randn(4, 16, device=device)
+    pos = torch.tensor(T - 1, device=device)
+
+    def launch(i):
+        ak, pk, pac, am, as_, pm, ps = S[i]
+        relation_select_packed(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:], pac, pk, pm, ps,
+                               g, bias, pos, L, TOP, K, False)
+
+    launch(0)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(sets):
+                launch(i)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(graph_iters):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / (graph_iters * sets)
+    cand = L + TOP * bs
+    nbytes = B * (2 * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K)
+    return {"kernel": "relation_select_kernel", "rows": B, "us_per_launch": us, "bytes_per_launch": nbytes,
+            "gb_per_s": nbytes / us / 1e3}
+
+
 def run_ours(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -304,9 +377,8 @@ def run_ours(args) -> None:
     B, T = args.batch, cfg.max_context
     prefix = T - 64 if args.prefix is None else args.prefix
     dec = StatefulDecoder(model, B, device, torch.bfloat16)
-    tokens = zipf_tokens(B, T, cfg.vocab_size, seed + rank).to(device)
-    bounds = torch.randint(0, cfg.boundary_vocab_size, (B, T),
-                           generator=torch.Generator().manual_seed(seed + 77 + rank)).to(device)
+    tokens, bounds = rank_inputs(cfg, seed, B, rank)
+    tokens, bounds = tokens.to(device), bounds.to(device)
 
     log(f"state allocated: {dec.state_bytes() / 1e9:.1f} GB")
     launches_before = _abi.launch_count()
@@ -393,15 +465,12 @@ def run_ours(args) -> None:
     clocks = sampler.stop() if sampler else None
     assert _abi.read_status() == 0, "a kernel reported a device-side error"
 
-    times = torch.tensor([total_ms, e2e_s * 1e3, warm_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        import torch.distributed as dist
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, warm_ms = [float(v) for v in times.tolist()]
+    total_ms, e2e_ms, warm_ms = max_over_ranks([total_ms, e2e_s * 1e3, warm_ms], world, device)
 
     if rank == 0:
         log(f"timed region done: {total_ms / args.steps:.3f} ms/step")
         table = kernel_table(dec)
+        rows256 = select_rows256(device)
         log("kernel table done")
         peaks = {}
         try:
@@ -418,13 +487,13 @@ def run_ours(args) -> None:
         log(f"cpu baseline: {cpu_steps} positions of {cpu_batch} sequences on {threads} threads")
         cpu_value, cpu_elapsed, cpu_threads = cpu_decode_rate(args.workload, cpu_batch, cpu_steps, 1, threads)
         line = {
-            "metric": METRIC, "value": world * B * args.steps / (total_ms / 1e3), "unit": UNIT,
+            "metric": METRIC, "value": job_rate(world, B, args.steps, total_ms), "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {**workload_config(args.workload, B, world),
                        "parameters": model.parameter_count(), "state_bytes_per_gpu": dec.state_bytes()},
-            "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
+            "e2e": {"value": job_rate(world, B, e2e_steps, e2e_ms), "unit": UNIT,
                     "h2d_bytes_per_step": 2 * B * 8, "d2h_bytes_per_step": B * 8,
                     "steps": e2e_steps},
             "gpu_launches": kernels_per_step * args.steps,
@@ -438,6 +507,9 @@ def run_ours(args) -> None:
                          "share_of_library_time": dom["us_per_step"] / lib_us,
                          "note": "batch-8 decode launches move < 1 MB each and are latency-bound"},
             "kernels": table,
+            "roofline_rows256": {**rows256, "peak": peak, "frac": rows256["gb_per_s"] / peak,
+                                 "note": "the selector at 256 rows of the 12-layer decode shape, the "
+                                         "smallest launch whose bytes (21 MB) are bandwidth-relevant"},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cpu_threads, "kind": "port",
                              "sample": f"{cpu_steps} decode positions of {cpu_batch} of the {B} sequences from a synthetic "
                                        "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
