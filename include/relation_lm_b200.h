@@ -53,6 +53,19 @@ typedef enum {
 #define RLM_DEV_TIMEOUT 1      /* a bounded wait on a bulk copy expired */
 #define RLM_DEV_POSITION 2     /* position / row index outside the caches */
 
+/*
+ * Programmatic dependent launch (extension; off by default).  When enabled, every kernel of this
+ * library is launched with programmatic stream serialisation: its CTAs may start while the kernel
+ * before it on the stream is still running, set up their barriers / tensor memory, request their
+ * weight tiles and, for the decode form of the selectors, request the key-cache windows and block
+ * statistics, and only then wait for the earlier kernels to complete.  Results are unchanged
+ * provided the caller keeps one rule: the key caches, block statistics and the `position` scalar
+ * passed to a selector must not be written by the kernel launched immediately before it on the
+ * same stream (in a decode step they are written by the cache append, several launches earlier).
+ * Returns the previous setting.  The setting is process-wide and read at launch (capture) time.
+ */
+int rlm_set_programmatic_launch(int enabled);
+
 /* Library identity.  rlm_last_error() returns a host string describing the
  * last non-zero status returned on the calling thread. */
 int rlm_abi_version(void);

@@ -24,6 +24,7 @@ struct EmbedArgs {
 };
 
 __global__ void __launch_bounds__(256) decode_embed_kernel(const EmbedArgs a) {
+    griddep_sync();
     const int b = blockIdx.x;
     const int64_t tok = a.tokens[b], bnd = a.boundaries[b];
     const int t = static_cast<int>(*a.position);
@@ -62,7 +63,7 @@ extern "C" int rlm_decode_embed(const int64_t* tokens, const int64_t* boundaries
     if (!valid_dtype(table_dtype)) { set_error("decode_embed: unknown dtype code"); return RLM_ERR_DTYPE; }
     EmbedArgs a{tokens, boundaries, token_table, boundary_table, position_table, position, out, status,
                 scale, batch, d_model, vocab, boundary_vocab, max_t, table_dtype};
-    decode_embed_kernel<<<batch, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(decode_embed_kernel, dim3(batch), dim3(256), 0, stream, a);
     count_launch();
     return check_launch("decode_embed_kernel");
 }

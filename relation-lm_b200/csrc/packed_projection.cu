@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    griddep_sync();      // barriers and tensor memory are set up; x may come from the previous kernel
 
     if (tid == 0) {
         // producer: fill the ring
@@ -221,6 +222,7 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
     }
 
     // LayerNorm of the rows, one warp per row, lane l owns the 16-byte chunks l, l+32, ...
+    griddep_sync();      // the weight slice is on its way; x may come from the previous kernel
     const int chunks = a.k / 8;
     for (int r = warp; r < m_here; r += kGemmThreads / 32) {
         const float* row = a.x + (m0 + r) * a.x_stride;
@@ -375,6 +377,7 @@ struct NormCastArgs {
 };
 
 __global__ void __launch_bounds__(kCastThreads) layer_norm_cast_kernel(const NormCastArgs a) {
+    griddep_sync();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (kCastThreads / 32) + (threadIdx.x >> 5);
     if (r >= a.m) return;
@@ -437,7 +440,7 @@ int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a,
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     dim3 grid(a.n / BN, (a.m + kBM - 1) / kBM);
-    kernel<<<grid, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mx, mw, a);
+    launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, mx, mw, a);
     count_launch();
     return check_launch("packed_projection_kernel");
 }
@@ -453,7 +456,7 @@ int launch_norm_gemm(const CUtensorMap& mw, const NormGemmArgs& a, void* stream)
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     dim3 grid(a.n / BN, (a.m + a.tile_rows - 1) / a.tile_rows);
-    kernel<<<grid, kGemmThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(mw, a);
+    launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, mw, a);
     count_launch();
     return check_launch("norm_projection_kernel");
 }
@@ -539,7 +542,7 @@ extern "C" int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const f
     a.x = x; a.gamma = gamma; a.beta = beta; a.out = out; a.x_stride = x_row_stride; a.eps = eps;
     a.m = rows; a.k = d_in; a.out_dtype = out_dtype;
     const int per_cta = kCastThreads / 32;
-    layer_norm_cast_kernel<<<(rows + per_cta - 1) / per_cta, kCastThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(layer_norm_cast_kernel, dim3((rows + per_cta - 1) / per_cta), dim3(kCastThreads), 0, stream, a);
     count_launch();
     return check_launch("layer_norm_cast_kernel");
 }

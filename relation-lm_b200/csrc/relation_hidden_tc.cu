@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
 
+    griddep_sync();      // weight tile requested, tensor memory allocated: now the previous kernel's outputs
     // gathered indices of the tile's sequences
 #pragma unroll 1
     for (int i = tid; i < RPT * (K + 1); i += kTcThreads) {
@@ -416,6 +417,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    griddep_sync();
     // current operand rows of the group's sequences (zero rows up to n_cols), copied
     // asynchronously straight to their swizzled places
     const size_t op_row = static_cast<size_t>(R) * 2;
@@ -536,7 +538,7 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
         int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
         if (rc != RLM_OK) return rc;
         dim3 grid(hdim / kTcBN, 2, (n_seq + kUpdMaxSeq - 1) / kUpdMaxSeq);
-        kernel<<<grid, kUpdThreads, update_smem_bytes(rdim, n_seq), static_cast<cudaStream_t>(stream)>>>(ma, mp, u);
+        launch_kernel(kernel, dim3(grid), dim3(kUpdThreads), update_smem_bytes(rdim, n_seq), stream, ma, mp, u);
         count_launch();
         rc = check_launch("expanded_row_update_kernel");
         if (rc != RLM_OK) return rc;
@@ -568,7 +570,7 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     dim3 grid(hdim / kTcBN, (n_rows + a.rows_per_tile - 1) / a.rows_per_tile);
-    kernel<<<grid, kTcThreads, gather_smem_bytes(rdim, k_out), static_cast<cudaStream_t>(stream)>>>(mm, a);
+    launch_kernel(kernel, dim3(grid), dim3(kTcThreads), gather_smem_bytes(rdim, k_out), stream, mm, a);
     count_launch();
     return check_launch("relation_hidden_tc_kernel");
 }

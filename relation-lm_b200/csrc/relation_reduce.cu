@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
     const int steps = R / 4;                              // float4 steps along the relation dimension
     const int r_lo = 4 * (rq * steps / kSplit), r_hi = 4 * ((rq + 1) * steps / kSplit);
     const int groups = (a.n_rows + kRB - 1) / kRB;
+    griddep_sync();      // the weight tiles are requested; indices and caches may come from the previous kernel
 
     for (int group = blockIdx.y; group < groups; group += gridDim.y) {
         __syncthreads();   // previous group's reads are done; weight tiles are staged
@@ -346,7 +347,7 @@ int launch_hidden_as(const HiddenArgs& a, void* stream) {
     int gy = (148 * 4 + tiles - 1) / tiles;
     if (gy > groups) gy = groups;
     dim3 grid(tiles, gy);
-    kernel<<<grid, kHiddenThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(kernel, dim3(grid), dim3(kHiddenThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch("relation_hidden_kernel");
 }
@@ -412,6 +413,7 @@ struct NormArgs {
 
 __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
+    griddep_sync();
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = a.k_out, D = a.dim;
     const int per = (D + 31) / 32;
@@ -507,6 +509,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 template <int kVecChunks>
 __global__ void __launch_bounds__(kNormThreads, 2) relation_norm_reduce_vec_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
+    griddep_sync();
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = a.k_out, D = a.dim;
     const int chunks = D / 8;
@@ -666,13 +669,13 @@ extern "C" int rlm_relation_norm_reduce(
     const bool vec = dim % 8 == 0 && aligned16(raw) && aligned16(norm_weight) && aligned16(norm_bias) &&
                      (!out || aligned16(out)) && (!residual || aligned16(residual));
     if (vec && dim <= 512)
-        relation_norm_reduce_vec_kernel<2><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+        launch_kernel(relation_norm_reduce_vec_kernel<2>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     else if (vec && dim <= 768)
-        relation_norm_reduce_vec_kernel<3><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+        launch_kernel(relation_norm_reduce_vec_kernel<3>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     else if (vec)
-        relation_norm_reduce_vec_kernel<4><<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+        launch_kernel(relation_norm_reduce_vec_kernel<4>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     else
-        relation_norm_reduce_kernel<<<n_rows, kNormThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+        launch_kernel(relation_norm_reduce_kernel, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch("relation_norm_reduce_kernel");
 }

@@ -289,20 +289,13 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
     const bool do_anchor = a.mode != kPartnerOnly, do_partner = a.mode != kAnchorOnly;
     const int buckets4 = 4 * a.buckets;
 
-    // Loads that depend on nothing go first: this thread's query element, the router
-    // parameters of its head and its slice of the two bias tables.
-    float qv = 0.0f;
-    if (a.mode == kPacked) {
-        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
-        else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, a.query_dtype);
-    } else if (a.mode == kAnchorOnly) {
-        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
-    } else {
-        if (tid < kD) qv = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
-    }
+    // Decode form: the caches, statistics and the position were written before the previous
+    // kernel of the stream started, so everything up to the bulk-copy requests may run while
+    // that kernel (the query projection) is still executing; only the queries wait for it.
+    // The per-row form and exclusion lists take indices from arbitrary producers: wait first.
+    const bool early = a.row_position == nullptr && a.row_batch == nullptr && a.exclude_list == nullptr &&
+                       a.mode != kPartnerOnly;
+    if (!early) griddep_sync();
     const int my_head = (lane & 7) >> 1;
     float ga = 0.0f, gp = 0.0f, ba = 0.0f, bp_ = 0.0f;
     if (do_anchor) ga = load_scalar(a.anchor_gamma, my_head, a.param_dtype);
@@ -367,6 +360,20 @@ __global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectA
             }
             bulk_g2s(smem_u32(smem + p.p_local) + ldst, static_cast<const char*>(a.partner_keys) + loff, lbytes, bar_p);
         }
+    }
+    if (early) griddep_sync();
+    // this thread's query element
+    float qv = 0.0f;
+    if (a.mode == kPacked) {
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
+        else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, a.query_dtype);
+    } else if (a.mode == kAnchorOnly) {
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
+    } else {
+        if (tid < kD) qv = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
     }
     // queries[0..255]: packed = aq | arq | partner base (exact 64 | router 64);
     // partner-only = (unused 128) | pq | prq; anchor-only = aq | arq
@@ -724,7 +731,7 @@ int launch(SelectArgs& a, void* stream) {
     }
     int rc = allow_large_smem(reinterpret_cast<const void*>(relation_select_kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
-    relation_select_kernel<<<a.n_rows, kThreads, plan.total, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(relation_select_kernel, dim3(a.n_rows), dim3(kThreads), plan.total, stream, a);
     count_launch();
     return check_launch("relation_select_kernel");
 }

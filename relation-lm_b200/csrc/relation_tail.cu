@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
 #ifdef RLM_TRACE
     __shared__ long long probe[16];
 #endif
+    griddep_sync();
     RLM_TPROBE(0);
 
     constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kTailBN * kBK * 2;
@@ -311,7 +312,7 @@ int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hi
     int rc = allow_large_smem(reinterpret_cast<const void*>(relation_tail_kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     dim3 grid(n_tiles, splits, m_tiles);
-    relation_tail_kernel<<<grid, kTailThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(ma, mw, a);
+    launch_kernel(relation_tail_kernel, dim3(grid), dim3(kTailThreads), smem_bytes, stream, ma, mw, a);
     count_launch();
     return check_launch("relation_tail_kernel");
 }

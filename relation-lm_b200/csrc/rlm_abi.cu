@@ -20,6 +20,9 @@ void set_error(const char* message) {
     std::snprintf(g_error, sizeof(g_error), "%s", message ? message : "");
 }
 
+std::atomic<int> g_programmatic{0};
+bool programmatic_launch_enabled() { return g_programmatic.load(std::memory_order_relaxed) != 0; }
+
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int check_launch(const char* kernel_name) {
@@ -58,6 +61,9 @@ int allow_large_smem(const void* kernel, int bytes) {
 }
 }  // namespace rlm
 
+extern "C" int rlm_set_programmatic_launch(int enabled) {
+    return rlm::g_programmatic.exchange(enabled ? 1 : 0, std::memory_order_relaxed);
+}
 extern "C" int rlm_abi_version(void) { return RLM_ABI_VERSION; }
 extern "C" const char* rlm_last_error(void) { return rlm::g_error; }
 extern "C" int64_t rlm_launch_count(void) { return rlm::g_launches.load(std::memory_order_relaxed); }

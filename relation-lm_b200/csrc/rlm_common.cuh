@@ -18,6 +18,30 @@ int check_launch(const char* kernel_name);    // cudaGetLastError -> rlm_status
 // Opts a kernel into `bytes` of dynamic shared memory, once per device.
 int allow_large_smem(const void* kernel, int bytes);
 
+// Whether kernels are launched with programmatic stream serialisation (rlm_set_programmatic_launch).
+bool programmatic_launch_enabled();
+
+// Launches `kernel`; with programmatic launch enabled the grid may start while the kernel before
+// it in the stream is still running, and every kernel here orders itself with griddep_wait()
+// before it touches anything an earlier kernel may have produced.
+template <typename... Params, typename... Args>
+inline void launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem_bytes, void* stream,
+                          Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attribute[1];
+    if (programmatic_launch_enabled()) {
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+    }
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // Shared memory one CTA may use on sm_100 (227 KB) and the part of it the kernels here
 // request dynamically (the rest covers their small static allocations).
 constexpr int kSmemPerCta = 232448;
@@ -30,6 +54,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // ------------------------------------------------------------------ device side
 
 constexpr float kNegInf = -__builtin_huge_valf();
+
+// Programmatic dependent launch: wait until every kernel earlier in the stream has completed and
+// its writes are visible (a no-op for an ordinary launch), then let the next kernel's CTAs start
+// their own preamble.  Before the wait a kernel may only touch what no earlier kernel of the
+// same stream can still be writing: its parameters (weights, tables) and its own shared memory.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_sync() { griddep_wait(); griddep_launch_dependents(); }
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
     return __uint_as_float(bits16 << 16);

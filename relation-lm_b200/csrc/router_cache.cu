@@ -105,6 +105,7 @@ __device__ __forceinline__ void router_update(const RouterArgs& a, int b, int la
 __global__ void __launch_bounds__(kThreads) router_cache_update_kernel(const RouterArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long bar_storage;
+    griddep_sync();
     const int b = blockIdx.x, layer = blockIdx.y, tid = threadIdx.x;
     const int t = static_cast<int>(*a.position);
     const int blk = t / a.block_size;
@@ -161,6 +162,7 @@ __device__ __forceinline__ float round_to(float v, int dtype) {
 }
 
 __global__ void __launch_bounds__(kThreads) router_cache_prefill_kernel(const PrefillArgs a) {
+    griddep_sync();
     const int b = blockIdx.x, blk = blockIdx.y, tid = threadIdx.x;
     const int s = tid / kD, c = tid % kD;
     const int bs = a.block_size, start = blk * bs;
@@ -241,7 +243,7 @@ int validate_and_launch(RouterArgs& a, void* stream, const char* who) {
         if (rc != RLM_OK) return rc;
     }
     dim3 grid(a.batch, a.layers);
-    router_cache_update_kernel<<<grid, kThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(router_cache_update_kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch(who);
 }
@@ -356,7 +358,7 @@ extern "C" int rlm_router_cache_prefill(
     a.batch = batch; a.max_t = max_t; a.n_blocks = n_blocks; a.block_size = block_size; a.length = length;
     a.raw_dtype = raw_dtype; a.cache_dtype = cache_dtype; a.stats_dtype = stats_dtype; a.weight_dtype = weight_dtype;
     dim3 grid(batch, (length + block_size - 1) / block_size);
-    router_cache_prefill_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    launch_kernel(router_cache_prefill_kernel, dim3(grid), dim3(kThreads), 0, stream, a);
     count_launch();
     return check_launch("router_cache_prefill_kernel");
 }

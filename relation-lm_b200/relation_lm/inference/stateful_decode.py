@@ -22,6 +22,7 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from relation_lm.inference.routed_model import RoutedRelationLM
+from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import decode_embed, norm_projection
 from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update,
                                                  relation_hidden_cache_update_out,
@@ -33,8 +34,10 @@ from relation_lm.kernels.router_cache import sparse_cache_append
 
 class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
-                 dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False) -> None:
+                 dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
+                 programmatic_launch: bool = True) -> None:
         cfg = model.config
+        self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
         self.w = model.decode_weights(self.device, dtype)
         self.input_scale = float(model.input_scale)
@@ -85,7 +88,13 @@ class StatefulDecoder:
         """Consume one token per sequence at the current position; returns (token logits
         ``[B, V]``, boundary logits ``[B, Vb]``) and advances the position."""
         if self.fused:
-            return self._step_fused(tokens, boundaries, keep_selection)
+            # The fused step keeps the selector's rule for programmatic launch: the caches are
+            # written by the append, two launches before the first selector.
+            previous = _abi.set_programmatic_launch(self.programmatic_launch)
+            try:
+                return self._step_fused(tokens, boundaries, keep_selection)
+            finally:
+                _abi.set_programmatic_launch(previous)
         cfg, w = self.config, self.w
         pos = self.position
         x = (F.embedding(tokens, w["token_embedding"]) + F.embedding(boundaries, w["boundary_embedding"])).float()

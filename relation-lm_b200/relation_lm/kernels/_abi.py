@@ -24,6 +24,7 @@ PROTOTYPES = {
     "rlm_router_cache_prefill": [_P, _L, _L, _P, _L, _L] + [_P] * 10 + [_I] * 9 + [_P],
     "rlm_packed_projection": [_P, _L, _P, _P] + [_I] * 5 + [_P, _P],
     "rlm_norm_projection": [_P, _L, _P, _P, _F, _P, _P] + [_I] * 5 + [_P, _P],
+    "rlm_set_programmatic_launch": [_I],
     "rlm_layer_norm_cast": [_P, _L, _P, _P, _F, _P] + [_I] * 3 + [_P],
     "rlm_relation_tail": [_P] * 7 + [_F] + [_P] * 4 + [_L] + [_I] * 5 + [_P, _P],
     "rlm_relation_tail_static": [_P] * 7 + [_F] + [_P] * 3 + [_I] * 5 + [_P, _P],
@@ -84,6 +85,13 @@ def read_status(device: torch.device | None = None, clear: bool = True) -> int:
 def launch_count() -> int:
     """Kernels launched by the library in this process."""
     return int(LIB.rlm_launch_count())
+
+
+def set_programmatic_launch(enabled: bool) -> bool:
+    """Switch programmatic dependent launch of the library's kernels on or off; returns the
+    previous setting.  While it is on, the caches, block statistics and position given to a
+    selector must not be written by the kernel launched just before it on the same stream."""
+    return bool(LIB.rlm_set_programmatic_launch(1 if enabled else 0))
 
 
 def ptr(t: torch.Tensor | None):
