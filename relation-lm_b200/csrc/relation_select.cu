@@ -273,7 +273,7 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
                      static_cast<uint32_t>(sel[3 * r + 2] * key_row), bar);
 }
 
-__global__ void __launch_bounds__(kThreads) relation_select_kernel(const SelectArgs a) {
+__global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
