@@ -12,6 +12,8 @@
 // Replaces the F.linear of src/relation_lm/inference/packed_cache.py:52-57 of the reference
 // project (and serves the query-side router projections, which have the same shape).
 
+#include <cstdlib>
+
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
@@ -224,58 +226,72 @@ __global__ void __launch_bounds__(kGemmThreads) norm_projection_kernel(
     // LayerNorm of the rows, one warp per row, lane l owns the 16-byte chunks l, l+32, ...
     griddep_sync();      // the weight slice is on its way; x may come from the previous kernel
     const int chunks = a.k / 8;
-    for (int r = warp; r < m_here; r += kGemmThreads / 32) {
-        const float* row = a.x + (m0 + r) * a.x_stride;
-        float v[kNormMaxPerLane][8];
-        float sum = 0.0f;
+    // two rows of a warp are in flight at a time (their loads are issued before either reduction)
+    for (int r0 = warp; r0 < m_here; r0 += 2 * (kGemmThreads / 32)) {
+        float v[2][kNormMaxPerLane][8];
+        float sum[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < kNormMaxPerLane; ++i) {
-            const int c = lane + 32 * i;
-            if (c < chunks) {
-                const float4 lo = *reinterpret_cast<const float4*>(row + 8 * c);
-                const float4 hi = *reinterpret_cast<const float4*>(row + 8 * c + 4);
-                v[i][0] = lo.x; v[i][1] = lo.y; v[i][2] = lo.z; v[i][3] = lo.w;
-                v[i][4] = hi.x; v[i][5] = hi.y; v[i][6] = hi.z; v[i][7] = hi.w;
+        for (int u = 0; u < 2; ++u) {
+            const int r = r0 + u * (kGemmThreads / 32);
+            if (r >= m_here) continue;
+            const float* row = a.x + (m0 + r) * a.x_stride;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) sum += v[i][e];
+            for (int i = 0; i < kNormMaxPerLane; ++i) {
+                const int c = lane + 32 * i;
+                if (c < chunks) {
+                    const float4 lo = *reinterpret_cast<const float4*>(row + 8 * c);
+                    const float4 hi = *reinterpret_cast<const float4*>(row + 8 * c + 4);
+                    v[u][i][0] = lo.x; v[u][i][1] = lo.y; v[u][i][2] = lo.z; v[u][i][3] = lo.w;
+                    v[u][i][4] = hi.x; v[u][i][5] = hi.y; v[u][i][6] = hi.z; v[u][i][7] = hi.w;
+                }
             }
         }
-        float mean = 0.0f, inv = 1.0f;
-        if (a.gamma) {
-            mean = warp_sum(sum) / static_cast<float>(a.k);
-            float sq = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int r = r0 + u * (kGemmThreads / 32);
+            if (r >= m_here) continue;
 #pragma unroll
             for (int i = 0; i < kNormMaxPerLane; ++i)
                 if (lane + 32 * i < chunks)
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) { float d = v[i][e] - mean; sq = fmaf(d, d, sq); }
-            inv = rsqrtf(warp_sum(sq) / static_cast<float>(a.k) + a.eps);
-        }
+                    for (int e = 0; e < 8; ++e) sum[u] += v[u][i][e];
+            float mean = 0.0f, inv = 1.0f;
+            if (a.gamma) {
+                mean = warp_sum(sum[u]) / static_cast<float>(a.k);
+                float sq = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kNormMaxPerLane; ++i) {
-            const int c = lane + 32 * i;
-            if (c >= chunks) continue;
-            uint32_t packed[4];
+                for (int i = 0; i < kNormMaxPerLane; ++i)
+                    if (lane + 32 * i < chunks)
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-                float y0 = (v[i][e] - mean) * inv, y1 = (v[i][e + 1] - mean) * inv;
-                if (a.gamma) {
-                    y0 = fmaf(y0, a.gamma[8 * c + e], a.beta[8 * c + e]);
-                    y1 = fmaf(y1, a.gamma[8 * c + e + 1], a.beta[8 * c + e + 1]);
-                }
-                if (a.w_dtype == RLM_BF16) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
-                    packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
-                } else {
-                    __half2 h = __floats2half2_rn(y0, y1);
-                    packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
-                }
+                        for (int e = 0; e < 8; ++e) { float d = v[u][i][e] - mean; sq = fmaf(d, d, sq); }
+                inv = rsqrtf(warp_sum(sq) / static_cast<float>(a.k) + a.eps);
             }
-            // K-major, 128-byte swizzle: 16-byte chunk index xor (row mod 8)
-            const int kb = c >> 3, c16 = c & 7;
-            unsigned char* dst = a_tile + kb * a.a_stride + (r >> 3) * 1024 + (r & 7) * 128 +
-                                 ((c16 ^ (r & 7)) << 4);
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+#pragma unroll
+            for (int i = 0; i < kNormMaxPerLane; ++i) {
+                const int c = lane + 32 * i;
+                if (c >= chunks) continue;
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    float y0 = (v[u][i][e] - mean) * inv, y1 = (v[u][i][e + 1] - mean) * inv;
+                    if (a.gamma) {
+                        y0 = fmaf(y0, a.gamma[8 * c + e], a.beta[8 * c + e]);
+                        y1 = fmaf(y1, a.gamma[8 * c + e + 1], a.beta[8 * c + e + 1]);
+                    }
+                    if (a.w_dtype == RLM_BF16) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                        packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(y0, y1);
+                        packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+                // K-major, 128-byte swizzle: 16-byte chunk index xor (row mod 8)
+                const int kb = c >> 3, c16 = c & 7;
+                unsigned char* dst = a_tile + kb * a.a_stride + (r >> 3) * 1024 + (r & 7) * 128 +
+                                     ((c16 ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
         }
     }
     fence_proxy_async();     // generic-proxy writes of the x tile -> visible to the tensor core
@@ -491,6 +507,9 @@ extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const f
     int bn = 128;
     if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
     if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
+#ifdef RLM_TUNE
+    if (const char* forced = getenv("RLM_GEMM_BN")) { int v = atoi(forced); if (v == 32 || (v == 64 && n_out % 64 == 0) || (v == 128 && n_out % 128 == 0)) bn = v; }
+#endif
     CUtensorMap mw;
     if (!make_map(&mw, weight, n_out, d_in, d_in, bn, weight_dtype)) {
         set_error("norm_projection: cuTensorMapEncodeTiled failed");
@@ -572,6 +591,9 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     int bn = 128;
     if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
     if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
+#ifdef RLM_TUNE
+    if (const char* forced = getenv("RLM_GEMM_BN")) { int v = atoi(forced); if (v == 32 || (v == 64 && n_out % 64 == 0) || (v == 128 && n_out % 128 == 0)) bn = v; }
+#endif
     // x tile: the box holds only the rows that exist (a multiple of 8, at most 128); the MMA
     // reads 128 rows of the stage, the rest is never stored
     const int box_rows = rows >= kBM ? kBM : ((rows + 7) / 8) * 8;

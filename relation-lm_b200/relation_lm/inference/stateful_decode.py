@@ -67,7 +67,7 @@ class StatefulDecoder:
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.head_weight = torch.cat((self.w["token_embedding"], self.w["boundary_w"]), 0).contiguous()
-            pad = (-self.head_weight.size(0)) % 32
+            pad = (-self.head_weight.size(0)) % 128        # whole 128-column tiles for the projection kernel
             if pad:
                 self.head_weight = torch.cat((self.head_weight, zeros(pad, cfg.d_model)), 0).contiguous()
 

@@ -13,7 +13,7 @@ from torch import Tensor
 
 from relation_lm.kernels import _abi
 
-_ROW_TILE = 128    # rows one CTA of the fused LayerNorm + projection kernel normalises
+_FUSED_NORM_ROWS = 16    # beyond this many rows normalising once beats normalising in every column tile
 
 
 @torch.library.custom_op("relation_lm::packed_projection", mutates_args=(), device_types="cuda")
@@ -53,8 +53,8 @@ def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: T
     if weight.dim() != 2 or weight.size(1) != x.size(1) or norm_weight.numel() != x.size(1):
         raise ValueError("weight must be [n_out, d_in] and the norm parameters [d_in]")
     rows, d_in = x.shape
-    if rows > _ROW_TILE:
-        # beyond one row tile: normalise once into a 16-bit matrix, then the TMA-fed GEMM
+    if rows > _FUSED_NORM_ROWS:
+        # normalise once into a 16-bit matrix, then the TMA-fed GEMM
         normalized = torch.empty((rows, d_in), device=device, dtype=weight.dtype)
         with _abi.device_guard(device):
             _abi.check(_abi.LIB.rlm_layer_norm_cast(
