@@ -77,3 +77,25 @@ def test_norm_projection_matches_layer_norm_then_linear(rows, d_in, n_out, dtype
     want = oracle.linear(normalized, w)
     assert torch.allclose(got, want, atol=2e-2, rtol=1e-2), (got - want).abs().max()
     assert_status_clear()
+
+
+@pytest.mark.parametrize("rows,d_in,n_out", [(40, 512, 128), (300, 512, 96)])
+def test_fused_norm_projection_entry_point_with_many_rows(rows, d_in, n_out):
+    """The fused LayerNorm + projection kernel itself (the Python wrapper prefers the
+    normalise-once path beyond 16 rows), row tiles included, through the C ABI."""
+    from relation_lm.kernels import _abi
+
+    g = torch.Generator().manual_seed(rows + n_out)
+    x = (torch.randn(rows, d_in, generator=g) * 2 + 0.3).cuda()
+    gamma, beta = (torch.rand(d_in, generator=g) + 0.5).cuda(), (torch.randn(d_in, generator=g) * 0.1).cuda()
+    w = (torch.randn(n_out, d_in, generator=g) * 0.05).bfloat16().cuda()
+    out = torch.empty(rows, n_out, device="cuda", dtype=torch.bfloat16)
+    with _abi.device_guard(x.device):
+        _abi.check(_abi.LIB.rlm_norm_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(gamma), _abi.ptr(beta), 1e-5, _abi.ptr(w), _abi.ptr(out), rows,
+            d_in, n_out, _abi.code(w), _abi.code(out), _abi.ptr(_abi.status_tensor(x.device)),
+            _abi.stream_ptr(x.device)))
+    normalized = F.layer_norm(x.cpu(), (d_in,), gamma.cpu(), beta.cpu(), 1e-5).bfloat16()
+    want = oracle.linear(normalized, w.cpu())
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=1e-2), (out.float().cpu() - want).abs().max()
+    assert_status_clear()
