@@ -271,6 +271,24 @@ int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const float* gamma
                         float eps, void* out, int rows, int d_in, int out_dtype, void* stream);
 
 /*
+ * Expanded-cache rows of the current position for every layer of a stack in one launch
+ * (extension, tensor cores): expanded[l, b, t, :H] = anchor_weight[l] . operand[l, b, t] + first_bias[l],
+ * expanded[l, b, t, H:] = partner_weight[l] . operand[l, b, t].  It is the cache half of
+ * rlm_relation_hidden_cache_update (src/relation_lm/kernels/relation_reduce.py:215-251) taken out
+ * of the per-layer loop, the "separate_update" mode the reference recommends for batched decode
+ * (src/relation_lm/kernels/relation_reduce.py:60-70): the operand rows of position t are all
+ * known once the packed projection has been appended, so the per-layer kernels can then use
+ * rlm_relation_hidden_cached.
+ *   expanded_cache [layers, B, T, 2H], operand_cache [layers, B, T, R], weights [layers, H, R],
+ *   first_bias [layers, H]: bfloat16 or float16 (one dtype); R a multiple of 64, H of 128.
+ */
+int rlm_expanded_cache_append(void* expanded_cache, const void* operand_cache,
+                              const void* anchor_weight, const void* partner_weight,
+                              const void* first_bias, const int64_t* position, int layers, int batch,
+                              int max_t, int relation_dim, int hidden_dim, int dtype,
+                              int32_t* status, void* stream);
+
+/*
  * Decode-state append for every layer of a stack in one launch (extension).  Does what a
  * reference decode step does per layer after PackedSparseCacheProjection.project
  * (src/relation_lm/inference/packed_cache.py:52-57): writes the four token features into

@@ -70,12 +70,13 @@ struct HiddenTcArgs {
 };
 
 struct RowUpdateArgs {
-    void* expanded_cache;
-    const void* operand_cache;
-    const void* first_bias;
+    void* expanded_cache;           // [layers, n_seq, max_t, 2H]
+    const void* operand_cache;      // [layers, n_seq, max_t, R]
+    const void* first_bias;         // [layers, H]
     const int64_t* position;
     int32_t* status;
     int n_seq, max_t, rdim, hdim, dtype;
+    int seq_groups;                 // grid.z = layers * seq_groups
 };
 
 // GELU(x) = x * Phi(x) with Phi(x) = 1 - erfc(|x| / sqrt 2) / 2 mirrored for x < 0, erfc from the
@@ -365,8 +366,9 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
 
 // ------------------------------------------------------------------ expanded row of position t
 
-// grid (H / 128, 2 halves, sequence groups of up to 64).  `n_cols` = sequences of the group
-// rounded up to 16 = MMA N = TMEM columns in use; `tmem_cols` the power of two allocated.
+// grid (H / 128, 2 halves, layers x sequence groups of up to 64); the weight tensor maps cover
+// the layers stacked along the rows ([layers * H, R]).  `n_cols` = sequences of the group rounded
+// up to 16 = MMA N = TMEM columns in use; `tmem_cols` the power of two allocated.
 __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
     const __grid_constant__ CUtensorMap map_wa, const __grid_constant__ CUtensorMap map_wp,
     const RowUpdateArgs a) {
@@ -378,7 +380,8 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
     const int tid = threadIdx.x, warp = tid >> 5;
     const int R = a.rdim, H = a.hdim;
     const int kblocks = R / kBK, chunks = R / 8;
-    const int h0 = blockIdx.x * kTcBN, half = blockIdx.y, s0 = blockIdx.z * kUpdMaxSeq;
+    const int layer = blockIdx.z / a.seq_groups;
+    const int h0 = blockIdx.x * kTcBN, half = blockIdx.y, s0 = (blockIdx.z - layer * a.seq_groups) * kUpdMaxSeq;
     const int n_here = min(a.n_seq - s0, kUpdMaxSeq);
     const int n_cols = (n_here + 15) & ~15;
     int tmem_cols = 32;
@@ -410,7 +413,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
         failed = 0;
         mbar_expect_tx(bar_w, w_bytes);
         for (int kb = 0; kb < kblocks; ++kb)
-            tma_load_2d(smem_u32(w_tile) + kb * kBM * 128u, map, kb * kBK, h0, bar_w);
+            tma_load_2d(smem_u32(w_tile) + kb * kBM * 128u, map, kb * kBK, layer * H + h0, bar_w);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -427,7 +430,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
         const uint32_t dst = smem_u32(cur_tile) + swizzled(j, c, cur_kblock);
         if (j < n_here)
             cp_async16(dst, static_cast<const char*>(a.operand_cache) +
-                                (static_cast<size_t>(s0 + j) * a.max_t + t) * op_row + 16 * c);
+                                ((static_cast<size_t>(layer) * a.n_seq + s0 + j) * a.max_t + t) * op_row + 16 * c);
         else
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
     }
@@ -463,7 +466,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
     if (!__syncthreads_or(!ready)) {
         // this thread owns hidden column h0 + tid of the half: one 2-byte store per sequence,
         // a warp's 32 stores of one sequence are 64 contiguous bytes of its cache row
-        const float bias = half == 0 ? load_scalar(a.first_bias, h0 + tid, a.dtype) : 0.0f;
+        const float bias = half == 0 ? load_scalar(a.first_bias, static_cast<int64_t>(layer) * H + h0 + tid, a.dtype) : 0.0f;
         const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
         uint16_t* cache = static_cast<uint16_t*>(a.expanded_cache);
         for (int c = 0; c < n_cols; c += 16) {
@@ -482,7 +485,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
                     __half hv = __float2half_rn(val);
                     bits = *reinterpret_cast<uint16_t*>(&hv);
                 }
-                cache[(static_cast<size_t>(s0 + c + j) * a.max_t + t) * 2 * H + half * H + h0 + tid] = bits;
+                cache[((static_cast<size_t>(layer) * a.n_seq + s0 + c + j) * a.max_t + t) * 2 * H + half * H + h0 + tid] = bits;
             }
         }
     } else if (tid == 0 && a.status) {
@@ -516,6 +519,31 @@ bool hidden_tc_applicable(bool update, int n_rows, int rdim, int hdim, int k_out
     return true;
 }
 
+// Expanded rows of the current position for `layers` stacked caches in one launch.
+int launch_row_update(void* expanded_cache, const void* operand_cache, const void* anchor_weight,
+                      const void* partner_weight, const void* first_bias, const int64_t* position,
+                      int layers, int n_seq, int max_t, int rdim, int hdim, int dtype, int32_t* status,
+                      void* stream) {
+    RowUpdateArgs u{};
+    u.expanded_cache = expanded_cache; u.operand_cache = operand_cache; u.first_bias = first_bias;
+    u.position = position; u.status = status; u.n_seq = n_seq; u.max_t = max_t; u.rdim = rdim;
+    u.hdim = hdim; u.dtype = dtype;
+    u.seq_groups = (n_seq + kUpdMaxSeq - 1) / kUpdMaxSeq;
+    CUtensorMap ma, mp;
+    if (!make_map(&ma, anchor_weight, layers * hdim, rdim, rdim, kTcBN, dtype) ||
+        !make_map(&mp, partner_weight, layers * hdim, rdim, rdim, kTcBN, dtype)) {
+        set_error("relation_hidden: cuTensorMapEncodeTiled failed");
+        return RLM_ERR_LAUNCH;
+    }
+    auto kernel = expanded_row_update_kernel;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    dim3 grid(hdim / kTcBN, 2, layers * u.seq_groups);
+    launch_kernel(kernel, grid, dim3(kUpdThreads), update_smem_bytes(rdim, n_seq), stream, ma, mp, u);
+    count_launch();
+    return check_launch("expanded_row_update_kernel");
+}
+
 int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cache,
                      const int32_t* anchor_index, const int32_t* partner_index,
                      const void* anchor_weight, const void* partner_weight, const void* product_weight,
@@ -524,23 +552,8 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
                      int out_dtype, int32_t* status, void* stream) {
     const uint32_t fmt = dtype == RLM_BF16 ? 1u : 0u;
     if (update) {
-        RowUpdateArgs u{};
-        u.expanded_cache = expanded_cache; u.operand_cache = operand_cache; u.first_bias = first_bias;
-        u.position = position; u.status = status; u.n_seq = n_seq; u.max_t = max_t; u.rdim = rdim;
-        u.hdim = hdim; u.dtype = dtype;
-        CUtensorMap ma, mp;
-        if (!make_map(&ma, anchor_weight, hdim, rdim, rdim, kTcBN, dtype) ||
-            !make_map(&mp, partner_weight, hdim, rdim, rdim, kTcBN, dtype)) {
-            set_error("relation_hidden: cuTensorMapEncodeTiled failed");
-            return RLM_ERR_LAUNCH;
-        }
-        auto kernel = expanded_row_update_kernel;
-        int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
-        if (rc != RLM_OK) return rc;
-        dim3 grid(hdim / kTcBN, 2, (n_seq + kUpdMaxSeq - 1) / kUpdMaxSeq);
-        launch_kernel(kernel, dim3(grid), dim3(kUpdThreads), update_smem_bytes(rdim, n_seq), stream, ma, mp, u);
-        count_launch();
-        rc = check_launch("expanded_row_update_kernel");
+        int rc = launch_row_update(expanded_cache, operand_cache, anchor_weight, partner_weight, first_bias,
+                                   position, 1, n_seq, max_t, rdim, hdim, dtype, status, stream);
         if (rc != RLM_OK) return rc;
     }
     HiddenTcArgs a{};
@@ -576,6 +589,35 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
 }
 
 }  // namespace rlm
+
+extern "C" int rlm_expanded_cache_append(void* expanded_cache, const void* operand_cache,
+                                         const void* anchor_weight, const void* partner_weight,
+                                         const void* first_bias, const int64_t* position, int layers,
+                                         int batch, int max_t, int relation_dim, int hidden_dim,
+                                         int dtype, int32_t* status, void* stream) {
+    using namespace rlm;
+    if (layers == 0 || batch == 0) return RLM_OK;
+    if (!expanded_cache || !operand_cache || !anchor_weight || !partner_weight || !first_bias || !position) {
+        set_error("expanded_cache_append: NULL pointer");
+        return RLM_ERR_NULL;
+    }
+    if (layers < 0 || batch < 0 || max_t < 1 || relation_dim < kBK || relation_dim % kBK != 0 ||
+        hidden_dim < 128 || hidden_dim % 128 != 0) {
+        set_error("expanded_cache_append: need relation_dim a multiple of 64 and hidden_dim a multiple of 128");
+        return RLM_ERR_SHAPE;
+    }
+    if (dtype != RLM_BF16 && dtype != RLM_F16) {
+        set_error("expanded_cache_append: caches and weights must be bfloat16 or float16");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(expanded_cache) || !aligned16(operand_cache) || !aligned16(anchor_weight) ||
+        !aligned16(partner_weight)) {
+        set_error("expanded_cache_append: tensors must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    return launch_row_update(expanded_cache, operand_cache, anchor_weight, partner_weight, first_bias, position,
+                             layers, batch, max_t, relation_dim, hidden_dim, dtype, status, stream);
+}
 
 #ifdef RLM_TRACE
 extern "C" int rlm_debug_span_tc(unsigned long long* host) {

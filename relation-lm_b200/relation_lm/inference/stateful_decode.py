@@ -24,7 +24,8 @@ from torch import Tensor
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import decode_embed, norm_projection
-from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update,
+from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
+                                                 relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
@@ -64,6 +65,8 @@ class StatefulDecoder:
         # The single-launch tail (second MLP layer + norm-reduce + residual) is optional: at
         # decode batch sizes its one-CTA finalisation costs more than the launch it saves.
         self.fused_tail = fused_tail and self.fused and 128 % cfg.k_max == 0 and cfg.k_max <= 32
+        # One tensor-core launch expands the position's operand rows of all layers (shapes permitting).
+        self.stacked_expand = self.fused and R % 64 == 0 and H % 128 == 0
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.head_weight = torch.cat((self.w["token_embedding"], self.w["boundary_w"]), 0).contiguous()
@@ -146,6 +149,10 @@ class StatefulDecoder:
         sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
                             self.partner_anchor_cache, *self.router_caches, *self.router_stats,
                             w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+        if self.stacked_expand:
+            # every layer's operand row of this position is known: expand them all at once
+            expanded_cache_append(self.expanded_cache, self.operand_cache, w["anchor_weight"],
+                                  w["partner_weight"], w["first_bias"], pos)
         if keep_selection:
             self.last_selection = []
         K = cfg.k_max
@@ -157,10 +164,14 @@ class StatefulDecoder:
                 self.partner_anchor_cache[l], self.partner_keys[l], self.router_stats[2][l],
                 self.router_stats[3][l], w["partner_gamma"][l], w["partner_bias"][l], pos,
                 cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
-            relation_hidden_cache_update_out(
-                self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
-                w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
-                w["first_bias"][l], pos)
+            if self.stacked_expand:
+                relation_hidden_cached_out(self.relation_hidden, self.expanded_cache[l], self.operand_cache[l],
+                                           anchor, partner, w["product_weight"][l])
+            else:
+                relation_hidden_cache_update_out(
+                    self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
+                    w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
+                    w["first_bias"][l], pos)
             if self.fused_tail:
                 relation_tail(self.relation_hidden, w["w2"][l], w["b2"][l], partner_score,
                               w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,

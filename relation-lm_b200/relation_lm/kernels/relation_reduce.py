@@ -103,6 +103,81 @@ def _(expanded_cache, operand_cache, anchor_index, partner_index, product_weight
         (operand_cache.size(0), partner_index.size(1), product_weight.size(0)), dtype=torch.float32)
 
 
+@torch.library.custom_op("relation_lm::relation_hidden_cached_out", mutates_args=("out",),
+                         device_types="cuda")
+def relation_hidden_cached_out(
+    out: Tensor,
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    product_weight: Tensor,
+) -> None:
+    """``relation_hidden_cached`` writing into a caller-owned ``out [B, K, H]`` of any float dtype
+    (extension: a 16-bit ``out`` feeds the second MLP layer without a cast)."""
+    device = _abi.require_cuda_contiguous(
+        out=out, expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, product_weight=product_weight)
+    batch, max_t, rdim = operand_cache.shape
+    hdim, k_out = product_weight.size(0), partner_index.size(1)
+    _check_indices(anchor_index, partner_index, batch)
+    if expanded_cache.shape != (batch, max_t, 2 * hdim) or product_weight.size(1) != rdim \
+            or out.shape != (batch, k_out, hdim):
+        raise ValueError("expected expanded_cache [B, T, 2H], product_weight [H, R] and out [B, K, H]")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cached(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(product_weight), None, _abi.ptr(out), batch, batch,
+            max_t, rdim, hdim, k_out, _abi.same_dtype("cache", expanded_cache, operand_cache),
+            _abi.code(product_weight), _abi.code(out), _abi.ptr(_abi.status_tensor(device)),
+            _abi.stream_ptr(device)))
+
+
+@relation_hidden_cached_out.register_fake
+def _(out, expanded_cache, operand_cache, anchor_index, partner_index, product_weight):
+    return None
+
+
+@torch.library.custom_op("relation_lm::expanded_cache_append", mutates_args=("expanded_cache",),
+                         device_types="cuda")
+def expanded_cache_append(
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_weight: Tensor,
+    partner_weight: Tensor,
+    first_bias: Tensor,
+    position: Tensor,
+) -> None:
+    """Expanded-cache rows of the current position for all layers of a stack in one launch
+    (extension, tensor cores): ``expanded[l, :, t] = [W_a[l] o + b_1[l], W_p[l] o]`` with
+    ``o = operand_cache[l, :, t]``.  Stacked 16-bit tensors: caches ``[L, B, T, .]``, weights
+    ``[L, H, R]``, bias ``[L, H]``.  The per-layer kernels then use ``relation_hidden_cached``."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_weight=anchor_weight,
+        partner_weight=partner_weight, first_bias=first_bias)
+    _abi.require_position(position, device)
+    if operand_cache.dim() != 4 or expanded_cache.dim() != 4 or anchor_weight.dim() != 3:
+        raise ValueError("expected stacked tensors: caches [L, B, T, .], weights [L, H, R], bias [L, H]")
+    layers, batch, max_t, rdim = operand_cache.shape
+    hdim = anchor_weight.size(1)
+    if expanded_cache.shape != (layers, batch, max_t, 2 * hdim) or anchor_weight.shape != (layers, hdim, rdim) \
+            or partner_weight.shape != anchor_weight.shape or first_bias.shape != (layers, hdim):
+        raise ValueError("expected expanded_cache [L, B, T, 2H], weights [L, H, R] and first_bias [L, H]")
+    dtype = _abi.same_dtype("cache", expanded_cache, operand_cache)
+    if len({anchor_weight.dtype, partner_weight.dtype, first_bias.dtype, expanded_cache.dtype}) != 1:
+        raise ValueError("caches, weights and bias must share one 16-bit dtype")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_expanded_cache_append(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_weight),
+            _abi.ptr(partner_weight), _abi.ptr(first_bias), _abi.ptr(position), layers, batch, max_t,
+            rdim, hdim, dtype, _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@expanded_cache_append.register_fake
+def _(expanded_cache, operand_cache, anchor_weight, partner_weight, first_bias, position):
+    return None
+
+
 @torch.library.custom_op("relation_lm::relation_hidden_cache_update",
                          mutates_args=("expanded_cache",), device_types="cuda")
 def relation_hidden_cache_update(

@@ -84,3 +84,32 @@ def test_same_results_as_the_small_launch_form():
     small = torch.cat(parts)
     assert torch.allclose(big, small, atol=1e-2, rtol=1e-2), (big - small).abs().max()
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("layers,B,H,R", [(3, 8, 256, 128), (2, 70, 384, 64), (1, 1, 128, 128)])
+def test_stacked_expanded_cache_append(layers, B, H, R, dtype):
+    """All layers' expanded rows of one position in one launch equal the per-layer update of
+    the oracle; every other row of the cache stays untouched."""
+    from relation_lm.kernels.relation_reduce import expanded_cache_append
+
+    T, t = 40, 23
+    g = torch.Generator().manual_seed(9300 + layers + B)
+    operand = torch.randn(layers, B, T, R, generator=g).to(dtype)
+    expanded = (torch.randn(layers, B, T, 2 * H, generator=g) * 0.3).to(dtype)
+    wa, wp = [(torch.randn(layers, H, R, generator=g) * 0.05).to(dtype) for _ in range(2)]
+    bias = (torch.randn(layers, H, generator=g) * 0.1).to(dtype)
+    cache = expanded.cuda().clone()
+    expanded_cache_append(cache, operand.cuda(), wa.cuda(), wp.cuda(), bias.cuda(), position_tensor(t))
+    got = cache.cpu()
+    anchor = torch.zeros(B, dtype=torch.int32)
+    partner = torch.zeros(B, 1, dtype=torch.int32)
+    for l in range(layers):
+        wm = torch.zeros(H, R).to(dtype)
+        _, want = oracle.relation_hidden(expanded[l], operand[l], anchor, partner, wm, wa[l], wp[l], bias[l],
+                                         position=t)
+        assert torch.allclose(got[l].float(), want.float(), atol=1e-2, rtol=1e-2), (l, (got[l].float() - want.float()).abs().max())
+    untouched = torch.ones(T, dtype=torch.bool)
+    untouched[t] = False
+    assert torch.equal(got[:, :, untouched], expanded[:, :, untouched])
+    assert_status_clear()
