@@ -218,13 +218,14 @@ def kernel_table(dec, graph_iters: int = 20):
     """Average launch duration of each library kernel on the decoder's own state, captured in
     CUDA graphs (one launch per layer per graph, so consecutive launches touch different
     caches), with the algorithmic bytes of SURVEY's per-row formulas."""
-    from relation_lm.kernels.packed_projection import norm_projection
-    from relation_lm.kernels.relation_reduce import (relation_hidden_cache_update_out,
-                                                     relation_norm_reduce_residual)
+    from relation_lm.kernels.packed_projection import packed_projection
+    from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update_out,
+                                                     relation_hidden_cached_out, relation_norm_reduce_residual)
     from relation_lm.kernels.relation_select import relation_select_packed
     from relation_lm.kernels.router_cache import sparse_cache_append
 
     cfg, w, B = dec.config, dec.w, dec.batch
+    stacked = getattr(dec, "stacked_expand", False)
     L, K, H, R, d = cfg.layers, cfg.k_max, cfg.hidden_dim, cfg.relation_dim, cfg.d_model
     dev = dec.device
     e = dec.anchor_keys.element_size()
@@ -246,16 +247,26 @@ def kernel_table(dec, graph_iters: int = 20):
                                w["partner_bias"][l], pos, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
 
     def hidden(l):
-        relation_hidden_cache_update_out(hidden_out, dec.expanded_cache[l], dec.operand_cache[l], anchor,
-                                         partner, w["anchor_weight"][l], w["partner_weight"][l],
-                                         w["product_weight"][l], w["first_bias"][l], pos)
+        if stacked:
+            relation_hidden_cached_out(hidden_out, dec.expanded_cache[l], dec.operand_cache[l], anchor,
+                                       partner, w["product_weight"][l])
+        else:
+            relation_hidden_cache_update_out(hidden_out, dec.expanded_cache[l], dec.operand_cache[l], anchor,
+                                             partner, w["anchor_weight"][l], w["partner_weight"][l],
+                                             w["product_weight"][l], w["first_bias"][l], pos)
+
+    def expand(_):
+        expanded_cache_append(dec.expanded_cache, dec.operand_cache, w["anchor_weight"], w["partner_weight"],
+                              w["first_bias"], pos)
 
     def reduce(l):
         relation_norm_reduce_residual(raw[l], scores, w["relation_norm_w"][l], w["relation_norm_b"][l], pos,
                                       cfg.norm_eps, residual, w["mix"][l])
 
+    normalized = torch.randn(B, d, device=dev).to(dec.dtype)
+
     def query(l):
-        norm_projection(residual, w["input_norm_w"][l], w["input_norm_b"][l], w["w_query"][l], cfg.norm_eps)
+        packed_projection(normalized, w["w_query"][l])
 
     def append(_):
         sparse_cache_append(packed, dec.anchor_keys, dec.partner_keys, dec.operand_cache,
@@ -266,17 +277,22 @@ def kernel_table(dec, graph_iters: int = 20):
     nb = cfg.max_context // cfg.block_size
     bytes_per_launch = {
         "relation_select_kernel": B * (e * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K),
-        "relation_hidden_kernel<update>": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + e * K * H) + e * 3 * H * R + B * e * (R + 2 * H),
+        "relation_hidden_kernel": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + e * K * H) + e * H * R
+                                  + (0 if stacked else e * 2 * H * R + B * e * (R + 2 * H)),
+        "expanded_row_update_kernel(all layers)": L * (e * 2 * H * R + B * e * (R + 2 * H)),
         "relation_norm_reduce_kernel": B * (e * K * d + 4 * K + 4 * d + 8 * d) + 4 * 3 * d,
-        "norm_projection_kernel(query)": B * (4 * d + e * 256) + e * 256 * d + 8 * d,
+        "packed_projection_kernel(query)": e * (B * d + 256 * d + B * 256),
         "router_cache_update_kernel(all layers)": L * B * (e * 64 * (2 + 4 + 4 + 2 * cfg.block_size + 4) + 2 * 64 * 4 + 2 * e * (256 + R)),
     }
     table = {}
     for name, fn, per_graph in (("relation_select_kernel", select, L),
-                                ("relation_hidden_kernel<update>", hidden, L),
+                                ("relation_hidden_kernel", hidden, L),
                                 ("relation_norm_reduce_kernel", reduce, L),
-                                ("norm_projection_kernel(query)", query, L),
-                                ("router_cache_update_kernel(all layers)", append, 1)):
+                                ("packed_projection_kernel(query)", query, L),
+                                ("router_cache_update_kernel(all layers)", append, 1),
+                                ("expanded_row_update_kernel(all layers)", expand, 1)):
+        if name.startswith("expanded_row_update") and not stacked:
+            continue
         for l in range(per_graph):
             fn(l)
         torch.cuda.synchronize()

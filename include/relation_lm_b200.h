@@ -207,11 +207,15 @@ int rlm_relation_hidden_cache_update(
  *   *position.  residual (optional, [N,D] f32, updated in place): residual += (*mix) * context,
  *   the `hidden + sigmoid(mix_logit) * context` of the reference's relation layer
  *   (src/relation_lm/models/stacked_relation.py:124) with mix a device fp32 scalar.
+ *   next_normalized (optional, with residual; [N,D] bfloat16 / float16 = next_dtype): LayerNorm of the
+ *   updated residual row with next_norm_weight / next_norm_bias [D] f32 and next_norm_eps, i.e. the
+ *   normalised input of the next layer's query projection (or of the output heads).
  */
 int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
-    float* residual, const float* mix,
+    float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
+    float next_norm_eps, void* next_normalized, int next_dtype,
     int n_rows, int k_out, int dim, int raw_dtype, int param_dtype,
     int32_t* status, void* stream);
 
@@ -370,12 +374,17 @@ int rlm_relation_tail_static(const void* relation_hidden, const void* second_wei
  * out[b] = (token_table[tokens[b]] + boundary_table[boundaries[b]]) * scale + position_table[*position]
  *   tokens, boundaries [B] int64; tables [V, d] / [Vb, d] table_dtype; position_table [T, d] f32;
  *   out [B, d] f32.  Ids outside the tables set RLM_DEV_POSITION and leave the row unwritten.
+ *   norm1_out / norm2_out (optional, [B, d] bfloat16 / float16 = norm_out_dtype): LayerNorm of the
+ *   embedded row with norm{1,2}_weight / norm{1,2}_bias [d] f32 and norm_eps — the normalised inputs of
+ *   the packed projection (memory norm) and of the first layer's query projection (input norm).
  */
 int rlm_decode_embed(const int64_t* tokens, const int64_t* boundaries, const void* token_table,
                      const void* boundary_table, const float* position_table,
                      const int64_t* position, float scale, float* out, int batch, int d_model,
-                     int vocab, int boundary_vocab, int max_t, int table_dtype, int32_t* status,
-                     void* stream);
+                     int vocab, int boundary_vocab, int max_t, int table_dtype,
+                     const float* norm1_weight, const float* norm1_bias, void* norm1_out,
+                     const float* norm2_weight, const float* norm2_bias, void* norm2_out,
+                     float norm_eps, int norm_out_dtype, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -406,6 +406,11 @@ struct NormArgs {
     float* out;               // context [N, D], or NULL when only the residual is wanted
     float* residual;          // optional [N, D] fp32: residual += (*mix) * context
     const float* mix;
+    const float* next_w;      // optional: LayerNorm of the updated residual row, written as 16-bit
+    const float* next_b;      //   values to next_out [N, D] (the next layer's normalised input)
+    void* next_out;
+    float next_eps;
+    int next_dtype;
     int32_t* status;
     float eps;
     int n_rows, k_out, dim, raw_dtype, param_dtype;
@@ -585,9 +590,12 @@ __global__ void __launch_bounds__(kNormThreads, 2) relation_norm_reduce_vec_kern
         }
     __syncthreads();
     const float mix = a.residual ? *a.mix : 0.0f;
-    for (int c = 4 * tid; c < D; c += 4 * kNormThreads) {
+    const int c = 4 * tid;                 // dim <= 1024: every thread owns at most four columns
+    const bool live = c < D;
+    float updated[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
         float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        const int used = K < kNormWarps ? K : kNormWarps;      // warps beyond K hold zeros they never wrote
+        const int used = K < kNormWarps ? K : kNormWarps;      // warps beyond K hold zeros
 #pragma unroll
         for (int w = 0; w < kNormWarps; ++w) {
             if (w >= used) break;
@@ -601,7 +609,14 @@ __global__ void __launch_bounds__(kNormThreads, 2) relation_norm_reduce_vec_kern
             r.x = fmaf(mix, total.x, r.x); r.y = fmaf(mix, total.y, r.y);
             r.z = fmaf(mix, total.z, r.z); r.w = fmaf(mix, total.w, r.w);
             *reinterpret_cast<float4*>(a.residual + at) = r;
+            updated[0] = r.x; updated[1] = r.y; updated[2] = r.z; updated[3] = r.w;
         }
+    }
+    if (a.next_out) {
+        __shared__ float scratch[18];
+        NormTarget t0{a.next_w, a.next_b, static_cast<uint16_t*>(a.next_out) + static_cast<size_t>(row) * D};
+        NormTarget t1{nullptr, nullptr, nullptr};
+        block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, a.next_dtype, scratch);
     }
 }
 
@@ -642,7 +657,8 @@ extern "C" int rlm_relation_hidden_cache_update(
 extern "C" int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
-    float* residual, const float* mix, int n_rows,
+    float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
+    float next_norm_eps, void* next_normalized, int next_dtype, int n_rows,
     int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
     using namespace rlm;
     if (n_rows == 0) return RLM_OK;
@@ -663,11 +679,22 @@ extern "C" int rlm_relation_norm_reduce(
     a.raw = raw; a.scores = partner_scores; a.weight = norm_weight; a.bias = norm_bias;
     a.position = position; a.row_position = row_position; a.out = out; a.status = status;
     a.residual = residual; a.mix = mix;
+    a.next_w = next_norm_weight; a.next_b = next_norm_bias; a.next_out = next_normalized;
+    a.next_eps = next_norm_eps; a.next_dtype = next_dtype;
     a.eps = norm_eps; a.n_rows = n_rows; a.k_out = k_out; a.dim = dim;
     a.raw_dtype = raw_dtype; a.param_dtype = param_dtype;
     int smem_bytes = kNormWarps * dim * 4;
     const bool vec = dim % 8 == 0 && aligned16(raw) && aligned16(norm_weight) && aligned16(norm_bias) &&
                      (!out || aligned16(out)) && (!residual || aligned16(residual));
+    if (next_normalized) {
+        if (!residual || !next_norm_weight || !next_norm_bias || !vec || !aligned16(next_norm_weight) ||
+            !aligned16(next_norm_bias) || !aligned16(next_normalized) ||
+            (next_dtype != RLM_BF16 && next_dtype != RLM_F16)) {
+            set_error("relation_norm_reduce: the normalised output needs the residual form, dim a multiple "
+                      "of 8, 16-byte aligned tensors and a 16-bit dtype");
+            return RLM_ERR_UNSUPPORTED;
+        }
+    }
     if (vec && dim <= 512)
         launch_kernel(relation_norm_reduce_vec_kernel<2>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     else if (vec && dim <= 768)

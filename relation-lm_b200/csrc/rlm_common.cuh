@@ -319,4 +319,56 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// LayerNorm of one row spread over a 256-thread CTA as four consecutive columns per thread
+// (column c = 4 * threadIdx.x; `live` = c < dim), written as 16-bit values to up to two
+// outputs that share the statistics but have their own affine parameters.  `scratch` holds 18
+// floats of shared memory.  Two-pass statistics (mean, then biased variance) as layer_norm does.
+struct NormTarget {
+    const float* gamma;
+    const float* beta;
+    void* out_row;       // NULL: target unused
+};
+
+__device__ __forceinline__ float block_sum256(float v, float* scratch) {
+    v = warp_sum(v);
+    __syncthreads();                       // the previous use of scratch is over
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += scratch[w];
+    return total;
+}
+
+__device__ __forceinline__ void block_layer_norm4(const float (&v)[4], bool live, int c, int dim, float eps,
+                                                  const NormTarget& t0, const NormTarget& t1,
+                                                  int out_dtype, float* scratch) {
+    const float mean = block_sum256(live ? (v[0] + v[1]) + (v[2] + v[3]) : 0.0f, scratch) / static_cast<float>(dim);
+    float d[4], sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { d[i] = live ? v[i] - mean : 0.0f; sq = fmaf(d[i], d[i], sq); }
+    const float inv = rsqrtf(block_sum256(sq, scratch) / static_cast<float>(dim) + eps);
+    if (!live) return;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const NormTarget& t = k ? t1 : t0;
+        if (!t.out_row) continue;
+        const float4 g = *reinterpret_cast<const float4*>(t.gamma + c);
+        const float4 b = *reinterpret_cast<const float4*>(t.beta + c);
+        const float y0 = fmaf(d[0] * inv, g.x, b.x), y1 = fmaf(d[1] * inv, g.y, b.y);
+        const float y2 = fmaf(d[2] * inv, g.z, b.z), y3 = fmaf(d[3] * inv, g.w, b.w);
+        uint2 packed;
+        if (out_dtype == RLM_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        } else {
+            __half2 lo = __floats2half2_rn(y0, y1), hi = __floats2half2_rn(y2, y3);
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(t.out_row) + c) = packed;
+    }
+}
+
 }  // namespace rlm

@@ -23,10 +23,12 @@ from torch import Tensor
 
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
-from relation_lm.kernels.packed_projection import decode_embed, norm_projection
+from relation_lm.kernels.packed_projection import (decode_embed_norm, layer_norm_cast,
+                                                    packed_projection)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
                                                  relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
+                                                 relation_norm_reduce_residual_norm,
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
@@ -69,6 +71,8 @@ class StatefulDecoder:
         self.stacked_expand = self.fused and R % 64 == 0 and H % 128 == 0
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
+            self.normalized = zeros(B, cfg.d_model)             # LayerNorm'd input of the next projection
+            self.memory_normalized = zeros(B, cfg.d_model)      # memory-norm'd input of the packed projection
             self.head_weight = torch.cat((self.w["token_embedding"], self.w["boundary_w"]), 0).contiguous()
             pad = (-self.head_weight.size(0)) % 128        # whole 128-column tiles for the projection kernel
             if pad:
@@ -138,14 +142,18 @@ class StatefulDecoder:
 
     def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool):
         """The same step with the elementwise glue folded into the library's kernels:
-        5 launches per layer (norm + query projection, select, relation hidden, second MLP layer
-        GEMM, norm-reduce + residual), or 4 with the fused tail."""
+        5 launches per layer (query projection, select, relation hidden, second MLP layer GEMM,
+        norm-reduce + residual + next LayerNorm), or 4 with the fused tail.  Every LayerNorm is
+        computed by the kernel that produces its input (the embedding, the residual update) and
+        handed on as a 16-bit matrix, so the projections are plain tensor-core GEMMs."""
         cfg, w = self.config, self.w
         pos = self.position
         tokens, boundaries = tokens.contiguous(), boundaries.contiguous()
-        hidden = decode_embed(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
-                              w["position_embedding"], pos, self.input_scale)
-        packed = norm_projection(hidden, w["memory_norm_w"], w["memory_norm_b"], w["w_packed"], cfg.norm_eps)
+        hidden = decode_embed_norm(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
+                                   w["position_embedding"], pos, self.input_scale,
+                                   w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
+                                   w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
+        packed = packed_projection(self.memory_normalized, w["w_packed"])
         sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
                             self.partner_anchor_cache, *self.router_caches, *self.router_stats,
                             w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
@@ -157,7 +165,7 @@ class StatefulDecoder:
             self.last_selection = []
         K = cfg.k_max
         for l in range(cfg.layers):
-            q = norm_projection(hidden, w["input_norm_w"][l], w["input_norm_b"][l], w["w_query"][l], cfg.norm_eps)
+            q = packed_projection(self.normalized, w["w_query"][l])
             anchor, _, partner, partner_score = relation_select_packed(
                 q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
                 self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
@@ -172,17 +180,22 @@ class StatefulDecoder:
                     self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
                     w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
                     w["first_bias"][l], pos)
+            last = l + 1 == cfg.layers
+            next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]
+            next_b = w["final_norm_b"] if last else w["input_norm_b"][l + 1]
             if self.fused_tail:
                 relation_tail(self.relation_hidden, w["w2"][l], w["b2"][l], partner_score,
                               w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,
                               hidden, w["mix"][l])
+                layer_norm_cast(hidden, next_w, next_b, cfg.norm_eps, self.normalized)
             else:
                 raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])            # [B, K, d]
-                relation_norm_reduce_residual(raw, partner_score, w["relation_norm_w"][l],
-                                              w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l])
+                relation_norm_reduce_residual_norm(raw, partner_score, w["relation_norm_w"][l],
+                                                   w["relation_norm_b"][l], pos, cfg.norm_eps, hidden,
+                                                   w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized)
             if keep_selection:
                 self.last_selection.append((anchor, partner))
-        logits = norm_projection(hidden, w["final_norm_w"], w["final_norm_b"], self.head_weight, cfg.norm_eps)
+        logits = packed_projection(self.normalized, self.head_weight)
         token_logits = logits[:, :cfg.vocab_size]
         boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size] + w["boundary_b"]
         pos.add_(1)

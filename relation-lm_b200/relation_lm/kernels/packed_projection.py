@@ -41,6 +41,27 @@ def _(x, weight):
     return x.new_empty((x.size(0), weight.size(0)))
 
 
+@torch.library.custom_op("relation_lm::layer_norm_cast", mutates_args=("out",), device_types="cuda")
+def layer_norm_cast(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, norm_eps: float, out: Tensor) -> None:
+    """``out = layer_norm(x)`` for fp32 rows ``[rows, d]`` into a bfloat16 / float16 matrix."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(norm_weight=norm_weight, norm_bias=norm_bias, out=out)
+    if x.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_bias.dtype != torch.float32:
+        raise ValueError("layer_norm_cast takes fp32 rows and fp32 LayerNorm parameters")
+    if out.shape != x.shape or norm_weight.numel() != x.size(1):
+        raise ValueError("out must have the shape of x and the norm parameters [d]")
+    rows, d_in = x.shape
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_layer_norm_cast(
+            _abi.ptr(x), x.stride(0), _abi.ptr(norm_weight), _abi.ptr(norm_bias), float(norm_eps),
+            _abi.ptr(out), rows, d_in, _abi.code(out), _abi.stream_ptr(device)))
+
+
+@layer_norm_cast.register_fake
+def _(x, norm_weight, norm_bias, norm_eps, out):
+    return None
+
+
 @torch.library.custom_op("relation_lm::norm_projection", mutates_args=(), device_types="cuda")
 def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: Tensor,
                     norm_eps: float) -> Tensor:
@@ -56,10 +77,7 @@ def norm_projection(x: Tensor, norm_weight: Tensor, norm_bias: Tensor, weight: T
     if rows > _FUSED_NORM_ROWS:
         # normalise once into a 16-bit matrix, then the TMA-fed GEMM
         normalized = torch.empty((rows, d_in), device=device, dtype=weight.dtype)
-        with _abi.device_guard(device):
-            _abi.check(_abi.LIB.rlm_layer_norm_cast(
-                _abi.ptr(x), x.stride(0), _abi.ptr(norm_weight), _abi.ptr(norm_bias), float(norm_eps),
-                _abi.ptr(normalized), rows, d_in, _abi.code(normalized), _abi.stream_ptr(device)))
+        layer_norm_cast(x, norm_weight, norm_bias, norm_eps, normalized)
         return packed_projection(normalized, weight)
     out = torch.empty((rows, weight.size(0)), device=device, dtype=weight.dtype)
     with _abi.device_guard(device):
@@ -94,10 +112,55 @@ def decode_embed(tokens: Tensor, boundaries: Tensor, token_table: Tensor, bounda
             _abi.ptr(position_table), _abi.ptr(position), float(scale), _abi.ptr(out), batch, d_model,
             token_table.size(0), boundary_table.size(0), position_table.size(0),
             _abi.same_dtype("embedding table", token_table, boundary_table),
+            None, None, None, None, None, None, 0.0, 0,
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
     return out
 
 
 @decode_embed.register_fake
 def _(tokens, boundaries, token_table, boundary_table, position_table, position, scale):
+    return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)
+
+
+@torch.library.custom_op("relation_lm::decode_embed_norm", mutates_args=("normalized1", "normalized2"),
+                         device_types="cuda")
+def decode_embed_norm(tokens: Tensor, boundaries: Tensor, token_table: Tensor, boundary_table: Tensor,
+                      position_table: Tensor, position: Tensor, scale: float, norm1_weight: Tensor,
+                      norm1_bias: Tensor, normalized1: Tensor, norm2_weight: Tensor, norm2_bias: Tensor,
+                      normalized2: Tensor, norm_eps: float) -> Tensor:
+    """``decode_embed`` that also writes two LayerNorms of the embedded rows as 16-bit matrices
+    (``normalized1`` with the memory norm for the packed projection, ``normalized2`` with the first
+    layer's input norm for its query projection); returns the fp32 rows."""
+    device = _abi.require_cuda_contiguous(tokens=tokens, boundaries=boundaries,
+                                          token_table=token_table, boundary_table=boundary_table,
+                                          position_table=position_table, norm1_weight=norm1_weight,
+                                          norm1_bias=norm1_bias, normalized1=normalized1,
+                                          norm2_weight=norm2_weight, norm2_bias=norm2_bias,
+                                          normalized2=normalized2)
+    _abi.require_position(position, device)
+    if tokens.dtype != torch.int64 or boundaries.dtype != torch.int64 or position_table.dtype != torch.float32:
+        raise ValueError("ids must be int64 and the position table float32")
+    batch, d_model = tokens.numel(), token_table.size(1)
+    for t in (norm1_weight, norm1_bias, norm2_weight, norm2_bias):
+        if t.dtype != torch.float32 or t.numel() != d_model:
+            raise ValueError("LayerNorm parameters must be float32 [d_model]")
+    if normalized1.shape != (batch, d_model) or normalized2.shape != (batch, d_model) \
+            or normalized1.dtype != normalized2.dtype:
+        raise ValueError("normalized outputs must be [B, d_model] of one 16-bit dtype")
+    out = torch.empty((batch, d_model), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_decode_embed(
+            _abi.ptr(tokens), _abi.ptr(boundaries), _abi.ptr(token_table), _abi.ptr(boundary_table),
+            _abi.ptr(position_table), _abi.ptr(position), float(scale), _abi.ptr(out), batch, d_model,
+            token_table.size(0), boundary_table.size(0), position_table.size(0),
+            _abi.same_dtype("embedding table", token_table, boundary_table),
+            _abi.ptr(norm1_weight), _abi.ptr(norm1_bias), _abi.ptr(normalized1),
+            _abi.ptr(norm2_weight), _abi.ptr(norm2_bias), _abi.ptr(normalized2), float(norm_eps),
+            _abi.code(normalized1), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out
+
+
+@decode_embed_norm.register_fake
+def _(tokens, boundaries, token_table, boundary_table, position_table, position, scale, norm1_weight,
+      norm1_bias, normalized1, norm2_weight, norm2_bias, normalized2, norm_eps):
     return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)

@@ -11,7 +11,7 @@ import torch
 import torch.nn.functional as F
 
 import oracle
-from gpu_util import assert_status_clear
+from gpu_util import assert_status_clear, position_tensor
 
 pytestmark = pytest.mark.gpu
 
@@ -98,4 +98,29 @@ def test_fused_norm_projection_entry_point_with_many_rows(rows, d_in, n_out):
     normalized = F.layer_norm(x.cpu(), (d_in,), gamma.cpu(), beta.cpu(), 1e-5).bfloat16()
     want = oracle.linear(normalized, w.cpu())
     assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=1e-2), (out.float().cpu() - want).abs().max()
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,d", [(8, 512), (3, 768), (33, 1024)])
+def test_decode_embed_with_layer_norm_outputs(B, d, dtype):
+    """Embedding rows plus their two LayerNorms (memory norm, first input norm) in one launch."""
+    from relation_lm.kernels.packed_projection import decode_embed, decode_embed_norm
+
+    g = torch.Generator().manual_seed(4400 + B + d)
+    V, Vb, T, t = 1000, 64, 32, 17
+    tok_table, bnd_table = (torch.randn(V, d, generator=g) * 0.5).to(dtype), (torch.randn(Vb, d, generator=g) * 0.5).to(dtype)
+    pos_table = torch.randn(T, d, generator=g) * 0.1
+    tokens, bounds = torch.randint(0, V, (B,), generator=g), torch.randint(0, Vb, (B,), generator=g)
+    w1, b1 = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.1
+    w2, b2 = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.1
+    n1 = torch.empty(B, d, device="cuda", dtype=dtype)
+    n2 = torch.empty(B, d, device="cuda", dtype=dtype)
+    args = (tokens.cuda(), bounds.cuda(), tok_table.cuda(), bnd_table.cuda(), pos_table.cuda(), position_tensor(t), 1.7)
+    plain = decode_embed(*args)
+    got = decode_embed_norm(*args, w1.cuda(), b1.cuda(), n1, w2.cuda(), b2.cuda(), n2, 1e-5)
+    assert torch.equal(got, plain)                       # the fp32 rows do not depend on the extra outputs
+    x = plain.cpu()
+    assert torch.allclose(n1.float().cpu(), F.layer_norm(x, (d,), w1, b1, 1e-5), atol=2e-2, rtol=1e-2)
+    assert torch.allclose(n2.float().cpu(), F.layer_norm(x, (d,), w2, b2, 1e-5), atol=2e-2, rtol=1e-2)
     assert_status_clear()

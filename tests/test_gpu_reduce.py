@@ -192,3 +192,32 @@ def test_per_row_forms_match_the_oracle():
     want_ctx = oracle.relation_norm_reduce(raw, scores, gamma, beta, 0, 1e-5, row_pos=row_pos)
     assert torch.allclose(ctx.cpu(), want_ctx, atol=FP32_ATOL, rtol=1e-5)
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,K,D", [(8, 8, 512), (5, 5, 768), (40, 8, 1024), (3, 4, 256)])
+def test_norm_reduce_residual_with_next_layer_norm(B, K, D, dtype):
+    """Residual update and the LayerNorm of the updated rows (the next projection's input) in
+    the norm-reduce launch: residual within fp32 tolerance, normalised rows within one 16-bit ulp."""
+    from relation_lm.kernels.relation_reduce import relation_norm_reduce_residual_norm
+
+    g = torch.Generator().manual_seed(7700 + B + D)
+    raw = torch.randn(B, K, D, generator=g).to(dtype)
+    scores = torch.randn(B, K, generator=g)
+    scores[::2, -1] = -torch.inf
+    gamma, beta = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    next_w, next_b = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    hidden = torch.randn(B, D, generator=g) * 2
+    mix = torch.tensor(0.37)
+    t = 300
+    got_hidden = hidden.cuda().clone()
+    normalized = torch.empty(B, D, device="cuda", dtype=dtype)
+    relation_norm_reduce_residual_norm(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(), position_tensor(t),
+                                       1e-5, got_hidden, mix.cuda(), next_w.cuda(), next_b.cuda(), 1e-5,
+                                       normalized)
+    context = oracle.relation_norm_reduce(raw, scores, gamma, beta, t, 1e-5)
+    want_hidden = hidden + mix * context
+    assert torch.allclose(got_hidden.cpu(), want_hidden, atol=FP32_ATOL, rtol=1e-5)
+    want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
+    assert torch.allclose(normalized.float().cpu(), want_norm, atol=2e-2, rtol=1e-2)
+    assert_status_clear()
