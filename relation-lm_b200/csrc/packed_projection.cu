@@ -12,11 +12,15 @@
 // Replaces the F.linear of src/relation_lm/inference/packed_cache.py:52-57 of the reference
 // project (and serves the query-side router projections, which have the same shape).
 
-#include <cstdlib>
-
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
+#ifdef RLM_TRACE
+__device__ long long g_trace_gemm[64 * 16];
+#define RLM_G_PROBE(i, who) do { if (threadIdx.x == (who) && blockIdx.x + blockIdx.y * gridDim.x < 64) g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + (i)] = clock64(); } while (0)
+#else
+#define RLM_G_PROBE(i, who) do { } while (0)
+#endif
 namespace {
 
 constexpr int kGemmThreads = 128;
@@ -33,6 +37,7 @@ struct GemmArgs {
     int out_dtype;
     uint32_t idesc;
     uint32_t a_bytes;      // bytes one x tile load delivers (box rows x 128)
+    int issuers;           // MMA-issuing warps (1 or 2)
 };
 
 template <int BN>
@@ -44,8 +49,14 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
+    RLM_G_PROBE(0, 0);
     constexpr int kStages = stages_for(BN);
-    constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    // one or two warps issue MMAs (K-blocks dealt round-robin into accumulators of their own, summed by
+    // the epilogue): a single thread issues a tcgen05.mma every ~60 cycles, which bounds short
+    // K loops; tensor-memory columns = issuers * BN, at least 32
+    const int issuers = a.issuers;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < static_cast<uint32_t>(issuers * BN)) tmem_cols *= 2;
     constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = BN * kBK * 2;
     // the ring must start on a 1024-byte boundary for the 128-byte swizzle
     unsigned char* ring = reinterpret_cast<unsigned char*>(
@@ -62,47 +73,104 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-        for (int i = 0; i < 2 * kStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        for (int i = 0; i < 2 * kStages; ++i) mbar_init(bar0 + 8u * i, 1);
+        mbar_init(acc_full, static_cast<uint32_t>(issuers));
         fence_barrier_init();
         failed = 0;
     }
     if (warp == 1) {   // one warp owns the TMEM allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    griddep_sync();      // barriers and tensor memory are set up; x may come from the previous kernel
+    RLM_G_PROBE(1, 0);
+    griddep_sync();
+    RLM_G_PROBE(2, 0);      // barriers and tensor memory are set up; x may come from the previous kernel
 
-    if (tid == 0) {
-        // producer: fill the ring
-        for (int it = 0; it < k_iters; ++it) {
-            const int s = it % kStages;
-            if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
-            mbar_expect_tx(full(s), a.a_bytes + kBBytes);
-            tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, it * kBK, m0, full(s));
-            tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, it * kBK, n0, full(s));
+    if (warp == 0) {
+        // producer: the first round of the ring is requested by one lane per stage at once (the
+        // stages are free), later rounds by lane 0 as stages are released
+        if (lane < kStages && lane < k_iters) {
+            mbar_expect_tx(full(lane), a.a_bytes + kBBytes);
+            tma_load_2d(ring_addr + lane * (kABytes + kBBytes), &map_x, lane * kBK, m0, full(lane));
+            tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, lane * kBK, n0, full(lane));
         }
-    } else if (tid == 32) {
-        // tensor-core issue: four UMMA K-steps of 16 per stage
+        __syncwarp();
+        RLM_G_PROBE(3, 0);
+        if (lane == 0) {
+            for (int it = kStages; it < k_iters; ++it) {
+                const int s = it % kStages;
+                if (!mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
+                mbar_expect_tx(full(s), a.a_bytes + kBBytes);
+                tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, it * kBK, m0, full(s));
+                tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, it * kBK, n0, full(s));
+            }
+        }
+        __syncwarp();
+    } else if (warp <= issuers) {
+        const int me = warp - 1;                              // issuer index: K-blocks me, me + issuers, ...
+        const uint32_t my_acc = tmem_base + static_cast<uint32_t>(me * BN);
+        // tensor-core issue: four UMMA K-steps of 16 per stage.  The whole warp walks the loop so
+        // that addresses and descriptors stay warp-uniform; one lane issues the instructions.
         bool ok = true;
-        for (int it = 0; it < k_iters && ok; ++it) {
+#ifdef RLM_TRACE
+        long long wait_cycles = 0, issue_cycles = 0, mma_cycles = 0, commit_cycles = 0;
+#endif
+        for (int it = me; it < k_iters && ok; it += issuers) {
             const int s = it % kStages;
+#ifdef RLM_TRACE
+            const long long w0 = clock64();
+#endif
             ok = mbar_wait(full(s), (it / kStages) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+#ifdef RLM_TRACE
+            const long long w1 = clock64();
+            wait_cycles += w1 - w0;
+#endif
             if (!ok) break;
+            if (it == 0) RLM_G_PROBE(4, 32);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t da = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes));
             const uint64_t db = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes) + kABytes);
+            if (lane == 0) {
+#ifdef RLM_TRACE
+                const long long m0c = clock64();
+#endif
 #pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk)      // +32 bytes along K inside the swizzle atom
-                umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, a.idesc, (it > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(empty(s));                       // stage reusable once these MMAs retire
+                for (int kk = 0; kk < kBK / 16; ++kk)      // +32 bytes along K inside the swizzle atom
+                    umma_f16(my_acc, da + 2 * kk, db + 2 * kk, a.idesc, (it >= issuers || kk > 0) ? 1u : 0u);
+#ifdef RLM_TRACE
+                const long long m1c = clock64();
+#endif
+                umma_commit(empty(s));                       // stage reusable once these MMAs retire
+#ifdef RLM_TRACE
+                const long long m2c = clock64();
+                mma_cycles += m1c - m0c;
+                commit_cycles += m2c - m1c;
+#endif
+            }
+            __syncwarp();
+#ifdef RLM_TRACE
+            issue_cycles += clock64() - w1;
+#endif
         }
-        if (!ok) failed = 1;
-        umma_commit(acc_full);                           // accumulator complete (or abandoned)
+#ifdef RLM_TRACE
+        if (tid == 32 && blockIdx.x + blockIdx.y * gridDim.x < 64) {
+            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 9] = wait_cycles;
+            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 10] = issue_cycles;
+            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 11] = mma_cycles;
+            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 12] = commit_cycles;
+        }
+#endif
+        if (lane == 0) {
+            if (!ok) failed = 1;
+            umma_commit(acc_full);                           // accumulator complete (or abandoned)
+        }
+        RLM_G_PROBE(5, 32);
     }
     __syncwarp();
 
@@ -110,6 +178,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     bool ready = mbar_wait(acc_full, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+    RLM_G_PROBE(6, 0);
     if (!__syncthreads_or(!ready)) {
         const int row = m0 + warp * 32 + lane;
 #pragma unroll
@@ -117,6 +186,13 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
             uint32_t v[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int extra = 1; extra < issuers; ++extra) {
+                uint32_t v2[16];
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + extra * BN + c, v2);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+            }
             if (row < a.m) {
                 const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
                 if (a.out_dtype == RLM_F32) {
@@ -147,11 +223,13 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     } else if (tid == 0 && a.status) {
         atomicOr(a.status, RLM_DEV_TIMEOUT);
     }
+    RLM_G_PROBE(7, 0);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+                     ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    RLM_G_PROBE(8, 32);
 }
 
 // ------------------------------------------------------------------ LayerNorm + projection
@@ -507,9 +585,6 @@ extern "C" int rlm_norm_projection(const float* x, int64_t x_row_stride, const f
     int bn = 128;
     if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
     if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
-#ifdef RLM_TUNE
-    if (const char* forced = getenv("RLM_GEMM_BN")) { int v = atoi(forced); if (v == 32 || (v == 64 && n_out % 64 == 0) || (v == 128 && n_out % 128 == 0)) bn = v; }
-#endif
     CUtensorMap mw;
     if (!make_map(&mw, weight, n_out, d_in, d_in, bn, weight_dtype)) {
         set_error("norm_projection: cuTensorMapEncodeTiled failed");
@@ -591,9 +666,6 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     int bn = 128;
     if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
     if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
-#ifdef RLM_TUNE
-    if (const char* forced = getenv("RLM_GEMM_BN")) { int v = atoi(forced); if (v == 32 || (v == 64 && n_out % 64 == 0) || (v == 128 && n_out % 128 == 0)) bn = v; }
-#endif
     // x tile: the box holds only the rows that exist (a multiple of 8, at most 128); the MMA
     // reads 128 rows of the stage, the rest is never stored
     const int box_rows = rows >= kBM ? kBM : ((rows + 7) / 8) * 8;
@@ -606,6 +678,10 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     GemmArgs a{};
     a.out = out; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
     a.a_bytes = static_cast<uint32_t>(box_rows) * kBK * 2;
+    // a single thread issues one tcgen05.mma per ~60 cycles, more than a 128-wide MMA runs: two warps issue
+    const int k_blocks = (d_in + kBK - 1) / kBK;
+    // (with an even ring depth each issuer owns its own stages, so every stage barrier is consumed in order)
+    a.issuers = (k_blocks >= 2 && stages_for(bn) % 2 == 0) ? 2 : 1;
     const uint32_t fmt = in_dtype == RLM_BF16 ? 1u : 0u;
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
               (static_cast<uint32_t>(kBM >> 4) << 24);
@@ -613,3 +689,9 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     if (bn == 64) return launch_gemm<64>(mx, mw, a, stream);
     return launch_gemm<128>(mx, mw, a, stream);
 }
+
+#ifdef RLM_TRACE
+extern "C" int rlm_debug_trace_gemm(long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_gemm, sizeof(long long) * 64 * 16));
+}
+#endif

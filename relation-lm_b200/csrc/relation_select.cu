@@ -169,7 +169,10 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
             float sc = valid[u] ? __fmul_rn(acc[u], 0.125f) : kNegInf;
             if (cand && j == 0 && r[u] < n_rows) cand[slot0 + r[u]] = sc;
             uint32_t key = float_key(sc);
-            if (valid[u] && (key > my_key || my_pos == 0x7fffffff)) { my_key = key; my_pos = pos[u]; }
+            if (valid[u] && (key > my_key || my_pos == 0x7fffffff || (key == my_key && pos[u] < my_pos))) {
+                my_key = key;
+                my_pos = pos[u];
+            }
         }
     }
     warp_argmax_key(my_key, my_pos);
