@@ -116,3 +116,35 @@ def test_fused_tail_decode_tracks_default_path():
         cos = torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0)
         assert cos > 0.995, (t, float(cos))
     assert_status_clear()
+
+
+def test_programmatic_launch_does_not_change_results():
+    """The fused bf16 step with and without programmatic dependent launch (kernels starting
+    their set-up and the selector its cache prefetch while the previous kernel still runs):
+    bit-identical logits, selections and state, eagerly and through the captured graph."""
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=9)
+    B, steps = 4, 48
+    g = torch.Generator().manual_seed(21)
+    tokens = torch.randint(0, 500, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, 16, (B, steps), generator=g).cuda()
+    plain = StatefulDecoder(model, B, "cuda", torch.bfloat16, programmatic_launch=False)
+    early = StatefulDecoder(model, B, "cuda", torch.bfloat16, programmatic_launch=True)
+    assert plain.fused and early.fused
+    for t in range(steps // 2):
+        a = plain.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        b = early.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), t
+        for (pa, pp), (ea, ep) in zip(plain.last_selection, early.last_selection):
+            assert torch.equal(pa, ea) and torch.equal(pp, ep), t
+    early.capture()
+    for t in range(steps // 2, steps):
+        a = plain.step(tokens[:, t], bounds[:, t])
+        early.static_tokens.copy_(tokens[:, t])
+        early.static_boundaries.copy_(bounds[:, t])
+        early.replay()
+        assert torch.equal(a[0], early.static_token_logits), t
+    for name in ("anchor_keys", "partner_keys", "operand_cache", "partner_anchor_cache", "expanded_cache"):
+        assert torch.equal(getattr(plain, name), getattr(early, name)), name
+    assert_status_clear()
