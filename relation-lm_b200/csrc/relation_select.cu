@@ -121,8 +121,11 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
 // The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand` the scores go to candidate slots
 // slot0 + r; in every case the warp's best (score, lowest position on ties) is folded into
 // (best_key, best_pos), identical in all lanes.
+// kU row groups of four rows are in flight per warp iteration.  `bs_shift` >= 0 says that the
+// block size is 1 << bs_shift (no division to find a remote row's block).
+template <int kU>
 __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
-                                        const int* sel, int bs, int first_valid, int pos0,
+                                        const int* sel, int bs, int bs_shift, int first_valid, int pos0,
                                         int exclude, const int* excl, int n_excl, const float* query,
                                         float* cand, int slot0, int wi, int nw, uint32_t& best_key,
                                         int& best_pos) {
@@ -134,18 +137,19 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
     for (int i = 0; i < 8; ++i) q[i] = query[8 * j + i];
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
-    // two independent row groups per iteration keep two fma chains in flight
-    for (int base = wi * 8; base < n_rows; base += 8 * nw) {
-        int r[2] = {base + sub, base + 4 + sub};
-        int pos[2];
-        bool valid[2];
-        float acc[2] = {0.0f, 0.0f};
-        float k[2][8];
+    for (int base = wi * 4 * kU; base < n_rows; base += 4 * kU * nw) {
+        int r[kU], pos[kU];
+        bool valid[kU];
+        float acc[kU];
+        float k[kU][8];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kU; ++u) {
+            r[u] = base + 4 * u + sub;
+            acc[u] = 0.0f;
             if (sel) {
-                int rank = r[u] / bs, o = r[u] - rank * bs;
-                bool in = r[u] < n_rows;
+                const int rank = bs_shift >= 0 ? r[u] >> bs_shift : r[u] / bs;
+                const int o = r[u] - rank * bs;
+                const bool in = r[u] < n_rows;
                 pos[u] = in ? sel[3 * rank] * bs + o : -1;
                 valid[u] = in && o < sel[3 * rank + 2];
             } else {
@@ -157,15 +161,14 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
             if (valid[u]) load8(rows + static_cast<size_t>(r[u]) * row_bytes, 8 * j, key_dtype, k[u]);
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < kU; ++u)
             if (valid[u]) acc[u] = seg8(k[u], q);
 #pragma unroll
-        for (int sft = 1; sft <= 4; sft <<= 1) {
-            acc[0] = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], sft));
-            acc[1] = __fadd_rn(acc[1], __shfl_xor_sync(0xffffffffu, acc[1], sft));
-        }
+        for (int sft = 1; sft <= 4; sft <<= 1)
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < kU; ++u) acc[u] = __fadd_rn(acc[u], __shfl_xor_sync(0xffffffffu, acc[u], sft));
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
             float sc = valid[u] ? __fmul_rn(acc[u], 0.125f) : kNegInf;
             if (cand && j == 0 && r[u] < n_rows) cand[slot0 + r[u]] = sc;
             uint32_t key = float_key(sc);
@@ -315,6 +318,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
     }
     RLM_PROBE(1);
     const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? 31 - __clz(bs) : -1;
     const int ks = a.key_dtype == RLM_F32 ? 4 : 2, ss = a.stats_dtype == RLM_F32 ? 4 : 2;
     const Plan& p = a.plan;
 
@@ -416,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
                          a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, kWarps / 2);
         else
-            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
+            score_rows<2>(smem + p.a_local, a.key_dtype, L, nullptr, bs, bs_shift, first_local, t - L + 1, -1, excl_s,
                        n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
@@ -440,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             RLM_PROBE(10);
             bk = 0;
             bp = 0x7fffffff;
-            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+            score_rows<2>(smem + p.remote, a.key_dtype, top * bs, sel, bs, bs_shift, 0, 0, -1, excl_s, n_excl, aq,
                        nullptr, 0, warp, kWarps, bk, bp);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             __syncthreads();
@@ -495,7 +499,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
         score_blocks(smem + p.p_mean, smem + p.p_std, a.stats_dtype, nb, n_complete, bs, t, ls,
                      a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, kWarps / 2);
     else
-        score_rows(smem + p.p_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
+        score_rows<2>(smem + p.p_local, a.key_dtype, L, nullptr, bs, bs_shift, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp);
     __syncthreads();
     RLM_PROBE(15);
@@ -517,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             return;
         }
         RLM_PROBE(19);
-        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+        score_rows<2>(smem + p.remote, a.key_dtype, top * bs, sel, bs, bs_shift, 0, 0, anchor_pos, excl_s, n_excl, pq,
                    cand, L, warp, kWarps, dk, dp);
         __syncthreads();
         RLM_PROBE(20);
@@ -650,17 +654,23 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
         int rank = 0;
         if (live) {
             const int home = c >> 2;                       // group of four that holds slot c
-            for (int g = part; g < n_groups; g += parts) {
-                float4 o = cand4[g];
-                if (g < home)                               // earlier slots win ties
-                    rank += (o.x >= mine) + (o.y >= mine) + (o.z >= mine) + (o.w >= mine);
-                else if (g > home)                          // later slots lose ties
-                    rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
-                else {
-                    const int m0 = g << 2;
-                    rank += (o.x > mine || (o.x == mine && m0 < c)) + (o.y > mine || (o.y == mine && m0 + 1 < c)) +
-                            (o.z > mine || (o.z == mine && m0 + 2 < c)) + (o.w > mine || (o.w == mine && m0 + 3 < c));
-                }
+            int g = part;
+#pragma unroll 4
+            for (; g < home; g += parts) {                  // earlier slots win ties
+                const float4 o = cand4[g];
+                rank += (o.x >= mine) + (o.y >= mine) + (o.z >= mine) + (o.w >= mine);
+            }
+            if (g == home) {
+                const float4 o = cand4[g];
+                const int m0 = g << 2;
+                rank += (o.x > mine || (o.x == mine && m0 < c)) + (o.y > mine || (o.y == mine && m0 + 1 < c)) +
+                        (o.z > mine || (o.z == mine && m0 + 2 < c)) + (o.w > mine || (o.w == mine && m0 + 3 < c));
+                g += parts;
+            }
+#pragma unroll 4
+            for (; g < n_groups; g += parts) {              // later slots lose ties
+                const float4 o = cand4[g];
+                rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
             }
         }
         for (int sft = 1; sft < parts; sft <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, sft);
@@ -668,7 +678,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             int pos;
             if (!(mine > kNegInf)) pos = t - L + 1;
             else if (c < L) pos = t - L + 1 + c;
-            else { int r = (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
+            else { int r = bs_shift >= 0 ? (c - L) >> bs_shift : (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
             a.out_partner[static_cast<size_t>(row) * K + rank] = pos;
             a.out_partner_score[static_cast<size_t>(row) * K + rank] = mine;
         }
