@@ -398,7 +398,7 @@ def run_ours(args) -> None:
 
     log(f"state allocated: {dec.state_bytes() / 1e9:.1f} GB")
     launches_before = _abi.launch_count()
-    dec.step(tokens[:, 0], bounds[:, 0])
+    dec.step_greedy(tokens[:, 0], bounds[:, 0])          # what the captured graph replays
     kernels_per_step = _abi.launch_count() - launches_before
     dec.reset()
     dec.capture()

@@ -244,10 +244,12 @@ int rlm_router_cache_prefill(
  *   x [rows, d_in] with a row stride in ELEMENTS (multiple of 8), weight [n_out, d_in]:
  *   bfloat16 or float16 (in_dtype); out [rows, n_out] contiguous, any rlm_dtype (out_dtype).
  *   d_in a multiple of 8, n_out a multiple of 32; fp32 operands return RLM_ERR_UNSUPPORTED.
+ *   bias (optional, [n_out] f32) is added to every row before the output is rounded, as F.linear
+ *   with a bias does (the boundary head of the output projection).
  */
-int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight, void* out,
-                          int rows, int d_in, int n_out, int in_dtype, int out_dtype,
-                          int32_t* status, void* stream);
+int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
+                          const float* bias, void* out, int rows, int d_in, int n_out, int in_dtype,
+                          int out_dtype, int32_t* status, void* stream);
 
 /*
  * LayerNorm fused into the projection, for decode batches (extension):
@@ -385,6 +387,15 @@ int rlm_decode_embed(const int64_t* tokens, const int64_t* boundaries, const voi
                      const float* norm1_weight, const float* norm1_bias, void* norm1_out,
                      const float* norm2_weight, const float* norm2_bias, void* norm2_out,
                      float norm_eps, int norm_out_dtype, int32_t* status, void* stream);
+
+/*
+ * Greedy next token (extension): next_token[b] = index of the largest of logits[b, 0:vocab]
+ * (ties to the lowest index), the `logits.argmax(-1)` that closes a greedy decode step; with
+ * `position` given the device position scalar is advanced by one in the same launch.
+ *   logits [rows, >= vocab] any rlm_dtype, row stride in ELEMENTS; next_token [rows] int64.
+ */
+int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token, int64_t* position,
+                     int rows, int vocab, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

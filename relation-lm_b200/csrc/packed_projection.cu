@@ -32,6 +32,7 @@ __host__ __device__ constexpr int stages_for(int bn) { return bn >= 128 ? 3 : 8;
 
 struct GemmArgs {
     void* out;
+    const float* bias;     // optional [n]: added to every row before the output is rounded
     int32_t* status;
     int m, n, k;
     int out_dtype;
@@ -192,6 +193,10 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+            }
+            if (a.bias) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + a.bias[n0 + c + i]);
             }
             if (row < a.m) {
                 const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
@@ -642,8 +647,8 @@ extern "C" int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const f
 }
 
 extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
-                                     void* out, int rows, int d_in, int n_out, int in_dtype,
-                                     int out_dtype, int32_t* status, void* stream) {
+                                     const float* bias, void* out, int rows, int d_in, int n_out,
+                                     int in_dtype, int out_dtype, int32_t* status, void* stream) {
     using namespace rlm;
     if (rows == 0) return RLM_OK;
     if (!x || !weight || !out) { set_error("packed_projection: NULL pointer"); return RLM_ERR_NULL; }
@@ -676,7 +681,7 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
         return RLM_ERR_LAUNCH;
     }
     GemmArgs a{};
-    a.out = out; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
+    a.out = out; a.bias = bias; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
     a.a_bytes = static_cast<uint32_t>(box_rows) * kBK * 2;
     // a single thread issues one tcgen05.mma per ~60 cycles, more than a 128-wide MMA runs: two warps issue
     const int k_blocks = (d_in + kBK - 1) / kBK;

@@ -23,7 +23,7 @@ from torch import Tensor
 
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
-from relation_lm.kernels.packed_projection import (decode_embed_norm, layer_norm_cast,
+from relation_lm.kernels.packed_projection import (decode_embed_norm, greedy_token, layer_norm_cast,
                                                     packed_projection)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
                                                  relation_hidden_cached_out,
@@ -77,6 +77,9 @@ class StatefulDecoder:
             pad = (-self.head_weight.size(0)) % 128        # whole 128-column tiles for the projection kernel
             if pad:
                 self.head_weight = torch.cat((self.head_weight, zeros(pad, cfg.d_model)), 0).contiguous()
+            # the boundary head's bias rides in the projection's epilogue (token columns: zero)
+            self.head_bias = torch.zeros(self.head_weight.size(0), device=self.device, dtype=torch.float32)
+            self.head_bias[cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size] = self.w["boundary_b"].float()
 
     # ------------------------------------------------------------------ state
     def reset(self) -> None:
@@ -102,6 +105,23 @@ class StatefulDecoder:
                 return self._step_fused(tokens, boundaries, keep_selection)
             finally:
                 _abi.set_programmatic_launch(previous)
+        return self._step_unfused(tokens, boundaries, keep_selection)
+
+    def step_greedy(self, tokens: Tensor, boundaries: Tensor) -> Tensor:
+        """One step followed by the greedy choice: returns the next token ids ``[B]`` (int64) and
+        advances the position.  On the fused path the arg-max and the position increment are one
+        launch of the library."""
+        if not self.fused:
+            token_logits, _ = self.step(tokens, boundaries)
+            return token_logits.argmax(-1)
+        previous = _abi.set_programmatic_launch(self.programmatic_launch)
+        try:
+            self._step_fused(tokens, boundaries, False, advance=False)
+            return greedy_token(self.last_logits, self.config.vocab_size, self.position)
+        finally:
+            _abi.set_programmatic_launch(previous)
+
+    def _step_unfused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool):
         cfg, w = self.config, self.w
         pos = self.position
         x = (F.embedding(tokens, w["token_embedding"]) + F.embedding(boundaries, w["boundary_embedding"])).float()
@@ -140,7 +160,7 @@ class StatefulDecoder:
         pos.add_(1)
         return token_logits, boundary_logits
 
-    def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool):
+    def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True):
         """The same step with the elementwise glue folded into the library's kernels:
         5 launches per layer (query projection, select, relation hidden, second MLP layer GEMM,
         norm-reduce + residual + next LayerNorm), or 4 with the fused tail.  Every LayerNorm is
@@ -195,10 +215,12 @@ class StatefulDecoder:
                                                    w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized)
             if keep_selection:
                 self.last_selection.append((anchor, partner))
-        logits = packed_projection(self.normalized, self.head_weight)
+        logits = packed_projection(self.normalized, self.head_weight, self.head_bias)
+        self.last_logits = logits                        # [B, padded vocab + boundary vocab]
         token_logits = logits[:, :cfg.vocab_size]
-        boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size] + w["boundary_b"]
-        pos.add_(1)
+        boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size]
+        if advance:
+            pos.add_(1)
         return token_logits, boundary_logits
 
     # ------------------------------------------------------------------ CUDA graph
@@ -213,13 +235,19 @@ class StatefulDecoder:
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):                                   # warm-up outside capture
-                self.step(self.static_tokens, self.static_boundaries)
+                self.step_greedy(self.static_tokens, self.static_boundaries)
                 self.position.fill_(saved)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                self.static_token_logits, self.static_boundary_logits = self.step(
-                    self.static_tokens, self.static_boundaries)
-                self.static_next = self.static_token_logits.argmax(-1)
+                if self.fused:
+                    self.static_next = self.step_greedy(self.static_tokens, self.static_boundaries)
+                    V, Vb = self.config.vocab_size, self.config.boundary_vocab_size
+                    self.static_token_logits = self.last_logits[:, :V]
+                    self.static_boundary_logits = self.last_logits[:, V:V + Vb]
+                else:
+                    self.static_token_logits, self.static_boundary_logits = self.step(
+                        self.static_tokens, self.static_boundaries)
+                    self.static_next = self.static_token_logits.argmax(-1)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         self.position.fill_(saved)
         self._graph = graph

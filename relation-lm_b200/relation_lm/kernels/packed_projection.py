@@ -17,8 +17,9 @@ _FUSED_NORM_ROWS = 16    # beyond this many rows normalising once beats normalis
 
 
 @torch.library.custom_op("relation_lm::packed_projection", mutates_args=(), device_types="cuda")
-def packed_projection(x: Tensor, weight: Tensor) -> Tensor:
-    """``x [rows, d] @ weight [n, d].T`` → ``[rows, n]`` in the operands' dtype (fp32 accumulate)."""
+def packed_projection(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
+    """``x [rows, d] @ weight [n, d].T (+ bias [n])`` → ``[rows, n]`` in the operands' dtype (fp32
+    accumulate; the optional fp32 bias is added before the result is rounded)."""
     device = _abi.require_cuda_rows(x=x)
     _abi.require_cuda_contiguous(weight=weight)
     if weight.device != device or weight.dim() != 2 or weight.size(1) != x.size(1):
@@ -27,17 +28,21 @@ def packed_projection(x: Tensor, weight: Tensor) -> Tensor:
         raise ValueError("packed_projection takes bfloat16 or float16 operands of one dtype")
     rows, d_in = x.shape
     n_out = weight.size(0)
+    if bias is not None:
+        _abi.require_cuda_contiguous(bias=bias)
+        if bias.dtype != torch.float32 or bias.numel() != n_out or bias.device != device:
+            raise ValueError("bias must be float32 [n_out] on the device of x")
     out = torch.empty((rows, n_out), device=device, dtype=x.dtype)
     with _abi.device_guard(device):
         _abi.check(_abi.LIB.rlm_packed_projection(
-            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(out), rows, d_in, n_out,
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(bias), _abi.ptr(out), rows, d_in, n_out,
             _abi.code(x), _abi.code(out), _abi.ptr(_abi.status_tensor(device)),
             _abi.stream_ptr(device)))
     return out
 
 
 @packed_projection.register_fake
-def _(x, weight):
+def _(x, weight, bias=None):
     return x.new_empty((x.size(0), weight.size(0)))
 
 
@@ -164,3 +169,29 @@ def decode_embed_norm(tokens: Tensor, boundaries: Tensor, token_table: Tensor, b
 def _(tokens, boundaries, token_table, boundary_table, position_table, position, scale, norm1_weight,
       norm1_bias, normalized1, norm2_weight, norm2_bias, normalized2, norm_eps):
     return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)
+
+
+def greedy_token(logits: Tensor, vocab: int, position: Tensor | None = None) -> Tensor:
+    """``logits[:, :vocab].argmax(-1)`` (ties to the lowest index) as int64 ``[rows]``; with
+    ``position`` (a 0-d int64 device tensor) the position is advanced by one in the same launch."""
+    return _greedy_token(logits, vocab, position)
+
+
+@torch.library.custom_op("relation_lm::greedy_token", mutates_args=("position",), device_types="cuda")
+def _greedy_token(logits: Tensor, vocab: int, position: Tensor | None) -> Tensor:
+    device = _abi.require_cuda_rows(logits=logits)
+    if logits.dim() != 2 or not 1 <= vocab <= logits.size(1):
+        raise ValueError("logits must be [rows, >= vocab]")
+    if position is not None:
+        _abi.require_position(position, device)
+    out = torch.empty((logits.size(0),), device=device, dtype=torch.int64)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_greedy_token(
+            _abi.ptr(logits), logits.stride(0), _abi.ptr(out), _abi.ptr(position), logits.size(0),
+            int(vocab), _abi.code(logits), _abi.stream_ptr(device)))
+    return out
+
+
+@_greedy_token.register_fake
+def _(logits, vocab, position):
+    return logits.new_empty((logits.size(0),), dtype=torch.int64)

@@ -124,3 +124,31 @@ def test_decode_embed_with_layer_norm_outputs(B, d, dtype):
     assert torch.allclose(n1.float().cpu(), F.layer_norm(x, (d,), w1, b1, 1e-5), atol=2e-2, rtol=1e-2)
     assert torch.allclose(n2.float().cpu(), F.layer_norm(x, (d,), w2, b2, 1e-5), atol=2e-2, rtol=1e-2)
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_projection_bias_and_greedy_token(dtype):
+    """Bias added in the projection's epilogue (before rounding) and the greedy arg-max with the
+    position increment, as the output head of a decode step uses them."""
+    from relation_lm.kernels.packed_projection import greedy_token, packed_projection
+
+    g = torch.Generator().manual_seed(8080)
+    rows, d, n, vocab = 8, 512, 1152, 1000
+    x = torch.randn(rows, d, generator=g).to(dtype)
+    w = (torch.randn(n, d, generator=g) * 0.05).to(dtype)
+    bias = torch.zeros(n)
+    bias[vocab:vocab + 64] = torch.randn(64, generator=g)
+    got = packed_projection(x.cuda(), w.cuda(), bias.cuda())
+    want = (oracle.linear(x, w) + bias).to(dtype)
+    assert torch.allclose(got.float().cpu(), want.float(), atol=2e-2, rtol=1e-2)
+    logits = got.clone()
+    logits[3, 17] = logits[3, 400] = 60000.0 if dtype == torch.float16 else 1.0e9      # planted tie: lowest index wins
+    logits[5, vocab + 3] = 60000.0 if dtype == torch.float16 else 1.0e9                # beyond the vocabulary: ignored
+    position = torch.tensor(41, device="cuda", dtype=torch.int64)
+    token = greedy_token(logits, vocab, position)
+    assert token.dtype == torch.int64 and int(position.item()) == 42
+    want_token = logits[:, :vocab].float().argmax(-1)
+    want_token[3] = 17
+    assert torch.equal(token, want_token)
+    assert torch.equal(greedy_token(logits, vocab), token) and int(position.item()) == 42
+    assert_status_clear()
