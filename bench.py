@@ -5,7 +5,7 @@
 
 A "step" is one decode position for a batch of sequences (one pass of the hot path:
 packed projection -> cache append / router update -> per layer select -> relation hidden ->
-second MLP layer -> norm-reduce -> heads).  Workload = BASELINE config 2: 6 relation layers,
+second MLP layer -> norm-reduce -> heads).  Workload = the 6-layer ctx-512 configuration: 6 relation layers,
 d_model 512, vocab 16000 + 256 boundary ids, context 512 (448-token prefix, then generated
 positions), block 32, local window 64, 2 remote blocks, 1 anchor, K = 8, bf16, batch 8 per
 GPU.  Token ids are bounded Zipf(s = 1.1) over the vocabulary, boundary ids uniform; weights
@@ -217,7 +217,7 @@ def job_rate(world: int, batch_per_rank: int, steps: int, max_ms: float) -> floa
 def kernel_table(dec, graph_iters: int = 20):
     """Average launch duration of each library kernel on the decoder's own state, captured in
     CUDA graphs (one launch per layer per graph, so consecutive launches touch different
-    caches), with the algorithmic bytes of SURVEY's per-row formulas."""
+    caches), with the algorithmic bytes of the per-row formulas (tensors a launch must read or write, once)."""
     from relation_lm.kernels.packed_projection import packed_projection
     from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update_out,
                                                      relation_hidden_cached_out, relation_norm_reduce_residual)

@@ -258,7 +258,7 @@ RUNNERS = {"select": run_select, "router": run_router, "router_sequence": run_ro
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the reference project")
     parser.add_argument("--out", default=str(HERE / "reference_kernels.pt"))
     args = parser.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
