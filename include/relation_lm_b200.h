@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define RLM_ABI_VERSION 1
+#define RLM_ABI_VERSION 2
 
 typedef enum { RLM_F32 = 0, RLM_BF16 = 1, RLM_F16 = 2 } rlm_dtype;
 

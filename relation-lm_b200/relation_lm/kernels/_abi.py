@@ -6,6 +6,7 @@ from pathlib import Path
 
 import torch
 
+ABI_VERSION = 2          # RLM_ABI_VERSION of include/relation_lm_b200.h this binding was written against
 _LIB_PATH = Path(__file__).resolve().parents[2] / "lib" / "librelation_lm_b200.so"
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -50,7 +51,7 @@ def _load() -> ctypes.CDLL:
     lib.rlm_launch_count.restype = ctypes.c_int64
     lib.rlm_relation_tail_scratch_bytes.argtypes = [_I, _I, _I]
     lib.rlm_relation_tail_scratch_bytes.restype = ctypes.c_int64
-    if lib.rlm_abi_version() != 1:
+    if lib.rlm_abi_version() != ABI_VERSION:
         raise ImportError("librelation_lm_b200.so has an unexpected ABI version")
     return lib
 

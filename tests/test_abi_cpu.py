@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     lib.rlm_abi_version.restype = ctypes.c_int
-    assert lib.rlm_abi_version() == 1
+    assert lib.rlm_abi_version() == _abi.ABI_VERSION == 2
 
 
 def test_binding_prototypes_cover_the_header():
