@@ -27,6 +27,8 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     lib.rlm_abi_version.restype = ctypes.c_int
+    from relation_lm.kernels import _abi
+
     assert lib.rlm_abi_version() == _abi.ABI_VERSION == 2
 
 
