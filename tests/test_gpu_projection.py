@@ -152,3 +152,27 @@ def test_projection_bias_and_greedy_token(dtype):
     assert torch.equal(token, want_token)
     assert torch.equal(greedy_token(logits, vocab), token) and int(position.item()) == 42
     assert_status_clear()
+
+
+def test_new_entry_points_reject_bad_arguments():
+    """Argument errors surface as ValueError before any launch (extension entry points)."""
+    from relation_lm.kernels.packed_projection import greedy_token, layer_norm_cast, packed_projection
+    from relation_lm.kernels.relation_reduce import expanded_cache_append
+
+    x = torch.randn(4, 512, device="cuda").bfloat16()
+    w = torch.randn(64, 512, device="cuda").bfloat16()
+    with pytest.raises(ValueError):
+        packed_projection(x, w, torch.zeros(32, device="cuda"))                 # bias of the wrong length
+    with pytest.raises(ValueError):
+        packed_projection(x, w, torch.zeros(64, device="cuda").bfloat16())      # bias must be fp32
+    with pytest.raises(ValueError):
+        greedy_token(torch.randn(4, 100, device="cuda"), 101)                   # vocabulary wider than the rows
+    with pytest.raises(ValueError):
+        layer_norm_cast(torch.randn(4, 512, device="cuda"), torch.ones(512, device="cuda"),
+                        torch.zeros(512, device="cuda"), 1e-5, torch.empty(4, 256, device="cuda").bfloat16())
+    caches = torch.zeros(2, 4, 8, 256, device="cuda"), torch.zeros(2, 4, 8, 64, device="cuda")
+    weights = torch.zeros(2, 128, 64, device="cuda")
+    with pytest.raises(ValueError):                                             # fp32 state is not a tensor-core format
+        expanded_cache_append(caches[0], caches[1], weights, weights, torch.zeros(2, 128, device="cuda"),
+                              torch.tensor(3, device="cuda"))
+    assert_status_clear()
