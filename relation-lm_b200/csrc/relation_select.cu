@@ -113,69 +113,79 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     return p;
 }
 
+// ---- lane-per-row scoring
+//
+// A lane owns a whole 64-wide row: it evaluates the canonical dot (eight 8-element fma chains
+// p0..p7 combined as ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7))) by itself, with no shuffles, so a
+// warp scores 32 rows per pass.  Rows are 128 (or 256) bytes apart in shared memory, so the
+// lanes of a quarter warp must not read the same 16-byte chunk index at the same time: step jj
+// of lane l handles the chunk pair of index (jj + l) & 3, lanes 4..7 of each group of eight
+// taking the pair's second chunk first.  Because a + b == b + a exactly, the pair sums and the
+// final tree are bit-identical to the fixed order; tree4() undoes the rotation.
+
+__device__ __forceinline__ int rot_chunk(int jj, int lane) { return 2 * ((jj + lane) & 3) + ((lane >> 2) & 1); }
+
+// (s0 + s1) + (s2 + s3) from x[jj] = s[(jj + r) & 3]
+__device__ __forceinline__ float tree4(const float (&x)[4], int r) {
+    const bool odd = (r & 1) != 0;
+    const float a = __fadd_rn(odd ? x[3] : x[0], odd ? x[0] : x[1]);
+    const float b = __fadd_rn(odd ? x[1] : x[2], odd ? x[2] : x[3]);
+    return __fadd_rn(a, b);
+}
+
 // Scores staged key rows against the query held in shared memory (f32 [64]) with the
 // `nw` warps of a group (this warp is number `wi`).  Two layouts:
 //   local window (sel == nullptr): row r is position pos0 + r, valid from `first_valid` on;
 //   remote blocks (sel != nullptr): row r belongs to the block of rank r / bs at offset
 //     o = r % bs, position sel[3 rank] * bs + o, valid while o < sel[3 rank + 2].
-// The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand` the scores go to candidate slots
-// slot0 + r; in every case the warp's best (score, lowest position on ties) is folded into
-// (best_key, best_pos), identical in all lanes.
-// kU row groups of four rows are in flight per warp iteration.  `bs_shift` >= 0 says that the
-// block size is 1 << bs_shift (no division to find a remote row's block).
-template <int kU>
+// The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand`
+// the scores go to candidate slots slot0 + r; in every case the warp's best (score, lowest
+// position on ties) is folded into (best_key, best_pos), identical in all lanes.
 __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
-                                        const int* sel, int bs, int bs_shift, int first_valid, int pos0,
+                                        const int* sel, int bs, int first_valid, int pos0,
                                         int exclude, const int* excl, int n_excl, const float* query,
                                         float* cand, int slot0, int wi, int nw, uint32_t& best_key,
                                         int& best_pos) {
     const int lane = threadIdx.x & 31;
-    const int j = lane & 7, sub = lane >> 3;
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
-    float q[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = query[8 * j + i];
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
-    for (int base = wi * 4 * kU; base < n_rows; base += 4 * kU * nw) {
-        int r[kU], pos[kU];
-        bool valid[kU];
-        float acc[kU];
-        float k[kU][8];
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            r[u] = base + 4 * u + sub;
-            acc[u] = 0.0f;
-            if (sel) {
-                const int rank = bs_shift >= 0 ? r[u] >> bs_shift : r[u] / bs;
-                const int o = r[u] - rank * bs;
-                const bool in = r[u] < n_rows;
-                pos[u] = in ? sel[3 * rank] * bs + o : -1;
-                valid[u] = in && o < sel[3 * rank + 2];
-            } else {
-                pos[u] = pos0 + r[u];
-                valid[u] = r[u] < n_rows && r[u] >= first_valid;
-            }
-            valid[u] = valid[u] && pos[u] != exclude;
-            for (int x = 0; x < n_excl; ++x) valid[u] = valid[u] && pos[u] != excl[x];
-            if (valid[u]) load8(rows + static_cast<size_t>(r[u]) * row_bytes, 8 * j, key_dtype, k[u]);
+    for (int base = wi * 32; base < n_rows; base += 32 * nw) {
+        const int r = base + lane;
+        int pos;
+        bool valid;
+        if (sel) {
+            const int rank = r / bs, o = r - rank * bs;
+            const bool in = r < n_rows;
+            pos = in ? sel[3 * rank] * bs + o : -1;
+            valid = in && o < sel[3 * rank + 2];
+        } else {
+            pos = pos0 + r;
+            valid = r < n_rows && r >= first_valid;
         }
+        valid = valid && pos != exclude;
+        for (int x = 0; x < n_excl; ++x) valid = valid && pos != excl[x];
+        float sc = kNegInf;
+        if (valid) {
+            const unsigned char* row = rows + static_cast<size_t>(r) * row_bytes;
+            float pair[4];
 #pragma unroll
-        for (int u = 0; u < kU; ++u)
-            if (valid[u]) acc[u] = seg8(k[u], q);
-#pragma unroll
-        for (int sft = 1; sft <= 4; sft <<= 1)
-#pragma unroll
-            for (int u = 0; u < kU; ++u) acc[u] = __fadd_rn(acc[u], __shfl_xor_sync(0xffffffffu, acc[u], sft));
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-            float sc = valid[u] ? __fmul_rn(acc[u], 0.125f) : kNegInf;
-            if (cand && j == 0 && r[u] < n_rows) cand[slot0 + r[u]] = sc;
-            uint32_t key = float_key(sc);
-            if (valid[u] && (key > my_key || my_pos == 0x7fffffff || (key == my_key && pos[u] < my_pos))) {
-                my_key = key;
-                my_pos = pos[u];
+            for (int jj = 0; jj < 4; ++jj) {
+                const int c0 = rot_chunk(jj, lane), c1 = c0 ^ 1;
+                float k0[8], k1[8], q0[8], q1[8];
+                load8(row, 8 * c0, key_dtype, k0);
+                load8(row, 8 * c1, key_dtype, k1);
+                load8(query, 8 * c0, RLM_F32, q0);
+                load8(query, 8 * c1, RLM_F32, q1);
+                pair[jj] = __fadd_rn(seg8(k0, q0), seg8(k1, q1));
             }
+            sc = __fmul_rn(tree4(pair, lane & 3), 0.125f);
+        }
+        if (cand && r < n_rows) cand[slot0 + r] = sc;
+        const uint32_t key = float_key(sc);
+        if (valid && (key > my_key || my_pos == 0x7fffffff || (key == my_key && pos < my_pos))) {
+            my_key = key;
+            my_pos = pos;
         }
     }
     warp_argmax_key(my_key, my_pos);
@@ -401,10 +411,11 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
     __syncthreads();
     RLM_PROBE(3);
 
-    // With remote blocks, half of the warps score blocks while the other half scores the
-    // local window; without, everybody scores rows.
+    // With remote blocks, half of the warps score blocks (eight lanes per block) while the other
+    // half scores the local window (a lane per row); without, everybody scores rows.
     const bool split = top > 0;
-    const int row_wi = split ? warp - kWarps / 2 : warp, row_nw = split ? kWarps / 2 : kWarps;
+    const int block_warps = split ? kWarps / 2 : 0;
+    const int row_wi = warp - block_warps, row_nw = kWarps - block_warps;
 
     int anchor_pos = 0;
     if (do_anchor) {
@@ -416,11 +427,11 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
         RLM_PROBE(4);
         uint32_t bk = 0;
         int bp = 0x7fffffff;
-        if (split && warp < kWarps / 2)
+        if (warp < block_warps)
             score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
-                         a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, kWarps / 2);
+                         a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
-            score_rows<2>(smem + p.a_local, a.key_dtype, L, nullptr, bs, bs_shift, first_local, t - L + 1, -1, excl_s,
+            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
                        n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
@@ -444,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             RLM_PROBE(10);
             bk = 0;
             bp = 0x7fffffff;
-            score_rows<2>(smem + p.remote, a.key_dtype, top * bs, sel, bs, bs_shift, 0, 0, -1, excl_s, n_excl, aq,
+            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
                        nullptr, 0, warp, kWarps, bk, bp);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             __syncthreads();
@@ -495,11 +506,11 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
     RLM_PROBE(14);
     uint32_t dk = 0;
     int dp = 0x7fffffff;
-    if (split && warp < kWarps / 2)
+    if (warp < block_warps)
         score_blocks(smem + p.p_mean, smem + p.p_std, a.stats_dtype, nb, n_complete, bs, t, ls,
-                     a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, kWarps / 2);
+                     a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
-        score_rows<2>(smem + p.p_local, a.key_dtype, L, nullptr, bs, bs_shift, first_local, t - L + 1, anchor_pos,
+        score_rows(smem + p.p_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp);
     __syncthreads();
     RLM_PROBE(15);
@@ -521,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             return;
         }
         RLM_PROBE(19);
-        score_rows<2>(smem + p.remote, a.key_dtype, top * bs, sel, bs, bs_shift, 0, 0, anchor_pos, excl_s, n_excl, pq,
+        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
                    cand, L, warp, kWarps, dk, dp);
         __syncthreads();
         RLM_PROBE(20);
