@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 // the 8-column chunks lane, lane + 32, ... (kVecChunks of them, at most four: dim <= 1024), so a partner row is
 // fetched with a few 16-byte loads per lane instead of one scalar load per column.
 template <int kVecChunks>
-__global__ void __launch_bounds__(kNormThreads, 2) relation_norm_reduce_vec_kernel(const NormArgs a) {
+__global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunks == 3 ? 3 : 2)) relation_norm_reduce_vec_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
     griddep_sync();
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
