@@ -40,6 +40,10 @@ import torch  # noqa: E402
 PREFIX = 448
 METRIC = "relation decode tokens/s at ctx512 K=8"
 UNIT = "tokens/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one relation_select_kernel launch at 256 rows of the
+# 12-layer decode shape (ncu capture summarised under profiles/), and its ratio to the algorithmic bytes
+NCU_SELECT_TRAFFIC_ROWS256 = 20_809_984
+NCU_SELECT_TRAFFIC_RATIO = 20_809_984 / 21_325_824
 CPU_SAMPLE_BATCH = 8   # the CPU arm keeps fp32 caches on the host: it decodes at most this many sequences
 
 
@@ -524,11 +528,16 @@ def run_ours(args) -> None:
             "roofline": {"kernel": dominant, "bound": "hbm", "achieved": dom["gb_per_s"], "peak": peak,
                          "unit": "GB/s", "frac": dom["gb_per_s"] / peak,
                          "peak_source": "measured" if peaks else "fallback",
-                         "traffic": None, "us_per_launch": dom["us_per_launch"],
+                         "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO)
+                                     if dominant == "relation_select_kernel" else None),
+                         "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (20.81 MB per "
+                                           "launch for 21.33 MB of algorithmic bytes), scaled by algorithmic bytes",
+                         "us_per_launch": dom["us_per_launch"],
                          "share_of_library_time": dom["us_per_step"] / lib_us,
                          "note": "batch-8 decode launches move < 1 MB each and are latency-bound"},
             "kernels": table,
             "roofline_rows256": {**rows256, "peak": peak, "frac": rows256["gb_per_s"] / peak,
+                                 "traffic": NCU_SELECT_TRAFFIC_ROWS256,
                                  "note": "the selector at 256 rows of the 12-layer decode shape, the "
                                          "smallest launch whose bytes (21 MB) are bandwidth-relevant"},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cpu_threads, "kind": "port",
