@@ -210,12 +210,16 @@ int rlm_relation_hidden_cache_update(
  *   next_normalized (optional, with residual; [N,D] bfloat16 / float16 = next_dtype): LayerNorm of the
  *   updated residual row with next_norm_weight / next_norm_bias [D] f32 and next_norm_eps, i.e. the
  *   normalised input of the next layer's query projection (or of the output heads).
+ *   raw_splits > 1: raw is the sum of raw_splits slices raw_split_stride ELEMENTS apart (the output of
+ *   rlm_packed_projection with split K); raw_bias (optional, [D] param_dtype) is added to every
+ *   partner row (the bias of the second relation-MLP layer).  Both need D a multiple of 8.
  */
 int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
     float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
-    float next_norm_eps, void* next_normalized, int next_dtype,
+    float next_norm_eps, void* next_normalized, int next_dtype, int raw_splits,
+    int64_t raw_split_stride, const void* raw_bias,
     int n_rows, int k_out, int dim, int raw_dtype, int param_dtype,
     int32_t* status, void* stream);
 
@@ -246,10 +250,13 @@ int rlm_router_cache_prefill(
  *   d_in a multiple of 8, n_out a multiple of 32; fp32 operands return RLM_ERR_UNSUPPORTED.
  *   bias (optional, [n_out] f32) is added to every row before the output is rounded, as F.linear
  *   with a bias does (the boundary head of the output projection).
+ *   k_splits > 1 (split K, for few rows and a long d_in): k_splits CTAs share an output tile and out
+ *   becomes k_splits fp32 slices [k_splits, rows, n_out] whose sum is the product (out_dtype
+ *   RLM_F32, no bias, k_splits a divisor of d_in / 64); rlm_relation_norm_reduce sums them.
  */
 int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
                           const float* bias, void* out, int rows, int d_in, int n_out, int in_dtype,
-                          int out_dtype, int32_t* status, void* stream);
+                          int out_dtype, int k_splits, int32_t* status, void* stream);
 
 /*
  * LayerNorm fused into the projection, for decode batches (extension):

@@ -39,6 +39,8 @@ struct GemmArgs {
     uint32_t idesc;
     uint32_t a_bytes;      // bytes one x tile load delivers (box rows x 128)
     int issuers;           // MMA-issuing warps (1 or 2)
+    int k_blocks_per_split;  // K-blocks of 64 one CTA contracts (all of them without split K)
+    int k_splits;
 };
 
 template <int BN>
@@ -65,7 +67,10 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     const uint32_t ring_addr = smem_u32(ring);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kBM;
-    const int k_iters = (a.k + kBK - 1) / kBK;
+    // split K: grid.z CTAs share an output tile, each contracts k_blocks_per_split K-blocks and
+    // writes its own fp32 slice out[z] (summed by the consumer)
+    const int k_first = blockIdx.z * a.k_blocks_per_split;
+    const int k_iters = min((a.k + kBK - 1) / kBK - k_first, a.k_blocks_per_split);
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
@@ -97,8 +102,8 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
         // stages are free), later rounds by lane 0 as stages are released
         if (lane < kStages && lane < k_iters) {
             mbar_expect_tx(full(lane), a.a_bytes + kBBytes);
-            tma_load_2d(ring_addr + lane * (kABytes + kBBytes), &map_x, lane * kBK, m0, full(lane));
-            tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, lane * kBK, n0, full(lane));
+            tma_load_2d(ring_addr + lane * (kABytes + kBBytes), &map_x, (k_first + lane) * kBK, m0, full(lane));
+            tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, (k_first + lane) * kBK, n0, full(lane));
         }
         __syncwarp();
         RLM_G_PROBE(3, 0);
@@ -107,8 +112,8 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
                 const int s = it % kStages;
                 if (!mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { failed = 1; break; }
                 mbar_expect_tx(full(s), a.a_bytes + kBBytes);
-                tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, it * kBK, m0, full(s));
-                tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, it * kBK, n0, full(s));
+                tma_load_2d(ring_addr + s * (kABytes + kBBytes), &map_x, (k_first + it) * kBK, m0, full(s));
+                tma_load_2d(ring_addr + s * (kABytes + kBBytes) + kABytes, &map_w, (k_first + it) * kBK, n0, full(s));
             }
         }
         __syncwarp();
@@ -199,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
                 for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + a.bias[n0 + c + i]);
             }
             if (row < a.m) {
-                const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
+                const size_t at = (static_cast<size_t>(blockIdx.z) * a.m + row) * a.n + n0 + c;
                 if (a.out_dtype == RLM_F32) {
                     float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
 #pragma unroll
@@ -538,7 +543,7 @@ int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& a,
     auto kernel = packed_projection_kernel<BN>;
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
-    dim3 grid(a.n / BN, (a.m + kBM - 1) / kBM);
+    dim3 grid(a.n / BN, (a.m + kBM - 1) / kBM, a.k_splits);
     launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, mx, mw, a);
     count_launch();
     return check_launch("packed_projection_kernel");
@@ -648,7 +653,8 @@ extern "C" int rlm_layer_norm_cast(const float* x, int64_t x_row_stride, const f
 
 extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const void* weight,
                                      const float* bias, void* out, int rows, int d_in, int n_out,
-                                     int in_dtype, int out_dtype, int32_t* status, void* stream) {
+                                     int in_dtype, int out_dtype, int k_splits, int32_t* status,
+                                     void* stream) {
     using namespace rlm;
     if (rows == 0) return RLM_OK;
     if (!x || !weight || !out) { set_error("packed_projection: NULL pointer"); return RLM_ERR_NULL; }
@@ -665,12 +671,16 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
         set_error("packed_projection: tensors must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
+    if (k_splits < 1 || (k_splits > 1 && (out_dtype != RLM_F32 || bias || ((d_in + kBK - 1) / kBK) % k_splits != 0))) {
+        set_error("packed_projection: split K needs fp32 output slices, no bias and a split count that divides d_in / 64");
+        return RLM_ERR_SHAPE;
+    }
     // Tile width: with few rows the weight read dominates, so pick the widest tile that still
     // gives about one CTA per SM; with many rows use wide tiles.
     const int m_tiles = (rows + kBM - 1) / kBM;
     int bn = 128;
-    if (n_out % 128 != 0 || n_out / 128 * m_tiles < 100) bn = 64;
-    if (n_out % 64 != 0 || (n_out / 64 * m_tiles < 100 && bn == 64)) bn = 32;
+    if (n_out % 128 != 0 || n_out / 128 * m_tiles * k_splits < 100) bn = 64;
+    if (n_out % 64 != 0 || (n_out / 64 * m_tiles * k_splits < 100 && bn == 64)) bn = 32;
     // x tile: the box holds only the rows that exist (a multiple of 8, at most 128); the MMA
     // reads 128 rows of the stage, the rest is never stored
     const int box_rows = rows >= kBM ? kBM : ((rows + 7) / 8) * 8;
@@ -684,7 +694,9 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     a.out = out; a.bias = bias; a.status = status; a.m = rows; a.n = n_out; a.k = d_in; a.out_dtype = out_dtype;
     a.a_bytes = static_cast<uint32_t>(box_rows) * kBK * 2;
     // a single thread issues one tcgen05.mma per ~60 cycles, more than a 128-wide MMA runs: two warps issue
-    const int k_blocks = (d_in + kBK - 1) / kBK;
+    const int k_blocks = ((d_in + kBK - 1) / kBK) / k_splits;
+    a.k_blocks_per_split = k_blocks;
+    a.k_splits = k_splits;
     // (with an even ring depth each issuer owns its own stages, so every stage barrier is consumed in order)
     a.issuers = (k_blocks >= 2 && stages_for(bn) % 2 == 0) ? 2 : 1;
     const uint32_t fmt = in_dtype == RLM_BF16 ? 1u : 0u;

@@ -406,6 +406,9 @@ struct NormArgs {
     float* out;               // context [N, D], or NULL when only the residual is wanted
     float* residual;          // optional [N, D] fp32: residual += (*mix) * context
     const float* mix;
+    int raw_splits;           // raw is the sum of this many slices, raw_split_stride elements apart (split-K GEMM)
+    int64_t raw_split_stride;
+    const void* raw_bias;     // optional [D] (param dtype): added to every partner row
     const float* next_w;      // optional: LayerNorm of the updated residual row, written as 16-bit
     const float* next_b;      //   values to next_out [N, D] (the next layer's normalised input)
     void* next_out;
@@ -525,11 +528,27 @@ __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunk
     float s0 = lane < K ? a.scores[static_cast<size_t>(row) * K + lane] : kNegInf;
     float s1 = lane + 32 < K ? a.scores[static_cast<size_t>(row) * K + lane + 32] : kNegInf;
     float x[kVecChunks][8];
+    // one 8-column chunk of partner row k: the slices of a split-K GEMM are summed and the bias added here
+    auto load_raw = [&](const char* row_k, int chunk, float (&dst)[8]) {
+        load8(row_k, 8 * chunk, a.raw_dtype, dst);
+        for (int sp = 1; sp < a.raw_splits; ++sp) {
+            float more[8];
+            load8(row_k + static_cast<size_t>(sp) * a.raw_split_stride * raw_elem, 8 * chunk, a.raw_dtype, more);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[e] += more[e];
+        }
+        if (a.raw_bias) {
+            float bias8[8];
+            load8(a.raw_bias, 8 * chunk, a.param_dtype, bias8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[e] += bias8[e];
+        }
+    };
     const char* raw_row = static_cast<const char*>(a.raw) + static_cast<size_t>(row) * K * D * raw_elem;
     if (warp < K) {
 #pragma unroll
         for (int i = 0; i < kVecChunks; ++i)
-            if (lane + 32 * i < chunks) load8(raw_row + static_cast<size_t>(warp) * D * raw_elem, 8 * (lane + 32 * i), a.raw_dtype, x[i]);
+            if (lane + 32 * i < chunks) load_raw(raw_row + static_cast<size_t>(warp) * D * raw_elem, lane + 32 * i, x[i]);
     }
 
     int k_limit = 32 - __clz(max(t, 0) + 1);   // ceil(log2(t + 2))
@@ -554,7 +573,7 @@ __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunk
         if (k != warp && wk != 0.0f) {
 #pragma unroll
             for (int i = 0; i < kVecChunks; ++i)
-                if (lane + 32 * i < chunks) load8(raw_row + static_cast<size_t>(k) * D * raw_elem, 8 * (lane + 32 * i), a.raw_dtype, x[i]);
+                if (lane + 32 * i < chunks) load_raw(raw_row + static_cast<size_t>(k) * D * raw_elem, lane + 32 * i, x[i]);
         }
         if (wk == 0.0f) continue;   // inactive slot contributes nothing
         float sum = 0.0f;
@@ -658,7 +677,8 @@ extern "C" int rlm_relation_norm_reduce(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
     float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
-    float next_norm_eps, void* next_normalized, int next_dtype, int n_rows,
+    float next_norm_eps, void* next_normalized, int next_dtype, int raw_splits,
+    int64_t raw_split_stride, const void* raw_bias, int n_rows,
     int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
     using namespace rlm;
     if (n_rows == 0) return RLM_OK;
@@ -681,11 +701,17 @@ extern "C" int rlm_relation_norm_reduce(
     a.residual = residual; a.mix = mix;
     a.next_w = next_norm_weight; a.next_b = next_norm_bias; a.next_out = next_normalized;
     a.next_eps = next_norm_eps; a.next_dtype = next_dtype;
+    a.raw_splits = raw_splits < 1 ? 1 : raw_splits; a.raw_split_stride = raw_split_stride; a.raw_bias = raw_bias;
     a.eps = norm_eps; a.n_rows = n_rows; a.k_out = k_out; a.dim = dim;
     a.raw_dtype = raw_dtype; a.param_dtype = param_dtype;
     int smem_bytes = kNormWarps * dim * 4;
     const bool vec = dim % 8 == 0 && aligned16(raw) && aligned16(norm_weight) && aligned16(norm_bias) &&
                      (!out || aligned16(out)) && (!residual || aligned16(residual));
+    if ((raw_splits > 1 || raw_bias) && (!vec || (raw_bias && !aligned16(raw_bias)) ||
+                                          (raw_splits > 1 && (raw_split_stride * dtype_size(raw_dtype)) % 16 != 0))) {
+        set_error("relation_norm_reduce: summed slices / a bias need dim a multiple of 8 and 16-byte aligned tensors");
+        return RLM_ERR_UNSUPPORTED;
+    }
     if (next_normalized) {
         if (!residual || !next_norm_weight || !next_norm_bias || !vec || !aligned16(next_norm_weight) ||
             !aligned16(next_norm_bias) || !aligned16(next_normalized) ||

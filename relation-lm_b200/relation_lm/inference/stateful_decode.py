@@ -24,11 +24,12 @@ from torch import Tensor
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import (decode_embed_norm, greedy_token, layer_norm_cast,
-                                                    packed_projection)
+                                                    packed_projection, packed_projection_slices)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
                                                  relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
                                                  relation_norm_reduce_residual_norm,
+                                                 relation_norm_reduce_residual_norm_slices,
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
@@ -38,7 +39,7 @@ from relation_lm.kernels.router_cache import sparse_cache_append
 class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
                  dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
-                 programmatic_launch: bool = True) -> None:
+                 programmatic_launch: bool = True, second_layer_split: bool = False) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -69,6 +70,15 @@ class StatefulDecoder:
         self.fused_tail = fused_tail and self.fused and 128 % cfg.k_max == 0 and cfg.k_max <= 32
         # One tensor-core launch expands the position's operand rows of all layers (shapes permitting).
         self.stacked_expand = self.fused and R % 64 == 0 and H % 128 == 0
+        # Second relation-MLP layer: cuBLAS (F.linear) by default.  Optionally, with at most one row
+        # tile (B * K <= 128), the library's GEMM splits the reduction over the hidden width across
+        # several CTAs and norm-reduce sums the slices: no library call in the step, a few percent slower.
+        self.second_layer_splits = 1
+        if self.fused and second_layer_split and B * cfg.k_max <= 128 and H % 64 == 0 and cfg.d_model % 32 == 0:
+            blocks = H // 64
+            self.second_layer_splits = next((s for s in (4, 2) if blocks % s == 0 and blocks // s >= 2), 1)
+        if self.second_layer_splits > 1:
+            self.b2_f32 = self.w["b2"].float().contiguous()                    # [L, d], dtype of the norm parameters
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.normalized = zeros(B, cfg.d_model)             # LayerNorm'd input of the next projection
@@ -208,6 +218,14 @@ class StatefulDecoder:
                               w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,
                               hidden, w["mix"][l])
                 layer_norm_cast(hidden, next_w, next_b, cfg.norm_eps, self.normalized)
+            elif self.second_layer_splits > 1:
+                # few rows, long reduction: split-K tensor-core GEMM, its fp32 slices summed by norm-reduce
+                slices = packed_projection_slices(self.relation_hidden.view(-1, self.relation_hidden.size(-1)),
+                                                  w["w2"][l], self.second_layer_splits)
+                relation_norm_reduce_residual_norm_slices(
+                    slices.view(self.second_layer_splits, -1, K, cfg.d_model), self.b2_f32[l], partner_score,
+                    w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l],
+                    next_w, next_b, cfg.norm_eps, self.normalized)
             else:
                 raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])            # [B, K, d]
                 relation_norm_reduce_residual_norm(raw, partner_score, w["relation_norm_w"][l],

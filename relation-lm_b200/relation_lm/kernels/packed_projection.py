@@ -36,7 +36,7 @@ def packed_projection(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> 
     with _abi.device_guard(device):
         _abi.check(_abi.LIB.rlm_packed_projection(
             _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(bias), _abi.ptr(out), rows, d_in, n_out,
-            _abi.code(x), _abi.code(out), _abi.ptr(_abi.status_tensor(device)),
+            _abi.code(x), _abi.code(out), 1, _abi.ptr(_abi.status_tensor(device)),
             _abi.stream_ptr(device)))
     return out
 
@@ -44,6 +44,33 @@ def packed_projection(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> 
 @packed_projection.register_fake
 def _(x, weight, bias=None):
     return x.new_empty((x.size(0), weight.size(0)))
+
+
+@torch.library.custom_op("relation_lm::packed_projection_slices", mutates_args=(), device_types="cuda")
+def packed_projection_slices(x: Tensor, weight: Tensor, splits: int) -> Tensor:
+    """Split-K form for few rows and a long reduction: ``splits`` CTAs share an output tile and the
+    result comes back as fp32 slices ``[splits, rows, n]`` whose sum is ``x @ weight.T`` (the consumer,
+    ``relation_norm_reduce_residual_norm_slices``, adds them up).  ``splits`` divides ``d / 64``."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(weight=weight)
+    if weight.device != device or weight.dim() != 2 or weight.size(1) != x.size(1):
+        raise ValueError("weight must be [n_out, d_in] on the device of x")
+    if x.dtype != weight.dtype or x.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("packed_projection takes bfloat16 or float16 operands of one dtype")
+    rows, d_in = x.shape
+    n_out = weight.size(0)
+    out = torch.empty((int(splits), rows, n_out), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_packed_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), None, _abi.ptr(out), rows, d_in, n_out,
+            _abi.code(x), _abi.code(out), int(splits), _abi.ptr(_abi.status_tensor(device)),
+            _abi.stream_ptr(device)))
+    return out
+
+
+@packed_projection_slices.register_fake
+def _(x, weight, splits):
+    return x.new_empty((splits, x.size(0), weight.size(0)), dtype=torch.float32)
 
 
 @torch.library.custom_op("relation_lm::layer_norm_cast", mutates_args=("out",), device_types="cuda")

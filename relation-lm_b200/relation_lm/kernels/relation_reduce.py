@@ -246,7 +246,7 @@ def relation_norm_reduce(
     with _abi.device_guard(device):
         _abi.check(_abi.LIB.rlm_relation_norm_reduce(
             _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
-            _abi.ptr(position), None, float(norm_eps), _abi.ptr(out), None, None, None, None, 0.0, None, 0,
+            _abi.ptr(position), None, float(norm_eps), _abi.ptr(out), None, None, None, None, 0.0, None, 0, 1, 0, None,
             batch, k_out, dim,
             _abi.code(raw), _abi.same_dtype("norm parameter", norm_weight, norm_bias),
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
@@ -336,7 +336,7 @@ def relation_norm_reduce_residual(
         _abi.check(_abi.LIB.rlm_relation_norm_reduce(
             _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
             _abi.ptr(position), None, float(norm_eps), None, _abi.ptr(hidden), _abi.ptr(mix),
-            None, None, 0.0, None, 0, batch, k_out, dim, _abi.code(raw),
+            None, None, 0.0, None, 0, 1, 0, None, batch, k_out, dim, _abi.code(raw),
             _abi.same_dtype("norm parameter", norm_weight, norm_bias),
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
 
@@ -384,7 +384,7 @@ def relation_norm_reduce_residual_norm(
             _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
             _abi.ptr(position), None, float(norm_eps), None, _abi.ptr(hidden), _abi.ptr(mix),
             _abi.ptr(next_norm_weight), _abi.ptr(next_norm_bias), float(next_norm_eps),
-            _abi.ptr(normalized), _abi.code(normalized), batch, k_out, dim, _abi.code(raw),
+            _abi.ptr(normalized), _abi.code(normalized), 1, 0, None, batch, k_out, dim, _abi.code(raw),
             _abi.same_dtype("norm parameter", norm_weight, norm_bias),
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
 
@@ -392,6 +392,59 @@ def relation_norm_reduce_residual_norm(
 @relation_norm_reduce_residual_norm.register_fake
 def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, mix, next_norm_weight,
       next_norm_bias, next_norm_eps, normalized):
+    return None
+
+
+@torch.library.custom_op("relation_lm::relation_norm_reduce_residual_norm_slices",
+                         mutates_args=("hidden", "normalized"), device_types="cuda")
+def relation_norm_reduce_residual_norm_slices(
+    raw_slices: Tensor,
+    raw_bias: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+    hidden: Tensor,
+    mix: Tensor,
+    next_norm_weight: Tensor,
+    next_norm_bias: Tensor,
+    next_norm_eps: float,
+    normalized: Tensor,
+) -> None:
+    """``relation_norm_reduce_residual_norm`` whose partner rows arrive as the fp32 slices of a
+    split-K projection, ``raw = raw_slices.sum(0) + raw_bias`` with ``raw_slices [S, B, K, D]`` and
+    ``raw_bias [D]`` in the dtype of the LayerNorm parameters (extension)."""
+    device = _abi.require_cuda_contiguous(raw_slices=raw_slices, raw_bias=raw_bias, partner_scores=partner_scores,
+                                          norm_weight=norm_weight, norm_bias=norm_bias, hidden=hidden, mix=mix,
+                                          next_norm_weight=next_norm_weight, next_norm_bias=next_norm_bias,
+                                          normalized=normalized)
+    _abi.require_position(position, device)
+    if raw_slices.dim() != 4 or raw_slices.dtype != torch.float32:
+        raise ValueError("raw_slices must be float32 [S, B, K, D]")
+    splits, batch, k_out, dim = raw_slices.shape
+    if partner_scores.shape != (batch, k_out) or partner_scores.dtype != torch.float32:
+        raise ValueError("partner_scores must be float32 [B, K]")
+    if hidden.shape != (batch, dim) or hidden.dtype != torch.float32 or mix.dtype != torch.float32 \
+            or mix.numel() != 1:
+        raise ValueError("hidden must be float32 [B, D] and mix a one-element float32 tensor")
+    if normalized.shape != (batch, dim) or next_norm_weight.dtype != torch.float32 \
+            or next_norm_bias.dtype != torch.float32 or next_norm_weight.numel() != dim or raw_bias.numel() != dim:
+        raise ValueError("normalized must be [B, D], raw_bias [D] and the next LayerNorm parameters float32 [D]")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_norm_reduce(
+            _abi.ptr(raw_slices), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
+            _abi.ptr(position), None, float(norm_eps), None, _abi.ptr(hidden), _abi.ptr(mix),
+            _abi.ptr(next_norm_weight), _abi.ptr(next_norm_bias), float(next_norm_eps),
+            _abi.ptr(normalized), _abi.code(normalized), splits, batch * k_out * dim, _abi.ptr(raw_bias),
+            batch, k_out, dim, _abi.code(raw_slices),
+            _abi.same_dtype("norm parameter", norm_weight, norm_bias, raw_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_norm_reduce_residual_norm_slices.register_fake
+def _(raw_slices, raw_bias, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, mix,
+      next_norm_weight, next_norm_bias, next_norm_eps, normalized):
     return None
 
 
@@ -524,7 +577,7 @@ def relation_norm_reduce_rows(
         _abi.check(_abi.LIB.rlm_relation_norm_reduce(
             _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
             None, _abi.ptr(row_position), float(norm_eps), _abi.ptr(out), None, None, None, None, 0.0,
-            None, 0, rows, k_out,
+            None, 0, 1, 0, None, rows, k_out,
             dim, _abi.code(raw), _abi.same_dtype("norm parameter", norm_weight, norm_bias),
             _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
     return out

@@ -221,3 +221,37 @@ def test_norm_reduce_residual_with_next_layer_norm(B, K, D, dtype):
     want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
     assert torch.allclose(normalized.float().cpu(), want_norm, atol=2e-2, rtol=1e-2)
     assert_status_clear()
+
+
+@pytest.mark.parametrize("splits", [2, 4])
+def test_split_k_second_layer_feeds_norm_reduce(splits):
+    """Second relation-MLP layer as a split-K tensor-core GEMM whose fp32 slices (and bias) are
+    summed inside norm-reduce: residual and next-layer LayerNorm against the fp32 reference."""
+    from relation_lm.kernels.packed_projection import packed_projection_slices
+    from relation_lm.kernels.relation_reduce import relation_norm_reduce_residual_norm_slices
+
+    g = torch.Generator().manual_seed(7900 + splits)
+    B, K, H, D, t = 8, 8, 2048, 512, 300
+    act = torch.randn(B, K, H, generator=g).bfloat16()
+    w2 = (torch.randn(D, H, generator=g) * 0.03).bfloat16()
+    b2 = torch.randn(D, generator=g) * 0.1
+    scores = torch.randn(B, K, generator=g)
+    scores[1::3, -2:] = -torch.inf
+    gamma, beta = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    next_w, next_b = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    hidden = torch.randn(B, D, generator=g)
+    mix = torch.tensor(0.61)
+    slices = packed_projection_slices(act.cuda().view(B * K, H), w2.cuda(), splits)
+    assert slices.shape == (splits, B * K, D) and slices.dtype == torch.float32
+    raw = oracle.linear(act.view(B * K, H), w2).view(B, K, D) + b2
+    assert torch.allclose(slices.sum(0).cpu().view(B, K, D) + b2, raw, atol=2e-3, rtol=1e-3)
+    got_hidden = hidden.cuda().clone()
+    normalized = torch.empty(B, D, device="cuda", dtype=torch.bfloat16)
+    relation_norm_reduce_residual_norm_slices(slices.view(splits, B, K, D), b2.cuda(), scores.cuda(), gamma.cuda(),
+                                              beta.cuda(), position_tensor(t), 1e-5, got_hidden, mix.cuda(),
+                                              next_w.cuda(), next_b.cuda(), 1e-5, normalized)
+    want_hidden = hidden + mix * oracle.relation_norm_reduce(raw, scores, gamma, beta, t, 1e-5)
+    assert torch.allclose(got_hidden.cpu(), want_hidden, atol=2e-3, rtol=1e-3), (got_hidden.cpu() - want_hidden).abs().max()
+    want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
+    assert torch.allclose(normalized.float().cpu(), want_norm, atol=2e-2, rtol=1e-2)
+    assert_status_clear()
