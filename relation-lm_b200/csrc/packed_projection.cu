@@ -94,17 +94,19 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
     RLM_G_PROBE(1, 0);
+    // Producer (warp 0): the first round of the ring is requested by one lane per stage at once
+    // (the stages are free), later rounds by lane 0 as stages are released.  The weight tiles do
+    // not depend on earlier kernels: they are requested before the dependency wait, x after it.
+    if (warp == 0 && lane < kStages && lane < k_iters) {
+        mbar_expect_tx(full(lane), a.a_bytes + kBBytes);
+        tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, (k_first + lane) * kBK, n0, full(lane));
+    }
     griddep_sync();
     RLM_G_PROBE(2, 0);      // barriers and tensor memory are set up; x may come from the previous kernel
 
     if (warp == 0) {
-        // producer: the first round of the ring is requested by one lane per stage at once (the
-        // stages are free), later rounds by lane 0 as stages are released
-        if (lane < kStages && lane < k_iters) {
-            mbar_expect_tx(full(lane), a.a_bytes + kBBytes);
+        if (lane < kStages && lane < k_iters)
             tma_load_2d(ring_addr + lane * (kABytes + kBBytes), &map_x, (k_first + lane) * kBK, m0, full(lane));
-            tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, (k_first + lane) * kBK, n0, full(lane));
-        }
         __syncwarp();
         RLM_G_PROBE(3, 0);
         if (lane == 0) {
