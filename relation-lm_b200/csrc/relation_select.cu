@@ -18,7 +18,10 @@ namespace rlm {
 #ifdef RLM_TRACE
 // Phase timestamps for working builds (never compiled into the shipped library).
 __device__ long long g_trace[64 * 32];
-#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x < 64) g_trace[blockIdx.x * 32 + (i)] = clock64(); } while (0)
+#ifndef RLM_TRACE_BASE
+#define RLM_TRACE_BASE 0
+#endif
+#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x >= RLM_TRACE_BASE && blockIdx.x < RLM_TRACE_BASE + 64) g_trace[(blockIdx.x - RLM_TRACE_BASE) * 32 + (i)] = clock64(); } while (0)
 #else
 #define RLM_PROBE(i) do { } while (0)
 #endif
@@ -83,13 +86,17 @@ struct SelectArgs {
     int local_window, top_blocks, k_out, strict_valid;
     int query_dtype, key_dtype, stats_dtype, param_dtype;
     int mode;
+    int shared_streams;                  // the partner's staging buffers alias the anchor's (see make_plan)
     Plan plan;
 };
 
 __host__ __device__ inline int align16(int x) { return (x + 15) & ~15; }
 
+// With `shared_streams` (packed mode only) the partner's statistics and local window take the
+// anchor's place once the anchor's first scoring pass has read them: a smaller footprint, so
+// more rows per SM, for launches of many rows.
 __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, int buckets,
-                                          int key_size, int stats_size, int mode) {
+                                          int key_size, int stats_size, int mode, bool shared_streams) {
     Plan p;
     int off = 0;
     int stats_bytes = nb * kD * stats_size;
@@ -97,10 +104,10 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     bool anchor = mode != kPartnerOnly, partner = mode != kAnchorOnly;
     p.a_mean = off; off += anchor ? stats_bytes : 0;
     p.a_std = off; off += anchor ? stats_bytes : 0;
-    p.p_mean = off; off += partner ? stats_bytes : 0;
-    p.p_std = off; off += partner ? stats_bytes : 0;
+    p.p_mean = shared_streams ? p.a_mean : off; off += partner && !shared_streams ? stats_bytes : 0;
+    p.p_std = shared_streams ? p.a_std : off; off += partner && !shared_streams ? stats_bytes : 0;
     p.a_local = off; off += anchor ? local_bytes : 0;
-    p.p_local = off; off += partner ? local_bytes : 0;
+    p.p_local = shared_streams ? p.a_local : off; off += partner && !shared_streams ? local_bytes : 0;
     p.remote = off; off += top * bs * kD * key_size;
     p.pa_row = off; off += 2 * kD * key_size;
     p.queries = off; off += 4 * kD * 4;
@@ -289,7 +296,10 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
                      static_cast<uint32_t>(sel[3 * r + 2] * key_row), bar);
 }
 
-__global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const SelectArgs a) {
+// kMinCtas = 3: the latency-oriented build (decode batches: one wave or less).  kMinCtas = 4:
+// launches of many rows, where rows in flight per SM set the throughput.
+template <int kMinCtas>
+__global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
@@ -369,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
             }
             bulk_g2s(smem_u32(smem + p.a_local) + ldst, static_cast<const char*>(a.anchor_keys) + loff, lbytes, bar_a);
         }
-        if (do_partner) {
+        if (do_partner && !a.shared_streams) {
             mbar_expect_tx(bar_p, 2 * sbytes + lbytes);
             if (sbytes) {
                 bulk_g2s(smem_u32(smem + p.p_mean), static_cast<const char*>(a.partner_mean) + seq_stats, sbytes, bar_p);
@@ -436,6 +446,21 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_kernel(const Sele
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
         RLM_PROBE(6);
+        if (a.shared_streams && tid == kThreads - 1) {
+            // every warp has read the anchor's statistics and local window: the partner's take
+            // their place while the anchor's remote blocks are fetched and scored
+            const uint32_t sbytes = top > 0 ? static_cast<uint32_t>(n_complete * stat_row) : 0u;
+            const uint32_t lbytes = static_cast<uint32_t>(n_local * key_row);
+            const size_t loff = seq_keys + static_cast<size_t>(ls) * key_row;
+            fence_proxy_async();
+            mbar_expect_tx(bar_p, 2 * sbytes + lbytes);
+            if (sbytes) {
+                bulk_g2s(smem_u32(smem + p.p_mean), static_cast<const char*>(a.partner_mean) + seq_stats, sbytes, bar_p);
+                bulk_g2s(smem_u32(smem + p.p_std), static_cast<const char*>(a.partner_std) + seq_stats, sbytes, bar_p);
+            }
+            bulk_g2s(smem_u32(smem + p.p_local) + static_cast<uint32_t>(first_local * key_row),
+                     static_cast<const char*>(a.partner_keys) + loff, lbytes, bar_p);
+        }
         if (top > 0) {
             if (warp == 0) {
                 pick_blocks(bscore, nb, top, bs, ls, sel);
@@ -746,16 +771,29 @@ int launch(SelectArgs& a, void* stream) {
             return RLM_ERR_ALIGN;
         }
     a.block_size = a.max_t / a.n_blocks;
+    a.shared_streams = 0;
     a.plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
-                       dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode);
+                       dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode, false);
+    // More rows than the SMs hold at once: rows in flight set the throughput, so the packed
+    // selector stages the two streams one after the other in the same buffers and the build
+    // with the smaller register budget runs.
+    constexpr int kSms = 148;
+    const int resident = kSmemPerCta / (a.plan.total + 1024 + 2304);
+    const bool many_rows = a.n_rows > kSms * (resident < 3 ? resident : 3);
+    if (many_rows && a.mode == kPacked) {
+        a.shared_streams = 1;
+        a.plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
+                           dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode, true);
+    }
     const Plan& plan = a.plan;
     if (plan.total > kSmemDynamicLimit) {
         set_error("relation_select: block statistics + local window + remote blocks exceed 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
-    int rc = allow_large_smem(reinterpret_cast<const void*>(relation_select_kernel), kSmemPerCta);
+    auto kernel = many_rows ? relation_select_kernel<4> : relation_select_kernel<3>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
-    launch_kernel(relation_select_kernel, dim3(a.n_rows), dim3(kThreads), plan.total, stream, a);
+    launch_kernel(kernel, dim3(a.n_rows), dim3(kThreads), plan.total, stream, a);
     count_launch();
     return check_launch("relation_select_kernel");
 }

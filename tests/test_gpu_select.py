@@ -132,6 +132,43 @@ def test_rows_form_equals_decode_form_at_every_position(strict):
     assert_status_clear()
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+def test_many_row_launch_equals_short_launches_and_oracle(dtype):
+    """A launch of more rows than the SMs hold at once takes the build that stages the partner
+    stream in the anchor stream's buffers; it must give what launches of 128 rows (the
+    latency-oriented build) give, and what the oracle gives on a sample of the rows."""
+    from relation_lm.kernels.relation_select import relation_select_packed_rows
+
+    B, T, NB, L, top, K = 4, 512, 16, 64, 2, 8
+    case = {"kind": "select", "seed": 7150, "batch": B, "rows": B * T, "context": T, "blocks": NB,
+            "local_window": L, "top_blocks": top, "k_out": K, "strict_valid": False, "dtype": dtype}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(T)
+    row_pos = torch.arange(T, dtype=torch.int32).repeat(B)
+    args = select_args(xg)
+    whole = relation_select_packed_rows(*args, row_batch.cuda(), row_pos.cuda(), L, top, K, False)
+    rows = B * T
+    for r0 in range(0, rows, 128):
+        sl = slice(r0, r0 + 128)
+        part_args = list(args)
+        for i in (0, 2, 7):       # anchor query, anchor router query, partner base: one row per query
+            part_args[i] = args[i][sl].contiguous()
+        part = relation_select_packed_rows(*part_args, row_batch[sl].cuda(), row_pos[sl].cuda(), L, top, K, False)
+        for w, q in zip(whole, part):
+            assert torch.equal(w[sl], q), r0
+    sample = torch.arange(5, rows, 37)
+    cpu_args = list(select_args(x))
+    for i in (0, 2, 7):
+        cpu_args[i] = cpu_args[i][sample].contiguous()
+    want = oracle.relation_select(*cpu_args, 0, L, top, K, False, row_batch=row_batch[sample],
+                                  row_pos=row_pos[sample])
+    assert torch.equal(whole[0].cpu()[sample], want[0]) and torch.equal(whole[2].cpu()[sample], want[2])
+    assert_scores_equal(whole[1][sample.cuda()], want[1])
+    assert_scores_equal(whole[3][sample.cuda()], want[3])
+    assert_status_clear()
+
+
 def test_full_window_selection_is_dense_argmax_and_topk():
     """With the window covering the whole history and no remote blocks the routed selection
     must equal dense argmax / top-k of causal scores (the reference's dense models,
