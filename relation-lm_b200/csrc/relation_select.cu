@@ -3,11 +3,12 @@
 // One CTA per query row.  Everything a row needs is staged in shared memory by
 // untiled bulk (TMA) copies that complete on mbarriers: both streams' block
 // statistics and local key windows are requested at kernel entry; the chosen
-// remote blocks and the partner-anchor cache row are requested as soon as the
-// indices that address them are known.  Scores are computed from shared memory
-// with 8 lanes per 64-wide row (16-byte reads, bank-conflict free for 16-bit
-// caches) in the canonical order documented in rlm_common.cuh, so the selected
-// indices do not depend on the launch geometry.
+// remote blocks are requested as soon as the block ranks are known, and the one
+// partner-anchor cache row is read directly from global memory.  Key rows are
+// scored from shared memory a lane per 64-wide row, block statistics with 8
+// lanes per block (16-byte reads, bank-conflict free for 16-bit caches), in
+// the canonical order documented in rlm_common.cuh, so the selected indices
+// do not depend on the launch geometry.
 //
 // Semantics follow src/relation_lm/kernels/relation_select.py:50-308 and
 // src/relation_lm/kernels/triton_select.py:23-252 of the reference project.
@@ -16,14 +17,22 @@
 
 namespace rlm {
 #ifdef RLM_TRACE
-// Phase timestamps for working builds (never compiled into the shipped library).
+// Phase timestamps for working builds (never compiled into the shipped library): kept in shared
+// memory while the CTA runs (a global store in front of a barrier would distort the phase it
+// measures) and copied out by thread 0 at its last probe.
 __device__ long long g_trace[64 * 32];
 #ifndef RLM_TRACE_BASE
 #define RLM_TRACE_BASE 0
 #endif
-#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x >= RLM_TRACE_BASE && blockIdx.x < RLM_TRACE_BASE + 64) g_trace[(blockIdx.x - RLM_TRACE_BASE) * 32 + (i)] = clock64(); } while (0)
+#define RLM_TRACE_DECL __shared__ long long trace_s[32]
+#define RLM_PROBE_T(i, thread) do { if (threadIdx.x == (thread)) trace_s[(i)] = clock64(); } while (0)
+#define RLM_PROBE(i) do { if (threadIdx.x == 0) { trace_s[(i)] = clock64(); \
+    if ((i) == 21 && blockIdx.x >= RLM_TRACE_BASE && blockIdx.x < RLM_TRACE_BASE + 64) \
+        for (int k_ = 0; k_ < 32; ++k_) g_trace[(blockIdx.x - RLM_TRACE_BASE) * 32 + k_] = trace_s[k_]; } } while (0)
 #else
+#define RLM_TRACE_DECL
 #define RLM_PROBE(i) do { } while (0)
+#define RLM_PROBE_T(i, thread) do { } while (0)
 #endif
 namespace {
 
@@ -44,13 +53,12 @@ struct Plan {
     int a_mean, a_std, p_mean, p_std;   // [NB,64] stats elements
     int a_local, p_local;               // [L,64] key elements
     int remote;                         // [TOP*BS,64] key elements (anchor phase, then partner phase)
-    int pa_row;                         // [128] key elements
     int queries;                        // f32: aq[64] arq[64] pq[64] prq[64]
     int params;                         // f32: softplus(gamma) a[4] p[4], bias a[4*buckets] p[4*buckets]
     int block_scores;                   // f32 [NB]
     int cand;                           // f32 [L + TOP*BS]
     int sel;                            // int [3*TOP]: block, usable, valid row count
-    int bars;                           // 5 mbarriers
+    int bars;                           // 4 mbarriers
     int total;
 };
 
@@ -109,28 +117,27 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     p.a_local = off; off += anchor ? local_bytes : 0;
     p.p_local = shared_streams ? p.a_local : off; off += partner && !shared_streams ? local_bytes : 0;
     p.remote = off; off += top * bs * kD * key_size;
-    p.pa_row = off; off += 2 * kD * key_size;
     p.queries = off; off += 4 * kD * 4;
     p.params = off; off += align16(8 * buckets * 4);
     p.block_scores = off; off += align16(((nb + 3) & ~3) * 4);
     p.cand = off; off += align16((local + top * bs) * 4);
     p.sel = off; off += align16(3 * (top > 0 ? top : 1) * 4);
-    p.bars = off; off += 5 * 8;
+    p.bars = off; off += 4 * 8;
     p.total = align16(off);
     return p;
 }
 
-// ---- lane-per-row scoring
+// ---- key-row scoring
 //
-// A lane owns a whole 64-wide row: it evaluates the canonical dot (eight 8-element fma chains
-// p0..p7 combined as ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7))) by itself, with no shuffles, so a
-// warp scores 32 rows per pass.  Rows are 128 (or 256) bytes apart in shared memory, so the
-// lanes of a quarter warp must not read the same 16-byte chunk index at the same time: step jj
-// of lane l handles the chunk pair of index (jj + l) & 3, lanes 4..7 of each group of eight
-// taking the pair's second chunk first.  Because a + b == b + a exactly, the pair sums and the
-// final tree are bit-identical to the fixed order; tree4() undoes the rotation.
-
-__device__ __forceinline__ int rot_chunk(int jj, int lane) { return 2 * ((jj + lane) & 3) + ((lane >> 2) & 1); }
+// The canonical dot of a 64-wide row is eight 8-element fma chains p0..p7 combined as
+// ((p0+p1)+(p2+p3))+((p4+p5)+(p6+p7)).  One, two or four lanes share a row (kLpr): with many
+// rows per warp a lane owns a whole row and needs no shuffles; with few rows the chains are
+// spread over two or four lanes (two xor-shuffle additions at most) so that all lanes of the
+// group work and the dependent chain per lane is shorter.  Rows are 128 (or 256) bytes apart in
+// shared memory, so the lanes of a quarter warp must not read the same 16-byte chunk index at
+// the same time: the order in which a lane walks its chunks is rotated by its row number.
+// Because a + b == b + a exactly, the sums are bit-identical to the fixed order whatever the
+// split; tree4() undoes the rotation.
 
 // (s0 + s1) + (s2 + s3) from x[jj] = s[(jj + r) & 3]
 __device__ __forceinline__ float tree4(const float (&x)[4], int r) {
@@ -138,6 +145,13 @@ __device__ __forceinline__ float tree4(const float (&x)[4], int r) {
     const float a = __fadd_rn(odd ? x[3] : x[0], odd ? x[0] : x[1]);
     const float b = __fadd_rn(odd ? x[1] : x[2], odd ? x[2] : x[3]);
     return __fadd_rn(a, b);
+}
+
+__device__ __forceinline__ float chunk_dot(const unsigned char* row, const float* query, int c, int key_dtype) {
+    float k[8], q[8];
+    load8(row, 8 * c, key_dtype, k);
+    load8(query, 8 * c, RLM_F32, q);
+    return seg8(k, q);
 }
 
 // Scores staged key rows against the query held in shared memory (f32 [64]) with the
@@ -148,17 +162,21 @@ __device__ __forceinline__ float tree4(const float (&x)[4], int r) {
 // The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand`
 // the scores go to candidate slots slot0 + r; in every case the warp's best (score, lowest
 // position on ties) is folded into (best_key, best_pos), identical in all lanes.
-__device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
-                                        const int* sel, int bs, int first_valid, int pos0,
-                                        int exclude, const int* excl, int n_excl, const float* query,
-                                        float* cand, int slot0, int wi, int nw, uint32_t& best_key,
-                                        int& best_pos) {
+template <bool kBf16, int kLpr>
+__device__ __noinline__ void score_rows_split(const unsigned char* rows, int key_dtype_arg, int n_rows,
+                                              const int* sel, int bs, int first_valid, int pos0,
+                                              int exclude, const int* excl, int n_excl, const float* query,
+                                              float* cand, int slot0, int wi, int nw, uint32_t& best_key,
+                                              int& best_pos) {
+    constexpr int kRows = 32 / kLpr;                 // rows per warp pass
     const int lane = threadIdx.x & 31;
+    const int sub = lane & (kLpr - 1), rl = lane / kLpr;
+    const int key_dtype = kBf16 ? RLM_BF16 : key_dtype_arg;
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
-    for (int base = wi * 32; base < n_rows; base += 32 * nw) {
-        const int r = base + lane;
+    for (int base = wi * kRows; base < n_rows; base += kRows * nw) {
+        const int r = base + rl;
         int pos;
         bool valid;
         if (sel) {
@@ -172,23 +190,35 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
         }
         valid = valid && pos != exclude;
         for (int x = 0; x < n_excl; ++x) valid = valid && pos != excl[x];
-        float sc = kNegInf;
+        float part = 0.0f;
         if (valid) {
             const unsigned char* row = rows + static_cast<size_t>(r) * row_bytes;
-            float pair[4];
+            if (kLpr == 1) {
+                // pair sums (p0+p1) .. (p6+p7), pair index rotated by the row, lanes 4..7 of
+                // each group of eight taking the pair's second chunk first
+                float pair[4];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int c0 = rot_chunk(jj, lane), c1 = c0 ^ 1;
-                float k0[8], k1[8], q0[8], q1[8];
-                load8(row, 8 * c0, key_dtype, k0);
-                load8(row, 8 * c1, key_dtype, k1);
-                load8(query, 8 * c0, RLM_F32, q0);
-                load8(query, 8 * c1, RLM_F32, q1);
-                pair[jj] = __fadd_rn(seg8(k0, q0), seg8(k1, q1));
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int c0 = 2 * ((jj + rl) & 3) + ((rl >> 2) & 1);
+                    pair[jj] = __fadd_rn(chunk_dot(row, query, c0, key_dtype), chunk_dot(row, query, c0 ^ 1, key_dtype));
+                }
+                part = tree4(pair, rl & 3);
+            } else if (kLpr == 2) {
+                // this lane: (p0+p1)+(p2+p3) or (p4+p5)+(p6+p7), chunk order rotated by the row
+                float x[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) x[jj] = chunk_dot(row, query, 4 * sub + ((jj + rl) & 3), key_dtype);
+                part = tree4(x, rl & 3);
+            } else {
+                // this lane: one pair sum, odd rows taking the second chunk first
+                const int c0 = 2 * sub + (rl & 1);
+                part = __fadd_rn(chunk_dot(row, query, c0, key_dtype), chunk_dot(row, query, c0 ^ 1, key_dtype));
             }
-            sc = __fmul_rn(tree4(pair, lane & 3), 0.125f);
         }
-        if (cand && r < n_rows) cand[slot0 + r] = sc;
+        if (kLpr >= 2) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 1));
+        if (kLpr == 4) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 2));
+        const float sc = valid ? __fmul_rn(part, 0.125f) : kNegInf;
+        if (cand && r < n_rows && sub == 0) cand[slot0 + r] = sc;
         const uint32_t key = float_key(sc);
         if (valid && (key > my_key || my_pos == 0x7fffffff || (key == my_key && pos < my_pos))) {
             my_key = key;
@@ -203,14 +233,36 @@ __device__ __noinline__ void score_rows(const unsigned char* rows, int key_dtype
     }
 }
 
+// Picks the split that keeps every lane of the group busy in the fewest passes (launches of at
+// most one CTA per SM, where a row's latency is what counts).
+template <bool kBf16>
+__device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
+                                           const int* sel, int bs, int first_valid, int pos0,
+                                           int exclude, const int* excl, int n_excl, const float* query,
+                                           float* cand, int slot0, int wi, int nw, uint32_t& best_key,
+                                           int& best_pos) {
+    const int lanes = gridDim.x <= 148 ? 32 * nw : 0;   // a row per lane when CTAs share the SMs: fewer instructions in total
+    if (4 * n_rows <= lanes)
+        score_rows_split<kBf16, 4>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+                                   query, cand, slot0, wi, nw, best_key, best_pos);
+    else if (2 * n_rows <= lanes)
+        score_rows_split<kBf16, 2>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+                                   query, cand, slot0, wi, nw, best_key, best_pos);
+    else
+        score_rows_split<kBf16, 1>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+                                   query, cand, slot0, wi, nw, best_key, best_pos);
+}
+
 // Block scores of the first `n_complete` blocks with the `nw` warps of a group; the other
 // entries of `out` (up to the next multiple of four) are set to -inf.
+template <bool kBf16>
 __device__ __noinline__ void score_blocks(const unsigned char* mean, const unsigned char* stdv,
-                                          int stats_dtype, int nb, int n_complete, int bs, int t,
+                                          int stats_dtype_arg, int nb, int n_complete, int bs, int t,
                                           int ls, int strict, int buckets, const float* rq,
                                           float sp, const float* bias, float* out, int wi, int nw) {
     const int lane = threadIdx.x & 31;
     const int j = lane & 7, sub = lane >> 3, head = j >> 1;
+    const int stats_dtype = kBf16 ? RLM_BF16 : stats_dtype_arg;
     const int row_bytes = kD * (stats_dtype == RLM_F32 ? 4 : 2);
     float q[8], aq[8];
 #pragma unroll
@@ -283,6 +335,65 @@ __device__ __noinline__ void pick_blocks(const float* scores, int nb, int top, i
     __syncwarp();
 }
 
+// Exact top-K of up to 32 * kN candidate scores by one warp.  Lane l holds slots kN*l ..
+// kN*l + kN - 1 as (score key, inverted slot) composites sorted in descending order (a fixed
+// compare-exchange network), so its head is its best remaining candidate.  Each of the K rounds
+// takes the largest head of the warp (one redux); among equal keys the lowest lane wins, which is
+// the lowest slot because lanes hold ascending slot ranges and equal keys are sorted by slot
+// inside a lane.  The winner pops its head.  Slots past the candidates hold key 0 and never
+// beat a score; a result whose score is -inf (or missing) reports position t - L + 1.
+template <int kN>
+__device__ __forceinline__ void topk_tournament(const float* cand, int cap4, int K, int L, int t, int bs,
+                                                int bs_shift, const int* sel, int32_t* out_pos, float* out_score) {
+    const int lane = threadIdx.x & 31;
+    const float4* cand4 = reinterpret_cast<const float4*>(cand);
+    uint64_t c[kN];
+#pragma unroll
+    for (int h = 0; h < kN / 4; ++h) {
+        const int g = lane * (kN / 4) + h;
+        const bool in = 4 * g < cap4;
+        const float4 v = in ? cand4[g] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t key = in ? float_key(x[i] + 0.0f) : 0u;       // -0 and +0 tie
+            c[4 * h + i] = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(4 * g + i));
+        }
+    }
+#define RLM_CE(i, j) do { const uint64_t hi_ = c[i] > c[j] ? c[i] : c[j], lo_ = c[i] > c[j] ? c[j] : c[i]; c[i] = hi_; c[j] = lo_; } while (0)
+    if (kN == 4) {
+        RLM_CE(0, 1); RLM_CE(2, 3); RLM_CE(0, 2); RLM_CE(1, 3); RLM_CE(1, 2);
+    } else {
+        RLM_CE(0, 1); RLM_CE(2, 3); RLM_CE(4, 5); RLM_CE(6, 7); RLM_CE(0, 2); RLM_CE(1, 3); RLM_CE(4, 6);
+        RLM_CE(5, 7); RLM_CE(1, 2); RLM_CE(5, 6); RLM_CE(0, 4); RLM_CE(3, 7); RLM_CE(1, 5); RLM_CE(2, 6);
+        RLM_CE(1, 4); RLM_CE(3, 6); RLM_CE(2, 4); RLM_CE(3, 5); RLM_CE(3, 4);
+    }
+#undef RLM_CE
+    uint32_t won_key = 0, won_slot = 0;
+    for (int r = 0; r < K; ++r) {
+        const uint32_t head = static_cast<uint32_t>(c[0] >> 32);
+        const uint32_t best = __reduce_max_sync(0xffffffffu, head);
+        const int w = __ffs(__ballot_sync(0xffffffffu, head == best)) - 1;
+        const uint32_t slot = 0xffffffffu - __shfl_sync(0xffffffffu, static_cast<uint32_t>(c[0]), w);
+        if (lane == r) { won_key = best; won_slot = slot; }
+        if (lane == w) {
+#pragma unroll
+            for (int i = 0; i + 1 < kN; ++i) c[i] = c[i + 1];
+            c[kN - 1] = 0;
+        }
+    }
+    if (lane < K) {
+        const float sc = won_key == 0u ? kNegInf : cand[won_slot];
+        const int cs = static_cast<int>(won_slot);
+        int pos;
+        if (!(sc > kNegInf)) pos = t - L + 1;
+        else if (cs < L) pos = t - L + 1 + cs;
+        else { const int rr = bs_shift >= 0 ? (cs - L) >> bs_shift : (cs - L) / bs; pos = sel[3 * rr] * bs + (cs - L - rr * bs); }
+        out_pos[lane] = pos;
+        out_score[lane] = sc;
+    }
+}
+
 __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned char* dst,
                                              const int* sel, int top, int bs, size_t key_row,
                                              size_t seq_keys, uint32_t bar) {
@@ -297,8 +408,10 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
 }
 
 // kMinCtas = 3: the latency-oriented build (decode batches: one wave or less).  kMinCtas = 4:
-// launches of many rows, where rows in flight per SM set the throughput.
-template <int kMinCtas>
+// launches of many rows, where rows in flight per SM set the throughput.  kBf16: queries, key
+// caches and block statistics are all bf16 (the decode configuration); the dtype branches
+// fold away, which matters because a row's time is largely instruction fetch.
+template <int kMinCtas, bool kBf16>
 __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
@@ -309,8 +422,11 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     __shared__ uint32_t group_max[2 * kWarps];
     __shared__ int short_count;
     if (threadIdx.x == 0) short_count = 0;
+    RLM_TRACE_DECL;
     RLM_PROBE(0);
     const int row = blockIdx.x;
+    const int key_dtype = kBf16 ? RLM_BF16 : a.key_dtype, stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype,
+              query_dtype = kBf16 ? RLM_BF16 : a.query_dtype;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool do_anchor = a.mode != kPartnerOnly, do_partner = a.mode != kAnchorOnly;
     const int buckets4 = 4 * a.buckets;
@@ -339,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     RLM_PROBE(1);
     const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks;
     const int bs_shift = (bs & (bs - 1)) == 0 ? 31 - __clz(bs) : -1;
-    const int ks = a.key_dtype == RLM_F32 ? 4 : 2, ss = a.stats_dtype == RLM_F32 ? 4 : 2;
+    const int ks = key_dtype == RLM_F32 ? 4 : 2, ss = stats_dtype == RLM_F32 ? 4 : 2;
     const Plan& p = a.plan;
 
     float* queries = reinterpret_cast<float*>(smem + p.queries);
@@ -350,8 +466,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     float* cand = reinterpret_cast<float*>(smem + p.cand);
     int* sel = reinterpret_cast<int*>(smem + p.sel);
     const uint32_t bars = smem_u32(smem + p.bars);
-    const uint32_t bar_a = bars, bar_p = bars + 8, bar_ra = bars + 16, bar_row = bars + 24,
-                   bar_rp = bars + 32;
+    const uint32_t bar_a = bars, bar_p = bars + 8, bar_ra = bars + 16, bar_rp = bars + 24;
 
     const int ls = max(t - L + 1, 0);
     const int first_local = ls - (t - L + 1);       // first valid slot of the local window
@@ -365,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     if (tid == 0) {
         // the issuing thread initialises the barriers itself; the others first touch them
         // after the block-wide barrier below
-        for (int i = 0; i < 5; ++i) mbar_init(bars + 8 * i, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bars + 8 * i, 1);
         fence_barrier_init();
         const uint32_t sbytes = top > 0 ? static_cast<uint32_t>(n_complete * stat_row) : 0u;
         const uint32_t lbytes = static_cast<uint32_t>(n_local * key_row);
@@ -392,15 +507,15 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     // this thread's query element
     float qv = 0.0f;
     if (a.mode == kPacked) {
-        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
-        else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, a.query_dtype);
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, query_dtype);
+        else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, query_dtype);
     } else if (a.mode == kAnchorOnly) {
-        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, a.query_dtype);
+        if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, query_dtype);
     } else {
-        if (tid < kD) qv = load_scalar(a.partner_base, row * a.pbase_stride + tid, a.query_dtype);
-        else if (tid < 2 * kD) qv = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, a.query_dtype);
+        if (tid < kD) qv = load_scalar(a.partner_base, row * a.pbase_stride + tid, query_dtype);
+        else if (tid < 2 * kD) qv = load_scalar(a.partner_router_query, row * a.prq_stride + tid - kD, query_dtype);
     }
     // queries[0..255]: packed = aq | arq | partner base (exact 64 | router 64);
     // partner-only = (unused 128) | pq | prq; anchor-only = aq | arq
@@ -438,11 +553,13 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         uint32_t bk = 0;
         int bp = 0x7fffffff;
         if (warp < block_warps)
-            score_blocks(smem + p.a_mean, smem + p.a_std, a.stats_dtype, nb, n_complete, bs, t, ls,
+            score_blocks<kBf16>(smem + p.a_mean, smem + p.a_std, stats_dtype, nb, n_complete, bs, t, ls,
                          a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
-            score_rows(smem + p.a_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
+            score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
                        n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp);
+        RLM_PROBE_T(22, 0);
+        RLM_PROBE_T(23, 128);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
         RLM_PROBE(6);
@@ -480,8 +597,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             RLM_PROBE(10);
             bk = 0;
             bp = 0x7fffffff;
-            score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+            score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
                        nullptr, 0, warp, kWarps, bk, bp);
+            RLM_PROBE_T(24, 0);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             __syncthreads();
             RLM_PROBE(11);
@@ -503,22 +621,15 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         }
         if (!do_partner) return;
         RLM_PROBE(12);
-        if (tid == 0) {
-            mbar_expect_tx(bar_row, static_cast<uint32_t>(2 * key_row));
-            bulk_g2s(smem_u32(smem + p.pa_row),
-                     static_cast<const char*>(a.partner_anchor_cache) + (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * key_row,
-                     static_cast<uint32_t>(2 * key_row), bar_row);
-        }
-        bool ok_row = mbar_wait(bar_row, 0);
-        if (__syncthreads_or(!ok_row)) {
-            if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
-            return;
-        }
-        RLM_PROBE(13);
+        // The anchor's contribution to the partner queries: one 2 x 64 row of the partner-anchor
+        // cache, read straight from global memory by the threads that own the elements (one
+        // dependent round trip, no staging).  The block-wide barrier below publishes pq / prq.
         if (tid < 2 * kD) {
-            float add = load_scalar(smem + p.pa_row, tid, a.key_dtype);
+            const float add = load_scalar(a.partner_anchor_cache,
+                                          (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * kD + tid, key_dtype);
             pq[tid] = __fadd_rn(pq[tid], add);   // pq[64..127] is prq
         }
+        RLM_PROBE(13);
     } else {
         anchor_pos = a.anchor_index_in[row];
     }
@@ -532,10 +643,10 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     uint32_t dk = 0;
     int dp = 0x7fffffff;
     if (warp < block_warps)
-        score_blocks(smem + p.p_mean, smem + p.p_std, a.stats_dtype, nb, n_complete, bs, t, ls,
+        score_blocks<kBf16>(smem + p.p_mean, smem + p.p_std, stats_dtype, nb, n_complete, bs, t, ls,
                      a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
-        score_rows(smem + p.p_local, a.key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
+        score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp);
     __syncthreads();
     RLM_PROBE(15);
@@ -557,7 +668,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             return;
         }
         RLM_PROBE(19);
-        score_rows(smem + p.remote, a.key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+        score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
                    cand, L, warp, kWarps, dk, dp);
         __syncthreads();
         RLM_PROBE(20);
@@ -567,6 +678,19 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     // threads share one candidate and scan interleaved groups of four slots.  Slots past the
     // valid candidates carry score -inf and the position of candidate slot 0.
     const int K = a.k_out;
+    if (cap4 <= 256) {
+        // Up to 256 candidate slots: warp 0 holds them all in registers (see topk_tournament)
+        if (warp == 0) {
+            if (cap4 <= 128)
+                topk_tournament<4>(cand, cap4, K, L, t, bs, bs_shift, sel, a.out_partner + static_cast<size_t>(row) * K,
+                                   a.out_partner_score + static_cast<size_t>(row) * K);
+            else
+                topk_tournament<8>(cand, cap4, K, L, t, bs, bs_shift, sel, a.out_partner + static_cast<size_t>(row) * K,
+                                   a.out_partner_score + static_cast<size_t>(row) * K);
+            RLM_PROBE(21);
+        }
+        return;
+    }
     // Threshold filter: the K-th largest of the sixteen half-warp maxima is a lower bound of
     // the K-th largest score, so only candidates at or above it can be selected.  They are
     // compacted into a short list and ranked exactly there; when the list is long (many equal
@@ -625,8 +749,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             return;
         }
     }
-    if (cap > 128) {
-        // Large candidate sets: tournament.  Each warp extracts the top K of the slots it
+    {
+        // Fallback for large candidate sets: tournament through shared memory.  Each warp extracts the top K of the slots it
         // owns (K rounds of redux arg-max, knocking winners out of the table); warp 0 then
         // extracts the top K of the 8 K survivors.  Any global top-K candidate is among the
         // top K of its own warp, and (score, lowest slot) ordering is kept at both levels.
@@ -672,58 +796,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             }
         }
         RLM_PROBE(21);
-        return;
     }
-    // Small candidate sets: exact top-K by rank counting.  A candidate's output slot is the
-    // number of candidates that beat it (higher score, or equal score in an earlier slot).
-    // `parts` adjacent threads share one candidate and scan interleaved groups of four slots.
-    // Slots past the valid candidates carry score -inf and the position of candidate slot 0.
-    int parts = 1;
-    while (parts < 8 && parts * 2 * cap <= kThreads) parts *= 2;
-    const float4* cand4 = reinterpret_cast<const float4*>(cand);
-    const int part = tid & (parts - 1);
-    const int n_groups = cap4 >> 2;
-    for (int c0 = 0; c0 < cap; c0 += kThreads / parts) {
-        const int c = c0 + tid / parts;
-        const bool live = c < cap;
-        const float mine = live ? cand[c] : 0.0f;
-        int rank = 0;
-        if (live) {
-            const int home = c >> 2;                       // group of four that holds slot c
-            int g = part;
-#pragma unroll 4
-            for (; g < home; g += parts) {                  // earlier slots win ties
-                const float4 o = cand4[g];
-                rank += (o.x >= mine) + (o.y >= mine) + (o.z >= mine) + (o.w >= mine);
-            }
-            if (g == home) {
-                const float4 o = cand4[g];
-                const int m0 = g << 2;
-                rank += (o.x > mine || (o.x == mine && m0 < c)) + (o.y > mine || (o.y == mine && m0 + 1 < c)) +
-                        (o.z > mine || (o.z == mine && m0 + 2 < c)) + (o.w > mine || (o.w == mine && m0 + 3 < c));
-                g += parts;
-            }
-#pragma unroll 4
-            for (; g < n_groups; g += parts) {              // later slots lose ties
-                const float4 o = cand4[g];
-                rank += (o.x > mine) + (o.y > mine) + (o.z > mine) + (o.w > mine);
-            }
-        }
-        for (int sft = 1; sft < parts; sft <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, sft);
-        if (live && part == 0 && rank < K) {
-            int pos;
-            if (!(mine > kNegInf)) pos = t - L + 1;
-            else if (c < L) pos = t - L + 1 + c;
-            else { int r = bs_shift >= 0 ? (c - L) >> bs_shift : (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
-            a.out_partner[static_cast<size_t>(row) * K + rank] = pos;
-            a.out_partner_score[static_cast<size_t>(row) * K + rank] = mine;
-        }
-    }
-    for (int k = cap + tid; k < K; k += kThreads) {
-        a.out_partner[static_cast<size_t>(row) * K + k] = t - L + 1;
-        a.out_partner_score[static_cast<size_t>(row) * K + k] = kNegInf;
-    }
-    RLM_PROBE(21);
 }
 
 int launch(SelectArgs& a, void* stream) {
@@ -790,7 +863,9 @@ int launch(SelectArgs& a, void* stream) {
         set_error("relation_select: block statistics + local window + remote blocks exceed 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
-    auto kernel = many_rows ? relation_select_kernel<4> : relation_select_kernel<3>;
+    const bool bf16 = a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
+    auto kernel = many_rows ? (bf16 ? relation_select_kernel<4, true> : relation_select_kernel<4, false>)
+                            : (bf16 ? relation_select_kernel<3, true> : relation_select_kernel<3, false>);
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     launch_kernel(kernel, dim3(a.n_rows), dim3(kThreads), plan.total, stream, a);
