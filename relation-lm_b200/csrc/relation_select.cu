@@ -394,6 +394,49 @@ __device__ __forceinline__ void topk_tournament(const float* cand, int cap4, int
     }
 }
 
+// Warp 0, at most 128 blocks and 32 remote blocks: block picking and the bulk-copy requests in
+// one pass.  Lane l holds the scores of blocks l, l + 32, ...; each of the `top` rounds takes
+// the best remaining block of the warp (two redux instructions; ties to the lowest index) and
+// hands it to lane `round`, which then requests its own block, after lane 0 has posted the byte
+// count of all of them.  Same result as pick_blocks + issue_remote.
+__device__ __noinline__ void pick_and_issue(const float* scores, int nb, int top, int bs, int ls, int* sel,
+                                            const unsigned char* keys, unsigned char* dst, size_t key_row,
+                                            size_t seq_keys, uint32_t bar) {
+    const int lane = threadIdx.x & 31;
+    uint32_t k[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) k[i] = lane + 32 * i < nb ? float_key(scores[lane + 32 * i]) : 0u;
+    int my_block = 0, my_rows = 0;
+    for (int r = 0; r < top; ++r) {
+        uint32_t bk = 0;
+        int bn = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (k[i] > bk) { bk = k[i]; bn = lane + 32 * i; }
+        warp_argmax_key(bk, bn);
+        if (!(key_float(bk) > -1.0e30f)) break;          // no usable block is left
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (lane + 32 * i == bn) k[i] = 0u;
+        if (lane == r) {
+            int rows = ls - bn * bs;
+            my_rows = rows < 0 ? 0 : (rows > bs ? bs : rows);
+            my_block = bn;
+        }
+    }
+    if (lane < top) { sel[3 * lane] = my_block; sel[3 * lane + 1] = 1; sel[3 * lane + 2] = my_rows; }
+    const uint32_t bytes = static_cast<uint32_t>(my_rows * key_row);
+    const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+    // The destination may have been read (never written) through the generic proxy before: those
+    // reads were ordered before this point by the block-wide barrier, as in any ring of bulk-copy
+    // stages released by its consumers, so no proxy fence is needed.
+    if (lane == 0) mbar_expect_tx(bar, total);
+    __syncwarp();
+    if (my_rows > 0)
+        bulk_g2s(smem_u32(dst) + static_cast<uint32_t>(lane * bs * key_row),
+                 keys + seq_keys + static_cast<size_t>(my_block) * bs * key_row, bytes, bar);
+}
+
 __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned char* dst,
                                              const int* sel, int top, int bs, size_t key_row,
                                              size_t seq_keys, uint32_t bar) {
@@ -580,11 +623,15 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         }
         if (top > 0) {
             if (warp == 0) {
-                pick_blocks(bscore, nb, top, bs, ls, sel);
-                RLM_PROBE(7);
-                if (lane == 0)
-                    issue_remote(static_cast<const unsigned char*>(a.anchor_keys), smem + p.remote, sel,
-                                 top, bs, key_row, seq_keys, bar_ra);
+                if (nb <= 128 && top <= 32) {
+                    pick_and_issue(bscore, nb, top, bs, ls, sel, static_cast<const unsigned char*>(a.anchor_keys),
+                                   smem + p.remote, key_row, seq_keys, bar_ra);
+                } else {
+                    pick_blocks(bscore, nb, top, bs, ls, sel);
+                    if (lane == 0)
+                        issue_remote(static_cast<const unsigned char*>(a.anchor_keys), smem + p.remote, sel,
+                                     top, bs, key_row, seq_keys, bar_ra);
+                }
                 RLM_PROBE(8);
             }
             __syncthreads();
@@ -652,12 +699,16 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     RLM_PROBE(15);
     if (top > 0) {
         if (warp == 0) {
-            pick_blocks(bscore, nb, top, bs, ls, sel);
-            RLM_PROBE(16);
-            if (lane == 0) {
-                fence_proxy_async();   // the anchor phase read this buffer through the generic proxy
-                issue_remote(static_cast<const unsigned char*>(a.partner_keys), smem + p.remote, sel, top,
-                             bs, key_row, seq_keys, bar_rp);
+            if (nb <= 128 && top <= 32) {
+                pick_and_issue(bscore, nb, top, bs, ls, sel, static_cast<const unsigned char*>(a.partner_keys),
+                               smem + p.remote, key_row, seq_keys, bar_rp);
+            } else {
+                pick_blocks(bscore, nb, top, bs, ls, sel);
+                if (lane == 0) {
+                    fence_proxy_async();   // the anchor phase read this buffer through the generic proxy
+                    issue_remote(static_cast<const unsigned char*>(a.partner_keys), smem + p.remote, sel, top,
+                                 bs, key_row, seq_keys, bar_rp);
+                }
             }
             RLM_PROBE(17);
         }
