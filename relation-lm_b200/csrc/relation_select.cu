@@ -24,7 +24,8 @@ __device__ long long g_trace[64 * 32];
 #ifndef RLM_TRACE_BASE
 #define RLM_TRACE_BASE 0
 #endif
-#define RLM_TRACE_DECL __shared__ long long trace_s[32]
+__shared__ long long trace_s[32];
+#define RLM_TRACE_DECL
 #define RLM_PROBE_T(i, thread) do { if (threadIdx.x == (thread)) trace_s[(i)] = clock64(); } while (0)
 #define RLM_PROBE(i) do { if (threadIdx.x == 0) { trace_s[(i)] = clock64(); \
     if ((i) == 21 && blockIdx.x >= RLM_TRACE_BASE && blockIdx.x < RLM_TRACE_BASE + 64) \
@@ -159,7 +160,9 @@ __device__ __forceinline__ float chunk_dot(const unsigned char* row, const float
 //   local window (sel == nullptr): row r is position pos0 + r, valid from `first_valid` on;
 //   remote blocks (sel != nullptr): row r belongs to the block of rank r / bs at offset
 //     o = r % bs, position sel[3 rank] * bs + o, valid while o < sel[3 rank + 2].
-// The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With `cand`
+// The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With a
+// barrier address in `bar` the rows are still being copied: the warp waits for them after it has
+// worked out its first rows' positions (`arrived` = false when the wait gave up).  With `cand`
 // the scores go to candidate slots slot0 + r; in every case the warp's best (score, lowest
 // position on ties) is folded into (best_key, best_pos), identical in all lanes.
 template <bool kBf16, int kLpr>
@@ -167,7 +170,7 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
                                               const int* sel, int bs, int first_valid, int pos0,
                                               int exclude, const int* excl, int n_excl, const float* query,
                                               float* cand, int slot0, int wi, int nw, uint32_t& best_key,
-                                              int& best_pos) {
+                                              int& best_pos, uint32_t bar, bool& arrived) {
     constexpr int kRows = 32 / kLpr;                 // rows per warp pass
     const int lane = threadIdx.x & 31;
     const int sub = lane & (kLpr - 1), rl = lane / kLpr;
@@ -175,12 +178,13 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
+    RLM_PROBE_T(25, 128);
     for (int base = wi * kRows; base < n_rows; base += kRows * nw) {
         const int r = base + rl;
         int pos;
         bool valid;
         if (sel) {
-            const int rank = r / bs, o = r - rank * bs;
+            const int rank = (bs & (bs - 1)) == 0 ? r >> (31 - __clz(bs)) : r / bs, o = r - rank * bs;
             const bool in = r < n_rows;
             pos = in ? sel[3 * rank] * bs + o : -1;
             valid = in && o < sel[3 * rank + 2];
@@ -191,6 +195,12 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         valid = valid && pos != exclude;
         for (int x = 0; x < n_excl; ++x) valid = valid && pos != excl[x];
         float part = 0.0f;
+        RLM_PROBE_T(26, 128);
+        if (bar != 0u) {          // the rows' bulk copies were given the time of the set-up above
+            arrived = mbar_wait(bar, 0);
+            bar = 0u;
+        }
+        valid = valid && arrived;
         if (valid) {
             const unsigned char* row = rows + static_cast<size_t>(r) * row_bytes;
             if (kLpr == 1) {
@@ -215,6 +225,7 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
                 part = __fadd_rn(chunk_dot(row, query, c0, key_dtype), chunk_dot(row, query, c0 ^ 1, key_dtype));
             }
         }
+        RLM_PROBE_T(27, 128);
         if (kLpr >= 2) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 1));
         if (kLpr == 4) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 2));
         const float sc = valid ? __fmul_rn(part, 0.125f) : kNegInf;
@@ -225,12 +236,14 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
             my_pos = pos;
         }
     }
+    RLM_PROBE_T(28, 128);
     warp_argmax_key(my_key, my_pos);
     if (my_pos != 0x7fffffff &&
         (my_key > best_key || best_pos == 0x7fffffff || (my_key == best_key && my_pos < best_pos))) {
         best_key = my_key;
         best_pos = my_pos;
     }
+    RLM_PROBE_T(29, 128);
 }
 
 // Picks the split that keeps every lane of the group busy in the fewest passes (launches of at
@@ -240,17 +253,17 @@ __device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dt
                                            const int* sel, int bs, int first_valid, int pos0,
                                            int exclude, const int* excl, int n_excl, const float* query,
                                            float* cand, int slot0, int wi, int nw, uint32_t& best_key,
-                                           int& best_pos) {
+                                           int& best_pos, uint32_t bar, bool& arrived) {
     const int lanes = gridDim.x <= 148 ? 32 * nw : 0;   // a row per lane when CTAs share the SMs: fewer instructions in total
     if (4 * n_rows <= lanes)
         score_rows_split<kBf16, 4>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
-                                   query, cand, slot0, wi, nw, best_key, best_pos);
+                                   query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
     else if (2 * n_rows <= lanes)
         score_rows_split<kBf16, 2>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
-                                   query, cand, slot0, wi, nw, best_key, best_pos);
+                                   query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
     else
         score_rows_split<kBf16, 1>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
-                                   query, cand, slot0, wi, nw, best_key, best_pos);
+                                   query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
 }
 
 // Block scores of the first `n_complete` blocks with the `nw` warps of a group; the other
@@ -600,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
                          a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
             score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
-                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp);
+                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok);
         RLM_PROBE_T(22, 0);
         RLM_PROBE_T(23, 128);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
@@ -636,19 +649,18 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             }
             __syncthreads();
             RLM_PROBE(9);
-            ok = mbar_wait(bar_ra, 0);
+            RLM_PROBE(10);
+            bk = 0;
+            bp = 0x7fffffff;
+            // each warp works out its rows' positions first and only then waits for the copies
+            score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+                       nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok);
+            RLM_PROBE_T(24, 0);
+            if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             if (__syncthreads_or(!ok)) {
                 if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
                 return;
             }
-            RLM_PROBE(10);
-            bk = 0;
-            bp = 0x7fffffff;
-            score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
-                       nullptr, 0, warp, kWarps, bk, bp);
-            RLM_PROBE_T(24, 0);
-            if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
-            __syncthreads();
             RLM_PROBE(11);
         }
         // Highest score wins; equal scores go to the lowest position (the reference's
@@ -694,7 +706,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
                      a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
         score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
-                   excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp);
+                   excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp);
     __syncthreads();
     RLM_PROBE(15);
     if (top > 0) {
@@ -713,15 +725,14 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             RLM_PROBE(17);
         }
         __syncthreads();
-        bool ok = mbar_wait(bar_rp, 0);
+        bool ok = true;
+        RLM_PROBE(19);
+        score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+                   cand, L, warp, kWarps, dk, dp, bar_rp, ok);
         if (__syncthreads_or(!ok)) {
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
-        RLM_PROBE(19);
-        score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
-                   cand, L, warp, kWarps, dk, dp);
-        __syncthreads();
         RLM_PROBE(20);
     }
     // Exact top-K by rank counting: a candidate's output slot is the number of candidates
