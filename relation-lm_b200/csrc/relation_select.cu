@@ -272,11 +272,12 @@ template <bool kBf16>
 __device__ __noinline__ void score_blocks(const unsigned char* mean, const unsigned char* stdv,
                                           int stats_dtype_arg, int nb, int n_complete, int bs, int t,
                                           int ls, int strict, int buckets, const float* rq,
-                                          float sp, const float* bias, float* out, int wi, int nw) {
+                                          const float* sp4, const float* bias, float* out, int wi, int nw) {
     const int lane = threadIdx.x & 31;
     const int j = lane & 7, sub = lane >> 3, head = j >> 1;
     const int stats_dtype = kBf16 ? RLM_BF16 : stats_dtype_arg;
     const int row_bytes = kD * (stats_dtype == RLM_F32 ? 4 : 2);
+    const float sp = sp4[head];
     float q[8], aq[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { q[i] = rq[8 * j + i]; aq[i] = fabsf(q[i]); }
@@ -314,6 +315,78 @@ __device__ __noinline__ void score_blocks(const unsigned char* mean, const unsig
             out[n] = eligible ? acc : kNegInf;
         }
     }
+}
+
+// The same block scores with four lanes per block, a head (16 statistics elements = chunks 2h and
+// 2h + 1) per lane: fewer instructions per block and eight blocks per warp pass, for caches of
+// more than 16 blocks.  Odd blocks of a pass take a head's second chunk first so that the eight
+// lanes of a quarter warp read eight different 16-byte chunk indices (rows are 128 or 256 bytes
+// apart in shared memory).  Every sum is one of the eight-lane form's sums with its operands
+// possibly swapped, so the scores are bit-identical.
+template <bool kBf16>
+__device__ __noinline__ void score_blocks_head(const unsigned char* mean, const unsigned char* stdv,
+                                               int stats_dtype_arg, int nb, int n_complete, int bs, int t,
+                                               int ls, int strict, int buckets, const float* rq,
+                                               const float* sp4, const float* bias, float* out, int wi, int nw) {
+    const int lane = threadIdx.x & 31;
+    const int head = lane & 3, bl = lane >> 2;
+    const int stats_dtype = kBf16 ? RLM_BF16 : stats_dtype_arg;
+    const int row_bytes = kD * (stats_dtype == RLM_F32 ? 4 : 2);
+    const int c0 = 2 * head + (bl & 1), c1 = c0 ^ 1;
+    float q0[8], q1[8], a0[8], a1[8];
+    load8(rq, 8 * c0, RLM_F32, q0);
+    load8(rq, 8 * c1, RLM_F32, q1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a0[i] = fabsf(q0[i]); a1[i] = fabsf(q1[i]); }
+    const float sp = sp4[head];
+    for (int n = n_complete + wi * 32 + lane; n < ((nb + 3) & ~3); n += 32 * nw) out[n] = kNegInf;
+    for (int base = wi * 8; base < n_complete; base += 8 * nw) {
+        const int n = base + bl;
+        const bool live = n < n_complete;
+        const int end = (n + 1) * bs - 1;
+        int dist = t - end;
+        if (dist < 0) dist = 0;
+        int bucket = 31 - __clz(dist + 1);
+        if (bucket > buckets - 1) bucket = buckets - 1;
+        float md = 0.0f, sd = 0.0f;
+        if (live) {
+            const unsigned char* m = mean + static_cast<size_t>(n) * row_bytes;
+            const unsigned char* sdev = stdv + static_cast<size_t>(n) * row_bytes;
+            float v[8], w[8];
+            load8(m, 8 * c0, stats_dtype, v);
+            load8(m, 8 * c1, stats_dtype, w);
+            md = __fadd_rn(seg8(v, q0), seg8(w, q1));
+            load8(sdev, 8 * c0, stats_dtype, v);
+            load8(sdev, 8 * c1, stats_dtype, w);
+            sd = __fadd_rn(seg8(v, a0), seg8(w, a1));
+        }
+        const float sh = __fadd_rn(__fmul_rn(__fadd_rn(md, __fmul_rn(sp, sd)), 0.25f),
+                                   live ? bias[head * buckets + bucket] : 0.0f);
+        float mx = fmaxf(sh, __shfl_xor_sync(0xffffffffu, sh, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float e = canon_exp(__fsub_rn(sh, mx));
+        e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, 1));       // e0 + e1 | e2 + e3
+        e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, 2));       // (e0 + e1) + (e2 + e3)
+        const float acc = __fadd_rn(mx, canon_log(e));
+        if (head == 0 && live) {
+            const bool eligible = !strict || end < ls;
+            out[n] = eligible ? acc : kNegInf;
+        }
+    }
+}
+
+// Eight lanes per block up to 16 complete blocks (one pass of four warps), a head per lane beyond.
+template <bool kBf16>
+__device__ __forceinline__ void score_blocks_any(const unsigned char* mean, const unsigned char* stdv,
+                                                 int stats_dtype, int nb, int n_complete, int bs, int t,
+                                                 int ls, int strict, int buckets, const float* rq,
+                                                 const float* sp4, const float* bias, float* out, int wi, int nw) {
+    if (n_complete > 16)
+        score_blocks_head<kBf16>(mean, stdv, stats_dtype, nb, n_complete, bs, t, ls, strict, buckets, rq, sp4,
+                                 bias, out, wi, nw);
+    else
+        score_blocks<kBf16>(mean, stdv, stats_dtype, nb, n_complete, bs, t, ls, strict, buckets, rq, sp4, bias,
+                            out, wi, nw);
 }
 
 // Warp 0: rank the block scores by counting (descending score, ties to the lowest index)
@@ -477,6 +550,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     __shared__ int surv_slot[kWarps * kMaxKOut];
     __shared__ uint32_t group_max[2 * kWarps];
     __shared__ int short_count;
+    __shared__ float softplus_s[8];
     if (threadIdx.x == 0) short_count = 0;
     RLM_TRACE_DECL;
     RLM_PROBE(0);
@@ -494,10 +568,10 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     const bool early = a.row_position == nullptr && a.row_batch == nullptr && a.exclude_list == nullptr &&
                        a.mode != kPartnerOnly;
     if (!early) griddep_sync();
-    const int my_head = (lane & 7) >> 1;
-    float ga = 0.0f, gp = 0.0f, ba = 0.0f, bp_ = 0.0f;
-    if (do_anchor) ga = load_scalar(a.anchor_gamma, my_head, a.param_dtype);
-    if (do_partner) gp = load_scalar(a.partner_gamma, my_head, a.param_dtype);
+    // threads 32..35 / 36..39 evaluate softplus(gamma) of the anchor / partner heads for everybody
+    const bool sp_thread = tid >= 32 && tid < 40 && (tid < 36 ? do_anchor : do_partner);
+    float gamma = 0.0f, ba = 0.0f, bp_ = 0.0f;
+    if (sp_thread) gamma = load_scalar(tid < 36 ? a.anchor_gamma : a.partner_gamma, tid & 3, a.param_dtype);
     if (tid < buckets4) {
         if (do_anchor) ba = load_scalar(a.anchor_bias, tid, a.param_dtype);
         if (do_partner) bp_ = load_scalar(a.partner_bias, tid, a.param_dtype);
@@ -585,9 +659,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     if (tid < cap4 - cap) cand[cap + tid] = kNegInf;   // padding slots never win a comparison
     const int n_excl = a.exclude_list ? a.exclude_count : 0;
     if (tid < n_excl) excl_s[tid] = a.exclude_list[static_cast<size_t>(row) * n_excl + tid];
-    // softplus of this lane's head, evaluated while the bulk copies fly
-    const float sp_a = canon_log(__fadd_rn(1.0f, canon_exp(ga)));
-    const float sp_p = canon_log(__fadd_rn(1.0f, canon_exp(gp)));
+    // softplus of the heads' gammas, evaluated while the bulk copies fly
+    if (sp_thread) softplus_s[tid - 32] = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
+    const float* sp_a = softplus_s, *sp_p = softplus_s + 4;
     RLM_PROBE(2);
     __syncthreads();
     RLM_PROBE(3);
@@ -609,8 +683,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         uint32_t bk = 0;
         int bp = 0x7fffffff;
         if (warp < block_warps)
-            score_blocks<kBf16>(smem + p.a_mean, smem + p.a_std, stats_dtype, nb, n_complete, bs, t, ls,
-                         a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
+            score_blocks_any<kBf16>(smem + p.a_mean, smem + p.a_std, stats_dtype, nb, n_complete, bs, t, ls,
+                                    a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
             score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
                        n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok);
@@ -702,8 +776,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     uint32_t dk = 0;
     int dp = 0x7fffffff;
     if (warp < block_warps)
-        score_blocks<kBf16>(smem + p.p_mean, smem + p.p_std, stats_dtype, nb, n_complete, bs, t, ls,
-                     a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
+        score_blocks_any<kBf16>(smem + p.p_mean, smem + p.p_std, stats_dtype, nb, n_complete, bs, t, ls,
+                                a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
         score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp);
