@@ -42,8 +42,8 @@ METRIC = "relation decode tokens/s at ctx512 K=8"
 UNIT = "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one relation_select_kernel launch at 256 rows of the
 # 12-layer decode shape (ncu capture summarised under profiles/), and its ratio to the algorithmic bytes
-NCU_SELECT_TRAFFIC_ROWS256 = 20_809_984
-NCU_SELECT_TRAFFIC_RATIO = 20_809_984 / 21_325_824
+NCU_SELECT_TRAFFIC_ROWS256 = 21_464_576
+NCU_SELECT_TRAFFIC_RATIO = 21_464_576 / 21_325_824
 CPU_SAMPLE_BATCH = 8   # the CPU arm keeps fp32 caches on the host: it decodes at most this many sequences
 
 
@@ -530,7 +530,7 @@ def run_ours(args) -> None:
                          "peak_source": "measured" if peaks else "fallback",
                          "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO)
                                      if dominant == "relation_select_kernel" else None),
-                         "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (20.81 MB per "
+                         "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (21.46 MB per "
                                            "launch for 21.33 MB of algorithmic bytes), scaled by algorithmic bytes",
                          "us_per_launch": dom["us_per_launch"],
                          "share_of_library_time": dom["us_per_step"] / lib_us,
