@@ -268,6 +268,15 @@ def kernel_table(dec, graph_iters: int = 20):
                                       cfg.norm_eps, residual, w["mix"][l])
 
     normalized = torch.randn(B, d, device=dev).to(dec.dtype)
+    fused_query = getattr(dec, "fused_query", False)
+    projected = torch.empty(B, 256, device=dev, dtype=dec.dtype)
+
+    def reduce_project(l):
+        from relation_lm.kernels.relation_reduce import relation_norm_reduce_residual_norm_project
+        relation_norm_reduce_residual_norm_project(
+            raw[l], scores, w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps, residual,
+            w["mix"][l], w["input_norm_w"][l], w["input_norm_b"][l], cfg.norm_eps, normalized,
+            w["w_query"][l], projected)
 
     def query(l):
         packed_projection(normalized, w["w_query"][l])
@@ -286,16 +295,25 @@ def kernel_table(dec, graph_iters: int = 20):
         "expanded_row_update_kernel(all layers)": L * (e * 2 * H * R + B * e * (R + 2 * H)),
         "relation_norm_reduce_kernel": B * (e * K * d + 4 * K + 4 * d + 8 * d) + 4 * 3 * d,
         "packed_projection_kernel(query)": e * (B * d + 256 * d + B * 256),
+        "relation_norm_reduce_project_kernel": B * (e * K * d + 4 * K + 4 * d + 8 * d) + 4 * 3 * d
+                                               + e * (B * d + 256 * d + B * 256),
         "router_cache_update_kernel(all layers)": L * B * (e * 64 * (2 + 4 + 4 + 2 * cfg.block_size + 4) + 2 * 64 * 4 + 2 * e * (256 + R)),
     }
     table = {}
-    for name, fn, per_graph in (("relation_select_kernel", select, L),
-                                ("relation_hidden_kernel", hidden, L),
-                                ("relation_norm_reduce_kernel", reduce, L),
-                                ("packed_projection_kernel(query)", query, L),
-                                ("router_cache_update_kernel(all layers)", append, 1),
-                                ("expanded_row_update_kernel(all layers)", expand, 1)):
+    # (kernel, launcher, launches per timing graph, launches per decode step): with the query
+    # projection inside norm-reduce only layer 0 projects separately and only the last layer's
+    # norm-reduce runs without a projection
+    for name, fn, per_graph, per_step in (
+            ("relation_select_kernel", select, L, L),
+            ("relation_hidden_kernel", hidden, L, L),
+            ("relation_norm_reduce_kernel", reduce, L, 1 if fused_query else L),
+            ("relation_norm_reduce_project_kernel", reduce_project, L, L - 1),
+            ("packed_projection_kernel(query)", query, L, 1 if fused_query else L),
+            ("router_cache_update_kernel(all layers)", append, 1, 1),
+            ("expanded_row_update_kernel(all layers)", expand, 1, 1)):
         if name.startswith("expanded_row_update") and not stacked:
+            continue
+        if name == "relation_norm_reduce_project_kernel" and not fused_query:
             continue
         for l in range(per_graph):
             fn(l)
@@ -316,7 +334,7 @@ def kernel_table(dec, graph_iters: int = 20):
         end.record()
         torch.cuda.synchronize()
         us = start.elapsed_time(end) * 1e3 / (graph_iters * per_graph)
-        launches_per_step = per_graph
+        launches_per_step = per_step
         table[name] = {"us_per_launch": us, "launches_per_step": launches_per_step,
                        "us_per_step": us * launches_per_step, "bytes_per_launch": bytes_per_launch[name],
                        "gb_per_s": bytes_per_launch[name] / us / 1e3}

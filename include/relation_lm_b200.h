@@ -224,6 +224,23 @@ int rlm_relation_norm_reduce(
     int32_t* status, void* stream);
 
 /*
+ * rlm_relation_norm_reduce in its residual + next-LayerNorm form, followed by the next layer's
+ * query projection in the same launch (extension, for decode batches of a few rows):
+ *   proj_out[N, proj_out_dim] = next_normalized[N, D] . proj_weight[proj_out_dim, D]^T,
+ * the F.linear of the reference's relation layer on its LayerNorm-ed input
+ * (src/relation_lm/models/stacked_relation.py:96-104), with fp32 accumulation over the 16-bit
+ * normalised row.  A cluster of proj_out_dim / 32 CTAs serves a row.
+ *   proj_weight, proj_out, next_normalized: bfloat16 / float16 (next_dtype); D a multiple of 64;
+ *   proj_out_dim = 32, 64, ... 256; every row uses *position; other arguments as above.
+ */
+int rlm_relation_norm_reduce_project(
+    const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
+    const int64_t* position, float norm_eps, float* residual, const float* mix,
+    const float* next_norm_weight, const float* next_norm_bias, float next_norm_eps, void* next_normalized,
+    const void* proj_weight, void* proj_out, int proj_out_dim, int next_dtype, const void* raw_bias,
+    int n_rows, int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream);
+
+/*
  * Prefill of the router state (extension): raw and convolved router keys and the block
  * statistics of positions [0, length) of ZERO-INITIALISED caches in one launch, leaving the
  * state that `length` successive rlm_router_cache_update calls would leave (including the

@@ -417,6 +417,10 @@ struct NormArgs {
     int32_t* status;
     float eps;
     int n_rows, k_out, dim, raw_dtype, param_dtype;
+    // fused projection of the normalised row (relation_norm_reduce_project_kernel only)
+    const void* proj_weight;  // [proj_out_dim, dim], the next_out dtype
+    void* proj_out;           // [N, proj_out_dim], the next_out dtype
+    int proj_out_dim;
 };
 
 __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(const NormArgs a) {
@@ -514,11 +518,12 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 // Vector form for feature widths that are a multiple of 8 (16-byte aligned rows): a lane owns
 // the 8-column chunks lane, lane + 32, ... (kVecChunks of them, at most four: dim <= 1024), so a partner row is
 // fetched with a few 16-byte loads per lane instead of one scalar load per column.
+// One row by one CTA; `partial` is [warps][dim] floats of shared memory.  With `normalized_copy`
+// (shared memory, dim 16-bit values) the next layer's normalised row is left there as well.
 template <int kVecChunks>
-__global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunks == 3 ? 3 : 2)) relation_norm_reduce_vec_kernel(const NormArgs a) {
-    extern __shared__ __align__(16) float partial[];   // [warps][dim]
-    griddep_sync();
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, float* partial,
+                                                    void* normalized_copy) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = a.k_out, D = a.dim;
     const int chunks = D / 8;
     const size_t raw_elem = a.raw_dtype == RLM_F32 ? 4 : 2;
@@ -634,9 +639,99 @@ __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunk
     if (a.next_out) {
         __shared__ float scratch[18];
         NormTarget t0{a.next_w, a.next_b, static_cast<uint16_t*>(a.next_out) + static_cast<size_t>(row) * D};
-        NormTarget t1{nullptr, nullptr, nullptr};
+        NormTarget t1{a.next_w, a.next_b, normalized_copy};
         block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, a.next_dtype, scratch);
     }
+}
+
+template <int kVecChunks>
+__global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunks == 3 ? 3 : 2)) relation_norm_reduce_vec_kernel(const NormArgs a) {
+    extern __shared__ __align__(16) float partial[];   // [warps][dim]
+    griddep_sync();
+    norm_reduce_vec_row<kVecChunks>(a, blockIdx.x, partial, nullptr);
+}
+
+// ---- norm-reduce + residual + next LayerNorm + the next layer's query projection, for decode
+// batches of a few rows.  A cluster of proj_out_dim / 32 CTAs serves one row: every CTA requests
+// its 32 x dim slice of the projection weight before the dependency wait (eight lanes per output
+// row, 16-byte pieces interleaved so that the lanes read contiguous bytes), CTA 0 of the cluster
+// does the row's norm-reduce and stores the normalised row (16-bit, as the tensor-core projection
+// would read it) into every CTA's shared memory through distributed shared memory, and after one
+// cluster barrier everybody finishes its 32 outputs with fp32 accumulation.  One launch instead of two, and the
+// weight fetch overlaps the norm-reduce chain.
+constexpr int kProjCols = 32;     // projection outputs per CTA
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores 16 bytes at the address that `local_ptr` has in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ void store_cluster_shared16(const void* local_ptr, uint32_t rank, const uint4& v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(remote), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <int kVecChunks>
+__global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_kernel(const NormArgs a) {
+    extern __shared__ __align__(16) float partial[];            // [warps][dim], CTA 0 of the cluster
+    __shared__ __align__(16) uint16_t normalized_row[1024];
+    constexpr int kPieces = 4 * kVecChunks;                      // 16-byte weight pieces per thread: dim <= 256 * kVecChunks
+    const int tid = threadIdx.x;
+    const int D = a.dim, pieces = D / 64;                        // dim is a multiple of 64
+    const uint32_t rank = cluster_rank();
+    const int slices = a.proj_out_dim / kProjCols;
+    const int row = blockIdx.x / slices;
+    const int col = static_cast<int>(rank) * kProjCols + (tid >> 3), part = tid & 7;
+    RLM_PROBE(0);
+    uint4 w[kPieces];
+    {
+        const uint4* wrow = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.proj_weight) +
+                                                           static_cast<size_t>(col) * D);
+#pragma unroll
+        for (int j = 0; j < kPieces; ++j)
+            if (j < pieces) w[j] = wrow[part + 8 * j];
+    }
+    RLM_PROBE(1);
+    griddep_sync();
+    RLM_PROBE(2);
+    if (rank == 0) {
+        norm_reduce_vec_row<kVecChunks>(a, row, partial, normalized_row);
+        __syncthreads();
+        if (tid < D / 8) {          // hand the normalised row to the other CTAs of the cluster
+            const uint4 v = reinterpret_cast<const uint4*>(normalized_row)[tid];
+            for (int r = 1; r < slices; ++r)
+                store_cluster_shared16(reinterpret_cast<uint4*>(normalized_row) + tid, static_cast<uint32_t>(r), v);
+        }
+    }
+    RLM_PROBE(3);
+    cluster_sync_all();             // release / acquire: the row is visible in every CTA's shared memory
+    RLM_PROBE(5);
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kPieces; ++j) {
+        if (j < pieces) {
+            float wf[8], xf[8];
+            Raw8 raw;
+            raw.lo = w[j];
+            raw.hi = make_uint4(0, 0, 0, 0);
+            convert8(raw, a.next_dtype, wf);
+            load8(normalized_row, 8 * (part + 8 * j), a.next_dtype, xf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(wf[e], xf[e], acc);
+        }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (part == 0)
+        store_scalar(a.proj_out, static_cast<int64_t>(row) * a.proj_out_dim + col, a.next_dtype, acc);
+    RLM_PROBE(6);
 }
 
 }  // namespace
@@ -673,14 +768,15 @@ extern "C" int rlm_relation_hidden_cache_update(
     return rlm::launch_hidden(a, true, stream);
 }
 
-extern "C" int rlm_relation_norm_reduce(
+namespace rlm {
+namespace {
+int norm_reduce_launch(
     const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
     const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
     float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
     float next_norm_eps, void* next_normalized, int next_dtype, int raw_splits,
-    int64_t raw_split_stride, const void* raw_bias, int n_rows,
-    int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
-    using namespace rlm;
+    int64_t raw_split_stride, const void* raw_bias, const void* proj_weight, void* proj_out, int proj_out_dim,
+    int n_rows, int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
     if (n_rows == 0) return RLM_OK;
     if (!raw || !partner_scores || !norm_weight || !norm_bias || (!out && !residual) ||
         (residual && !mix) || (!position && !row_position)) {
@@ -721,6 +817,25 @@ extern "C" int rlm_relation_norm_reduce(
             return RLM_ERR_UNSUPPORTED;
         }
     }
+    if (proj_out) {
+        if (!proj_weight || !next_normalized || dim % 64 != 0 || proj_out_dim < kProjCols ||
+            proj_out_dim % kProjCols != 0 || proj_out_dim > 8 * kProjCols || !aligned16(proj_weight)) {
+            set_error("relation_norm_reduce_project: needs the normalised output, dim a multiple of 64, "
+                      "32..256 projection outputs in steps of 32 and a 16-byte aligned weight");
+            return RLM_ERR_UNSUPPORTED;
+        }
+        a.proj_weight = proj_weight; a.proj_out = proj_out; a.proj_out_dim = proj_out_dim;
+        const unsigned slices = static_cast<unsigned>(proj_out_dim / kProjCols);
+        const dim3 grid(static_cast<unsigned>(n_rows) * slices);
+        if (dim <= 512)
+            launch_kernel_cluster(relation_norm_reduce_project_kernel<2>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
+        else if (dim <= 768)
+            launch_kernel_cluster(relation_norm_reduce_project_kernel<3>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
+        else
+            launch_kernel_cluster(relation_norm_reduce_project_kernel<4>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
+        count_launch();
+        return check_launch("relation_norm_reduce_project_kernel");
+    }
     if (vec && dim <= 512)
         launch_kernel(relation_norm_reduce_vec_kernel<2>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     else if (vec && dim <= 768)
@@ -731,6 +846,37 @@ extern "C" int rlm_relation_norm_reduce(
         launch_kernel(relation_norm_reduce_kernel, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch("relation_norm_reduce_kernel");
+}
+}  // namespace
+}  // namespace rlm
+
+extern "C" int rlm_relation_norm_reduce(
+    const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
+    const int64_t* position, const int32_t* row_position, float norm_eps, float* out,
+    float* residual, const float* mix, const float* next_norm_weight, const float* next_norm_bias,
+    float next_norm_eps, void* next_normalized, int next_dtype, int raw_splits,
+    int64_t raw_split_stride, const void* raw_bias, int n_rows,
+    int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
+    return rlm::norm_reduce_launch(raw, partner_scores, norm_weight, norm_bias, position, row_position, norm_eps,
+                                   out, residual, mix, next_norm_weight, next_norm_bias, next_norm_eps,
+                                   next_normalized, next_dtype, raw_splits, raw_split_stride, raw_bias, nullptr,
+                                   nullptr, 0, n_rows, k_out, dim, raw_dtype, param_dtype, status, stream);
+}
+
+extern "C" int rlm_relation_norm_reduce_project(
+    const void* raw, const float* partner_scores, const void* norm_weight, const void* norm_bias,
+    const int64_t* position, float norm_eps, float* residual, const float* mix,
+    const float* next_norm_weight, const float* next_norm_bias, float next_norm_eps, void* next_normalized,
+    const void* proj_weight, void* proj_out, int proj_out_dim, int next_dtype, const void* raw_bias, int n_rows,
+    int k_out, int dim, int raw_dtype, int param_dtype, int32_t* status, void* stream) {
+    if (!proj_weight || !proj_out) {
+        rlm::set_error("relation_norm_reduce_project: NULL projection weight or output");
+        return RLM_ERR_NULL;
+    }
+    return rlm::norm_reduce_launch(raw, partner_scores, norm_weight, norm_bias, position, nullptr, norm_eps, nullptr,
+                                   residual, mix, next_norm_weight, next_norm_bias, next_norm_eps, next_normalized,
+                                   next_dtype, 1, 0, raw_bias, proj_weight, proj_out, proj_out_dim, n_rows, k_out,
+                                   dim, raw_dtype, param_dtype, status, stream);
 }
 
 #ifdef RLM_TRACE

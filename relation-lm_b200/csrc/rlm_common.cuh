@@ -42,6 +42,30 @@ inline void launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size
     cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+// The same for a kernel whose CTAs form clusters of `cluster_x` along x.
+template <typename... Params, typename... Args>
+inline void launch_kernel_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, unsigned cluster_x,
+                                  size_t smem_bytes, void* stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster_x;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.numAttrs = 1;
+    if (programmatic_launch_enabled()) {
+        attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[1].val.programmaticStreamSerializationAllowed = 1;
+        config.numAttrs = 2;
+    }
+    config.attrs = attribute;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // Shared memory one CTA may use on sm_100 (227 KB) and the part of it the kernels here
 // request dynamically (the rest covers their small static allocations).
 constexpr int kSmemPerCta = 232448;

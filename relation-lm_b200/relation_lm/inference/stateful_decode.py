@@ -29,6 +29,7 @@ from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation
                                                  relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
                                                  relation_norm_reduce_residual_norm,
+                                                 relation_norm_reduce_residual_norm_project,
                                                  relation_norm_reduce_residual_norm_slices,
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
@@ -39,7 +40,8 @@ from relation_lm.kernels.router_cache import sparse_cache_append
 class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
                  dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
-                 programmatic_launch: bool = True, second_layer_split: bool = False) -> None:
+                 programmatic_launch: bool = True, second_layer_split: bool = False,
+                 fused_query: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -79,6 +81,14 @@ class StatefulDecoder:
             self.second_layer_splits = next((s for s in (4, 2) if blocks % s == 0 and blocks // s >= 2), 1)
         if self.second_layer_splits > 1:
             self.b2_f32 = self.w["b2"].float().contiguous()                    # [L, d], dtype of the norm parameters
+        # Next layer's query projection inside norm-reduce (a cluster of CTAs per row): one launch
+        # fewer per layer for batches of a few rows; larger batches keep the tensor-core projection.
+        n_query = self.w["w_query"].shape[1]
+        can_fuse_query = (self.fused and not self.fused_tail and self.second_layer_splits == 1
+                          and n_query % 32 == 0 and n_query <= 256)
+        self.fused_query = can_fuse_query and (B <= 32 if fused_query is None else bool(fused_query))
+        if self.fused_query:
+            self.query = zeros(B, n_query)
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.normalized = zeros(B, cfg.d_model)             # LayerNorm'd input of the next projection
@@ -195,7 +205,9 @@ class StatefulDecoder:
             self.last_selection = []
         K = cfg.k_max
         for l in range(cfg.layers):
-            q = packed_projection(self.normalized, w["w_query"][l])
+            # layer 0 projects the embedding's normalised rows; later layers find their queries
+            # written by the previous layer's norm-reduce when that fusion is on
+            q = self.query if (self.fused_query and l > 0) else packed_projection(self.normalized, w["w_query"][l])
             anchor, _, partner, partner_score = relation_select_packed(
                 q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
                 self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
@@ -228,9 +240,15 @@ class StatefulDecoder:
                     next_w, next_b, cfg.norm_eps, self.normalized)
             else:
                 raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])            # [B, K, d]
-                relation_norm_reduce_residual_norm(raw, partner_score, w["relation_norm_w"][l],
-                                                   w["relation_norm_b"][l], pos, cfg.norm_eps, hidden,
-                                                   w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized)
+                if self.fused_query and not last:
+                    relation_norm_reduce_residual_norm_project(
+                        raw, partner_score, w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,
+                        hidden, w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized,
+                        w["w_query"][l + 1], self.query)
+                else:
+                    relation_norm_reduce_residual_norm(raw, partner_score, w["relation_norm_w"][l],
+                                                       w["relation_norm_b"][l], pos, cfg.norm_eps, hidden,
+                                                       w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized)
             if keep_selection:
                 self.last_selection.append((anchor, partner))
         logits = packed_projection(self.normalized, self.head_weight, self.head_bias)

@@ -22,6 +22,7 @@ PROTOTYPES = {
     "rlm_relation_hidden_cached": [_P] * 7 + [_I] * 9 + [_P, _P],
     "rlm_relation_hidden_cache_update": [_P] * 10 + [_I] * 8 + [_P, _P],
     "rlm_relation_norm_reduce": [_P] * 6 + [_F, _P, _P, _P, _P, _P, _F, _P, _I, _I, _L, _P] + [_I] * 5 + [_P, _P],
+    "rlm_relation_norm_reduce_project": [_P] * 5 + [_F, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _P] + [_I] * 5 + [_P, _P],
     "rlm_router_cache_prefill": [_P, _L, _L, _P, _L, _L] + [_P] * 10 + [_I] * 9 + [_P],
     "rlm_packed_projection": [_P, _L, _P, _P, _P] + [_I] * 6 + [_P, _P],
     "rlm_greedy_token": [_P, _L, _P, _P] + [_I] * 3 + [_P],

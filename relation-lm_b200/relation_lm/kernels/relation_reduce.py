@@ -346,6 +346,64 @@ def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, m
     return None
 
 
+@torch.library.custom_op("relation_lm::relation_norm_reduce_residual_norm_project",
+                         mutates_args=("hidden", "normalized", "projected"), device_types="cuda")
+def relation_norm_reduce_residual_norm_project(
+    raw: Tensor,
+    partner_scores: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+    hidden: Tensor,
+    mix: Tensor,
+    next_norm_weight: Tensor,
+    next_norm_bias: Tensor,
+    next_norm_eps: float,
+    normalized: Tensor,
+    projection_weight: Tensor,
+    projected: Tensor,
+) -> None:
+    """``relation_norm_reduce_residual_norm`` that also applies the next layer's query projection
+    (extension, decode batches of a few rows): ``projected = normalized @ projection_weight.T`` with
+    ``projection_weight [N, D]`` and ``projected [B, N]`` in the dtype of ``normalized``,
+    ``N`` = 32, 64, ... 256 and ``D`` a multiple of 64.  One launch; a cluster of ``N / 32`` CTAs per row."""
+    device = _abi.require_cuda_contiguous(raw=raw, partner_scores=partner_scores,
+                                          norm_weight=norm_weight, norm_bias=norm_bias,
+                                          hidden=hidden, mix=mix, next_norm_weight=next_norm_weight,
+                                          next_norm_bias=next_norm_bias, normalized=normalized,
+                                          projection_weight=projection_weight, projected=projected)
+    _abi.require_position(position, device)
+    batch, k_out, dim = raw.shape
+    if partner_scores.shape != (batch, k_out) or partner_scores.dtype != torch.float32:
+        raise ValueError("partner_scores must be float32 [B, K]")
+    if hidden.shape != (batch, dim) or hidden.dtype != torch.float32 or mix.dtype != torch.float32 \
+            or mix.numel() != 1:
+        raise ValueError("hidden must be float32 [B, D] and mix a one-element float32 tensor")
+    if normalized.shape != (batch, dim) or next_norm_weight.dtype != torch.float32 \
+            or next_norm_bias.dtype != torch.float32 or next_norm_weight.numel() != dim:
+        raise ValueError("normalized must be [B, D] and the next LayerNorm parameters float32 [D]")
+    n_out = projection_weight.shape[0]
+    if projection_weight.shape != (n_out, dim) or projected.shape != (batch, n_out) \
+            or projection_weight.dtype != normalized.dtype or projected.dtype != normalized.dtype:
+        raise ValueError("projection_weight must be [N, D] and projected [B, N] in the dtype of normalized")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_norm_reduce_project(
+            _abi.ptr(raw), _abi.ptr(partner_scores), _abi.ptr(norm_weight), _abi.ptr(norm_bias),
+            _abi.ptr(position), float(norm_eps), _abi.ptr(hidden), _abi.ptr(mix),
+            _abi.ptr(next_norm_weight), _abi.ptr(next_norm_bias), float(next_norm_eps),
+            _abi.ptr(normalized), _abi.ptr(projection_weight), _abi.ptr(projected), n_out,
+            _abi.code(normalized), None, batch, k_out, dim, _abi.code(raw),
+            _abi.same_dtype("norm parameter", norm_weight, norm_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_norm_reduce_residual_norm_project.register_fake
+def _(raw, partner_scores, norm_weight, norm_bias, position, norm_eps, hidden, mix, next_norm_weight,
+      next_norm_bias, next_norm_eps, normalized, projection_weight, projected):
+    return None
+
+
 @torch.library.custom_op("relation_lm::relation_norm_reduce_residual_norm",
                          mutates_args=("hidden", "normalized"), device_types="cuda")
 def relation_norm_reduce_residual_norm(

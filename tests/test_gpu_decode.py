@@ -174,3 +174,30 @@ def test_split_k_second_layer_decode_tracks_default_path():
             assert torch.allclose(a[0].float(), b[0].float(), atol=0.25, rtol=0.05), t
     assert agree >= steps - 2          # rounding may flip a rare near-tie
     assert_status_clear()
+
+
+def test_query_projection_inside_norm_reduce_tracks_separate_launches():
+    """The decode step with the next layer's query projection inside norm-reduce (default for
+    small batches) against the step with separate tensor-core projections: same selections, logits
+    within bf16 noise."""
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=17)
+    B, steps = 4, 24
+    g = torch.Generator().manual_seed(29)
+    tokens = torch.randint(0, 500, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, 16, (B, steps), generator=g).cuda()
+    separate = StatefulDecoder(model, B, "cuda", torch.bfloat16, fused_query=False)
+    fused = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    assert fused.fused_query and not separate.fused_query
+    agree = 0
+    for t in range(steps):
+        a = separate.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        b = fused.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        same = all(torch.equal(pa, sa) and torch.equal(pp, sp_)
+                   for (pa, pp), (sa, sp_) in zip(separate.last_selection, fused.last_selection))
+        agree += int(same)
+        if same:
+            assert torch.allclose(a[0].float(), b[0].float(), atol=0.25, rtol=0.05), t
+    assert agree >= steps - 2          # rounding may flip a rare near-tie
+    assert_status_clear()

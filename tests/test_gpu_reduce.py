@@ -223,6 +223,41 @@ def test_norm_reduce_residual_with_next_layer_norm(B, K, D, dtype):
     assert_status_clear()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,K,D,N", [(8, 8, 512, 256), (1, 8, 512, 256), (5, 5, 768, 192), (3, 4, 1024, 32),
+                                     (32, 8, 256, 128)])
+def test_norm_reduce_with_the_next_query_projection(B, K, D, N, dtype):
+    """Norm-reduce + residual + next LayerNorm + next query projection in one launch (a cluster
+    of N / 32 CTAs per row): residual and normalised rows identical to the launch without the
+    projection, projected rows equal to the fp32 product of the 16-bit normalised rows."""
+    from relation_lm.kernels.relation_reduce import (relation_norm_reduce_residual_norm,
+                                                     relation_norm_reduce_residual_norm_project)
+
+    g = torch.Generator().manual_seed(7900 + B + D + N)
+    raw = torch.randn(B, K, D, generator=g).to(dtype).cuda()
+    scores = torch.randn(B, K, generator=g)
+    scores[::2, -1] = -torch.inf
+    scores = scores.cuda()
+    gamma, beta = (torch.rand(D, generator=g) + 0.5).cuda(), (torch.randn(D, generator=g) * 0.1).cuda()
+    next_w, next_b = (torch.rand(D, generator=g) + 0.5).cuda(), (torch.randn(D, generator=g) * 0.1).cuda()
+    hidden = (torch.randn(B, D, generator=g) * 2).cuda()
+    weight = (torch.randn(N, D, generator=g) * D ** -0.5).to(dtype).cuda()
+    mix = torch.tensor(0.37).cuda()
+    pos = position_tensor(300)
+    plain_hidden, plain_norm = hidden.clone(), torch.empty(B, D, device="cuda", dtype=dtype)
+    relation_norm_reduce_residual_norm(raw, scores, gamma, beta, pos, 1e-5, plain_hidden, mix, next_w, next_b,
+                                       1e-5, plain_norm)
+    got_hidden, got_norm = hidden.clone(), torch.empty(B, D, device="cuda", dtype=dtype)
+    projected = torch.full((B, N), float("nan"), device="cuda", dtype=dtype)
+    relation_norm_reduce_residual_norm_project(raw, scores, gamma, beta, pos, 1e-5, got_hidden, mix, next_w,
+                                               next_b, 1e-5, got_norm, weight, projected)
+    assert torch.equal(got_hidden, plain_hidden)
+    assert torch.equal(got_norm, plain_norm)
+    want = got_norm.double() @ weight.double().T
+    assert torch.allclose(projected.double(), want, atol=2e-2, rtol=1e-2)
+    assert_status_clear()
+
+
 @pytest.mark.parametrize("splits", [2, 4])
 def test_split_k_second_layer_feeds_norm_reduce(splits):
     """Second relation-MLP layer as a split-K tensor-core GEMM whose fp32 slices (and bias) are
