@@ -102,9 +102,14 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
     const int ws = a.weight_dtype == RLM_F32 ? 4 : 2;
     const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
     const int segs = R / 8;
+    // quotients by the two run-time divisors of the index arithmetic: shifts when they are powers of two
+    const int segs_shift = (segs & (segs - 1)) == 0 ? 31 - __clz(segs) : -1;
+    const int k_shift = (K & (K - 1)) == 0 ? 31 - __clz(K) : -1;
+    auto div_segs = [&](int x) { return segs_shift >= 0 ? x >> segs_shift : x / segs; };
+    auto div_k = [&](int x) { return k_shift >= 0 ? x >> k_shift : x / K; };
     // weight tiles: every load of this thread is issued before the first conversion
     for (int i = tid; i < kHT * segs; i += kHiddenThreads) {
-        const int r = i / segs, sgm = i - r * segs;
+        const int r = div_segs(i), sgm = i - r * segs;
         Raw8 rm, ra, rp;
         rm.lo = rm.hi = make_uint4(0, 0, 0, 0);
         ra = rm;
@@ -165,8 +170,8 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         RLM_PROBE(2);
         // product matrix: prod[rb*K + k][:] = operand[p_k] * operand[anchor]
         for (int i = tid; i < kRows * segs; i += kHiddenThreads) {
-            const int prow = i / segs, sgm = i - prow * segs;
-            const int rb = prow / K, k = prow - rb * K;
+            const int prow = div_segs(i), sgm = i - prow * segs;
+            const int rb = div_k(prow), k = prow - rb * K;
             float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (prow < tile_rows && seq[rb] >= 0) {
                 const char* operand = static_cast<const char*>(a.operand_cache) +
@@ -183,7 +188,7 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         }
         if (kUpdate) {
             for (int i = tid; i < kRB * segs; i += kHiddenThreads) {
-                const int rb = i / segs, sgm = i - rb * segs;
+                const int rb = div_segs(i), sgm = i - rb * segs;
                 float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 if (seq[rb] >= 0)
                     load8(static_cast<const char*>(a.operand_cache) +
@@ -202,7 +207,7 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         for (int e = 0; e < kPairs; ++e) {
             const int o = tid + e * kHiddenThreads;
             const int prow = o / (kHT / 2), hh = 2 * (o - prow * (kHT / 2));
-            const int rb = prow / K, k = prow - rb * K;
+            const int rb = div_k(prow), k = prow - rb * K;
             const bool live = prow < tile_rows && row0 + rb < a.n_rows && seq[rb < kRB ? rb : 0] >= 0 &&
                               h0 + hh < H;
             out_row[e] = live ? row0 + rb : -1;
@@ -295,7 +300,7 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             if (out_row[e] < 0) continue;
             const int o = tid + e * kHiddenThreads;
             const int prow = o / (kHT / 2), hh = 2 * (o - prow * (kHT / 2));
-            const int rb = prow / K;
+            const int rb = div_k(prow);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 if (h0 + hh + j >= H) continue;
