@@ -525,7 +525,9 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 // fetched with a few 16-byte loads per lane instead of one scalar load per column.
 // One row by one CTA; `partial` is [warps][dim] floats of shared memory.  With `normalized_copy`
 // (shared memory, dim 16-bit values) the next layer's normalised row is left there as well.
-template <int kVecChunks>
+// kEarly (kernels without an occupancy target): the affine parameters, the residual row and the
+// mixing weight are requested into registers at the top instead of where the chain reaches them.
+template <int kVecChunks, bool kEarly>
 __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, float* partial,
                                                     void* normalized_copy) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -538,6 +540,25 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
     float s0 = lane < K ? a.scores[static_cast<size_t>(row) * K + lane] : kNegInf;
     float s1 = lane + 32 < K ? a.scores[static_cast<size_t>(row) * K + lane + 32] : kNegInf;
     float x[kVecChunks][8];
+    float gm_early[kEarly ? kVecChunks : 1][8], bt_early[kEarly ? kVecChunks : 1][8];
+    float4 res_early = make_float4(0.0f, 0.0f, 0.0f, 0.0f), next_g = res_early, next_b = res_early;
+    float mix_early = 0.0f;
+    if (kEarly) {
+#pragma unroll
+        for (int i = 0; i < kVecChunks; ++i)
+            if (lane + 32 * i < chunks) {
+                load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm_early[i]);
+                load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt_early[i]);
+            }
+        if (4 * tid < D) {
+            if (a.residual) res_early = *reinterpret_cast<const float4*>(a.residual + static_cast<size_t>(row) * D + 4 * tid);
+            if (a.next_out) {
+                next_g = *reinterpret_cast<const float4*>(a.next_w + 4 * tid);
+                next_b = *reinterpret_cast<const float4*>(a.next_b + 4 * tid);
+            }
+        }
+        if (a.residual) mix_early = *a.mix;
+    }
     // one 8-column chunk of partner row k: the slices of a split-K GEMM are summed and the bias added here
     auto load_raw = [&](const char* row_k, int chunk, float (&dst)[8]) {
         load8(row_k, 8 * chunk, a.raw_dtype, dst);
@@ -604,8 +625,13 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
         for (int i = 0; i < kVecChunks; ++i)
             if (lane + 32 * i < chunks) {
                 float gm[8], bt[8];       // cache-resident affine parameters, read where they are used
-                load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm);
-                load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt);
+                if (kEarly) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) { gm[e] = gm_early[i][e]; bt[e] = bt_early[i][e]; }
+                } else {
+                    load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm);
+                    load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt);
+                }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[i][e] = fmaf(wk, fmaf(x[i][e] * inv, gm[e], bt[e]), y[i][e]);
             }
@@ -618,7 +644,7 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
             dst[1] = make_float4(y[i][4], y[i][5], y[i][6], y[i][7]);
         }
     __syncthreads();
-    const float mix = a.residual ? *a.mix : 0.0f;
+    const float mix = kEarly ? mix_early : (a.residual ? *a.mix : 0.0f);
     const int c = 4 * tid;                 // dim <= 1024: every thread owns at most four columns
     const bool live = c < D;
     float updated[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -634,7 +660,7 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
         const size_t at = static_cast<size_t>(row) * D + c;
         if (a.out) *reinterpret_cast<float4*>(a.out + at) = total;
         if (a.residual) {
-            float4 r = *reinterpret_cast<float4*>(a.residual + at);
+            float4 r = kEarly ? res_early : *reinterpret_cast<float4*>(a.residual + at);
             r.x = fmaf(mix, total.x, r.x); r.y = fmaf(mix, total.y, r.y);
             r.z = fmaf(mix, total.z, r.z); r.w = fmaf(mix, total.w, r.w);
             *reinterpret_cast<float4*>(a.residual + at) = r;
@@ -645,7 +671,8 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
         __shared__ float scratch[18];
         NormTarget t0{a.next_w, a.next_b, static_cast<uint16_t*>(a.next_out) + static_cast<size_t>(row) * D};
         NormTarget t1{a.next_w, a.next_b, normalized_copy};
-        block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, a.next_dtype, scratch);
+        block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, a.next_dtype, scratch,
+                          kEarly ? &next_g : nullptr, kEarly ? &next_b : nullptr);
     }
 }
 
@@ -653,7 +680,7 @@ template <int kVecChunks>
 __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunks == 3 ? 3 : 2)) relation_norm_reduce_vec_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
     griddep_sync();
-    norm_reduce_vec_row<kVecChunks>(a, blockIdx.x, partial, nullptr);
+    norm_reduce_vec_row<kVecChunks, false>(a, blockIdx.x, partial, nullptr);
 }
 
 // ---- norm-reduce + residual + next LayerNorm + the next layer's query projection, for decode
@@ -706,7 +733,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
     griddep_sync();
     RLM_PROBE(2);
     if (rank == 0) {
-        norm_reduce_vec_row<kVecChunks>(a, row, partial, normalized_row);
+        norm_reduce_vec_row<kVecChunks, true>(a, row, partial, normalized_row);
         __syncthreads();
         if (tid < D / 8) {          // hand the normalised row to the other CTAs of the cluster
             const uint4 v = reinterpret_cast<const uint4*>(normalized_row)[tid];

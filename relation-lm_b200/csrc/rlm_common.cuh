@@ -366,7 +366,9 @@ __device__ __forceinline__ float block_sum256(float v, float* scratch) {
 
 __device__ __forceinline__ void block_layer_norm4(const float (&v)[4], bool live, int c, int dim, float eps,
                                                   const NormTarget& t0, const NormTarget& t1,
-                                                  int out_dtype, float* scratch) {
+                                                  int out_dtype, float* scratch,
+                                                  const float4* loaded_gamma = nullptr,
+                                                  const float4* loaded_beta = nullptr) {
     const float mean = block_sum256(live ? (v[0] + v[1]) + (v[2] + v[3]) : 0.0f, scratch) / static_cast<float>(dim);
     float d[4], sq = 0.0f;
 #pragma unroll
@@ -377,8 +379,9 @@ __device__ __forceinline__ void block_layer_norm4(const float (&v)[4], bool live
     for (int k = 0; k < 2; ++k) {
         const NormTarget& t = k ? t1 : t0;
         if (!t.out_row) continue;
-        const float4 g = *reinterpret_cast<const float4*>(t.gamma + c);
-        const float4 b = *reinterpret_cast<const float4*>(t.beta + c);
+        // both targets of a caller that hands in loaded parameters share them
+        const float4 g = loaded_gamma ? *loaded_gamma : *reinterpret_cast<const float4*>(t.gamma + c);
+        const float4 b = loaded_beta ? *loaded_beta : *reinterpret_cast<const float4*>(t.beta + c);
         const float y0 = fmaf(d[0] * inv, g.x, b.x), y1 = fmaf(d[1] * inv, g.y, b.y);
         const float y2 = fmaf(d[2] * inv, g.z, b.z), y3 = fmaf(d[3] * inv, g.w, b.w);
         uint2 packed;
