@@ -163,8 +163,8 @@ __device__ __forceinline__ float chunk_dot(const unsigned char* row, const float
 // The rows at position `exclude` and at the positions excl[0 .. n_excl) score -inf.  With a
 // barrier address in `bar` the rows are still being copied: the warp waits for them after it has
 // worked out its first rows' positions (`arrived` = false when the wait gave up).  With `cand`
-// the scores go to candidate slots slot0 + r; in every case the warp's best (score, lowest
-// position on ties) is folded into (best_key, best_pos), identical in all lanes.
+// the scores go to candidate slots slot0 + r and nothing else happens; without, the warp's best
+// (score, lowest position on ties) is folded into (best_key, best_pos), identical in all lanes.
 template <bool kBf16, int kLpr>
 __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key_dtype_arg, int n_rows,
                                               const int* sel, int bs, int first_valid, int pos0,
@@ -229,7 +229,10 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         if (kLpr >= 2) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 1));
         if (kLpr == 4) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 2));
         const float sc = valid ? __fmul_rn(part, 0.125f) : kNegInf;
-        if (cand && r < n_rows && sub == 0) cand[slot0 + r] = sc;
+        if (cand) {                 // the partner stream only fills the candidate table
+            if (r < n_rows && sub == 0) cand[slot0 + r] = sc;
+            continue;
+        }
         const uint32_t key = float_key(sc);
         if (valid && (key > my_key || my_pos == 0x7fffffff || (key == my_key && pos < my_pos))) {
             my_key = key;
@@ -237,6 +240,7 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         }
     }
     RLM_PROBE_T(28, 128);
+    if (cand) return;
     warp_argmax_key(my_key, my_pos);
     if (my_pos != 0x7fffffff &&
         (my_key > best_key || best_pos == 0x7fffffff || (my_key == best_key && my_pos < best_pos))) {
