@@ -40,10 +40,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxKOut = 32;  // partner slots per query
-#ifndef RLM_FILTER_MIN_CAP
-#define RLM_FILTER_MIN_CAP 129
-#endif
-constexpr int kFilterMinCap = RLM_FILTER_MIN_CAP;  // smallest candidate count that takes the threshold filter
 constexpr int kMaxExclude = 8; // extra excluded positions per query (multi-anchor selection)
 constexpr int kD = 64;        // exact-score width == router heads * head width
 
@@ -813,10 +809,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         }
         RLM_PROBE(20);
     }
-    // Exact top-K by rank counting: a candidate's output slot is the number of candidates
-    // that beat it (higher score, or equal score in an earlier slot).  `parts` adjacent
-    // threads share one candidate and scan interleaved groups of four slots.  Slots past the
-    // valid candidates carry score -inf and the position of candidate slot 0.
+    // Exact top-K of the candidate table: output slot k holds the k-th best candidate (higher
+    // score first, equal scores by the earlier slot); results without a finite score report
+    // score -inf and the position of candidate slot 0.
     const int K = a.k_out;
     if (cap4 <= 256) {
         // Up to 256 candidate slots: warp 0 holds them all in registers (see topk_tournament)
@@ -834,8 +829,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     // Threshold filter: the K-th largest of the sixteen half-warp maxima is a lower bound of
     // the K-th largest score, so only candidates at or above it can be selected.  They are
     // compacted into a short list and ranked exactly there; when the list is long (many equal
-    // or -inf scores) the general paths below take over with the score table untouched.
-    if (cap >= kFilterMinCap && K <= 2 * kWarps && cap > 16 * (K - 1)) {
+    // or -inf scores) the tournament through shared memory below takes over with the score
+    // table untouched.
+    if (K <= 2 * kWarps && cap > 16 * (K - 1)) {
         uint32_t kmax = 0;
         for (int c = tid; c < cap; c += kThreads) kmax = max(kmax, float_key(cand[c] + 0.0f));
 #pragma unroll

@@ -101,6 +101,34 @@ def test_packed_select_matches_oracle_at_baseline_shapes(shape, strict):
     assert_status_clear()
 
 
+@pytest.mark.parametrize("shape", [
+    (4, 2048, 32, 128, 2, 8, "bf16"),     # 256 candidates: register tournament of eight per lane, head-per-lane blocks
+    (2, 4096, 64, 128, 4, 8, "bf16"),     # 384 candidates: threshold filter, two block scores per lane when picking
+    (3, 512, 16, 64, 2, 32, "fp32"),      # 128 candidates, 32 partner slots
+    (2, 256, 8, 8, 1, 16, "bf16"),        # more partner slots (16) than some positions have candidates
+])
+def test_tie_heavy_inputs_keep_the_lowest_position(shape):
+    """Quantised inputs (every dot product exact, neighbouring blocks' statistics and every third
+    key row duplicated): equal scores everywhere, so block picking, the anchor arg-max and the
+    top-K must all break ties the way the oracle does (lowest block, lowest position)."""
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    B, T, NB, L, top, K, dtype = shape
+    case = {"kind": "select", "seed": 7300 + T + K, "batch": B, "context": T, "blocks": NB, "local_window": L,
+            "top_blocks": top, "k_out": K, "strict_valid": False, "dtype": dtype, "quantize": True}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    bs = T // NB
+    for t in sorted({0, 3, L - 1, L, 2 * bs + 1, T // 2, T - 1}):
+        a, a_s, p, p_s = relation_select_packed(*select_args(xg), position_tensor(t), L, top, K, False)
+        oa, oa_s, op, op_s, _ = oracle.relation_select(*select_args(x), t, L, top, K, False)
+        assert torch.equal(a.cpu(), oa), (shape, t)
+        assert torch.equal(p.cpu(), op), (shape, t)
+        assert_scores_equal(a_s, oa_s)
+        assert_scores_equal(p_s, op_s)
+    assert_status_clear()
+
+
 @pytest.mark.parametrize("strict", [False, True])
 def test_rows_form_equals_decode_form_at_every_position(strict):
     """Per-row positions: every t of a context-128 sequence in one launch (fp32, block 16)."""
