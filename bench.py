@@ -622,6 +622,17 @@ def run_kernel_case(args) -> None:
                 sc, gm, bt = torch.randn(B, K, device=dev), torch.ones(d, device=dev), torch.zeros(d, device=dev)
             raw = S[i % sets]
             fn = lambda: relation_norm_reduce(raw, sc, gm, bt, pos, 1e-5)  # noqa: E731
+        elif args.kernel_case == "norm_project":
+            if i == 0:
+                from relation_lm.kernels.relation_reduce import relation_norm_reduce_residual_norm_project
+                S = [rn(B, K, d) for _ in range(sets)]
+                sc, gm, bt = torch.randn(B, K, device=dev), torch.ones(d, device=dev), torch.zeros(d, device=dev)
+                residual, mix = torch.randn(B, d, device=dev), torch.tensor(0.3, device=dev)
+                normalized, wq = rn(B, d), rn(256, d) * 0.04
+                projected = rn(B, 256)
+            raw = S[i % sets]
+            fn = lambda: relation_norm_reduce_residual_norm_project(  # noqa: E731
+                raw, sc, gm, bt, pos, 1e-5, residual, mix, gm, bt, 1e-5, normalized, wq, projected)
         else:
             if i == 0:
                 S = [([rn(B, T, 64) for _ in range(4)], [rn(B, nb, 4, 16) for _ in range(4)]) for _ in range(sets)]
@@ -648,7 +659,7 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
-    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "router"),
+    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router"),
                         default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")

@@ -527,13 +527,18 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_kernel(cons
 // (shared memory, dim 16-bit values) the next layer's normalised row is left there as well.
 // kEarly (kernels without an occupancy target): the affine parameters, the residual row and the
 // mixing weight are requested into registers at the top instead of where the chain reaches them.
-template <int kVecChunks, bool kEarly>
+template <int kVecChunks, bool kEarly, bool kPlain>
 __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, float* partial,
                                                     void* normalized_copy) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // kPlain: bf16 partner rows in one slice without a bias, fp32 parameters, bf16 normalised
+    // output (the decode step): the dtype and slice branches fold away
+    const int raw_dtype = kPlain ? RLM_BF16 : a.raw_dtype, param_dtype = kPlain ? RLM_F32 : a.param_dtype;
+    const int next_dtype = kPlain ? RLM_BF16 : a.next_dtype, raw_splits = kPlain ? 1 : a.raw_splits;
+    const void* raw_bias = kPlain ? nullptr : a.raw_bias;
     const int K = a.k_out, D = a.dim;
     const int chunks = D / 8;
-    const size_t raw_elem = a.raw_dtype == RLM_F32 ? 4 : 2;
+    const size_t raw_elem = raw_dtype == RLM_F32 ? 4 : 2;
 
     // loads that depend on nothing first: position, scores, this warp's first partner row, affine
     const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
@@ -547,8 +552,8 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
 #pragma unroll
         for (int i = 0; i < kVecChunks; ++i)
             if (lane + 32 * i < chunks) {
-                load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm_early[i]);
-                load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt_early[i]);
+                load8(a.weight, 8 * (lane + 32 * i), param_dtype, gm_early[i]);
+                load8(a.bias, 8 * (lane + 32 * i), param_dtype, bt_early[i]);
             }
         if (4 * tid < D) {
             if (a.residual) res_early = *reinterpret_cast<const float4*>(a.residual + static_cast<size_t>(row) * D + 4 * tid);
@@ -561,16 +566,16 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
     }
     // one 8-column chunk of partner row k: the slices of a split-K GEMM are summed and the bias added here
     auto load_raw = [&](const char* row_k, int chunk, float (&dst)[8]) {
-        load8(row_k, 8 * chunk, a.raw_dtype, dst);
-        for (int sp = 1; sp < a.raw_splits; ++sp) {
+        load8(row_k, 8 * chunk, raw_dtype, dst);
+        for (int sp = 1; sp < raw_splits; ++sp) {
             float more[8];
-            load8(row_k + static_cast<size_t>(sp) * a.raw_split_stride * raw_elem, 8 * chunk, a.raw_dtype, more);
+            load8(row_k + static_cast<size_t>(sp) * a.raw_split_stride * raw_elem, 8 * chunk, raw_dtype, more);
 #pragma unroll
             for (int e = 0; e < 8; ++e) dst[e] += more[e];
         }
-        if (a.raw_bias) {
+        if (raw_bias) {
             float bias8[8];
-            load8(a.raw_bias, 8 * chunk, a.param_dtype, bias8);
+            load8(raw_bias, 8 * chunk, param_dtype, bias8);
 #pragma unroll
             for (int e = 0; e < 8; ++e) dst[e] += bias8[e];
         }
@@ -629,8 +634,8 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
 #pragma unroll
                     for (int e = 0; e < 8; ++e) { gm[e] = gm_early[i][e]; bt[e] = bt_early[i][e]; }
                 } else {
-                    load8(a.weight, 8 * (lane + 32 * i), a.param_dtype, gm);
-                    load8(a.bias, 8 * (lane + 32 * i), a.param_dtype, bt);
+                    load8(a.weight, 8 * (lane + 32 * i), param_dtype, gm);
+                    load8(a.bias, 8 * (lane + 32 * i), param_dtype, bt);
                 }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[i][e] = fmaf(wk, fmaf(x[i][e] * inv, gm[e], bt[e]), y[i][e]);
@@ -671,16 +676,16 @@ __device__ __forceinline__ void norm_reduce_vec_row(const NormArgs& a, int row, 
         __shared__ float scratch[18];
         NormTarget t0{a.next_w, a.next_b, static_cast<uint16_t*>(a.next_out) + static_cast<size_t>(row) * D};
         NormTarget t1{a.next_w, a.next_b, normalized_copy};
-        block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, a.next_dtype, scratch,
+        block_layer_norm4(updated, live, c, D, a.next_eps, t0, t1, next_dtype, scratch,
                           kEarly ? &next_g : nullptr, kEarly ? &next_b : nullptr);
     }
 }
 
-template <int kVecChunks>
+template <int kVecChunks, bool kPlain>
 __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunks == 3 ? 3 : 2)) relation_norm_reduce_vec_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];   // [warps][dim]
     griddep_sync();
-    norm_reduce_vec_row<kVecChunks, false>(a, blockIdx.x, partial, nullptr);
+    norm_reduce_vec_row<kVecChunks, false, kPlain>(a, blockIdx.x, partial, nullptr);
 }
 
 // ---- norm-reduce + residual + next LayerNorm + the next layer's query projection, for decode
@@ -709,13 +714,14 @@ __device__ __forceinline__ void store_cluster_shared16(const void* local_ptr, ui
                  ::"r"(remote), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-template <int kVecChunks>
+template <int kVecChunks, bool kPlain>
 __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_kernel(const NormArgs a) {
     extern __shared__ __align__(16) float partial[];            // [warps][dim], CTA 0 of the cluster
     __shared__ __align__(16) uint16_t normalized_row[1024];
     constexpr int kPieces = 4 * kVecChunks;                      // 16-byte weight pieces per thread: dim <= 256 * kVecChunks
     const int tid = threadIdx.x;
     const int D = a.dim, pieces = D / 64;                        // dim is a multiple of 64
+    const int next_dtype = kPlain ? RLM_BF16 : a.next_dtype;
     const uint32_t rank = cluster_rank();
     const int slices = a.proj_out_dim / kProjCols;
     const int row = blockIdx.x / slices;
@@ -733,7 +739,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
     griddep_sync();
     RLM_PROBE(2);
     if (rank == 0) {
-        norm_reduce_vec_row<kVecChunks, true>(a, row, partial, normalized_row);
+        norm_reduce_vec_row<kVecChunks, true, kPlain>(a, row, partial, normalized_row);
         __syncthreads();
         if (tid < D / 8) {          // hand the normalised row to the other CTAs of the cluster
             const uint4 v = reinterpret_cast<const uint4*>(normalized_row)[tid];
@@ -752,8 +758,8 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
             Raw8 raw;
             raw.lo = w[j];
             raw.hi = make_uint4(0, 0, 0, 0);
-            convert8(raw, a.next_dtype, wf);
-            load8(normalized_row, 8 * (part + 8 * j), a.next_dtype, xf);
+            convert8(raw, next_dtype, wf);
+            load8(normalized_row, 8 * (part + 8 * j), next_dtype, xf);
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc = fmaf(wf[e], xf[e], acc);
         }
@@ -762,7 +768,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
     if (part == 0)
-        store_scalar(a.proj_out, static_cast<int64_t>(row) * a.proj_out_dim + col, a.next_dtype, acc);
+        store_scalar(a.proj_out, static_cast<int64_t>(row) * a.proj_out_dim + col, next_dtype, acc);
     RLM_PROBE(6);
 }
 
@@ -859,22 +865,24 @@ int norm_reduce_launch(
         a.proj_weight = proj_weight; a.proj_out = proj_out; a.proj_out_dim = proj_out_dim;
         const unsigned slices = static_cast<unsigned>(proj_out_dim / kProjCols);
         const dim3 grid(static_cast<unsigned>(n_rows) * slices);
-        if (dim <= 512)
-            launch_kernel_cluster(relation_norm_reduce_project_kernel<2>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
-        else if (dim <= 768)
-            launch_kernel_cluster(relation_norm_reduce_project_kernel<3>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
-        else
-            launch_kernel_cluster(relation_norm_reduce_project_kernel<4>, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
+        const bool plain = raw_dtype == RLM_BF16 && param_dtype == RLM_F32 && next_dtype == RLM_BF16 &&
+                           a.raw_splits == 1 && !raw_bias;
+        auto kernel = dim <= 512 ? (plain ? relation_norm_reduce_project_kernel<2, true> : relation_norm_reduce_project_kernel<2, false>)
+                    : dim <= 768 ? (plain ? relation_norm_reduce_project_kernel<3, true> : relation_norm_reduce_project_kernel<3, false>)
+                                 : (plain ? relation_norm_reduce_project_kernel<4, true> : relation_norm_reduce_project_kernel<4, false>);
+        launch_kernel_cluster(kernel, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
         count_launch();
         return check_launch("relation_norm_reduce_project_kernel");
     }
-    if (vec && dim <= 512)
-        launch_kernel(relation_norm_reduce_vec_kernel<2>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
-    else if (vec && dim <= 768)
-        launch_kernel(relation_norm_reduce_vec_kernel<3>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
-    else if (vec)
-        launch_kernel(relation_norm_reduce_vec_kernel<4>, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
-    else
+    // the decode step's dtypes (bf16 rows in one slice, fp32 parameters) take builds without dtype branches
+    const bool plain_rows = raw_dtype == RLM_BF16 && param_dtype == RLM_F32 && a.raw_splits == 1 && !raw_bias &&
+                            (!next_normalized || next_dtype == RLM_BF16);
+    if (vec) {
+        auto kernel = dim <= 512 ? (plain_rows ? relation_norm_reduce_vec_kernel<2, true> : relation_norm_reduce_vec_kernel<2, false>)
+                    : dim <= 768 ? (plain_rows ? relation_norm_reduce_vec_kernel<3, true> : relation_norm_reduce_vec_kernel<3, false>)
+                                 : (plain_rows ? relation_norm_reduce_vec_kernel<4, true> : relation_norm_reduce_vec_kernel<4, false>);
+        launch_kernel(kernel, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
+    } else
         launch_kernel(relation_norm_reduce_kernel, dim3(n_rows), dim3(kNormThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch("relation_norm_reduce_kernel");
