@@ -79,10 +79,13 @@ __device__ __forceinline__ void store8(float* dst, const float (&f)[8]) {
 }
 
 // NR = relation rows per thread: the tile's kRB*K rows are dealt to 8 thread rows.
-template <bool kUpdate, int NR>
+// kBf16: caches, weights and output are all bfloat16 (the decode step): dtype branches fold away.
+template <bool kUpdate, int NR, bool kBf16>
 __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const HiddenArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x;
+    const int cache_dtype = kBf16 ? RLM_BF16 : a.cache_dtype, weight_dtype = kBf16 ? RLM_BF16 : a.weight_dtype,
+              out_dtype = kBf16 ? RLM_BF16 : a.out_dtype;
     const int R = a.rdim, H = a.hdim, K = a.k_out;
     const int stride = R + kPad;
     const int tile_rows = kRB * K;
@@ -99,8 +102,8 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
 
     RLM_PROBE(0);
     const int h0 = blockIdx.x * kHT;
-    const int ws = a.weight_dtype == RLM_F32 ? 4 : 2;
-    const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
+    const int ws = weight_dtype == RLM_F32 ? 4 : 2;
+    const int cs = cache_dtype == RLM_F32 ? 4 : 2;
     const int segs = R / 8;
     // quotients by the two run-time divisors of the index arithmetic: shifts when they are powers of two
     const int segs_shift = (segs & (segs - 1)) == 0 ? 31 - __clz(segs) : -1;
@@ -116,19 +119,19 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
         rp = rm;
         if (h0 + r < H) {
             const size_t off = static_cast<size_t>(h0 + r) * R * ws;
-            rm = load8_raw(static_cast<const char*>(a.product_weight) + off, 8 * sgm, a.weight_dtype);
+            rm = load8_raw(static_cast<const char*>(a.product_weight) + off, 8 * sgm, weight_dtype);
             if (kUpdate) {
-                ra = load8_raw(static_cast<const char*>(a.anchor_weight) + off, 8 * sgm, a.weight_dtype);
-                rp = load8_raw(static_cast<const char*>(a.partner_weight) + off, 8 * sgm, a.weight_dtype);
+                ra = load8_raw(static_cast<const char*>(a.anchor_weight) + off, 8 * sgm, weight_dtype);
+                rp = load8_raw(static_cast<const char*>(a.partner_weight) + off, 8 * sgm, weight_dtype);
             }
         }
         float f[8];
-        convert8(rm, a.weight_dtype, f);
+        convert8(rm, weight_dtype, f);
         store8(wm + r * stride + 8 * sgm, f);
         if (kUpdate) {
-            convert8(ra, a.weight_dtype, f);
+            convert8(ra, weight_dtype, f);
             store8(wa + r * stride + 8 * sgm, f);
-            convert8(rp, a.weight_dtype, f);
+            convert8(rp, weight_dtype, f);
             store8(wp + r * stride + 8 * sgm, f);
         }
     }
@@ -176,11 +179,11 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             if (prow < tile_rows && seq[rb] >= 0) {
                 const char* operand = static_cast<const char*>(a.operand_cache) +
                                       static_cast<size_t>(seq[rb]) * a.max_t * R * cs;
-                Raw8 ra = load8_raw(operand + static_cast<size_t>(idx[rb][0]) * R * cs, 8 * sgm, a.cache_dtype);
-                Raw8 rp = load8_raw(operand + static_cast<size_t>(idx[rb][k + 1]) * R * cs, 8 * sgm, a.cache_dtype);
+                Raw8 ra = load8_raw(operand + static_cast<size_t>(idx[rb][0]) * R * cs, 8 * sgm, cache_dtype);
+                Raw8 rp = load8_raw(operand + static_cast<size_t>(idx[rb][k + 1]) * R * cs, 8 * sgm, cache_dtype);
                 float oa[8], op[8];
-                convert8(ra, a.cache_dtype, oa);
-                convert8(rp, a.cache_dtype, op);
+                convert8(ra, cache_dtype, oa);
+                convert8(rp, cache_dtype, op);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = op[e] * oa[e];
             }
@@ -193,7 +196,7 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
                 if (seq[rb] >= 0)
                     load8(static_cast<const char*>(a.operand_cache) +
                               (static_cast<size_t>(seq[rb]) * a.max_t + t) * R * cs,
-                          8 * sgm, a.cache_dtype, o);
+                          8 * sgm, cache_dtype, o);
                 store8(cur + rb * R + 8 * sgm, o);
             }
         }
@@ -222,13 +225,13 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             const bool two = h0 + hh + 1 < H;
             if (!sub_a[e]) {
                 const int64_t at = ebase + static_cast<int64_t>(ai) * 2 * H + h0 + hh;
-                base_a[e].x = load_scalar(a.expanded_cache, at, a.cache_dtype);
-                if (two) base_a[e].y = load_scalar(a.expanded_cache, at + 1, a.cache_dtype);
+                base_a[e].x = load_scalar(a.expanded_cache, at, cache_dtype);
+                if (two) base_a[e].y = load_scalar(a.expanded_cache, at + 1, cache_dtype);
             }
             if (!sub_p[e]) {
                 const int64_t at = ebase + static_cast<int64_t>(pi) * 2 * H + H + h0 + hh;
-                base_p[e].x = load_scalar(a.expanded_cache, at, a.cache_dtype);
-                if (two) base_p[e].y = load_scalar(a.expanded_cache, at + 1, a.cache_dtype);
+                base_p[e].x = load_scalar(a.expanded_cache, at, cache_dtype);
+                if (two) base_p[e].y = load_scalar(a.expanded_cache, at + 1, cache_dtype);
             }
         }
         __syncthreads();
@@ -288,10 +291,10 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
                     float v = 0.0f;
 #pragma unroll
                     for (int q = 0; q < kSplit; ++q) v += red2[((q * kRB + rb) * 2 + half) * kHT + hh + j];
-                    if (half == 0) v += load_scalar(a.first_bias, h0 + hh + j, a.weight_dtype);
+                    if (half == 0) v += load_scalar(a.first_bias, h0 + hh + j, weight_dtype);
                     store_scalar(a.expanded_cache,
                                  (static_cast<int64_t>(seq[rb]) * a.max_t + t) * 2 * H + half * H + h0 + hh + j,
-                                 a.cache_dtype, v);
+                                 cache_dtype, v);
                 }
             }
         }
@@ -316,11 +319,11 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
                         fa += red2[((q * kRB + rb) * 2 + 0) * kHT + hh + j];
                         fp += red2[((q * kRB + rb) * 2 + 1) * kHT + hh + j];
                     }
-                    if (sub_a[e]) ba = fa + load_scalar(a.first_bias, h0 + hh + j, a.weight_dtype);
+                    if (sub_a[e]) ba = fa + load_scalar(a.first_bias, h0 + hh + j, weight_dtype);
                     if (sub_p[e]) bp = fp;
                 }
                 store_scalar(a.out, (static_cast<int64_t>(out_row[e]) * K + out_k[e]) * H + h0 + hh + j,
-                             a.out_dtype, gelu_erf(v + (ba + bp)));
+                             out_dtype, gelu_erf(v + (ba + bp)));
             }
         }
         RLM_PROBE(5);
@@ -341,7 +344,8 @@ int launch_hidden_as(const HiddenArgs& a, void* stream) {
         set_error("relation_hidden: relation_dim too large for the staged weight tiles");
         return RLM_ERR_SMEM;
     }
-    auto kernel = relation_hidden_kernel<kUpdate, NR>;
+    const bool bf16 = a.cache_dtype == RLM_BF16 && a.weight_dtype == RLM_BF16 && a.out_dtype == RLM_BF16;
+    auto kernel = bf16 ? relation_hidden_kernel<kUpdate, NR, true> : relation_hidden_kernel<kUpdate, NR, false>;
     if (smem_bytes > 48 * 1024) {
         int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
         if (rc != RLM_OK) return rc;

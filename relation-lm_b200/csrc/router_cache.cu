@@ -43,13 +43,18 @@ struct RouterArgs {
     int token_width[4];
 };
 
+// kBf16: raw keys, caches, statistics and conv weights are all bfloat16 (the decode step), so the
+// dtype branches fold away.
+template <bool kBf16>
 __device__ __forceinline__ void router_update(const RouterArgs& a, int b, int layer,
                                               unsigned char* smem, uint32_t bar, int t) {
     const int tid = threadIdx.x;
+    const int raw_dtype = kBf16 ? RLM_BF16 : a.raw_dtype, cache_dtype = kBf16 ? RLM_BF16 : a.cache_dtype,
+              stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype, weight_dtype = kBf16 ? RLM_BF16 : a.weight_dtype;
     const int s = tid / kD, c = tid % kD;
     const int bs = a.block_size;
     const int blk = t / bs, start = blk * bs;
-    const int cs = a.cache_dtype == RLM_F32 ? 4 : 2;
+    const int cs = cache_dtype == RLM_F32 ? 4 : 2;
     const uint32_t tile_bytes = static_cast<uint32_t>(bs) * kD * cs;
     const int64_t seq = static_cast<int64_t>(layer) * a.batch + b;   // row of the [layers*B, ...] tensors
     if (tid == 0) {
@@ -62,19 +67,19 @@ __device__ __forceinline__ void router_update(const RouterArgs& a, int b, int la
     const int64_t row_t = (seq * a.max_t + t) * kD + c;
     const int64_t row_1 = (seq * a.max_t + max(t - 1, 0)) * kD + c;
     const int64_t row_2 = (seq * a.max_t + max(t - 2, 0)) * kD + c;
-    const float raw = load_scalar(a.raw[s], b * a.raw_stride[s] + layer * a.raw_layer_stride + c, a.raw_dtype);
-    const float prev1 = load_scalar(a.raw_cache[s], row_1, a.cache_dtype);
-    const float prev2 = load_scalar(a.raw_cache[s], row_2, a.cache_dtype);
+    const float raw = load_scalar(a.raw[s], b * a.raw_stride[s] + layer * a.raw_layer_stride + c, raw_dtype);
+    const float prev1 = load_scalar(a.raw_cache[s], row_1, cache_dtype);
+    const float prev2 = load_scalar(a.raw_cache[s], row_2, cache_dtype);
     const int64_t wrow = (static_cast<int64_t>(layer) * kD + c) * 3;
-    const float w0 = load_scalar(a.weight[s], wrow + 0, a.weight_dtype);
-    const float w1 = load_scalar(a.weight[s], wrow + 1, a.weight_dtype);
-    const float w2 = load_scalar(a.weight[s], wrow + 2, a.weight_dtype);
+    const float w0 = load_scalar(a.weight[s], wrow + 0, weight_dtype);
+    const float w1 = load_scalar(a.weight[s], wrow + 1, weight_dtype);
+    const float w2 = load_scalar(a.weight[s], wrow + 2, weight_dtype);
     const float v1 = t >= 1 ? 1.0f : 0.0f, v2 = t >= 2 ? 1.0f : 0.0f;
     float conv = __fmul_rn(raw, w2);
     conv = __fadd_rn(conv, __fmul_rn(__fmul_rn(prev1, w1), v1));
     conv = __fadd_rn(conv, __fmul_rn(__fmul_rn(prev2, w0), v2));
-    store_scalar(a.raw_cache[s], row_t, a.cache_dtype, raw);
-    store_scalar(a.conv_cache[s], row_t, a.cache_dtype, conv);
+    store_scalar(a.raw_cache[s], row_t, cache_dtype, raw);
+    store_scalar(a.conv_cache[s], row_t, cache_dtype, conv);
     if (a.out) a.out[(seq * 2 + s) * kD + c] = conv;
 
     bool ok = mbar_wait(bar, 0);
@@ -86,23 +91,25 @@ __device__ __forceinline__ void router_update(const RouterArgs& a, int b, int la
     const int cur = t - start;
     float sum = 0.0f;
     for (int r = 0; r < bs; ++r) {
-        float x = r == cur ? conv : load_scalar(tile, r * kD + c, a.cache_dtype);
+        float x = r == cur ? conv : load_scalar(tile, r * kD + c, cache_dtype);
         sum = __fadd_rn(sum, x);
     }
     const float mean = __fdiv_rn(sum, static_cast<float>(bs));
     float acc = 0.0f;
     for (int r = 0; r < bs; ++r) {
-        float x = r == cur ? conv : load_scalar(tile, r * kD + c, a.cache_dtype);
+        float x = r == cur ? conv : load_scalar(tile, r * kD + c, cache_dtype);
         float d = __fsub_rn(x, mean);
         acc = __fmaf_rn(d, d, acc);
     }
     const float sd = __fsqrt_rn(__fdiv_rn(acc, static_cast<float>(bs)));
     const int64_t stat = (seq * a.n_blocks + blk) * kD + c;
-    store_scalar(a.mean[s], stat, a.stats_dtype, mean);
-    store_scalar(a.stdv[s], stat, a.stats_dtype, sd);
+    store_scalar(a.mean[s], stat, stats_dtype, mean);
+    store_scalar(a.stdv[s], stat, stats_dtype, sd);
 }
 
+template <bool kBf16>
 __global__ void __launch_bounds__(kThreads) router_cache_update_kernel(const RouterArgs a) {
+    const int raw_dtype = kBf16 ? RLM_BF16 : a.raw_dtype, cache_dtype = kBf16 ? RLM_BF16 : a.cache_dtype;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long bar_storage;
     griddep_sync();
@@ -128,12 +135,12 @@ __global__ void __launch_bounds__(kThreads) router_cache_update_kernel(const Rou
         for (int i = 0; i < 4; ++i) {
             const int w = a.token_width[i];
             for (int c = tid; c < w; c += kThreads)
-                store_scalar(a.token_cache[i], (seq * a.max_t + t) * w + c, a.cache_dtype,
-                             load_scalar(a.packed, src + first + c, a.raw_dtype));
+                store_scalar(a.token_cache[i], (seq * a.max_t + t) * w + c, cache_dtype,
+                             load_scalar(a.packed, src + first + c, raw_dtype));
             first += w;
         }
     }
-    router_update(a, b, layer, smem, bar, t);
+    router_update<kBf16>(a, b, layer, smem, bar, t);
 }
 
 // Prefill: conv + statistics of positions [0, length) of zero-initialised caches in one launch,
@@ -238,12 +245,15 @@ int validate_and_launch(RouterArgs& a, void* stream, const char* who) {
         set_error("router update: block tile exceeds 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
+    const bool bf16 = a.raw_dtype == RLM_BF16 && a.cache_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16 &&
+                      a.weight_dtype == RLM_BF16;
+    auto kernel = bf16 ? router_cache_update_kernel<true> : router_cache_update_kernel<false>;
     if (smem_bytes > 48 * 1024) {
-        int rc = allow_large_smem(reinterpret_cast<const void*>(router_cache_update_kernel), kSmemPerCta);
+        int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
         if (rc != RLM_OK) return rc;
     }
     dim3 grid(a.batch, a.layers);
-    launch_kernel(router_cache_update_kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, a);
+    launch_kernel(kernel, dim3(grid), dim3(kThreads), smem_bytes, stream, a);
     count_launch();
     return check_launch(who);
 }
