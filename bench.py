@@ -483,21 +483,19 @@ def run_ours(args) -> None:
     warm_ms = s.elapsed_time(e) / min(args.steps, 64)
 
     # end to end: host token ids in, greedy token out, every step
-    host_in = torch.zeros(2, B, dtype=torch.int64).pin_memory()
-    host_out = torch.zeros(B, dtype=torch.int64).pin_memory()
-    host_in[0].copy_(tokens[:, prefix].cpu())
-    dec.position.fill_(prefix)
-    stream = torch.cuda.current_stream(device)
+    # (the decoder's host-transfer graph: pinned ids -> device at its head, chosen tokens -> pinned
+    # memory at its tail, one launch and one stream synchronisation per position)
+    dec.position.fill_(prefix)                          # the capture's warm-up steps run at the current position
+    dec.capture_host_io()
+    dec.host_tokens.copy_(tokens[:, prefix].cpu())
+    dec.host_boundaries.zero_()
+    torch.cuda.synchronize()
     e2e_steps = min(args.steps, 64)
     barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        dec.static_tokens.copy_(host_in[0], non_blocking=True)
-        dec.static_boundaries.copy_(host_in[1], non_blocking=True)
-        dec.replay()
-        host_out.copy_(dec.static_next, non_blocking=True)
-        stream.synchronize()
-        host_in[0].copy_(host_out)                      # greedy feedback through the host
+        chosen = dec.step_host()
+        dec.host_tokens.copy_(chosen)                   # greedy feedback through the host
     e2e_s = time.perf_counter() - t0
     barrier()
     clocks = sampler.stop() if sampler else None

@@ -429,7 +429,7 @@ __device__ __noinline__ void pick_blocks(const float* scores, int nb, int top, i
 // inside a lane.  The winner pops its head.  Slots past the candidates hold key 0 and never
 // beat a score; a result whose score is -inf (or missing) reports position t - L + 1.
 template <int kN>
-__device__ __forceinline__ void topk_tournament(const float* cand, int cap4, int K, int L, int t, int bs,
+__device__ __noinline__ void topk_tournament(const float* cand, int cap4, int K, int L, int t, int bs,
                                                 int bs_shift, const int* sel, int32_t* out_pos, float* out_score) {
     const int lane = threadIdx.x & 31;
     const float4* cand4 = reinterpret_cast<const float4*>(cand);
@@ -477,6 +477,124 @@ __device__ __forceinline__ void topk_tournament(const float* cand, int cap4, int
         else { const int rr = bs_shift >= 0 ? (cs - L) >> bs_shift : (cs - L) / bs; pos = sel[3 * rr] * bs + (cs - L - rr * bs); }
         out_pos[lane] = pos;
         out_score[lane] = sc;
+    }
+}
+
+// Exact top-K of more than 256 candidate slots, by the whole CTA (out of line: the decode shapes
+// never come here, and the selector's common path stays compact).
+__device__ __noinline__ void topk_large(float* cand, int cap, int K, int L, int t, int bs, const int* sel,
+                                        int32_t* out_pos, float* out_score) {
+    __shared__ uint32_t surv_key[kWarps * kMaxKOut];
+    __shared__ int surv_slot[kWarps * kMaxKOut];
+    __shared__ uint32_t group_max[2 * kWarps];
+    __shared__ int short_count;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) short_count = 0;
+    __syncthreads();
+    // Threshold filter: the K-th largest of the sixteen half-warp maxima is a lower bound of
+    // the K-th largest score, so only candidates at or above it can be selected.  They are
+    // compacted into a short list and ranked exactly there; when the list is long (many equal
+    // or -inf scores) the tournament through shared memory below takes over with the score
+    // table untouched.
+    if (K <= 2 * kWarps && cap > 16 * (K - 1)) {
+        uint32_t kmax = 0;
+        for (int c = tid; c < cap; c += kThreads) kmax = max(kmax, float_key(cand[c] + 0.0f));
+#pragma unroll
+        for (int s = 8; s > 0; s >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, s));
+        if ((lane & 15) == 0) group_max[tid >> 4] = kmax;
+        __syncthreads();
+        const uint32_t g = group_max[lane & 15];
+        int grank = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t o = __shfl_sync(0xffffffffu, g, j);
+            grank += (o > g) || (o == g && j < (lane & 15));
+        }
+        const unsigned holder = __ballot_sync(0xffffffffu, grank == K - 1) & 0xffffu;
+        const uint32_t tau = __shfl_sync(0xffffffffu, g, __ffs(holder) - 1);
+        for (int c0 = 0; c0 < cap; c0 += kThreads) {
+            const int c = c0 + tid;
+            const uint32_t key = c < cap ? float_key(cand[c] + 0.0f) : 0u;
+            const bool pass = c < cap && key >= tau;
+            const unsigned m = __ballot_sync(0xffffffffu, pass);
+            int base = 0;
+            if (lane == 0 && m) base = atomicAdd(&short_count, __popc(m));
+            base = __shfl_sync(0xffffffffu, base, 0);
+            const int at = base + __popc(m & ((1u << lane) - 1u));
+            if (pass && at < kWarps * kMaxKOut) { surv_key[at] = key; surv_slot[at] = c; }
+        }
+        __syncthreads();
+        const int n = short_count;
+        if (tau > float_key(kNegInf) && n <= kThreads / 4) {
+            const int i = tid >> 2, part = tid & 3;
+            int rank = 0, c = 0;
+            uint32_t key = 0;
+            if (i < n) {
+                key = surv_key[i];
+                c = surv_slot[i];
+                for (int j = part; j < n; j += 4) {
+                    const uint32_t ok = surv_key[j];
+                    rank += (ok > key) || (ok == key && surv_slot[j] < c);
+                }
+            }
+            rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+            rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+            if (i < n && part == 0 && rank < K) {
+                int pos;
+                if (c < L) pos = t - L + 1 + c;
+                else { int r = (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
+                out_pos[rank] = pos;
+                out_score[rank] = cand[c];
+            }
+            return;
+        }
+    }
+    {
+        // Fallback for large candidate sets: tournament through shared memory.  Each warp extracts the top K of the slots it
+        // owns (K rounds of redux arg-max, knocking winners out of the table); warp 0 then
+        // extracts the top K of the 8 K survivors.  Any global top-K candidate is among the
+        // top K of its own warp, and (score, lowest slot) ordering is kept at both levels.
+        for (int r = 0; r < K; ++r) {
+            uint32_t bk = 0;
+            int bc = 0x7fffffff;
+            for (int c = warp * 32 + lane; c < cap; c += kThreads) {
+                uint32_t key = float_key(cand[c]);
+                if (key > bk || bc == 0x7fffffff) { bk = key; bc = c; }
+            }
+            warp_argmax_key(bk, bc);
+            if (lane == 0) {
+                surv_key[warp * kMaxKOut + r] = bc == 0x7fffffff ? 0u : bk;
+                surv_slot[warp * kMaxKOut + r] = bc;
+                if (bc != 0x7fffffff) cand[bc] = __uint_as_float(0xffffffffu);   // below every score: key 0
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int r = 0; r < K; ++r) {
+                uint32_t bk = 0;
+                int bc = 0x7fffffff, bi = -1;
+                for (int i = lane; i < kWarps * K; i += 32) {
+                    const int e = (i / K) * kMaxKOut + (i - (i / K) * K);
+                    uint32_t key = surv_key[e];
+                    int c = surv_slot[e];
+                    if (key != 0u && (key > bk || (key == bk && c < bc) || bc == 0x7fffffff)) { bk = key; bc = c; bi = e; }
+                }
+                const int mine = bc;
+                warp_argmax_key(bk, bc);
+                if (bc != 0x7fffffff && mine == bc && bi >= 0) surv_key[bi] = 0u;
+                if (lane == 0) {
+                    const float sc = bc == 0x7fffffff ? kNegInf : key_float(bk);
+                    int pos;
+                    if (!(sc > kNegInf)) pos = t - L + 1;
+                    else if (bc < L) pos = t - L + 1 + bc;
+                    else { int rr = (bc - L) / bs; pos = sel[3 * rr] * bs + (bc - L - rr * bs); }
+                    out_pos[r] = pos;
+                    out_score[r] = sc;
+                }
+                __syncwarp();
+            }
+        }
     }
 }
 
@@ -546,12 +664,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
     __shared__ int excl_s[kMaxExclude];
-    __shared__ uint32_t surv_key[kWarps * kMaxKOut];
-    __shared__ int surv_slot[kWarps * kMaxKOut];
-    __shared__ uint32_t group_max[2 * kWarps];
-    __shared__ int short_count;
     __shared__ float softplus_s[8];
-    if (threadIdx.x == 0) short_count = 0;
     RLM_TRACE_DECL;
     RLM_PROBE(0);
     const int row = blockIdx.x;
@@ -826,113 +939,9 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         }
         return;
     }
-    // Threshold filter: the K-th largest of the sixteen half-warp maxima is a lower bound of
-    // the K-th largest score, so only candidates at or above it can be selected.  They are
-    // compacted into a short list and ranked exactly there; when the list is long (many equal
-    // or -inf scores) the tournament through shared memory below takes over with the score
-    // table untouched.
-    if (K <= 2 * kWarps && cap > 16 * (K - 1)) {
-        uint32_t kmax = 0;
-        for (int c = tid; c < cap; c += kThreads) kmax = max(kmax, float_key(cand[c] + 0.0f));
-#pragma unroll
-        for (int s = 8; s > 0; s >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, s));
-        if ((lane & 15) == 0) group_max[tid >> 4] = kmax;
-        __syncthreads();
-        const uint32_t g = group_max[lane & 15];
-        int grank = 0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const uint32_t o = __shfl_sync(0xffffffffu, g, j);
-            grank += (o > g) || (o == g && j < (lane & 15));
-        }
-        const unsigned holder = __ballot_sync(0xffffffffu, grank == K - 1) & 0xffffu;
-        const uint32_t tau = __shfl_sync(0xffffffffu, g, __ffs(holder) - 1);
-        for (int c0 = 0; c0 < cap; c0 += kThreads) {
-            const int c = c0 + tid;
-            const uint32_t key = c < cap ? float_key(cand[c] + 0.0f) : 0u;
-            const bool pass = c < cap && key >= tau;
-            const unsigned m = __ballot_sync(0xffffffffu, pass);
-            int base = 0;
-            if (lane == 0 && m) base = atomicAdd(&short_count, __popc(m));
-            base = __shfl_sync(0xffffffffu, base, 0);
-            const int at = base + __popc(m & ((1u << lane) - 1u));
-            if (pass && at < kWarps * kMaxKOut) { surv_key[at] = key; surv_slot[at] = c; }
-        }
-        __syncthreads();
-        const int n = short_count;
-        if (tau > float_key(kNegInf) && n <= kThreads / 4) {
-            const int i = tid >> 2, part = tid & 3;
-            int rank = 0, c = 0;
-            uint32_t key = 0;
-            if (i < n) {
-                key = surv_key[i];
-                c = surv_slot[i];
-                for (int j = part; j < n; j += 4) {
-                    const uint32_t ok = surv_key[j];
-                    rank += (ok > key) || (ok == key && surv_slot[j] < c);
-                }
-            }
-            rank += __shfl_xor_sync(0xffffffffu, rank, 1);
-            rank += __shfl_xor_sync(0xffffffffu, rank, 2);
-            if (i < n && part == 0 && rank < K) {
-                int pos;
-                if (c < L) pos = t - L + 1 + c;
-                else { int r = (c - L) / bs; pos = sel[3 * r] * bs + (c - L - r * bs); }
-                a.out_partner[static_cast<size_t>(row) * K + rank] = pos;
-                a.out_partner_score[static_cast<size_t>(row) * K + rank] = cand[c];
-            }
-            RLM_PROBE(21);
-            return;
-        }
-    }
-    {
-        // Fallback for large candidate sets: tournament through shared memory.  Each warp extracts the top K of the slots it
-        // owns (K rounds of redux arg-max, knocking winners out of the table); warp 0 then
-        // extracts the top K of the 8 K survivors.  Any global top-K candidate is among the
-        // top K of its own warp, and (score, lowest slot) ordering is kept at both levels.
-        for (int r = 0; r < K; ++r) {
-            uint32_t bk = 0;
-            int bc = 0x7fffffff;
-            for (int c = warp * 32 + lane; c < cap; c += kThreads) {
-                uint32_t key = float_key(cand[c]);
-                if (key > bk || bc == 0x7fffffff) { bk = key; bc = c; }
-            }
-            warp_argmax_key(bk, bc);
-            if (lane == 0) {
-                surv_key[warp * kMaxKOut + r] = bc == 0x7fffffff ? 0u : bk;
-                surv_slot[warp * kMaxKOut + r] = bc;
-                if (bc != 0x7fffffff) cand[bc] = __uint_as_float(0xffffffffu);   // below every score: key 0
-            }
-            __syncwarp();
-        }
-        __syncthreads();
-        if (warp == 0) {
-            for (int r = 0; r < K; ++r) {
-                uint32_t bk = 0;
-                int bc = 0x7fffffff, bi = -1;
-                for (int i = lane; i < kWarps * K; i += 32) {
-                    const int e = (i / K) * kMaxKOut + (i - (i / K) * K);
-                    uint32_t key = surv_key[e];
-                    int c = surv_slot[e];
-                    if (key != 0u && (key > bk || (key == bk && c < bc) || bc == 0x7fffffff)) { bk = key; bc = c; bi = e; }
-                }
-                const int mine = bc;
-                warp_argmax_key(bk, bc);
-                if (bc != 0x7fffffff && mine == bc && bi >= 0) surv_key[bi] = 0u;
-                if (lane == 0) {
-                    const float sc = bc == 0x7fffffff ? kNegInf : key_float(bk);
-                    int pos;
-                    if (!(sc > kNegInf)) pos = t - L + 1;
-                    else if (bc < L) pos = t - L + 1 + bc;
-                    else { int rr = (bc - L) / bs; pos = sel[3 * rr] * bs + (bc - L - rr * bs); }
-                    a.out_partner[static_cast<size_t>(row) * K + r] = pos;
-                    a.out_partner_score[static_cast<size_t>(row) * K + r] = sc;
-                }
-                __syncwarp();
-            }
-        }
-        RLM_PROBE(21);
-    }
+    topk_large(cand, cap, K, L, t, bs, sel, a.out_partner + static_cast<size_t>(row) * K,
+               a.out_partner_score + static_cast<size_t>(row) * K);
+    RLM_PROBE(21);
 }
 
 int launch(SelectArgs& a, void* stream) {

@@ -290,3 +290,39 @@ class StatefulDecoder:
 
     def replay(self) -> None:
         self._graph.replay()
+
+    def capture_host_io(self) -> None:
+        """Capture the greedy step together with its host transfers: the token and boundary ids are
+        copied from the pinned tensors ``host_tokens`` / ``host_boundaries`` ``[B]`` (int64) at the
+        head of the graph and the chosen tokens land in the pinned ``host_next`` at its tail, so a
+        serving loop pays one graph launch and one stream synchronisation per position
+        (``step_host``).  State and position are left exactly as they were."""
+        B = self.batch
+        self.host_tokens = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.host_boundaries = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.host_next = torch.zeros(B, dtype=torch.int64).pin_memory()
+        tokens = torch.zeros(B, device=self.device, dtype=torch.int64)
+        boundaries = torch.zeros(B, device=self.device, dtype=torch.int64)
+        saved = int(self.position.item())
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):                                   # warm-up outside capture
+                self.step_greedy(tokens, boundaries)
+                self.position.fill_(saved)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                tokens.copy_(self.host_tokens, non_blocking=True)
+                boundaries.copy_(self.host_boundaries, non_blocking=True)
+                chosen = self.step_greedy(tokens, boundaries)
+                self.host_next.copy_(chosen, non_blocking=True)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self.position.fill_(saved)
+        self._host_graph, self._host_graph_buffers = graph, (tokens, boundaries, chosen)
+
+    def step_host(self) -> Tensor:
+        """One position through the graph of ``capture_host_io``: reads ``host_tokens`` /
+        ``host_boundaries``, returns ``host_next`` (valid on return: the stream is synchronised)."""
+        self._host_graph.replay()
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.host_next

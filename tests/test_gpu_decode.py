@@ -201,3 +201,27 @@ def test_query_projection_inside_norm_reduce_tracks_separate_launches():
             assert torch.allclose(a[0].float(), b[0].float(), atol=0.25, rtol=0.05), t
     assert agree >= steps - 2          # rounding may flip a rare near-tie
     assert_status_clear()
+
+
+def test_host_transfer_graph_equals_the_plain_greedy_step():
+    """``capture_host_io`` / ``step_host``: ids from pinned host memory in, chosen tokens in pinned
+    host memory out, all inside one graph; same tokens as ``step_greedy`` on device tensors."""
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    model = _small_model(seed=19)
+    B, steps = 3, 12
+    g = torch.Generator().manual_seed(31)
+    tokens = torch.randint(0, 500, (B, steps), generator=g)
+    bounds = torch.randint(0, 16, (B, steps), generator=g)
+    plain = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    hosted = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    hosted.capture_host_io()
+    assert int(hosted.position.item()) == 0
+    for t in range(steps):
+        want = plain.step_greedy(tokens[:, t].cuda(), bounds[:, t].cuda())
+        hosted.host_tokens.copy_(tokens[:, t])
+        hosted.host_boundaries.copy_(bounds[:, t])
+        got = hosted.step_host()
+        assert torch.equal(got, want.cpu()), t
+    assert int(hosted.position.item()) == steps == int(plain.position.item())
+    assert_status_clear()
