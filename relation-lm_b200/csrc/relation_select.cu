@@ -658,7 +658,7 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
 // launches of many rows, where rows in flight per SM set the throughput.  kBf16: queries, key
 // caches and block statistics are all bf16 (the decode configuration); the dtype branches
 // fold away, which matters because a row's time is largely instruction fetch.
-template <int kMinCtas, bool kBf16>
+template <int kMinCtas, bool kBf16, bool kDecode>
 __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t warp_key[2 * kWarps];
@@ -668,18 +668,24 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     RLM_TRACE_DECL;
     RLM_PROBE(0);
     const int row = blockIdx.x;
+    // kDecode: the packed operator in its decode form (a row per sequence, one position for all, no
+    // exclusion list): the other forms' branches fold away
+    const int mode = kDecode ? static_cast<int>(kPacked) : a.mode;
+    const int32_t* row_batch = kDecode ? nullptr : a.row_batch;
+    const int32_t* row_position = kDecode ? nullptr : a.row_position;
+    const int32_t* exclude_list = kDecode ? nullptr : a.exclude_list;
     const int key_dtype = kBf16 ? RLM_BF16 : a.key_dtype, stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype,
               query_dtype = kBf16 ? RLM_BF16 : a.query_dtype;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool do_anchor = a.mode != kPartnerOnly, do_partner = a.mode != kAnchorOnly;
+    const bool do_anchor = mode != kPartnerOnly, do_partner = mode != kAnchorOnly;
     const int buckets4 = 4 * a.buckets;
 
     // Decode form: the caches, statistics and the position were written before the previous
     // kernel of the stream started, so everything up to the bulk-copy requests may run while
     // that kernel (the query projection) is still executing; only the queries wait for it.
     // The per-row form and exclusion lists take indices from arbitrary producers: wait first.
-    const bool early = a.row_position == nullptr && a.row_batch == nullptr && a.exclude_list == nullptr &&
-                       a.mode != kPartnerOnly;
+    const bool early = row_position == nullptr && row_batch == nullptr && exclude_list == nullptr &&
+                       mode != kPartnerOnly;
     if (!early) griddep_sync();
     // threads 32..35 / 36..39 evaluate softplus(gamma) of the anchor / partner heads for everybody
     const bool sp_thread = tid >= 32 && tid < 40 && (tid < 36 ? do_anchor : do_partner);
@@ -689,8 +695,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         if (do_anchor) ba = load_scalar(a.anchor_bias, tid, a.param_dtype);
         if (do_partner) bp_ = load_scalar(a.partner_bias, tid, a.param_dtype);
     }
-    const int b = a.row_batch ? a.row_batch[row] : row;
-    const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
+    const int b = row_batch ? row_batch[row] : row;
+    const int t = row_position ? row_position[row] : static_cast<int>(*a.position);
     if (b < 0 || b >= a.n_seq || t < 0 || t >= a.max_t) {
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
         return;
@@ -749,11 +755,11 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     if (early) griddep_sync();
     // this thread's query element
     float qv = 0.0f;
-    if (a.mode == kPacked) {
+    if (mode == kPacked) {
         if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, query_dtype);
         else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, query_dtype);
         else qv = load_scalar(a.partner_base, row * a.pbase_stride + tid - 2 * kD, query_dtype);
-    } else if (a.mode == kAnchorOnly) {
+    } else if (mode == kAnchorOnly) {
         if (tid < kD) qv = load_scalar(a.anchor_query, row * a.aq_stride + tid, query_dtype);
         else if (tid < 2 * kD) qv = load_scalar(a.anchor_router_query, row * a.arq_stride + tid - kD, query_dtype);
     } else {
@@ -762,16 +768,16 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     }
     // queries[0..255]: packed = aq | arq | partner base (exact 64 | router 64);
     // partner-only = (unused 128) | pq | prq; anchor-only = aq | arq
-    if (a.mode == kPartnerOnly) { if (tid < 2 * kD) queries[2 * kD + tid] = qv; }
-    else if (a.mode == kPacked || tid < 2 * kD) queries[tid] = qv;
+    if (mode == kPartnerOnly) { if (tid < 2 * kD) queries[2 * kD + tid] = qv; }
+    else if (mode == kPacked || tid < 2 * kD) queries[tid] = qv;
     if (tid < buckets4) { bias_a[tid] = ba; bias_p[tid] = bp_; }
     for (int i = tid + kThreads; i < buckets4; i += kThreads) {      // bias tables wider than the CTA
         if (do_anchor) bias_a[i] = load_scalar(a.anchor_bias, i, a.param_dtype);
         if (do_partner) bias_p[i] = load_scalar(a.partner_bias, i, a.param_dtype);
     }
     if (tid < cap4 - cap) cand[cap + tid] = kNegInf;   // padding slots never win a comparison
-    const int n_excl = a.exclude_list ? a.exclude_count : 0;
-    if (tid < n_excl) excl_s[tid] = a.exclude_list[static_cast<size_t>(row) * n_excl + tid];
+    const int n_excl = exclude_list ? a.exclude_count : 0;
+    if (tid < n_excl) excl_s[tid] = exclude_list[static_cast<size_t>(row) * n_excl + tid];
     // softplus of the heads' gammas, evaluated while the bulk copies fly
     if (sp_thread) softplus_s[tid - 32] = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
     const float* sp_a = softplus_s, *sp_p = softplus_s + 4;
@@ -1009,8 +1015,11 @@ int launch(SelectArgs& a, void* stream) {
         return RLM_ERR_SMEM;
     }
     const bool bf16 = a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
-    auto kernel = many_rows ? (bf16 ? relation_select_kernel<4, true> : relation_select_kernel<4, false>)
-                            : (bf16 ? relation_select_kernel<3, true> : relation_select_kernel<3, false>);
+    const bool decode = bf16 && a.mode == kPacked && !a.row_batch && !a.row_position && !a.exclude_list;
+    auto kernel = many_rows ? (decode ? relation_select_kernel<4, true, true>
+                                      : bf16 ? relation_select_kernel<4, true, false> : relation_select_kernel<4, false, false>)
+                            : (decode ? relation_select_kernel<3, true, true>
+                                      : bf16 ? relation_select_kernel<3, true, false> : relation_select_kernel<3, false, false>);
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     launch_kernel(kernel, dim3(a.n_rows), dim3(kThreads), plan.total, stream, a);
