@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     RLM_G_PROBE(6, 0);
     if (!__syncthreads_or(!ready)) {
         const int row = m0 + warp * 32 + lane;
-#pragma unroll
+#pragma unroll 1                 // executed once per CTA: compact code beats unrolling
         for (int c = 0; c < BN; c += 16) {
             uint32_t v[16];
             tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
