@@ -197,6 +197,29 @@ def test_many_row_launch_equals_short_launches_and_oracle(dtype):
     assert_status_clear()
 
 
+def test_decode_form_of_many_sequences_equals_the_rows_form():
+    """600 bf16 sequences in the decode form (one launch: the many-row build of the decode-form
+    kernel) against the per-row form of the same queries in launches of 150 rows."""
+    from relation_lm.kernels.relation_select import relation_select_packed, relation_select_packed_rows
+
+    B, T, NB, L, top, K, t = 600, 128, 8, 32, 2, 8, 101
+    case = {"kind": "select", "seed": 7160, "batch": B, "context": T, "blocks": NB, "local_window": L,
+            "top_blocks": top, "k_out": K, "strict_valid": False, "dtype": "bf16"}
+    xg = to_cuda(cases.make_inputs(case))
+    args = select_args(xg)
+    whole = relation_select_packed(*args, position_tensor(t), L, top, K, False)
+    for r0 in range(0, B, 150):
+        sl = slice(r0, r0 + 150)
+        part_args = list(args)
+        for i in (0, 2, 7):       # anchor query, anchor router query, partner base: one row per query
+            part_args[i] = args[i][sl].contiguous()
+        rows = torch.arange(r0, r0 + 150, dtype=torch.int32, device="cuda")
+        part = relation_select_packed_rows(*part_args, rows, torch.full_like(rows, t), L, top, K, False)
+        for w, q in zip(whole, part):
+            assert torch.equal(w[sl], q), r0
+    assert_status_clear()
+
+
 def test_full_window_selection_is_dense_argmax_and_topk():
     """With the window covering the whole history and no remote blocks the routed selection
     must equal dense argmax / top-k of causal scores (the reference's dense models,
