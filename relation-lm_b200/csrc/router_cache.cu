@@ -43,14 +43,14 @@ struct RouterArgs {
     int token_width[4];
 };
 
-// kBf16: raw keys, caches, statistics and conv weights are all bfloat16 (the decode step), so the
-// dtype branches fold away.
+// kBf16: raw keys, caches and statistics are all bfloat16 (the decode step), so their dtype
+// branches fold away; the three conv weights of a channel keep their run-time dtype.
 template <bool kBf16>
 __device__ __forceinline__ void router_update(const RouterArgs& a, int b, int layer,
                                               unsigned char* smem, uint32_t bar, int t) {
     const int tid = threadIdx.x;
     const int raw_dtype = kBf16 ? RLM_BF16 : a.raw_dtype, cache_dtype = kBf16 ? RLM_BF16 : a.cache_dtype,
-              stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype, weight_dtype = kBf16 ? RLM_BF16 : a.weight_dtype;
+              stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype, weight_dtype = a.weight_dtype;
     const int s = tid / kD, c = tid % kD;
     const int bs = a.block_size;
     const int blk = t / bs, start = blk * bs;
@@ -245,8 +245,7 @@ int validate_and_launch(RouterArgs& a, void* stream, const char* who) {
         set_error("router update: block tile exceeds 227 KB of shared memory");
         return RLM_ERR_SMEM;
     }
-    const bool bf16 = a.raw_dtype == RLM_BF16 && a.cache_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16 &&
-                      a.weight_dtype == RLM_BF16;
+    const bool bf16 = a.raw_dtype == RLM_BF16 && a.cache_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
     auto kernel = bf16 ? router_cache_update_kernel<true> : router_cache_update_kernel<false>;
     if (smem_bytes > 48 * 1024) {
         int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
