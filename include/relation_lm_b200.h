@@ -62,7 +62,8 @@ typedef enum {
  * provided the caller keeps one rule: the key caches, block statistics and the `position` scalar
  * passed to a selector must not be written by the kernel launched immediately before it on the
  * same stream (in a decode step they are written by the cache append, several launches earlier).
- * Returns the previous setting.  The setting is process-wide and read at launch (capture) time.
+ * Returns the previous setting.  The setting belongs to the calling host thread (another thread's
+ * launches are not affected) and is read at launch (capture) time.
  */
 int rlm_set_programmatic_launch(int enabled);
 
@@ -352,6 +353,8 @@ int rlm_sparse_cache_append(
  *   scratch: caller-owned device memory of at least rlm_relation_tail_scratch_bytes() bytes,
  *   ZERO before the first call; the kernel leaves it zero again, so one buffer serves every
  *   call that is ordered on a stream.  Calls that overlap on the GPU need separate buffers.
+ *   A launch that reported RLM_DEV_TIMEOUT through `status` leaves partial sums behind: zero the
+ *   buffer again before the next call.
  *   K must divide 128; d a multiple of 64 up to 1024; H a multiple of 8.
  */
 int64_t rlm_relation_tail_scratch_bytes(int batch, int k_out, int d_model);
@@ -379,8 +382,13 @@ int rlm_relation_tail(const void* relation_hidden, const void* second_weight,
  *     RLM_ERR_SHAPE before any work is enqueued.
  *   - The function allocates nothing and frees nothing (no cudaMalloc, no cudaFree, no library
  *     routine that allocates).  The first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress) and remembers it; make that first call with the device current and
- *     before any stream capture begins.
+ *     (cudaGetSymbolAddress), remembers it and opts the kernel into its shared-memory size; the
+ *     CUDA runtime may also load the kernel and the array onto the device at that moment, which
+ *     is the one time device memory is touched on the caller's behalf.  So make one warm-up call
+ *     per device at start-up, with the device current and before any stream capture begins;
+ *     every later call leaves free device memory unchanged.
+ *   - Sizes, dtypes and alignment are checked before anything is put on the stream: a rejected
+ *     call has enqueued nothing.
  *   - All calls on one device share the one array, and it still holds what the previous call
  *     left; each call clears the part it uses on `stream` before launching.  Two calls that can
  *     run at the same time on one GPU (different streams without an ordering between them)
@@ -420,6 +428,16 @@ int rlm_decode_embed(const int64_t* tokens, const int64_t* boundaries, const voi
  */
 int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token, int64_t* position,
                      int rows, int vocab, int dtype, void* stream);
+
+/*
+ * Self-test of the bounded device-side wait (extension, test support; no counterpart in the
+ * reference project).  Launches one CTA that waits, for at most `cycle_limit` SM cycles
+ * (1 .. 2^24), on an mbarrier nothing will ever complete, then ORs RLM_DEV_TIMEOUT into *status
+ * and returns — the path every kernel of the library takes when one of its bulk copies does not
+ * arrive.  `waited_cycles` (optional device int64) receives the cycles spent waiting.
+ */
+int rlm_selftest_bounded_wait(int32_t* status, int64_t cycle_limit, int64_t* waited_cycles,
+                              void* stream);
 
 #ifdef __cplusplus
 }

@@ -78,6 +78,7 @@ class OracleDecoder:
             hidden = hidden + w["mix"][l] * context
             self.last_selection.append((anchor, partner))
         final = self._round(F.layer_norm(hidden, (cfg.d_model,), w["final_norm_w"], w["final_norm_b"], cfg.norm_eps))
+        self.last_final = final
         token_logits = final @ w["token_embedding"].T
         boundary_logits = final @ w["boundary_w"].T + w["boundary_b"]
         self.position += 1

@@ -15,12 +15,6 @@
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
-#ifdef RLM_TRACE
-__device__ long long g_trace_gemm[64 * 16];
-#define RLM_G_PROBE(i, who) do { if (threadIdx.x == (who) && blockIdx.x + blockIdx.y * gridDim.x < 64) g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + (i)] = clock64(); } while (0)
-#else
-#define RLM_G_PROBE(i, who) do { } while (0)
-#endif
 namespace {
 
 constexpr int kGemmThreads = 128;
@@ -52,7 +46,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
-    RLM_G_PROBE(0, 0);
     constexpr int kStages = stages_for(BN);
     // one or two warps issue MMAs (K-blocks dealt round-robin into accumulators of their own, summed by
     // the epilogue): a single thread issues a tcgen05.mma every ~60 cycles, which bounds short
@@ -93,7 +86,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    RLM_G_PROBE(1, 0);
     // Producer (warp 0): the first round of the ring is requested by one lane per stage at once
     // (the stages are free), later rounds by lane 0 as stages are released.  The weight tiles do
     // not depend on earlier kernels: they are requested before the dependency wait, x after it.
@@ -102,13 +94,12 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
         tma_load_2d(ring_addr + lane * (kABytes + kBBytes) + kABytes, &map_w, (k_first + lane) * kBK, n0, full(lane));
     }
     griddep_sync();
-    RLM_G_PROBE(2, 0);      // barriers and tensor memory are set up; x may come from the previous kernel
+    // barriers and tensor memory are set up; x may come from the previous kernel
 
     if (warp == 0) {
         if (lane < kStages && lane < k_iters)
             tma_load_2d(ring_addr + lane * (kABytes + kBBytes), &map_x, (k_first + lane) * kBK, m0, full(lane));
         __syncwarp();
-        RLM_G_PROBE(3, 0);
         if (lane == 0) {
             for (int it = kStages; it < k_iters; ++it) {
                 const int s = it % kStages;
@@ -125,60 +116,26 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
         // tensor-core issue: four UMMA K-steps of 16 per stage.  The whole warp walks the loop so
         // that addresses and descriptors stay warp-uniform; one lane issues the instructions.
         bool ok = true;
-#ifdef RLM_TRACE
-        long long wait_cycles = 0, issue_cycles = 0, mma_cycles = 0, commit_cycles = 0;
-#endif
         for (int it = me; it < k_iters && ok; it += issuers) {
             const int s = it % kStages;
-#ifdef RLM_TRACE
-            const long long w0 = clock64();
-#endif
             ok = mbar_wait(full(s), (it / kStages) & 1);
             ok = __all_sync(0xffffffffu, ok);
-#ifdef RLM_TRACE
-            const long long w1 = clock64();
-            wait_cycles += w1 - w0;
-#endif
             if (!ok) break;
-            if (it == 0) RLM_G_PROBE(4, 32);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t da = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes));
             const uint64_t db = smem_desc_sw128(ring_addr + s * (kABytes + kBBytes) + kABytes);
             if (lane == 0) {
-#ifdef RLM_TRACE
-                const long long m0c = clock64();
-#endif
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk)      // +32 bytes along K inside the swizzle atom
                     umma_f16(my_acc, da + 2 * kk, db + 2 * kk, a.idesc, (it >= issuers || kk > 0) ? 1u : 0u);
-#ifdef RLM_TRACE
-                const long long m1c = clock64();
-#endif
                 umma_commit(empty(s));                       // stage reusable once these MMAs retire
-#ifdef RLM_TRACE
-                const long long m2c = clock64();
-                mma_cycles += m1c - m0c;
-                commit_cycles += m2c - m1c;
-#endif
             }
             __syncwarp();
-#ifdef RLM_TRACE
-            issue_cycles += clock64() - w1;
-#endif
         }
-#ifdef RLM_TRACE
-        if (tid == 32 && blockIdx.x + blockIdx.y * gridDim.x < 64) {
-            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 9] = wait_cycles;
-            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 10] = issue_cycles;
-            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 11] = mma_cycles;
-            g_trace_gemm[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + 12] = commit_cycles;
-        }
-#endif
         if (lane == 0) {
             if (!ok) failed = 1;
             umma_commit(acc_full);                           // accumulator complete (or abandoned)
         }
-        RLM_G_PROBE(5, 32);
     }
     __syncwarp();
 
@@ -186,7 +143,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     bool ready = mbar_wait(acc_full, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
-    RLM_G_PROBE(6, 0);
     if (!__syncthreads_or(!ready)) {
         const int row = m0 + warp * 32 + lane;
 #pragma unroll 1                 // executed once per CTA: compact code beats unrolling
@@ -235,13 +191,11 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
     } else if (tid == 0 && a.status) {
         atomicOr(a.status, RLM_DEV_TIMEOUT);
     }
-    RLM_G_PROBE(7, 0);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"(tmem_cols) : "memory");
-    RLM_G_PROBE(8, 32);
 }
 
 // ------------------------------------------------------------------ LayerNorm + projection
@@ -709,8 +663,3 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     return launch_gemm<128>(mx, mw, a, stream);
 }
 
-#ifdef RLM_TRACE
-extern "C" int rlm_debug_trace_gemm(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_gemm, sizeof(long long) * 64 * 16));
-}
-#endif

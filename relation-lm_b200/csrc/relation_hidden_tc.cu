@@ -37,16 +37,6 @@
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
-#ifdef RLM_TRACE
-// Phase timestamps for working builds (never compiled into the shipped library).
-__device__ long long g_trace_tc[64 * 32];
-__device__ unsigned long long g_span_tc[1024 * 3];
-__device__ __forceinline__ unsigned long long tc_globaltimer() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ unsigned tc_smid() { unsigned s; asm volatile("mov.u32 %0, %smid;" : "=r"(s)); return s; }
-#define RLM_TC_PROBE(i) do { if (threadIdx.x == 0) { const int blk_ = blockIdx.x + blockIdx.y * gridDim.x; if (blk_ < 64) g_trace_tc[blk_ * 32 + (i)] = clock64(); if (blk_ < 1024 && ((i) == 0 || (i) == 8)) { g_span_tc[blk_ * 3 + ((i) ? 1 : 0)] = tc_globaltimer(); g_span_tc[blk_ * 3 + 2] = tc_smid(); } } } while (0)
-#else
-#define RLM_TC_PROBE(i) do { } while (0)
-#endif
 namespace {
 
 constexpr int kTcThreads = 256;
@@ -151,7 +141,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
     __shared__ int idx_s[2 * kBM];      // [rows_per_tile][K + 1]
     __shared__ int seq_s[kBM];
 
-    RLM_TC_PROBE(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int R = a.rdim, H = a.hdim, K = a.k_out, RPT = a.rows_per_tile;
     const int kblocks = R / kBK, chunks = R / 8;
@@ -203,7 +192,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         }
     }
     __syncthreads();      // also publishes the barrier initialisation
-    RLM_TC_PROBE(1);
 
     // A tile: the partner operand rows go straight to their swizzled places in the A tile as
     // 16-byte asynchronous copies while the anchor chunks they are multiplied with wait in
@@ -247,11 +235,9 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
             }
         }
     }
-    RLM_TC_PROBE(2);
     fence_proxy_async();     // generic-proxy writes of the tile -> visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    RLM_TC_PROBE(3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -272,12 +258,10 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         umma_commit(bar_acc);     // accumulator complete (or abandoned)
     }
     __syncwarp();
-    RLM_TC_PROBE(4);
 
     bool ready = mbar_wait(bar_acc, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
-    RLM_TC_PROBE(5);
     const bool staged = kOut != RLM_F32;
     if (!__syncthreads_or(!ready)) {
     // The operand tiles are consumed: all threads request the expanded-cache segments of the
@@ -301,7 +285,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
         }
         cp_async_wait_all();
         __syncthreads();
-        RLM_TC_PROBE(6);
         // This thread's share: pair row `pr`, hidden columns [h0 + 64 ch, h0 + 64 ch + 64).
         const int pr = 32 * (warp & 3) + lane, ch = warp >> 2;
         const int prb = (pr * a.inv_k16) >> 16;
@@ -355,13 +338,11 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
     } else if (tid == 0 && a.status) {
         atomicOr(a.status, RLM_DEV_TIMEOUT);
     }
-    RLM_TC_PROBE(7);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"(kTcBN) : "memory");
-    RLM_TC_PROBE(8);
 }
 
 // ------------------------------------------------------------------ expanded row of position t
@@ -619,11 +600,3 @@ extern "C" int rlm_expanded_cache_append(void* expanded_cache, const void* opera
                              layers, batch, max_t, relation_dim, hidden_dim, dtype, status, stream);
 }
 
-#ifdef RLM_TRACE
-extern "C" int rlm_debug_span_tc(unsigned long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_span_tc, sizeof(unsigned long long) * 1024 * 3));
-}
-extern "C" int rlm_debug_trace_tc(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_tc, sizeof(long long) * 64 * 32));
-}
-#endif

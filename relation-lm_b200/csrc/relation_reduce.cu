@@ -17,12 +17,6 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
                      const void* first_bias, const int64_t* position, const int32_t* row_batch, void* out,
                      int n_rows, int n_seq, int max_t, int rdim, int hdim, int k_out, int dtype,
                      int out_dtype, int32_t* status, void* stream);
-#ifdef RLM_TRACE
-__device__ long long g_trace_reduce[64 * 32];
-#define RLM_PROBE(i) do { if (threadIdx.x == 0 && blockIdx.x + blockIdx.y * gridDim.x < 64) g_trace_reduce[(blockIdx.x + blockIdx.y * gridDim.x) * 32 + (i)] = clock64(); } while (0)
-#else
-#define RLM_PROBE(i) do { } while (0)
-#endif
 namespace {
 
 
@@ -100,7 +94,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
     __shared__ int idx[kRB][kMaxK + 1];
     __shared__ int seq[kRB];
 
-    RLM_PROBE(0);
     const int h0 = blockIdx.x * kHT;
     const int ws = weight_dtype == RLM_F32 ? 4 : 2;
     const int cs = cache_dtype == RLM_F32 ? 4 : 2;
@@ -143,7 +136,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             return;
         }
     }
-    RLM_PROBE(1);
     const int rq = tid / kGroupThreads, t7 = tid - rq * kGroupThreads;
     const int tx = t7 & 15, ty = t7 >> 4;                // hidden columns {tx, tx+16}; rows {ty + 8 i}
     const int steps = R / 4;                              // float4 steps along the relation dimension
@@ -170,7 +162,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             }
         }
         __syncthreads();
-        RLM_PROBE(2);
         // product matrix: prod[rb*K + k][:] = operand[p_k] * operand[anchor]
         for (int i = tid; i < kRows * segs; i += kHiddenThreads) {
             const int prow = div_segs(i), sgm = i - prow * segs;
@@ -235,7 +226,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             }
         }
         __syncthreads();
-        RLM_PROBE(3);
 
         // partial sums over this group's quarter of the relation dimension
         float acc[NR][2];
@@ -278,7 +268,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
             red2[((rq * kRB + rb) * 2 + half) * kHT + tx + 16] = f1;
         }
         __syncthreads();
-        RLM_PROBE(4);
 
         if (kUpdate && tid < kRB * 2 * (kHT / 2)) {
             // fresh expanded rows -> cache row t (rounded to the cache dtype)
@@ -326,7 +315,6 @@ __global__ void __launch_bounds__(kHiddenThreads) relation_hidden_kernel(const H
                              out_dtype, gelu_erf(v + (ba + bp)));
             }
         }
-        RLM_PROBE(5);
     }
 }
 
@@ -730,7 +718,6 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
     const int slices = a.proj_out_dim / kProjCols;
     const int row = blockIdx.x / slices;
     const int col = static_cast<int>(rank) * kProjCols + (tid >> 3), part = tid & 7;
-    RLM_PROBE(0);
     uint4 w[kPieces];
     {
         const uint4* wrow = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.proj_weight) +
@@ -739,9 +726,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
         for (int j = 0; j < kPieces; ++j)
             if (j < pieces) w[j] = wrow[part + 8 * j];
     }
-    RLM_PROBE(1);
     griddep_sync();
-    RLM_PROBE(2);
     if (rank == 0) {
         norm_reduce_vec_row<kVecChunks, true, kPlain>(a, row, partial, normalized_row);
         __syncthreads();
@@ -751,9 +736,7 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
                 store_cluster_shared16(reinterpret_cast<uint4*>(normalized_row) + tid, static_cast<uint32_t>(r), v);
         }
     }
-    RLM_PROBE(3);
     cluster_sync_all();             // release / acquire: the row is visible in every CTA's shared memory
-    RLM_PROBE(5);
     float acc = 0.0f;
 #pragma unroll
     for (int j = 0; j < kPieces; ++j) {
@@ -773,7 +756,6 @@ __global__ void __launch_bounds__(kNormThreads) relation_norm_reduce_project_ker
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
     if (part == 0)
         store_scalar(a.proj_out, static_cast<int64_t>(row) * a.proj_out_dim + col, next_dtype, acc);
-    RLM_PROBE(6);
 }
 
 }  // namespace
@@ -923,8 +905,3 @@ extern "C" int rlm_relation_norm_reduce_project(
                                    dim, raw_dtype, param_dtype, status, stream);
 }
 
-#ifdef RLM_TRACE
-extern "C" int rlm_debug_trace_reduce(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_reduce, sizeof(long long) * 64 * 32));
-}
-#endif

@@ -16,25 +16,6 @@
 #include "rlm_common.cuh"
 
 namespace rlm {
-#ifdef RLM_TRACE
-// Phase timestamps for working builds (never compiled into the shipped library): kept in shared
-// memory while the CTA runs (a global store in front of a barrier would distort the phase it
-// measures) and copied out by thread 0 at its last probe.
-__device__ long long g_trace[64 * 32];
-#ifndef RLM_TRACE_BASE
-#define RLM_TRACE_BASE 0
-#endif
-__shared__ long long trace_s[32];
-#define RLM_TRACE_DECL
-#define RLM_PROBE_T(i, thread) do { if (threadIdx.x == (thread)) trace_s[(i)] = clock64(); } while (0)
-#define RLM_PROBE(i) do { if (threadIdx.x == 0) { trace_s[(i)] = clock64(); \
-    if ((i) == 21 && blockIdx.x >= RLM_TRACE_BASE && blockIdx.x < RLM_TRACE_BASE + 64) \
-        for (int k_ = 0; k_ < 32; ++k_) g_trace[(blockIdx.x - RLM_TRACE_BASE) * 32 + k_] = trace_s[k_]; } } while (0)
-#else
-#define RLM_TRACE_DECL
-#define RLM_PROBE(i) do { } while (0)
-#define RLM_PROBE_T(i, thread) do { } while (0)
-#endif
 namespace {
 
 constexpr int kThreads = 256;
@@ -174,7 +155,6 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
     const int row_bytes = kD * (key_dtype == RLM_F32 ? 4 : 2);
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
-    RLM_PROBE_T(25, 128);
     for (int base = wi * kRows; base < n_rows; base += kRows * nw) {
         const int r = base + rl;
         int pos;
@@ -191,7 +171,6 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         valid = valid && pos != exclude;
         for (int x = 0; x < n_excl; ++x) valid = valid && pos != excl[x];
         float part = 0.0f;
-        RLM_PROBE_T(26, 128);
         if (bar != 0u) {          // the rows' bulk copies were given the time of the set-up above
             arrived = mbar_wait(bar, 0);
             bar = 0u;
@@ -221,7 +200,6 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
                 part = __fadd_rn(chunk_dot(row, query, c0, key_dtype), chunk_dot(row, query, c0 ^ 1, key_dtype));
             }
         }
-        RLM_PROBE_T(27, 128);
         if (kLpr >= 2) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 1));
         if (kLpr == 4) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, 2));
         const float sc = valid ? __fmul_rn(part, 0.125f) : kNegInf;
@@ -235,7 +213,6 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
             my_pos = pos;
         }
     }
-    RLM_PROBE_T(28, 128);
     if (cand) return;
     warp_argmax_key(my_key, my_pos);
     if (my_pos != 0x7fffffff &&
@@ -243,7 +220,6 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         best_key = my_key;
         best_pos = my_pos;
     }
-    RLM_PROBE_T(29, 128);
 }
 
 // Picks the split that keeps every lane of the group busy in the fewest passes (launches of at
@@ -665,8 +641,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     __shared__ int warp_pos[2 * kWarps];
     __shared__ int excl_s[kMaxExclude];
     __shared__ float softplus_s[8];
-    RLM_TRACE_DECL;
-    RLM_PROBE(0);
     const int row = blockIdx.x;
     // kDecode: the packed operator in its decode form (a row per sequence, one position for all, no
     // exclusion list): the other forms' branches fold away
@@ -699,9 +673,11 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     const int t = row_position ? row_position[row] : static_cast<int>(*a.position);
     if (b < 0 || b >= a.n_seq || t < 0 || t >= a.max_t) {
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
+        // keep the stream's ordering chain intact on this path too: a kernel launched after this
+        // one relies on "my predecessor has waited for its own predecessor"
+        if (early) griddep_sync();
         return;
     }
-    RLM_PROBE(1);
     const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks;
     const int bs_shift = (bs & (bs - 1)) == 0 ? 31 - __clz(bs) : -1;
     const int ks = key_dtype == RLM_F32 ? 4 : 2, ss = stats_dtype == RLM_F32 ? 4 : 2;
@@ -781,9 +757,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     // softplus of the heads' gammas, evaluated while the bulk copies fly
     if (sp_thread) softplus_s[tid - 32] = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
     const float* sp_a = softplus_s, *sp_p = softplus_s + 4;
-    RLM_PROBE(2);
     __syncthreads();
-    RLM_PROBE(3);
 
     // With remote blocks, half of the warps score blocks (eight lanes per block) while the other
     // half scores the local window (a lane per row); without, everybody scores rows.
@@ -798,7 +772,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
-        RLM_PROBE(4);
         uint32_t bk = 0;
         int bp = 0x7fffffff;
         if (warp < block_warps)
@@ -807,11 +780,8 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         else
             score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
                        n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok);
-        RLM_PROBE_T(22, 0);
-        RLM_PROBE_T(23, 128);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
-        RLM_PROBE(6);
         if (a.shared_streams && tid == kThreads - 1) {
             // every warp has read the anchor's statistics and local window: the partner's take
             // their place while the anchor's remote blocks are fetched and scored
@@ -838,23 +808,18 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
                         issue_remote(static_cast<const unsigned char*>(a.anchor_keys), smem + p.remote, sel,
                                      top, bs, key_row, seq_keys, bar_ra);
                 }
-                RLM_PROBE(8);
             }
             __syncthreads();
-            RLM_PROBE(9);
-            RLM_PROBE(10);
             bk = 0;
             bp = 0x7fffffff;
             // each warp works out its rows' positions first and only then waits for the copies
             score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
                        nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok);
-            RLM_PROBE_T(24, 0);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             if (__syncthreads_or(!ok)) {
                 if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
                 return;
             }
-            RLM_PROBE(11);
         }
         // Highest score wins; equal scores go to the lowest position (the reference's
         // left-most local arg-max followed by its "equal and earlier" merge rule).
@@ -872,7 +837,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             a.out_anchor_score[row] = key_float(best_key);
         }
         if (!do_partner) return;
-        RLM_PROBE(12);
         // The anchor's contribution to the partner queries: one 2 x 64 row of the partner-anchor
         // cache, read straight from global memory by the threads that own the elements (one
         // dependent round trip, no staging).  The block-wide barrier below publishes pq / prq.
@@ -881,7 +845,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
                                           (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * kD + tid, key_dtype);
             pq[tid] = __fadd_rn(pq[tid], add);   // pq[64..127] is prq
         }
-        RLM_PROBE(13);
     } else {
         anchor_pos = a.anchor_index_in[row];
     }
@@ -891,7 +854,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
         return;
     }
-    RLM_PROBE(14);
     uint32_t dk = 0;
     int dp = 0x7fffffff;
     if (warp < block_warps)
@@ -901,7 +863,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp);
     __syncthreads();
-    RLM_PROBE(15);
     if (top > 0) {
         if (warp == 0) {
             if (nb <= 128 && top <= 32) {
@@ -915,18 +876,15 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
                                  bs, key_row, seq_keys, bar_rp);
                 }
             }
-            RLM_PROBE(17);
         }
         __syncthreads();
         bool ok = true;
-        RLM_PROBE(19);
         score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
                    cand, L, warp, kWarps, dk, dp, bar_rp, ok);
         if (__syncthreads_or(!ok)) {
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
         }
-        RLM_PROBE(20);
     }
     // Exact top-K of the candidate table: output slot k holds the k-th best candidate (higher
     // score first, equal scores by the earlier slot); results without a finite score report
@@ -941,13 +899,11 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
             else
                 topk_tournament<8>(cand, cap4, K, L, t, bs, bs_shift, sel, a.out_partner + static_cast<size_t>(row) * K,
                                    a.out_partner_score + static_cast<size_t>(row) * K);
-            RLM_PROBE(21);
         }
         return;
     }
     topk_large(cand, cap, K, L, t, bs, sel, a.out_partner + static_cast<size_t>(row) * K,
                a.out_partner_score + static_cast<size_t>(row) * K);
-    RLM_PROBE(21);
 }
 
 int launch(SelectArgs& a, void* stream) {
@@ -1104,8 +1060,3 @@ extern "C" int rlm_partner_topk(
     return rlm::launch(a, stream);
 }
 
-#ifdef RLM_TRACE
-extern "C" int rlm_debug_trace(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace, sizeof(long long) * 64 * 32));
-}
-#endif

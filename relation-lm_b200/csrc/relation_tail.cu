@@ -21,12 +21,6 @@
 #include "rlm_tcgen05.cuh"
 
 namespace rlm {
-#ifdef RLM_TRACE
-__device__ long long g_trace_tail[64];
-#define RLM_TPROBE(i) do { if (threadIdx.x == 0) probe[(i)] = clock64(); } while (0)
-#else
-#define RLM_TPROBE(i) do { } while (0)
-#endif
 namespace {
 
 constexpr int kTailThreads = 256;
@@ -63,11 +57,7 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
     __shared__ int is_last;
-#ifdef RLM_TRACE
-    __shared__ long long probe[16];
-#endif
     griddep_sync();
-    RLM_TPROBE(0);
 
     constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kTailBN * kBK * 2;
     unsigned char* ring = reinterpret_cast<unsigned char*>(
@@ -100,7 +90,6 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    RLM_TPROBE(1);
 
     if (tid == 0) {
         for (int it = 0; it < k_iters; ++it) {
@@ -133,7 +122,6 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
     const bool good = !__syncthreads_or(!ready);
-    RLM_TPROBE(2);
     if (good && warp < 4 && k_iters > 0) {
         // partial tile -> scratch accumulator (vector atomics; rows that do not exist are skipped)
         const int row = m0 + warp * 32 + lane;
@@ -155,11 +143,9 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
     } else if (!good && tid == 0 && a.status) {
         atomicOr(a.status, RLM_DEV_TIMEOUT);
     }
-    RLM_TPROBE(3);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __threadfence();
     __syncthreads();
-    RLM_TPROBE(4);
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"(kTailBN) : "memory");
@@ -171,7 +157,6 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    RLM_TPROBE(5);
 
     // ---- the last CTA of this row tile: bias + LayerNorm + softmax + weighted sum + residual
     const int K = a.k_out, D = a.d;
@@ -193,7 +178,6 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
             bet[i] = *reinterpret_cast<const float4*>(a.norm_b + 4 * c4);
         }
     }
-    RLM_TPROBE(6);
     for (int b = seq_lo + warp; b < seq_hi; b += kTailThreads / 32) {      // one warp per sequence
         float s = lane < K ? a.scores[static_cast<size_t>(b) * K + lane] : kNegInf;
         const bool active = lane < K && lane < k_limit && s > -1.0e30f;
@@ -260,19 +244,12 @@ __global__ void __launch_bounds__(kTailThreads, 1) relation_tail_kernel(
             }
         }
     }
-    RLM_TPROBE(7);
-    RLM_TPROBE(8);
-#ifdef RLM_TRACE
-    __syncthreads();
-    if (tid < 16) g_trace_tail[tid] = probe[tid];
-#endif
     if (tid == 0) a.counters[blockIdx.z] = 0;
 }
 
-// Host-side validation, tiling and launch.
-int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hidden_dtype,
-                         void* stream) {
-    if (a.batch == 0) return RLM_OK;
+// Everything that can be wrong with the sizes, dtypes and alignment of a call, checked before
+// any work is put on the stream (`a.scratch` may still be unset: it is checked when given).
+int validate_relation_tail(const void* hidden, const void* w2, const TailArgs& a, int hidden_dtype) {
     if (a.batch < 0 || a.k_out < 1 || a.k_out > kTailMaxK || kBM % a.k_out != 0 || a.d < 64 ||
         a.d % 64 != 0 || a.d > 128 * kTailMaxVec || a.h < 64 || a.h % 8 != 0) {
         set_error("relation_tail: need K dividing 128 (K <= 32), d a multiple of 64 up to 1024, H a multiple of 8");
@@ -287,6 +264,15 @@ int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hi
         set_error("relation_tail: tensors must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
+    return RLM_OK;
+}
+
+// Host-side validation, tiling and launch.
+int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hidden_dtype,
+                         void* stream) {
+    if (a.batch == 0) return RLM_OK;
+    const int valid = validate_relation_tail(hidden, w2, a, hidden_dtype);
+    if (valid != RLM_OK) return valid;
     a.rows = a.batch * a.k_out;
     const int m_tiles = (a.rows + kBM - 1) / kBM;
     const int n_tiles = a.d / kTailBN;
@@ -399,11 +385,6 @@ extern "C" int rlm_relation_tail(const void* relation_hidden, const void* second
     return launch_relation_tail(relation_hidden, second_weight, a, dtype, stream);
 }
 
-#ifdef RLM_TRACE
-extern "C" int rlm_debug_trace_tail(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, rlm::g_trace_tail, sizeof(long long) * 16));
-}
-#endif
 
 // The fused relation tail for callers that cannot provide scratch memory: identical
 // arithmetic to rlm_relation_tail, with the split-K accumulator in the library's built-in
@@ -428,8 +409,16 @@ extern "C" int rlm_relation_tail_static(const void* relation_hidden, const void*
                   "use rlm_relation_tail with a caller buffer for larger problems");
         return RLM_ERR_SHAPE;
     }
+    TailArgs a{};
+    a.bias2 = second_bias; a.scores = partner_scores; a.norm_w = norm_weight; a.norm_b = norm_bias;
+    a.position = position; a.residual = residual; a.mix = mix; a.context = context;
+    a.status = status; a.eps = norm_eps; a.batch = batch; a.k_out = k_out; a.d = d_model; a.h = hidden_dim;
+    a.w_dtype = dtype;
+    // sizes, dtypes and alignment are settled before anything is put on the stream
+    int rc = validate_relation_tail(relation_hidden, second_weight, a, dtype);
+    if (rc != RLM_OK) return rc;
     void* scratch = nullptr;
-    int rc = static_scratch_address(&scratch);
+    rc = static_scratch_address(&scratch);
     if (rc != RLM_OK) return rc;
     // The array keeps whatever the previous call left.  A completed call leaves zeros, but a call
     // that was cut short would not, so the part this call uses is cleared on the stream first.
@@ -440,12 +429,7 @@ extern "C" int rlm_relation_tail_static(const void* relation_hidden, const void*
         set_error("relation_tail_static: clearing the built-in scratch failed");
         return RLM_ERR_LAUNCH;
     }
-    TailArgs a{};
-    a.bias2 = second_bias; a.scores = partner_scores; a.norm_w = norm_weight; a.norm_b = norm_bias;
-    a.position = position; a.residual = residual; a.mix = mix; a.context = context;
     a.scratch = static_cast<float*>(scratch);
     a.counters = reinterpret_cast<int*>(static_cast<char*>(scratch) + kStaticAccBytes);
-    a.status = status; a.eps = norm_eps; a.batch = batch; a.k_out = k_out; a.d = d_model; a.h = hidden_dim;
-    a.w_dtype = dtype;
     return launch_relation_tail(relation_hidden, second_weight, a, dtype, stream);
 }

@@ -20,8 +20,11 @@ void set_error(const char* message) {
     std::snprintf(g_error, sizeof(g_error), "%s", message ? message : "");
 }
 
-std::atomic<int> g_programmatic{0};
-bool programmatic_launch_enabled() { return g_programmatic.load(std::memory_order_relaxed) != 0; }
+// Per host thread: a decode loop that opts in on its own thread cannot change how another
+// thread's launches (for instance the plain operators, whose callers know nothing of the
+// ordering rule that comes with programmatic launch) are issued.
+thread_local int g_programmatic = 0;
+bool programmatic_launch_enabled() { return g_programmatic != 0; }
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -62,7 +65,9 @@ int allow_large_smem(const void* kernel, int bytes) {
 }  // namespace rlm
 
 extern "C" int rlm_set_programmatic_launch(int enabled) {
-    return rlm::g_programmatic.exchange(enabled ? 1 : 0, std::memory_order_relaxed);
+    const int previous = rlm::g_programmatic;
+    rlm::g_programmatic = enabled ? 1 : 0;
+    return previous;
 }
 extern "C" int rlm_abi_version(void) { return RLM_ABI_VERSION; }
 extern "C" const char* rlm_last_error(void) { return rlm::g_error; }

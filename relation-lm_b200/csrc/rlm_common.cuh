@@ -273,16 +273,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after about 2^31 SM cycles (roughly a second) and reports false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after `limit` SM cycles and reports false.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - start > (1ll << 31)) return false;
+        if (clock64() - start > limit) return false;
     }
+}
+
+// The wait every kernel uses: about 2^31 SM cycles (roughly a second).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    return mbar_wait_limit(bar, parity, 1ll << 31);
 }
 
 // Global -> shared bulk copy; both addresses 16-byte aligned, bytes a multiple of 16.

@@ -62,6 +62,11 @@ class StatefulDecoder:
         self.router_stats = [zeros(L, B, nb, 4, 16) for _ in range(4)]  # mean a, std a, mean p, std p
         self.position = torch.zeros((), device=self.device, dtype=torch.int64)
         self.last_selection: list[tuple[Tensor, Tensor]] = []
+        # When set to a list, the fused step appends one dict of cloned intermediates per layer
+        # (and one for the embedding / append stage), so that a checker can feed every kernel's own
+        # inputs to an independent implementation.  Not for captured graphs.
+        self.trace: list[dict[str, Tensor]] | None = None
+        self.last_final: Tensor | None = None           # final LayerNorm output of the last step
         self._graph = None
         # Low-precision decode batches take the fused path: LayerNorm folded into the tcgen05
         # projections, 16-bit relation hidden states, residual update inside norm-reduce.
@@ -175,6 +180,7 @@ class StatefulDecoder:
             if keep_selection:
                 self.last_selection.append((anchor, partner))
         final = F.layer_norm(hidden, (cfg.d_model,), w["final_norm_w"], w["final_norm_b"], cfg.norm_eps).to(self.dtype)
+        self.last_final = final
         token_logits = F.linear(final, w["token_embedding"])
         boundary_logits = F.linear(final, w["boundary_w"], w["boundary_b"])
         pos.add_(1)
@@ -203,6 +209,11 @@ class StatefulDecoder:
                                   w["partner_weight"], w["first_bias"], pos)
         if keep_selection:
             self.last_selection = []
+        trace = self.trace
+        if trace is not None:
+            trace.append({"stage": "append", "embedded": hidden.clone(), "packed": packed.clone(),
+                          "memory_normalized": self.memory_normalized.clone(),
+                          "normalized": self.normalized.clone()})
         K = cfg.k_max
         for l in range(cfg.layers):
             # layer 0 projects the embedding's normalised rows; later layers find their queries
@@ -214,6 +225,11 @@ class StatefulDecoder:
                 self.partner_anchor_cache[l], self.partner_keys[l], self.router_stats[2][l],
                 self.router_stats[3][l], w["partner_gamma"][l], w["partner_bias"][l], pos,
                 cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+            if trace is not None:
+                entry = {"stage": "layer", "layer": l, "query": q.clone(), "anchor": anchor.clone(),
+                         "partner": partner.clone(), "partner_score": partner_score.clone(),
+                         "hidden_before": hidden.clone()}
+                trace.append(entry)
             if self.stacked_expand:
                 relation_hidden_cached_out(self.relation_hidden, self.expanded_cache[l], self.operand_cache[l],
                                            anchor, partner, w["product_weight"][l])
@@ -240,6 +256,8 @@ class StatefulDecoder:
                     next_w, next_b, cfg.norm_eps, self.normalized)
             else:
                 raw = F.linear(self.relation_hidden, w["w2"][l], w["b2"][l])            # [B, K, d]
+                if trace is not None:
+                    entry["raw"] = raw.clone()
                 if self.fused_query and not last:
                     relation_norm_reduce_residual_norm_project(
                         raw, partner_score, w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,
@@ -249,8 +267,14 @@ class StatefulDecoder:
                     relation_norm_reduce_residual_norm(raw, partner_score, w["relation_norm_w"][l],
                                                        w["relation_norm_b"][l], pos, cfg.norm_eps, hidden,
                                                        w["mix"][l], next_w, next_b, cfg.norm_eps, self.normalized)
+            if trace is not None:
+                entry.update(relation_hidden=self.relation_hidden.clone(), hidden_after=hidden.clone(),
+                             next_normalized=self.normalized.clone())
+                if self.fused_query and not last:
+                    entry["next_query"] = self.query.clone()
             if keep_selection:
                 self.last_selection.append((anchor, partner))
+        self.last_final = self.normalized
         logits = packed_projection(self.normalized, self.head_weight, self.head_bias)
         self.last_logits = logits                        # [B, padded vocab + boundary vocab]
         token_logits = logits[:, :cfg.vocab_size]

@@ -34,6 +34,7 @@ PROTOTYPES = {
     "rlm_relation_tail_static": [_P] * 7 + [_F] + [_P] * 3 + [_I] * 5 + [_P, _P],
     "rlm_decode_embed": [_P] * 6 + [_F, _P] + [_I] * 6 + [_P] * 6 + [_F, _I] + [_P, _P],
     "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
+    "rlm_selftest_bounded_wait": [_P, _L, _P, _P],
 }
 
 

@@ -510,10 +510,17 @@ _TAIL_SCRATCH: dict[tuple[int, int], Tensor] = {}
 
 
 def _tail_scratch(device: torch.device, nbytes: int) -> Tensor:
-    """Zero-initialised per-device scratch of the fused tail; grown on demand, reused after."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    """Zero-initialised scratch of the fused tail, one buffer per (device, stream): launches on
+    different streams may overlap on the GPU and must not share split-K sums.  Grown on demand
+    and reused after; growing inside a stream capture is refused (the buffer would belong to the
+    graph's private pool)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, int(torch.cuda.current_stream(device).cuda_stream))
     buf = _TAIL_SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("relation_tail: call once with these sizes on this stream before capturing it "
+                               "(the scratch buffer has to be allocated outside the capture)")
         buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         _TAIL_SCRATCH[key] = buf
     return buf
@@ -536,8 +543,8 @@ def relation_tail(
     (extension): ``hidden += mix * norm_reduce(relation_hidden @ W2.T + b2, scores)``.
     ``relation_hidden [B, K, H]``, ``second_weight [d, H]`` and ``second_bias [d]`` share
     bfloat16 or float16; ``hidden [B, d]`` and the norm parameters are fp32.  The split-K
-    partial sums meet in a per-device scratch buffer that is allocated once (first call on a
-    device, before any stream capture) and left zero by every launch."""
+    partial sums meet in a scratch buffer kept per device and stream, allocated at the first call
+    on that stream (which must come before any capture of it) and left zero by every launch."""
     device = _abi.require_cuda_contiguous(
         relation_hidden=relation_hidden, second_weight=second_weight, second_bias=second_bias,
         partner_scores=partner_scores, norm_weight=norm_weight, norm_bias=norm_bias,

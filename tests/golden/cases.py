@@ -134,7 +134,25 @@ def multi_anchor_inputs(case) -> dict[str, torch.Tensor]:
     return {"hidden": torch.randn(B, T, d, generator=g), "memory": torch.randn(B, T, d, generator=g)}
 
 
-_BUILDERS = {"select": select_inputs, "router": router_inputs,
+def stack_inputs(case) -> dict[str, torch.Tensor]:
+    """Token and boundary ids of a single-anchor layer stack case.  The model itself is rebuilt
+    from ``case['model_seed']`` by ``RoutedRelationLM`` (its state dict is hashed in the golden)."""
+    g = _gen(case["seed"])
+    B, T = case["batch"], case["context"]
+    return {"tokens": torch.randint(0, case["vocab"], (B, T), generator=g),
+            "boundaries": torch.randint(0, case["boundary_vocab"], (B, T), generator=g)}
+
+
+def stack_config_kwargs(case) -> dict:
+    """Keyword arguments of ``RoutedRelationConfig`` for a stack case: the local window covers the
+    whole history and no remote block is used, so routed selection equals dense selection."""
+    return dict(vocab_size=case["vocab"], boundary_vocab_size=case["boundary_vocab"],
+                d_model=case["d_model"], layers=case["layers"], max_context=case["context"],
+                block_size=case["block_size"], local_window=case["context"], top_blocks=0,
+                k_max=case["k_out"])
+
+
+_BUILDERS = {"select": select_inputs, "stack": stack_inputs, "router": router_inputs,
              "router_sequence": router_sequence_inputs, "reduce": reduce_inputs,
              "norm_reduce": norm_reduce_inputs, "packed": packed_inputs,
              "multi_anchor": multi_anchor_inputs}
@@ -149,7 +167,7 @@ def checksum(inputs) -> str:
     for key in sorted(inputs):
         values = inputs[key]
         for v in (values if isinstance(values, (list, tuple)) else [values]):
-            v = v.contiguous()
+            v = v.contiguous().reshape(-1)
             raw = v.view(torch.uint8) if v.dtype != torch.bool else v.to(torch.uint8)
             h.update(key.encode())
             h.update(raw.numpy().tobytes())
@@ -222,6 +240,14 @@ def all_cases() -> dict[str, dict]:
             "eps": 1.0e-5, "positions": [0, 1, 2, 5, 6, 30, 511], "all_inactive": i == 1}
     c["multi_anchor_dense"] = {"kind": "multi_anchor", "seed": 6000, "batch": 2, "context": 24,
                                "d_model": 48, "anchors": 4, "partners": 4}
+    # single-anchor relation layers against the reference's dense RelationBlock / StackedRelationLayers
+    c["stack_two_layers"] = {"kind": "stack", "seed": 7000, "model_seed": 7001, "batch": 2, "context": 64,
+                             "d_model": 128, "layers": 2, "block_size": 8, "k_out": 8, "vocab": 300,
+                             "boundary_vocab": 16}
+    # the single-layer fp32 configuration: d_model 256, hidden 1024, context 128, block 16, batch 1
+    c["stack_single_layer_d256"] = {"kind": "stack", "seed": 7010, "model_seed": 1001, "batch": 1,
+                                    "context": 128, "d_model": 256, "layers": 1, "block_size": 16,
+                                    "k_out": 8, "vocab": 300, "boundary_vocab": 16}
     c["packed_d576"] = {"kind": "packed", "seed": 5000, "rows": 8, "d_model": 576}
     c["packed_d512"] = {"kind": "packed", "seed": 5001, "rows": 3, "d_model": 512}
     return c

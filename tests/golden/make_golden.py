@@ -251,7 +251,52 @@ def run_multi_anchor(case, x):
             "partner_index": info["partner_index"].to(torch.int32), "partner_active": info["partner_active"]}
 
 
-RUNNERS = {"select": run_select, "router": run_router, "router_sequence": run_router_sequence,
+def _routed_model_module():
+    """This repository's parameter container, loaded by file path: its package shares the name
+    ``relation_lm`` with the reference's, so it cannot be imported the ordinary way here."""
+    import importlib.util
+
+    name = "b200_routed_model"
+    if name in sys.modules:
+        return sys.modules[name]
+    path = HERE.parents[1] / "relation-lm_b200" / "relation_lm" / "inference" / "routed_model.py"
+    spec = importlib.util.spec_from_file_location(name, path)
+    module = importlib.util.module_from_spec(spec)
+    sys.modules[name] = module
+    spec.loader.exec_module(module)
+    return module
+
+
+def run_stack(case, x):
+    """The reference's dense single-anchor layers (models/stacked_relation.py:65-136, 152-182) with
+    the weights of this repository's seeded ``RoutedRelationLM``: embeddings as
+    models/relation_lm.py:130-131, ``memory = LayerNorm(x)``, ``hidden = x``."""
+    from relation_lm.models.stacked_relation import RelationBlockConfig, StackedRelationLayers
+
+    rm = _routed_model_module()
+    cfg = rm.RoutedRelationConfig(**cases.stack_config_kwargs(case))
+    model = rm.RoutedRelationLM(cfg, seed=case["model_seed"]).eval()
+    block_cfg = RelationBlockConfig(d_model=cfg.d_model, gate_dim=cfg.gate_dim, relation_dim=cfg.relation_dim,
+                                    hidden_dim=cfg.hidden_dim, k_max=cfg.k_max,
+                                    mix_logit_init=cfg.mix_logit_init)
+    stack = StackedRelationLayers([block_cfg] * cfg.layers).eval()
+    for mine, theirs in zip(model.blocks, stack.blocks):
+        theirs.load_state_dict({k: v for k, v in mine.state_dict().items() if not k.startswith("router.")})
+    stack.final_norm.load_state_dict(model.final_norm.state_dict())
+    T = case["context"]
+    with torch.no_grad():
+        embedded = (model.token_embedding(x["tokens"]) + model.boundary_embedding(x["boundaries"])) \
+            * model.input_scale + model.position_embedding[:T]
+        memory = model.memory_norm(embedded)
+        output, diagnostics = stack(embedded, memory, return_diagnostics=True)
+    layers = [{"anchor_index": d["anchor_index"].to(torch.int32), "partner_index": d["partner_index"].to(torch.int32),
+               "partner_scores": d["partner_scores"], "partner_weights": d["partner_weights"],
+               "active_partner_mask": d["active_partner_mask"]} for d in diagnostics]
+    return {"model_sha256": cases.checksum({k: v for k, v in model.state_dict().items()}),
+            "layers": layers, "output": output}
+
+
+RUNNERS = {"select": run_select, "stack": run_stack, "router": run_router, "router_sequence": run_router_sequence,
            "reduce": run_reduce, "norm_reduce": run_norm_reduce, "packed": run_packed,
            "multi_anchor": run_multi_anchor}
 
@@ -260,11 +305,16 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", required=True, help="checkout of the reference project")
     parser.add_argument("--out", default=str(HERE / "reference_kernels.pt"))
+    parser.add_argument("--only", default=None,
+                        help="regenerate only the cases whose name starts with this prefix and keep "
+                             "the other entries of the existing file")
     args = parser.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
     _patch_interpreter()
-    golden = {}
+    golden = torch.load(args.out, weights_only=False) if args.only else {}
     for name, case in cases.all_cases().items():
+        if args.only and not name.startswith(args.only):
+            continue
         inputs = cases.make_inputs(case)
         golden[name] = {"case": case, "input_sha256": cases.checksum(inputs),
                         "outputs": RUNNERS[case["kind"]](case, inputs)}

@@ -30,3 +30,16 @@ def assert_scores_equal(got: torch.Tensor, want: torch.Tensor) -> None:
     """Bit-for-bit equality of fp32 scores (infinities included)."""
     assert torch.equal(got.cpu().view(torch.int32), want.view(torch.int32)), \
         (got.cpu() - want).abs().nan_to_num(0).max()
+
+
+def assert_rel_close(got: torch.Tensor, want: torch.Tensor, rel: float = 1.0e-2, what: str = "") -> None:
+    """Relative-to-the-row bound: every element of ``got`` lies within ``rel`` times the largest
+    magnitude of its own row of ``want`` (rows = last dimension).  Unlike ``atol + rtol * |x|``
+    the bound does not loosen for rows of small values."""
+    got = got.detach().float().cpu()
+    want = want.detach().float().cpu()
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    scale = want.abs().amax(-1, keepdim=True)
+    err = (got - want).abs()
+    bound = rel * scale + 1.0e-7
+    assert bool((err <= bound).all()), (what, float((err / (scale + 1.0e-30)).max()))

@@ -225,3 +225,50 @@ def test_host_transfer_graph_equals_the_plain_greedy_step():
         assert torch.equal(got, want.cpu()), t
     assert int(hosted.position.item()) == steps == int(plain.position.item())
     assert_status_clear()
+
+
+@pytest.mark.parametrize("name", ["stack_two_layers", "stack_single_layer_d256"])
+def test_fp32_decode_reproduces_the_dense_reference_stack(golden, name):
+    """The GPU step (fp32) against the reference's dense ``StackedRelationLayers`` outputs stored in
+    the golden file: full-history window, no remote blocks — anchors and finite-score partners
+    identical at every position and layer, the stack's output within 2e-5."""
+    import cases
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+    from test_oracle_stack import compare_with_dense_reference, stack_model
+
+    entry = golden[name]
+    case = entry["case"]
+    x = cases.make_inputs(case)
+    assert cases.checksum(x) == entry["input_sha256"]
+    model = stack_model(case)
+    assert cases.checksum(dict(model.state_dict())) == entry["outputs"]["model_sha256"]
+    decoder = StatefulDecoder(model, case["batch"], "cuda", torch.float32)
+    compare_with_dense_reference(entry, decoder, x["tokens"], x["boundaries"], to_device=lambda v: v.cuda())
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("strict", [False, True])
+def test_single_layer_fp32_configuration_matches_cpu_port_at_every_position(strict):
+    """The single-layer fp32 configuration as a composed layer: d_model 256, hidden 1024, context
+    128, block 16, window 32, 2 remote blocks, K = 8, batch 1 — selections identical and the
+    reduced state (the residual stream after the layer, through the final LayerNorm) within 2e-5
+    of the CPU port at every position."""
+    from oracle.decode_port import OracleDecoder
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    cfg = RoutedRelationConfig(vocab_size=300, boundary_vocab_size=16, d_model=256, layers=1, max_context=128,
+                               block_size=16, local_window=32, top_blocks=2, strict_valid=strict)
+    model = RoutedRelationLM(cfg, seed=1001)
+    gpu = StatefulDecoder(model, 1, "cuda", torch.float32)
+    cpu = OracleDecoder(model, 1, torch.float32)
+    g = torch.Generator().manual_seed(1001)
+    tokens = torch.randint(0, 300, (1, 128), generator=g)
+    bounds = torch.randint(0, 16, (1, 128), generator=g)
+    for t in range(128):
+        gpu.step(tokens[:, t].cuda(), bounds[:, t].cuda(), keep_selection=True)
+        cpu.step(tokens[:, t], bounds[:, t])
+        (ga, gp), (ca, cp) = gpu.last_selection[0], cpu.last_selection[0]
+        assert torch.equal(ga.cpu(), ca) and torch.equal(gp.cpu(), cp), t
+        assert torch.allclose(gpu.last_final.cpu(), cpu.last_final, atol=2e-5, rtol=1e-5), t
+    assert_status_clear()

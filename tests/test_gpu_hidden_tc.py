@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle
-from gpu_util import assert_status_clear, position_tensor
+from gpu_util import assert_rel_close, assert_status_clear, position_tensor
 
 pytestmark = pytest.mark.gpu
 
@@ -40,8 +40,8 @@ def test_update_form_matches_the_oracle(B, K, H, R, dtype):
     got = relation_hidden_cache_update(cache, operand.cuda(), anchor.cuda(), partner.cuda(), wa.cuda(),
                                        wp.cuda(), wm.cuda(), bias.cuda(), position_tensor(t))
     want, want_cache = oracle.relation_hidden(expanded, operand, anchor, partner, wm, wa, wp, bias, position=t)
-    assert torch.allclose(got.cpu(), want, atol=1e-2, rtol=1e-2), (got.cpu() - want).abs().max()
-    assert torch.allclose(cache.float().cpu(), want_cache.float(), atol=1e-2, rtol=1e-2)
+    assert_rel_close(got, want, 1e-2)
+    assert_rel_close(cache, want_cache, 1e-2)
     untouched = torch.ones(T, dtype=torch.bool)
     untouched[t] = False
     assert torch.equal(cache.cpu()[:, untouched], expanded[:, untouched])
@@ -64,7 +64,7 @@ def test_cached_form_and_low_precision_output(out_dtype):
         relation_hidden_cache_update_out(got, expanded.cuda().clone(), operand.cuda(), anchor.cuda(),
                                          partner.cuda(), wa.cuda(), wp.cuda(), wm.cuda(), bias.cuda(),
                                          position_tensor(t))
-    assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), (got.float().cpu() - want).abs().max()
+    assert_rel_close(got, want, 1e-2)
     assert_status_clear()
 
 
@@ -82,7 +82,7 @@ def test_same_results_as_the_small_launch_form():
     parts = [relation_hidden_cached_rows(ex, op, anchor[i:i + 8].cuda(), partner[i:i + 8].cuda(), wm_d,
                                          rows[i:i + 8].cuda()) for i in range(0, B, 8)]
     small = torch.cat(parts)
-    assert torch.allclose(big, small, atol=1e-2, rtol=1e-2), (big - small).abs().max()
+    assert_rel_close(big, small, 1e-2)
     assert_status_clear()
 
 
@@ -108,7 +108,7 @@ def test_stacked_expanded_cache_append(layers, B, H, R, dtype):
         wm = torch.zeros(H, R).to(dtype)
         _, want = oracle.relation_hidden(expanded[l], operand[l], anchor, partner, wm, wa[l], wp[l], bias[l],
                                          position=t)
-        assert torch.allclose(got[l].float(), want.float(), atol=1e-2, rtol=1e-2), (l, (got[l].float() - want.float()).abs().max())
+        assert_rel_close(got[l], want, 1e-2, f"layer {l}")
     untouched = torch.ones(T, dtype=torch.bool)
     untouched[t] = False
     assert torch.equal(got[:, :, untouched], expanded[:, :, untouched])

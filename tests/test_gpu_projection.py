@@ -11,7 +11,7 @@ import torch
 import torch.nn.functional as F
 
 import oracle
-from gpu_util import assert_status_clear, position_tensor
+from gpu_util import assert_rel_close, assert_status_clear, position_tensor
 
 pytestmark = pytest.mark.gpu
 
@@ -28,7 +28,7 @@ def test_packed_projection_matches_oracle(rows, d_in, n_out, dtype):
     w = (torch.randn(n_out, d_in, generator=g) * 0.05).to(dtype)
     got = packed_projection(x.cuda(), w.cuda()).float().cpu()
     want = oracle.linear(x, w)
-    assert torch.allclose(got, want, atol=1e-2, rtol=1e-2), (got - want).abs().max()
+    assert_rel_close(got, want, 1e-2)
     assert_status_clear()
 
 
@@ -47,7 +47,7 @@ def test_strided_rows_and_six_way_split_like_the_reference_test():
     assert parts[4].stride(0) == 512                         # router slices stay views of the packed result
     for part, weight in zip(parts, weights, strict=True):
         want = F.linear(memory.float(), weight.float())
-        assert torch.allclose(part.float(), want, atol=1e-2, rtol=1e-2)
+        assert_rel_close(part, want, 1e-2)
     assert_status_clear()
 
 
@@ -75,7 +75,7 @@ def test_norm_projection_matches_layer_norm_then_linear(rows, d_in, n_out, dtype
     got = norm_projection(wide.cuda()[:, :d_in], gamma.cuda(), beta.cuda(), w.cuda(), 1e-5).float().cpu()
     normalized = F.layer_norm(x, (d_in,), gamma, beta, 1e-5).to(dtype)
     want = oracle.linear(normalized, w)
-    assert torch.allclose(got, want, atol=2e-2, rtol=1e-2), (got - want).abs().max()
+    assert_rel_close(got, want, 1e-2)
     assert_status_clear()
 
 
@@ -97,7 +97,7 @@ def test_fused_norm_projection_entry_point_with_many_rows(rows, d_in, n_out):
             _abi.stream_ptr(x.device)))
     normalized = F.layer_norm(x.cpu(), (d_in,), gamma.cpu(), beta.cpu(), 1e-5).bfloat16()
     want = oracle.linear(normalized, w.cpu())
-    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=1e-2), (out.float().cpu() - want).abs().max()
+    assert_rel_close(out, want, 1e-2)
     assert_status_clear()
 
 
@@ -121,8 +121,8 @@ def test_decode_embed_with_layer_norm_outputs(B, d, dtype):
     got = decode_embed_norm(*args, w1.cuda(), b1.cuda(), n1, w2.cuda(), b2.cuda(), n2, 1e-5)
     assert torch.equal(got, plain)                       # the fp32 rows do not depend on the extra outputs
     x = plain.cpu()
-    assert torch.allclose(n1.float().cpu(), F.layer_norm(x, (d,), w1, b1, 1e-5), atol=2e-2, rtol=1e-2)
-    assert torch.allclose(n2.float().cpu(), F.layer_norm(x, (d,), w2, b2, 1e-5), atol=2e-2, rtol=1e-2)
+    assert_rel_close(n1, F.layer_norm(x, (d,), w1, b1, 1e-5), 1e-2)
+    assert_rel_close(n2, F.layer_norm(x, (d,), w2, b2, 1e-5), 1e-2)
     assert_status_clear()
 
 
@@ -140,7 +140,7 @@ def test_projection_bias_and_greedy_token(dtype):
     bias[vocab:vocab + 64] = torch.randn(64, generator=g)
     got = packed_projection(x.cuda(), w.cuda(), bias.cuda())
     want = (oracle.linear(x, w) + bias).to(dtype)
-    assert torch.allclose(got.float().cpu(), want.float(), atol=2e-2, rtol=1e-2)
+    assert_rel_close(got, want, 1e-2)
     logits = got.clone()
     logits[3, 17] = logits[3, 400] = 60000.0 if dtype == torch.float16 else 1.0e9      # planted tie: lowest index wins
     logits[5, vocab + 3] = 60000.0 if dtype == torch.float16 else 1.0e9                # beyond the vocabulary: ignored

@@ -8,7 +8,7 @@ import torch.nn.functional as F
 
 import cases
 import oracle
-from gpu_util import assert_status_clear, position_tensor, to_cuda
+from gpu_util import assert_rel_close, assert_status_clear, position_tensor, to_cuda
 
 pytestmark = pytest.mark.gpu
 
@@ -22,7 +22,7 @@ def _names(kind):
 def _close(got, want, low):
     got, want = got.float().cpu(), want.float()
     if low:
-        assert torch.allclose(got, want, atol=1e-2, rtol=1e-2), (got - want).abs().max()
+        assert_rel_close(got, want, 1e-2)        # 16-bit operands: 1e-2 of the row's largest magnitude
     else:
         assert torch.allclose(got, want, atol=FP32_ATOL, rtol=1e-5), (got - want).abs().max()
 
@@ -152,14 +152,14 @@ def test_reduce_tail_low_precision_inputs(dtype):
     hidden = relation_hidden_cached(expanded.cuda(), operand.cuda(), anchor_index.cuda(),
                                     partner_index.cuda(), factors.product_weight.cuda())
     want, _ = oracle.relation_hidden(expanded, operand, anchor_index, partner_index, factors.product_weight)
-    assert torch.allclose(hidden.cpu(), want, atol=1e-2, rtol=1e-2)
+    assert_rel_close(hidden, want, 1e-2)
     raw = (torch.randn(B, K, D, generator=g)).to(dtype)
     scores = torch.randn(B, K, generator=g)
     scores[:, -1] = -torch.inf
     gamma, beta = torch.ones(D).to(dtype), torch.zeros(D).to(dtype)
     got = relation_norm_reduce(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(), position_tensor(300), 1e-5)
     want = oracle.relation_norm_reduce(raw, scores, gamma, beta, 300, 1e-5)
-    assert torch.allclose(got.cpu(), want, atol=1e-2, rtol=1e-2)
+    assert_rel_close(got, want, 1e-2)
     assert_status_clear()
 
 
@@ -183,7 +183,7 @@ def test_per_row_forms_match_the_oracle():
                                          wm.cuda(), row_batch.cuda())
     want, _ = oracle.relation_hidden(expanded, operand, anchor, partner, wm, row_batch=row_batch,
                                      row_pos=row_pos)
-    assert torch.allclose(hidden.cpu(), want, atol=1e-2, rtol=1e-2)
+    assert_rel_close(hidden, want, 1e-2)
     raw = torch.randn(N, K, D, generator=g)
     scores = torch.randn(N, K, generator=g)
     scores[::3, -2:] = -torch.inf
@@ -219,7 +219,7 @@ def test_norm_reduce_residual_with_next_layer_norm(B, K, D, dtype):
     want_hidden = hidden + mix * context
     assert torch.allclose(got_hidden.cpu(), want_hidden, atol=FP32_ATOL, rtol=1e-5)
     want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
-    assert torch.allclose(normalized.float().cpu(), want_norm, atol=2e-2, rtol=1e-2)
+    assert_rel_close(normalized, want_norm, 1e-2)
     assert_status_clear()
 
 
@@ -254,7 +254,7 @@ def test_norm_reduce_with_the_next_query_projection(B, K, D, N, dtype):
     assert torch.equal(got_hidden, plain_hidden)
     assert torch.equal(got_norm, plain_norm)
     want = got_norm.double() @ weight.double().T
-    assert torch.allclose(projected.double(), want, atol=2e-2, rtol=1e-2)
+    assert_rel_close(projected, want.float(), 1e-2)
     assert_status_clear()
 
 
@@ -288,5 +288,5 @@ def test_split_k_second_layer_feeds_norm_reduce(splits):
     want_hidden = hidden + mix * oracle.relation_norm_reduce(raw, scores, gamma, beta, t, 1e-5)
     assert torch.allclose(got_hidden.cpu(), want_hidden, atol=2e-3, rtol=1e-3), (got_hidden.cpu() - want_hidden).abs().max()
     want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
-    assert torch.allclose(normalized.float().cpu(), want_norm, atol=2e-2, rtol=1e-2)
+    assert_rel_close(normalized, want_norm, 1e-2)
     assert_status_clear()

@@ -274,3 +274,29 @@ def test_argument_validation():
     relation_select_packed(*args, position_tensor(case["context"] + 3), 16, 1, 4, False)
     assert _abi.read_status() == 2
     assert _abi.read_status() == 0
+
+
+def test_a_bounded_wait_that_expires_reports_timeout_and_leaves_the_context_usable():
+    """The expiry path of the kernels' bulk-copy waits, exercised without faulting anything: a
+    wait of a few thousand cycles on a barrier nobody completes sets RLM_DEV_TIMEOUT in the
+    status word, the kernel returns, and the next launch works."""
+    from relation_lm.kernels import _abi
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    assert _abi.read_status() == 0
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    _abi.check(_abi.LIB.rlm_selftest_bounded_wait(_abi.ptr(_abi.status_tensor(device)), 4000, _abi.ptr(waited),
+                                                  _abi.stream_ptr(device)))
+    assert _abi.read_status() == 1                    # RLM_DEV_TIMEOUT, cleared by the read
+    assert 4000 < int(waited.item()) < 4_000_000
+    with pytest.raises(ValueError):
+        _abi.check(_abi.LIB.rlm_selftest_bounded_wait(_abi.ptr(_abi.status_tensor(device)), 1 << 40, None,
+                                                      _abi.stream_ptr(device)))
+    # the context is intact: an ordinary selection still runs and matches the oracle
+    case = cases.all_cases()["select_c512_compat"]
+    x = cases.make_inputs(case)
+    from relation_lm.kernels.relation_select import relation_select_packed
+    got = relation_select_packed(*select_args(to_cuda(x)), position_tensor(300), 64, 2, 8, False)
+    want = oracle.relation_select(*select_args(x), 300, 64, 2, 8, False)
+    assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[2].cpu(), want[2])
+    assert_status_clear()

@@ -37,6 +37,15 @@ def _inputs(batch, k_out, hdim, dim, seed):
     return hidden_rel, w2, b2, scores.to(dev), gamma, beta, hidden, mix, position
 
 
+def _oracle_expected(x, t):
+    import oracle
+
+    hidden_rel, w2, b2, scores, gamma, beta, hidden, mix, _ = [v.cpu() for v in x]
+    raw = oracle.linear(hidden_rel, w2) + b2.float()
+    context = oracle.relation_norm_reduce(raw, scores, gamma, beta, t, 1e-5)
+    return hidden + mix * context
+
+
 def _call_static(lib, x, residual, status, stream):
     hidden_rel, w2, b2, scores, gamma, beta, _, mix, position = x
     batch, k_out, hdim = hidden_rel.shape
@@ -74,6 +83,19 @@ def test_static_scratch_entry_matches_caller_scratch_entry_twice():
     for x, (mine, theirs) in zip((first, second), outs):
         assert not torch.equal(mine, x[6])                 # the residual was updated
         assert torch.allclose(mine, theirs, atol=ATOL, rtol=RTOL), (mine - theirs).abs().max()
+        # and against the CPU oracle's unfused composition, like tests/test_gpu_tail.py
+        want = _oracle_expected(x, 300)
+        assert torch.allclose(mine.cpu(), want, atol=ATOL, rtol=RTOL), (mine.cpu() - want).abs().max()
+    # after the warm-up calls above, further calls leave the free device memory where it was
+    again = [x[6].clone() for x in (first, second)]
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for x, mine in zip((first, second), again):
+        assert _call_static(lib, x, mine, status, stream) == 0, lib.rlm_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    for mine, (earlier, _) in zip(again, outs):
+        assert torch.allclose(mine, earlier, atol=ATOL, rtol=RTOL)
 
 
 def test_static_scratch_entry_rejects_problems_beyond_its_array():
@@ -85,3 +107,9 @@ def test_static_scratch_entry_rejects_problems_beyond_its_array():
     too_many_rows = _inputs(17, 8, 512, 256, seed=4103)    # 136 rows > 128
     rc = _call_static(lib, too_many_rows, too_many_rows[6].clone(), status, stream)
     assert rc == -2 and b"128 rows" in lib.rlm_last_error()
+    # a shape the kernel cannot tile is refused before anything reaches the stream
+    odd_width = _inputs(4, 8, 512, 96, seed=4104)          # d_model not a multiple of 64
+    untouched = odd_width[6].clone()
+    assert _call_static(lib, odd_width, untouched, status, stream) == -2
+    torch.cuda.synchronize()
+    assert torch.equal(untouched, odd_width[6])
