@@ -118,3 +118,34 @@ def test_helper_functions_follow_the_reference():
              + torch.nn.functional.linear(p, f.partner_weight)
              + torch.nn.functional.linear(a * p, f.product_weight))
     assert torch.allclose(direct, split, atol=1e-5)
+
+
+def test_programmatic_launch_switch_belongs_to_the_calling_thread():
+    """A decode loop that turns programmatic launch on in its own thread must not change how
+    another thread's operators are launched, whatever the interleaving."""
+    import threading
+
+    from relation_lm.kernels import _abi
+
+    assert _abi.set_programmatic_launch(False) is False
+    seen = {}
+    a_on, b_done = threading.Event(), threading.Event()
+
+    def decoder_thread():
+        seen["a_before"] = _abi.set_programmatic_launch(True)
+        a_on.set()
+        b_done.wait(10)
+        seen["a_restore"] = _abi.set_programmatic_launch(False)     # what this thread had set: True
+
+    def other_thread():
+        a_on.wait(10)
+        seen["b_sees"] = _abi.set_programmatic_launch(False)        # untouched by the first thread
+        b_done.set()
+
+    threads = [threading.Thread(target=decoder_thread), threading.Thread(target=other_thread)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(20)
+    assert seen == {"a_before": False, "a_restore": True, "b_sees": False}
+    assert _abi.set_programmatic_launch(False) is False              # and the main thread never saw it
