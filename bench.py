@@ -31,7 +31,12 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
-for _p in (ROOT, ROOT / "relation-lm_b200"):
+REFERENCE_INSTALL = ROOT / "baseline" / "_ref"        # `pip install --target` of the reference project, if present
+# Both this repository's package and the reference's are called `relation_lm` (same module paths,
+# same operator names): a process imports one of them.  The sub-process modes that run the
+# reference's own code put its install first and leave this repository's package off the path.
+_REFERENCE_PROCESS = any(a in ("--op-microbench=reference", "--dense-cpu") for a in sys.argv[1:])
+for _p in ((REFERENCE_INSTALL,) if _REFERENCE_PROCESS else (ROOT, ROOT / "relation-lm_b200")):
     if str(_p) not in sys.path:
         sys.path.insert(0, str(_p))
 
@@ -44,7 +49,8 @@ UNIT = "tokens/s"
 # 12-layer decode shape (ncu capture summarised under profiles/), and its ratio to the algorithmic bytes
 NCU_SELECT_TRAFFIC_ROWS256 = 21_464_576
 NCU_SELECT_TRAFFIC_RATIO = 21_464_576 / 21_325_824
-CPU_SAMPLE_BATCH = 8   # the CPU arm keeps fp32 caches on the host: it decodes at most this many sequences
+# the CPU port keeps fp32 caches on the host (58 MB per sequence at ctx 512 / d 512, 750 MB at ctx 2048 / d 768)
+CPU_MAX_BATCH = {"cfg2": 64, "cfg5": 8}
 
 
 def log(message: str) -> None:
@@ -121,9 +127,11 @@ class ClockSampler:
 # ---------------------------------------------------------------------------- CPU arm
 
 
-def cpu_decode_rate(workload: str, batch: int, steps: int, warmup: int, threads: int):
+def cpu_decode_rate(workload: str, batch: int, steps: int, warmup: int, threads: int, runs: int = 1):
     """The CPU port of the decode step on the host cores, from a synthetic state at the end
-    of the prefix (cache contents do not change the work done)."""
+    of the prefix (cache contents do not change the work done).  `warmup` untimed positions, then
+    `runs` timed runs of `steps` positions each; returns the median run's (tokens/s, seconds),
+    the threads used and every run's rate."""
     import oracle
     from oracle.decode_port import OracleDecoder
 
@@ -143,35 +151,47 @@ def cpu_decode_rate(workload: str, batch: int, steps: int, warmup: int, threads:
         if i % 2 == 1:
             s.abs_()
     dec.position = prefix
-    tokens = zipf_tokens(batch, warmup + steps, cfg.vocab_size, seed)
-    bounds = torch.randint(0, cfg.boundary_vocab_size, (batch, warmup + steps), generator=g)
-    for i in range(warmup):
-        dec.step(tokens[:, i], bounds[:, i])
-    start = time.perf_counter()
-    for i in range(warmup, warmup + steps):
+    total = warmup + runs * steps
+    tokens = zipf_tokens(batch, total, cfg.vocab_size, seed)
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (batch, total), generator=g)
+
+    def advance(i):
         if dec.position >= cfg.max_context:
             dec.position = prefix
         dec.step(tokens[:, i], bounds[:, i])
-    elapsed = time.perf_counter() - start
-    return batch * steps / elapsed, elapsed, threads
+
+    for i in range(warmup):
+        advance(i)
+    elapsed = []
+    for r in range(runs):
+        start = time.perf_counter()
+        for i in range(warmup + r * steps, warmup + (r + 1) * steps):
+            advance(i)
+        elapsed.append(time.perf_counter() - start)
+    median = statistics.median(elapsed)
+    return batch * steps / median, median, threads, [batch * steps / e for e in elapsed]
 
 
 def run_reference(args) -> None:
+    """The reference arm: the CPU implementation of the same decode step on the host cores, all
+    threads, decoding the same number of sequences as the GPU arm's whole job (up to
+    CPU_MAX_BATCH: the CPU port keeps fp32 caches on the host)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     steps = max(1, args.steps)
-    cpu_batch = min(args.batch, CPU_SAMPLE_BATCH)
-    value, elapsed, threads = cpu_decode_rate(args.workload, cpu_batch, steps, args.warmup, 0)
+    world = max(1, args.gpus)
+    cpu_batch = min(args.batch * world, CPU_MAX_BATCH[args.workload])
+    value, elapsed, threads, _ = cpu_decode_rate(args.workload, cpu_batch, steps, args.warmup, 0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": elapsed / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": workload_config(args.workload, args.batch, 1),
+        "config": {**workload_config(args.workload, args.batch, world), "sequences_decoded": cpu_batch},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{steps} decode positions of {cpu_batch} of the {args.batch} sequences from a synthetic "
-                                   "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
+                         "sample": f"{steps} decode positions of {cpu_batch} of the job's {args.batch * world} sequences "
+                                   "from a synthetic end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference ships no CPU-runnable sparse decode (its kernels are Triton-only and its "
                 "decode driver is not public); this arm times the CPU restatement of the same step",
@@ -341,47 +361,227 @@ def kernel_table(dec, graph_iters: int = 20):
     return table
 
 
-def select_rows256(device, graph_iters: int = 10):
-    """The selector at the row count where bandwidth starts to matter: 256 rows of the 12-layer
-    decode shape (ctx 2048, block 64, window 128, 2 remote blocks, K 8, bf16), three cache sets of
-    268 MB so that consecutive launches miss L2, timed inside a captured graph."""
-    from relation_lm.kernels.relation_select import relation_select_packed
-
-    B, T, bs, L, TOP, K = 256, 2048, 64, 128, 2, 8
-    nb, sets = T // bs, 3
-    rn = lambda *shape: torch.randn(*shape, device=device).bfloat16()  # noqa: E731
-    S = [(rn(B, T, 64), rn(B, T, 64), rn(B, T, 128), rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs(),
-          rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs()) for _ in range(sets)]
-    q, g, bias = rn(B, 256), torch.randn(4, device=device), torch.randn(4, 16, device=device)
-    pos = torch.tensor(T - 1, device=device)
-
-    def launch(i):
-        ak, pk, pac, am, as_, pm, ps = S[i]
-        relation_select_packed(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:], pac, pk, pm, ps,
-                               g, bias, pos, L, TOP, K, False)
-
-    launch(0)
+def _time_graph(launchers, device, replays: int = 10) -> float:
+    """Average device time, in microseconds, of the launches in `launchers` captured back to back
+    in one CUDA graph (three warm-up replays, then `replays` timed ones)."""
+    launchers[0]()
     torch.cuda.synchronize()
     stream = torch.cuda.Stream(device)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
         with torch.cuda.graph(graph, stream=stream):
-            for i in range(sets):
-                launch(i)
+            for fn in launchers:
+                fn()
     torch.cuda.synchronize()
     for _ in range(3):
         graph.replay()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(graph_iters):
+    for _ in range(replays):
         graph.replay()
     end.record()
     torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / (graph_iters * sets)
+    return start.elapsed_time(end) * 1e3 / (replays * len(launchers))
+
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def rows256_table(device) -> dict:
+    """The three per-row kernels at the row count where bandwidth starts to matter: 256 rows of the
+    12-layer decode shape (d_model 768, hidden 3072, block 64, window 128, 2 remote blocks, K 8,
+    bf16).  Each kernel rotates through enough independent input sets that the bytes TOUCHED
+    between two uses of a set exceed twice the L2 capacity, so every launch reads from DRAM."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached_out, relation_norm_reduce
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    B, T, bs, L, TOP, K, d, H, R = 256, 2048, 64, 128, 2, 8, 768, 3072, 128
+    nb = T // bs
+    rn = lambda *shape: torch.randn(*shape, device=device).bfloat16()  # noqa: E731
+    pos = torch.tensor(T - 1, device=device)
+    table = {}
+
+    def sets_for(bytes_touched: int) -> int:
+        return max(3, -(-2 * L2_BYTES // bytes_touched) + 1)
+
+    # selector
     cand = L + TOP * bs
-    nbytes = B * (2 * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K)
-    return {"kernel": "relation_select_kernel", "rows": B, "us_per_launch": us, "bytes_per_launch": nbytes,
-            "gb_per_s": nbytes / us / 1e3}
+    select_bytes = B * (2 * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K)
+    n = sets_for(select_bytes)
+    S = [(rn(B, T, 64), rn(B, T, 64), rn(B, T, 128), rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs(),
+          rn(B, nb, 4, 16), rn(B, nb, 4, 16).abs()) for _ in range(n)]
+    q, g, bias = rn(B, 256), torch.randn(4, device=device), torch.randn(4, 16, device=device)
+
+    def select(i):
+        ak, pk, pac, am, as_, pm, ps = S[i]
+        return lambda: relation_select_packed(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:], pac, pk,
+                                              pm, ps, g, bias, pos, L, TOP, K, False)
+
+    us = _time_graph([select(i) for i in range(n)], device)
+    table["relation_select_kernel"] = {"us_per_launch": us, "bytes_per_launch": select_bytes, "input_sets": n}
+    del S
+    # relation hidden, cached form on the tensor cores (a short cache: the gathered rows are random anyway)
+    Th = 128
+    hidden_bytes = B * (2 * (1 + K) * (H + R) + 8 + 4 * K + 2 * K * H) + 2 * H * R
+    n = sets_for(hidden_bytes)
+    S = [(rn(B, Th, 2 * H), rn(B, Th, R), torch.empty(B, K, H, device=device, dtype=torch.bfloat16)) for _ in range(n)]
+    wm = rn(H, R) * 0.02
+    ai = torch.randint(0, Th, (B,), device=device, dtype=torch.int32)
+    pi = torch.randint(0, Th, (B, K), device=device, dtype=torch.int32)
+
+    def hidden(i):
+        ex, op, out = S[i]
+        return lambda: relation_hidden_cached_out(out, ex, op, ai, pi, wm)
+
+    us = _time_graph([hidden(i) for i in range(n)], device)
+    table["relation_hidden_tc_kernel"] = {"us_per_launch": us, "bytes_per_launch": hidden_bytes, "input_sets": n}
+    del S
+    # norm-reduce
+    norm_bytes = B * (2 * K * d + 4 * K + 4 * d) + 2 * 4 * d
+    n = sets_for(norm_bytes)
+    S = [rn(B, K, d) for _ in range(n)]
+    sc, gm, bt = torch.randn(B, K, device=device), torch.ones(d, device=device), torch.zeros(d, device=device)
+    us = _time_graph([(lambda raw=raw: relation_norm_reduce(raw, sc, gm, bt, pos, 1e-5)) for raw in S], device)
+    table["relation_norm_reduce_vec_kernel"] = {"us_per_launch": us, "bytes_per_launch": norm_bytes, "input_sets": n}
+    for row in table.values():
+        row["rows"] = B
+        row["gb_per_s"] = row["bytes_per_launch"] / row["us_per_launch"] / 1e3
+    return table
+
+
+def measure_decode(workload: str, batch: int, args, rank: int, world: int, device, barrier) -> dict:
+    """Prefix + timed decode positions of one workload on this rank's sequences; returns the
+    pieces of the result line (timings already reduced to the maximum over ranks)."""
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+    from relation_lm.kernels import _abi
+
+    model, seed = make_model(workload)
+    cfg = model.config
+    B, T = batch, cfg.max_context
+    prefix = T - 64 if args.prefix is None else args.prefix
+    dec = StatefulDecoder(model, B, device, torch.bfloat16)
+    tokens, bounds = rank_inputs(cfg, seed, B, rank)
+    tokens, bounds = tokens.to(device), bounds.to(device)
+    log(f"{workload}: state allocated, {dec.state_bytes() / 1e9:.1f} GB")
+    launches_before = _abi.launch_count()
+    dec.step_greedy(tokens[:, 0], bounds[:, 0])          # what the captured graph replays
+    kernels_per_step = _abi.launch_count() - launches_before
+    dec.reset()
+    dec.capture()
+    for t in range(prefix):                              # the prefix, through the captured step
+        dec.static_tokens.copy_(tokens[:, t])
+        dec.static_boundaries.copy_(bounds[:, t])
+        dec.replay()
+    torch.cuda.synchronize()
+    log(f"{workload}: prefix of {prefix} positions done")
+    assert int(dec.position.item()) == prefix
+    assert _abi.read_status() == 0, "a kernel reported a device-side error during the prefix"
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    done = [0]
+
+    def run_steps(count: int, timed: bool):
+        events = []
+        for _ in range(count):
+            t = prefix + (done[0] % 64)
+            if t == prefix and done[0]:
+                dec.position.fill_(prefix)
+            dec.static_tokens.copy_(tokens[:, t])
+            dec.static_boundaries.copy_(bounds[:, t])
+            flush.zero_()
+            if timed:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                dec.replay()
+                e.record()
+                events.append((s, e))
+            else:
+                dec.replay()
+            done[0] += 1
+        return events
+
+    run_steps(args.warmup, False)
+    barrier()
+    events = run_steps(args.steps, True)
+    barrier()
+    total_ms = sum(s.elapsed_time(e) for s, e in events)
+
+    # the same steps without the L2 flush (weights stay L2-resident between positions)
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dec.position.fill_(prefix)
+    warm_steps = min(args.steps, 64)
+    s.record()
+    for _ in range(warm_steps):
+        dec.replay()
+    e.record()
+    torch.cuda.synchronize()
+    warm_ms = s.elapsed_time(e) / warm_steps
+
+    # end to end: host token ids in, greedy token out, every step (the decoder's host-transfer
+    # graph: pinned ids -> device at its head, chosen tokens -> pinned memory at its tail, one
+    # launch and one stream synchronisation per position)
+    dec.position.fill_(prefix)                          # the capture's warm-up steps run at the current position
+    dec.capture_host_io()
+    dec.host_tokens.copy_(tokens[:, prefix].cpu())
+    dec.host_boundaries.zero_()
+    torch.cuda.synchronize()
+    e2e_steps = min(args.steps, 64)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        chosen = dec.step_host()
+        dec.host_tokens.copy_(chosen)                   # greedy feedback through the host
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    assert _abi.read_status() == 0, "a kernel reported a device-side error"
+    total_ms, e2e_ms, warm_ms = max_over_ranks([total_ms, e2e_s * 1e3, warm_ms], world, device)
+    result = {
+        "value": job_rate(world, B, args.steps, total_ms), "ms_per_step": total_ms / args.steps,
+        "e2e": {"value": job_rate(world, B, e2e_steps, e2e_ms), "unit": UNIT,
+                "h2d_bytes_per_step": 2 * B * 8, "d2h_bytes_per_step": B * 8, "steps": e2e_steps},
+        "l2_warm": {"ms_per_step": warm_ms, "value": world * B / (warm_ms / 1e3), "unit": UNIT,
+                    "note": "same steps back to back without the L2 flush"},
+        "gpu_launches": kernels_per_step * args.steps, "launches_per_step": kernels_per_step,
+        "parameters": model.parameter_count(), "state_bytes_per_gpu": dec.state_bytes(),
+    }
+    if rank == 0:
+        log(f"{workload}: timed region done, {total_ms / args.steps:.3f} ms/step")
+        result["kernels"] = kernel_table(dec)
+    del dec, flush
+    torch.cuda.empty_cache()
+    return result
+
+
+def roofline_of(table: dict, peak: float, peaks_found: bool) -> dict:
+    """The roofline record of the library kernel with the largest share of a decode step."""
+    dominant = max(table, key=lambda k: table[k]["us_per_step"])
+    dom = table[dominant]
+    lib_us = sum(v["us_per_step"] for v in table.values())
+    return {"kernel": dominant, "bound": "hbm", "achieved": dom["gb_per_s"], "peak": peak,
+            "unit": "GB/s", "frac": dom["gb_per_s"] / peak,
+            "peak_source": "measured" if peaks_found else "fallback",
+            "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO)
+                        if dominant == "relation_select_kernel" else None),
+            "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (21.46 MB per "
+                              "launch for 21.33 MB of algorithmic bytes), scaled by algorithmic bytes",
+            "us_per_launch": dom["us_per_launch"], "bytes_per_launch": dom["bytes_per_launch"],
+            "share_of_library_time": dom["us_per_step"] / lib_us}
+
+
+def run_subprocess_json(mode: str, timeout: int):
+    """Runs `bench.py <mode>` in a child process and parses its one JSON line; a dict with
+    "unavailable" on any failure (the child imports the reference's package, which cannot share a
+    process with this repository's)."""
+    try:
+        done = subprocess.run([sys.executable, str(ROOT / "bench.py"), mode], capture_output=True, text=True,
+                              timeout=timeout)
+        lines = [ln for ln in done.stdout.splitlines() if ln.startswith("{")]
+        if done.returncode != 0 or not lines:
+            return {"unavailable": (done.stderr.strip().splitlines() or ["no output"])[-1][:200]}
+        return json.loads(lines[-1])
+    except (subprocess.TimeoutExpired, OSError, ValueError) as exc:
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
 
 
 def run_ours(args) -> None:
@@ -407,163 +607,191 @@ def run_ours(args) -> None:
             os.dup2(saved_stdout, 1)
             os.close(saved_stdout)
 
-    from relation_lm.inference.stateful_decode import StatefulDecoder
-    from relation_lm.kernels import _abi
-
-    model, seed = make_model(args.workload)
-    cfg = model.config
-    B, T = args.batch, cfg.max_context
-    prefix = T - 64 if args.prefix is None else args.prefix
-    dec = StatefulDecoder(model, B, device, torch.bfloat16)
-    tokens, bounds = rank_inputs(cfg, seed, B, rank)
-    tokens, bounds = tokens.to(device), bounds.to(device)
-
-    log(f"state allocated: {dec.state_bytes() / 1e9:.1f} GB")
-    launches_before = _abi.launch_count()
-    dec.step_greedy(tokens[:, 0], bounds[:, 0])          # what the captured graph replays
-    kernels_per_step = _abi.launch_count() - launches_before
-    dec.reset()
-    dec.capture()
-    # prefix: PREFIX positions through the captured step
-    for t in range(prefix):
-        dec.static_tokens.copy_(tokens[:, t])
-        dec.static_boundaries.copy_(bounds[:, t])
-        dec.replay()
-    torch.cuda.synchronize()
-    log(f"prefix of {prefix} positions done")
-    assert int(dec.position.item()) == prefix
-    assert _abi.read_status() == 0, "a kernel reported a device-side error during the prefix"
-
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
-
-    def run_steps(count: int, timed: bool):
-        events = []
-        for i in range(count):
-            t = prefix + (int(run_steps.done) % 64)
-            if t == prefix and run_steps.done:
-                dec.position.fill_(prefix)
-            dec.static_tokens.copy_(tokens[:, t])
-            dec.static_boundaries.copy_(bounds[:, t])
-            flush.zero_()
-            if timed:
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                dec.replay()
-                e.record()
-                events.append((s, e))
-            else:
-                dec.replay()
-            run_steps.done += 1
-        return events
-
-    run_steps.done = 0
-    run_steps(args.warmup, False)
-
     def barrier():
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
         torch.cuda.synchronize()
 
+    B = args.batch
     sampler = ClockSampler(local) if rank == 0 else None
-    barrier()
-    events = run_steps(args.steps, True)
-    barrier()
-    total_ms = sum(s.elapsed_time(e) for s, e in events)
-
-    # the same steps without the L2 flush (weights stay L2-resident between positions)
-    barrier()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dec.position.fill_(prefix)
-    s.record()
-    for i in range(min(args.steps, 64)):
-        dec.replay()
-    e.record()
-    torch.cuda.synchronize()
-    warm_ms = s.elapsed_time(e) / min(args.steps, 64)
-
-    # end to end: host token ids in, greedy token out, every step
-    # (the decoder's host-transfer graph: pinned ids -> device at its head, chosen tokens -> pinned
-    # memory at its tail, one launch and one stream synchronisation per position)
-    dec.position.fill_(prefix)                          # the capture's warm-up steps run at the current position
-    dec.capture_host_io()
-    dec.host_tokens.copy_(tokens[:, prefix].cpu())
-    dec.host_boundaries.zero_()
-    torch.cuda.synchronize()
-    e2e_steps = min(args.steps, 64)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        chosen = dec.step_host()
-        dec.host_tokens.copy_(chosen)                   # greedy feedback through the host
-    e2e_s = time.perf_counter() - t0
-    barrier()
+    main = measure_decode(args.workload, B, args, rank, world, device, barrier)
     clocks = sampler.stop() if sampler else None
-    assert _abi.read_status() == 0, "a kernel reported a device-side error"
-
-    total_ms, e2e_ms, warm_ms = max_over_ranks([total_ms, e2e_s * 1e3, warm_ms], world, device)
+    # the strong-scaling companion: 256 sequences of the 12-layer configuration split over the ranks
+    sharded = None
+    if args.workload == "cfg2" and not args.no_cfg5 and 256 % world == 0:
+        sharded = measure_decode("cfg5", 256 // world, args, rank, world, device, barrier)
 
     if rank == 0:
-        log(f"timed region done: {total_ms / args.steps:.3f} ms/step")
-        table = kernel_table(dec)
-        rows256 = select_rows256(device)
-        log("kernel table done")
         peaks = {}
         try:
             peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
         except OSError:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
-        dominant = max(table, key=lambda k: table[k]["us_per_step"])
-        dom = table[dominant]
-        lib_us = sum(v["us_per_step"] for v in table.values())
+        rows256 = rows256_table(device)
+        for row in rows256.values():
+            row["frac"] = row["gb_per_s"] / peak
+        rows256["relation_select_kernel"]["traffic"] = NCU_SELECT_TRAFFIC_ROWS256
+        log("kernel tables done")
         threads = os.cpu_count() or 1
-        cpu_steps = 6
-        cpu_batch = min(B, CPU_SAMPLE_BATCH)
+        cpu_batch = min(B, CPU_MAX_BATCH[args.workload])
+        extras = {}
         if world == 1:
-            log(f"cpu baseline: {cpu_steps} positions of {cpu_batch} sequences on {threads} threads")
-            cpu_value, cpu_elapsed, cpu_threads = cpu_decode_rate(args.workload, cpu_batch, cpu_steps, 1, threads)
-            cpu_sample = (f"{cpu_steps} decode positions of {cpu_batch} of the {B} sequences from a synthetic "
-                          "end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)")
+            log(f"cpu baseline: 5 runs of 8 positions of {cpu_batch} sequences on {threads} threads, then on 1")
+            cpu_value, _, cpu_threads, cpu_runs = cpu_decode_rate(args.workload, cpu_batch, 8, 2, threads, runs=5)
+            one_value, _, _, _ = cpu_decode_rate(args.workload, cpu_batch, 2, 1, 1, runs=3)
+            cpu_sample = (f"median of 5 runs of 8 decode positions (2 warm-up positions) of {cpu_batch} of the {B} "
+                          "sequences from a synthetic end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)")
+            cpu_extra = {"runs": cpu_runs, "one_thread": {"value": one_value, "unit": UNIT, "cores": 1,
+                                                          "sample": "median of 3 runs of 2 positions"}}
+            if REFERENCE_INSTALL.exists():
+                cpu_extra["dense_reference"] = run_subprocess_json("--dense-cpu", 300)
+                extras["reference_triton"] = run_subprocess_json("--op-microbench=reference", 420)
+                extras["ours_same_protocol"] = run_subprocess_json("--op-microbench=ours", 240)
+            else:
+                cpu_extra["dense_reference"] = {"unavailable": "the reference install (baseline/_ref) is not present"}
         else:                       # the host cores are busy with the other ranks: measured at N=1 only
-            cpu_value, cpu_threads, cpu_sample = None, 0, "not run with more than one GPU rank"
+            cpu_value, cpu_threads, cpu_sample, cpu_extra = None, 0, "not run with more than one GPU rank", {}
+        roofline = roofline_of(main["kernels"], peak, bool(peaks))
+        roofline["note"] = "batch-8 decode launches move < 1 MB each and are latency-bound"
         line = {
-            "metric": METRIC, "value": job_rate(world, B, args.steps, total_ms), "unit": UNIT,
+            "metric": METRIC, "value": main["value"], "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {**workload_config(args.workload, B, world),
-                       "parameters": model.parameter_count(), "state_bytes_per_gpu": dec.state_bytes()},
-            "e2e": {"value": job_rate(world, B, e2e_steps, e2e_ms), "unit": UNIT,
-                    "h2d_bytes_per_step": 2 * B * 8, "d2h_bytes_per_step": B * 8,
-                    "steps": e2e_steps},
-            "gpu_launches": kernels_per_step * args.steps,
-            "l2_warm": {"ms_per_step": warm_ms, "value": world * B / (warm_ms / 1e3), "unit": UNIT,
-                        "note": "same steps back to back without the L2 flush"},
-            "clocks": clocks,
-            "roofline": {"kernel": dominant, "bound": "hbm", "achieved": dom["gb_per_s"], "peak": peak,
-                         "unit": "GB/s", "frac": dom["gb_per_s"] / peak,
-                         "peak_source": "measured" if peaks else "fallback",
-                         "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO)
-                                     if dominant == "relation_select_kernel" else None),
-                         "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (21.46 MB per "
-                                           "launch for 21.33 MB of algorithmic bytes), scaled by algorithmic bytes",
-                         "us_per_launch": dom["us_per_launch"],
-                         "share_of_library_time": dom["us_per_step"] / lib_us,
-                         "note": "batch-8 decode launches move < 1 MB each and are latency-bound"},
-            "kernels": table,
-            "roofline_rows256": {**rows256, "peak": peak, "frac": rows256["gb_per_s"] / peak,
-                                 "traffic": NCU_SELECT_TRAFFIC_ROWS256,
-                                 "note": "the selector at 256 rows of the 12-layer decode shape, the "
-                                         "smallest launch whose bytes (21 MB) are bandwidth-relevant"},
+                       "parameters": main["parameters"], "state_bytes_per_gpu": main["state_bytes_per_gpu"]},
+            "e2e": main["e2e"], "gpu_launches": main["gpu_launches"], "launches_per_step": main["launches_per_step"],
+            "l2_warm": main["l2_warm"], "clocks": clocks, "roofline": roofline, "kernels": main["kernels"],
+            "roofline_rows256": {**rows256["relation_select_kernel"], "kernel": "relation_select_kernel", "peak": peak,
+                                 "note": "the selector at 256 rows of the 12-layer decode shape, the smallest launch "
+                                         "whose bytes (21 MB) are bandwidth-relevant; input sets rotated so that "
+                                         "every launch misses L2"},
+            "rows256": rows256,
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": cpu_threads, "kind": "port",
-                             "sample": cpu_sample},
+                             "sample": cpu_sample, **cpu_extra},
+            **extras,
         }
+        if sharded is not None:
+            line["cfg5"] = {
+                "workload": workload_config("cfg5", 256 // world, world)["workload"], "scaling": "strong",
+                "global_batch": 256, "batch_per_gpu": 256 // world, "value": sharded["value"], "unit": UNIT,
+                "ms_per_step": sharded["ms_per_step"], "e2e": sharded["e2e"], "l2_warm": sharded["l2_warm"],
+                "launches_per_step": sharded["launches_per_step"],
+                "state_bytes_per_gpu": sharded["state_bytes_per_gpu"],
+                "roofline": roofline_of(sharded["kernels"], peak, bool(peaks)), "kernels": sharded["kernels"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------- reference-side child modes
+
+
+def run_op_microbench(which: str) -> None:
+    """The four reference-shaped operators at the ctx-512 decode shapes (batch 1 and 8, bf16
+    caches), timed with the reference's own microbenchmark protocol (50 warm-up calls, 400 timed
+    calls back to back between two CUDA events: benchmarks/benchmark_relation_select.py:96-107 of
+    the reference project) and, where the operator can be captured, as 20 launches inside a CUDA
+    graph.  Both packages expose the same module paths and signatures, so this one function times
+    whichever `relation_lm` the process imports: the reference's Triton operators JIT-compiled on
+    this GPU, or this repository's CUDA library."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached, relation_norm_reduce
+    from relation_lm.kernels.relation_select import relation_select_packed
+    from relation_lm.kernels.router_cache import router_cache_update
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(17)
+    T, NB, L, TOP, K, d, H, R = 512, 16, 64, 2, 8, 512, 2048, 128
+    bs = T // NB
+    rn = lambda *shape: torch.randn(*shape, device=dev).bfloat16()  # noqa: E731
+
+    def eager_us(fn, warmup=50, repeats=400):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(repeats):
+            fn()
+        end.record()
+        end.synchronize()
+        return start.elapsed_time(end) * 1e3 / repeats
+
+    def graph_us(fn):
+        try:
+            return _time_graph([fn] * 20, dev, replays=20)
+        except Exception as exc:  # noqa: BLE001 - a JIT operator that cannot be captured is reported, not fatal
+            torch.cuda.synchronize()
+            return f"not captured: {type(exc).__name__}"
+
+    out = {"package": which, "protocol": "50 warm-up + 400 timed eager calls; 20 launches per CUDA graph x 20 replays",
+           "shape": "ctx 512, block 32, window 64, 2 remote blocks, K 8, d 512, hidden 2048, bf16"}
+    for batch in (1, 8):
+        pos = torch.tensor(T - 1, device=dev, dtype=torch.long)
+        sel = (rn(batch, 64), rn(batch, T, 64), rn(batch, 64), rn(batch, NB, 4, 16), rn(batch, NB, 4, 16).abs(),
+               torch.randn(4, device=dev), torch.randn(4, 16, device=dev), rn(batch, 128), rn(batch, T, 128),
+               rn(batch, T, 64), rn(batch, NB, 4, 16), rn(batch, NB, 4, 16).abs(), torch.randn(4, device=dev),
+               torch.randn(4, 16, device=dev))
+        packed = rn(batch, 512)
+        caches = [rn(batch, T, 64) for _ in range(4)]
+        stats = [rn(batch, NB, 4, 16) for _ in range(4)]
+        conv = torch.randn(64, 3, device=dev) * 0.1
+        expanded, operand, wm = rn(batch, T, 2 * H), rn(batch, T, R), rn(H, R) * 0.02
+        ai = torch.randint(0, T, (batch,), device=dev, dtype=torch.int32)
+        pi = torch.randint(0, T, (batch, K), device=dev, dtype=torch.int32)
+        raw, scores = rn(batch, K, d), torch.randn(batch, K, device=dev)
+        gm, bt = torch.ones(d, device=dev), torch.zeros(d, device=dev)
+        ops = {
+            "relation_select_packed": lambda: relation_select_packed(*sel, pos, L, TOP, K, False),
+            "router_cache_update": lambda: router_cache_update(packed[:, 384:448], packed[:, 448:512], *caches,
+                                                               *stats, conv, conv, pos, bs),
+            "relation_hidden_cached": lambda: relation_hidden_cached(expanded, operand, ai, pi, wm),
+            "relation_norm_reduce": lambda: relation_norm_reduce(raw, scores, gm, bt, pos, 1e-5),
+        }
+        for name, fn in ops.items():
+            out[f"{name}_b{batch}"] = {"eager_us": eager_us(fn), "graph_us": graph_us(fn)}
+    print(json.dumps(out), flush=True)
+
+
+def run_dense_cpu() -> None:
+    """The reference's own eager CPU code at the ctx-512 decode shape (fp32, batch 8): one dense
+    `RelationBlock.forward` over the whole sequence (models/stacked_relation.py:65-136) and one
+    `DistilledBlockRouter.anchor_scores` (routing/block_router.py:103-110) — its only CPU
+    implementation of the selection / reduction semantics.  2 warm-ups, median of 5 runs."""
+    from relation_lm.models.stacked_relation import RelationBlock, RelationBlockConfig
+    from relation_lm.routing.block_router import BlockRouterConfig, DistilledBlockRouter
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    torch.manual_seed(1002)
+    B, T, d, layers = 8, 512, 512, 6
+    block = RelationBlock(RelationBlockConfig(d_model=d, hidden_dim=4 * d)).eval()
+    router = DistilledBlockRouter(BlockRouterConfig(d_model=d, block_size=32)).eval()
+    hidden, memory = torch.randn(B, T, d), torch.randn(B, T, d)
+
+    def median_ms(fn):
+        with torch.no_grad():
+            for _ in range(2):
+                fn()
+            times = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                fn()
+                times.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(times)
+
+    block_ms = median_ms(lambda: block(hidden, memory))
+    router_ms = median_ms(lambda: router.anchor_scores(hidden, memory))
+    print(json.dumps({
+        "kind": "reference", "cores": threads, "dtype": "f32",
+        "relation_block_forward_ms": block_ms, "router_anchor_scores_ms": router_ms,
+        "value": B * T / (layers * block_ms / 1e3), "unit": UNIT,
+        "sample": f"dense forward of one RelationBlock over {B} x {T} positions (d {d}), median of 5 after 2 warm-ups; "
+                  f"tokens/s = {B} x {T} positions / ({layers} layers x that time)"}), flush=True)
 
 
 def run_kernel_case(args) -> None:
@@ -664,7 +892,19 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=256)
     parser.add_argument("--ctx", type=int, default=2048,
                         help="cache length of --kernel-case runs (shorter caches keep profiler captures small)")
+    parser.add_argument("--no-cfg5", action="store_true",
+                        help="skip the 256-sequence 12-layer companion measurement of the default run")
+    parser.add_argument("--op-microbench", choices=("ours", "reference"), default=None,
+                        help="child mode: time the four reference-shaped operators of one package")
+    parser.add_argument("--dense-cpu", action="store_true",
+                        help="child mode: time the reference's dense eager CPU modules (needs baseline/_ref)")
     args = parser.parse_args()
+    if args.op_microbench:
+        run_op_microbench(args.op_microbench)
+        return
+    if args.dense_cpu:
+        run_dense_cpu()
+        return
     if args.kernel_case:
         run_kernel_case(args)
         return
