@@ -301,6 +301,15 @@ def kernel_table(dec, graph_iters: int = 20):
     def query(l):
         packed_projection(normalized, w["w_query"][l])
 
+    layer_tail = getattr(dec, "layer_tail", False)
+
+    def tail(l):
+        from relation_lm.kernels.relation_reduce import relation_layer_tail
+        relation_layer_tail(dec.expanded_cache[l], dec.operand_cache[l], anchor, partner, scores,
+                            w["product_weight"][l], w["w2"][l], w["b2"][l], w["relation_norm_w"][l],
+                            w["relation_norm_b"][l], pos, cfg.norm_eps, residual, w["mix"][l], w["input_norm_w"][l],
+                            w["input_norm_b"][l], cfg.norm_eps, normalized, w["w_query"][l], projected)
+
     def append(_):
         sparse_cache_append(packed, dec.anchor_keys, dec.partner_keys, dec.operand_cache,
                             dec.partner_anchor_cache, *dec.router_caches, *dec.router_stats,
@@ -317,6 +326,8 @@ def kernel_table(dec, graph_iters: int = 20):
         "packed_projection_kernel(query)": e * (B * d + 256 * d + B * 256),
         "relation_norm_reduce_project_kernel": B * (e * K * d + 4 * K + 4 * d + 8 * d) + 4 * 3 * d
                                                + e * (B * d + 256 * d + B * 256),
+        "relation_layer_tail_kernel": e * (H * R + d * H + 256 * d) + B * (e * (1 + K) * (H + R) + 8 + 8 * K + 8 * d + e * d + e * 256)
+                                      + 4 * 4 * d + e * d,
         "router_cache_update_kernel(all layers)": L * B * (e * 64 * (2 + 4 + 4 + 2 * cfg.block_size + 4) + 2 * 64 * 4 + 2 * e * (256 + R)),
     }
     table = {}
@@ -325,15 +336,19 @@ def kernel_table(dec, graph_iters: int = 20):
     # norm-reduce runs without a projection
     for name, fn, per_graph, per_step in (
             ("relation_select_kernel", select, L, L),
+            ("relation_layer_tail_kernel", tail, L, L),
             ("relation_hidden_kernel", hidden, L, L),
             ("relation_norm_reduce_kernel", reduce, L, 1 if fused_query else L),
             ("relation_norm_reduce_project_kernel", reduce_project, L, L - 1),
-            ("packed_projection_kernel(query)", query, L, 1 if fused_query else L),
+            ("packed_projection_kernel(query)", query, L, 1 if (fused_query or layer_tail) else L),
             ("router_cache_update_kernel(all layers)", append, 1, 1),
             ("expanded_row_update_kernel(all layers)", expand, 1, 1)):
         if name.startswith("expanded_row_update") and not stacked:
             continue
         if name == "relation_norm_reduce_project_kernel" and not fused_query:
+            continue
+        if (name == "relation_layer_tail_kernel") != layer_tail and name in (
+                "relation_layer_tail_kernel", "relation_hidden_kernel", "relation_norm_reduce_kernel"):
             continue
         for l in range(per_graph):
             fn(l)

@@ -366,6 +366,37 @@ int rlm_relation_tail(const void* relation_hidden, const void* second_weight,
                       int hidden_dim, int dtype, int32_t* status, void* stream);
 
 /*
+ * The whole relation tail of a layer in one launch, for decode batches of a few sequences
+ * (extension): relation hidden states (relation_lm::relation_hidden_cached,
+ * src/relation_lm/kernels/relation_reduce.py:149-183), the second relation-MLP layer the reference
+ * leaves to F.linear (benchmarks/benchmark_relation_reduce.py:55-64), relation_lm::relation_norm_reduce
+ * (relation_reduce.py:420-450), `hidden + sigmoid(mix) * context` (models/stacked_relation.py:124),
+ * the LayerNorm of the updated row and, with `query_weight`, the next layer's query-side projection.
+ * A thread-block cluster of H / 128 CTAs serves up to 64 (sequence, partner) pairs; the hidden
+ * states stay on chip (tcgen05 GEMMs chained through shared memory, split-K sums exchanged
+ * through distributed shared memory in a fixed order: results are deterministic).
+ *   expanded_cache [B,T,2H], operand_cache [B,T,R], product_weight [H,R], second_weight [d,H],
+ *   second_bias [d], query_weight [NQ,d] (optional), normalized [B,d] and query [B,NQ] outputs:
+ *   all bfloat16 or all float16 (dtype); anchor_index [B], partner_index [B,K] int32 (gathered
+ *   indices are clamped to the cache); partner_scores [B,K], norm / next-norm parameters [d],
+ *   residual [B,d] (in/out) and mix (one element): float32.
+ * Supported: H = 4 d with d in {128, 256, 512}, R a multiple of 64 up to 256, K <= 64, NQ a
+ * multiple of 16 * (H / 128) with at most 64 outputs per CTA; anything else returns
+ * RLM_ERR_UNSUPPORTED.  rlm_relation_layer_tail_supported() also checks that the device can
+ * host one cluster (1 = supported).  No scratch memory is used.
+ */
+int rlm_relation_layer_tail_supported(int n_seq, int k_out, int relation_dim, int hidden_dim,
+                                      int d_model, int n_query, int dtype);
+int rlm_relation_layer_tail(
+    const void* expanded_cache, const void* operand_cache, const int32_t* anchor_index,
+    const int32_t* partner_index, const float* partner_scores, const void* product_weight,
+    const void* second_weight, const void* second_bias, const float* norm_weight, const float* norm_bias,
+    const int64_t* position, float norm_eps, float* residual, const float* mix,
+    const float* next_norm_weight, const float* next_norm_bias, float next_norm_eps, void* normalized,
+    const void* query_weight, void* query, int n_seq, int k_out, int max_t, int relation_dim,
+    int hidden_dim, int d_model, int n_query, int dtype, int32_t* status, void* stream);
+
+/*
  * rlm_relation_tail for callers that cannot hand over scratch memory.  This entry point has no
  * counterpart in the reference project.
  *

@@ -56,6 +56,55 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
         : "r"(addr));
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(addr));
+}
+
+// ---- device helpers shared by the relation-MLP kernels
+
+// GELU(x) = x * Phi(x) with Phi(x) = 1 - erfc(|x| / sqrt 2) / 2 mirrored for x < 0, erfc from the
+// Abramowitz & Stegun 7.1.26 polynomial (absolute error below 1.5e-7) on the hardware
+// reciprocal and exponential: about a third of the instructions of erff, enough for 16-bit
+// outputs.  The polynomial coefficients carry the factor 1/2.
+__device__ __forceinline__ float gelu_tc(float x) {
+    const float z = fabsf(x) * 0.70710678118654752f;
+    float t, e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * z * -1.4426950408889634f));
+    float p = 0.5307027145f;
+    p = fmaf(p, t, -0.7265760135f);
+    p = fmaf(p, t, 0.7107068705f);
+    p = fmaf(p, t, -0.142248368f);
+    p = fmaf(p, t, 0.127414796f);
+    const float h = p * t * e;                 // erfc(z) / 2
+    return x * (x >= 0.0f ? 1.0f - h : h);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& raw, int dtype, float (&f)[8]) {
+    Raw8 r;
+    r.lo = raw;
+    r.hi = make_uint4(0, 0, 0, 0);
+    convert8(r, dtype, f);
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int dtype) {
+    if (dtype == RLM_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Byte offset of 16-byte chunk c (0 .. R/8) of row r inside a K-major tile stored as
+// K-blocks of `rows` x 128 bytes with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swizzled(int r, int c, uint32_t kblock_bytes) {
+    return static_cast<uint32_t>(c >> 3) * kblock_bytes + static_cast<uint32_t>(r >> 3) * 1024u +
+           static_cast<uint32_t>(r & 7) * 128u + static_cast<uint32_t>(((c & 7) ^ (r & 7)) << 4);
+}
 
 // ---- host side: tensor maps
 

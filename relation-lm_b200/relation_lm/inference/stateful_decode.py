@@ -26,6 +26,7 @@ from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import (decode_embed_norm, greedy_token, layer_norm_cast,
                                                     packed_projection, packed_projection_slices)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
+                                                 relation_layer_tail, relation_layer_tail_supported,
                                                  relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
                                                  relation_norm_reduce_residual_norm,
@@ -41,7 +42,7 @@ class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
                  dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
                  programmatic_launch: bool = True, second_layer_split: bool = False,
-                 fused_query: bool | None = None) -> None:
+                 fused_query: bool | None = None, layer_tail: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -92,7 +93,15 @@ class StatefulDecoder:
         can_fuse_query = (self.fused and not self.fused_tail and self.second_layer_splits == 1
                           and n_query % 32 == 0 and n_query <= 256)
         self.fused_query = can_fuse_query and (B <= 32 if fused_query is None else bool(fused_query))
-        if self.fused_query:
+        # The whole relation tail of a layer (relation hidden, second MLP layer, norm-reduce, residual,
+        # next LayerNorm, next query projection) as ONE cluster launch with the hidden states on chip:
+        # two launches per layer and no library GEMM in the step, for small batches of d <= 512.
+        can_tail = (self.fused and not self.fused_tail and self.second_layer_splits == 1 and self.stacked_expand
+                    and B <= 64 and relation_layer_tail_supported(B, cfg.k_max, R, H, cfg.d_model, n_query, dtype))
+        self.layer_tail = can_tail if layer_tail is None else (bool(layer_tail) and can_tail)
+        if self.layer_tail:
+            self.fused_query = False
+        if self.fused_query or self.layer_tail:
             self.query = zeros(B, n_query)
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
@@ -188,8 +197,9 @@ class StatefulDecoder:
 
     def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True):
         """The same step with the elementwise glue folded into the library's kernels:
-        5 launches per layer (query projection, select, relation hidden, second MLP layer GEMM,
-        norm-reduce + residual + next LayerNorm), or 4 with the fused tail.  Every LayerNorm is
+        2 launches per layer with the single-launch relation tail (select, tail), otherwise up to 5
+        (query projection, select, relation hidden, second MLP layer GEMM, norm-reduce + residual +
+        next LayerNorm).  Every LayerNorm is
         computed by the kernel that produces its input (the embedding, the residual update) and
         handed on as a 16-bit matrix, so the projections are plain tensor-core GEMMs."""
         cfg, w = self.config, self.w
@@ -218,7 +228,8 @@ class StatefulDecoder:
         for l in range(cfg.layers):
             # layer 0 projects the embedding's normalised rows; later layers find their queries
             # written by the previous layer's norm-reduce when that fusion is on
-            q = self.query if (self.fused_query and l > 0) else packed_projection(self.normalized, w["w_query"][l])
+            q = self.query if ((self.fused_query or self.layer_tail) and l > 0) \
+                else packed_projection(self.normalized, w["w_query"][l])
             anchor, _, partner, partner_score = relation_select_packed(
                 q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
                 self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
@@ -230,6 +241,22 @@ class StatefulDecoder:
                          "partner": partner.clone(), "partner_score": partner_score.clone(),
                          "hidden_before": hidden.clone()}
                 trace.append(entry)
+            last = l + 1 == cfg.layers
+            next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]
+            next_b = w["final_norm_b"] if last else w["input_norm_b"][l + 1]
+            if self.layer_tail:
+                relation_layer_tail(self.expanded_cache[l], self.operand_cache[l], anchor, partner, partner_score,
+                                    w["product_weight"][l], w["w2"][l], w["b2"][l], w["relation_norm_w"][l],
+                                    w["relation_norm_b"][l], pos, cfg.norm_eps, hidden, w["mix"][l], next_w, next_b,
+                                    cfg.norm_eps, self.normalized, None if last else w["w_query"][l + 1],
+                                    None if last else self.query)
+                if trace is not None:
+                    entry.update(hidden_after=hidden.clone(), next_normalized=self.normalized.clone())
+                    if not last:
+                        entry["next_query"] = self.query.clone()
+                if keep_selection:
+                    self.last_selection.append((anchor, partner))
+                continue
             if self.stacked_expand:
                 relation_hidden_cached_out(self.relation_hidden, self.expanded_cache[l], self.operand_cache[l],
                                            anchor, partner, w["product_weight"][l])
@@ -238,9 +265,6 @@ class StatefulDecoder:
                     self.relation_hidden, self.expanded_cache[l], self.operand_cache[l], anchor, partner,
                     w["anchor_weight"][l], w["partner_weight"][l], w["product_weight"][l],
                     w["first_bias"][l], pos)
-            last = l + 1 == cfg.layers
-            next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]
-            next_b = w["final_norm_b"] if last else w["input_norm_b"][l + 1]
             if self.fused_tail:
                 relation_tail(self.relation_hidden, w["w2"][l], w["b2"][l], partner_score,
                               w["relation_norm_w"][l], w["relation_norm_b"][l], pos, cfg.norm_eps,

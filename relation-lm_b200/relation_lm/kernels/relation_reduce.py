@@ -651,3 +651,93 @@ def relation_norm_reduce_rows(
 @relation_norm_reduce_rows.register_fake
 def _(raw, partner_scores, norm_weight, norm_bias, row_position, norm_eps):
     return raw.new_empty((raw.size(0), raw.size(2)), dtype=torch.float32)
+
+
+def relation_layer_tail_supported(n_seq: int, k_out: int, relation_dim: int, hidden_dim: int, d_model: int,
+                                  n_query: int, dtype: torch.dtype) -> bool:
+    """Whether ``relation_layer_tail`` serves these sizes on the current device."""
+    if dtype not in (torch.bfloat16, torch.float16):
+        return False
+    return bool(_abi.LIB.rlm_relation_layer_tail_supported(int(n_seq), int(k_out), int(relation_dim),
+                                                           int(hidden_dim), int(d_model), int(n_query),
+                                                           _abi.DTYPE_CODE[dtype]))
+
+
+@torch.library.custom_op("relation_lm::relation_layer_tail", mutates_args=("hidden", "normalized", "query"),
+                         device_types="cuda")
+def relation_layer_tail(
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    partner_scores: Tensor,
+    product_weight: Tensor,
+    second_weight: Tensor,
+    second_bias: Tensor,
+    norm_weight: Tensor,
+    norm_bias: Tensor,
+    position: Tensor,
+    norm_eps: float,
+    hidden: Tensor,
+    mix: Tensor,
+    next_norm_weight: Tensor,
+    next_norm_bias: Tensor,
+    next_norm_eps: float,
+    normalized: Tensor,
+    query_weight: Tensor | None,
+    query: Tensor | None,
+) -> None:
+    """One launch for a layer's whole relation tail (extension; decode batches of a few sequences):
+    ``relation_hidden_cached`` -> second relation-MLP layer -> ``relation_norm_reduce`` ->
+    ``hidden += mix * context`` -> ``normalized = LayerNorm(hidden)`` (16-bit) and, when
+    ``query_weight [NQ, d]`` is given, ``query = normalized @ query_weight.T``.  The relation hidden
+    states never reach device memory and no library GEMM is called.  Caches and weights share
+    bfloat16 or float16; ``hidden [B, d]`` and all LayerNorm parameters are fp32."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, partner_scores=partner_scores, product_weight=product_weight,
+        second_weight=second_weight, second_bias=second_bias, norm_weight=norm_weight, norm_bias=norm_bias,
+        hidden=hidden, mix=mix, next_norm_weight=next_norm_weight, next_norm_bias=next_norm_bias,
+        normalized=normalized, query_weight=query_weight, query=query)
+    _abi.require_position(position, device)
+    batch, max_t, rdim = operand_cache.shape
+    hdim, dim = product_weight.size(0), second_weight.size(0)
+    k_out = partner_index.size(1)
+    if expanded_cache.shape != (batch, max_t, 2 * hdim) or product_weight.shape != (hdim, rdim) \
+            or second_weight.shape != (dim, hdim) or second_bias.numel() != dim \
+            or anchor_index.shape != (batch,) or partner_index.shape != (batch, k_out) \
+            or partner_scores.shape != (batch, k_out) or hidden.shape != (batch, dim) \
+            or normalized.shape != (batch, dim):
+        raise ValueError("relation_layer_tail: inconsistent shapes")
+    if anchor_index.dtype != torch.int32 or partner_index.dtype != torch.int32:
+        raise ValueError("index tensors must be int32")
+    for name, t in (("partner_scores", partner_scores), ("hidden", hidden), ("mix", mix),
+                    ("norm_weight", norm_weight), ("norm_bias", norm_bias),
+                    ("next_norm_weight", next_norm_weight), ("next_norm_bias", next_norm_bias)):
+        if t.dtype != torch.float32:
+            raise ValueError(f"{name} must be float32")
+    n_query = 0
+    if query_weight is not None:
+        if query is None or query_weight.dim() != 2 or query_weight.size(1) != dim \
+                or query.shape != (batch, query_weight.size(0)):
+            raise ValueError("query_weight [NQ, d] needs an output query [B, NQ]")
+        n_query = query_weight.size(0)
+    sixteen = [expanded_cache, operand_cache, product_weight, second_weight, second_bias, normalized]
+    if query_weight is not None:
+        sixteen += [query_weight, query]
+    dtype = _abi.same_dtype("16-bit operand", *sixteen)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_layer_tail(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index), _abi.ptr(partner_index),
+            _abi.ptr(partner_scores), _abi.ptr(product_weight), _abi.ptr(second_weight), _abi.ptr(second_bias),
+            _abi.ptr(norm_weight), _abi.ptr(norm_bias), _abi.ptr(position), float(norm_eps), _abi.ptr(hidden),
+            _abi.ptr(mix), _abi.ptr(next_norm_weight), _abi.ptr(next_norm_bias), float(next_norm_eps),
+            _abi.ptr(normalized), _abi.ptr(query_weight), _abi.ptr(query), batch, k_out, max_t, rdim, hdim,
+            dim, n_query, dtype, _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_layer_tail.register_fake
+def _(expanded_cache, operand_cache, anchor_index, partner_index, partner_scores, product_weight,
+      second_weight, second_bias, norm_weight, norm_bias, position, norm_eps, hidden, mix,
+      next_norm_weight, next_norm_bias, next_norm_eps, normalized, query_weight, query):
+    return None
