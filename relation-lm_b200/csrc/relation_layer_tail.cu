@@ -138,9 +138,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) relation_layer_tail_kernel(
     __shared__ __align__(8) unsigned long long bars[4];          // W_m, W_2, product GEMM done, second GEMM done
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
-    __shared__ int idx_s[kLtMaxPairs + kLtMaxSeq];               // partner rows, then anchor rows (clamped)
     __shared__ int pair_seq_s[kLtMaxPairs];
-    __shared__ float score_s[kLtMaxPairs];
     __shared__ float weight_s[kLtMaxPairs];
     __shared__ __align__(8) float2 stats_out[kLtMaxPairs];       // this CTA's (mean, M2) per pair
     __shared__ __align__(8) float2 ln_s[kLtMaxPairs];            // (mean, rstd) per pair over the full width
@@ -196,76 +194,77 @@ __global__ void __launch_bounds__(kLtThreads, 1) relation_layer_tail_kernel(
     }
     griddep_sync();
 
-    // ---- indices and scores of this cluster's sequences
+    // ---- gathers.  Four threads share a row to gather: they read its index themselves (one
+    // broadcast load) and issue their quarter of its copies at once, so no shared-memory round
+    // trip lies between the selector's indices and the first gather.  Partner operand rows go
+    // straight into the swizzled product tile; copy group 0 = operand rows (needed by the
+    // product GEMM), group 1 = this CTA's 128 columns of the two expanded-cache terms (needed by
+    // its epilogue).
+    const size_t op_row = static_cast<size_t>(R) * 2, ex_row = static_cast<size_t>(H) * 4;
+    const int entry = tid >> 2, quarter = tid & 3;
+    int my_pair_row = 0, my_anchor_row = 0;
+    if (entry < pairs) {
+        const int bl = entry / K;
+        const int p = a.partner_index[static_cast<size_t>(s0) * K + entry];
+        my_pair_row = min(max(p, 0), a.max_t - 1);            // empty slots carry a sentinel that may be negative
+        if (quarter == 0) pair_seq_s[entry] = bl;
+        const char* src = static_cast<const char*>(a.operand_cache) +
+                          (static_cast<size_t>(s0 + bl) * a.max_t + my_pair_row) * op_row;
+        for (int c = quarter; c < chunks; c += 4)
+            cp_async16(smem_u32(p_tile) + swizzled(entry, c, p_kblock), src + 16 * c);
+    } else if (entry < pairs_pad) {
+        for (int c = quarter; c < chunks; c += 4)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};"
+                         ::"r"(smem_u32(p_tile) + swizzled(entry, c, p_kblock)), "r"(0) : "memory");
+    }
+    if (entry < nseq) {
+        const int an = a.anchor_index[s0 + entry];
+        my_anchor_row = min(max(an, 0), a.max_t - 1);
+        const char* src = static_cast<const char*>(a.operand_cache) +
+                          (static_cast<size_t>(s0 + entry) * a.max_t + my_anchor_row) * op_row;
+        for (int c = quarter; c < chunks; c += 4)
+            cp_async16(smem_u32(op_a) + static_cast<uint32_t>(entry * R * 2 + 16 * c), src + 16 * c);
+    }
+    cp_async_commit();
+    if (entry < pairs) {
+        const char* src = static_cast<const char*>(a.expanded_cache) +
+                          (static_cast<size_t>(s0 + entry / K) * a.max_t + my_pair_row) * ex_row +
+                          static_cast<size_t>(H + h0) * 2;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            cp_async16(smem_u32(term_p) + entry * kLtTermStride + 16 * (4 * quarter + i), src + 16 * (4 * quarter + i));
+    }
+    if (entry < nseq) {
+        const char* src = static_cast<const char*>(a.expanded_cache) +
+                          (static_cast<size_t>(s0 + entry) * a.max_t + my_anchor_row) * ex_row +
+                          static_cast<size_t>(h0) * 2;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            cp_async16(smem_u32(term_a) + entry * kLtTermStride + 16 * (4 * quarter + i), src + 16 * (4 * quarter + i));
+    }
+    cp_async_commit();
+    // softmax weights over the active partner slots of every sequence (needed much later): a few
+    // threads of the last warp read the scores themselves while the gathers are in flight
     const int t = static_cast<int>(*a.position);
     const bool bad_position = t < 0 || t >= a.max_t;          // the same in every CTA of the grid
-    if (tid < pairs) {
-        const int bl = tid / K;
-        pair_seq_s[tid] = bl;
-        int p = a.partner_index[static_cast<size_t>(s0) * K + tid];
-        idx_s[tid] = min(max(p, 0), a.max_t - 1);             // empty slots carry a sentinel that may be negative
-        score_s[tid] = a.partner_scores[static_cast<size_t>(s0) * K + tid];
-    } else if (tid >= kLtMaxPairs && tid < kLtMaxPairs + nseq) {
-        int an = a.anchor_index[s0 + tid - kLtMaxPairs];
-        idx_s[tid] = min(max(an, 0), a.max_t - 1);
-    }
-    __syncthreads();
-    // softmax weights over the active partner slots of every sequence (needed much later; computed
-    // by a few threads of the last warp while the gathers are in flight)
     if (tid >= kLtThreads - kLtMaxSeq && tid - (kLtThreads - kLtMaxSeq) < nseq) {
         const int b = tid - (kLtThreads - kLtMaxSeq);
+        const float* sc = a.partner_scores + static_cast<size_t>(s0 + b) * K;
         int k_limit = 32 - __clz(max(t, 0) + 1);               // ceil(log2(t + 2))
         k_limit = min(max(k_limit, 1), K);
         float mx = -1.0e4f;
-        for (int k = 0; k < K; ++k) {
-            const float sc = score_s[b * K + k];
-            if (k < k_limit && sc > -1.0e30f) mx = fmaxf(mx, sc);
-        }
+        for (int k = 0; k < K; ++k)
+            if (k < k_limit && sc[k] > -1.0e30f) mx = fmaxf(mx, sc[k]);
         float den = 0.0f;
         for (int k = 0; k < K; ++k) {
-            const float sc = score_s[b * K + k];
-            const float e = (k < k_limit && sc > -1.0e30f) ? expf(sc - mx) : 0.0f;
+            const float e = (k < k_limit && sc[k] > -1.0e30f) ? expf(sc[k] - mx) : 0.0f;
             weight_s[b * K + k] = e;
             den += e;
         }
         den = 1.0f / fmaxf(den, 1.0e-9f);
         for (int k = 0; k < K; ++k) weight_s[b * K + k] *= den;
     }
-
-    // ---- gathers: partner operand rows straight into the swizzled product tile, anchor operand
-    // rows, and this CTA's 128 columns of the two expanded-cache terms
-    const size_t op_row = static_cast<size_t>(R) * 2, ex_row = static_cast<size_t>(H) * 4;
-    for (int i = tid; i < pairs_pad * chunks; i += kLtThreads) {
-        const int j = i / chunks, c = i - j * chunks;
-        const uint32_t dst = smem_u32(p_tile) + swizzled(j, c, p_kblock);
-        if (j < pairs)
-            cp_async16(dst, static_cast<const char*>(a.operand_cache) +
-                                (static_cast<size_t>(s0 + pair_seq_s[j]) * a.max_t + idx_s[j]) * op_row + 16 * c);
-        else
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
-    }
-    for (int i = tid; i < nseq * chunks; i += kLtThreads) {
-        const int b = i / chunks, c = i - b * chunks;
-        cp_async16(smem_u32(op_a) + static_cast<uint32_t>(b * R * 2 + 16 * c),
-                   static_cast<const char*>(a.operand_cache) +
-                       (static_cast<size_t>(s0 + b) * a.max_t + idx_s[kLtMaxPairs + b]) * op_row + 16 * c);
-    }
-    for (int i = tid; i < pairs * 16; i += kLtThreads) {
-        const int j = i >> 4, c = i & 15;
-        cp_async16(smem_u32(term_p) + j * kLtTermStride + 16 * c,
-                   static_cast<const char*>(a.expanded_cache) +
-                       (static_cast<size_t>(s0 + pair_seq_s[j]) * a.max_t + idx_s[j]) * ex_row +
-                       static_cast<size_t>(H + h0) * 2 + 16 * c);
-    }
-    for (int i = tid; i < nseq * 16; i += kLtThreads) {
-        const int b = i >> 4, c = i & 15;
-        cp_async16(smem_u32(term_a) + b * kLtTermStride + 16 * c,
-                   static_cast<const char*>(a.expanded_cache) +
-                       (static_cast<size_t>(s0 + b) * a.max_t + idx_s[kLtMaxPairs + b]) * ex_row +
-                       static_cast<size_t>(h0) * 2 + 16 * c);
-    }
-    cp_async_commit();
-    cp_async_wait_all();
+    cp_async_wait_group1();                                    // the operand rows have arrived
     __syncthreads();
     // products o[a] * o[p], in fp32, rounded to the operand dtype, in place
     for (int i = tid; i < pairs * chunks; i += kLtThreads) {
@@ -308,22 +307,12 @@ __global__ void __launch_bounds__(kLtThreads, 1) relation_layer_tail_kernel(
     if (!mbar_wait(bar_d1, 0)) failed = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // the W_m slice is consumed: its place takes this CTA's rows of the query-projection weight
-    // (rows padded by one 16-byte chunk per cooperating thread: conflict-free reads below)
     const int nq_own = a.query_weight ? a.n_query / C : 0;
     int tpo = 16;                                              // threads per projection output: 2 .. 16
     while (tpo > 2 && (nseq * nq_own * tpo > kLtThreads || (D / 8) / tpo < 2)) tpo >>= 1;
     const uint32_t wq_stride = static_cast<uint32_t>(D) * 2u + 16u * static_cast<uint32_t>(tpo);
-    if (nq_own > 0) {
-        const int row_chunks = D / 8;
-        for (int i = tid; i < nq_own * row_chunks; i += kLtThreads) {
-            const int j = i / row_chunks, c = i - j * row_chunks;
-            cp_async16(smem_u32(wm_tile) + j * wq_stride + 16 * c,
-                       static_cast<const char*>(a.query_weight) +
-                           (static_cast<size_t>(rank) * nq_own + j) * D * 2 + 16 * c);
-        }
-        cp_async_commit();
-    }
+    cp_async_wait_all();                                       // the expanded-cache terms have arrived
+    __syncthreads();
 
     // ---- epilogue of the product GEMM: + expanded-cache terms, GELU, hidden slice as the K-major
     // B tile of the second GEMM (row = pair, K = this CTA's hidden columns).  Warps 0-3 take the
@@ -383,6 +372,19 @@ __global__ void __launch_bounds__(kLtThreads, 1) relation_layer_tail_kernel(
         umma_commit(bar_d2);
     }
     __syncwarp();
+    // the W_m slice was consumed by the first GEMM: while the second one runs, its place takes this
+    // CTA's rows of the query-projection weight (rows padded by one 16-byte chunk per cooperating
+    // thread: conflict-free reads in the projection below)
+    if (nq_own > 0) {
+        const int w_chunks = D / 8;
+        for (int i = tid; i < nq_own * w_chunks; i += kLtThreads) {
+            const int j = i / w_chunks, c = i - j * w_chunks;
+            cp_async16(smem_u32(wm_tile) + j * wq_stride + 16 * c,
+                       static_cast<const char*>(a.query_weight) +
+                           (static_cast<size_t>(rank) * nq_own + j) * D * 2 + 16 * c);
+        }
+        cp_async_commit();
+    }
     if (!mbar_wait(bar_d2, 0)) failed = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
