@@ -703,6 +703,196 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------- whole-sequence (prefill) workload
+
+
+def run_prefill(args) -> None:
+    """`--workload cfg3`: relation_select + relation_reduce over whole sequences — batch 8, context
+    4096, d_model 512, block 64, window 128, 4 remote blocks, K 8, bf16, hidden states N(0, 1) with
+    5 % of the positions scaled by 4 (seeded).  One step = one pass of the routed layer over all
+    `batch x 4096` query rows (LayerNorm, query projection, per-row selection, relation hidden,
+    second MLP layer, norm-reduce, residual); the sequences' caches and block statistics are
+    built once before the timed region (their build time is reported).  Sequences are sharded
+    over the ranks."""
+    from relation_lm.inference.prefill import RoutedPrefillLayer
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+    from relation_lm.kernels import _abi
+    from relation_lm.kernels.packed_projection import packed_projection
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows_out, relation_norm_reduce_rows
+    from relation_lm.kernels.relation_select import relation_select_packed_rows
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    T, d = 4096, 512
+    cfg = RoutedRelationConfig(vocab_size=64, boundary_vocab_size=8, d_model=d, layers=1, max_context=T,
+                               block_size=64, local_window=128, top_blocks=4, k_max=8)
+    layer = RoutedPrefillLayer(RoutedRelationLM(cfg, seed=1003), 0, device, torch.bfloat16)
+    B = max(1, 8 // world)
+    g = torch.Generator().manual_seed(1003 + rank)
+    x = torch.randn(B, T, d, generator=g)
+    strong = torch.rand(B, T, generator=g) < 0.05
+    x = torch.where(strong[..., None], x * 4.0, x).to(device)
+    N, K, H = B * T, cfg.k_max, cfg.hidden_dim
+
+    def timed(fn, repeats=1):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(repeats):
+            out = fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / repeats, out
+
+    layer.build_state(x)                                     # warm-up of every kernel of the build
+    build_ms, state = timed(lambda: layer.build_state(x))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    for _ in range(max(3, args.warmup)):
+        layer.forward(x, state)
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    events = []
+    for _ in range(args.steps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        layer.forward(x, state)
+        e.record()
+        events.append((s, e))
+    barrier()
+    total_ms = sum(s.elapsed_time(e) for s, e in events)
+    clocks = sampler.stop() if sampler else None
+    # end to end: the hidden states come from pinned host memory and the layer's output goes back
+    host_in = x.cpu().pin_memory()
+    host_out = torch.empty_like(host_in).pin_memory()
+    dev_in = torch.empty_like(x)
+    e2e_steps = min(args.steps, 8)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dev_in.copy_(host_in, non_blocking=True)
+        host_out.copy_(layer.forward(dev_in, state), non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    assert _abi.read_status() == 0, "a kernel reported a device-side error"
+    total_ms, e2e_ms, build_ms = max_over_ranks([total_ms, e2e_ms, build_ms], world, device)
+    if rank == 0:
+        keep: dict = {}
+        layer.forward(x, state, keep)
+        w = layer.w
+        q, rb, rp = keep["query"], keep["row_batch"], keep["row_position"]
+        hidden_rel = torch.empty(N, K, H, device=device, dtype=torch.bfloat16)
+        parts = {
+            "relation_select_kernel(rows)": lambda: relation_select_packed_rows(
+                q[:, 0:64], state["anchor_keys"], q[:, 64:128], state["anchor_mean"], state["anchor_std"],
+                w["anchor_gamma"], w["anchor_bias"], q[:, 128:256], state["partner_anchor_cache"],
+                state["partner_keys"], state["partner_mean"], state["partner_std"], w["partner_gamma"],
+                w["partner_bias"], rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid),
+            "relation_hidden_tc_kernel(rows)": lambda: relation_hidden_cached_rows_out(
+                hidden_rel, state["expanded_cache"], state["operand_cache"], keep["anchor"], keep["partner"],
+                w["product_weight"], rb),
+            "packed_projection_kernel(second layer)": lambda: packed_projection(hidden_rel.view(N * K, H), w["w2"], w["b2"]),
+            "relation_norm_reduce_kernel(rows)": lambda: relation_norm_reduce_rows(
+                keep["raw"], keep["partner_score"], w["relation_norm_w"], w["relation_norm_b"], rp, cfg.norm_eps),
+        }
+        kernels = {}
+        for name, fn in parts.items():
+            fn()
+            ms, _ = timed(fn, repeats=5)
+            kernels[name] = {"us_per_launch": ms * 1e3}
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        nb, cand = T // cfg.block_size, cfg.local_window + cfg.top_blocks * cfg.block_size
+        logical = N * (2 * (4 * nb * 64 + 2 * cand * 64 + 384) + 560 + 8 + 8 * K)
+        compulsory = 2 * (B * T * (64 + 64 + 128) + 4 * B * nb * 64 + N * 256) + N * (8 + 8 * K)
+        flops = N * 2 * (2 * cand * 64 + 2 * 2 * nb * 64)
+        sel_us = kernels["relation_select_kernel(rows)"]["us_per_launch"]
+        fma_peak = 148 * 128 * 2 * (float(peaks.get("sm_max_mhz", 1965.0)) * 1e6) / 1e12
+        kernels["relation_select_kernel(rows)"].update(
+            compulsory_bytes=compulsory, logical_bytes=logical, fp32_flops=flops,
+            compulsory_gb_per_s=compulsory / sel_us / 1e3, logical_gb_per_s=logical / sel_us / 1e3,
+            tflops=flops / sel_us / 1e6, frac_of_fp32_fma_peak=flops / sel_us / 1e6 / fma_peak)
+        kernels["relation_hidden_tc_kernel(rows)"]["tflops"] = 2 * N * K * cfg.relation_dim * H / kernels["relation_hidden_tc_kernel(rows)"]["us_per_launch"] / 1e6
+        kernels["packed_projection_kernel(second layer)"]["tflops"] = 2 * N * K * H * d / kernels["packed_projection_kernel(second layer)"]["us_per_launch"] / 1e6
+        dominant = max(kernels, key=lambda k: kernels[k]["us_per_launch"])
+        line = {
+            "metric": "relation prefill tokens/s at ctx4096 K=8", "value": world * N * args.steps / (total_ms / 1e3),
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg3 relation_select + relation_reduce prefill: batch 8, ctx 4096, d_model 512, "
+                                   "block 64, window 128, 4 remote blocks, 1 anchor, K=8, 5% strong-anchor positions",
+                       "batch_per_gpu": B, "global_batch": B * world, "rows_per_step": world * N,
+                       "l2": "flushed between steps", "state_build_ms": build_ms},
+            "e2e": {"value": world * N * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": N * d * 4, "d2h_bytes_per_step": N * d * 4, "steps": e2e_steps},
+            "gpu_launches": 6 * args.steps, "clocks": clocks, "kernels": kernels,
+            "roofline": {"kernel": "relation_select_kernel(rows)", "bound": "hbm", "achieved": compulsory / sel_us / 1e3,
+                         "peak": peak, "unit": "GB/s", "frac": compulsory / sel_us / 1e3 / peak,
+                         "peak_source": "measured" if peaks else "fallback", "traffic": None,
+                         "note": "compulsory bytes (every input and output tensor once); the per-row form re-reads "
+                                 "shared windows from L2: logical bytes and the fp32 FMA fraction are in `kernels`",
+                         "dominant_kernel_of_the_pass": dominant},
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_prefill_rate(layer, state, keep)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_prefill_rate(layer, state, keep, sample: int = 1024) -> dict:
+    """The CPU oracle on a bounded sample of the same query rows (selection, relation hidden, second
+    MLP layer, norm-reduce), all host threads; tokens/s = sampled rows / time."""
+    import oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    oracle.set_threads(threads)
+    cfg = layer.config
+    wc = {k: v.float().cpu() for k, v in layer.w.items()}
+    g = torch.Generator().manual_seed(5)
+    n_rows = keep["query"].size(0)
+    rows = torch.randint(0, n_rows, (sample,), generator=g)
+    q = keep["query"].cpu()[rows]
+    rb, rp = keep["row_batch"].cpu()[rows], keep["row_position"].cpu()[rows]
+    caches = {n: state[n].float().cpu() for n in ("anchor_keys", "partner_keys", "partner_anchor_cache", "anchor_mean",
+                                                   "anchor_std", "partner_mean", "partner_std", "expanded_cache",
+                                                   "operand_cache")}
+    start = time.perf_counter()
+    anchor, _, partner, score, _ = oracle.relation_select(
+        q[:, 0:64], caches["anchor_keys"], q[:, 64:128], caches["anchor_mean"], caches["anchor_std"],
+        wc["anchor_gamma"], wc["anchor_bias"], q[:, 128:256], caches["partner_anchor_cache"], caches["partner_keys"],
+        caches["partner_mean"], caches["partner_std"], wc["partner_gamma"], wc["partner_bias"], 0,
+        cfg.local_window, cfg.top_blocks, cfg.k_max, cfg.strict_valid, row_batch=rb, row_pos=rp)
+    hidden, _ = oracle.relation_hidden(caches["expanded_cache"], caches["operand_cache"], anchor,
+                                       partner.clamp(0, cfg.max_context - 1), wc["product_weight"], row_batch=rb, row_pos=rp)
+    raw = hidden @ wc["w2"].T + wc["b2"]
+    oracle.relation_norm_reduce(raw, score, wc["relation_norm_w"], wc["relation_norm_b"], 0, cfg.norm_eps, row_pos=rp)
+    elapsed = time.perf_counter() - start
+    return {"value": sample / elapsed, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{sample} of the {n_rows} query rows: oracle selection + relation hidden + second layer + norm-reduce"}
+
+
 # ---------------------------------------------------------------------------- reference-side child modes
 
 
@@ -896,7 +1086,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("cfg2", "cfg5"), default="cfg2")
+    parser.add_argument("--workload", choices=("cfg2", "cfg5", "cfg3"), default="cfg2")
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
@@ -922,6 +1112,9 @@ def main() -> None:
         return
     if args.kernel_case:
         run_kernel_case(args)
+        return
+    if args.workload == "cfg3":
+        run_prefill(args)
         return
     if args.batch is None:
         args.batch = 8 if args.workload == "cfg2" else 256 // max(1, args.gpus)

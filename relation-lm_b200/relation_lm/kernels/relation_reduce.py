@@ -617,6 +617,46 @@ def _(expanded_cache, operand_cache, anchor_index, partner_index, product_weight
         (partner_index.size(0), partner_index.size(1), product_weight.size(0)), dtype=torch.float32)
 
 
+@torch.library.custom_op("relation_lm::relation_hidden_cached_rows_out", mutates_args=("out",),
+                         device_types="cuda")
+def relation_hidden_cached_rows_out(
+    out: Tensor,
+    expanded_cache: Tensor,
+    operand_cache: Tensor,
+    anchor_index: Tensor,
+    partner_index: Tensor,
+    product_weight: Tensor,
+    row_batch: Tensor,
+) -> None:
+    """``relation_hidden_cached_rows`` into a caller-owned ``out [N, K, H]`` of any float dtype: a
+    prefill pass over thousands of rows keeps the hidden states in 16 bits (half the bytes of the
+    fp32 form, and the dtype the second relation-MLP layer's tensor-core GEMM reads)."""
+    device = _abi.require_cuda_contiguous(
+        out=out, expanded_cache=expanded_cache, operand_cache=operand_cache, anchor_index=anchor_index,
+        partner_index=partner_index, product_weight=product_weight, row_batch=row_batch)
+    n_seq, max_t, rdim = operand_cache.shape
+    rows, k_out = partner_index.shape
+    hdim = product_weight.size(0)
+    _check_indices(anchor_index, partner_index, rows)
+    if row_batch.dtype != torch.int32 or row_batch.numel() != rows:
+        raise ValueError("row_batch must be int32 with one entry per query row")
+    if expanded_cache.shape != (n_seq, max_t, 2 * hdim) or product_weight.size(1) != rdim \
+            or out.shape != (rows, k_out, hdim):
+        raise ValueError("expanded_cache must be [B, T, 2H], product_weight [H, R] and out [N, K, H]")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_hidden_cached(
+            _abi.ptr(expanded_cache), _abi.ptr(operand_cache), _abi.ptr(anchor_index),
+            _abi.ptr(partner_index), _abi.ptr(product_weight), _abi.ptr(row_batch), _abi.ptr(out),
+            rows, n_seq, max_t, rdim, hdim, k_out,
+            _abi.same_dtype("cache", expanded_cache, operand_cache), _abi.code(product_weight),
+            _abi.code(out), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@relation_hidden_cached_rows_out.register_fake
+def _(out, expanded_cache, operand_cache, anchor_index, partner_index, product_weight, row_batch):
+    return None
+
+
 @torch.library.custom_op("relation_lm::relation_norm_reduce_rows", mutates_args=(),
                          device_types="cuda")
 def relation_norm_reduce_rows(
