@@ -461,6 +461,37 @@ int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token
                      int rows, int vocab, int dtype, void* stream);
 
 /*
+ * Routed multi-anchor selection, all slots of a query row in one launch (extension).  The
+ * reference's multi-anchor layer is dense (src/relation_lm/models/multi_relation_blocks.py:69-148);
+ * this applies its rules inside each slot's routed candidate set (local window + that slot's
+ * best remote blocks): slot s is active at position t iff s <= t (:82-84); slots choose anchors
+ * one after another, positions taken by earlier slots barred (:86-93); an inactive slot reports
+ * anchor 0 (:94); every slot's partner selection bars the anchors of all active slots (:133-139);
+ * inactive slots have no partners (:140-142); a partner slot is active iff its score is finite
+ * (:144-147: inactive partner slots report index 0 and score -inf).
+ *   anchor_query, anchor_router_query [N,S,64], partner_base [N,S,128] (query-side half of the
+ *   factorised partner query; the anchor-side half comes from partner_anchor_cache)   query_dtype
+ *     (slots contiguous inside a row; the row strides in ELEMENTS are passed, so the three may be
+ *     column slices of one query-side projection)
+ *   anchor_keys, partner_keys [S,B,T,64], partner_anchor_cache [S,B,T,128]              key_dtype
+ *   *_mean, *_std [S,B,NB,4,16] stats_dtype; *_gamma [S,4], *_bias [S,4,buckets] param_dtype
+ *   row_batch, row_position [N] int32
+ *   out_anchor [N,S] i32, out_anchor_score [N,S] f32, out_anchor_active [N,S] u8,
+ *   out_partner [N,S,K] i32, out_partner_score [N,S,K] f32.  1 <= S <= 8.
+ */
+int rlm_relation_select_multi_rows(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    const int32_t* row_batch, const int32_t* row_position, int32_t* out_anchor, float* out_anchor_score,
+    uint8_t* out_anchor_active, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
+    int n_rows, int n_seq, int slots,
+    int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out, int strict_valid,
+    int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream);
+
+/*
  * Self-test of the bounded device-side wait (extension, test support; no counterpart in the
  * reference project).  Launches one CTA that waits, for at most `cycle_limit` SM cycles
  * (1 .. 2^24), on an mbarrier nothing will ever complete, then ORs RLM_DEV_TIMEOUT into *status

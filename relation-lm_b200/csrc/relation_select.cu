@@ -634,14 +634,17 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
 // launches of many rows, where rows in flight per SM set the throughput.  kBf16: queries, key
 // caches and block statistics are all bf16 (the decode configuration); the dtype branches
 // fold away, which matters because a row's time is largely instruction fetch.
-template <int kMinCtas, bool kBf16, bool kDecode>
-__global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+// The selection of one query row by the whole CTA.  kMulti: called in a loop by the multi-anchor
+// kernel (one call per slot and phase): the caller has already ordered itself after earlier
+// kernels, hands in the four mbarriers of this call, and in partner-only mode the partner queries
+// are completed here with the anchor's row of the partner-anchor cache.
+template <bool kBf16, bool kDecode, bool kMulti>
+__device__ __forceinline__ void select_row(const SelectArgs& a, const int row, unsigned char* smem,
+                                           const uint32_t bars) {
     __shared__ uint32_t warp_key[2 * kWarps];
     __shared__ int warp_pos[2 * kWarps];
     __shared__ int excl_s[kMaxExclude];
     __shared__ float softplus_s[8];
-    const int row = blockIdx.x;
     // kDecode: the packed operator in its decode form (a row per sequence, one position for all, no
     // exclusion list): the other forms' branches fold away
     const int mode = kDecode ? static_cast<int>(kPacked) : a.mode;
@@ -660,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     // The per-row form and exclusion lists take indices from arbitrary producers: wait first.
     const bool early = row_position == nullptr && row_batch == nullptr && exclude_list == nullptr &&
                        mode != kPartnerOnly;
-    if (!early) griddep_sync();
+    if (!early && !kMulti) griddep_sync();
     // threads 32..35 / 36..39 evaluate softplus(gamma) of the anchor / partner heads for everybody
     const bool sp_thread = tid >= 32 && tid < 40 && (tid < 36 ? do_anchor : do_partner);
     float gamma = 0.0f, ba = 0.0f, bp_ = 0.0f;
@@ -690,7 +693,6 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     float* bscore = reinterpret_cast<float*>(smem + p.block_scores);
     float* cand = reinterpret_cast<float*>(smem + p.cand);
     int* sel = reinterpret_cast<int*>(smem + p.sel);
-    const uint32_t bars = smem_u32(smem + p.bars);
     const uint32_t bar_a = bars, bar_p = bars + 8, bar_ra = bars + 16, bar_rp = bars + 24;
 
     const int ls = max(t - L + 1, 0);
@@ -847,6 +849,12 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
         }
     } else {
         anchor_pos = a.anchor_index_in[row];
+        if (kMulti && tid < 2 * kD) {
+            // factorised partner queries of a multi-anchor slot: query-side base + the anchor's cached row
+            const float add = load_scalar(a.partner_anchor_cache,
+                                          (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * kD + tid, key_dtype);
+            pq[tid] = __fadd_rn(pq[tid], add);   // written by this very thread above; pq[64..127] is prq
+        }
     }
 
     bool okp = mbar_wait(bar_p, 0);
@@ -904,6 +912,119 @@ __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(con
     }
     topk_large(cand, cap, K, L, t, bs, sel, a.out_partner + static_cast<size_t>(row) * K,
                a.out_partner_score + static_cast<size_t>(row) * K);
+}
+
+template <int kMinCtas, bool kBf16, bool kDecode>
+__global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    select_row<kBf16, kDecode, false>(a, blockIdx.x, smem, smem_u32(smem + a.plan.bars));
+}
+
+// ---- routed multi-anchor selection: S anchor slots per query row, one launch
+//
+// Rules of the reference's dense multi-anchor layer (src/relation_lm/models/multi_relation_blocks.py)
+// applied inside each slot's routed candidate set: slot s is active for a query at position t iff
+// s <= t (:82-84); slots choose their anchors one after another and a position taken by an earlier
+// slot is barred (:86-93); an inactive slot reports anchor 0 (:94); the partner selection of every
+// slot bars the anchors of all active slots (:133-139); an inactive slot has no partners
+// (:140-142); a partner slot is active iff its score is finite (:144-147).  Every slot has its own
+// key caches, block statistics and router parameters (leading slot dimension).
+constexpr int kMaxSlots = kMaxExclude;
+
+struct MultiSelectArgs {
+    SelectArgs base;               // slot 0's pointers; per-slot strides below (bytes)
+    Plan plan_anchor, plan_partner;
+    int slots;
+    size_t keys_slot, pac_slot, stats_slot, gamma_slot, bias_slot;   // bytes between slots
+    int32_t* out_anchor;           // [N, S]
+    float* out_anchor_score;       // [N, S]
+    uint8_t* out_anchor_active;    // [N, S]
+    int32_t* out_partner;          // [N, S, K]
+    float* out_partner_score;      // [N, S, K]
+};
+
+__device__ __forceinline__ const void* slot_ptr(const void* p, size_t bytes) {
+    return static_cast<const char*>(p) + bytes;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 3) relation_select_multi_kernel(const MultiSelectArgs m) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long call_bars[4 * 2 * kMaxSlots];
+    __shared__ int taken_s[kMaxSlots];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const int S = m.slots, K = m.base.k_out;
+    griddep_sync();
+    const int b = m.base.row_batch[row], t = m.base.row_position[row];
+    if (b < 0 || b >= m.base.n_seq || t < 0 || t >= m.base.max_t) {
+        if (tid == 0 && m.base.status) atomicOr(m.base.status, RLM_DEV_POSITION);
+        return;
+    }
+    if (tid < kMaxSlots) taken_s[tid] = -1;
+    __syncthreads();
+    const int esz = m.base.query_dtype == RLM_F32 ? 4 : 2;
+    // anchors: slot after slot, each barring the positions taken before it
+    for (int s = 0; s < S; ++s) {
+        const bool slot_live = s <= t;
+        int32_t* out_idx = m.out_anchor + static_cast<size_t>(row) * S + s;
+        float* out_sc = m.out_anchor_score + static_cast<size_t>(row) * S + s;
+        if (slot_live) {
+            SelectArgs a = m.base;
+            a.mode = kAnchorOnly;
+            a.plan = m.plan_anchor;
+            a.anchor_query = slot_ptr(m.base.anchor_query, static_cast<size_t>(s) * kD * esz);
+            a.anchor_router_query = slot_ptr(m.base.anchor_router_query, static_cast<size_t>(s) * kD * esz);
+            a.anchor_keys = slot_ptr(m.base.anchor_keys, s * m.keys_slot);
+            a.anchor_mean = slot_ptr(m.base.anchor_mean, s * m.stats_slot);
+            a.anchor_std = slot_ptr(m.base.anchor_std, s * m.stats_slot);
+            a.anchor_gamma = slot_ptr(m.base.anchor_gamma, s * m.gamma_slot);
+            a.anchor_bias = slot_ptr(m.base.anchor_bias, s * m.bias_slot);
+            a.exclude_list = s > 0 ? taken_s - static_cast<ptrdiff_t>(row) * s : nullptr;   // [row * s + i] == taken_s[i]
+            a.exclude_count = s;
+            a.out_anchor = out_idx - row;                    // [row] lands on (row, s)
+            a.out_anchor_score = out_sc - row;
+            select_row<kBf16, false, true>(a, row, smem, smem_u32(&call_bars[4 * s]));
+        }
+        __syncthreads();
+        if (tid == 0) {                                      // the thread that stored the slot's result
+            const bool live = slot_live && *out_sc > kNegInf;
+            if (!live) { *out_idx = 0; *out_sc = kNegInf; }
+            taken_s[s] = live ? *out_idx : -1;
+            m.out_anchor_active[static_cast<size_t>(row) * S + s] = live ? 1 : 0;
+        }
+        __syncthreads();
+    }
+    // partners: every live slot bars the anchors of all slots
+    for (int s = 0; s < S; ++s) {
+        int32_t* out_idx = m.out_partner + (static_cast<size_t>(row) * S + s) * K;
+        float* out_sc = m.out_partner_score + (static_cast<size_t>(row) * S + s) * K;
+        const bool live = taken_s[s] >= 0;
+        if (live) {
+            SelectArgs a = m.base;
+            a.mode = kPartnerOnly;
+            a.plan = m.plan_partner;
+            a.partner_base = slot_ptr(m.base.partner_base, static_cast<size_t>(s) * 2 * kD * esz);
+            a.partner_router_query = slot_ptr(m.base.partner_base, (static_cast<size_t>(s) * 2 * kD + kD) * esz);
+            a.prq_stride = m.base.pbase_stride;
+            a.partner_anchor_cache = slot_ptr(m.base.partner_anchor_cache, s * m.pac_slot);
+            a.partner_keys = slot_ptr(m.base.partner_keys, s * m.keys_slot);
+            a.partner_mean = slot_ptr(m.base.partner_mean, s * m.stats_slot);
+            a.partner_std = slot_ptr(m.base.partner_std, s * m.stats_slot);
+            a.partner_gamma = slot_ptr(m.base.partner_gamma, s * m.gamma_slot);
+            a.partner_bias = slot_ptr(m.base.partner_bias, s * m.bias_slot);
+            a.anchor_index_in = taken_s + s - row;           // [row] == taken_s[s]
+            a.exclude_list = taken_s - static_cast<ptrdiff_t>(row) * S;
+            a.exclude_count = S;
+            a.out_partner = out_idx - static_cast<ptrdiff_t>(row) * K;
+            a.out_partner_score = out_sc - static_cast<ptrdiff_t>(row) * K;
+            select_row<kBf16, false, true>(a, row, smem, smem_u32(&call_bars[4 * (S + s)]));
+        }
+        __syncthreads();
+        if (tid < K) {                                       // the threads that stored the slot's results
+            if (!live || !(out_sc[tid] > kNegInf)) { out_idx[tid] = 0; out_sc[tid] = kNegInf; }
+        }
+        __syncthreads();
+    }
 }
 
 int launch(SelectArgs& a, void* stream) {
@@ -983,8 +1104,89 @@ int launch(SelectArgs& a, void* stream) {
     return check_launch("relation_select_kernel");
 }
 
+int launch_multi(MultiSelectArgs& m, void* stream) {
+    SelectArgs& a = m.base;
+    if (a.n_rows == 0) return RLM_OK;
+    if (a.n_rows < 0 || a.n_seq < 1 || a.max_t < 1 || a.n_blocks < 1 || a.buckets < 1 || a.local_window < 1 ||
+        a.top_blocks < 0 || a.max_t % a.n_blocks != 0 || m.slots < 1 || m.slots > kMaxSlots || a.k_out < 1 ||
+        a.k_out > kMaxKOut) {
+        set_error("relation_select_multi_rows: sizes must be positive, T a multiple of the block count, 1..8 slots, K <= 32");
+        return RLM_ERR_SHAPE;
+    }
+    if (!valid_dtype(a.query_dtype) || !valid_dtype(a.key_dtype) || !valid_dtype(a.stats_dtype) || !valid_dtype(a.param_dtype)) {
+        set_error("relation_select_multi_rows: unknown dtype code");
+        return RLM_ERR_DTYPE;
+    }
+    const void* need[] = {a.anchor_query, a.anchor_keys, a.anchor_router_query, a.anchor_mean, a.anchor_std, a.anchor_gamma,
+                          a.anchor_bias, a.partner_base, a.partner_anchor_cache, a.partner_keys, a.partner_mean,
+                          a.partner_std, a.partner_gamma, a.partner_bias, a.row_batch, a.row_position, m.out_anchor,
+                          m.out_anchor_score, m.out_anchor_active, m.out_partner, m.out_partner_score};
+    for (const void* q : need) if (!q) { set_error("relation_select_multi_rows: NULL pointer"); return RLM_ERR_NULL; }
+    const void* bulk[] = {a.anchor_keys, a.anchor_mean, a.anchor_std, a.partner_keys, a.partner_mean, a.partner_std,
+                          a.partner_anchor_cache};
+    for (const void* q : bulk)
+        if (!aligned16(q)) {
+            set_error("relation_select_multi_rows: key caches, block statistics and the partner-anchor cache must be 16-byte aligned");
+            return RLM_ERR_ALIGN;
+        }
+    a.block_size = a.max_t / a.n_blocks;
+    a.shared_streams = 0;
+    const int ks = dtype_size(a.key_dtype), ss = dtype_size(a.stats_dtype), ps = dtype_size(a.param_dtype);
+    m.plan_anchor = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets, ks, ss, kAnchorOnly, false);
+    m.plan_partner = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets, ks, ss, kPartnerOnly, false);
+    const int total = m.plan_anchor.total > m.plan_partner.total ? m.plan_anchor.total : m.plan_partner.total;
+    if (total > kSmemDynamicLimit) {
+        set_error("relation_select_multi_rows: block statistics + local window + remote blocks exceed 227 KB of shared memory");
+        return RLM_ERR_SMEM;
+    }
+    m.keys_slot = static_cast<size_t>(a.n_seq) * a.max_t * kD * ks;
+    m.pac_slot = static_cast<size_t>(a.n_seq) * a.max_t * 2 * kD * ks;
+    m.stats_slot = static_cast<size_t>(a.n_seq) * a.n_blocks * kD * ss;
+    m.gamma_slot = static_cast<size_t>(4) * ps;
+    m.bias_slot = static_cast<size_t>(4) * a.buckets * ps;
+    if (a.aq_stride < static_cast<int64_t>(m.slots) * kD || a.arq_stride < static_cast<int64_t>(m.slots) * kD ||
+        a.pbase_stride < static_cast<int64_t>(m.slots) * 2 * kD) {
+        set_error("relation_select_multi_rows: a query row stride is shorter than the slots it holds");
+        return RLM_ERR_SHAPE;
+    }
+    const bool bf16 = a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
+    auto kernel = bf16 ? relation_select_multi_kernel<true> : relation_select_multi_kernel<false>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    launch_kernel(kernel, dim3(a.n_rows), dim3(kThreads), total, stream, m);
+    count_launch();
+    return check_launch("relation_select_multi_kernel");
+}
+
 }  // namespace
 }  // namespace rlm
+
+extern "C" int rlm_relation_select_multi_rows(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    const int32_t* row_batch, const int32_t* row_position, int32_t* out_anchor, float* out_anchor_score,
+    uint8_t* out_anchor_active, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
+    int n_rows, int n_seq, int slots,
+    int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out, int strict_valid,
+    int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream) {
+    rlm::MultiSelectArgs m{};
+    rlm::SelectArgs& a = m.base;
+    a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = anchor_router_query;
+    a.anchor_mean = anchor_mean; a.anchor_std = anchor_std; a.anchor_gamma = anchor_gamma; a.anchor_bias = anchor_bias;
+    a.partner_base = partner_base; a.partner_anchor_cache = partner_anchor_cache; a.partner_keys = partner_keys;
+    a.partner_mean = partner_mean; a.partner_std = partner_std; a.partner_gamma = partner_gamma; a.partner_bias = partner_bias;
+    a.row_batch = row_batch; a.row_position = row_position; a.status = status;
+    a.n_rows = n_rows; a.n_seq = n_seq; a.max_t = max_t; a.n_blocks = n_blocks; a.buckets = buckets;
+    a.local_window = local_window; a.top_blocks = top_blocks; a.k_out = k_out; a.strict_valid = strict_valid != 0;
+    a.query_dtype = query_dtype; a.key_dtype = key_dtype; a.stats_dtype = stats_dtype; a.param_dtype = param_dtype;
+    a.aq_stride = anchor_query_stride; a.arq_stride = anchor_router_query_stride; a.pbase_stride = partner_base_stride;
+    m.slots = slots; m.out_anchor = out_anchor; m.out_anchor_score = out_anchor_score;
+    m.out_anchor_active = out_anchor_active; m.out_partner = out_partner; m.out_partner_score = out_partner_score;
+    return rlm::launch_multi(m, stream);
+}
 
 extern "C" int rlm_relation_select_packed(
     const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,

@@ -1,9 +1,9 @@
-"""Routed multi-anchor selection (extension).
+"""``relation_lm::relation_select_multi_rows`` — routed multi-anchor selection (extension).
 
 The reference project's multi-anchor layer is dense: every slot scores all causal positions
-(src/relation_lm/models/multi_relation_blocks.py:69-148).  This is its routed form, built from
-the per-row selectors of this library.  Its rules are the reference's, applied inside each
-slot's routed candidate set (local window + that slot's best remote blocks):
+(src/relation_lm/models/multi_relation_blocks.py:69-148).  This is its routed form, one launch
+for all slots of every query row.  Its rules are the reference's, applied inside each slot's
+routed candidate set (local window + that slot's best remote blocks):
 
 * slot ``s`` is active for a query at position ``t`` iff ``s <= t``          (:82-84);
 * slots choose their anchors one after another, a position taken by an earlier slot is barred
@@ -20,9 +20,10 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from relation_lm.kernels.triton_select import anchor_select_rows, partner_topk_rows
+from relation_lm.kernels import _abi
 
 
+@torch.library.custom_op("relation_lm::relation_select_multi_rows", mutates_args=(), device_types="cuda")
 def relation_select_multi_rows(
     anchor_query: Tensor,            # [N, S, 64]
     anchor_keys: Tensor,             # [S, B, T, 64]
@@ -44,40 +45,73 @@ def relation_select_multi_rows(
     top_blocks: int,
     partners_per_anchor: int,
     strict_valid: bool,
-):
+) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     """Returns ``(anchor_index [N,S] i32, anchor_score [N,S], anchor_active [N,S] bool,
     partner_index [N,S,K] i32, partner_score [N,S,K], partner_active [N,S,K] bool)``."""
+    for name, query in (("anchor_query", anchor_query), ("anchor_router_query", anchor_router_query),
+                        ("partner_base", partner_base)):
+        if not query.is_cuda or query.dim() != 3 or query.stride(2) != 1 or query.stride(1) != query.size(2):
+            raise ValueError(f"{name} must be a CUDA tensor [N, S, width] whose slots are contiguous inside a row "
+                             "(the row stride is free: a column slice of one projection is fine)")
+    device = _abi.require_cuda_contiguous(
+        anchor_keys=anchor_keys,
+        anchor_block_mean=anchor_block_mean, anchor_block_std=anchor_block_std, anchor_gamma=anchor_gamma,
+        anchor_bias=anchor_bias, partner_anchor_cache=partner_anchor_cache,
+        partner_keys=partner_keys, partner_block_mean=partner_block_mean, partner_block_std=partner_block_std,
+        partner_gamma=partner_gamma, partner_bias=partner_bias, row_batch=row_batch, row_position=row_position)
+    if anchor_query.dim() != 3 or anchor_query.size(2) != 64:
+        raise ValueError("anchor_query must be [N, S, 64]")
     rows, slots = anchor_query.shape[0], anchor_query.shape[1]
     if slots > 8:
         raise ValueError("at most 8 anchor slots")
-    device = anchor_query.device
-    active = torch.arange(slots, device=device)[None, :] <= row_position[:, None]
-    taken = torch.full((rows, slots), -1, dtype=torch.int32, device=device)
-    anchor_index = torch.zeros((rows, slots), dtype=torch.int32, device=device)
-    anchor_score = torch.full((rows, slots), -torch.inf, device=device)
-    for s in range(slots):
-        idx, score = anchor_select_rows(
-            anchor_query[:, s].contiguous(), anchor_keys[s], anchor_router_query[:, s].contiguous(),
-            anchor_block_mean[s], anchor_block_std[s], anchor_gamma[s], anchor_bias[s], row_batch,
-            row_position, taken.clone(), local_window, top_blocks, strict_valid)
-        live = active[:, s] & torch.isfinite(score)
-        anchor_index[:, s] = torch.where(live, idx, torch.zeros_like(idx))
-        anchor_score[:, s] = torch.where(live, score, torch.full_like(score, -torch.inf))
-        taken[:, s] = torch.where(live, idx, torch.full_like(idx, -1))
-        active[:, s] = live
+    if anchor_keys.dim() != 4 or anchor_keys.size(0) != slots or anchor_keys.size(3) != 64:
+        raise ValueError("anchor_keys must be [S, B, T, 64]")
+    _, batch, max_t, _ = anchor_keys.shape
+    nb = anchor_block_mean.size(2)
+    if anchor_router_query.shape != (rows, slots, 64) or partner_base.shape != (rows, slots, 128) \
+            or partner_anchor_cache.shape != (slots, batch, max_t, 128) or partner_keys.shape != anchor_keys.shape \
+            or anchor_block_mean.shape != (slots, batch, nb, 4, 16) or partner_block_mean.shape != anchor_block_mean.shape \
+            or anchor_gamma.shape != (slots, 4) or anchor_bias.dim() != 3 or anchor_bias.shape[:2] != (slots, 4):
+        raise ValueError("relation_select_multi_rows: inconsistent shapes")
+    if row_batch.dtype != torch.int32 or row_position.dtype != torch.int32 \
+            or row_batch.numel() != rows or row_position.numel() != rows:
+        raise ValueError("row_batch and row_position must be int32 with one entry per query row")
     k = int(partners_per_anchor)
-    partner_index = torch.zeros((rows, slots, k), dtype=torch.int32, device=device)
-    partner_score = torch.full((rows, slots, k), -torch.inf, device=device)
-    batch_index = row_batch.long()
-    for s in range(slots):
-        v = partner_base[:, s].float() + partner_anchor_cache[s][batch_index, anchor_index[:, s].long()].float()
-        v = v.to(partner_base.dtype)
-        idx, score = partner_topk_rows(
-            v[:, :64].contiguous(), partner_keys[s], v[:, 64:].contiguous(), partner_block_mean[s],
-            partner_block_std[s], partner_gamma[s], partner_bias[s], row_batch, row_position,
-            taken[:, s].contiguous(), taken, local_window, top_blocks, k, strict_valid)
-        live = active[:, s, None] & torch.isfinite(score)
-        partner_index[:, s] = torch.where(live, idx, torch.zeros_like(idx))
-        partner_score[:, s] = torch.where(live, score, torch.full_like(score, -torch.inf))
-    return (anchor_index, anchor_score, active, partner_index, partner_score,
+    anchor_index = torch.empty((rows, slots), dtype=torch.int32, device=device)
+    anchor_score = torch.empty((rows, slots), dtype=torch.float32, device=device)
+    anchor_active = torch.empty((rows, slots), dtype=torch.uint8, device=device)
+    partner_index = torch.empty((rows, slots, k), dtype=torch.int32, device=device)
+    partner_score = torch.empty((rows, slots, k), dtype=torch.float32, device=device)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_select_multi_rows(
+            _abi.ptr(anchor_query), _abi.ptr(anchor_keys), _abi.ptr(anchor_router_query),
+            _abi.ptr(anchor_block_mean), _abi.ptr(anchor_block_std), _abi.ptr(anchor_gamma), _abi.ptr(anchor_bias),
+            _abi.ptr(partner_base), _abi.ptr(partner_anchor_cache), _abi.ptr(partner_keys),
+            _abi.ptr(partner_block_mean), _abi.ptr(partner_block_std), _abi.ptr(partner_gamma),
+            _abi.ptr(partner_bias), _abi.ptr(row_batch), _abi.ptr(row_position), _abi.ptr(anchor_index),
+            _abi.ptr(anchor_score), _abi.ptr(anchor_active), _abi.ptr(partner_index), _abi.ptr(partner_score),
+            anchor_query.stride(0), anchor_router_query.stride(0), partner_base.stride(0),
+            rows, batch, slots, max_t, nb, anchor_bias.size(2), int(local_window), int(top_blocks), k,
+            int(bool(strict_valid)),
+            _abi.same_dtype("query", anchor_query, anchor_router_query, partner_base),
+            _abi.same_dtype("key cache", anchor_keys, partner_keys, partner_anchor_cache),
+            _abi.same_dtype("block statistics", anchor_block_mean, anchor_block_std, partner_block_mean, partner_block_std),
+            _abi.same_dtype("router parameter", anchor_gamma, anchor_bias, partner_gamma, partner_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return (anchor_index, anchor_score, anchor_active.bool(), partner_index, partner_score,
             torch.isfinite(partner_score))
+
+
+@relation_select_multi_rows.register_fake
+def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_block_std, anchor_gamma,
+      anchor_bias, partner_base, partner_anchor_cache, partner_keys, partner_block_mean, partner_block_std,
+      partner_gamma, partner_bias, row_batch, row_position, local_window, top_blocks, partners_per_anchor,
+      strict_valid):
+    rows, slots = anchor_query.size(0), anchor_query.size(1)
+    k = partners_per_anchor
+    f32 = torch.float32
+    return (anchor_query.new_empty((rows, slots), dtype=torch.int32), anchor_query.new_empty((rows, slots), dtype=f32),
+            anchor_query.new_empty((rows, slots), dtype=torch.bool),
+            anchor_query.new_empty((rows, slots, k), dtype=torch.int32),
+            anchor_query.new_empty((rows, slots, k), dtype=f32),
+            anchor_query.new_empty((rows, slots, k), dtype=torch.bool))

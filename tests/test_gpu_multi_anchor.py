@@ -69,7 +69,8 @@ def test_routed_multi_anchor_matches_oracle_composition(strict):
     assert torch.equal(got[0].cpu(), anchors)
     assert torch.equal(got[2].cpu(), active)
     for s in range(S):
-        v = (x["pb"][:, s].float() + x["pac"][s][row_batch.long(), anchors[:, s].long()].float()).to(dt)
+        # the kernel adds the anchor's cached row to the query-side base in fp32, like the packed selector
+        v = x["pb"][:, s].float() + x["pac"][s][row_batch.long(), anchors[:, s].long()].float()
         idx, score = oracle.partner_topk(v[:, :64], x["pk"][s], v[:, 64:], x["pm"][s], x["ps"][s], x["pg"][s],
                                          x["pbias"][s], 0, taken[:, s], L, top, K, strict, row_batch=row_batch,
                                          row_pos=row_pos, exclude_index=taken)
