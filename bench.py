@@ -860,6 +860,164 @@ def run_prefill(args) -> None:
         dist.destroy_process_group()
 
 
+def run_multi_anchor(args) -> None:
+    """`--workload cfg4`: a `RelationBlockStack`-shaped routed multi-anchor stack — depth 4, batch 16,
+    context 2048, d_model 512, 4 distinct anchors per query each choosing 4 partners, all anchors
+    barred from all partner sets, block 32, 3 remote blocks, bf16, N(0, 1) inputs, random-init
+    weights.  One step = the whole stack over all `batch x 2048` query rows: per layer the memory-side
+    projection and state build, then the routed pass.  Sequences are sharded over the ranks."""
+    from relation_lm.inference.multi_anchor import MultiAnchorConfig, MultiAnchorPrefill, MultiAnchorRoutedStack
+    from relation_lm.kernels import _abi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = MultiAnchorConfig()
+    stack = MultiAnchorRoutedStack(cfg, seed=1004)
+    runner = MultiAnchorPrefill(stack, device, torch.bfloat16)
+    B, T, d = max(1, 16 // world), cfg.max_context, cfg.d_model
+    g = torch.Generator().manual_seed(1004 + rank)
+    hidden = torch.randn(B, T, d, generator=g).to(device)
+    memory = torch.randn(B, T, d, generator=g).bfloat16().to(device)
+    N = B * T
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    launches_before = _abi.launch_count()
+    runner.forward(hidden, memory)
+    launches = _abi.launch_count() - launches_before
+    for _ in range(max(3, args.warmup) - 1):
+        runner.forward(hidden, memory)
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    events = []
+    for _ in range(args.steps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        runner.forward(hidden, memory)
+        e.record()
+        events.append((s, e))
+    barrier()
+    total_ms = sum(s.elapsed_time(e) for s, e in events)
+    clocks = sampler.stop() if sampler else None
+    host_in = hidden.cpu().pin_memory()
+    host_out = torch.empty_like(host_in).pin_memory()
+    dev_in = torch.empty_like(hidden)
+    e2e_steps = min(args.steps, 8)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dev_in.copy_(host_in, non_blocking=True)
+        host_out.copy_(runner.forward(dev_in, memory), non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    assert _abi.read_status() == 0, "a kernel reported a device-side error"
+    total_ms, e2e_ms = max_over_ranks([total_ms, e2e_ms], world, device)
+    if rank == 0:
+        # per-stage times of the first layer
+        stages = {}
+
+        def stage(name, fn):
+            fn()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn()
+            e.record()
+            torch.cuda.synchronize()
+            stages[name] = {"ms": s.elapsed_time(e)}
+            return out
+
+        state = stage("state build (projection, per-slot caches, router prefill, expanded cache)",
+                      lambda: runner.build_state(0, memory))
+        work = hidden.clone()
+        keep: dict = {}
+        stage("routed pass (norm, query projection, multi-anchor selection, hidden, second layer, norm-reduce, mix)",
+              lambda: runner.forward_layer(0, work, state, keep))
+        from relation_lm.kernels.multi_select import relation_select_multi_rows
+        w = runner.layers[0]
+        S, K = cfg.anchors_per_block, cfg.partners_per_anchor
+        q = keep["query"]
+        stage("relation_select_multi_kernel", lambda: relation_select_multi_rows(
+            q[:, :S * 64].unflatten(1, (S, 64)), state["anchor_keys"], q[:, S * 64:S * 128].unflatten(1, (S, 64)),
+            state["anchor_mean"], state["anchor_std"], w["anchor_gamma"], w["anchor_bias"],
+            q[:, S * 128:].unflatten(1, (S, 128)), state["partner_anchor_cache"], state["partner_keys"],
+            state["partner_mean"], state["partner_std"], w["partner_gamma"], w["partner_bias"], keep["row_batch"],
+            keep["row_position"], cfg.local_window, cfg.top_blocks, K, cfg.strict_valid))
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        nb, cand = T // cfg.block_size, cfg.local_window + cfg.top_blocks * cfg.block_size
+        sel_ms = stages["relation_select_multi_kernel"]["ms"]
+        logical = N * S * (2 * (4 * nb * 64 + 2 * cand * 64 + 384) + 560 + 8 + 8 * K)
+        compulsory = 2 * S * (B * T * (64 + 64 + 128) + 4 * B * nb * 64) + 2 * N * S * 256 + N * S * (9 + 8 * K)
+        stages["relation_select_multi_kernel"].update(
+            compulsory_bytes=compulsory, logical_bytes=logical, compulsory_gb_per_s=compulsory / sel_ms / 1e6,
+            logical_gb_per_s=logical / sel_ms / 1e6)
+        line = {
+            "metric": "multi-anchor relation stack tokens/s at ctx2048, 4 anchors x 4 partners, depth 4",
+            "value": world * N * args.steps / (total_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg4 routed MultiAnchorRelationBlock stack: depth 4, batch 16, ctx 2048, d_model 512, "
+                                   "4 anchors x 4 partners, block 32, window 64, 3 remote blocks",
+                       "batch_per_gpu": B, "global_batch": B * world, "rows_per_step": world * N,
+                       "l2": "flushed between steps"},
+            "e2e": {"value": world * N * e2e_steps / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": N * d * 4,
+                    "d2h_bytes_per_step": N * d * 4, "steps": e2e_steps},
+            "gpu_launches": launches * args.steps, "launches_per_step": launches, "clocks": clocks, "stages_layer0": stages,
+            "roofline": {"kernel": "relation_select_multi_kernel", "bound": "hbm", "achieved": compulsory / sel_ms / 1e6,
+                         "peak": peak, "unit": "GB/s", "frac": compulsory / sel_ms / 1e6 / peak,
+                         "peak_source": "measured" if peaks else "fallback", "traffic": None,
+                         "note": "compulsory bytes; the per-row form re-reads shared windows from L2 (logical bytes in stages_layer0)"},
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_multi_anchor_rate(stack, runner, state, keep)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_multi_anchor_rate(stack, runner, state, keep, sample: int = 256) -> dict:
+    """The CPU port's routed multi-anchor selection on a bounded sample of one layer's query rows
+    (the selection dominates the CPU time), all host threads."""
+    import oracle
+    from oracle.multi_anchor_port import OracleMultiAnchor
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    oracle.set_threads(threads)
+    port = OracleMultiAnchor(stack, torch.bfloat16)
+    g = torch.Generator().manual_seed(6)
+    n_rows = keep["query"].size(0)
+    rows = torch.randint(0, n_rows, (sample,), generator=g)
+    cpu_state = {k: v.float().cpu() for k, v in state.items() if k != "packed"}
+    q = keep["query"].cpu()[rows]
+    start = time.perf_counter()
+    port.select(0, q, cpu_state, keep["row_batch"].cpu()[rows], keep["row_position"].cpu()[rows])
+    elapsed = time.perf_counter() - start
+    depth = stack.config.depth
+    return {"value": sample / (elapsed * depth), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{sample} of the {n_rows} query rows of one layer: oracle multi-anchor selection; "
+                      f"tokens/s = rows / (time x {depth} layers)"}
+
+
 def cpu_prefill_rate(layer, state, keep, sample: int = 1024) -> dict:
     """The CPU oracle on a bounded sample of the same query rows (selection, relation hidden, second
     MLP layer, norm-reduce), all host threads; tokens/s = sampled rows / time."""
@@ -1086,7 +1244,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("cfg2", "cfg5", "cfg3"), default="cfg2")
+    parser.add_argument("--workload", choices=("cfg2", "cfg5", "cfg3", "cfg4"), default="cfg2")
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
@@ -1115,6 +1273,9 @@ def main() -> None:
         return
     if args.workload == "cfg3":
         run_prefill(args)
+        return
+    if args.workload == "cfg4":
+        run_multi_anchor(args)
         return
     if args.batch is None:
         args.batch = 8 if args.workload == "cfg2" else 256 // max(1, args.gpus)

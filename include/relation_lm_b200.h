@@ -492,6 +492,17 @@ int rlm_relation_select_multi_rows(
     int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream);
 
 /*
+ * Slot mixing of a multi-anchor relation layer (extension; the last lines of
+ * MultiAnchorRelationBlock.forward, src/relation_lm/models/multi_relation_blocks.py:170-178):
+ *   w[n,s] = slot_weight[s] * active[n,s] / max(sum_s' slot_weight[s'] * active[n,s'], 1e-9)
+ *   hidden[n] += (*gate) * sum_s w[n,s] * slot_context[n,s]
+ *   slot_context [N,S,d] f32, anchor_active [N,S] u8, slot_weight [S] f32 (softmax of the learned
+ *   logits), gate one f32 (sigmoid of the residual gate), hidden [N,d] f32 in/out; S <= 8, d % 4 == 0.
+ */
+int rlm_slot_mix_residual(const float* slot_context, const uint8_t* anchor_active, const float* slot_weight,
+                          const float* gate, float* hidden, int n_rows, int slots, int d_model, void* stream);
+
+/*
  * Self-test of the bounded device-side wait (extension, test support; no counterpart in the
  * reference project).  Launches one CTA that waits, for at most `cycle_limit` SM cycles
  * (1 .. 2^24), on an mbarrier nothing will ever complete, then ORs RLM_DEV_TIMEOUT into *status

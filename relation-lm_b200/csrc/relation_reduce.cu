@@ -905,3 +905,73 @@ extern "C" int rlm_relation_norm_reduce_project(
                                    dim, raw_dtype, param_dtype, status, stream);
 }
 
+
+// ------------------------------------------------------------------ multi-anchor slot mixing
+//
+// Last step of a multi-anchor relation layer (src/relation_lm/models/multi_relation_blocks.py:170-178
+// of the reference project): the slots' contexts are mixed with learned softmax weights
+// renormalised over the slots that are active for the query, and the result enters the residual
+// stream through a sigmoid gate:
+//   w[n, s]  = slot_weight[s] * active[n, s] / max(sum_s' slot_weight[s'] * active[n, s'], 1e-9)
+//   hidden[n] += gate * sum_s w[n, s] * slot_context[n, s]
+namespace rlm {
+namespace {
+constexpr int kMixMaxSlots = 8;
+
+__global__ void __launch_bounds__(256) slot_mix_residual_kernel(
+    const float* __restrict__ slot_context, const uint8_t* __restrict__ active, const float* __restrict__ slot_weight,
+    const float* __restrict__ gate, float* __restrict__ hidden, int n_rows, int slots, int dim) {
+    griddep_sync();
+    const int vecs = dim >> 2;                                  // float4 columns per row
+    const float g = *gate;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+         i < static_cast<int64_t>(n_rows) * vecs; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int n = static_cast<int>(i / vecs), c = static_cast<int>(i - static_cast<int64_t>(n) * vecs);
+        float w[kMixMaxSlots], total = 0.0f;
+#pragma unroll
+        for (int s = 0; s < kMixMaxSlots; ++s) {
+            w[s] = s < slots && active[static_cast<size_t>(n) * slots + s] ? slot_weight[s] : 0.0f;
+            total += w[s];
+        }
+        const float inv = 1.0f / fmaxf(total, 1.0e-9f);
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int s = 0; s < kMixMaxSlots; ++s) {
+            if (w[s] == 0.0f) continue;
+            const float4 v = reinterpret_cast<const float4*>(slot_context + (static_cast<size_t>(n) * slots + s) * dim)[c];
+            const float ws = w[s] * inv;
+            acc.x = fmaf(ws, v.x, acc.x); acc.y = fmaf(ws, v.y, acc.y); acc.z = fmaf(ws, v.z, acc.z); acc.w = fmaf(ws, v.w, acc.w);
+        }
+        float4* h = reinterpret_cast<float4*>(hidden + static_cast<size_t>(n) * dim) + c;
+        float4 hv = *h;
+        hv.x = fmaf(g, acc.x, hv.x); hv.y = fmaf(g, acc.y, hv.y); hv.z = fmaf(g, acc.z, hv.z); hv.w = fmaf(g, acc.w, hv.w);
+        *h = hv;
+    }
+}
+}  // namespace
+}  // namespace rlm
+
+extern "C" int rlm_slot_mix_residual(const float* slot_context, const uint8_t* anchor_active, const float* slot_weight,
+                                     const float* gate, float* hidden, int n_rows, int slots, int d_model,
+                                     void* stream) {
+    using namespace rlm;
+    if (n_rows == 0) return RLM_OK;
+    if (!slot_context || !anchor_active || !slot_weight || !gate || !hidden) {
+        set_error("slot_mix_residual: NULL pointer");
+        return RLM_ERR_NULL;
+    }
+    if (n_rows < 0 || slots < 1 || slots > kMixMaxSlots || d_model < 4 || d_model % 4 != 0) {
+        set_error("slot_mix_residual: 1..8 slots and a width that is a multiple of 4");
+        return RLM_ERR_SHAPE;
+    }
+    if (!aligned16(slot_context) || !aligned16(hidden)) {
+        set_error("slot_mix_residual: contexts and residual rows must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    const int64_t work = static_cast<int64_t>(n_rows) * (d_model / 4);
+    const int blocks = static_cast<int>(work / 256 + 1 < 148 * 8 ? work / 256 + 1 : 148 * 8);
+    launch_kernel(slot_mix_residual_kernel, dim3(blocks), dim3(256), 0, stream, slot_context, anchor_active,
+                  slot_weight, gate, hidden, n_rows, slots, d_model);
+    count_launch();
+    return check_launch("slot_mix_residual_kernel");
+}

@@ -36,6 +36,7 @@ PROTOTYPES = {
     "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
     "rlm_selftest_bounded_wait": [_P, _L, _P, _P],
     "rlm_relation_select_multi_rows": [_P] * 21 + [_L] * 3 + [_I] * 14 + [_P, _P],
+    "rlm_slot_mix_residual": [_P] * 5 + [_I] * 3 + [_P],
     "rlm_relation_layer_tail_supported": [_I] * 7,
     "rlm_relation_layer_tail": [_P] * 11 + [_F, _P, _P, _P, _P, _F, _P, _P, _P] + [_I] * 8 + [_P, _P],
 }

@@ -115,3 +115,33 @@ def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_
             anchor_query.new_empty((rows, slots, k), dtype=torch.int32),
             anchor_query.new_empty((rows, slots, k), dtype=f32),
             anchor_query.new_empty((rows, slots, k), dtype=torch.bool))
+
+
+@torch.library.custom_op("relation_lm::slot_mix_residual", mutates_args=("hidden",), device_types="cuda")
+def slot_mix_residual(slot_context: Tensor, anchor_active: Tensor, slot_weight: Tensor, gate: Tensor,
+                      hidden: Tensor) -> None:
+    """Last step of a multi-anchor layer (extension; multi_relation_blocks.py:170-178 of the reference):
+    ``hidden += gate * sum_s w[:, s] * slot_context[:, s]`` with ``w`` the slot weights
+    (``slot_weight [S]``, the softmax of the learned logits) renormalised over each row's active
+    slots.  ``slot_context [N, S, d]``, ``hidden [N, d]``, ``gate`` (one element): fp32;
+    ``anchor_active [N, S]`` bool."""
+    device = _abi.require_cuda_contiguous(slot_context=slot_context, anchor_active=anchor_active,
+                                          slot_weight=slot_weight, gate=gate, hidden=hidden)
+    rows, slots, dim = slot_context.shape
+    if anchor_active.shape != (rows, slots) or slot_weight.numel() != slots or hidden.shape != (rows, dim) \
+            or gate.numel() != 1:
+        raise ValueError("slot_mix_residual: inconsistent shapes")
+    if anchor_active.dtype not in (torch.bool, torch.uint8):
+        raise ValueError("anchor_active must be bool")
+    for name, t in (("slot_context", slot_context), ("slot_weight", slot_weight), ("gate", gate), ("hidden", hidden)):
+        if t.dtype != torch.float32:
+            raise ValueError(f"{name} must be float32")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_slot_mix_residual(
+            _abi.ptr(slot_context), _abi.ptr(anchor_active.view(torch.uint8)), _abi.ptr(slot_weight), _abi.ptr(gate),
+            _abi.ptr(hidden), rows, slots, dim, _abi.stream_ptr(device)))
+
+
+@slot_mix_residual.register_fake
+def _(slot_context, anchor_active, slot_weight, gate, hidden):
+    return None

@@ -143,6 +143,20 @@ def stack_inputs(case) -> dict[str, torch.Tensor]:
             "boundaries": torch.randint(0, case["boundary_vocab"], (B, T), generator=g)}
 
 
+def multi_stack_inputs(case) -> dict[str, torch.Tensor]:
+    g = _gen(case["seed"])
+    B, T, d = case["batch"], case["context"], case["d_model"]
+    return {"hidden": torch.randn(B, T, d, generator=g), "memory": torch.randn(B, T, d, generator=g)}
+
+
+def multi_stack_config_kwargs(case) -> dict:
+    """Keyword arguments of ``MultiAnchorConfig`` for a multi-anchor stack case (full-history
+    window, no remote blocks: routed selection equals dense selection)."""
+    return dict(d_model=case["d_model"], relation_dim=case["relation_dim"], anchors_per_block=case["anchors"],
+                partners_per_anchor=case["partners"], depth=case["depth"], max_context=case["context"],
+                block_size=case["block_size"], local_window=case["context"], top_blocks=0)
+
+
 def stack_config_kwargs(case) -> dict:
     """Keyword arguments of ``RoutedRelationConfig`` for a stack case: the local window covers the
     whole history and no remote block is used, so routed selection equals dense selection."""
@@ -152,7 +166,7 @@ def stack_config_kwargs(case) -> dict:
                 k_max=case["k_out"])
 
 
-_BUILDERS = {"select": select_inputs, "stack": stack_inputs, "router": router_inputs,
+_BUILDERS = {"select": select_inputs, "stack": stack_inputs, "multi_stack": multi_stack_inputs, "router": router_inputs,
              "router_sequence": router_sequence_inputs, "reduce": reduce_inputs,
              "norm_reduce": norm_reduce_inputs, "packed": packed_inputs,
              "multi_anchor": multi_anchor_inputs}
@@ -248,6 +262,10 @@ def all_cases() -> dict[str, dict]:
     c["stack_single_layer_d256"] = {"kind": "stack", "seed": 7010, "model_seed": 1001, "batch": 1,
                                     "context": 128, "d_model": 256, "layers": 1, "block_size": 16,
                                     "k_out": 8, "vocab": 300, "boundary_vocab": 16}
+    # multi-anchor layers against the reference's dense MultiAnchorRelationBlock / RelationBlockStack
+    c["multi_stack_dense"] = {"kind": "multi_stack", "seed": 7100, "model_seed": 7101, "batch": 2, "context": 32,
+                              "d_model": 64, "relation_dim": 64, "anchors": 4, "partners": 4, "depth": 2,
+                              "block_size": 8}
     c["packed_d576"] = {"kind": "packed", "seed": 5000, "rows": 8, "d_model": 576}
     c["packed_d512"] = {"kind": "packed", "seed": 5001, "rows": 3, "d_model": 512}
     return c

@@ -296,7 +296,45 @@ def run_stack(case, x):
             "layers": layers, "output": output}
 
 
-RUNNERS = {"select": run_select, "stack": run_stack, "router": run_router, "router_sequence": run_router_sequence,
+def _multi_anchor_module():
+    import importlib.util
+
+    name = "b200_multi_anchor"
+    if name in sys.modules:
+        return sys.modules[name]
+    path = HERE.parents[1] / "relation-lm_b200" / "relation_lm" / "inference" / "multi_anchor.py"
+    spec = importlib.util.spec_from_file_location(name, path)
+    module = importlib.util.module_from_spec(spec)
+    sys.modules[name] = module
+    spec.loader.exec_module(module)
+    return module
+
+
+def run_multi_stack(case, x):
+    """The reference's dense ``RelationBlockStack`` (models/multi_relation_blocks.py:190-207) with the
+    weights of this repository's seeded ``MultiAnchorRoutedStack`` (same parameter names)."""
+    from relation_lm.models.multi_relation_blocks import MultiRelationBlockConfig, RelationBlockStack
+
+    ma = _multi_anchor_module()
+    cfg = ma.MultiAnchorConfig(**cases.multi_stack_config_kwargs(case))
+    mine = ma.MultiAnchorRoutedStack(cfg, seed=case["model_seed"]).eval()
+    ref_cfg = MultiRelationBlockConfig(d_model=cfg.d_model, gate_dim=cfg.gate_dim, relation_dim=cfg.relation_dim,
+                                       ff_mult=cfg.ff_mult, anchors_per_block=cfg.anchors_per_block,
+                                       partners_per_anchor=cfg.partners_per_anchor)
+    theirs = RelationBlockStack(ref_cfg, cfg.depth).eval()
+    for a, b in zip(mine.blocks, theirs.blocks):
+        b.load_state_dict({k: v for k, v in a.state_dict().items() if not k.startswith("router.")})
+    theirs.final_norm.load_state_dict(mine.final_norm.state_dict())
+    with torch.no_grad():
+        output, diagnostics = theirs(x["hidden"], x["memory"])
+    layers = [{"anchor_index": d["anchor_index"].to(torch.int32), "anchor_active": d["anchor_active"],
+               "partner_index": d["partner_index"].to(torch.int32), "partner_active": d["partner_active"],
+               "partner_weight": d["partner_weight"], "slot_weight": d["slot_weight"],
+               "relation_context": d["relation_context"]} for d in diagnostics]
+    return {"model_sha256": cases.checksum(dict(mine.state_dict())), "layers": layers, "output": output}
+
+
+RUNNERS = {"select": run_select, "stack": run_stack, "multi_stack": run_multi_stack, "router": run_router, "router_sequence": run_router_sequence,
            "reduce": run_reduce, "norm_reduce": run_norm_reduce, "packed": run_packed,
            "multi_anchor": run_multi_anchor}
 

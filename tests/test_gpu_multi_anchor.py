@@ -87,3 +87,121 @@ def test_routed_multi_anchor_matches_oracle_composition(strict):
         assert torch.all(partners <= row_pos[r])
         assert not set(partners.tolist()) & set(chosen.tolist())
     assert_status_clear()
+
+
+def _check_layer_against_port(runner, port, layer, kept, rows, hidden_before, hidden_after):
+    """One layer of the GPU pass, kernel by kernel on the GPU's own inputs, for the query rows `rows`."""
+    from gpu_util import assert_rel_close, assert_scores_equal
+
+    cfg = runner.config
+    S, K, d = cfg.anchors_per_block, cfg.partners_per_anchor, cfg.d_model
+    state = {k: v.float().cpu() for k, v in kept["state"].items() if k != "packed"}
+    row_batch, row_pos = kept["row_batch"].cpu()[rows], kept["row_position"].cpu()[rows]
+    q = kept["query"].cpu()[rows]
+    anchors, active, partners, scores = port.select(layer, q, state, row_batch, row_pos)
+    assert torch.equal(kept["anchor"].cpu()[rows], anchors)
+    assert torch.equal(kept["anchor_active"].cpu()[rows], active)
+    assert torch.equal(kept["partner"].cpu()[rows], partners)
+    assert_scores_equal(kept["partner_score"][rows.cuda()], scores)
+    w = port.layers[layer]
+    n = rows.numel()
+    pair_index = (rows[:, None] * S + torch.arange(S)[None, :]).reshape(-1)            # rows of the [N * S, ...] tensors
+    pair_rows = row_batch.repeat_interleave(S)
+    want_hidden, _ = oracle.relation_hidden(state["expanded_cache"], state["operand_cache"], anchors.view(n * S),
+                                            partners.view(n * S, K), w["product_weight"], row_batch=pair_rows,
+                                            row_pos=row_pos.repeat_interleave(S))
+    live = scores.view(n * S, K) > -torch.inf
+    got_hidden = kept["hidden_rel"][pair_index.cuda()].cpu()
+    assert_rel_close(got_hidden[live], want_hidden[live], 1e-2, "relation hidden")
+    got_raw = kept["raw"][pair_index.cuda()].cpu()
+    assert_rel_close(got_raw[live], (oracle.linear(got_hidden, w["w2"]) + w["b2"])[live], 1e-2, "second layer")
+    no_limit = torch.full((n * S,), (1 << 30) - 2, dtype=torch.int32)
+    want_ctx = oracle.relation_norm_reduce(got_raw, scores.view(n * S, K), w["relation_norm_w"], w["relation_norm_b"],
+                                           0, cfg.norm_eps, row_pos=no_limit).view(n, S, d)
+    assert_rel_close(kept["slot_context"][rows.cuda()], want_ctx, 1e-4, "slot context")
+    weight = w["slot_weight"][None, :] * active
+    weight = weight / weight.sum(-1, keepdim=True).clamp_min(1.0e-9)
+    want_after = hidden_before[rows] + w["gate"] * (want_ctx * weight[..., None]).sum(1)
+    assert_rel_close(hidden_after[rows], want_after, 1e-4, "residual")
+
+
+def test_routed_multi_anchor_stack_matches_cpu_port():
+    """Depth-2 routed multi-anchor stack (4 slots x 4 partners, block 32, window 64, 3 remote blocks,
+    bf16) on 2 sequences of 256: state bit-equal to the port's, every kernel of every layer
+    against the port on the GPU pass's own inputs, all rows."""
+    from oracle.multi_anchor_port import OracleMultiAnchor
+    from relation_lm.inference.multi_anchor import MultiAnchorConfig, MultiAnchorPrefill, MultiAnchorRoutedStack
+
+    cfg = MultiAnchorConfig(d_model=128, depth=2, max_context=256, block_size=32, local_window=64, top_blocks=3)
+    stack = MultiAnchorRoutedStack(cfg, seed=4405)
+    runner = MultiAnchorPrefill(stack, "cuda", torch.bfloat16)
+    port = OracleMultiAnchor(stack, torch.bfloat16)
+    g = torch.Generator().manual_seed(4406)
+    B, T, d = 2, cfg.max_context, cfg.d_model
+    hidden = torch.randn(B, T, d, generator=g)
+    memory = torch.randn(B, T, d, generator=g).bfloat16()
+    rows = torch.arange(B * T)
+    current = hidden.cuda()
+    for layer in range(cfg.depth):
+        state = runner.build_state(layer, memory.cuda())
+        from gpu_util import assert_rel_close
+        want_packed = oracle.linear(memory.view(B * T, d), port.layers[layer]["w_memory"]).view(B, T, -1)
+        assert_rel_close(state["packed"], want_packed, 1e-2, "memory-side projection")
+        # everything downstream of that projection, from the GPU's own projection: bit for bit
+        want_state = port.build_state(layer, memory.float(), packed=state["packed"].cpu())
+        for name, want in want_state.items():
+            if name == "expanded_cache":
+                assert_rel_close(state[name], want, 1e-2, name)
+            else:
+                assert torch.equal(state[name].float().cpu(), want), (layer, name)
+        before = current.clone()
+        kept = {"state": state}
+        runner.forward_layer(layer, current, state, kept)
+        _check_layer_against_port(runner, port, layer, kept, rows, before.view(B * T, d).cpu(),
+                                  current.view(B * T, d).cpu())
+    assert_status_clear()
+
+
+def test_multi_anchor_stack_configuration_at_full_shape():
+    """The multi-anchor configuration itself — depth 4, batch 16, context 2048, d_model 512, 4 anchors
+    x 4 partners, block 32, 3 remote blocks, bf16, N(0, 1) inputs: size-independent properties on all
+    32 768 rows of every layer (distinct causal anchors, no anchor in any partner set, activity
+    rules), and 1 500 sampled rows of the first and last layer against the port."""
+    from oracle.multi_anchor_port import OracleMultiAnchor
+    from relation_lm.inference.multi_anchor import MultiAnchorConfig, MultiAnchorPrefill, MultiAnchorRoutedStack
+
+    cfg = MultiAnchorConfig()
+    assert (cfg.depth, cfg.max_context, cfg.d_model, cfg.anchors_per_block, cfg.partners_per_anchor,
+            cfg.block_size, cfg.top_blocks) == (4, 2048, 512, 4, 4, 32, 3)
+    stack = MultiAnchorRoutedStack(cfg, seed=1004)
+    runner = MultiAnchorPrefill(stack, "cuda", torch.bfloat16)
+    port = OracleMultiAnchor(stack, torch.bfloat16)
+    g = torch.Generator().manual_seed(1004)
+    B, T, d, S = 16, cfg.max_context, cfg.d_model, cfg.anchors_per_block
+    hidden = torch.randn(B, T, d, generator=g).cuda()
+    memory = torch.randn(B, T, d, generator=g).bfloat16().cuda()
+    sample = torch.randint(0, B * T, (1500,), generator=g).unique()
+    current = hidden.clone()
+    for layer in range(cfg.depth):
+        state = runner.build_state(layer, memory)
+        before = current.clone()
+        kept = {"state": state}
+        runner.forward_layer(layer, current, state, kept)
+        anchor, active = kept["anchor"].cpu().long(), kept["anchor_active"].cpu()
+        partner, pactive = kept["partner"].cpu().long(), kept["partner_active"].cpu()
+        rp = kept["row_position"].cpu().long()
+        assert torch.equal(active, torch.arange(S)[None, :] <= rp[:, None])           # slot s active iff s <= t
+        assert bool((anchor <= rp[:, None]).all()) and bool((anchor[~active] == 0).all())
+        masked = torch.where(active, anchor, -1 - torch.arange(S)[None, :])            # inactive slots: unique dummies
+        ordered = masked.sort(-1).values
+        assert bool((ordered[:, 1:] != ordered[:, :-1]).all())                         # distinct anchors
+        assert bool((partner <= rp[:, None, None]).all())
+        clash = (partner[:, :, :, None] == masked[:, None, None, :]) & pactive[..., None]
+        assert not bool(clash.any())                                                   # no anchor in any partner set
+        assert not bool(pactive[~active].any())
+        if layer in (0, cfg.depth - 1):
+            _check_layer_against_port(runner, port, layer, kept, sample, before.view(B * T, d).cpu(),
+                                      current.view(B * T, d).cpu())
+        del kept, state
+    assert torch.isfinite(current).all()
+    assert_status_clear()
