@@ -461,6 +461,24 @@ int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token
                      int rows, int vocab, int dtype, void* stream);
 
 /*
+ * Projection of at most 16 rows on the CUDA cores (extension; the F.linear of one decode position,
+ * src/relation_lm/inference/packed_cache.py:52-57, and the output heads of
+ * src/relation_lm/models/relation_lm.py:121-124, 204-207):
+ *   out[m, n] = sum_k x[m, k] * weight[n, k] (+ bias[n])
+ *   x [rows, d] (row stride in ELEMENTS), weight [n, d], out [rows, n]: bfloat16 or float16 (dtype),
+ *   bias [n] f32 optional; d = 256 or 512 (RLM_ERR_UNSUPPORTED otherwise: use rlm_packed_projection).
+ * Greedy head (vocab > 0): also next_token[m] = arg-max of the rounded out[m, 0:vocab] (lowest index
+ * on ties) as int64 and, with `position`, the device position scalar advanced by one — what
+ * rlm_greedy_token does in a launch of its own.  `argmax_scratch` is caller-owned device memory of
+ * rlm_skinny_argmax_scratch_bytes() bytes, ZERO before the first call; every launch leaves it
+ * zero.  Launches that share it must be ordered on a stream.
+ */
+int64_t rlm_skinny_argmax_scratch_bytes(void);
+int rlm_skinny_projection(const void* x, int64_t x_row_stride, const void* weight, const float* bias,
+                          void* out, int rows, int d_in, int n_out, int dtype, int vocab,
+                          void* argmax_scratch, int64_t* next_token, int64_t* position, void* stream);
+
+/*
  * Routed multi-anchor selection, all slots of a query row in one launch (extension).  The
  * reference's multi-anchor layer is dense (src/relation_lm/models/multi_relation_blocks.py:69-148);
  * this applies its rules inside each slot's routed candidate set (local window + that slot's

@@ -24,7 +24,9 @@ from torch import Tensor
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import (decode_embed_norm, greedy_token, layer_norm_cast,
-                                                    packed_projection, packed_projection_slices)
+                                                    packed_projection, packed_projection_slices,
+                                                    skinny_argmax_scratch_bytes, skinny_projection,
+                                                    skinny_projection_greedy, skinny_projection_supported)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
                                                  relation_layer_tail, relation_layer_tail_supported,
                                                  relation_hidden_cached_out,
@@ -103,6 +105,12 @@ class StatefulDecoder:
             self.fused_query = False
         if self.fused_query or self.layer_tail:
             self.query = zeros(B, n_query)
+        # Projections of a handful of rows stream their weights through the CUDA cores (no tensor-memory
+        # set-up); the head's launch then also takes the greedy arg-max and the position increment.
+        self.skinny = self.fused and skinny_projection_supported(B, cfg.d_model, dtype)
+        self._project = skinny_projection if self.skinny else packed_projection
+        if self.skinny:
+            self.argmax_scratch = torch.zeros(skinny_argmax_scratch_bytes(), device=self.device, dtype=torch.uint8)
         if self.fused:
             self.relation_hidden = zeros(B, cfg.k_max, H)
             self.normalized = zeros(B, cfg.d_model)             # LayerNorm'd input of the next projection
@@ -150,6 +158,8 @@ class StatefulDecoder:
             return token_logits.argmax(-1)
         previous = _abi.set_programmatic_launch(self.programmatic_launch)
         try:
+            if self.skinny:
+                return self._step_fused(tokens, boundaries, False, advance=False, greedy=True)
             self._step_fused(tokens, boundaries, False, advance=False)
             return greedy_token(self.last_logits, self.config.vocab_size, self.position)
         finally:
@@ -195,7 +205,8 @@ class StatefulDecoder:
         pos.add_(1)
         return token_logits, boundary_logits
 
-    def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True):
+    def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True,
+                    greedy: bool = False):
         """The same step with the elementwise glue folded into the library's kernels:
         2 launches per layer with the single-launch relation tail (select, tail), otherwise up to 5
         (query projection, select, relation hidden, second MLP layer GEMM, norm-reduce + residual +
@@ -209,7 +220,7 @@ class StatefulDecoder:
                                    w["position_embedding"], pos, self.input_scale,
                                    w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
                                    w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
-        packed = packed_projection(self.memory_normalized, w["w_packed"])
+        packed = self._project(self.memory_normalized, w["w_packed"])
         sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
                             self.partner_anchor_cache, *self.router_caches, *self.router_stats,
                             w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
@@ -229,7 +240,7 @@ class StatefulDecoder:
             # layer 0 projects the embedding's normalised rows; later layers find their queries
             # written by the previous layer's norm-reduce when that fusion is on
             q = self.query if ((self.fused_query or self.layer_tail) and l > 0) \
-                else packed_projection(self.normalized, w["w_query"][l])
+                else self._project(self.normalized, w["w_query"][l])
             anchor, _, partner, partner_score = relation_select_packed(
                 q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
                 self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
@@ -299,7 +310,13 @@ class StatefulDecoder:
             if keep_selection:
                 self.last_selection.append((anchor, partner))
         self.last_final = self.normalized
-        logits = packed_projection(self.normalized, self.head_weight, self.head_bias)
+        if greedy:
+            # head projection + greedy arg-max + position increment in one launch
+            logits, chosen = skinny_projection_greedy(self.normalized, self.head_weight, self.head_bias,
+                                                      cfg.vocab_size, self.argmax_scratch, pos)
+            self.last_logits = logits
+            return chosen
+        logits = self._project(self.normalized, self.head_weight, self.head_bias)
         self.last_logits = logits                        # [B, padded vocab + boundary vocab]
         token_logits = logits[:, :cfg.vocab_size]
         boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size]

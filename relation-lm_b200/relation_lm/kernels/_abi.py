@@ -37,6 +37,7 @@ PROTOTYPES = {
     "rlm_selftest_bounded_wait": [_P, _L, _P, _P],
     "rlm_relation_select_multi_rows": [_P] * 21 + [_L] * 3 + [_I] * 14 + [_P, _P],
     "rlm_slot_mix_residual": [_P] * 5 + [_I] * 3 + [_P],
+    "rlm_skinny_projection": [_P, _L, _P, _P, _P] + [_I] * 5 + [_P] * 4,
     "rlm_relation_layer_tail_supported": [_I] * 7,
     "rlm_relation_layer_tail": [_P] * 11 + [_F, _P, _P, _P, _P, _F, _P, _P, _P] + [_I] * 8 + [_P, _P],
 }
@@ -55,6 +56,8 @@ def _load() -> ctypes.CDLL:
     lib.rlm_abi_version.restype = ctypes.c_int
     lib.rlm_last_error.restype = ctypes.c_char_p
     lib.rlm_launch_count.restype = ctypes.c_int64
+    lib.rlm_skinny_argmax_scratch_bytes.argtypes = []
+    lib.rlm_skinny_argmax_scratch_bytes.restype = ctypes.c_int64
     lib.rlm_relation_tail_scratch_bytes.argtypes = [_I, _I, _I]
     lib.rlm_relation_tail_scratch_bytes.restype = ctypes.c_int64
     if lib.rlm_abi_version() != ABI_VERSION:

@@ -222,3 +222,71 @@ def _greedy_token(logits: Tensor, vocab: int, position: Tensor | None) -> Tensor
 @_greedy_token.register_fake
 def _(logits, vocab, position):
     return logits.new_empty((logits.size(0),), dtype=torch.int64)
+
+
+def skinny_projection_supported(rows: int, d_in: int, dtype: torch.dtype) -> bool:
+    """Whether ``skinny_projection`` serves these sizes (a handful of rows, a weight row in registers)."""
+    return 1 <= rows <= 16 and d_in in (256, 512) and dtype in (torch.bfloat16, torch.float16)
+
+
+@torch.library.custom_op("relation_lm::skinny_projection", mutates_args=(), device_types="cuda")
+def skinny_projection(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
+    """``x [rows <= 16, d] @ weight [n, d].T (+ bias)`` on the CUDA cores (extension): for a decode
+    batch the product is a stream of the weight matrix, read once by whole warps with no tensor-memory
+    or tensor-map set-up.  Same contract as ``packed_projection``; ``d`` must be 256 or 512."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(weight=weight, bias=bias)
+    if weight.dim() != 2 or weight.size(1) != x.size(1) or x.dtype != weight.dtype:
+        raise ValueError("weight must be [n_out, d_in] with the dtype of x")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != weight.size(0)):
+        raise ValueError("bias must be float32 [n_out]")
+    out = torch.empty((x.size(0), weight.size(0)), device=device, dtype=x.dtype)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_skinny_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(bias), _abi.ptr(out), x.size(0), x.size(1),
+            weight.size(0), _abi.code(x), 0, None, None, None, _abi.stream_ptr(device)))
+    return out
+
+
+@skinny_projection.register_fake
+def _(x, weight, bias=None):
+    return x.new_empty((x.size(0), weight.size(0)))
+
+
+@torch.library.custom_op("relation_lm::skinny_projection_greedy", mutates_args=("scratch", "position"),
+                         device_types="cuda")
+def skinny_projection_greedy(x: Tensor, weight: Tensor, bias: Tensor | None, vocab: int, scratch: Tensor,
+                             position: Tensor | None) -> tuple[Tensor, Tensor]:
+    """The output head of a greedy decode step in one launch (extension): ``logits = x @ weight.T + bias``
+    and ``next_token = logits[:, :vocab].argmax(-1)`` (lowest index on ties; int64), and with ``position``
+    the device position advanced by one.  ``scratch``: a zeroed uint8 tensor of
+    ``skinny_argmax_scratch_bytes()`` bytes, allocated once by the caller and left zero by every launch."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(weight=weight, bias=bias, scratch=scratch)
+    if weight.dim() != 2 or weight.size(1) != x.size(1) or x.dtype != weight.dtype:
+        raise ValueError("weight must be [n_out, d_in] with the dtype of x")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != weight.size(0)):
+        raise ValueError("bias must be float32 [n_out]")
+    if scratch.dtype != torch.uint8 or scratch.numel() < skinny_argmax_scratch_bytes():
+        raise ValueError("scratch must be a uint8 tensor of skinny_argmax_scratch_bytes() bytes")
+    if not 1 <= vocab <= weight.size(0):
+        raise ValueError("vocab must lie within the projection's outputs")
+    if position is not None:
+        _abi.require_position(position, device)
+    out = torch.empty((x.size(0), weight.size(0)), device=device, dtype=x.dtype)
+    next_token = torch.empty((x.size(0),), device=device, dtype=torch.int64)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_skinny_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(bias), _abi.ptr(out), x.size(0), x.size(1),
+            weight.size(0), _abi.code(x), int(vocab), _abi.ptr(scratch), _abi.ptr(next_token), _abi.ptr(position),
+            _abi.stream_ptr(device)))
+    return out, next_token
+
+
+@skinny_projection_greedy.register_fake
+def _(x, weight, bias, vocab, scratch, position):
+    return x.new_empty((x.size(0), weight.size(0))), x.new_empty((x.size(0),), dtype=torch.int64)
+
+
+def skinny_argmax_scratch_bytes() -> int:
+    return int(_abi.LIB.rlm_skinny_argmax_scratch_bytes())

@@ -36,7 +36,7 @@ def test_binding_prototypes_cover_the_header():
     from relation_lm.kernels import _abi
 
     bound = set(_abi.PROTOTYPES) | {"rlm_abi_version", "rlm_last_error", "rlm_launch_count",
-                                    "rlm_relation_tail_scratch_bytes"}
+                                    "rlm_relation_tail_scratch_bytes", "rlm_skinny_argmax_scratch_bytes"}
     assert set(_declared_symbols()) <= bound
 
 

