@@ -1,18 +1,22 @@
-// Projection of a handful of rows (decode batches: at most 16) on the CUDA cores (sm_100a):
+// Projection of a handful of rows (decode batches: at most 16) without tensor memory (sm_100a):
 //   out[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n])
 // for 16-bit x [M, d], w [N, d] with fp32 accumulation.  With so few rows the product is a stream
-// of the weight matrix: no tensor-memory allocation, no tensor map, no shared-memory ring — every
-// warp reads whole weight rows with 16-byte loads (requested before the dependency wait, they
-// depend on no earlier kernel), multiplies them with the rows of x held as fp32 in shared memory
-// and folds the 32 lanes' partial sums of (columns x rows) = 32 values with a halving butterfly
-// (31 shuffles for all of them together).
+// of the weight matrix, so the kernel is built around that stream: no tensor-memory allocation,
+// no tensor map, no shared-memory ring.  A warp owns eight output columns; lane (n = lane / 4,
+// part = lane % 4) reads 16 bytes of weight row n per step of 32 k-values — 64 contiguous bytes
+// per row and instruction, all of a warp's loads requested up front, before the dependency wait
+// (weights depend on no earlier kernel).  The arithmetic is the warp-level tensor instruction
+// mma.sync.m16n8k16 (rows of x, padded to 16, as the A operand from shared memory): because a dot
+// product does not care in which order k is visited, a lane's eight consecutive k-values feed two
+// instructions directly, with the rows of x read at the matching k — no transposition, no
+// shuffle reduction, and each lane ends with finished outputs.
 //
-// Optional greedy head (the `logits.argmax(-1)` and `position += 1` that close a decode step,
+// Optional greedy head (the `logits.argmax(-1)` and `position += 1` that close a decode step;
 // src/relation_lm/models/relation_lm.py:204-207 of the reference project gives the heads): every
 // CTA folds its columns below `vocab` into one 64-bit key per row (rounded logit, lowest index on
-// ties) with atomicMax; the CTA that finishes last turns the keys into token ids, clears keys and
-// counter for the next launch and advances the position.  The maximum does not depend on the
-// order of the atomics, so the result is deterministic.
+// ties), one atomicMax per row and CTA; the CTA that finishes last turns the keys into token ids,
+// clears keys and counter for the next launch and advances the position.  A maximum does not
+// depend on the order of the atomics: the result is deterministic.
 //
 // Stands where the reference calls F.linear on one position's rows
 // (src/relation_lm/inference/packed_cache.py:52-57; the heads of relation_lm.py:121-124).
@@ -24,6 +28,7 @@ namespace {
 
 constexpr int kSkThreads = 256;
 constexpr int kSkWarps = kSkThreads / 32;
+constexpr int kSkMaxRows = 16;
 
 struct SkinnyArgs {
     const void* x;            // [M, d] 16-bit, row stride in elements
@@ -36,100 +41,80 @@ struct SkinnyArgs {
     int64_t* position;        // optional: += 1
     int64_t x_stride;
     int rows, d, n, vocab, dtype;
-    int groups;               // column groups of kCols columns in total
+    int groups;               // groups of eight output columns
 };
 
-// kRows: rows of x padded to 8 or 16; kCols = 32 / kRows columns per warp pass; kCpl: 16-byte
-// chunks of a weight row per lane (d = 256 * kCpl).
-template <int kRows, int kCpl, bool kBf16>
+template <bool kBf16>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    if (kBf16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// kSteps = d / 32 steps of 32 k-values; kUpper: rows 8..15 of x exist (more than eight rows).
+template <int kSteps, bool kUpper, bool kBf16>
 __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const SkinnyArgs a) {
-    constexpr int kCols = 32 / kRows;
-    extern __shared__ __align__(16) float xs[];               // [kRows][d]
+    // rows of x in the operands' own 16-bit format, each row padded by 64 bytes: the two rows a
+    // quarter warp reads (64 bytes of each) lie in different halves of the banks
+    extern __shared__ __align__(16) unsigned char xs[];
+    __shared__ unsigned long long cta_best[kSkMaxRows];
     __shared__ unsigned int last_flag;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int dtype = kBf16 ? static_cast<int>(RLM_BF16) : static_cast<int>(RLM_F16);
     const int d = a.d;
+    const uint32_t row_bytes = static_cast<uint32_t>(d) * 2u + 64u;
+    const int n_row = lane >> 2, part = lane & 3;
     const int warps_total = gridDim.x * kSkWarps;
-    const int first = blockIdx.x * kSkWarps + warp;
+    int g = blockIdx.x * kSkWarps + warp;
 
-    // the first group's weight chunks, requested before anything an earlier kernel produced
-    uint4 wreg[kCols][kCpl];
-    auto load_group = [&](int g) {
+    // this warp's first eight weight rows, requested before anything an earlier kernel produced
+    uint4 wreg[kSteps];
+    auto load_group = [&](int group) {
+        const int col = group * 8 + n_row;
+        const uint4* wrow = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.w) +
+                                                           static_cast<size_t>(col < a.n ? col : a.n - 1) * d);
 #pragma unroll
-        for (int c = 0; c < kCols; ++c) {
-            const int col = g * kCols + c;
-            const uint4* wrow = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.w) +
-                                                               static_cast<size_t>(col < a.n ? col : a.n - 1) * d);
-#pragma unroll
-            for (int i = 0; i < kCpl; ++i) wreg[c][i] = wrow[lane + 32 * i];
-        }
+        for (int s = 0; s < kSteps; ++s) wreg[s] = wrow[4 * s + part];
     };
-    if (first < a.groups) load_group(first);
+    if (g < a.groups) load_group(g);
+    if (tid < kSkMaxRows) cta_best[tid] = 0ull;
     griddep_sync();
-    // rows of x as fp32 (rows beyond M: zeros)
-    for (int i = tid; i < kRows * (d / 8); i += kSkThreads) {
+    for (int i = tid; i < (kUpper ? 16 : 8) * (d / 8); i += kSkThreads) {
         const int m = i / (d / 8), c = i - m * (d / 8);
-        float f[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        uint4 v = make_uint4(0, 0, 0, 0);
         if (m < a.rows)
-            load8(static_cast<const uint16_t*>(a.x) + static_cast<size_t>(m) * a.x_stride, 8 * c, dtype, f);
-        float4* dst = reinterpret_cast<float4*>(xs + m * d + 8 * c);
-        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+            v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.x) + static_cast<size_t>(m) * a.x_stride + 8 * c);
+        *reinterpret_cast<uint4*>(xs + m * row_bytes + 16 * c) = v;
     }
     __syncthreads();
 
-    unsigned long long best = 0ull;                             // this lane's (row, column slot) arg-max key
-    for (int g = first; g < a.groups; g += warps_total) {
-        float acc[kCols][kRows];
+    unsigned long long best_lo = 0ull, best_hi = 0ull;         // arg-max keys of rows n_row and n_row + 8
+    for (; g < a.groups; g += warps_total) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const unsigned char* xlo = xs + n_row * row_bytes + 16 * part;
+        const unsigned char* xhi = xlo + 8 * row_bytes;
 #pragma unroll
-        for (int c = 0; c < kCols; ++c)
-#pragma unroll
-            for (int m = 0; m < kRows; ++m) acc[c][m] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kCpl; ++i) {
-            float wf[kCols][8];
-#pragma unroll
-            for (int c = 0; c < kCols; ++c) {
-                Raw8 r;
-                r.lo = wreg[c][i];
-                r.hi = make_uint4(0, 0, 0, 0);
-                convert8(r, dtype, wf[c]);
-            }
-#pragma unroll
-            for (int m = 0; m < kRows; ++m) {
-                const float4* xp = reinterpret_cast<const float4*>(xs + m * d + 8 * (lane + 32 * i));
-                const float4 x0 = xp[0], x1 = xp[1];
-#pragma unroll
-                for (int c = 0; c < kCols; ++c) {
-                    float s = acc[c][m];
-                    s = fmaf(wf[c][0], x0.x, s); s = fmaf(wf[c][1], x0.y, s); s = fmaf(wf[c][2], x0.z, s); s = fmaf(wf[c][3], x0.w, s);
-                    s = fmaf(wf[c][4], x1.x, s); s = fmaf(wf[c][5], x1.y, s); s = fmaf(wf[c][6], x1.z, s); s = fmaf(wf[c][7], x1.w, s);
-                    acc[c][m] = s;
-                }
-            }
+        for (int s = 0; s < kSteps; ++s) {
+            // eight consecutive k-values of weight row n_row, and of rows n_row / n_row + 8 of x at the same k
+            const uint4 lo = *reinterpret_cast<const uint4*>(xlo + 64 * s);
+            uint4 hi = make_uint4(0, 0, 0, 0);
+            if (kUpper) hi = *reinterpret_cast<const uint4*>(xhi + 64 * s);
+            mma16816<kBf16>(acc, lo.x, hi.x, lo.y, hi.y, wreg[s].x, wreg[s].y);
+            mma16816<kBf16>(acc, lo.z, hi.z, lo.w, hi.w, wreg[s].z, wreg[s].w);
         }
+        const int group = g;
         const int next = g + warps_total;
-        if (next < a.groups) load_group(next);                  // the next group's weights fly during the reduction
-        // halving butterfly over the 32 (column, row) sums: lane l ends with the total of element l
-        float v[32];
+        if (next < a.groups) load_group(next);
+        // this lane holds out[n_row][2 part, 2 part + 1] and out[n_row + 8][same columns]
 #pragma unroll
-        for (int c = 0; c < kCols; ++c)
-#pragma unroll
-            for (int m = 0; m < kRows; ++m) v[c * kRows + m] = acc[c][m];
-#pragma unroll
-        for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
-            const bool upper = (lane & off) != 0;
-#pragma unroll
-            for (int i = 0; i < n / 2; ++i) {
-                const float keep = upper ? v[i + n / 2] : v[i];
-                const float send = upper ? v[i] : v[i + n / 2];
-                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-            }
-        }
-        const int c = lane / kRows, m = lane - c * kRows;
-        const int col = g * kCols + c;
-        if (col < a.n && m < a.rows) {
-            float value = v[0] + (a.bias ? a.bias[col] : 0.0f);
+        for (int e = 0; e < 4; ++e) {
+            const int m = n_row + (e >> 1) * 8, col = group * 8 + 2 * part + (e & 1);
+            if ((e >> 1) && !kUpper) continue;
+            if (m >= a.rows || col >= a.n) continue;
+            float value = acc[e] + (a.bias ? a.bias[col] : 0.0f);
             uint16_t bits;
             if (kBf16) { __nv_bfloat16 h = __float2bfloat16_rn(value); bits = *reinterpret_cast<uint16_t*>(&h); value = __bfloat162float(h); }
             else { __half h = __float2half_rn(value); bits = *reinterpret_cast<uint16_t*>(&h); value = __half2float(h); }
@@ -137,18 +122,26 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
             if (a.keys && col < a.vocab) {
                 const unsigned long long key = (static_cast<unsigned long long>(float_key(value + 0.0f)) << 32) |
                                                (0xffffffffu - static_cast<unsigned int>(col));
-                best = key > best ? key : best;
+                if (e >> 1) best_hi = key > best_hi ? key : best_hi;
+                else best_lo = key > best_lo ? key : best_lo;
             }
         }
     }
     if (a.keys) {
-        // the lanes of one row (same m, different column slot) first, then one atomic per row and warp
+        // the four lanes of a row, then the CTA's warps through shared memory, then one atomic per row
 #pragma unroll
-        for (int off = kRows; off < 32; off <<= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
-            best = other > best ? other : best;
+        for (int off = 1; off < 4; off <<= 1) {
+            const unsigned long long o_lo = __shfl_xor_sync(0xffffffffu, best_lo, off);
+            const unsigned long long o_hi = __shfl_xor_sync(0xffffffffu, best_hi, off);
+            best_lo = o_lo > best_lo ? o_lo : best_lo;
+            best_hi = o_hi > best_hi ? o_hi : best_hi;
         }
-        if (lane < kRows && lane < a.rows && best) atomicMax(a.keys + lane, best);
+        if (part == 0) {
+            if (best_lo) atomicMax(&cta_best[n_row], best_lo);
+            if (kUpper && best_hi) atomicMax(&cta_best[n_row + 8], best_hi);
+        }
+        __syncthreads();
+        if (tid < a.rows && cta_best[tid]) atomicMax(a.keys + tid, cta_best[tid]);
         __threadfence();
         __syncthreads();
         if (tid == 0) last_flag = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
@@ -167,17 +160,13 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
     }
 }
 
-template <int kRows, int kCpl>
+template <int kSteps, bool kUpper>
 int launch_skinny(const SkinnyArgs& a, void* stream) {
-    constexpr int kCols = 32 / kRows;
-    auto kernel = a.dtype == RLM_BF16 ? skinny_projection_kernel<kRows, kCpl, true> : skinny_projection_kernel<kRows, kCpl, false>;
-    const int smem = kRows * a.d * 4;
-    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
-    if (rc != RLM_OK) return rc;
-    // enough CTAs to cover the SMs twice, never more warps than column groups
+    auto kernel = a.dtype == RLM_BF16 ? skinny_projection_kernel<kSteps, kUpper, true> : skinny_projection_kernel<kSteps, kUpper, false>;
+    const int smem = (kUpper ? 16 : 8) * (a.d * 2 + 64);
+    // a warp per group of eight columns while they last, at most four CTAs per SM
     int ctas = (a.groups + kSkWarps - 1) / kSkWarps;
-    if (ctas > 2 * 148) ctas = 2 * 148;
-    (void)kCols;
+    if (ctas > 4 * 148) ctas = 4 * 148;
     launch_kernel(kernel, dim3(ctas), dim3(kSkThreads), smem, stream, a);
     count_launch();
     return check_launch("skinny_projection_kernel");
@@ -197,7 +186,7 @@ extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const 
         return RLM_ERR_SHAPE;
     }
     if (d_in != 256 && d_in != 512) {
-        set_error("skinny_projection: built for d = 256 and d = 512 (a weight row in registers); use rlm_packed_projection otherwise");
+        set_error("skinny_projection: built for d = 256 and d = 512 (a warp's weight rows in registers); use rlm_packed_projection otherwise");
         return RLM_ERR_UNSUPPORTED;
     }
     if (dtype != RLM_BF16 && dtype != RLM_F16) {
@@ -221,13 +210,9 @@ extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const 
         a.next_token = next_token;
         a.position = position;
     }
-    const int cpl = d_in / 256;
-    if (rows <= 8) {
-        a.groups = (n_out + 3) / 4;
-        return cpl == 1 ? launch_skinny<8, 1>(a, stream) : launch_skinny<8, 2>(a, stream);
-    }
-    a.groups = (n_out + 1) / 2;
-    return cpl == 1 ? launch_skinny<16, 1>(a, stream) : launch_skinny<16, 2>(a, stream);
+    a.groups = (n_out + 7) / 8;
+    if (rows <= 8) return d_in == 256 ? launch_skinny<8, false>(a, stream) : launch_skinny<16, false>(a, stream);
+    return d_in == 256 ? launch_skinny<8, true>(a, stream) : launch_skinny<16, true>(a, stream);
 }
 
 // Bytes of the greedy head's scratch: 16 arg-max keys and the CTA counter.  Zero it once; every
