@@ -479,6 +479,30 @@ int rlm_skinny_projection(const void* x, int64_t x_row_stride, const void* weigh
                           void* argmax_scratch, int64_t* next_token, int64_t* position, void* stream);
 
 /*
+ * Packed sparse-cache projection of one decode position for every layer, with the state update in
+ * its epilogue (extension): what a reference decode step does with
+ * PackedSparseCacheProjection.project (src/relation_lm/inference/packed_cache.py:52-57), the four
+ * token-cache row writes and relation_lm::router_cache_update (src/relation_lm/kernels/router_cache.py:175-241)
+ * per layer, in ONE launch.  Column c of layer l's 384 + R packed columns goes where the state keeps
+ * it: anchor key | partner key | operand | partner-anchor -> row *position of the token caches;
+ * router keys -> raw cache, three-tap causal convolution, conv cache, and the current block's mean /
+ * biased std (ascending rows, the fresh un-rounded value at the current row) — each channel by
+ * the thread that holds its output.  Results equal rlm_skinny_projection followed by
+ * rlm_sparse_cache_append bit for bit.
+ *   x [B <= 16, d] (row stride in ELEMENTS), weight [layers * (384 + R), d], packed_out [B, layers * (384 + R)]
+ *   (optional), caches [layers, B, T, w] and statistics [layers, B, NB, 4, 16]: all bfloat16 or all
+ *   float16 (dtype); conv weights [layers, 64, 3] f32; d = 256 or 512.
+ */
+int rlm_packed_projection_append(
+    const void* x, int64_t x_row_stride, const void* weight, void* packed_out, int relation_dim,
+    void* anchor_keys, void* partner_keys, void* operand_cache, void* partner_anchor_cache,
+    void* anchor_raw_cache, void* partner_raw_cache, void* anchor_conv_cache, void* partner_conv_cache,
+    void* anchor_mean, void* anchor_std, void* partner_mean, void* partner_std,
+    const float* anchor_conv_weight, const float* partner_conv_weight, const int64_t* position,
+    int layers, int batch, int d_in, int max_t, int n_blocks, int block_size, int dtype, int32_t* status,
+    void* stream);
+
+/*
  * Routed multi-anchor selection, all slots of a query row in one launch (extension).  The
  * reference's multi-anchor layer is dense (src/relation_lm/models/multi_relation_blocks.py:69-148);
  * this applies its rules inside each slot's routed candidate set (local window + that slot's

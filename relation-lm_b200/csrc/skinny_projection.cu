@@ -44,6 +44,87 @@ struct SkinnyArgs {
     int groups;               // groups of eight output columns
 };
 
+// State append in the projection's epilogue (the packed projection of a decode step): every output
+// element is stored where the step's state keeps it instead of (or besides) a packed row.  Column
+// c of layer l's 384 + R packed columns (src/relation_lm/inference/packed_cache.py:10-17):
+// anchor key | partner key | operand | partner-anchor -> row `position` of the four token caches;
+// anchor / partner router key, channel ch -> the router update of that channel
+// (src/relation_lm/kernels/router_cache.py:33-172): raw key, three-tap causal convolution over the
+// raw cache, conv cache row, and mean / biased std of the channel over the current block's conv
+// rows in ascending order with the fresh (un-rounded) value at the current row.  Every step of
+// that update is per channel, so the lane that holds the channel's output does all of it.
+struct SkinnyAppend {
+    void* token_cache[4];     // [layers, B, T, w]: anchor keys, partner keys, operand, partner-anchor
+    void* raw_cache[2];       // [layers, B, T, 64]
+    void* conv_cache[2];
+    void* mean[2];            // [layers, B, NB, 64]
+    void* stdv[2];
+    const float* weight[2];   // [layers, 64, 3] fp32
+    const int64_t* position;
+    int32_t* status;
+    int max_t, n_blocks, block_size, layers, rdim;
+};
+
+template <bool kBf16>
+__device__ __forceinline__ float from16(uint16_t bits) {
+    return kBf16 ? bf16_bits_to_float(bits) : __half2float(*reinterpret_cast<const __half*>(&bits));
+}
+template <bool kBf16>
+__device__ __forceinline__ uint16_t to16(float v) {
+    if (kBf16) { __nv_bfloat16 h = __float2bfloat16_rn(v); return *reinterpret_cast<uint16_t*>(&h); }
+    __half h = __float2half_rn(v);
+    return *reinterpret_cast<uint16_t*>(&h);
+}
+
+// One packed output of sequence m, column col (already rounded: `bits`, `value`), at position t.
+template <bool kBf16>
+__device__ __forceinline__ void append_output(const SkinnyAppend& ap, int batch, int m, int col, int t,
+                                              uint16_t bits, float value) {
+    const int width = 384 + ap.rdim;
+    const int l = col / width, c = col - l * width;
+    const int64_t seq = static_cast<int64_t>(l) * batch + m;
+    const int R = ap.rdim;
+    if (c < 256 + R) {
+        int which, w, cc;
+        if (c < 64) { which = 0; w = 64; cc = c; }
+        else if (c < 128) { which = 1; w = 64; cc = c - 64; }
+        else if (c < 128 + R) { which = 2; w = R; cc = c - 128; }
+        else { which = 3; w = 128; cc = c - 128 - R; }
+        static_cast<uint16_t*>(ap.token_cache[which])[(seq * ap.max_t + t) * w + cc] = bits;
+        return;
+    }
+    const int s = (c - 256 - R) >> 6, ch = (c - 256 - R) & 63;
+    const int bs = ap.block_size, blk = t / bs, start = blk * bs;
+    uint16_t* raw_cache = static_cast<uint16_t*>(ap.raw_cache[s]);
+    uint16_t* conv_cache = static_cast<uint16_t*>(ap.conv_cache[s]);
+    const int64_t base = seq * ap.max_t * 64 + ch;
+    const float prev1 = from16<kBf16>(raw_cache[base + static_cast<int64_t>(max(t - 1, 0)) * 64]);
+    const float prev2 = from16<kBf16>(raw_cache[base + static_cast<int64_t>(max(t - 2, 0)) * 64]);
+    const float* w3 = ap.weight[s] + (static_cast<int64_t>(l) * 64 + ch) * 3;
+    float conv = __fmul_rn(value, w3[2]);
+    conv = __fadd_rn(conv, __fmul_rn(__fmul_rn(prev1, w3[1]), t >= 1 ? 1.0f : 0.0f));
+    conv = __fadd_rn(conv, __fmul_rn(__fmul_rn(prev2, w3[0]), t >= 2 ? 1.0f : 0.0f));
+    raw_cache[base + static_cast<int64_t>(t) * 64] = bits;
+    conv_cache[base + static_cast<int64_t>(t) * 64] = to16<kBf16>(conv);
+    const int cur = t - start;
+    float sum = 0.0f;
+    for (int r = 0; r < bs; ++r) {
+        const float x = r == cur ? conv : from16<kBf16>(conv_cache[base + static_cast<int64_t>(start + r) * 64]);
+        sum = __fadd_rn(sum, x);
+    }
+    const float mean = __fdiv_rn(sum, static_cast<float>(bs));
+    float acc = 0.0f;
+    for (int r = 0; r < bs; ++r) {
+        const float x = r == cur ? conv : from16<kBf16>(conv_cache[base + static_cast<int64_t>(start + r) * 64]);
+        const float dv = __fsub_rn(x, mean);
+        acc = __fmaf_rn(dv, dv, acc);
+    }
+    const float sd = __fsqrt_rn(__fdiv_rn(acc, static_cast<float>(bs)));
+    const int64_t stat = (seq * ap.n_blocks + blk) * 64 + ch;
+    static_cast<uint16_t*>(ap.mean[s])[stat] = to16<kBf16>(mean);
+    static_cast<uint16_t*>(ap.stdv[s])[stat] = to16<kBf16>(sd);
+}
+
 template <bool kBf16>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -56,8 +137,8 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // kSteps = d / 32 steps of 32 k-values; kUpper: rows 8..15 of x exist (more than eight rows).
-template <int kSteps, bool kUpper, bool kBf16>
-__global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const SkinnyArgs a) {
+template <int kSteps, bool kUpper, bool kBf16, bool kAppend>
+__global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const SkinnyArgs a, const SkinnyAppend ap) {
     // rows of x in the operands' own 16-bit format, each row padded by 64 bytes: the two rows a
     // quarter warp reads (64 bytes of each) lie in different halves of the banks
     extern __shared__ __align__(16) unsigned char xs[];
@@ -90,6 +171,15 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
         *reinterpret_cast<uint4*>(xs + m * row_bytes + 16 * c) = v;
     }
     __syncthreads();
+    int t = 0;
+    if (kAppend) {
+        t = static_cast<int>(*ap.position);
+        const int blk = t / ap.block_size;
+        if (t < 0 || t >= ap.max_t || blk >= ap.n_blocks || (blk + 1) * ap.block_size > ap.max_t) {
+            if (tid == 0 && ap.status) atomicOr(ap.status, RLM_DEV_POSITION);
+            return;
+        }
+    }
 
     unsigned long long best_lo = 0ull, best_hi = 0ull;         // arg-max keys of rows n_row and n_row + 8
     for (; g < a.groups; g += warps_total) {
@@ -118,8 +208,9 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
             uint16_t bits;
             if (kBf16) { __nv_bfloat16 h = __float2bfloat16_rn(value); bits = *reinterpret_cast<uint16_t*>(&h); value = __bfloat162float(h); }
             else { __half h = __float2half_rn(value); bits = *reinterpret_cast<uint16_t*>(&h); value = __half2float(h); }
-            static_cast<uint16_t*>(a.out)[static_cast<size_t>(m) * a.n + col] = bits;
-            if (a.keys && col < a.vocab) {
+            if (a.out) static_cast<uint16_t*>(a.out)[static_cast<size_t>(m) * a.n + col] = bits;
+            if (kAppend) append_output<kBf16>(ap, a.rows, m, col, t, bits, value);
+            if (!kAppend && a.keys && col < a.vocab) {
                 const unsigned long long key = (static_cast<unsigned long long>(float_key(value + 0.0f)) << 32) |
                                                (0xffffffffu - static_cast<unsigned int>(col));
                 if (e >> 1) best_hi = key > best_hi ? key : best_hi;
@@ -127,7 +218,7 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
             }
         }
     }
-    if (a.keys) {
+    if (!kAppend && a.keys) {
         // the four lanes of a row, then the CTA's warps through shared memory, then one atomic per row
 #pragma unroll
         for (int off = 1; off < 4; off <<= 1) {
@@ -161,26 +252,31 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
 }
 
 template <int kSteps, bool kUpper>
-int launch_skinny(const SkinnyArgs& a, void* stream) {
-    auto kernel = a.dtype == RLM_BF16 ? skinny_projection_kernel<kSteps, kUpper, true> : skinny_projection_kernel<kSteps, kUpper, false>;
+int launch_skinny(const SkinnyArgs& a, const SkinnyAppend* append, void* stream) {
+    auto kernel = append ? (a.dtype == RLM_BF16 ? skinny_projection_kernel<kSteps, kUpper, true, true>
+                                                : skinny_projection_kernel<kSteps, kUpper, false, true>)
+                         : (a.dtype == RLM_BF16 ? skinny_projection_kernel<kSteps, kUpper, true, false>
+                                                : skinny_projection_kernel<kSteps, kUpper, false, false>);
+    const SkinnyAppend ap = append ? *append : SkinnyAppend{};
     const int smem = (kUpper ? 16 : 8) * (a.d * 2 + 64);
     // a warp per group of eight columns while they last, at most four CTAs per SM
     int ctas = (a.groups + kSkWarps - 1) / kSkWarps;
     if (ctas > 4 * 148) ctas = 4 * 148;
-    launch_kernel(kernel, dim3(ctas), dim3(kSkThreads), smem, stream, a);
+    launch_kernel(kernel, dim3(ctas), dim3(kSkThreads), smem, stream, a, ap);
     count_launch();
     return check_launch("skinny_projection_kernel");
 }
 
-}  // namespace
-}  // namespace rlm
+int dispatch_skinny(SkinnyArgs& a, const SkinnyAppend* append, void* stream) {
+    a.groups = (a.n + 7) / 8;
+    if (a.rows <= 8)
+        return a.d == 256 ? launch_skinny<8, false>(a, append, stream) : launch_skinny<16, false>(a, append, stream);
+    return a.d == 256 ? launch_skinny<8, true>(a, append, stream) : launch_skinny<16, true>(a, append, stream);
+}
 
-extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const void* weight, const float* bias,
-                                     void* out, int rows, int d_in, int n_out, int dtype, int vocab,
-                                     void* argmax_scratch, int64_t* next_token, int64_t* position, void* stream) {
-    using namespace rlm;
-    if (rows == 0 || n_out == 0) return RLM_OK;
-    if (!x || !weight || !out) { set_error("skinny_projection: NULL pointer"); return RLM_ERR_NULL; }
+int check_skinny_operands(const void* x, int64_t x_row_stride, const void* weight, int rows, int d_in, int n_out,
+                          int dtype) {
+    if (!x || !weight) { set_error("skinny_projection: NULL pointer"); return RLM_ERR_NULL; }
     if (rows < 0 || rows > 16 || n_out < 1 || x_row_stride < d_in) {
         set_error("skinny_projection: at most 16 rows");
         return RLM_ERR_SHAPE;
@@ -197,6 +293,20 @@ extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const 
         set_error("skinny_projection: rows of x and the weight must be 16-byte aligned");
         return RLM_ERR_ALIGN;
     }
+    return RLM_OK;
+}
+
+}  // namespace
+}  // namespace rlm
+
+extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const void* weight, const float* bias,
+                                     void* out, int rows, int d_in, int n_out, int dtype, int vocab,
+                                     void* argmax_scratch, int64_t* next_token, int64_t* position, void* stream) {
+    using namespace rlm;
+    if (rows == 0 || n_out == 0) return RLM_OK;
+    if (!out) { set_error("skinny_projection: NULL pointer"); return RLM_ERR_NULL; }
+    int rc = check_skinny_operands(x, x_row_stride, weight, rows, d_in, n_out, dtype);
+    if (rc != RLM_OK) return rc;
     if (vocab > 0 && (!argmax_scratch || !next_token || vocab > n_out)) {
         set_error("skinny_projection: the greedy head needs scratch (rlm_skinny_argmax_scratch_bytes), next_token and vocab <= n");
         return RLM_ERR_NULL;
@@ -210,9 +320,45 @@ extern "C" int rlm_skinny_projection(const void* x, int64_t x_row_stride, const 
         a.next_token = next_token;
         a.position = position;
     }
-    a.groups = (n_out + 7) / 8;
-    if (rows <= 8) return d_in == 256 ? launch_skinny<8, false>(a, stream) : launch_skinny<16, false>(a, stream);
-    return d_in == 256 ? launch_skinny<8, true>(a, stream) : launch_skinny<16, true>(a, stream);
+    return dispatch_skinny(a, nullptr, stream);
+}
+
+extern "C" int rlm_packed_projection_append(
+    const void* x, int64_t x_row_stride, const void* weight, void* packed_out, int relation_dim,
+    void* anchor_keys, void* partner_keys, void* operand_cache, void* partner_anchor_cache,
+    void* anchor_raw_cache, void* partner_raw_cache, void* anchor_conv_cache, void* partner_conv_cache,
+    void* anchor_mean, void* anchor_std, void* partner_mean, void* partner_std,
+    const float* anchor_conv_weight, const float* partner_conv_weight, const int64_t* position,
+    int layers, int batch, int d_in, int max_t, int n_blocks, int block_size, int dtype, int32_t* status,
+    void* stream) {
+    using namespace rlm;
+    if (batch == 0) return RLM_OK;
+    const void* need[] = {anchor_keys, partner_keys, operand_cache, partner_anchor_cache, anchor_raw_cache,
+                          partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std,
+                          partner_mean, partner_std, anchor_conv_weight, partner_conv_weight, position};
+    for (const void* q : need)
+        if (!q) { set_error("packed_projection_append: NULL pointer"); return RLM_ERR_NULL; }
+    if (layers < 1 || relation_dim < 8 || relation_dim % 8 != 0 || max_t < 1 || n_blocks < 1 || block_size < 1 ||
+        n_blocks * block_size != max_t) {
+        set_error("packed_projection_append: need layers >= 1, R a multiple of 8, T = blocks x block size");
+        return RLM_ERR_SHAPE;
+    }
+    const int n_out = layers * (384 + relation_dim);
+    int rc = check_skinny_operands(x, x_row_stride, weight, batch, d_in, n_out, dtype);
+    if (rc != RLM_OK) return rc;
+    SkinnyArgs a{};
+    a.x = x; a.w = weight; a.out = packed_out; a.x_stride = x_row_stride;
+    a.rows = batch; a.d = d_in; a.n = n_out; a.dtype = dtype;
+    SkinnyAppend ap{};
+    ap.token_cache[0] = anchor_keys; ap.token_cache[1] = partner_keys; ap.token_cache[2] = operand_cache;
+    ap.token_cache[3] = partner_anchor_cache;
+    ap.raw_cache[0] = anchor_raw_cache; ap.raw_cache[1] = partner_raw_cache;
+    ap.conv_cache[0] = anchor_conv_cache; ap.conv_cache[1] = partner_conv_cache;
+    ap.mean[0] = anchor_mean; ap.mean[1] = partner_mean; ap.stdv[0] = anchor_std; ap.stdv[1] = partner_std;
+    ap.weight[0] = anchor_conv_weight; ap.weight[1] = partner_conv_weight;
+    ap.position = position; ap.status = status; ap.max_t = max_t; ap.n_blocks = n_blocks; ap.block_size = block_size;
+    ap.layers = layers; ap.rdim = relation_dim;
+    return dispatch_skinny(a, &ap, stream);
 }
 
 // Bytes of the greedy head's scratch: 16 arg-max keys and the CTA counter.  Zero it once; every

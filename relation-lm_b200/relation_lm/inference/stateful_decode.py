@@ -37,7 +37,7 @@ from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
-from relation_lm.kernels.router_cache import sparse_cache_append
+from relation_lm.kernels.router_cache import packed_projection_append, sparse_cache_append
 
 
 class StatefulDecoder:
@@ -220,10 +220,17 @@ class StatefulDecoder:
                                    w["position_embedding"], pos, self.input_scale,
                                    w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
                                    w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
-        packed = self._project(self.memory_normalized, w["w_packed"])
-        sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
-                            self.partner_anchor_cache, *self.router_caches, *self.router_stats,
-                            w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+        if self.skinny:
+            # the packed projection's epilogue writes the token caches and updates the router state
+            packed = packed_projection_append(self.memory_normalized, w["w_packed"], self.anchor_keys,
+                                              self.partner_keys, self.operand_cache, self.partner_anchor_cache,
+                                              *self.router_caches, *self.router_stats, w["anchor_conv_weight"],
+                                              w["partner_conv_weight"], pos, cfg.block_size)
+        else:
+            packed = self._project(self.memory_normalized, w["w_packed"])
+            sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
+                                self.partner_anchor_cache, *self.router_caches, *self.router_stats,
+                                w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
         if self.stacked_expand:
             # every layer's operand row of this position is known: expand them all at once
             expanded_cache_append(self.expanded_cache, self.operand_cache, w["anchor_weight"],

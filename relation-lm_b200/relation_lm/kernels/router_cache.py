@@ -192,3 +192,69 @@ def _(anchor_raw, partner_raw, anchor_raw_cache, partner_raw_cache, anchor_conv_
       partner_conv_cache, anchor_mean, anchor_std, partner_mean, partner_std,
       anchor_conv_weight, partner_conv_weight, block_size):
     return None
+
+
+@torch.library.custom_op("relation_lm::packed_projection_append", mutates_args=_APPEND_MUTATED, device_types="cuda")
+def packed_projection_append(
+    x: Tensor,
+    weight: Tensor,
+    anchor_keys: Tensor,
+    partner_keys: Tensor,
+    operand_cache: Tensor,
+    partner_anchor_cache: Tensor,
+    anchor_raw_cache: Tensor,
+    partner_raw_cache: Tensor,
+    anchor_conv_cache: Tensor,
+    partner_conv_cache: Tensor,
+    anchor_mean: Tensor,
+    anchor_std: Tensor,
+    partner_mean: Tensor,
+    partner_std: Tensor,
+    anchor_conv_weight: Tensor,
+    partner_conv_weight: Tensor,
+    position: Tensor,
+    block_size: int,
+) -> Tensor:
+    """The packed projection of one decode position for all layers with ``sparse_cache_append`` in its
+    epilogue (extension; decode batches of at most 16 rows, ``d`` 256 or 512): one launch writes the
+    token-cache rows and updates both router streams of every layer, each output element by the
+    thread that computed it.  Returns the packed rows ``[B, layers * (384 + R)]``; the state equals
+    ``sparse_cache_append(skinny_projection(x, weight), ...)`` bit for bit."""
+    device = _abi.require_cuda_contiguous(
+        weight=weight, anchor_keys=anchor_keys, partner_keys=partner_keys, operand_cache=operand_cache,
+        partner_anchor_cache=partner_anchor_cache, anchor_raw_cache=anchor_raw_cache,
+        partner_raw_cache=partner_raw_cache, anchor_conv_cache=anchor_conv_cache,
+        partner_conv_cache=partner_conv_cache, anchor_mean=anchor_mean, anchor_std=anchor_std,
+        partner_mean=partner_mean, partner_std=partner_std, anchor_conv_weight=anchor_conv_weight,
+        partner_conv_weight=partner_conv_weight)
+    _abi.require_cuda_rows(x=x)
+    _abi.require_position(position, device)
+    layers, batch, max_t, rdim = operand_cache.shape
+    width = 384 + rdim
+    if x.shape[0] != batch or weight.shape != (layers * width, x.shape[1]) or anchor_keys.shape != (layers, batch, max_t, 64) \
+            or partner_anchor_cache.shape != (layers, batch, max_t, 128) or anchor_raw_cache.shape != (layers, batch, max_t, 64) \
+            or anchor_mean.size(0) != layers or anchor_conv_weight.shape != (layers, 64, 3):
+        raise ValueError("caches must be [layers, B, T, width], weight [layers * (384 + R), d], conv weights [layers, 64, 3]")
+    if anchor_conv_weight.dtype != torch.float32 or partner_conv_weight.dtype != torch.float32:
+        raise ValueError("conv weights must be float32")
+    dtype = _abi.same_dtype("16-bit operand", x, weight, anchor_keys, partner_keys, operand_cache, partner_anchor_cache,
+                            anchor_raw_cache, partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean,
+                            anchor_std, partner_mean, partner_std)
+    packed = torch.empty((batch, layers * width), device=device, dtype=x.dtype)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_packed_projection_append(
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(packed), rdim, _abi.ptr(anchor_keys),
+            _abi.ptr(partner_keys), _abi.ptr(operand_cache), _abi.ptr(partner_anchor_cache),
+            _abi.ptr(anchor_raw_cache), _abi.ptr(partner_raw_cache), _abi.ptr(anchor_conv_cache),
+            _abi.ptr(partner_conv_cache), _abi.ptr(anchor_mean), _abi.ptr(anchor_std), _abi.ptr(partner_mean),
+            _abi.ptr(partner_std), _abi.ptr(anchor_conv_weight), _abi.ptr(partner_conv_weight), _abi.ptr(position),
+            layers, batch, x.size(1), max_t, anchor_mean.size(2), int(block_size), dtype,
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return packed
+
+
+@packed_projection_append.register_fake
+def _(x, weight, anchor_keys, partner_keys, operand_cache, partner_anchor_cache, anchor_raw_cache,
+      partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std, partner_mean,
+      partner_std, anchor_conv_weight, partner_conv_weight, position, block_size):
+    return x.new_empty((x.size(0), weight.size(0)))

@@ -164,3 +164,38 @@ def test_prefill_equals_sequential_updates(dtype, length):
         host = {n: new[n].to(td) for n in STATE}
     for n in STATE:
         assert torch.equal(dev[n].cpu(), host[n]), n
+
+
+@pytest.mark.parametrize("position", [0, 1, 31, 32, 200])
+def test_projection_with_state_append_in_its_epilogue_equals_the_two_launch_form(position):
+    """``packed_projection_append`` (projection of one decode position for all layers, token-cache rows
+    and router update in the epilogue) against ``skinny_projection`` + ``sparse_cache_append``: the
+    packed rows and all twelve state tensors bit for bit, stale rows beyond the position included."""
+    from relation_lm.kernels.packed_projection import skinny_projection
+    from relation_lm.kernels.router_cache import packed_projection_append, sparse_cache_append
+
+    layers, B, T, bs, R, d = 3, 8, 256, 32, 128, 512
+    nb, width = T // bs, 384 + R
+    g = torch.Generator().manual_seed(8200 + position)
+    rn = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    x = rn(B, d).bfloat16().cuda()
+    weight = (rn(layers * width, d) * 0.05).bfloat16().cuda()
+    conv_a, conv_p = (rn(layers, 64, 3) * 0.1).cuda(), (rn(layers, 64, 3) * 0.1).cuda()
+
+    def fresh_state():
+        gs = torch.Generator().manual_seed(8300 + position)
+        tok = [torch.zeros(layers, B, T, w_, dtype=torch.bfloat16, device="cuda") for w_ in (64, 64, R, 128)]
+        router = [torch.randn(layers, B, T, 64, generator=gs).bfloat16().cuda() for _ in range(4)]
+        stats = [torch.randn(layers, B, nb, 4, 16, generator=gs).bfloat16().cuda() for _ in range(4)]
+        return tok, router, stats
+
+    pos = position_tensor(position)
+    tok1, router1, stats1 = fresh_state()
+    packed1 = packed_projection_append(x, weight, *tok1, *router1, *stats1, conv_a, conv_p, pos, bs)
+    tok2, router2, stats2 = fresh_state()
+    packed2 = skinny_projection(x, weight)
+    sparse_cache_append(packed2, *tok2, *router2, *stats2, conv_a, conv_p, pos, bs)
+    assert torch.equal(packed1, packed2)
+    for mine, theirs in zip(tok1 + router1 + stats1, tok2 + router2 + stats2):
+        assert torch.equal(mine, theirs)
+    assert_status_clear()
