@@ -503,6 +503,26 @@ int rlm_packed_projection_append(
     void* stream);
 
 /*
+ * Whole-sequence (prefill) form of rlm_relation_select_packed (extension): query rows
+ * b * query_length + t for every position t < query_length of every sequence b; row (b, t) equals
+ * the decode operator at position t of sequence b (src/relation_lm/kernels/relation_select.py:50-308),
+ * given final block statistics, bit for bit.  One CTA serves a tile of 32 consecutive positions:
+ * the block statistics they share and the union of their local windows are staged once; every
+ * warp then walks one query's chain at a time (remote blocks are read where they lie).  Same
+ * tensors as the decode form without `position`; at most 512 candidates per query.
+ */
+int rlm_relation_select_packed_prefill(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    int32_t* out_anchor, float* out_anchor_score, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
+    int n_seq, int query_length, int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out,
+    int strict_valid, int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status,
+    void* stream);
+
+/*
  * Routed multi-anchor selection, all slots of a query row in one launch (extension).  The
  * reference's multi-anchor layer is dense (src/relation_lm/models/multi_relation_blocks.py:69-148);
  * this applies its rules inside each slot's routed candidate set (local window + that slot's

@@ -142,7 +142,9 @@ __device__ __forceinline__ float chunk_dot(const unsigned char* row, const float
 // worked out its first rows' positions (`arrived` = false when the wait gave up).  With `cand`
 // the scores go to candidate slots slot0 + r and nothing else happens; without, the warp's best
 // (score, lowest position on ties) is folded into (best_key, best_pos), identical in all lanes.
-template <bool kBf16, int kLpr>
+// kAtPosition: `rows` is the sequence's whole key cache and a candidate row is read where it lies
+// (row = its position), straight from global memory / L2, instead of from a staged copy.
+template <bool kBf16, int kLpr, bool kAtPosition = false>
 __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key_dtype_arg, int n_rows,
                                               const int* sel, int bs, int first_valid, int pos0,
                                               int exclude, const int* excl, int n_excl, const float* query,
@@ -177,7 +179,7 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
         }
         valid = valid && arrived;
         if (valid) {
-            const unsigned char* row = rows + static_cast<size_t>(r) * row_bytes;
+            const unsigned char* row = rows + static_cast<size_t>(kAtPosition ? pos : r) * row_bytes;
             if (kLpr == 1) {
                 // pair sums (p0+p1) .. (p6+p7), pair index rotated by the row, lanes 4..7 of
                 // each group of eight taking the pair's second chunk first
@@ -425,6 +427,12 @@ __device__ __noinline__ void topk_tournament(const float* cand, int cap4, int K,
 #define RLM_CE(i, j) do { const uint64_t hi_ = c[i] > c[j] ? c[i] : c[j], lo_ = c[i] > c[j] ? c[j] : c[i]; c[i] = hi_; c[j] = lo_; } while (0)
     if (kN == 4) {
         RLM_CE(0, 1); RLM_CE(2, 3); RLM_CE(0, 2); RLM_CE(1, 3); RLM_CE(1, 2);
+    } else if (kN > 8) {
+        // odd-even transposition sort, descending (up to 512 candidate slots per warp)
+#pragma unroll
+        for (int round = 0; round < kN; ++round)
+#pragma unroll
+            for (int i = round & 1; i + 1 < kN; i += 2) RLM_CE(i, i + 1);
     } else {
         RLM_CE(0, 1); RLM_CE(2, 3); RLM_CE(4, 5); RLM_CE(6, 7); RLM_CE(0, 2); RLM_CE(1, 3); RLM_CE(4, 6);
         RLM_CE(5, 7); RLM_CE(1, 2); RLM_CE(5, 6); RLM_CE(0, 4); RLM_CE(3, 7); RLM_CE(1, 5); RLM_CE(2, 6);
@@ -1027,6 +1035,227 @@ __global__ void __launch_bounds__(kThreads, 3) relation_select_multi_kernel(cons
     }
 }
 
+// ---- whole-sequence (prefill) selection: a tile of consecutive positions per CTA
+//
+// Query row (b, t) of a whole-sequence pass sees the same block statistics as its neighbours (the
+// complete blocks at t) and a local window that overlaps theirs in all but one row.  One CTA
+// therefore serves a tile of kTileQ consecutive positions of one sequence: the statistics of both
+// streams and the union of the tile's local windows are staged in shared memory once, then every
+// warp takes the tile's queries one at a time and walks the whole chain for its query on its own
+// — block scores, local scores, block picking, remote scores (read where the blocks lie, from
+// L2), anchor, partner queries, partner scores, top-K — with warp-level synchronisation only.
+// The arithmetic is the per-row kernel's own (the same device functions), so indices and scores
+// are bit-identical to relation_select_kernel's.
+constexpr int kTileQ = 32;
+
+struct TileArgs {
+    SelectArgs base;          // packed mode; queries [n_seq * q_len, ...]; row = b * q_len + t
+    int q_len;                // query positions 0 .. q_len - 1 of every sequence
+    int warp_bytes, stats_bytes, window_rows;
+};
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 2) relation_select_tile_kernel(const TileArgs m) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const SelectArgs& a = m.base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int key_dtype = kBf16 ? RLM_BF16 : a.key_dtype, stats_dtype = kBf16 ? RLM_BF16 : a.stats_dtype,
+              query_dtype = kBf16 ? RLM_BF16 : a.query_dtype;
+    const int tiles_per_seq = (m.q_len + kTileQ - 1) / kTileQ;
+    const int b = blockIdx.x / tiles_per_seq, t0 = (blockIdx.x - b * tiles_per_seq) * kTileQ;
+    const int t_end = min(t0 + kTileQ, m.q_len);               // exclusive
+    const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks, K = a.k_out;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? 31 - __clz(bs) : -1;
+    const int ks = key_dtype == RLM_F32 ? 4 : 2, ss = stats_dtype == RLM_F32 ? 4 : 2;
+    const size_t key_row = static_cast<size_t>(kD) * ks, stat_row = static_cast<size_t>(kD) * ss;
+    const int buckets4 = 4 * a.buckets;
+    griddep_sync();
+
+    // ---- shared staging: statistics of the blocks complete at the tile's last position, and the
+    // union of the local windows: positions [w_lo, t_end)
+    unsigned char* st[4] = {smem, smem + m.stats_bytes, smem + 2 * m.stats_bytes, smem + 3 * m.stats_bytes};
+    unsigned char* win_a = smem + 4 * m.stats_bytes;
+    unsigned char* win_p = win_a + static_cast<size_t>(m.window_rows) * key_row;
+    unsigned char* warp_base = win_p + static_cast<size_t>(m.window_rows) * key_row + static_cast<size_t>(warp) * m.warp_bytes;
+    const int n_stage = top > 0 ? min(t_end / bs, nb) : 0;
+    const int w_lo = max(t0 - L + 1, 0);
+    const size_t seq_stats = static_cast<size_t>(b) * nb * stat_row, seq_keys = static_cast<size_t>(b) * a.max_t * key_row;
+    {
+        const char* src[4] = {static_cast<const char*>(a.anchor_mean) + seq_stats, static_cast<const char*>(a.anchor_std) + seq_stats,
+                              static_cast<const char*>(a.partner_mean) + seq_stats, static_cast<const char*>(a.partner_std) + seq_stats};
+        const int stat_chunks = static_cast<int>(n_stage * stat_row / 16);
+        for (int i = tid; i < 4 * stat_chunks; i += kThreads) {
+            const int which = i / stat_chunks, c = i - which * stat_chunks;
+            cp_async16(smem_u32(st[which]) + 16 * c, src[which] + 16 * c);
+        }
+        const int win_chunks = static_cast<int>((t_end - w_lo) * key_row / 16);
+        const char* ka = static_cast<const char*>(a.anchor_keys) + seq_keys + w_lo * key_row;
+        const char* kp = static_cast<const char*>(a.partner_keys) + seq_keys + w_lo * key_row;
+        for (int i = tid; i < win_chunks; i += kThreads) {
+            cp_async16(smem_u32(win_a) + 16 * i, ka + 16 * i);
+            cp_async16(smem_u32(win_p) + 16 * i, kp + 16 * i);
+        }
+        cp_async_commit();
+    }
+    // per-warp scratch
+    float* queries = reinterpret_cast<float*>(warp_base);                     // aq | arq | pq | prq
+    float* params = queries + 4 * kD;                                         // softplus a[4] p[4], bias a, bias p
+    float* sp_a = params, *sp_p = params + 4, *bias_a = params + 8, *bias_p = bias_a + buckets4;
+    float* bscore = bias_p + buckets4;
+    float* cand = bscore + ((nb + 3) & ~3);
+    const int cap = L + top * bs, cap4 = (cap + 3) & ~3;
+    int* sel = reinterpret_cast<int*>(cand + cap4);
+    for (int i = lane; i < buckets4; i += 32) {
+        bias_a[i] = load_scalar(a.anchor_bias, i, a.param_dtype);
+        bias_p[i] = load_scalar(a.partner_bias, i, a.param_dtype);
+    }
+    if (lane < 8) {
+        const float gamma = load_scalar(lane < 4 ? a.anchor_gamma : a.partner_gamma, lane & 3, a.param_dtype);
+        params[lane] = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
+    }
+    for (int i = cap + lane; i < cap4; i += 32) cand[i] = kNegInf;
+    cp_async_wait_all();
+    __syncthreads();
+
+    for (int t = t0 + warp; t < t_end; t += kWarps) {
+        const int row = b * m.q_len + t;
+        const int ls = max(t - L + 1, 0), first_local = ls - (t - L + 1);
+        const int n_complete = min((t + 1) / bs, nb);
+        // this query's rows of the projections
+        for (int i = lane; i < 4 * kD; i += 32) {
+            float v;
+            if (i < kD) v = load_scalar(a.anchor_query, row * a.aq_stride + i, query_dtype);
+            else if (i < 2 * kD) v = load_scalar(a.anchor_router_query, row * a.arq_stride + i - kD, query_dtype);
+            else v = load_scalar(a.partner_base, row * a.pbase_stride + i - 2 * kD, query_dtype);
+            queries[i] = v;
+        }
+        __syncwarp();
+        const float* aq = queries, *arq = queries + kD;
+        float* pq = queries + 2 * kD, *prq = queries + 3 * kD;
+        // the query's window starts (t - L + 1 - w_lo) rows into the staged union (negative rows are never valid)
+        const unsigned char* local_a = win_a + static_cast<ptrdiff_t>(t - L + 1 - w_lo) * static_cast<ptrdiff_t>(key_row);
+        const unsigned char* local_p = win_p + static_cast<ptrdiff_t>(t - L + 1 - w_lo) * static_cast<ptrdiff_t>(key_row);
+        bool ok = true;
+        // ---- anchor
+        uint32_t bk = 0;
+        int bp = 0x7fffffff;
+        if (top > 0) {
+            if (n_complete > 16)
+                score_blocks_head<kBf16>(st[0], st[1], stats_dtype, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets,
+                                         arq, sp_a, bias_a, bscore, 0, 1);
+            else
+                score_blocks<kBf16>(st[0], st[1], stats_dtype, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets,
+                                    arq, sp_a, bias_a, bscore, 0, 1);
+        }
+        score_rows_split<kBf16, 1>(local_a, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, nullptr, 0, aq,
+                                   nullptr, 0, 0, 1, bk, bp, 0u, ok);
+        if (top > 0) {
+            __syncwarp();
+            pick_blocks(bscore, nb, top, bs, ls, sel);
+            uint32_t rk = 0;
+            int rp = 0x7fffffff;
+            score_rows_split<kBf16, 1, true>(static_cast<const unsigned char*>(a.anchor_keys) + seq_keys, key_dtype,
+                                             top * bs, sel, bs, 0, 0, -1, nullptr, 0, aq, nullptr, 0, 0, 1, rk, rp, 0u, ok);
+            if (rp != 0x7fffffff && (rk > bk || bp == 0x7fffffff || (rk == bk && rp < bp))) { bk = rk; bp = rp; }
+        }
+        int anchor_pos = bp;
+        if (anchor_pos == 0x7fffffff) { anchor_pos = 0; bk = float_key(kNegInf); }
+        if (lane == 0) {
+            a.out_anchor[row] = anchor_pos;
+            a.out_anchor_score[row] = key_float(bk);
+        }
+        // ---- partner queries: query-side base + the anchor's cached row
+        for (int i = lane; i < 2 * kD; i += 32) {
+            const float add = load_scalar(a.partner_anchor_cache,
+                                          (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * kD + i, key_dtype);
+            pq[i] = __fadd_rn(pq[i], add);
+        }
+        __syncwarp();
+        // ---- partners
+        uint32_t dk = 0;
+        int dp = 0x7fffffff;
+        if (top > 0) {
+            if (n_complete > 16)
+                score_blocks_head<kBf16>(st[2], st[3], stats_dtype, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets,
+                                         prq, sp_p, bias_p, bscore, 0, 1);
+            else
+                score_blocks<kBf16>(st[2], st[3], stats_dtype, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets,
+                                    prq, sp_p, bias_p, bscore, 0, 1);
+        }
+        score_rows_split<kBf16, 1>(local_p, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos, nullptr, 0, pq,
+                                   cand, 0, 0, 1, dk, dp, 0u, ok);
+        if (top > 0) {
+            __syncwarp();
+            pick_blocks(bscore, nb, top, bs, ls, sel);
+            score_rows_split<kBf16, 1, true>(static_cast<const unsigned char*>(a.partner_keys) + seq_keys, key_dtype,
+                                             top * bs, sel, bs, 0, 0, anchor_pos, nullptr, 0, pq, cand, L, 0, 1, dk, dp,
+                                             0u, ok);
+        }
+        __syncwarp();
+        int32_t* out_pos = a.out_partner + static_cast<size_t>(row) * K;
+        float* out_sc = a.out_partner_score + static_cast<size_t>(row) * K;
+        if (cap4 <= 128) topk_tournament<4>(cand, cap4, K, L, t, bs, bs_shift, sel, out_pos, out_sc);
+        else if (cap4 <= 256) topk_tournament<8>(cand, cap4, K, L, t, bs, bs_shift, sel, out_pos, out_sc);
+        else topk_tournament<16>(cand, cap4, K, L, t, bs, bs_shift, sel, out_pos, out_sc);
+        __syncwarp();
+    }
+}
+
+int tile_warp_bytes(const SelectArgs& a) {
+    const int cap4 = (a.local_window + a.top_blocks * a.block_size + 3) & ~3;
+    const int floats = 4 * kD + 8 + 8 * a.buckets + ((a.n_blocks + 3) & ~3) + cap4;
+    return align16(floats * 4 + 3 * (a.top_blocks > 0 ? a.top_blocks : 1) * 4) + 16;
+}
+
+int launch_tile(TileArgs& m, void* stream) {
+    SelectArgs& a = m.base;
+    if (a.n_seq < 1 || m.q_len < 1 || m.q_len > a.max_t || a.max_t < 1 || a.n_blocks < 1 || a.buckets < 1 ||
+        a.local_window < 1 || a.top_blocks < 0 || a.max_t % a.n_blocks != 0 || a.k_out < 1 || a.k_out > kMaxKOut) {
+        set_error("relation_select_packed_prefill: sizes must be positive, T a multiple of the block count, K <= 32, "
+                  "query length <= T");
+        return RLM_ERR_SHAPE;
+    }
+    if (!valid_dtype(a.query_dtype) || !valid_dtype(a.key_dtype) || !valid_dtype(a.stats_dtype) || !valid_dtype(a.param_dtype)) {
+        set_error("relation_select_packed_prefill: unknown dtype code");
+        return RLM_ERR_DTYPE;
+    }
+    const void* need[] = {a.anchor_query, a.anchor_keys, a.anchor_router_query, a.anchor_mean, a.anchor_std, a.anchor_gamma,
+                          a.anchor_bias, a.partner_base, a.partner_anchor_cache, a.partner_keys, a.partner_mean,
+                          a.partner_std, a.partner_gamma, a.partner_bias, a.out_anchor, a.out_anchor_score, a.out_partner,
+                          a.out_partner_score};
+    for (const void* q : need) if (!q) { set_error("relation_select_packed_prefill: NULL pointer"); return RLM_ERR_NULL; }
+    const void* bulk[] = {a.anchor_keys, a.anchor_mean, a.anchor_std, a.partner_keys, a.partner_mean, a.partner_std,
+                          a.partner_anchor_cache};
+    for (const void* q : bulk)
+        if (!aligned16(q)) {
+            set_error("relation_select_packed_prefill: key caches, block statistics and the partner-anchor cache must be 16-byte aligned");
+            return RLM_ERR_ALIGN;
+        }
+    a.block_size = a.max_t / a.n_blocks;
+    a.mode = kPacked;
+    const int cap = a.local_window + a.top_blocks * a.block_size;
+    if (cap > 512) {
+        set_error("relation_select_packed_prefill: at most 512 candidates per query (window + remote blocks)");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    m.warp_bytes = tile_warp_bytes(a);
+    m.stats_bytes = align16(a.n_blocks * kD * dtype_size(a.stats_dtype));
+    m.window_rows = a.local_window + kTileQ;
+    const int total = 4 * m.stats_bytes + 2 * m.window_rows * kD * dtype_size(a.key_dtype) + kWarps * m.warp_bytes;
+    if (total > kSmemDynamicLimit) {
+        set_error("relation_select_packed_prefill: block statistics + window union exceed 227 KB of shared memory");
+        return RLM_ERR_SMEM;
+    }
+    const bool bf16 = a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
+    auto kernel = bf16 ? relation_select_tile_kernel<true> : relation_select_tile_kernel<false>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    const int tiles = a.n_seq * ((m.q_len + kTileQ - 1) / kTileQ);
+    launch_kernel(kernel, dim3(tiles), dim3(kThreads), total, stream, m);
+    count_launch();
+    return check_launch("relation_select_tile_kernel");
+}
+
 int launch(SelectArgs& a, void* stream) {
     if (a.n_rows == 0) return RLM_OK;
     if (a.n_rows < 0 || a.n_seq < 1 || a.max_t < 1 || a.n_blocks < 1 || a.buckets < 1 ||
@@ -1160,6 +1389,32 @@ int launch_multi(MultiSelectArgs& m, void* stream) {
 
 }  // namespace
 }  // namespace rlm
+
+extern "C" int rlm_relation_select_packed_prefill(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    int32_t* out_anchor, float* out_anchor_score, int32_t* out_partner, float* out_partner_score,
+    int64_t anchor_query_stride, int64_t anchor_router_query_stride, int64_t partner_base_stride,
+    int n_seq, int query_length, int max_t, int n_blocks, int buckets, int local_window, int top_blocks, int k_out,
+    int strict_valid, int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status,
+    void* stream) {
+    rlm::TileArgs m{};
+    rlm::SelectArgs& a = m.base;
+    a.aq_stride = anchor_query_stride; a.arq_stride = anchor_router_query_stride; a.pbase_stride = partner_base_stride;
+    a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = anchor_router_query;
+    a.anchor_mean = anchor_mean; a.anchor_std = anchor_std; a.anchor_gamma = anchor_gamma; a.anchor_bias = anchor_bias;
+    a.partner_base = partner_base; a.partner_anchor_cache = partner_anchor_cache; a.partner_keys = partner_keys;
+    a.partner_mean = partner_mean; a.partner_std = partner_std; a.partner_gamma = partner_gamma; a.partner_bias = partner_bias;
+    a.out_anchor = out_anchor; a.out_anchor_score = out_anchor_score; a.out_partner = out_partner;
+    a.out_partner_score = out_partner_score; a.status = status;
+    a.n_rows = n_seq * query_length; a.n_seq = n_seq; a.max_t = max_t; a.n_blocks = n_blocks; a.buckets = buckets;
+    a.local_window = local_window; a.top_blocks = top_blocks; a.k_out = k_out; a.strict_valid = strict_valid != 0;
+    a.query_dtype = query_dtype; a.key_dtype = key_dtype; a.stats_dtype = stats_dtype; a.param_dtype = param_dtype;
+    m.q_len = query_length;
+    return rlm::launch_tile(m, stream);
+}
 
 extern "C" int rlm_relation_select_multi_rows(
     const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,

@@ -106,18 +106,31 @@ __device__ __forceinline__ void append_output(const SkinnyAppend& ap, int batch,
     conv = __fadd_rn(conv, __fmul_rn(__fmul_rn(prev2, w3[0]), t >= 2 ? 1.0f : 0.0f));
     raw_cache[base + static_cast<int64_t>(t) * 64] = bits;
     conv_cache[base + static_cast<int64_t>(t) * 64] = to16<kBf16>(conv);
+    // the block's rows are fetched sixteen at a time (independent loads in flight together), then
+    // folded in ascending order; the second pass finds them in L1
     const int cur = t - start;
+    const uint16_t* column = conv_cache + base + static_cast<int64_t>(start) * 64;
     float sum = 0.0f;
-    for (int r = 0; r < bs; ++r) {
-        const float x = r == cur ? conv : from16<kBf16>(conv_cache[base + static_cast<int64_t>(start + r) * 64]);
-        sum = __fadd_rn(sum, x);
+    for (int r0 = 0; r0 < bs; r0 += 16) {
+        uint16_t raw16[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw16[i] = r0 + i < bs ? column[static_cast<int64_t>(r0 + i) * 64] : 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (r0 + i < bs) sum = __fadd_rn(sum, r0 + i == cur ? conv : from16<kBf16>(raw16[i]));
     }
     const float mean = __fdiv_rn(sum, static_cast<float>(bs));
     float acc = 0.0f;
-    for (int r = 0; r < bs; ++r) {
-        const float x = r == cur ? conv : from16<kBf16>(conv_cache[base + static_cast<int64_t>(start + r) * 64]);
-        const float dv = __fsub_rn(x, mean);
-        acc = __fmaf_rn(dv, dv, acc);
+    for (int r0 = 0; r0 < bs; r0 += 16) {
+        uint16_t raw16[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw16[i] = r0 + i < bs ? column[static_cast<int64_t>(r0 + i) * 64] : 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (r0 + i < bs) {
+                const float dv = __fsub_rn(r0 + i == cur ? conv : from16<kBf16>(raw16[i]), mean);
+                acc = __fmaf_rn(dv, dv, acc);
+            }
     }
     const float sd = __fsqrt_rn(__fdiv_rn(acc, static_cast<float>(bs)));
     const int64_t stat = (seq * ap.n_blocks + blk) * 64 + ch;

@@ -28,7 +28,7 @@ from torch import Tensor
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels.packed_projection import layer_norm_cast, packed_projection
 from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows_out, relation_norm_reduce_rows
-from relation_lm.kernels.relation_select import relation_select_packed_rows
+from relation_lm.kernels.relation_select import relation_select_packed_prefill, relation_select_packed_rows
 from relation_lm.kernels.router_cache import router_cache_prefill
 
 
@@ -36,7 +36,8 @@ class RoutedPrefillLayer:
     """Layer ``layer`` of a ``RoutedRelationLM`` applied to whole sequences ``[B, T, d]``."""
 
     def __init__(self, model: RoutedRelationLM, layer: int = 0, device="cuda",
-                 dtype: torch.dtype = torch.bfloat16) -> None:
+                 dtype: torch.dtype = torch.bfloat16, tiled_select: bool = True) -> None:
+        self.tiled_select = bool(tiled_select)
         if dtype not in (torch.bfloat16, torch.float16):
             raise ValueError("the prefill path runs its projections on the tensor cores: bfloat16 or float16")
         self.config, self.layer, self.device, self.dtype = model.config, int(layer), torch.device(device), dtype
@@ -105,11 +106,17 @@ class RoutedPrefillLayer:
         normalized = torch.empty(N, d, device=self.device, dtype=self.dtype)
         layer_norm_cast(x.view(N, d), w["input_norm_w"], w["input_norm_b"], cfg.norm_eps, normalized)
         q = packed_projection(normalized, w["w_query"])
-        anchor, anchor_score, partner, partner_score = relation_select_packed_rows(
-            q[:, 0:64], state["anchor_keys"], q[:, 64:128], state["anchor_mean"], state["anchor_std"],
-            w["anchor_gamma"], w["anchor_bias"], q[:, 128:256], state["partner_anchor_cache"],
-            state["partner_keys"], state["partner_mean"], state["partner_std"], w["partner_gamma"],
-            w["partner_bias"], rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+        select_args = (q[:, 0:64], state["anchor_keys"], q[:, 64:128], state["anchor_mean"], state["anchor_std"],
+                       w["anchor_gamma"], w["anchor_bias"], q[:, 128:256], state["partner_anchor_cache"],
+                       state["partner_keys"], state["partner_mean"], state["partner_std"], w["partner_gamma"],
+                       w["partner_bias"])
+        if self.tiled_select and cfg.local_window + cfg.top_blocks * cfg.block_size <= 512:
+            # all positions of every sequence: tiles of consecutive positions share their staging
+            anchor, anchor_score, partner, partner_score = relation_select_packed_prefill(
+                *select_args, T, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+        else:
+            anchor, anchor_score, partner, partner_score = relation_select_packed_rows(
+                *select_args, rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
         hidden_rel = torch.empty(N, K, H, device=self.device, dtype=self.dtype)
         relation_hidden_cached_rows_out(hidden_rel, state["expanded_cache"], state["operand_cache"], anchor,
                                         partner, w["product_weight"], rb)

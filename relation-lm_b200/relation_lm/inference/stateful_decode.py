@@ -44,7 +44,8 @@ class StatefulDecoder:
     def __init__(self, model: RoutedRelationLM, batch: int, device="cuda",
                  dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
                  programmatic_launch: bool = True, second_layer_split: bool = False,
-                 fused_query: bool | None = None, layer_tail: bool | None = None) -> None:
+                 fused_query: bool | None = None, layer_tail: bool | None = None,
+                 skinny: bool | None = None, append_in_projection: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -107,7 +108,12 @@ class StatefulDecoder:
             self.query = zeros(B, n_query)
         # Projections of a handful of rows stream their weights through the CUDA cores (no tensor-memory
         # set-up); the head's launch then also takes the greedy arg-max and the position increment.
-        self.skinny = self.fused and skinny_projection_supported(B, cfg.d_model, dtype)
+        can_skinny = self.fused and skinny_projection_supported(B, cfg.d_model, dtype)
+        self.skinny = can_skinny if skinny is None else (bool(skinny) and can_skinny)
+        # ... and the packed projection can take the cache append and router update into its epilogue
+        # (one launch fewer; off by default: the channels' serial statistics in the epilogue cost more
+        # than the separate, fully parallel append launch that overlaps its neighbours)
+        self.append_in_projection = bool(append_in_projection) and self.skinny
         self._project = skinny_projection if self.skinny else packed_projection
         if self.skinny:
             self.argmax_scratch = torch.zeros(skinny_argmax_scratch_bytes(), device=self.device, dtype=torch.uint8)
@@ -220,7 +226,7 @@ class StatefulDecoder:
                                    w["position_embedding"], pos, self.input_scale,
                                    w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
                                    w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
-        if self.skinny:
+        if self.append_in_projection:
             # the packed projection's epilogue writes the token caches and updates the router state
             packed = packed_projection_append(self.memory_normalized, w["w_packed"], self.anchor_keys,
                                               self.partner_keys, self.operand_cache, self.partner_anchor_cache,

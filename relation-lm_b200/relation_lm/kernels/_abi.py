@@ -35,6 +35,7 @@ PROTOTYPES = {
     "rlm_decode_embed": [_P] * 6 + [_F, _P] + [_I] * 6 + [_P] * 6 + [_F, _I] + [_P, _P],
     "rlm_sparse_cache_append": [_P, _L, _I] + [_P] * 16 + [_I] * 9 + [_P, _P],
     "rlm_selftest_bounded_wait": [_P, _L, _P, _P],
+    "rlm_relation_select_packed_prefill": [_P] * 18 + [_L] * 3 + [_I] * 13 + [_P, _P],
     "rlm_relation_select_multi_rows": [_P] * 21 + [_L] * 3 + [_I] * 14 + [_P, _P],
     "rlm_slot_mix_residual": [_P] * 5 + [_I] * 3 + [_P],
     "rlm_skinny_projection": [_P, _L, _P, _P, _P] + [_I] * 5 + [_P] * 4,

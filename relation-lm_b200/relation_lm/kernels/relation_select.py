@@ -155,3 +155,78 @@ def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_
             anchor_query.new_empty((rows,), dtype=torch.float32),
             anchor_query.new_empty((rows, k_out), dtype=torch.int32),
             anchor_query.new_empty((rows, k_out), dtype=torch.float32))
+
+
+@torch.library.custom_op("relation_lm::relation_select_packed_prefill", mutates_args=(), device_types="cuda")
+def relation_select_packed_prefill(
+    anchor_query: Tensor,
+    anchor_keys: Tensor,
+    anchor_router_query: Tensor,
+    anchor_block_mean: Tensor,
+    anchor_block_std: Tensor,
+    anchor_gamma: Tensor,
+    anchor_bias: Tensor,
+    partner_base: Tensor,
+    partner_anchor_cache: Tensor,
+    partner_keys: Tensor,
+    partner_block_mean: Tensor,
+    partner_block_std: Tensor,
+    partner_gamma: Tensor,
+    partner_bias: Tensor,
+    query_length: int,
+    local_window: int,
+    top_blocks: int,
+    k_out: int,
+    strict_valid: bool,
+) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """Whole-sequence form (extension): the queries are rows ``b * query_length + t`` for every
+    position ``t < query_length`` of every sequence ``b`` of caches ``[B, T, ...]``; row ``(b, t)``
+    equals ``relation_select_packed`` at ``position = t`` on sequence ``b`` (given final block
+    statistics), bit for bit.  A CTA serves a tile of consecutive positions: their shared block
+    statistics and the union of their local windows are staged once, and every warp walks one
+    query's chain at a time.  At most 512 candidates per query (window + remote blocks)."""
+    _abi.require_cuda_rows(anchor_query=anchor_query, anchor_router_query=anchor_router_query,
+                           partner_base=partner_base)
+    device = _abi.require_cuda_contiguous(
+        anchor_keys=anchor_keys, anchor_block_mean=anchor_block_mean, anchor_block_std=anchor_block_std,
+        anchor_gamma=anchor_gamma, anchor_bias=anchor_bias, partner_anchor_cache=partner_anchor_cache,
+        partner_keys=partner_keys, partner_block_mean=partner_block_mean, partner_block_std=partner_block_std,
+        partner_gamma=partner_gamma, partner_bias=partner_bias)
+    n_seq, max_t = anchor_keys.size(0), anchor_keys.size(1)
+    rows = n_seq * int(query_length)
+    if anchor_query.shape != (rows, 64) or anchor_router_query.shape != (rows, 64) or partner_base.shape != (rows, 128):
+        raise ValueError("queries must hold one row per (sequence, position): [B * query_length, width]")
+    if anchor_block_mean.size(2) * anchor_block_mean.size(3) != 64 or anchor_block_mean.size(3) != 16:
+        raise ValueError("this build supports gate width 64 with 4 router heads of width 16")
+    query_dtype = _abi.same_dtype("query", anchor_query, anchor_router_query, partner_base)
+    key_dtype = _abi.same_dtype("key cache", anchor_keys, partner_keys, partner_anchor_cache)
+    stats_dtype = _abi.same_dtype("block statistics", anchor_block_mean, anchor_block_std,
+                                  partner_block_mean, partner_block_std)
+    param_dtype = _abi.same_dtype("gamma/bias", anchor_gamma, anchor_bias, partner_gamma, partner_bias)
+    out_anchor = torch.empty((rows,), device=device, dtype=torch.int32)
+    out_anchor_score = torch.empty((rows,), device=device, dtype=torch.float32)
+    out_partner = torch.empty((rows, k_out), device=device, dtype=torch.int32)
+    out_partner_score = torch.empty((rows, k_out), device=device, dtype=torch.float32)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_select_packed_prefill(
+            _abi.ptr(anchor_query), _abi.ptr(anchor_keys), _abi.ptr(anchor_router_query),
+            _abi.ptr(anchor_block_mean), _abi.ptr(anchor_block_std), _abi.ptr(anchor_gamma),
+            _abi.ptr(anchor_bias), _abi.ptr(partner_base), _abi.ptr(partner_anchor_cache),
+            _abi.ptr(partner_keys), _abi.ptr(partner_block_mean), _abi.ptr(partner_block_std),
+            _abi.ptr(partner_gamma), _abi.ptr(partner_bias), _abi.ptr(out_anchor), _abi.ptr(out_anchor_score),
+            _abi.ptr(out_partner), _abi.ptr(out_partner_score), anchor_query.stride(0),
+            anchor_router_query.stride(0), partner_base.stride(0), n_seq, int(query_length), max_t,
+            anchor_block_mean.size(1), anchor_bias.size(1), int(local_window), int(top_blocks), int(k_out),
+            int(bool(strict_valid)), query_dtype, key_dtype, stats_dtype, param_dtype,
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return out_anchor, out_anchor_score, out_partner, out_partner_score
+
+
+@relation_select_packed_prefill.register_fake
+def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_block_std, anchor_gamma,
+      anchor_bias, partner_base, partner_anchor_cache, partner_keys, partner_block_mean, partner_block_std,
+      partner_gamma, partner_bias, query_length, local_window, top_blocks, k_out, strict_valid):
+    rows = anchor_query.size(0)
+    return (anchor_query.new_empty((rows,), dtype=torch.int32), anchor_query.new_empty((rows,), dtype=torch.float32),
+            anchor_query.new_empty((rows, k_out), dtype=torch.int32),
+            anchor_query.new_empty((rows, k_out), dtype=torch.float32))

@@ -7,7 +7,7 @@ import torch
 
 import cases
 import oracle
-from gpu_util import (assert_scores_equal, assert_status_clear, position_tensor, select_args,
+from gpu_util import (SELECT_KEYS, assert_scores_equal, assert_status_clear, position_tensor, select_args,
                       to_cuda)
 
 pytestmark = pytest.mark.gpu
@@ -299,4 +299,41 @@ def test_a_bounded_wait_that_expires_reports_timeout_and_leaves_the_context_usab
     got = relation_select_packed(*select_args(to_cuda(x)), position_tensor(300), 64, 2, 8, False)
     want = oracle.relation_select(*select_args(x), 300, 64, 2, 8, False)
     assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[2].cpu(), want[2])
+    assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+@pytest.mark.parametrize("context,blocks,local_window,top_blocks,k_out,strict,query_length", [
+    (256, 8, 64, 2, 8, False, 256),       # block 32, window 64
+    (256, 8, 64, 2, 8, True, 256),
+    (128, 8, 32, 0, 5, False, 128),       # no remote blocks
+    (512, 8, 128, 4, 8, False, 500),      # block 64, window 128, 384 candidates; ragged last tile
+    (192, 24, 16, 3, 4, True, 70),        # block 8, more than 16 blocks, queries for a prefix only
+])
+def test_whole_sequence_selector_equals_the_per_row_selector(context, blocks, local_window, top_blocks, k_out,
+                                                             strict, query_length, dtype):
+    """Tiles of consecutive positions (shared staging, a query per warp) against the per-row form: all
+    four outputs bit for bit at every position of every sequence, and the oracle on a sample."""
+    from relation_lm.kernels.relation_select import relation_select_packed_prefill, relation_select_packed_rows
+
+    B = 3
+    case = {"kind": "select", "seed": 8800 + context + top_blocks, "batch": B, "context": context, "blocks": blocks,
+            "rows": B * query_length, "local_window": local_window, "top_blocks": top_blocks, "k_out": k_out,
+            "strict_valid": strict, "dtype": dtype, "quantize": dtype == "fp32"}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(query_length)
+    row_pos = torch.arange(query_length, dtype=torch.int32).repeat(B)
+    tiled = relation_select_packed_prefill(*select_args(xg), query_length, local_window, top_blocks, k_out, strict)
+    rows = relation_select_packed_rows(*select_args(xg), row_batch.cuda(), row_pos.cuda(), local_window, top_blocks,
+                                       k_out, strict)
+    for mine, theirs in zip(tiled, rows):
+        assert torch.equal(mine.view(torch.int32), theirs.view(torch.int32))
+    sample = torch.arange(0, B * query_length, 7)
+    want = oracle.relation_select(*[x[k][sample] if x[k].size(0) == B * query_length and k in
+                                    ("anchor_query", "anchor_router_query", "partner_base") else x[k]
+                                    for k in SELECT_KEYS], 0, local_window, top_blocks, k_out, strict,
+                                  row_batch=row_batch[sample], row_pos=row_pos[sample])
+    assert torch.equal(tiled[0].cpu()[sample], want[0]) and torch.equal(tiled[2].cpu()[sample], want[2])
+    assert_scores_equal(tiled[3][sample.cuda()], want[3])
     assert_status_clear()
