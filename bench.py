@@ -1211,6 +1211,42 @@ def run_kernel_case(args) -> None:
                 w_packed = rn(12 * (384 + R), d) * 0.02          # the 12-layer packed projection matrix
             x = S[i % sets]
             fn = lambda: packed_projection(x, w_packed)  # noqa: E731
+        elif args.kernel_case == "tail":
+            if i == 0:
+                from relation_lm.kernels.relation_reduce import relation_layer_tail
+                Bt, Tt, dt_, Ht = min(B, 64), 512, 512, 2048     # the 6-layer decode configuration's layer
+                S = [(rn(Bt, Tt, 2 * Ht), rn(Bt, Tt, R), rn(Ht, R) * 0.05, rn(dt_, Ht) * 0.03, rn(256, dt_) * 0.05)
+                     for _ in range(sets)]
+                b2, gm, bt = rn(dt_) * 0.1, torch.ones(dt_, device=dev), torch.zeros(dt_, device=dev)
+                ai = torch.randint(0, Tt, (Bt,), device=dev, dtype=torch.int32)
+                pi = torch.randint(0, Tt, (Bt, K), device=dev, dtype=torch.int32)
+                sc = torch.randn(Bt, K, device=dev)
+                residual, mix = torch.randn(Bt, dt_, device=dev), torch.tensor(0.2, device=dev)
+                normalized, query = rn(Bt, dt_), rn(Bt, 256)
+                pos = torch.tensor(Tt - 1, device=dev)
+            ex, op, wm, w2, wq = S[i % sets]
+            fn = lambda: relation_layer_tail(ex, op, ai, pi, sc, wm, w2, b2, gm, bt, pos, 1e-5, residual, mix,  # noqa: E731
+                                             gm, bt, 1e-5, normalized, wq, query)
+        elif args.kernel_case == "head":
+            if i == 0:
+                from relation_lm.kernels.packed_projection import skinny_argmax_scratch_bytes, skinny_projection_greedy
+                Bh = min(B, 16)
+                S = [rn(16640, 512) * 0.05 for _ in range(sets)]          # vocabulary + boundary heads, d 512
+                xh, bias = rn(Bh, 512), torch.zeros(16640, device=dev)
+                scratch = torch.zeros(skinny_argmax_scratch_bytes(), dtype=torch.uint8, device=dev)
+                posh = torch.zeros((), dtype=torch.int64, device=dev)
+            wh = S[i % sets]
+            fn = lambda: skinny_projection_greedy(xh, wh, bias, 16000, scratch, posh)  # noqa: E731
+        elif args.kernel_case == "select_tile":
+            if i == 0:
+                from relation_lm.kernels.relation_select import relation_select_packed_prefill
+                Bs, Ts, nbs = 8, 4096, 64                              # the long-context configuration
+                S = [(rn(Bs, Ts, 64), rn(Bs, Ts, 64), rn(Bs, Ts, 128), rn(Bs, nbs, 4, 16), rn(Bs, nbs, 4, 16).abs(),
+                      rn(Bs, nbs, 4, 16), rn(Bs, nbs, 4, 16).abs()) for _ in range(2)]
+                q, g, bias = rn(Bs * Ts, 256), torch.randn(4, device=dev), torch.randn(4, 16, device=dev)
+            ak, pk, pac, am, as_, pm, ps = S[i % 2]
+            fn = lambda: relation_select_packed_prefill(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:],  # noqa: E731
+                                                        pac, pk, pm, ps, g, bias, Ts, 128, 4, K, False)
         elif args.kernel_case == "norm":
             if i == 0:
                 S = [rn(B, K, d) for _ in range(sets)]
@@ -1254,7 +1290,8 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=None, help="sequences per GPU")
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
-    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router"),
+    parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router",
+                                                 "tail", "head", "select_tile"),
                         default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")

@@ -341,7 +341,7 @@ int launch_hidden_as(const HiddenArgs& a, void* stream) {
     const int tiles = (a.hdim + kHT - 1) / kHT;
     const int groups = (a.n_rows + kRB - 1) / kRB;
     // a few CTAs per SM; beyond that a CTA keeps its weight tiles and walks several groups
-    int gy = (148 * 4 + tiles - 1) / tiles;
+    int gy = (sm_count() * 4 + tiles - 1) / tiles;
     if (gy > groups) gy = groups;
     dim3 grid(tiles, gy);
     launch_kernel(kernel, dim3(grid), dim3(kHiddenThreads), smem_bytes, stream, a);
@@ -969,7 +969,8 @@ extern "C" int rlm_slot_mix_residual(const float* slot_context, const uint8_t* a
         return RLM_ERR_ALIGN;
     }
     const int64_t work = static_cast<int64_t>(n_rows) * (d_model / 4);
-    const int blocks = static_cast<int>(work / 256 + 1 < 148 * 8 ? work / 256 + 1 : 148 * 8);
+    const int64_t most = static_cast<int64_t>(sm_count()) * 8;
+    const int blocks = static_cast<int>(work / 256 + 1 < most ? work / 256 + 1 : most);
     launch_kernel(slot_mix_residual_kernel, dim3(blocks), dim3(256), 0, stream, slot_context, anchor_active,
                   slot_weight, gate, hidden, n_rows, slots, d_model);
     count_launch();

@@ -73,6 +73,7 @@ struct SelectArgs {
     int query_dtype, key_dtype, stats_dtype, param_dtype;
     int mode;
     int shared_streams;                  // the partner's staging buffers alias the anchor's (see make_plan)
+    int sm_count;                        // streaming multiprocessors of the device the launch goes to
     Plan plan;
 };
 
@@ -231,8 +232,8 @@ __device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dt
                                            const int* sel, int bs, int first_valid, int pos0,
                                            int exclude, const int* excl, int n_excl, const float* query,
                                            float* cand, int slot0, int wi, int nw, uint32_t& best_key,
-                                           int& best_pos, uint32_t bar, bool& arrived) {
-    const int lanes = gridDim.x <= 148 ? 32 * nw : 0;   // a row per lane when CTAs share the SMs: fewer instructions in total
+                                           int& best_pos, uint32_t bar, bool& arrived, int sm_count_arg) {
+    const int lanes = static_cast<int>(gridDim.x) <= sm_count_arg ? 32 * nw : 0;   // a row per lane when CTAs share the SMs: fewer instructions in total
     if (4 * n_rows <= lanes)
         score_rows_split<kBf16, 4>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
                                    query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
@@ -789,7 +790,7 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
                                     a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
             score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
-                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok);
+                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok, a.sm_count);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
         if (a.shared_streams && tid == kThreads - 1) {
@@ -824,7 +825,7 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
             bp = 0x7fffffff;
             // each warp works out its rows' positions first and only then waits for the copies
             score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
-                       nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok);
+                       nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok, a.sm_count);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             if (__syncthreads_or(!ok)) {
                 if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
@@ -877,7 +878,7 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
                                 a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
         score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
-                   excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp);
+                   excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp, a.sm_count);
     __syncthreads();
     if (top > 0) {
         if (warp == 0) {
@@ -896,7 +897,7 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
         __syncthreads();
         bool ok = true;
         score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
-                   cand, L, warp, kWarps, dk, dp, bar_rp, ok);
+                   cand, L, warp, kWarps, dk, dp, bar_rp, ok, a.sm_count);
         if (__syncthreads_or(!ok)) {
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
@@ -1307,7 +1308,8 @@ int launch(SelectArgs& a, void* stream) {
     // More rows than the SMs hold at once: rows in flight set the throughput, so the packed
     // selector stages the two streams one after the other in the same buffers and the build
     // with the smaller register budget runs.
-    constexpr int kSms = 148;
+    const int kSms = sm_count();
+    a.sm_count = kSms;
     const int resident = kSmemPerCta / (a.plan.total + 1024 + 2304);
     const bool many_rows = a.n_rows > kSms * (resident < 3 ? resident : 3);
     if (many_rows && a.mode == kPacked) {
@@ -1360,6 +1362,7 @@ int launch_multi(MultiSelectArgs& m, void* stream) {
         }
     a.block_size = a.max_t / a.n_blocks;
     a.shared_streams = 0;
+    a.sm_count = sm_count();
     const int ks = dtype_size(a.key_dtype), ss = dtype_size(a.stats_dtype), ps = dtype_size(a.param_dtype);
     m.plan_anchor = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets, ks, ss, kAnchorOnly, false);
     m.plan_partner = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets, ks, ss, kPartnerOnly, false);

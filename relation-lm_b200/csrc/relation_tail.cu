@@ -278,7 +278,7 @@ int launch_relation_tail(const void* hidden, const void* w2, TailArgs& a, int hi
     const int n_tiles = a.d / kTailBN;
     const int total_blocks = (a.h + kBK - 1) / kBK;
     // enough K-splits for about one CTA per SM, at most eight ring stages' worth of work each
-    int splits = (148 + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
+    int splits = (sm_count() + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
     if (splits > total_blocks) splits = total_blocks;
     if (splits < 1) splits = 1;
     a.k_blocks_per_split = (total_blocks + splits - 1) / splits;

@@ -26,6 +26,21 @@ void set_error(const char* message) {
 thread_local int g_programmatic = 0;
 bool programmatic_launch_enabled() { return g_programmatic != 0; }
 
+int sm_count() {
+    static std::atomic<int> cached[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) { cudaGetLastError(); return 148; }
+    int n = cached[device].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = 148;
+        }
+        cached[device].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int check_launch(const char* kernel_name) {

@@ -18,6 +18,9 @@ int check_launch(const char* kernel_name);    // cudaGetLastError -> rlm_status
 // Opts a kernel into `bytes` of dynamic shared memory, once per device.
 int allow_large_smem(const void* kernel, int bytes);
 
+// Streaming multiprocessors of the current device (queried once per device; 148 on a B200).
+int sm_count();
+
 // Whether kernels are launched with programmatic stream serialisation (rlm_set_programmatic_launch).
 bool programmatic_launch_enabled();
 

@@ -274,7 +274,7 @@ int launch_skinny(const SkinnyArgs& a, const SkinnyAppend* append, void* stream)
     const int smem = (kUpper ? 16 : 8) * (a.d * 2 + 64);
     // a warp per group of eight columns while they last, at most four CTAs per SM
     int ctas = (a.groups + kSkWarps - 1) / kSkWarps;
-    if (ctas > 4 * 148) ctas = 4 * 148;
+    if (ctas > 4 * sm_count()) ctas = 4 * sm_count();
     launch_kernel(kernel, dim3(ctas), dim3(kSkThreads), smem, stream, a, ap);
     count_launch();
     return check_launch("skinny_projection_kernel");
