@@ -397,6 +397,38 @@ int rlm_relation_layer_tail(
     int hidden_dim, int d_model, int n_query, int dtype, int32_t* status, void* stream);
 
 /*
+ * A whole relation layer of a decode step in one launch (extension): rlm_relation_select_packed in
+ * its decode form (one query row per sequence, all at *position) followed by
+ * rlm_relation_layer_tail, in the tail's cluster.  The first CTAs of a cluster each select for one
+ * of the cluster's sequences, in the shared memory the tail's tiles occupy from the gathers on,
+ * while the weight slices stream in; the indices and scores are written to the out_* arrays
+ * (results identical to the two separate calls, bit for bit) and handed to the tail through a
+ * cluster barrier.
+ * Arguments: the selector's (see rlm_relation_select_packed; queries, caches and block statistics
+ * in `dtype`, router parameters in `param_dtype`), then the tail's.  Supported when the tail is,
+ * the selector's working set (block statistics, local window, remote blocks) fits the tile memory
+ * (about 45 KB at relation width 64, 53 KB at 128); rlm_relation_layer_supported() answers 1 then, and rlm_relation_layer returns
+ * RLM_ERR_UNSUPPORTED otherwise (use the two launches).
+ */
+int rlm_relation_layer_supported(int n_seq, int k_out, int relation_dim, int hidden_dim, int d_model,
+                                 int n_query, int dtype, int max_t, int n_blocks, int buckets,
+                                 int local_window, int top_blocks);
+int rlm_relation_layer(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    const int64_t* position, int32_t* out_anchor, float* out_anchor_score, int32_t* out_partner,
+    float* out_partner_score, int64_t anchor_query_stride, int64_t anchor_router_query_stride,
+    int64_t partner_base_stride, int n_blocks, int buckets, int local_window, int top_blocks, int strict_valid,
+    int param_dtype,
+    const void* expanded_cache, const void* operand_cache, const void* product_weight, const void* second_weight,
+    const void* second_bias, const float* norm_weight, const float* norm_bias, float norm_eps, float* residual,
+    const float* mix, const float* next_norm_weight, const float* next_norm_bias, float next_norm_eps,
+    void* normalized, const void* query_weight, void* query, int n_seq, int k_out, int max_t, int relation_dim,
+    int hidden_dim, int d_model, int n_query, int dtype, int32_t* status, void* stream);
+
+/*
  * rlm_relation_tail for callers that cannot hand over scratch memory.  This entry point has no
  * counterpart in the reference project.
  *

@@ -37,6 +37,7 @@ from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation
                                                  relation_norm_reduce,
                                                  relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
+from relation_lm.kernels.relation_layer import relation_layer, relation_layer_supported
 from relation_lm.kernels.router_cache import packed_projection_append, sparse_cache_append
 
 
@@ -45,7 +46,8 @@ class StatefulDecoder:
                  dtype: torch.dtype = torch.bfloat16, fused_tail: bool = False,
                  programmatic_launch: bool = True, second_layer_split: bool = False,
                  fused_query: bool | None = None, layer_tail: bool | None = None,
-                 skinny: bool | None = None, append_in_projection: bool | None = None) -> None:
+                 skinny: bool | None = None, append_in_projection: bool | None = None,
+                 whole_layer: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -106,6 +108,13 @@ class StatefulDecoder:
             self.fused_query = False
         if self.fused_query or self.layer_tail:
             self.query = zeros(B, n_query)
+        # ... and the selector can run in front of the tail inside the same cluster: one launch per layer.
+        # Off by default: with the step's working set cold in L2 it measured 3-5 % slower than the two
+        # launches (equal when warm), whose selector overlaps the tail's weight loads just as well.
+        can_whole = self.layer_tail and relation_layer_supported(
+            B, cfg.k_max, R, H, cfg.d_model, n_query, dtype, T, nb, self.w["anchor_bias"].shape[-1],
+            cfg.local_window, cfg.top_blocks)
+        self.whole_layer = bool(whole_layer) and can_whole
         # Projections of a handful of rows stream their weights through the CUDA cores (no tensor-memory
         # set-up); the head's launch then also takes the greedy arg-max and the position increment.
         can_skinny = self.fused and skinny_projection_supported(B, cfg.d_model, dtype)
@@ -214,7 +223,8 @@ class StatefulDecoder:
     def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True,
                     greedy: bool = False):
         """The same step with the elementwise glue folded into the library's kernels:
-        2 launches per layer with the single-launch relation tail (select, tail), otherwise up to 5
+        1 launch per layer where the selector fits in front of the single-launch relation tail, 2
+        (select, tail) where only the tail applies, otherwise up to 5
         (query projection, select, relation hidden, second MLP layer GEMM, norm-reduce + residual +
         next LayerNorm).  Every LayerNorm is
         computed by the kernel that produces its input (the embedding, the residual update) and
@@ -254,6 +264,31 @@ class StatefulDecoder:
             # written by the previous layer's norm-reduce when that fusion is on
             q = self.query if ((self.fused_query or self.layer_tail) and l > 0) \
                 else self._project(self.normalized, w["w_query"][l])
+            last = l + 1 == cfg.layers
+            next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]
+            next_b = w["final_norm_b"] if last else w["input_norm_b"][l + 1]
+            if self.whole_layer:
+                if trace is not None:
+                    entry = {"stage": "layer", "layer": l, "query": q.clone(), "hidden_before": hidden.clone()}
+                    trace.append(entry)
+                anchor, _, partner, partner_score = relation_layer(
+                    q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
+                    self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
+                    self.partner_anchor_cache[l], self.partner_keys[l], self.router_stats[2][l],
+                    self.router_stats[3][l], w["partner_gamma"][l], w["partner_bias"][l], pos,
+                    cfg.local_window, cfg.top_blocks, K, cfg.strict_valid,
+                    self.expanded_cache[l], self.operand_cache[l], w["product_weight"][l], w["w2"][l], w["b2"][l],
+                    w["relation_norm_w"][l], w["relation_norm_b"][l], cfg.norm_eps, hidden, w["mix"][l], next_w,
+                    next_b, cfg.norm_eps, self.normalized, None if last else w["w_query"][l + 1],
+                    None if last else self.query)
+                if trace is not None:
+                    entry.update(anchor=anchor.clone(), partner=partner.clone(), partner_score=partner_score.clone(),
+                                 hidden_after=hidden.clone(), next_normalized=self.normalized.clone())
+                    if not last:
+                        entry["next_query"] = self.query.clone()
+                if keep_selection:
+                    self.last_selection.append((anchor, partner))
+                continue
             anchor, _, partner, partner_score = relation_select_packed(
                 q[:, 0:64], self.anchor_keys[l], q[:, 64:128], self.router_stats[0][l],
                 self.router_stats[1][l], w["anchor_gamma"][l], w["anchor_bias"][l], q[:, 128:256],
@@ -265,9 +300,6 @@ class StatefulDecoder:
                          "partner": partner.clone(), "partner_score": partner_score.clone(),
                          "hidden_before": hidden.clone()}
                 trace.append(entry)
-            last = l + 1 == cfg.layers
-            next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]
-            next_b = w["final_norm_b"] if last else w["input_norm_b"][l + 1]
             if self.layer_tail:
                 relation_layer_tail(self.expanded_cache[l], self.operand_cache[l], anchor, partner, partner_score,
                                     w["product_weight"][l], w["w2"][l], w["b2"][l], w["relation_norm_w"][l],

@@ -42,6 +42,9 @@ PROTOTYPES = {
     "rlm_packed_projection_append": [_P, _L, _P, _P, _I] + [_P] * 15 + [_I] * 7 + [_P, _P],
     "rlm_relation_layer_tail_supported": [_I] * 7,
     "rlm_relation_layer_tail": [_P] * 11 + [_F, _P, _P, _P, _P, _F, _P, _P, _P] + [_I] * 8 + [_P, _P],
+    "rlm_relation_layer_supported": [_I] * 12,
+    "rlm_relation_layer": [_P] * 19 + [_L] * 3 + [_I] * 6 + [_P] * 7 + [_F, _P, _P, _P, _P, _F, _P, _P, _P]
+                          + [_I] * 8 + [_P, _P],
 }
 
 

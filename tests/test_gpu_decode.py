@@ -307,3 +307,35 @@ def test_single_launch_layer_tail_decode_tracks_the_multi_launch_step():
             assert torch.allclose(a[0].float(), b[0].float(), atol=0.25, rtol=0.05), t
     assert agree >= steps - 3
     assert_status_clear()
+
+
+def test_one_launch_per_layer_equals_select_then_tail_bit_for_bit():
+    """The selector run in front of the tail inside the tail's cluster changes no arithmetic: logits
+    and selections of every step equal those of the two-launch form."""
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    cfg = RoutedRelationConfig()
+    model = RoutedRelationLM(cfg, seed=77)
+    B, steps = 5, 80
+    g = torch.Generator().manual_seed(78)
+    tokens = torch.randint(0, cfg.vocab_size, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (B, steps), generator=g).cuda()
+    two = StatefulDecoder(model, B, "cuda", torch.bfloat16, whole_layer=False)
+    one = StatefulDecoder(model, B, "cuda", torch.bfloat16, whole_layer=True)
+    if not one.whole_layer:
+        pytest.skip("the one-launch layer is not available for this configuration on this device")
+    assert two.layer_tail and not two.whole_layer
+    graphed = StatefulDecoder(model, B, "cuda", torch.bfloat16, whole_layer=True)
+    graphed.capture()
+    for t in range(steps):
+        a = two.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        b = one.step(tokens[:, t], bounds[:, t], keep_selection=True)
+        graphed.static_tokens.copy_(tokens[:, t])
+        graphed.static_boundaries.copy_(bounds[:, t])
+        graphed.replay()
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), t
+        assert torch.equal(b[0], graphed.static_token_logits), t
+        for (pa, pp), (sa, sp_) in zip(two.last_selection, one.last_selection):
+            assert torch.equal(pa, sa) and torch.equal(pp, sp_), t
+    assert_status_clear()

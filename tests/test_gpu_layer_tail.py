@@ -98,3 +98,78 @@ def test_layer_tail_rejects_shapes_it_does_not_serve():
     x = _case(2, 8, 768, 128, 16, 0, torch.bfloat16, 1)
     with pytest.raises(ValueError):
         _run(x, 5, torch.bfloat16)
+
+
+# ---- the selector in front of the tail, one launch for the layer
+
+def _layer_case(B, K, d, R, T, NB, L, top, n_query, dtype, seed):
+    import cases
+
+    name = {torch.bfloat16: "bf16", torch.float16: "fp16"}[dtype]
+    sel = cases.make_inputs({"kind": "select", "seed": seed, "batch": B, "context": T, "blocks": NB,
+                             "local_window": L, "top_blocks": top, "k_out": K, "strict_valid": True, "dtype": name})
+    tail = _case(B, K, d, R, T, n_query, dtype, seed + 1)
+    return sel, tail
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,K,d,R,T,NB,L,top,n_query", [
+    (8, 8, 512, 128, 512, 16, 64, 2, 256),      # the ctx-512 decode configuration's layer
+    (1, 8, 512, 128, 512, 16, 64, 2, 256),
+    (5, 8, 256, 128, 256, 8, 32, 2, 256),       # clusters of 8 CTAs
+    (3, 4, 128, 64, 128, 8, 16, 1, 0),          # clusters of 4 CTAs, relation width 64
+    (32, 4, 128, 64, 128, 8, 16, 1, 64),        # 8 clusters of 4 CTAs, a selecting CTA per sequence
+])
+def test_whole_layer_equals_select_then_tail(B, K, d, R, T, NB, L, top, n_query, dtype):
+    from gpu_util import select_args, to_cuda
+    from relation_lm.kernels.relation_layer import relation_layer, relation_layer_supported
+    from relation_lm.kernels.relation_reduce import relation_layer_tail
+    from relation_lm.kernels.relation_select import relation_select_packed
+
+    sel, x = _layer_case(B, K, d, R, T, NB, L, top, n_query, dtype, 6200 + B + d)
+    buckets = sel["anchor_bias"].size(1)
+    if not relation_layer_supported(B, K, R, 4 * d, d, n_query, dtype, T, NB, buckets, L, top):
+        pytest.skip("the selector does not fit in front of the tail for these sizes on this device")
+    sg, dev = to_cuda(sel), to_cuda(x)
+    for t in (0, 1, L - 1, T // 2 + 3, T - 1):
+        pos = position_tensor(t)
+        a, a_s, p, p_s = relation_select_packed(*select_args(sg), pos, L, top, K, True)
+        want_hidden = dev["hidden"].clone()
+        want_norm = torch.zeros(B, d, device="cuda", dtype=dtype)
+        want_query = torch.zeros(B, n_query, device="cuda", dtype=dtype) if n_query else None
+        relation_layer_tail(dev["expanded"], dev["operand"], a, p, p_s, dev["wm"], dev["w2"], dev["b2"],
+                            dev["gamma"], dev["beta"], pos, 1e-5, want_hidden, dev["mix"], dev["next_w"],
+                            dev["next_b"], 1e-5, want_norm, dev["wq"], want_query)
+        hidden = dev["hidden"].clone()
+        norm = torch.full((B, d), float("nan"), device="cuda", dtype=dtype)
+        query = torch.full((B, n_query), float("nan"), device="cuda", dtype=dtype) if n_query else None
+        ga, ga_s, gp, gp_s = relation_layer(
+            *select_args(sg), pos, L, top, K, True, dev["expanded"], dev["operand"], dev["wm"], dev["w2"],
+            dev["b2"], dev["gamma"], dev["beta"], 1e-5, hidden, dev["mix"], dev["next_w"], dev["next_b"], 1e-5,
+            norm, dev["wq"], query)
+        assert torch.equal(ga, a) and torch.equal(gp, p), t
+        assert torch.equal(ga_s.view(torch.int32), a_s.view(torch.int32)), t
+        assert torch.equal(gp_s.view(torch.int32), p_s.view(torch.int32)), t
+        if B <= 4 * (4 * d // 128):
+            assert torch.equal(hidden, want_hidden) and torch.equal(norm, want_norm), t
+            if n_query:
+                assert torch.equal(query, want_query), t
+        else:
+            # more sequences than 4 clusters' CTAs: the two forms split the sequences over clusters
+            # differently, and the order of a cluster's sums depends on its number of rows
+            assert_rel_close(hidden, want_hidden, 1e-2, "residual")
+            assert_rel_close(norm, want_norm, 1e-2, "normalized")
+            if n_query:
+                assert_rel_close(query, want_query, 1e-2, "query")
+        # and against the oracle's selection on the same inputs
+        oa, _, op, _, _ = oracle.relation_select(*select_args(sel), t, L, top, K, True)
+        assert torch.equal(ga.cpu(), oa) and torch.equal(gp.cpu(), op), t
+    assert_status_clear()
+
+
+def test_whole_layer_rejects_a_selector_that_does_not_fit():
+    from relation_lm.kernels.relation_layer import relation_layer_supported
+
+    # the tail's tile memory is about 50 KB: 64 blocks of statistics + a 128-row window + 4 blocks of 64 keys need more
+    assert not relation_layer_supported(4, 8, 128, 512, 128, 0, torch.bfloat16, 4096, 64, 8, 128, 4)
+    assert not relation_layer_supported(4, 8, 128, 3072, 768, 0, torch.bfloat16, 128, 8, 8, 16, 1)   # d 768
