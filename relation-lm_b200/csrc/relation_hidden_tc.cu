@@ -304,6 +304,254 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
                      ::"r"(tmem_base), "r"(kTcBN) : "memory");
 }
 
+// ------------------------------------------------------------------ many rows: a CTA per pair tile, all hidden tiles
+//
+// Launches of thousands of rows (whole-sequence passes) repeat the operand gather and the product
+// for every one of the H / 128 hidden tiles in the kernel above, and its three CTAs per SM overlap
+// only by chance.  Here a CTA of 16 warps keeps one tile of 128 pairs: the product tile is built
+// once, then the hidden tiles stream through a two-stage pipeline — weight tile j + 2 (TMA) and
+// the expanded-cache terms of tile j + 1 (cp.async) are in flight and the MMA of tile j + 1 runs
+// into the second half of the tensor memory while the warps finish tile j (tcgen05.ld, + terms,
+// GELU, 16-bit results staged over the partner terms, coalesced stores).  16-bit outputs only.
+constexpr int kRowsThreads = 512;
+
+struct RowsPlan { uint32_t a_tile, w_tile[2], terms[2], partner_rows, total; };
+
+__host__ __device__ inline RowsPlan rows_plan(int rdim, int rows_per_tile) {
+    RowsPlan p;
+    const uint32_t tile_bytes = static_cast<uint32_t>(rdim / kBK) * kBM * 128u;
+    p.a_tile = 0;
+    p.w_tile[0] = tile_bytes;
+    p.w_tile[1] = 2 * tile_bytes;
+    p.partner_rows = static_cast<uint32_t>(rows_per_tile) * kRowStride;
+    const uint32_t staged = (p.partner_rows + kBM * kRowStride + 127u) & ~127u;
+    p.terms[0] = 3 * tile_bytes;
+    p.terms[1] = p.terms[0] + staged;
+    p.total = p.terms[1] + staged;
+    return p;
+}
+
+template <int kDt, int kOut>
+__global__ void __launch_bounds__(kRowsThreads, 1) relation_hidden_rows_kernel(
+    const __grid_constant__ CUtensorMap map_wm, const HiddenTcArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[4];      // weight tile landed [2], accumulator complete [2]
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+    __shared__ int idx_s[2 * kBM];      // [rows_per_tile][K + 1]
+    __shared__ int seq_s[kBM];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int R = a.rdim, H = a.hdim, K = a.k_out, RPT = a.rows_per_tile;
+    const int kblocks = R / kBK, chunks = R / 8, n_tiles = H / kTcBN;
+    const int row0 = blockIdx.x * RPT;
+    const int tile_pairs = RPT * K;
+
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const RowsPlan plan = rows_plan(R, RPT);
+    const uint32_t tile_bytes = static_cast<uint32_t>(kblocks) * kBM * 128u;
+    unsigned char* a_tile = base + plan.a_tile;
+
+    const uint32_t bar_w[2] = {smem_u32(&bars[0]), smem_u32(&bars[1])};
+    const uint32_t bar_acc[2] = {smem_u32(&bars[2]), smem_u32(&bars[3])};
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wm) : "memory");
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&bars[i]), 1);
+        fence_barrier_init();
+        failed = 0;
+        for (int j = 0; j < 2 && j < n_tiles; ++j) {
+            mbar_expect_tx(bar_w[j], tile_bytes);
+            for (int kb = 0; kb < kblocks; ++kb)
+                tma_load_2d(smem_u32(base + plan.w_tile[j]) + kb * kBM * 128u, &map_wm, kb * kBK, j * kTcBN, bar_w[j]);
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(2 * kTcBN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    griddep_sync();
+#pragma unroll 1
+    for (int i = tid; i < RPT * (K + 1); i += kRowsThreads) {
+        const int rb = i / (K + 1), j = i - rb * (K + 1), row = row0 + rb;
+        int v = 0;
+        if (row < a.n_rows)
+            v = j == 0 ? a.anchor_index[row] : a.partner_index[static_cast<size_t>(row) * K + j - 1];
+        idx_s[i] = min(max(v, 0), a.max_t - 1);
+        if (j == 0) {
+            int b = row < a.n_rows ? (a.row_batch ? a.row_batch[row] : row) : -1;
+            if (row < a.n_rows && (b < 0 || b >= a.n_seq)) {
+                if (a.status) atomicOr(a.status, RLM_DEV_POSITION);
+                b = -1;
+            }
+            seq_s[rb] = b;
+        }
+    }
+    __syncthreads();      // also publishes the barrier initialisation
+
+    // product tile, once: partner operand rows copied to their swizzled places, multiplied in
+    // place (fp32) with the anchor chunks held in registers
+    const size_t op_row = static_cast<size_t>(R) * 2;
+    {
+        constexpr int kRound = 4;
+        const int rows_per_pass = kRowsThreads / chunks;
+        const int bc = tid % chunks, r_first = tid / chunks;
+        for (int r0 = r_first < rows_per_pass ? r_first : kBM; r0 < kBM; r0 += kRound * rows_per_pass) {
+            uint4 anchor_chunk[kRound];
+#pragma unroll
+            for (int u = 0; u < kRound; ++u) {
+                const int r = r0 + u * rows_per_pass;
+                anchor_chunk[u] = make_uint4(0, 0, 0, 0);
+                if (r >= kBM) continue;
+                const int rb = (r * a.inv_k16) >> 16, k = r - rb * K;
+                const uint32_t dst = smem_u32(a_tile) + swizzled(r, bc, kBM * 128u);
+                if (r < tile_pairs && seq_s[rb < RPT ? rb : 0] >= 0) {
+                    const char* operand = static_cast<const char*>(a.operand_cache) +
+                                          static_cast<size_t>(seq_s[rb]) * a.max_t * op_row + 16 * bc;
+                    cp_async16(dst, operand + idx_s[rb * (K + 1) + k + 1] * op_row);
+                    anchor_chunk[u] = *reinterpret_cast<const uint4*>(operand + idx_s[rb * (K + 1)] * op_row);
+                } else {
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+                }
+            }
+            cp_async_commit();
+            cp_async_wait_all();
+#pragma unroll
+            for (int u = 0; u < kRound; ++u) {
+                const int r = r0 + u * rows_per_pass;
+                if (r >= kBM) continue;
+                uint4* cell = reinterpret_cast<uint4*>(a_tile + swizzled(r, bc, kBM * 128u));
+                float fa[8], fp[8];
+                unpack8(anchor_chunk[u], kDt, fa);
+                unpack8(*cell, kDt, fp);
+                *cell = make_uint4(pack2(fp[0] * fa[0], fp[1] * fa[1], kDt), pack2(fp[2] * fa[2], fp[3] * fa[3], kDt),
+                                   pack2(fp[4] * fa[4], fp[5] * fa[5], kDt), pack2(fp[6] * fa[6], fp[7] * fa[7], kDt));
+            }
+        }
+    }
+    // the expanded-cache terms of hidden tile j: row g < RPT of the staging area is the anchor term
+    // of sequence g, row RPT + r the partner term of pair r (16 threads copy a 256-byte row)
+    auto request_terms = [&](int j) {
+        if (j < n_tiles) {
+            unsigned char* dst = base + plan.terms[j & 1];
+            const int c = tid & 15, n_rows_staged = RPT + tile_pairs, h0 = j * kTcBN;
+#pragma unroll 1
+            for (int g = tid >> 4; g < n_rows_staged; g += kRowsThreads / 16) {
+                const int r = g - RPT;
+                const int rb = g < RPT ? g : (r * a.inv_k16) >> 16;
+                if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
+                const int at = g < RPT ? idx_s[rb * (K + 1)] : idx_s[rb * (K + 1) + (r - rb * K) + 1];
+                const char* src = static_cast<const char*>(a.expanded_cache) +
+                                  ((static_cast<size_t>(seq_s[rb]) * a.max_t + at) * 2 * H + (g < RPT ? 0 : H) + h0) * 2;
+                cp_async16(smem_u32(dst) + g * kRowStride + 16 * c, src + 16 * c);
+            }
+        }
+        cp_async_commit();
+    };
+    request_terms(0);
+    fence_proxy_async();     // generic-proxy writes of the product tile -> visible to the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    // thread 0: MMA of hidden tile j into accumulator j & 1 once its weight tile has landed
+    auto issue_mma = [&](int j) {
+        const int b = j & 1;
+        if (mbar_wait(bar_w[b], (j >> 1) & 1)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const uint64_t da = smem_desc_sw128(smem_u32(a_tile) + kb * kBM * 128u);
+                const uint64_t db = smem_desc_sw128(smem_u32(base + plan.w_tile[b]) + kb * kBM * 128u);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; ++kk)
+                    umma_f16(tmem_base + b * kTcBN, da + 2 * kk, db + 2 * kk, a.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+        } else {
+            failed = 1;
+        }
+        umma_commit(bar_acc[b]);     // accumulator complete (or abandoned)
+    };
+    if (tid == 0) issue_mma(0);
+
+    // this thread's share of a tile: pair row `pr`, hidden columns [32 cg, 32 cg + 32) of the tile
+    const int pr = 32 * (warp & 3) + lane, cg = warp >> 2;
+    const int prb = (pr * a.inv_k16) >> 16;
+    const bool pair_live = pr < tile_pairs && row0 + prb < a.n_rows && seq_s[prb < RPT ? prb : 0] >= 0;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    bool good = true;
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+        const int b = j & 1;
+        request_terms(j + 1);                                  // into the buffer tile j - 1 has left
+        if (tid == 0) {
+            if (j + 1 < n_tiles) issue_mma(j + 1);             // accumulator (j + 1) & 1 was read out in iteration j - 1
+        }
+        bool ready = mbar_wait(bar_acc[b], (j >> 1) & 1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (tid == 0 && ready && j + 2 < n_tiles) {            // weight buffer b is consumed: tile j + 2 may land
+            mbar_expect_tx(bar_w[b], tile_bytes);
+            for (int kb = 0; kb < kblocks; ++kb)
+                tma_load_2d(smem_u32(base + plan.w_tile[b]) + kb * kBM * 128u, &map_wm, kb * kBK, (j + 2) * kTcBN, bar_w[b]);
+        }
+        cp_async_wait_group1();                                // the terms of tile j (tile j + 1's may be in flight)
+        ready = ready && (*reinterpret_cast<volatile int*>(&failed) == 0);
+        if (__syncthreads_or(!ready)) { good = false; break; }
+        unsigned char* g_anchor = base + plan.terms[b];
+        unsigned char* g_partner = g_anchor + plan.partner_rows;
+        const unsigned char* ga = g_anchor + (prb < RPT ? prb : 0) * kRowStride + 64 * cg;
+        unsigned char* gp = g_partner + pr * kRowStride + 64 * cg;      // results replace the partner term
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + lane_base + b * kTcBN + 32 * cg + 16 * q, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (!pair_live) continue;
+            float y[16];
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                float fa[8], fp[8];
+                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
+                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    y[8 * hlf + i] = gelu_tc(__uint_as_float(v[8 * hlf + i]) + (fa[i] + fp[i]));
+            }
+            uint4* o = reinterpret_cast<uint4*>(gp + 32 * q);
+            o[0] = make_uint4(pack2(y[0], y[1], kOut), pack2(y[2], y[3], kOut), pack2(y[4], y[5], kOut), pack2(y[6], y[7], kOut));
+            o[1] = make_uint4(pack2(y[8], y[9], kOut), pack2(y[10], y[11], kOut), pack2(y[12], y[13], kOut),
+                              pack2(y[14], y[15], kOut));
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        {
+            // the tile's rows leave row by row: a warp stores two 256-byte pair rows per instruction
+            const int c = tid & 15, h0 = j * kTcBN;
+#pragma unroll 2
+            for (int r = tid >> 4; r < tile_pairs; r += kRowsThreads / 16) {
+                const int rb = (r * a.inv_k16) >> 16;
+                if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
+                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) +
+                                          (static_cast<size_t>(row0) * K + r) * H + h0 + 8 * c) =
+                    *reinterpret_cast<const uint4*>(g_partner + r * kRowStride + 16 * c);
+            }
+        }
+        __syncthreads();                                       // staging buffer b and accumulator b are free
+    }
+    if (!good) {
+        cp_async_wait_all();
+        if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
+    }
+    cp_async_wait_all();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"(2 * kTcBN) : "memory");
+}
+
 // ------------------------------------------------------------------ expanded row of position t
 
 // grid (H / 128, 2 halves, layers x sequence groups of up to 64); the weight tensor maps cover
@@ -520,9 +768,25 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
         kernel = out_dtype == RLM_F32 ? relation_hidden_tc_kernel<RLM_F16, RLM_F32>
                : out_dtype == RLM_BF16 ? relation_hidden_tc_kernel<RLM_F16, RLM_BF16>
                                        : relation_hidden_tc_kernel<RLM_F16, RLM_F16>;
+    const int row_tiles = (n_rows + a.rows_per_tile - 1) / a.rows_per_tile;
+    const size_t rows_smem = 1024 + rows_plan(rdim, a.rows_per_tile).total;
+    if (out_dtype != RLM_F32 && row_tiles >= 2 * sm_count() && hdim / kTcBN >= 2 &&
+        rows_smem <= static_cast<size_t>(kSmemDynamicLimit)) {
+        // many row tiles: a CTA per pair tile walks all hidden tiles (see relation_hidden_rows_kernel)
+        Kernel rows_kernel =
+            dtype == RLM_BF16 ? (out_dtype == RLM_BF16 ? relation_hidden_rows_kernel<RLM_BF16, RLM_BF16>
+                                                       : relation_hidden_rows_kernel<RLM_BF16, RLM_F16>)
+                              : (out_dtype == RLM_BF16 ? relation_hidden_rows_kernel<RLM_F16, RLM_BF16>
+                                                       : relation_hidden_rows_kernel<RLM_F16, RLM_F16>);
+        int rc = allow_large_smem(reinterpret_cast<const void*>(rows_kernel), kSmemPerCta);
+        if (rc != RLM_OK) return rc;
+        launch_kernel(rows_kernel, dim3(row_tiles), dim3(kRowsThreads), rows_smem, stream, mm, a);
+        count_launch();
+        return check_launch("relation_hidden_rows_kernel");
+    }
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
-    dim3 grid(hdim / kTcBN, (n_rows + a.rows_per_tile - 1) / a.rows_per_tile);
+    dim3 grid(hdim / kTcBN, row_tiles);
     launch_kernel(kernel, dim3(grid), dim3(kTcThreads), gather_smem_bytes(rdim, k_out), stream, mm, a);
     count_launch();
     return check_launch("relation_hidden_tc_kernel");

@@ -86,6 +86,44 @@ def test_same_results_as_the_small_launch_form():
     assert_status_clear()
 
 
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16),
+                                             (torch.bfloat16, torch.float16)])
+@pytest.mark.parametrize("N,K,H,R", [(6000, 8, 512, 128),      # 375 pair tiles, four hidden tiles
+                                     (9001, 5, 256, 64),       # ragged last tile, K that does not divide 128
+                                     (20000, 4, 384, 128)])    # three hidden tiles (odd count)
+def test_many_rows_form_matches_the_oracle_and_the_per_tile_form(N, K, H, R, dtype, out_dtype):
+    """Launches of thousands of rows (a CTA per pair tile walking all hidden tiles through a
+    two-stage pipeline) against the oracle on sampled rows, and bit for bit against launches small
+    enough to take the one-tile-per-CTA kernel (same contraction, same epilogue arithmetic)."""
+    from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows_out
+
+    B, T = 6, 160
+    g = torch.Generator().manual_seed(9300 + N + K)
+    operand = torch.randn(B, T, R, generator=g).to(dtype)
+    expanded = (torch.randn(B, T, 2 * H, generator=g) * 0.3).to(dtype)
+    wm = (torch.randn(H, R, generator=g) * 0.05).to(dtype)
+    rows = torch.randint(0, B, (N,), generator=g, dtype=torch.int32)
+    anchor = torch.randint(0, T, (N,), generator=g, dtype=torch.int32)
+    partner = torch.randint(0, T, (N, K), generator=g, dtype=torch.int32)
+    partner[::7, -1] = -5                 # empty-slot sentinel: clamped, never faults
+    ex, op, wm_d = expanded.cuda(), operand.cuda(), wm.cuda()
+    an, pa, rw = anchor.cuda(), partner.cuda(), rows.cuda()
+    got = torch.full((N, K, H), float("nan"), device="cuda", dtype=out_dtype)
+    relation_hidden_cached_rows_out(got, ex, op, an, pa, wm_d, rw)
+    assert bool(torch.isfinite(got.float()).all())
+    sample = torch.randperm(N, generator=g)[:300]
+    for i in sample.tolist():
+        want, _ = oracle.relation_hidden(expanded[rows[i]:rows[i] + 1], operand[rows[i]:rows[i] + 1], anchor[i:i + 1],
+                                         partner[i:i + 1].clamp(0, T - 1), wm)
+        assert_rel_close(got[i:i + 1], want, 1e-2, f"row {i}")
+    step = 2048                            # 128 or fewer pair tiles per launch: the per-tile kernel
+    for lo in range(0, N, step):
+        part = torch.empty((min(step, N - lo), K, H), device="cuda", dtype=out_dtype)
+        relation_hidden_cached_rows_out(part, ex, op, an[lo:lo + step], pa[lo:lo + step], wm_d, rw[lo:lo + step])
+        assert torch.equal(part, got[lo:lo + step]), lo
+    assert_status_clear()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("layers,B,H,R", [(3, 8, 256, 128), (2, 70, 384, 64), (1, 1, 128, 128)])
 def test_stacked_expanded_cache_append(layers, B, H, R, dtype):
