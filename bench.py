@@ -1247,6 +1247,18 @@ def run_kernel_case(args) -> None:
             ak, pk, pac, am, as_, pm, ps = S[i % 2]
             fn = lambda: relation_select_packed_prefill(q[:, :64], ak, q[:, 64:128], am, as_, g, bias, q[:, 128:],  # noqa: E731
                                                         pac, pk, pm, ps, g, bias, Ts, 128, 4, K, False)
+        elif args.kernel_case == "hidden_rows":
+            if i == 0:
+                from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows_out
+                Bs, Ts, Hs = 8, 4096, 2048                             # the long-context configuration (d_model 512)
+                Ns = Bs * Ts
+                ex, op, wm = rn(Bs, Ts, 2 * Hs) * 0.3, rn(Bs, Ts, R), rn(Hs, R) * 0.05
+                rows = torch.arange(Ns, device=dev, dtype=torch.int32) // Ts
+                at = torch.arange(Ns, device=dev, dtype=torch.int32) % Ts
+                ai = (torch.rand(Ns, device=dev) * (at + 1)).int().clamp(max=Ts - 1)
+                pi = (torch.rand(Ns, K, device=dev) * (at[:, None] + 1)).int().clamp(max=Ts - 1)
+                hidden_out = torch.empty(Ns, K, Hs, device=dev, dtype=torch.bfloat16)      # 1.07 GB: larger than L2
+            fn = lambda: relation_hidden_cached_rows_out(hidden_out, ex, op, ai, pi, wm, rows)  # noqa: E731
         elif args.kernel_case == "norm":
             if i == 0:
                 S = [rn(B, K, d) for _ in range(sets)]
@@ -1291,7 +1303,7 @@ def main() -> None:
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
     parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router",
-                                                 "tail", "head", "select_tile"),
+                                                 "tail", "head", "select_tile", "hidden_rows"),
                         default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")

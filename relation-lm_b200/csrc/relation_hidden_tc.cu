@@ -261,12 +261,16 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
             float y[16];
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
-                float fa[8], fp[8];
-                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
-                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
+                float2 fa[4], fp[4];
+                unpack8_pairs(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
+                unpack8_pairs(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    y[8 * hlf + i] = gelu_tc(__uint_as_float(v[8 * hlf + i]) + (fa[i] + fp[i]));
+                for (int i = 0; i < 4; ++i) {
+                    const float2 acc = make_float2(__uint_as_float(v[8 * hlf + 2 * i]), __uint_as_float(v[8 * hlf + 2 * i + 1]));
+                    const float2 g = gelu_tc2(__fadd2_rn(acc, __fadd2_rn(fa[i], fp[i])));
+                    y[8 * hlf + 2 * i] = g.x;
+                    y[8 * hlf + 2 * i + 1] = g.y;
+                }
             }
             if (!staged) {
                 const size_t at = (static_cast<size_t>(row0) * K + pr) * H + h0 + 64 * ch + 16 * q;
@@ -512,12 +516,16 @@ __global__ void __launch_bounds__(kRowsThreads, 1) relation_hidden_rows_kernel(
             float y[16];
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
-                float fa[8], fp[8];
-                unpack8(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
-                unpack8(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
+                float2 fa[4], fp[4];
+                unpack8_pairs(*reinterpret_cast<const uint4*>(ga + 32 * q + 16 * hlf), kDt, fa);
+                unpack8_pairs(*reinterpret_cast<const uint4*>(gp + 32 * q + 16 * hlf), kDt, fp);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    y[8 * hlf + i] = gelu_tc(__uint_as_float(v[8 * hlf + i]) + (fa[i] + fp[i]));
+                for (int i = 0; i < 4; ++i) {
+                    const float2 acc = make_float2(__uint_as_float(v[8 * hlf + 2 * i]), __uint_as_float(v[8 * hlf + 2 * i + 1]));
+                    const float2 g = gelu_tc2(__fadd2_rn(acc, __fadd2_rn(fa[i], fp[i])));
+                    y[8 * hlf + 2 * i] = g.x;
+                    y[8 * hlf + 2 * i + 1] = g.y;
+                }
             }
             uint4* o = reinterpret_cast<uint4*>(gp + 32 * q);
             o[0] = make_uint4(pack2(y[0], y[1], kOut), pack2(y[2], y[3], kOut), pack2(y[4], y[5], kOut), pack2(y[6], y[7], kOut));

@@ -83,6 +83,42 @@ __device__ __forceinline__ float gelu_tc(float x) {
     return x * (x >= 0.0f ? 1.0f - h : h);
 }
 
+// gelu_tc of two values at once on the two-wide fp32 instructions (the same operations in the same
+// order, so each half equals gelu_tc of its input bit for bit): the epilogues that apply GELU to
+// millions of values are bound by instruction issue, not by the arithmetic pipes.
+__device__ __forceinline__ float2 gelu_tc2(float2 x) {
+    const float2 z = __fmul2_rn(make_float2(fabsf(x.x), fabsf(x.y)), make_float2(0.70710678118654752f, 0.70710678118654752f));
+    const float2 den = __ffma2_rn(make_float2(0.3275911f, 0.3275911f), z, make_float2(1.0f, 1.0f));
+    const float2 arg = __fmul2_rn(__fmul2_rn(z, z), make_float2(-1.4426950408889634f, -1.4426950408889634f));
+    float2 t, e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(den.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(den.y));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(arg.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(arg.y));
+    float2 p = make_float2(0.5307027145f, 0.5307027145f);
+    p = __ffma2_rn(p, t, make_float2(-0.7265760135f, -0.7265760135f));
+    p = __ffma2_rn(p, t, make_float2(0.7107068705f, 0.7107068705f));
+    p = __ffma2_rn(p, t, make_float2(-0.142248368f, -0.142248368f));
+    p = __ffma2_rn(p, t, make_float2(0.127414796f, 0.127414796f));
+    const float2 h = __fmul2_rn(__fmul2_rn(p, t), e);                                   // erfc(z) / 2
+    const float2 c = __ffma2_rn(h, make_float2(-1.0f, -1.0f), make_float2(1.0f, 1.0f));  // 1 - h
+    return __fmul2_rn(x, make_float2(x.x >= 0.0f ? c.x : h.x, x.y >= 0.0f ? c.y : h.y));
+}
+
+// Eight consecutive 16-bit values as four pairs (elements 2i, 2i + 1), for the two-wide instructions.
+__device__ __forceinline__ void unpack8_pairs(const uint4& raw, int dtype, float2 (&f)[4]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (dtype == RLM_BF16) {
+            f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+        } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            f[i] = __half22float2(h);
+        }
+    }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& raw, int dtype, float (&f)[8]) {
     Raw8 r;
     r.lo = raw;
