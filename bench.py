@@ -951,16 +951,19 @@ def run_multi_anchor(args) -> None:
         keep: dict = {}
         stage("routed pass (norm, query projection, multi-anchor selection, hidden, second layer, norm-reduce, mix)",
               lambda: runner.forward_layer(0, work, state, keep))
-        from relation_lm.kernels.multi_select import relation_select_multi_rows
+        from relation_lm.kernels.multi_select import relation_select_multi_prefill, relation_select_multi_rows
         w = runner.layers[0]
         S, K = cfg.anchors_per_block, cfg.partners_per_anchor
         q = keep["query"]
+        select_args = (q[:, :S * 64].unflatten(1, (S, 64)), state["anchor_keys"], q[:, S * 64:S * 128].unflatten(1, (S, 64)),
+                       state["anchor_mean"], state["anchor_std"], w["anchor_gamma"], w["anchor_bias"],
+                       q[:, S * 128:].unflatten(1, (S, 128)), state["partner_anchor_cache"], state["partner_keys"],
+                       state["partner_mean"], state["partner_std"], w["partner_gamma"], w["partner_bias"])
+        stage("relation_select_multi_tile_kernel", lambda: relation_select_multi_prefill(
+            *select_args, T, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid))
         stage("relation_select_multi_kernel", lambda: relation_select_multi_rows(
-            q[:, :S * 64].unflatten(1, (S, 64)), state["anchor_keys"], q[:, S * 64:S * 128].unflatten(1, (S, 64)),
-            state["anchor_mean"], state["anchor_std"], w["anchor_gamma"], w["anchor_bias"],
-            q[:, S * 128:].unflatten(1, (S, 128)), state["partner_anchor_cache"], state["partner_keys"],
-            state["partner_mean"], state["partner_std"], w["partner_gamma"], w["partner_bias"], keep["row_batch"],
-            keep["row_position"], cfg.local_window, cfg.top_blocks, K, cfg.strict_valid))
+            *select_args, keep["row_batch"], keep["row_position"], cfg.local_window, cfg.top_blocks, K, cfg.strict_valid))
+        stages["relation_select_multi_kernel"]["note"] = "the per-row form, not on the pass's path: timed for comparison"
         peaks = {}
         try:
             peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -968,12 +971,13 @@ def run_multi_anchor(args) -> None:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         nb, cand = T // cfg.block_size, cfg.local_window + cfg.top_blocks * cfg.block_size
-        sel_ms = stages["relation_select_multi_kernel"]["ms"]
         logical = N * S * (2 * (4 * nb * 64 + 2 * cand * 64 + 384) + 560 + 8 + 8 * K)
         compulsory = 2 * S * (B * T * (64 + 64 + 128) + 4 * B * nb * 64) + 2 * N * S * 256 + N * S * (9 + 8 * K)
-        stages["relation_select_multi_kernel"].update(
-            compulsory_bytes=compulsory, logical_bytes=logical, compulsory_gb_per_s=compulsory / sel_ms / 1e6,
-            logical_gb_per_s=logical / sel_ms / 1e6)
+        for name in ("relation_select_multi_tile_kernel", "relation_select_multi_kernel"):
+            ms = stages[name]["ms"]
+            stages[name].update(compulsory_bytes=compulsory, logical_bytes=logical,
+                                compulsory_gb_per_s=compulsory / ms / 1e6, logical_gb_per_s=logical / ms / 1e6)
+        sel_ms = stages["relation_select_multi_tile_kernel"]["ms"]
         line = {
             "metric": "multi-anchor relation stack tokens/s at ctx2048, 4 anchors x 4 partners, depth 4",
             "value": world * N * args.steps / (total_ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -986,10 +990,10 @@ def run_multi_anchor(args) -> None:
             "e2e": {"value": world * N * e2e_steps / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": N * d * 4,
                     "d2h_bytes_per_step": N * d * 4, "steps": e2e_steps},
             "gpu_launches": launches * args.steps, "launches_per_step": launches, "clocks": clocks, "stages_layer0": stages,
-            "roofline": {"kernel": "relation_select_multi_kernel", "bound": "hbm", "achieved": compulsory / sel_ms / 1e6,
+            "roofline": {"kernel": "relation_select_multi_tile_kernel", "bound": "hbm", "achieved": compulsory / sel_ms / 1e6,
                          "peak": peak, "unit": "GB/s", "frac": compulsory / sel_ms / 1e6 / peak,
                          "peak_source": "measured" if peaks else "fallback", "traffic": None,
-                         "note": "compulsory bytes; the per-row form re-reads shared windows from L2 (logical bytes in stages_layer0)"},
+                         "note": "compulsory bytes; the selector's caches stay in L2 and it is bound by instruction issue (logical bytes in stages_layer0)"},
         }
         if world == 1:
             line["cpu_baseline"] = cpu_multi_anchor_rate(stack, runner, state, keep)

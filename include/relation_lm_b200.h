@@ -586,6 +586,26 @@ int rlm_relation_select_multi_rows(
     int query_dtype, int key_dtype, int stats_dtype, int param_dtype, int32_t* status, void* stream);
 
 /*
+ * rlm_relation_select_multi_rows for whole sequences (extension): the query rows are
+ * b * query_length + t for every position t < query_length of every sequence b, all tensors bfloat16
+ * (router parameters any dtype).  A CTA serves a tile of consecutive positions; the block statistics
+ * and the window union of one slot and stream are staged once per tile and phase, and every warp
+ * walks its queries through the 2 S phases (anchors of slot 0 .. S - 1, then partners).  Results are
+ * those of rlm_relation_select_multi_rows on the same rows, bit for bit.  At most 512 candidates
+ * per query (window + remote blocks); other dtypes return RLM_ERR_UNSUPPORTED.
+ */
+int rlm_relation_select_multi_prefill(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    int32_t* out_anchor, float* out_anchor_score, uint8_t* out_anchor_active, int32_t* out_partner,
+    float* out_partner_score, int64_t anchor_query_stride, int64_t anchor_router_query_stride,
+    int64_t partner_base_stride, int query_length, int n_seq, int slots, int max_t, int n_blocks, int buckets,
+    int local_window, int top_blocks, int k_out, int strict_valid, int query_dtype, int key_dtype, int stats_dtype,
+    int param_dtype, int32_t* status, void* stream);
+
+/*
  * Slot mixing of a multi-anchor relation layer (extension; the last lines of
  * MultiAnchorRelationBlock.forward, src/relation_lm/models/multi_relation_blocks.py:170-178):
  *   w[n,s] = slot_weight[s] * active[n,s] / max(sum_s' slot_weight[s'] * active[n,s'], 1e-9)

@@ -202,11 +202,24 @@ __device__ __forceinline__ float pair_dot_abs_bf16(const uint4 w0, const uint4 w
 
 // score_rows_split<true, 1> for one warp with the query in registers (same arguments otherwise;
 // no exclusion list, rows already in place).  `stride`: bytes between rows.
-template <bool kAtPosition>
+// Further excluded positions of a query (the anchors of a multi-anchor row's slots; -1 = none).
+struct ExclRegs { int v[kMaxExclude]; int n; };
+
+template <bool kExcl>
+__device__ __forceinline__ bool not_excluded(int pos, const ExclRegs* ex) {
+    bool keep = true;
+    if (kExcl) {
+#pragma unroll
+        for (int x = 0; x < kMaxExclude; ++x) keep = keep && (x >= ex->n || pos != ex->v[x]);
+    }
+    return keep;
+}
+
+template <bool kAtPosition, bool kExcl = false>
 __device__ __forceinline__ void score_rows_warp(const unsigned char* rows, uint32_t stride, int n_rows, const int* sel,
                                                 int bs, int bs_shift, int first_valid, int pos0, int exclude,
                                                 const QueryRegs& q, float* cand, int slot0, uint32_t& best_key,
-                                                int& best_pos) {
+                                                int& best_pos, const ExclRegs* ex = nullptr) {
     const int lane = threadIdx.x & 31;
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
@@ -223,7 +236,7 @@ __device__ __forceinline__ void score_rows_warp(const unsigned char* rows, uint3
             pos = pos0 + r;
             valid = r < n_rows && r >= first_valid;
         }
-        valid = valid && pos != exclude;
+        valid = valid && pos != exclude && not_excluded<kExcl>(pos, ex);
         float sc = kNegInf;
         if (valid) {
             const uint4* row = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(kAtPosition ? pos : r) * stride);
@@ -259,9 +272,11 @@ __device__ __forceinline__ void score_rows_warp(const unsigned char* rows, uint3
 // load instruction covers four whole rows: lane = 8 (row % 4) + chunk), parked in the warp's
 // padded staging buffer (32 rows of kPadRow bytes) and scored from there a row per lane, exactly
 // like the local window.  Arguments as score_rows_warp with sel != nullptr.
+template <bool kExcl = false>
 __device__ __forceinline__ void score_remote_warp(const unsigned char* keys, int n_rows, const int* sel, int bs,
                                                   int bs_shift, int exclude, const QueryRegs& q, unsigned char* stage,
-                                                  float* cand, int slot0, uint32_t& best_key, int& best_pos) {
+                                                  float* cand, int slot0, uint32_t& best_key, int& best_pos,
+                                                  const ExclRegs* ex = nullptr) {
     const int lane = threadIdx.x & 31, chunk = lane & 7, rq = lane >> 3;
     uint32_t my_key = 0;
     int my_pos = 0x7fffffff;
@@ -296,7 +311,7 @@ __device__ __forceinline__ void score_remote_warp(const unsigned char* keys, int
         for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(park + i * (4 * kPadRow)) = v[i];
         __syncwarp();
         const int r = base + lane;
-        const bool valid = pos >= 0 && pos != exclude;
+        const bool valid = pos >= 0 && pos != exclude && not_excluded<kExcl>(pos, ex);
         float sc = kNegInf;
         if (valid) {
             const uint4* row = reinterpret_cast<const uint4*>(stage + lane * kPadRow);
@@ -655,6 +670,284 @@ __global__ void __launch_bounds__(32 * kTileWarps, 16 / kTileWarps) relation_sel
     }
 }
 
+// ---- whole-sequence multi-anchor selection: the tiled form of relation_select_multi_kernel (bf16)
+//
+// A CTA of kTileWarps warps serves 4 kTileWarps consecutive positions of one sequence; every warp
+// keeps its queries and walks them through 2 S phases — the anchors of slot 0 .. S - 1 (each barring
+// the positions taken before it), then the partners of slot 0 .. S - 1 (each barring all anchors).
+// A phase's block statistics and window union (one slot, one stream) are staged for the whole CTA
+// in one of two buffers while the previous phase is being computed.  Rules and arithmetic are
+// relation_select_multi_kernel's (same results bit for bit).
+struct MultiTileArgs {
+    MultiSelectArgs m;
+    int q_len;
+    int warp_bytes, stats_bytes, window_rows, param_bytes, stage_bytes;
+};
+
+template <int kTileWarps>
+__global__ void __launch_bounds__(32 * kTileWarps, 16 / kTileWarps) relation_select_multi_tile_kernel(const MultiTileArgs ta) {
+    constexpr int kTileQ = 4 * kTileWarps, kTileThreads = 32 * kTileWarps;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const MultiSelectArgs& m = ta.m;
+    const SelectArgs& a = m.base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int S = m.slots, K = a.k_out;
+    const int tiles_per_seq = (ta.q_len + kTileQ - 1) / kTileQ;
+    const int b = blockIdx.x / tiles_per_seq, t0 = (blockIdx.x - b * tiles_per_seq) * kTileQ;
+    const int t_end = min(t0 + kTileQ, ta.q_len);
+    const int nb = a.n_blocks, bs = a.block_size, L = a.local_window, top = a.top_blocks;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? 31 - __clz(bs) : -1;
+    constexpr size_t key_row = 2 * kD, stat_row = 2 * kD;
+    const int buckets4 = 4 * a.buckets;
+    griddep_sync();
+
+    // two staging buffers: mean | std | window union of one slot and stream
+    unsigned char* stage_buf[2] = {smem, smem + ta.stage_bytes};
+    float* params = reinterpret_cast<float*>(smem + 2 * ta.stage_bytes);      // per slot: softplus a[4] p[4], bias a, bias p
+    const int slot_params = 8 + 2 * buckets4;
+    unsigned char* warp_base = reinterpret_cast<unsigned char*>(params) + ta.param_bytes + static_cast<size_t>(warp) * ta.warp_bytes;
+    const int n_stage = top > 0 ? min(t_end / bs, nb) : 0;
+    const int w_lo = max(t0 - L + 1, 0);
+    auto request_phase = [&](int ph) {
+        if (ph < 2 * S) {
+            const int s = ph < S ? ph : ph - S;
+            const bool partner = ph >= S;
+            unsigned char* dst = stage_buf[ph & 1];
+            const size_t seq_stats = s * m.stats_slot + static_cast<size_t>(b) * nb * stat_row;
+            const size_t seq_keys = s * m.keys_slot + static_cast<size_t>(b) * a.max_t * key_row;
+            const char* mean = static_cast<const char*>(partner ? a.partner_mean : a.anchor_mean) + seq_stats;
+            const char* stdv = static_cast<const char*>(partner ? a.partner_std : a.anchor_std) + seq_stats;
+            const char* keys = static_cast<const char*>(partner ? a.partner_keys : a.anchor_keys) + seq_keys + w_lo * key_row;
+            const int stat_chunks = n_stage * 8;
+            for (int i = tid; i < 2 * stat_chunks; i += kTileThreads) {
+                const int which = i >= stat_chunks, c = i - which * stat_chunks;
+                cp_async16(smem_u32(dst) + which * ta.stats_bytes + (c >> 3) * kPadRow + 16 * (c & 7),
+                           (which ? stdv : mean) + 16 * c);
+            }
+            const int win_chunks = (t_end - w_lo) * 8;
+            for (int i = tid; i < win_chunks; i += kTileThreads)
+                cp_async16(smem_u32(dst) + 2 * ta.stats_bytes + (i >> 3) * kPadRow + 16 * (i & 7), keys + 16 * i);
+        }
+        cp_async_commit();
+    };
+    request_phase(0);
+    for (int i = tid; i < S * slot_params; i += kTileThreads) {
+        const int s = i / slot_params, j = i - s * slot_params;
+        float v;
+        if (j < 8) {
+            const float gamma = load_scalar(slot_ptr(j < 4 ? a.anchor_gamma : a.partner_gamma, s * m.gamma_slot), j & 3, a.param_dtype);
+            v = canon_log(__fadd_rn(1.0f, canon_exp(gamma)));
+        } else if (j < 8 + buckets4) {
+            v = load_scalar(slot_ptr(a.anchor_bias, s * m.bias_slot), j - 8, a.param_dtype);
+        } else {
+            v = load_scalar(slot_ptr(a.partner_bias, s * m.bias_slot), j - 8 - buckets4, a.param_dtype);
+        }
+        params[i] = v;
+    }
+    // per-warp scratch
+    float* queries = reinterpret_cast<float*>(warp_base);                     // exact query | router query (paired layout)
+    uint32_t* short_list = reinterpret_cast<uint32_t*>(queries + 2 * kD);     // 64 words of the top-K filter
+    int* taken = reinterpret_cast<int*>(short_list + 64);                     // [4 queries][kMaxSlots]
+    float* bscore = reinterpret_cast<float*>(taken + 4 * kMaxSlots);
+    float* cand = bscore + ((nb + 3) & ~3);
+    const int cap = L + top * bs, cap4 = (cap + 3) & ~3;
+    int* sel = reinterpret_cast<int*>(cand + cap4);
+    unsigned char* park = warp_base + ta.warp_bytes - 32 * kPadRow;           // remote rows of a pass
+    for (int i = cap + lane; i < cap4; i += 32) cand[i] = kNegInf;
+    for (int i = lane; i < 4 * kMaxSlots; i += 32) taken[i] = -1;
+    const size_t esz = 2;
+
+    for (int ph = 0; ph < 2 * S; ++ph) {
+        request_phase(ph + 1);                       // into the buffer phase ph - 1 has left
+        cp_async_wait_group1();
+        __syncthreads();                             // phase ph is staged (and, first time, the parameters are written)
+        const int s = ph < S ? ph : ph - S;
+        const bool partner = ph >= S;
+        const unsigned char* st_mean = stage_buf[ph & 1];
+        const unsigned char* st_std = st_mean + ta.stats_bytes;
+        const unsigned char* win = st_mean + 2 * ta.stats_bytes;
+        const float* sp = params + s * slot_params + (partner ? 4 : 0);
+        const float* bias = params + s * slot_params + 8 + (partner ? buckets4 : 0);
+        const unsigned char* seq_keys = static_cast<const unsigned char*>(partner ? a.partner_keys : a.anchor_keys) +
+                                        s * m.keys_slot + static_cast<size_t>(b) * a.max_t * key_row;
+        int qi = 0;
+        for (int t = t0 + warp; t < t_end; t += kTileWarps, ++qi) {
+            const int row = b * ta.q_len + t;
+            const int ls = max(t - L + 1, 0), first_local = ls - (t - L + 1);
+            const int n_complete = min((t + 1) / bs, nb);
+            int* mine = taken + qi * kMaxSlots;
+            const unsigned char* local = win + static_cast<ptrdiff_t>(t - L + 1 - w_lo) * static_cast<ptrdiff_t>(kPadRow);
+            ExclRegs ex;
+            if (!partner) {
+                // ---- anchor of slot s: active iff s <= t; the positions taken by slots 0 .. s - 1 are barred
+                int32_t* out_idx = m.out_anchor + static_cast<size_t>(row) * S + s;
+                float* out_sc = m.out_anchor_score + static_cast<size_t>(row) * S + s;
+                uint8_t* out_live = m.out_anchor_active + static_cast<size_t>(row) * S + s;
+                if (s > t) {
+                    if (lane == 0) { *out_idx = 0; *out_sc = kNegInf; *out_live = 0; }
+                    continue;                        // taken[s] stays -1
+                }
+                for (int i = lane; i < 2 * kD; i += 32) {
+                    const float v = i < kD ? load_scalar(a.anchor_query, row * a.aq_stride + s * kD + i, RLM_BF16)
+                                           : load_scalar(a.anchor_router_query, row * a.arq_stride + s * kD + i - kD, RLM_BF16);
+                    queries[(i & ~(kD - 1)) | paired_index(i & (kD - 1))] = v;
+                }
+                ex.n = s;
+#pragma unroll
+                for (int x = 0; x < kMaxExclude; ++x) ex.v[x] = x < s ? mine[x] : -1;
+                __syncwarp();
+                QueryRegs q;
+                if (top > 0) {
+                    load_query_regs(queries + kD, q);
+                    score_blocks_warp(st_mean, st_std, kPadRow, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets, q, sp,
+                                      bias, bscore);
+                }
+                load_query_regs(queries, q);
+                uint32_t bk = 0;
+                int bp = 0x7fffffff;
+                score_rows_warp<false, true>(local, kPadRow, L, nullptr, bs, bs_shift, first_local, t - L + 1, -1, q, nullptr,
+                                             0, bk, bp, &ex);
+                if (top > 0) {
+                    __syncwarp();
+                    if (nb <= 128) pick_blocks_warp(bscore, nb, top, bs, ls, sel);
+                    else pick_blocks(bscore, nb, top, bs, ls, sel);
+                    score_remote_warp<true>(seq_keys, top * bs, sel, bs, bs_shift, -1, q, park, nullptr, 0, bk, bp, &ex);
+                }
+                const float score = bp == 0x7fffffff ? kNegInf : key_float(bk);
+                const bool live = score > kNegInf;
+                if (lane == 0) {
+                    *out_idx = live ? bp : 0;
+                    *out_sc = live ? score : kNegInf;
+                    *out_live = live ? 1 : 0;
+                    mine[s] = live ? bp : -1;
+                }
+                __syncwarp();
+            } else {
+                // ---- partners of slot s: none without an anchor; the anchors of all slots are barred
+                int32_t* out_idx = m.out_partner + (static_cast<size_t>(row) * S + s) * K;
+                float* out_sc = m.out_partner_score + (static_cast<size_t>(row) * S + s) * K;
+                const int anchor_pos = mine[s];
+                if (anchor_pos < 0) {
+                    if (lane < K) { out_idx[lane] = 0; out_sc[lane] = kNegInf; }
+                    continue;
+                }
+                const unsigned char* pac = static_cast<const unsigned char*>(a.partner_anchor_cache) + s * m.pac_slot;
+                for (int i = lane; i < 2 * kD; i += 32) {
+                    const float base = load_scalar(a.partner_base, row * a.pbase_stride + s * 2 * kD + i, RLM_BF16);
+                    const float add = load_scalar(pac, (static_cast<size_t>(b) * a.max_t + anchor_pos) * 2 * kD + i, RLM_BF16);
+                    queries[(i & ~(kD - 1)) | paired_index(i & (kD - 1))] = __fadd_rn(base, add);
+                }
+                ex.n = S;
+#pragma unroll
+                for (int x = 0; x < kMaxExclude; ++x) ex.v[x] = x < S ? mine[x] : -1;
+                __syncwarp();
+                QueryRegs q;
+                if (top > 0) {
+                    load_query_regs(queries + kD, q);
+                    score_blocks_warp(st_mean, st_std, kPadRow, nb, n_complete, bs, t, ls, a.strict_valid, a.buckets, q, sp,
+                                      bias, bscore);
+                }
+                load_query_regs(queries, q);
+                uint32_t dk = 0;
+                int dp = 0x7fffffff;
+                score_rows_warp<false, true>(local, kPadRow, L, nullptr, bs, bs_shift, first_local, t - L + 1, anchor_pos, q,
+                                             cand, 0, dk, dp, &ex);
+                if (top > 0) {
+                    __syncwarp();
+                    if (nb <= 128) pick_blocks_warp(bscore, nb, top, bs, ls, sel);
+                    else pick_blocks(bscore, nb, top, bs, ls, sel);
+                    score_remote_warp<true>(seq_keys, top * bs, sel, bs, bs_shift, anchor_pos, q, park, cand, L, dk, dp, &ex);
+                }
+                __syncwarp();
+                bool exact = false;
+                if (cap4 <= 128) exact = topk_filter<4>(cand, cap4, K, L, t, bs, bs_shift, sel, short_list, out_idx, out_sc);
+                else if (cap4 <= 256) exact = topk_filter<8>(cand, cap4, K, L, t, bs, bs_shift, sel, short_list, out_idx, out_sc);
+                else exact = topk_filter<16>(cand, cap4, K, L, t, bs, bs_shift, sel, short_list, out_idx, out_sc);
+                if (!exact) {
+                    if (cap4 <= 128) topk_tournament<4>(cand, cap4, K, L, t, bs, bs_shift, sel, out_idx, out_sc);
+                    else if (cap4 <= 256) topk_tournament<8>(cand, cap4, K, L, t, bs, bs_shift, sel, out_idx, out_sc);
+                    else topk_tournament<16>(cand, cap4, K, L, t, bs, bs_shift, sel, out_idx, out_sc);
+                    // slots without a finite score report index 0 (written by this very lane just above)
+                    if (lane < K && !(out_sc[lane] > kNegInf)) { out_idx[lane] = 0; out_sc[lane] = kNegInf; }
+                }
+                __syncwarp();
+            }
+        }
+        __syncthreads();                             // everybody has left buffer ph & 1
+    }
+    cp_async_wait_all();
+    (void)esz;
+}
+
+int launch_multi_tile(MultiTileArgs& ta, void* stream) {
+    MultiSelectArgs& m = ta.m;
+    SelectArgs& a = m.base;
+    if (a.n_seq < 1 || ta.q_len < 1 || ta.q_len > a.max_t || a.max_t < 1 || a.n_blocks < 1 || a.buckets < 1 ||
+        a.local_window < 1 || a.top_blocks < 0 || a.max_t % a.n_blocks != 0 || m.slots < 1 || m.slots > kMaxSlots ||
+        a.k_out < 1 || a.k_out > kMaxKOut) {
+        set_error("relation_select_multi_prefill: sizes must be positive, T a multiple of the block count, 1..8 slots, "
+                  "K <= 32, query length <= T");
+        return RLM_ERR_SHAPE;
+    }
+    if (a.query_dtype != RLM_BF16 || a.key_dtype != RLM_BF16 || a.stats_dtype != RLM_BF16 || !valid_dtype(a.param_dtype)) {
+        set_error("relation_select_multi_prefill: queries, caches and block statistics must be bfloat16 "
+                  "(relation_select_multi_rows serves the other dtypes)");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    const void* need[] = {a.anchor_query, a.anchor_keys, a.anchor_router_query, a.anchor_mean, a.anchor_std, a.anchor_gamma,
+                          a.anchor_bias, a.partner_base, a.partner_anchor_cache, a.partner_keys, a.partner_mean,
+                          a.partner_std, a.partner_gamma, a.partner_bias, m.out_anchor, m.out_anchor_score,
+                          m.out_anchor_active, m.out_partner, m.out_partner_score};
+    for (const void* q : need) if (!q) { set_error("relation_select_multi_prefill: NULL pointer"); return RLM_ERR_NULL; }
+    const void* bulk[] = {a.anchor_keys, a.anchor_mean, a.anchor_std, a.partner_keys, a.partner_mean, a.partner_std,
+                          a.partner_anchor_cache};
+    for (const void* q : bulk)
+        if (!aligned16(q)) {
+            set_error("relation_select_multi_prefill: key caches, block statistics and the partner-anchor cache must be 16-byte aligned");
+            return RLM_ERR_ALIGN;
+        }
+    a.block_size = a.max_t / a.n_blocks;
+    const int cap = a.local_window + a.top_blocks * a.block_size;
+    if (cap > 512) {
+        set_error("relation_select_multi_prefill: at most 512 candidates per query (window + remote blocks)");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    const int ps = dtype_size(a.param_dtype);
+    m.keys_slot = static_cast<size_t>(a.n_seq) * a.max_t * kD * 2;
+    m.pac_slot = static_cast<size_t>(a.n_seq) * a.max_t * 2 * kD * 2;
+    m.stats_slot = static_cast<size_t>(a.n_seq) * a.n_blocks * kD * 2;
+    m.gamma_slot = static_cast<size_t>(4) * ps;
+    m.bias_slot = static_cast<size_t>(4) * a.buckets * ps;
+    if (a.aq_stride < static_cast<int64_t>(m.slots) * kD || a.arq_stride < static_cast<int64_t>(m.slots) * kD ||
+        a.pbase_stride < static_cast<int64_t>(m.slots) * 2 * kD) {
+        set_error("relation_select_multi_prefill: a query row stride is shorter than the slots it holds");
+        return RLM_ERR_SHAPE;
+    }
+    const int cap4 = (cap + 3) & ~3;
+    const int floats = 2 * kD + 64 + 4 * kMaxSlots + ((a.n_blocks + 3) & ~3) + cap4;
+    ta.warp_bytes = align16(floats * 4 + 3 * (a.top_blocks > 0 ? a.top_blocks : 1) * 4) + 16 + 32 * static_cast<int>(kPadRow);
+    ta.stats_bytes = align16(a.n_blocks * static_cast<int>(kPadRow));
+    ta.param_bytes = align16(m.slots * (8 + 8 * a.buckets) * 4);
+    int warps = 16, total = 0;
+    for (;; warps = 8) {
+        ta.window_rows = a.local_window + 4 * warps;
+        ta.stage_bytes = (2 * ta.stats_bytes + ta.window_rows * static_cast<int>(kPadRow) + 127) & ~127;
+        total = 2 * ta.stage_bytes + ta.param_bytes + warps * ta.warp_bytes;
+        if (total <= kSmemDynamicLimit || warps == 8) break;
+    }
+    if (total > kSmemDynamicLimit) {
+        set_error("relation_select_multi_prefill: block statistics + window union exceed 227 KB of shared memory");
+        return RLM_ERR_SMEM;
+    }
+    auto kernel = warps == 16 ? relation_select_multi_tile_kernel<16> : relation_select_multi_tile_kernel<8>;
+    int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
+    if (rc != RLM_OK) return rc;
+    const int tiles = a.n_seq * ((ta.q_len + 4 * warps - 1) / (4 * warps));
+    launch_kernel(kernel, dim3(tiles), dim3(32 * warps), total, stream, ta);
+    count_launch();
+    return check_launch("relation_select_multi_tile_kernel");
+}
+
 int tile_warp_bytes(const SelectArgs& a) {
     const int cap4 = (a.local_window + a.top_blocks * a.block_size + 3) & ~3;
     const int floats = 4 * kD + 64 + ((a.n_blocks + 3) & ~3) + cap4;
@@ -819,6 +1112,35 @@ extern "C" int rlm_relation_select_packed_prefill(
     a.query_dtype = query_dtype; a.key_dtype = key_dtype; a.stats_dtype = stats_dtype; a.param_dtype = param_dtype;
     m.q_len = query_length;
     return rlm::launch_tile(m, stream);
+}
+
+extern "C" int rlm_relation_select_multi_prefill(
+    const void* anchor_query, const void* anchor_keys, const void* anchor_router_query,
+    const void* anchor_mean, const void* anchor_std, const void* anchor_gamma, const void* anchor_bias,
+    const void* partner_base, const void* partner_anchor_cache, const void* partner_keys,
+    const void* partner_mean, const void* partner_std, const void* partner_gamma, const void* partner_bias,
+    int32_t* out_anchor, float* out_anchor_score, uint8_t* out_anchor_active, int32_t* out_partner,
+    float* out_partner_score, int64_t anchor_query_stride, int64_t anchor_router_query_stride,
+    int64_t partner_base_stride, int query_length, int n_seq, int slots, int max_t, int n_blocks, int buckets,
+    int local_window, int top_blocks, int k_out, int strict_valid, int query_dtype, int key_dtype, int stats_dtype,
+    int param_dtype, int32_t* status, void* stream) {
+    if (n_seq == 0 || query_length == 0) return RLM_OK;
+    rlm::MultiTileArgs ta{};
+    rlm::MultiSelectArgs& m = ta.m;
+    rlm::SelectArgs& a = m.base;
+    a.anchor_query = anchor_query; a.anchor_keys = anchor_keys; a.anchor_router_query = anchor_router_query;
+    a.anchor_mean = anchor_mean; a.anchor_std = anchor_std; a.anchor_gamma = anchor_gamma; a.anchor_bias = anchor_bias;
+    a.partner_base = partner_base; a.partner_anchor_cache = partner_anchor_cache; a.partner_keys = partner_keys;
+    a.partner_mean = partner_mean; a.partner_std = partner_std; a.partner_gamma = partner_gamma; a.partner_bias = partner_bias;
+    a.status = status; a.n_rows = n_seq * query_length; a.n_seq = n_seq; a.max_t = max_t; a.n_blocks = n_blocks;
+    a.buckets = buckets; a.local_window = local_window; a.top_blocks = top_blocks; a.k_out = k_out;
+    a.strict_valid = strict_valid != 0;
+    a.query_dtype = query_dtype; a.key_dtype = key_dtype; a.stats_dtype = stats_dtype; a.param_dtype = param_dtype;
+    a.aq_stride = anchor_query_stride; a.arq_stride = anchor_router_query_stride; a.pbase_stride = partner_base_stride;
+    m.slots = slots; m.out_anchor = out_anchor; m.out_anchor_score = out_anchor_score;
+    m.out_anchor_active = out_anchor_active; m.out_partner = out_partner; m.out_partner_score = out_partner_score;
+    ta.q_len = query_length;
+    return rlm::launch_multi_tile(ta, stream);
 }
 
 extern "C" int rlm_relation_select_multi_rows(

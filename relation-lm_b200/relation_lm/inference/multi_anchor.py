@@ -181,10 +181,12 @@ class MultiAnchorRoutedStack(nn.Module):
 class MultiAnchorPrefill:
     """The routed pass of a ``MultiAnchorRoutedStack`` over whole sequences on one GPU."""
 
-    def __init__(self, stack: MultiAnchorRoutedStack, device="cuda", dtype: torch.dtype = torch.bfloat16) -> None:
+    def __init__(self, stack: MultiAnchorRoutedStack, device="cuda", dtype: torch.dtype = torch.bfloat16,
+                 tiled_select: bool = True) -> None:
         if dtype not in (torch.bfloat16, torch.float16):
             raise ValueError("the routed pass runs its projections on the tensor cores: bfloat16 or float16")
         self.config, self.device, self.dtype = stack.config, torch.device(device), dtype
+        self.tiled_select = bool(tiled_select)           # whole-sequence selector (bfloat16) instead of the per-row one
         self.layers = [stack.layer_weights(l, self.device, dtype) for l in range(stack.config.depth)]
         self.final_norm_w = stack.final_norm.weight.detach().to(self.device, torch.float32)
         self.final_norm_b = stack.final_norm.bias.detach().to(self.device, torch.float32)
@@ -228,7 +230,8 @@ class MultiAnchorPrefill:
 
     def forward_layer(self, layer: int, hidden: Tensor, state: dict[str, Tensor], keep: dict | None = None) -> Tensor:
         """Updates the residual stream ``hidden [B, T, d]`` (fp32) in place and returns it."""
-        from relation_lm.kernels.multi_select import relation_select_multi_rows, slot_mix_residual
+        from relation_lm.kernels.multi_select import (relation_select_multi_prefill, relation_select_multi_rows,
+                                                      slot_mix_residual)
         from relation_lm.kernels.packed_projection import layer_norm_cast, packed_projection
         from relation_lm.kernels.relation_reduce import relation_hidden_cached_rows_out, relation_norm_reduce_rows
 
@@ -242,11 +245,19 @@ class MultiAnchorPrefill:
         anchor_query = q[:, :S * 64].unflatten(1, (S, 64))                       # column slices of one projection
         anchor_router_query = q[:, S * 64:S * 128].unflatten(1, (S, 64))
         partner_base = q[:, S * 128:].unflatten(1, (S, 128))
-        anchor, anchor_score, anchor_active, partner, partner_score, partner_active = relation_select_multi_rows(
-            anchor_query, state["anchor_keys"], anchor_router_query, state["anchor_mean"], state["anchor_std"],
-            w["anchor_gamma"], w["anchor_bias"], partner_base, state["partner_anchor_cache"], state["partner_keys"],
-            state["partner_mean"], state["partner_std"], w["partner_gamma"], w["partner_bias"], rb, rp,
-            cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+        select_args = (anchor_query, state["anchor_keys"], anchor_router_query, state["anchor_mean"], state["anchor_std"],
+                       w["anchor_gamma"], w["anchor_bias"], partner_base, state["partner_anchor_cache"],
+                       state["partner_keys"], state["partner_mean"], state["partner_std"], w["partner_gamma"],
+                       w["partner_bias"])
+        tiled = (self.tiled_select and self.dtype == torch.bfloat16
+                 and cfg.local_window + cfg.top_blocks * cfg.block_size <= 512)
+        if tiled:
+            # whole sequences: tiles of consecutive positions share the staged statistics and windows
+            anchor, anchor_score, anchor_active, partner, partner_score, partner_active = relation_select_multi_prefill(
+                *select_args, T, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+        else:
+            anchor, anchor_score, anchor_active, partner, partner_score, partner_active = relation_select_multi_rows(
+                *select_args, rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
         pair_rows = rb.repeat_interleave(S)
         hidden_rel = torch.empty(N * S, K, H, device=self.device, dtype=self.dtype)
         relation_hidden_cached_rows_out(hidden_rel, state["expanded_cache"], state["operand_cache"],

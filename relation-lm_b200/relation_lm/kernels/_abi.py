@@ -37,6 +37,7 @@ PROTOTYPES = {
     "rlm_selftest_bounded_wait": [_P, _L, _P, _P],
     "rlm_relation_select_packed_prefill": [_P] * 18 + [_L] * 3 + [_I] * 13 + [_P, _P],
     "rlm_relation_select_multi_rows": [_P] * 21 + [_L] * 3 + [_I] * 14 + [_P, _P],
+    "rlm_relation_select_multi_prefill": [_P] * 19 + [_L] * 3 + [_I] * 14 + [_P, _P],
     "rlm_slot_mix_residual": [_P] * 5 + [_I] * 3 + [_P],
     "rlm_skinny_projection": [_P, _L, _P, _P, _P] + [_I] * 5 + [_P] * 4,
     "rlm_packed_projection_append": [_P, _L, _P, _P, _I] + [_P] * 15 + [_I] * 7 + [_P, _P],

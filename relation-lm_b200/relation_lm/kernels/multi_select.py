@@ -1,4 +1,4 @@
-"""``relation_lm::relation_select_multi_rows`` — routed multi-anchor selection (extension).
+"""``relation_lm::relation_select_multi_rows`` / ``relation_select_multi_prefill`` — routed multi-anchor selection (extension).
 
 The reference project's multi-anchor layer is dense: every slot scores all causal positions
 (src/relation_lm/models/multi_relation_blocks.py:69-148).  This is its routed form, one launch
@@ -107,6 +107,95 @@ def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_
       anchor_bias, partner_base, partner_anchor_cache, partner_keys, partner_block_mean, partner_block_std,
       partner_gamma, partner_bias, row_batch, row_position, local_window, top_blocks, partners_per_anchor,
       strict_valid):
+    rows, slots = anchor_query.size(0), anchor_query.size(1)
+    k = partners_per_anchor
+    f32 = torch.float32
+    return (anchor_query.new_empty((rows, slots), dtype=torch.int32), anchor_query.new_empty((rows, slots), dtype=f32),
+            anchor_query.new_empty((rows, slots), dtype=torch.bool),
+            anchor_query.new_empty((rows, slots, k), dtype=torch.int32),
+            anchor_query.new_empty((rows, slots, k), dtype=f32),
+            anchor_query.new_empty((rows, slots, k), dtype=torch.bool))
+
+
+@torch.library.custom_op("relation_lm::relation_select_multi_prefill", mutates_args=(), device_types="cuda")
+def relation_select_multi_prefill(
+    anchor_query: Tensor,            # [B * Tq, S, 64]
+    anchor_keys: Tensor,             # [S, B, T, 64]
+    anchor_router_query: Tensor,     # [B * Tq, S, 64]
+    anchor_block_mean: Tensor,       # [S, B, NB, 4, 16]
+    anchor_block_std: Tensor,
+    anchor_gamma: Tensor,            # [S, 4]
+    anchor_bias: Tensor,             # [S, 4, buckets]
+    partner_base: Tensor,            # [B * Tq, S, 128]
+    partner_anchor_cache: Tensor,    # [S, B, T, 128]
+    partner_keys: Tensor,            # [S, B, T, 64]
+    partner_block_mean: Tensor,
+    partner_block_std: Tensor,
+    partner_gamma: Tensor,
+    partner_bias: Tensor,
+    query_length: int,
+    local_window: int,
+    top_blocks: int,
+    partners_per_anchor: int,
+    strict_valid: bool,
+) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Whole-sequence form of ``relation_select_multi_rows`` (bfloat16 tensors): query row
+    ``b * query_length + t`` is position ``t`` of sequence ``b``; same results, bit for bit.  A CTA
+    serves a tile of consecutive positions and stages each slot's block statistics and window union
+    once per tile."""
+    for name, query in (("anchor_query", anchor_query), ("anchor_router_query", anchor_router_query),
+                        ("partner_base", partner_base)):
+        if not query.is_cuda or query.dim() != 3 or query.stride(2) != 1 or query.stride(1) != query.size(2):
+            raise ValueError(f"{name} must be a CUDA tensor [N, S, width] whose slots are contiguous inside a row")
+    device = _abi.require_cuda_contiguous(
+        anchor_keys=anchor_keys, anchor_block_mean=anchor_block_mean, anchor_block_std=anchor_block_std,
+        anchor_gamma=anchor_gamma, anchor_bias=anchor_bias, partner_anchor_cache=partner_anchor_cache,
+        partner_keys=partner_keys, partner_block_mean=partner_block_mean, partner_block_std=partner_block_std,
+        partner_gamma=partner_gamma, partner_bias=partner_bias)
+    rows, slots = anchor_query.shape[0], anchor_query.shape[1]
+    if anchor_keys.dim() != 4 or anchor_keys.size(0) != slots or anchor_keys.size(3) != 64 or slots > 8:
+        raise ValueError("anchor_keys must be [S, B, T, 64] with at most 8 slots")
+    _, batch, max_t, _ = anchor_keys.shape
+    nb = anchor_block_mean.size(2)
+    tq = int(query_length)
+    if rows != batch * tq or tq < 1 or tq > max_t:
+        raise ValueError("the queries must be the positions 0 .. query_length - 1 of every sequence")
+    if anchor_query.size(2) != 64 or anchor_router_query.shape != (rows, slots, 64) \
+            or partner_base.shape != (rows, slots, 128) \
+            or partner_anchor_cache.shape != (slots, batch, max_t, 128) or partner_keys.shape != anchor_keys.shape \
+            or anchor_block_mean.shape != (slots, batch, nb, 4, 16) or partner_block_mean.shape != anchor_block_mean.shape \
+            or anchor_gamma.shape != (slots, 4) or anchor_bias.dim() != 3 or anchor_bias.shape[:2] != (slots, 4):
+        raise ValueError("relation_select_multi_prefill: inconsistent shapes")
+    k = int(partners_per_anchor)
+    anchor_index = torch.empty((rows, slots), dtype=torch.int32, device=device)
+    anchor_score = torch.empty((rows, slots), dtype=torch.float32, device=device)
+    anchor_active = torch.empty((rows, slots), dtype=torch.uint8, device=device)
+    partner_index = torch.empty((rows, slots, k), dtype=torch.int32, device=device)
+    partner_score = torch.empty((rows, slots, k), dtype=torch.float32, device=device)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_relation_select_multi_prefill(
+            _abi.ptr(anchor_query), _abi.ptr(anchor_keys), _abi.ptr(anchor_router_query),
+            _abi.ptr(anchor_block_mean), _abi.ptr(anchor_block_std), _abi.ptr(anchor_gamma), _abi.ptr(anchor_bias),
+            _abi.ptr(partner_base), _abi.ptr(partner_anchor_cache), _abi.ptr(partner_keys),
+            _abi.ptr(partner_block_mean), _abi.ptr(partner_block_std), _abi.ptr(partner_gamma),
+            _abi.ptr(partner_bias), _abi.ptr(anchor_index), _abi.ptr(anchor_score), _abi.ptr(anchor_active),
+            _abi.ptr(partner_index), _abi.ptr(partner_score),
+            anchor_query.stride(0), anchor_router_query.stride(0), partner_base.stride(0),
+            tq, batch, slots, max_t, nb, anchor_bias.size(2), int(local_window), int(top_blocks), k,
+            int(bool(strict_valid)),
+            _abi.same_dtype("query", anchor_query, anchor_router_query, partner_base),
+            _abi.same_dtype("key cache", anchor_keys, partner_keys, partner_anchor_cache),
+            _abi.same_dtype("block statistics", anchor_block_mean, anchor_block_std, partner_block_mean, partner_block_std),
+            _abi.same_dtype("router parameter", anchor_gamma, anchor_bias, partner_gamma, partner_bias),
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return (anchor_index, anchor_score, anchor_active.bool(), partner_index, partner_score,
+            torch.isfinite(partner_score))
+
+
+@relation_select_multi_prefill.register_fake
+def _(anchor_query, anchor_keys, anchor_router_query, anchor_block_mean, anchor_block_std, anchor_gamma,
+      anchor_bias, partner_base, partner_anchor_cache, partner_keys, partner_block_mean, partner_block_std,
+      partner_gamma, partner_bias, query_length, local_window, top_blocks, partners_per_anchor, strict_valid):
     rows, slots = anchor_query.size(0), anchor_query.size(1)
     k = partners_per_anchor
     f32 = torch.float32

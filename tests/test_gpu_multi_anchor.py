@@ -205,3 +205,41 @@ def test_multi_anchor_stack_configuration_at_full_shape():
         del kept, state
     assert torch.isfinite(current).all()
     assert_status_clear()
+
+
+@pytest.mark.parametrize("S,B,T,NB,L,top,K,Tq,strict", [
+    (4, 2, 2048, 64, 64, 3, 4, 2048, True),      # the multi-anchor configuration's shape (block 32, 160 candidates)
+    (4, 3, 256, 8, 64, 3, 4, 256, False),
+    (3, 2, 512, 8, 128, 2, 8, 300, True),        # block 64, 256 candidates, queries over a prefix only, ragged last tile
+    (8, 1, 192, 12, 16, 1, 2, 192, False),       # eight slots, block 16 (remote passes span blocks)
+    (2, 2, 128, 4, 128, 0, 4, 128, True),        # no remote blocks: the window is the whole history
+])
+def test_whole_sequence_multi_anchor_selector_equals_the_per_row_selector(S, B, T, NB, L, top, K, Tq, strict):
+    """The tiled whole-sequence form against the per-row multi-anchor kernel on the same rows: anchors,
+    anchor scores, activity flags, partner indices and scores, all bit for bit (and therefore the
+    oracle composition the per-row kernel is pinned to)."""
+    from relation_lm.kernels.multi_select import relation_select_multi_prefill, relation_select_multi_rows
+
+    g = torch.Generator().manual_seed(4500 + S + T)
+    N = B * Tq
+    dt = torch.bfloat16
+    rn = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    x = [rn(N, S, 64).to(dt), rn(S, B, T, 64).to(dt), rn(N, S, 64).to(dt), rn(S, B, NB, 4, 16).to(dt),
+         rn(S, B, NB, 4, 16).abs().to(dt), rn(S, 4), rn(S, 4, 16), rn(N, S, 128).to(dt), rn(S, B, T, 128).to(dt),
+         rn(S, B, T, 64).to(dt), rn(S, B, NB, 4, 16).to(dt), rn(S, B, NB, 4, 16).abs().to(dt), rn(S, 4), rn(S, 4, 16)]
+    # some exact duplicates among the keys of slot 0: ties between positions, and between slots' choices
+    x[1][0, :, 5::17] = x[1][0, :, 4:5]
+    x[9][0, :, 3::11] = x[9][0, :, 2:3]
+    d = [v.cuda() for v in x]
+    row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(Tq).cuda()
+    row_pos = torch.arange(Tq, dtype=torch.int32).repeat(B).cuda()
+    want = relation_select_multi_rows(*d, row_batch, row_pos, L, top, K, strict)
+    got = relation_select_multi_prefill(*d, Tq, L, top, K, strict)
+    names = ("anchor", "anchor score", "anchor active", "partner", "partner score", "partner active")
+    for name, a, b in zip(names, got, want):
+        if a.dtype == torch.float32:
+            assert torch.equal(a.view(torch.int32), b.view(torch.int32)), name
+        else:
+            assert torch.equal(a, b), name
+    assert bool(got[2].any()) and bool(got[5].any())
+    assert_status_clear()
