@@ -506,6 +506,26 @@ int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token
  * zero.  Launches that share it must be ordered on a stream.
  */
 int64_t rlm_skinny_argmax_scratch_bytes(void);
+
+/*
+ * The front of a decode step in one launch (extension): the embedding of one position
+ * (src/relation_lm/models/relation_lm.py:130-131: (token + boundary embedding) * scale + position
+ * embedding), two LayerNorms of the embedded rows and one projection of each,
+ *   out_first [B, n_first]  = LayerNorm(x; norm1) @ weight[:n_first].T
+ *   out_second [B, n_second] = LayerNorm(x; norm2) @ weight[n_first:].T
+ * (in the decode step: the packed projection of the memory-normed rows,
+ * src/relation_lm/inference/packed_cache.py:52-57, and layer 0's query projection of its input-normed
+ * rows).  weight [n_first + n_second, d]: the two matrices stacked.  hidden [B, d] fp32 receives x;
+ * norm1_out / norm2_out [B, d] (optional) the normalised rows.  Tables, weight and outputs share
+ * bfloat16 or float16; position table and LayerNorm parameters fp32.  B <= 16, d in {256, 512},
+ * n_first a multiple of 8.  Token / boundary ids out of range set RLM_DEV_POSITION in `status`.
+ */
+int rlm_decode_front(
+    const int64_t* tokens, const int64_t* boundaries, const void* token_table, const void* boundary_table,
+    const float* position_table, const int64_t* position, float scale, const float* norm1_weight,
+    const float* norm1_bias, const float* norm2_weight, const float* norm2_bias, float norm_eps, const void* weight,
+    float* hidden, void* norm1_out, void* norm2_out, void* out_first, void* out_second, int batch, int d_model,
+    int n_first, int n_second, int vocab, int boundary_vocab, int max_t, int dtype, int32_t* status, void* stream);
 int rlm_skinny_projection(const void* x, int64_t x_row_stride, const void* weight, const float* bias,
                           void* out, int rows, int d_in, int n_out, int dtype, int vocab,
                           void* argmax_scratch, int64_t* next_token, int64_t* position, void* stream);

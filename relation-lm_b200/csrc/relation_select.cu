@@ -22,10 +22,10 @@ namespace {
 // launches of many rows, where rows in flight per SM set the throughput.  kBf16: queries, key
 // caches and block statistics are all bf16 (the decode configuration); the dtype branches
 // fold away, which matters because a row's time is largely instruction fetch.
-template <int kMinCtas, bool kBf16, bool kDecode>
+template <int kMinCtas, bool kBf16, bool kDecode, bool kResident = false>
 __global__ void __launch_bounds__(kThreads, kMinCtas) relation_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    select_row<kBf16, kDecode, false>(a, blockIdx.x, smem, smem_u32(smem + a.plan.bars));
+    select_row<kBf16, kDecode, false, kResident>(a, blockIdx.x, smem, smem_u32(smem + a.plan.bars));
 }
 
 // ---- routed multi-anchor selection: S anchor slots per query row, one launch
@@ -1014,12 +1014,12 @@ int launch_tile(TileArgs& m, void* stream) {
 int launch(SelectArgs& a, void* stream) {
     if (a.n_rows == 0) return RLM_OK;
     bool many_rows = false;
-    const int ready = prepare(a, many_rows);
+    const int ready = prepare(a, many_rows, true);
     if (ready != RLM_OK) return ready;
     const Plan& plan = a.plan;
     const bool bf16 = a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 && a.stats_dtype == RLM_BF16;
     const bool decode = bf16 && a.mode == kPacked && !a.row_batch && !a.row_position && !a.exclude_list;
-    auto kernel = many_rows ? (decode ? relation_select_kernel<4, true, true>
+    auto kernel = a.resident ? relation_select_kernel<1, true, true, true> : many_rows ? (decode ? relation_select_kernel<4, true, true>
                                       : bf16 ? relation_select_kernel<4, true, false> : relation_select_kernel<4, false, false>)
                             : (decode ? relation_select_kernel<3, true, true>
                                       : bf16 ? relation_select_kernel<3, true, false> : relation_select_kernel<3, false, false>);

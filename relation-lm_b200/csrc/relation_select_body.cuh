@@ -69,6 +69,7 @@ struct SelectArgs {
     int mode;
     int shared_streams;                  // the partner's staging buffers alias the anchor's (see make_plan)
     int sm_count;                        // streaming multiprocessors of the device the launch goes to
+    int resident;                        // decode form with the whole key caches staged (see select_row)
     Plan plan;
 };
 
@@ -77,12 +78,15 @@ __host__ __device__ inline int align16(int x) { return (x + 15) & ~15; }
 // With `shared_streams` (packed mode only) the partner's statistics and local window take the
 // anchor's place once the anchor's first scoring pass has read them: a smaller footprint, so
 // more rows per SM, for launches of many rows.
+// resident_rows > 0: the whole key cache of the sequence (that many rows) takes the place of the
+// local window, and no buffer is kept for remote blocks (see SelectArgs::resident).
 __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, int buckets,
-                                          int key_size, int stats_size, int mode, bool shared_streams) {
+                                          int key_size, int stats_size, int mode, bool shared_streams,
+                                          int resident_rows = 0) {
     Plan p;
     int off = 0;
     int stats_bytes = nb * kD * stats_size;
-    int local_bytes = local * kD * key_size;
+    int local_bytes = (resident_rows > 0 ? resident_rows : local) * kD * key_size;
     bool anchor = mode != kPartnerOnly, partner = mode != kAnchorOnly;
     p.a_mean = off; off += anchor ? stats_bytes : 0;
     p.a_std = off; off += anchor ? stats_bytes : 0;
@@ -90,7 +94,7 @@ __host__ __device__ inline Plan make_plan(int nb, int bs, int local, int top, in
     p.p_std = shared_streams ? p.a_std : off; off += partner && !shared_streams ? stats_bytes : 0;
     p.a_local = off; off += anchor ? local_bytes : 0;
     p.p_local = shared_streams ? p.a_local : off; off += partner && !shared_streams ? local_bytes : 0;
-    p.remote = off; off += top * bs * kD * key_size;
+    p.remote = off; off += resident_rows > 0 ? 0 : top * bs * kD * key_size;
     p.queries = off; off += 4 * kD * 4;
     p.params = off; off += align16(8 * buckets * 4);
     p.block_scores = off; off += align16(((nb + 3) & ~3) * 4);
@@ -222,7 +226,7 @@ __device__ __noinline__ void score_rows_split(const unsigned char* rows, int key
 
 // Picks the split that keeps every lane of the group busy in the fewest passes (launches of at
 // most one CTA per SM, where a row's latency is what counts).
-template <bool kBf16>
+template <bool kBf16, bool kAtPosition = false>
 __device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dtype, int n_rows,
                                            const int* sel, int bs, int first_valid, int pos0,
                                            int exclude, const int* excl, int n_excl, const float* query,
@@ -230,13 +234,13 @@ __device__ __forceinline__ void score_rows(const unsigned char* rows, int key_dt
                                            int& best_pos, uint32_t bar, bool& arrived, int sm_count_arg) {
     const int lanes = static_cast<int>(gridDim.x) <= sm_count_arg ? 32 * nw : 0;   // a row per lane when CTAs share the SMs: fewer instructions in total
     if (4 * n_rows <= lanes)
-        score_rows_split<kBf16, 4>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+        score_rows_split<kBf16, 4, kAtPosition>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
                                    query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
     else if (2 * n_rows <= lanes)
-        score_rows_split<kBf16, 2>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+        score_rows_split<kBf16, 2, kAtPosition>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
                                    query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
     else
-        score_rows_split<kBf16, 1>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
+        score_rows_split<kBf16, 1, kAtPosition>(rows, key_dtype, n_rows, sel, bs, first_valid, pos0, exclude, excl, n_excl,
                                    query, cand, slot0, wi, nw, best_key, best_pos, bar, arrived);
 }
 
@@ -638,7 +642,11 @@ __device__ __forceinline__ void issue_remote(const unsigned char* keys, unsigned
 // kernel (one call per slot and phase): the caller has already ordered itself after earlier
 // kernels, hands in the four mbarriers of this call, and in partner-only mode the partner queries
 // are completed here with the anchor's row of the partner-anchor cache.
-template <bool kBf16, bool kDecode, bool kMulti>
+// kResident (decode form): the sequence's whole key caches up to the position are requested at entry
+// in place of the local windows, so the remote blocks need no second round of copies once they
+// are picked — two dependent memory round trips fewer per row, for contexts whose caches fit the
+// shared memory (2 x T x 128 bytes at 16 bits).
+template <bool kBf16, bool kDecode, bool kMulti, bool kResident = false>
 __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, unsigned char* smem,
                                            const uint32_t bars) {
     __shared__ uint32_t warp_key[2 * kWarps];
@@ -703,6 +711,9 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
     const size_t seq_keys = static_cast<size_t>(b) * a.max_t * key_row;
     const size_t seq_stats = static_cast<size_t>(b) * nb * stat_row;
     const int cap = L + top * bs, cap4 = (cap + 3) & ~3;
+    // resident form: row r of the window is position t - L + 1 + r of the resident cache (rows before
+    // position 0 are never valid, hence never read)
+    const ptrdiff_t window_offset = kResident ? static_cast<ptrdiff_t>(t - L + 1) * static_cast<ptrdiff_t>(key_row) : 0;
 
     if (tid == 0) {
         // the issuing thread initialises the barriers itself; the others first touch them
@@ -710,9 +721,10 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
         for (int i = 0; i < 4; ++i) mbar_init(bars + 8 * i, 1);
         fence_barrier_init();
         const uint32_t sbytes = top > 0 ? static_cast<uint32_t>(n_complete * stat_row) : 0u;
-        const uint32_t lbytes = static_cast<uint32_t>(n_local * key_row);
-        const size_t loff = seq_keys + static_cast<size_t>(ls) * key_row;
-        const uint32_t ldst = static_cast<uint32_t>(first_local * key_row);
+        // resident form: positions 0 .. t at rows 0 .. t; otherwise the local window at its slots
+        const uint32_t lbytes = static_cast<uint32_t>((kResident ? t + 1 : n_local) * key_row);
+        const size_t loff = seq_keys + (kResident ? 0 : static_cast<size_t>(ls) * key_row);
+        const uint32_t ldst = kResident ? 0u : static_cast<uint32_t>(first_local * key_row);
         if (do_anchor) {
             mbar_expect_tx(bar_a, 2 * sbytes + lbytes);
             if (sbytes) {
@@ -780,8 +792,8 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
             score_blocks_any<kBf16>(smem + p.a_mean, smem + p.a_std, stats_dtype, nb, n_complete, bs, t, ls,
                                     a.strict_valid, a.buckets, arq, sp_a, bias_a, bscore, warp, block_warps);
         else
-            score_rows<kBf16>(smem + p.a_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1, excl_s,
-                       n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok, a.sm_count);
+            score_rows<kBf16>(smem + p.a_local + window_offset, key_dtype, L, nullptr, bs, first_local, t - L + 1, -1,
+                       excl_s, n_excl, aq, nullptr, 0, row_wi, row_nw, bk, bp, 0u, ok, a.sm_count);
         if (lane == 0) { warp_key[warp] = bk; warp_pos[warp] = bp; }
         __syncthreads();
         if (a.shared_streams && tid == kThreads - 1) {
@@ -801,7 +813,9 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
         }
         if (top > 0) {
             if (warp == 0) {
-                if (nb <= 128 && top <= 32) {
+                if (kResident) {
+                    pick_blocks(bscore, nb, top, bs, ls, sel);
+                } else if (nb <= 128 && top <= 32) {
                     pick_and_issue(bscore, nb, top, bs, ls, sel, static_cast<const unsigned char*>(a.anchor_keys),
                                    smem + p.remote, key_row, seq_keys, bar_ra);
                 } else {
@@ -814,9 +828,12 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
             __syncthreads();
             bk = 0;
             bp = 0x7fffffff;
-            // each warp works out its rows' positions first and only then waits for the copies
-            score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
-                       nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok, a.sm_count);
+            if (kResident)      // the picked blocks' rows are already here, at their positions
+                score_rows<kBf16, true>(smem + p.a_local, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+                                        nullptr, 0, warp, kWarps, bk, bp, 0u, ok, a.sm_count);
+            else                // each warp works out its rows' positions first and only then waits for the copies
+                score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, -1, excl_s, n_excl, aq,
+                           nullptr, 0, warp, kWarps, bk, bp, bar_ra, ok, a.sm_count);
             if (lane == 0) { warp_key[kWarps + warp] = bk; warp_pos[kWarps + warp] = bp; }
             if (__syncthreads_or(!ok)) {
                 if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
@@ -868,12 +885,14 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
         score_blocks_any<kBf16>(smem + p.p_mean, smem + p.p_std, stats_dtype, nb, n_complete, bs, t, ls,
                                 a.strict_valid, a.buckets, prq, sp_p, bias_p, bscore, warp, block_warps);
     else
-        score_rows<kBf16>(smem + p.p_local, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
+        score_rows<kBf16>(smem + p.p_local + window_offset, key_dtype, L, nullptr, bs, first_local, t - L + 1, anchor_pos,
                    excl_s, n_excl, pq, cand, 0, row_wi, row_nw, dk, dp, 0u, okp, a.sm_count);
     __syncthreads();
     if (top > 0) {
         if (warp == 0) {
-            if (nb <= 128 && top <= 32) {
+            if (kResident) {
+                pick_blocks(bscore, nb, top, bs, ls, sel);
+            } else if (nb <= 128 && top <= 32) {
                 pick_and_issue(bscore, nb, top, bs, ls, sel, static_cast<const unsigned char*>(a.partner_keys),
                                smem + p.remote, key_row, seq_keys, bar_rp);
             } else {
@@ -887,8 +906,12 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
         }
         __syncthreads();
         bool ok = true;
-        score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
-                   cand, L, warp, kWarps, dk, dp, bar_rp, ok, a.sm_count);
+        if (kResident)
+            score_rows<kBf16, true>(smem + p.p_local, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+                                    cand, L, warp, kWarps, dk, dp, 0u, ok, a.sm_count);
+        else
+            score_rows<kBf16>(smem + p.remote, key_dtype, top * bs, sel, bs, 0, 0, anchor_pos, excl_s, n_excl, pq,
+                       cand, L, warp, kWarps, dk, dp, bar_rp, ok, a.sm_count);
         if (__syncthreads_or(!ok)) {
             if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_TIMEOUT);
             return;
@@ -915,7 +938,7 @@ __device__ __forceinline__ void select_row(const SelectArgs& a, const int row, u
 }
 
 // Validation and shared-memory plan of a selector launch: everything but the launch itself.
-int prepare(SelectArgs& a, bool& many_rows) {
+int prepare(SelectArgs& a, bool& many_rows, bool allow_resident = false) {
     if (a.n_rows < 0 || a.n_seq < 1 || a.max_t < 1 || a.n_blocks < 1 || a.buckets < 1 ||
         a.local_window < 1 || a.top_blocks < 0 || a.max_t % a.n_blocks != 0) {
         set_error("relation_select: sizes must be positive and T a multiple of the block count");
@@ -973,6 +996,19 @@ int prepare(SelectArgs& a, bool& many_rows) {
         a.shared_streams = 1;
         a.plan = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
                            dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode, true);
+    }
+    // At most one row per SM, 16-bit bf16 decode form, caches that fit: stage the whole key caches
+    // (see select_row, kResident)
+    a.resident = 0;
+    if (allow_resident && !many_rows && a.n_rows <= kSms && a.mode == kPacked && !a.row_batch && !a.row_position &&
+        !a.exclude_list && a.top_blocks > 0 && a.query_dtype == RLM_BF16 && a.key_dtype == RLM_BF16 &&
+        a.stats_dtype == RLM_BF16) {
+        const Plan whole = make_plan(a.n_blocks, a.block_size, a.local_window, a.top_blocks, a.buckets,
+                                     dtype_size(a.key_dtype), dtype_size(a.stats_dtype), a.mode, false, a.max_t);
+        if (whole.total <= kSmemDynamicLimit - 4096) {
+            a.plan = whole;
+            a.resident = 1;
+        }
     }
     const Plan& plan = a.plan;
     if (plan.total > kSmemDynamicLimit) {

@@ -264,6 +264,172 @@ __global__ void __launch_bounds__(kSkThreads) skinny_projection_kernel(const Ski
     }
 }
 
+// ---- the front of a decode step in one launch: embedding + two LayerNorms + two projections
+//
+//   x[b]   = (token_embedding[tokens[b]] + boundary_embedding[boundaries[b]]) * scale + position_embedding[t]
+//   out_first  = LayerNorm_1(x) @ w[:n_first].T        (the packed projection of the memory-normed rows)
+//   out_second = LayerNorm_2(x) @ w[n_first:].T        (layer 0's query projection of its input-normed rows)
+// (src/relation_lm/models/relation_lm.py:130-131, src/relation_lm/inference/packed_cache.py:52-57 of
+// the reference project).  Every CTA builds the at most 16 embedded rows and both normalised copies
+// in its own shared memory (a warp per row: a few KB out of L2) instead of reading them from a
+// launch of their own, then streams its share of the concatenated weight exactly as
+// skinny_projection_kernel does.  CTA 0 also stores x (fp32) and the two normalised rows.
+struct FrontArgs {
+    SkinnyArgs proj;          // w = concatenated weight [n, d]; out = out_first [M, n_first]; no bias, no head
+    void* out_second;         // [M, n - n_first]
+    int n_first;              // a multiple of 8
+    const int64_t* tokens;
+    const int64_t* boundaries;
+    const void* token_table;
+    const void* boundary_table;
+    const float* position_table;
+    const int64_t* position;
+    float* hidden;            // [M, d] fp32
+    int32_t* status;
+    float scale, eps;
+    int vocab, boundary_vocab, max_t;
+    const float* norm_w[2];
+    const float* norm_b[2];
+    void* norm_out[2];        // [M, d] 16-bit
+};
+
+template <int kSteps, bool kUpper, bool kBf16>
+__global__ void __launch_bounds__(kSkThreads) skinny_front_kernel(const FrontArgs f) {
+    extern __shared__ __align__(16) unsigned char xs[];
+    const SkinnyArgs& a = f.proj;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int d = 32 * kSteps, per = kSteps;                // columns per lane of a row: d / 32
+    constexpr int kRows = kUpper ? 16 : 8;
+    const uint32_t row_bytes = static_cast<uint32_t>(d) * 2u + 64u;
+    unsigned char* xs_second = xs + kRows * row_bytes;
+    const int n_row = lane >> 2, part = lane & 3;
+    const int warps_total = gridDim.x * kSkWarps;
+    int g = blockIdx.x * kSkWarps + warp;
+
+    uint4 wreg[kSteps];
+    auto load_group = [&](int group) {
+        const int col = group * 8 + n_row;
+        const uint4* wrow = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.w) +
+                                                           static_cast<size_t>(col < a.n ? col : a.n - 1) * d);
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) wreg[s] = wrow[4 * s + part];
+    };
+    if (g < a.groups) load_group(g);
+    griddep_sync();
+    const int t = static_cast<int>(*f.position);
+    if (t < 0 || t >= f.max_t) {
+        if (tid == 0 && f.status) atomicOr(f.status, RLM_DEV_POSITION);
+        return;
+    }
+    // a warp per row: this lane's `per` consecutive columns
+    for (int m = warp; m < kRows; m += kSkWarps) {
+        uint16_t* x1 = reinterpret_cast<uint16_t*>(xs + m * row_bytes) + per * lane;
+        uint16_t* x2 = reinterpret_cast<uint16_t*>(xs_second + m * row_bytes) + per * lane;
+        if (m >= a.rows) {
+#pragma unroll
+            for (int i = 0; i < per; ++i) { x1[i] = 0; x2[i] = 0; }
+            continue;
+        }
+        int64_t tok = f.tokens[m], bnd = f.boundaries[m];
+        if (tok < 0 || tok >= f.vocab || bnd < 0 || bnd >= f.boundary_vocab) {
+            if (lane == 0 && f.status) atomicOr(f.status, RLM_DEV_POSITION);
+            tok = 0;
+            bnd = 0;
+        }
+        const int c0 = per * lane;
+        float v[per];
+        {
+            const uint16_t* tr = static_cast<const uint16_t*>(f.token_table) + tok * d + c0;
+            const uint16_t* br = static_cast<const uint16_t*>(f.boundary_table) + bnd * d + c0;
+            const float* pr = f.position_table + static_cast<int64_t>(t) * d + c0;
+#pragma unroll
+            for (int i = 0; i < per; i += 8) {
+                const uint4 tv = *reinterpret_cast<const uint4*>(tr + i), bv = *reinterpret_cast<const uint4*>(br + i);
+                const uint16_t* th = reinterpret_cast<const uint16_t*>(&tv);
+                const uint16_t* bh = reinterpret_cast<const uint16_t*>(&bv);
+                const float4 p0 = *reinterpret_cast<const float4*>(pr + i), p1 = *reinterpret_cast<const float4*>(pr + i + 4);
+                const float pe[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // the sum of the two embeddings is rounded to the table dtype first (an addition of two 16-bit tensors)
+                    const float e = from16<kBf16>(to16<kBf16>(from16<kBf16>(th[j]) + from16<kBf16>(bh[j])));
+                    v[i + j] = e * f.scale + pe[j];
+                }
+            }
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < per; ++i) sum += v[i];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        const float mean = sum / static_cast<float>(d);
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < per; ++i) { const float dv = v[i] - mean; sq = fmaf(dv, dv, sq); }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        const float inv = rsqrtf(sq / static_cast<float>(d) + f.eps);
+        const bool store = blockIdx.x == 0;
+        if (store) {
+#pragma unroll
+            for (int i = 0; i < per; i += 4)
+                *reinterpret_cast<float4*>(f.hidden + static_cast<int64_t>(m) * d + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            uint16_t* xk = k ? x2 : x1;
+            const float* gw = f.norm_w[k] + c0;
+            const float* gb = f.norm_b[k] + c0;
+#pragma unroll
+            for (int i = 0; i < per; ++i) xk[i] = to16<kBf16>(fmaf((v[i] - mean) * inv, gw[i], gb[i]));
+            if (store && f.norm_out[k]) {
+                uint16_t* o = static_cast<uint16_t*>(f.norm_out[k]) + static_cast<int64_t>(m) * d + c0;
+#pragma unroll
+                for (int i = 0; i < per; i += 8) *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<const uint4*>(xk + i);
+            }
+        }
+    }
+    __syncthreads();
+
+    for (; g < a.groups; g += warps_total) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const bool second = g * 8 >= f.n_first;
+        const unsigned char* xlo = (second ? xs_second : xs) + n_row * row_bytes + 16 * part;
+        const unsigned char* xhi = xlo + 8 * row_bytes;
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(xlo + 64 * s);
+            uint4 hi = make_uint4(0, 0, 0, 0);
+            if (kUpper) hi = *reinterpret_cast<const uint4*>(xhi + 64 * s);
+            mma16816<kBf16>(acc, lo.x, hi.x, lo.y, hi.y, wreg[s].x, wreg[s].y);
+            mma16816<kBf16>(acc, lo.z, hi.z, lo.w, hi.w, wreg[s].z, wreg[s].w);
+        }
+        const int group = g;
+        const int next = g + warps_total;
+        if (next < a.groups) load_group(next);
+        uint16_t* out = static_cast<uint16_t*>(second ? f.out_second : a.out);
+        const int width = second ? a.n - f.n_first : f.n_first, first_col = second ? f.n_first : 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int m = n_row + (e >> 1) * 8, col = group * 8 + 2 * part + (e & 1);
+            if ((e >> 1) && !kUpper) continue;
+            if (m >= a.rows || col >= a.n) continue;
+            out[static_cast<size_t>(m) * width + col - first_col] = to16<kBf16>(acc[e]);
+        }
+    }
+}
+
+template <int kSteps, bool kUpper>
+int launch_front(const FrontArgs& f, void* stream) {
+    auto kernel = f.proj.dtype == RLM_BF16 ? skinny_front_kernel<kSteps, kUpper, true> : skinny_front_kernel<kSteps, kUpper, false>;
+    const int smem = 2 * (kUpper ? 16 : 8) * (f.proj.d * 2 + 64);
+    int ctas = (f.proj.groups + kSkWarps - 1) / kSkWarps;
+    if (ctas > 4 * sm_count()) ctas = 4 * sm_count();
+    launch_kernel(kernel, dim3(ctas), dim3(kSkThreads), smem, stream, f);
+    count_launch();
+    return check_launch("skinny_front_kernel");
+}
+
 template <int kSteps, bool kUpper>
 int launch_skinny(const SkinnyArgs& a, const SkinnyAppend* append, void* stream) {
     auto kernel = append ? (a.dtype == RLM_BF16 ? skinny_projection_kernel<kSteps, kUpper, true, true>
@@ -372,6 +538,49 @@ extern "C" int rlm_packed_projection_append(
     ap.position = position; ap.status = status; ap.max_t = max_t; ap.n_blocks = n_blocks; ap.block_size = block_size;
     ap.layers = layers; ap.rdim = relation_dim;
     return dispatch_skinny(a, &ap, stream);
+}
+
+extern "C" int rlm_decode_front(
+    const int64_t* tokens, const int64_t* boundaries, const void* token_table, const void* boundary_table,
+    const float* position_table, const int64_t* position, float scale, const float* norm1_weight,
+    const float* norm1_bias, const float* norm2_weight, const float* norm2_bias, float norm_eps, const void* weight,
+    float* hidden, void* norm1_out, void* norm2_out, void* out_first, void* out_second, int batch, int d_model,
+    int n_first, int n_second, int vocab, int boundary_vocab, int max_t, int dtype, int32_t* status, void* stream) {
+    using namespace rlm;
+    if (batch == 0) return RLM_OK;
+    if (!tokens || !boundaries || !token_table || !boundary_table || !position_table || !position || !norm1_weight ||
+        !norm1_bias || !norm2_weight || !norm2_bias || !weight || !hidden || !out_first || !out_second) {
+        set_error("decode_front: NULL pointer");
+        return RLM_ERR_NULL;
+    }
+    if (batch < 0 || batch > 16 || n_first < 8 || n_first % 8 != 0 || n_second < 1 || vocab < 1 || boundary_vocab < 1 ||
+        max_t < 1) {
+        set_error("decode_front: at most 16 rows; the first projection's width must be a multiple of 8");
+        return RLM_ERR_SHAPE;
+    }
+    if (d_model != 256 && d_model != 512) {
+        set_error("decode_front: built for d = 256 and d = 512");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (dtype != RLM_BF16 && dtype != RLM_F16) {
+        set_error("decode_front: bfloat16 or float16 tables and weights");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    const void* vec[] = {token_table, boundary_table, position_table, norm1_weight, norm1_bias, norm2_weight, norm2_bias,
+                         weight, hidden, norm1_out, norm2_out};
+    for (const void* q : vec)
+        if (q && !aligned16(q)) { set_error("decode_front: tensors must be 16-byte aligned"); return RLM_ERR_ALIGN; }
+    FrontArgs f{};
+    f.proj.w = weight; f.proj.out = out_first; f.proj.rows = batch; f.proj.d = d_model; f.proj.n = n_first + n_second;
+    f.proj.dtype = dtype; f.proj.groups = (f.proj.n + 7) / 8;
+    f.out_second = out_second; f.n_first = n_first;
+    f.tokens = tokens; f.boundaries = boundaries; f.token_table = token_table; f.boundary_table = boundary_table;
+    f.position_table = position_table; f.position = position; f.hidden = hidden; f.status = status;
+    f.scale = scale; f.eps = norm_eps; f.vocab = vocab; f.boundary_vocab = boundary_vocab; f.max_t = max_t;
+    f.norm_w[0] = norm1_weight; f.norm_w[1] = norm2_weight; f.norm_b[0] = norm1_bias; f.norm_b[1] = norm2_bias;
+    f.norm_out[0] = norm1_out; f.norm_out[1] = norm2_out;
+    if (batch <= 8) return d_model == 256 ? launch_front<8, false>(f, stream) : launch_front<16, false>(f, stream);
+    return d_model == 256 ? launch_front<8, true>(f, stream) : launch_front<16, true>(f, stream);
 }
 
 // Bytes of the greedy head's scratch: 16 arg-max keys and the CTA counter.  Zero it once; every

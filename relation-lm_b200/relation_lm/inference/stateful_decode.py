@@ -23,7 +23,8 @@ from torch import Tensor
 
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
-from relation_lm.kernels.packed_projection import (decode_embed_norm, greedy_token, layer_norm_cast,
+from relation_lm.kernels.packed_projection import (decode_embed_norm, decode_front, decode_front_supported,
+                                                    greedy_token, layer_norm_cast,
                                                     packed_projection, packed_projection_slices,
                                                     skinny_argmax_scratch_bytes, skinny_projection,
                                                     skinny_projection_greedy, skinny_projection_supported)
@@ -47,7 +48,7 @@ class StatefulDecoder:
                  programmatic_launch: bool = True, second_layer_split: bool = False,
                  fused_query: bool | None = None, layer_tail: bool | None = None,
                  skinny: bool | None = None, append_in_projection: bool | None = None,
-                 whole_layer: bool | None = None) -> None:
+                 whole_layer: bool | None = None, fused_front: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -123,6 +124,13 @@ class StatefulDecoder:
         # (one launch fewer; off by default: the channels' serial statistics in the epilogue cost more
         # than the separate, fully parallel append launch that overlaps its neighbours)
         self.append_in_projection = bool(append_in_projection) and self.skinny
+        # ... and the step's front (embedding, two LayerNorms, packed projection, layer 0's query projection)
+        # is one launch of the same kind over the two weight matrices stacked: three launches fewer
+        can_front = (self.skinny and not self.append_in_projection and (self.fused_query or self.layer_tail)
+                     and decode_front_supported(B, cfg.d_model, self.w["w_packed"].shape[0], dtype))
+        self.fused_front = can_front if fused_front is None else (bool(fused_front) and can_front)
+        if self.fused_front:
+            self.front_weight = torch.cat((self.w["w_packed"], self.w["w_query"][0]), 0).contiguous()
         self._project = skinny_projection if self.skinny else packed_projection
         if self.skinny:
             self.argmax_scratch = torch.zeros(skinny_argmax_scratch_bytes(), device=self.device, dtype=torch.uint8)
@@ -232,11 +240,22 @@ class StatefulDecoder:
         cfg, w = self.config, self.w
         pos = self.position
         tokens, boundaries = tokens.contiguous(), boundaries.contiguous()
-        hidden = decode_embed_norm(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
-                                   w["position_embedding"], pos, self.input_scale,
-                                   w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
-                                   w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
-        if self.append_in_projection:
+        if self.fused_front:
+            hidden, packed = decode_front(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
+                                          w["position_embedding"], pos, self.input_scale, w["memory_norm_w"],
+                                          w["memory_norm_b"], w["input_norm_w"][0], w["input_norm_b"][0], cfg.norm_eps,
+                                          self.front_weight, w["w_packed"].shape[0], self.memory_normalized,
+                                          self.normalized, self.query)
+        else:
+            hidden = decode_embed_norm(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
+                                       w["position_embedding"], pos, self.input_scale,
+                                       w["memory_norm_w"], w["memory_norm_b"], self.memory_normalized,
+                                       w["input_norm_w"][0], w["input_norm_b"][0], self.normalized, cfg.norm_eps)
+        if self.fused_front:
+            sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
+                                self.partner_anchor_cache, *self.router_caches, *self.router_stats,
+                                w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
+        elif self.append_in_projection:
             # the packed projection's epilogue writes the token caches and updates the router state
             packed = packed_projection_append(self.memory_normalized, w["w_packed"], self.anchor_keys,
                                               self.partner_keys, self.operand_cache, self.partner_anchor_cache,
@@ -262,7 +281,7 @@ class StatefulDecoder:
         for l in range(cfg.layers):
             # layer 0 projects the embedding's normalised rows; later layers find their queries
             # written by the previous layer's norm-reduce when that fusion is on
-            q = self.query if ((self.fused_query or self.layer_tail) and l > 0) \
+            q = self.query if ((self.fused_query or self.layer_tail) and (l > 0 or self.fused_front)) \
                 else self._project(self.normalized, w["w_query"][l])
             last = l + 1 == cfg.layers
             next_w = w["final_norm_w"] if last else w["input_norm_w"][l + 1]

@@ -198,6 +198,61 @@ def _(tokens, boundaries, token_table, boundary_table, position_table, position,
     return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)
 
 
+def decode_front_supported(batch: int, d_model: int, n_first: int, dtype: torch.dtype) -> bool:
+    return batch <= 16 and d_model in (256, 512) and n_first % 8 == 0 and dtype in (torch.bfloat16, torch.float16)
+
+
+@torch.library.custom_op("relation_lm::decode_front", mutates_args=("norm1_out", "norm2_out", "out_second"),
+                         device_types="cuda")
+def decode_front(tokens: Tensor, boundaries: Tensor, token_table: Tensor, boundary_table: Tensor,
+                 position_table: Tensor, position: Tensor, scale: float, norm1_weight: Tensor, norm1_bias: Tensor,
+                 norm2_weight: Tensor, norm2_bias: Tensor, norm_eps: float, weight: Tensor, n_first: int,
+                 norm1_out: Tensor, norm2_out: Tensor, out_second: Tensor) -> tuple[Tensor, Tensor]:
+    """The front of a decode step in one launch (extension): embedding of one position, two LayerNorms
+    of the embedded rows and one projection of each — ``weight[:n_first]`` of the ``norm1`` rows (returned,
+    ``[B, n_first]``) and ``weight[n_first:]`` of the ``norm2`` rows (into ``out_second``).  Also returns
+    the embedded rows (fp32) and stores the two normalised copies.  At most 16 rows, ``d`` 256 or 512."""
+    device = _abi.require_cuda_contiguous(
+        tokens=tokens, boundaries=boundaries, token_table=token_table, boundary_table=boundary_table,
+        position_table=position_table, norm1_weight=norm1_weight, norm1_bias=norm1_bias, norm2_weight=norm2_weight,
+        norm2_bias=norm2_bias, weight=weight, norm1_out=norm1_out, norm2_out=norm2_out, out_second=out_second)
+    _abi.require_position(position, device)
+    if tokens.dtype != torch.int64 or boundaries.dtype != torch.int64:
+        raise ValueError("token and boundary ids must be int64")
+    batch, d_model = tokens.numel(), token_table.size(1)
+    n_total = weight.size(0)
+    n_first = int(n_first)
+    if boundaries.numel() != batch or boundary_table.size(1) != d_model or position_table.size(1) != d_model \
+            or weight.dim() != 2 or weight.size(1) != d_model or not 0 < n_first < n_total \
+            or norm1_out.shape != (batch, d_model) or norm2_out.shape != (batch, d_model) \
+            or out_second.shape != (batch, n_total - n_first):
+        raise ValueError("decode_front: inconsistent shapes")
+    for name, t in (("position_table", position_table), ("norm1_weight", norm1_weight), ("norm1_bias", norm1_bias),
+                    ("norm2_weight", norm2_weight), ("norm2_bias", norm2_bias)):
+        if t.dtype != torch.float32 or (name != "position_table" and t.numel() != d_model):
+            raise ValueError(f"{name} must be float32 of the model width")
+    dtype = _abi.same_dtype("16-bit operand", token_table, boundary_table, weight, norm1_out, norm2_out, out_second)
+    hidden = torch.empty((batch, d_model), device=device, dtype=torch.float32)
+    out_first = torch.empty((batch, n_first), device=device, dtype=weight.dtype)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_decode_front(
+            _abi.ptr(tokens), _abi.ptr(boundaries), _abi.ptr(token_table), _abi.ptr(boundary_table),
+            _abi.ptr(position_table), _abi.ptr(position), float(scale), _abi.ptr(norm1_weight), _abi.ptr(norm1_bias),
+            _abi.ptr(norm2_weight), _abi.ptr(norm2_bias), float(norm_eps), _abi.ptr(weight), _abi.ptr(hidden),
+            _abi.ptr(norm1_out), _abi.ptr(norm2_out), _abi.ptr(out_first), _abi.ptr(out_second), batch, d_model,
+            n_first, n_total - n_first, token_table.size(0), boundary_table.size(0), position_table.size(0), dtype,
+            _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+    return hidden, out_first
+
+
+@decode_front.register_fake
+def _(tokens, boundaries, token_table, boundary_table, position_table, position, scale, norm1_weight, norm1_bias,
+      norm2_weight, norm2_bias, norm_eps, weight, n_first, norm1_out, norm2_out, out_second):
+    batch = tokens.numel()
+    return (token_table.new_empty((batch, token_table.size(1)), dtype=torch.float32),
+            weight.new_empty((batch, n_first)))
+
+
 def greedy_token(logits: Tensor, vocab: int, position: Tensor | None = None) -> Tensor:
     """``logits[:, :vocab].argmax(-1)`` (ties to the lowest index) as int64 ``[rows]``; with
     ``position`` (a 0-d int64 device tensor) the position is advanced by one in the same launch."""

@@ -130,7 +130,7 @@ def _check_position(dec, wc, t, tokens_t, bounds_t, before, trace):
     assert_rel_close(layers[0]["query"], want_q0, 1e-2, f"query t={t} l=0")
 
 
-@pytest.mark.parametrize("mode", ["whole_layer", "layer_tail", "separate"])
+@pytest.mark.parametrize("mode", ["whole_layer", "layer_tail", "layer_tail_separate_front", "separate"])
 def test_fused_bf16_step_of_the_ctx512_decode_configuration_is_pinned_per_kernel(mode):
     from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
     from relation_lm.inference.stateful_decode import StatefulDecoder
@@ -140,10 +140,12 @@ def test_fused_bf16_step_of_the_ctx512_decode_configuration_is_pinned_per_kernel
     model = RoutedRelationLM(cfg, seed=1002)
     B, T = 8, cfg.max_context
     layer_tail = mode != "separate"
-    dec = StatefulDecoder(model, B, "cuda", torch.bfloat16, layer_tail=layer_tail, whole_layer=mode == "whole_layer")
+    dec = StatefulDecoder(model, B, "cuda", torch.bfloat16, layer_tail=layer_tail, whole_layer=mode == "whole_layer",
+                          fused_front=mode != "layer_tail_separate_front")
     if layer_tail and not dec.layer_tail:
         pytest.skip("clusters of 16 CTAs are not available on this device")
     assert dec.whole_layer == (mode == "whole_layer")
+    assert dec.fused_front == (mode != "layer_tail_separate_front")
     assert dec.fused and dec.stacked_expand and not dec.fused_tail and dec.layer_tail == layer_tail
     assert dec.fused_query != layer_tail
     wc = {k: v.float().cpu() for k, v in dec.w.items()}

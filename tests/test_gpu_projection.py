@@ -225,3 +225,42 @@ def test_skinny_projection_with_greedy_head(dtype):
         assert int(position.item()) == 42 + call
         assert not scratch.any()
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,d,n_first,n_second", [(8, 512, 3072, 256), (1, 512, 3072, 256), (16, 256, 512, 256),
+                                                  (11, 256, 1000, 72)])
+def test_decode_front_matches_embedding_norms_and_projections(B, d, n_first, n_second, dtype):
+    """One launch for embedding + two LayerNorms + two projections against the separate launches:
+    embedded rows bit-equal, normalised rows within one 16-bit step, projections within 1e-2 of
+    the oracle's product of the launch's own normalised rows."""
+    from relation_lm.kernels.packed_projection import decode_embed_norm, decode_front
+
+    g = torch.Generator().manual_seed(8800 + B + d)
+    V, Vb, T, t = 700, 16, 64, 37
+    tok_table = torch.randn(V, d, generator=g).to(dtype)
+    bnd_table = (torch.randn(Vb, d, generator=g) * 0.5).to(dtype)
+    pos_table = torch.randn(T, d, generator=g) * 0.3
+    w1, b1 = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.1
+    w2, b2 = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.1
+    weight = (torch.randn(n_first + n_second, d, generator=g) * 0.05).to(dtype)
+    tokens = torch.randint(0, V, (B,), generator=g)
+    bounds = torch.randint(0, Vb, (B,), generator=g)
+    dev = lambda x: x.cuda()  # noqa: E731
+    n1 = torch.full((B, d), float("nan"), device="cuda", dtype=dtype)
+    n2 = torch.full((B, d), float("nan"), device="cuda", dtype=dtype)
+    second = torch.full((B, n_second), float("nan"), device="cuda", dtype=dtype)
+    hidden, first = decode_front(dev(tokens), dev(bounds), dev(tok_table), dev(bnd_table), dev(pos_table),
+                                 position_tensor(t), 1.7, dev(w1), dev(b1), dev(w2), dev(b2), 1e-5, dev(weight), n_first,
+                                 n1, n2, second)
+    r1 = torch.empty(B, d, device="cuda", dtype=dtype)
+    r2 = torch.empty(B, d, device="cuda", dtype=dtype)
+    ref_hidden = decode_embed_norm(dev(tokens), dev(bounds), dev(tok_table), dev(bnd_table), dev(pos_table),
+                                   position_tensor(t), 1.7, dev(w1), dev(b1), r1, dev(w2), dev(b2), r2, 1e-5)
+    assert torch.equal(hidden, ref_hidden)
+    step = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    for got, ref in ((n1, r1), (n2, r2)):
+        assert bool(((got.float() - ref.float()).abs() <= step * ref.float().abs() + 1e-6).all())
+    assert_rel_close(first, oracle.linear(n1.cpu(), weight[:n_first]), 1e-2, "first projection")
+    assert_rel_close(second, oracle.linear(n2.cpu(), weight[n_first:]), 1e-2, "second projection")
+    assert_status_clear()

@@ -337,3 +337,34 @@ def test_whole_sequence_selector_equals_the_per_row_selector(context, blocks, lo
     assert torch.equal(tiled[0].cpu()[sample], want[0]) and torch.equal(tiled[2].cpu()[sample], want[2])
     assert_scores_equal(tiled[3][sample.cuda()], want[3])
     assert_status_clear()
+
+
+@pytest.mark.parametrize("B,T,NB,L,top,K", [
+    (8, 512, 16, 64, 2, 8),       # the ctx-512 decode configuration: both key caches resident (128 KB)
+    (3, 768, 12, 32, 3, 4),       # block 64; the largest context whose caches still fit
+    (2, 256, 16, 128, 4, 8),      # window of half the context
+])
+def test_decode_form_with_resident_caches_equals_the_rows_form_and_oracle(B, T, NB, L, top, K):
+    """bf16 decode launches of at most one row per SM stage the sequence's whole key caches up to the
+    position instead of window + picked blocks (no second round of copies): same indices and scores,
+    bit for bit, as the per-row form (which stages window and blocks) and as the oracle."""
+    from relation_lm.kernels.relation_select import relation_select_packed, relation_select_packed_rows
+
+    case = {"kind": "select", "seed": 7300 + T, "batch": B, "context": T, "blocks": NB, "local_window": L,
+            "top_blocks": top, "k_out": K, "strict_valid": True, "dtype": "bf16"}
+    x = cases.make_inputs(case)
+    xg = to_cuda(x)
+    rows = torch.arange(B, dtype=torch.int32).cuda()
+    bs = T // NB
+    for t in sorted({0, 1, L - 1, L, bs - 1, bs, 2 * bs + 1, T // 2, T - 2, T - 1}):
+        got = relation_select_packed(*select_args(xg), position_tensor(t), L, top, K, True)
+        ref = relation_select_packed_rows(*select_args(xg), rows, torch.full((B,), t, dtype=torch.int32).cuda(),
+                                          L, top, K, True)
+        for a, b in zip(got, ref):
+            assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a,
+                               b.view(torch.int32) if b.dtype == torch.float32 else b), t
+        oa, oa_s, op, op_s, _ = oracle.relation_select(*select_args(x), t, L, top, K, True)
+        assert torch.equal(got[0].cpu(), oa) and torch.equal(got[2].cpu(), op), t
+        assert_scores_equal(got[1], oa_s)
+        assert_scores_equal(got[3], op_s)
+    assert_status_clear()
