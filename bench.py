@@ -315,10 +315,32 @@ def kernel_table(dec, graph_iters: int = 20):
                             dec.partner_anchor_cache, *dec.router_caches, *dec.router_stats,
                             w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
 
+    fused_front = getattr(dec, "fused_front", False)
+    norm_rows = [torch.empty(B, d, device=dev, dtype=dec.dtype) for _ in range(2)]
+
+    def front(_):
+        from relation_lm.kernels.packed_projection import decode_front
+        decode_front(tokens_in, tokens_in % cfg.boundary_vocab_size, w["token_embedding"], w["boundary_embedding"],
+                     w["position_embedding"], pos, dec.input_scale, w["memory_norm_w"], w["memory_norm_b"],
+                     w["input_norm_w"][0], w["input_norm_b"][0], cfg.norm_eps, dec.front_weight, w["w_packed"].shape[0],
+                     norm_rows[0], norm_rows[1], projected)
+
+    def head(_):
+        from relation_lm.kernels.packed_projection import skinny_projection
+        skinny_projection(normalized, dec.head_weight, dec.head_bias)
+
+    tokens_in = torch.randint(0, cfg.vocab_size, (B,), device=dev)
     cand = cfg.local_window + cfg.top_blocks * cfg.block_size
     nb = cfg.max_context // cfg.block_size
+    # bf16 decode launches of at most one row per SM keep both key caches resident when they fit
+    resident = (dec.dtype == torch.bfloat16 and B <= 148 and cfg.top_blocks > 0
+                and 2 * cfg.max_context * 128 + 4 * nb * 128 + 8192 <= 223 * 1024)
+    key_rows = cfg.max_context if resident else cand
+    n_head = dec.head_weight.size(0) if getattr(dec, "skinny", False) else 0
     bytes_per_launch = {
-        "relation_select_kernel": B * (e * (4 * nb * 64 + 2 * cand * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K),
+        "skinny_front_kernel": e * ((L * (384 + R) + 256) * d + 2 * B * d + B * (L * (384 + R) + 256)) + 8 * B * d,
+        "skinny_projection_kernel(head)": e * (n_head * d + B * d + B * n_head),
+        "relation_select_kernel": B * (e * (4 * nb * 64 + 2 * key_rows * 64 + 64 + 64 + 128 + 128) + 2 * (4 + 64) * 4 + 8 + 8 * K),
         "relation_hidden_kernel": B * (e * ((1 + K) * H + (1 + K) * R) + 8 + 4 * K + e * K * H) + e * H * R
                                   + (0 if stacked else e * 2 * H * R + B * e * (R + 2 * H)),
         "expanded_row_update_kernel(all layers)": L * (e * 2 * H * R + B * e * (R + 2 * H)),
@@ -335,6 +357,8 @@ def kernel_table(dec, graph_iters: int = 20):
     # projection inside norm-reduce only layer 0 projects separately and only the last layer's
     # norm-reduce runs without a projection
     for name, fn, per_graph, per_step in (
+            ("skinny_front_kernel", front, 1, 1),
+            ("skinny_projection_kernel(head)", head, 1, 1),
             ("relation_select_kernel", select, L, L),
             ("relation_layer_tail_kernel", tail, L, L),
             ("relation_hidden_kernel", hidden, L, L),
@@ -344,6 +368,12 @@ def kernel_table(dec, graph_iters: int = 20):
             ("router_cache_update_kernel(all layers)", append, 1, 1),
             ("expanded_row_update_kernel(all layers)", expand, 1, 1)):
         if name.startswith("expanded_row_update") and not stacked:
+            continue
+        if name == "skinny_front_kernel" and not fused_front:
+            continue
+        if name == "skinny_projection_kernel(head)" and not n_head:
+            continue
+        if name == "packed_projection_kernel(query)" and fused_front:
             continue
         if name == "relation_norm_reduce_project_kernel" and not fused_query:
             continue
@@ -660,7 +690,9 @@ def run_ours(args) -> None:
                           "sequences from a synthetic end-of-prefix state, CPU port of the step (C oracle + fp32 torch matmuls)")
             cpu_extra = {"runs": cpu_runs, "one_thread": {"value": one_value, "unit": UNIT, "cores": 1,
                                                           "sample": "median of 3 runs of 2 positions"}}
-            if REFERENCE_INSTALL.exists():
+            if args.no_extras:
+                cpu_extra["dense_reference"] = {"unavailable": "skipped (--no-extras)"}
+            elif REFERENCE_INSTALL.exists():
                 cpu_extra["dense_reference"] = run_subprocess_json("--dense-cpu", 300)
                 extras["reference_triton"] = run_subprocess_json("--op-microbench=reference", 420)
                 extras["ours_same_protocol"] = run_subprocess_json("--op-microbench=ours", 240)
@@ -1314,6 +1346,9 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=256)
     parser.add_argument("--ctx", type=int, default=2048,
                         help="cache length of --kernel-case runs (shorter caches keep profiler captures small)")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the child-process legs (the reference's Triton operators and dense CPU modules): "
+                             "for profiler runs, which would otherwise list their launches too")
     parser.add_argument("--no-cfg5", action="store_true",
                         help="skip the 256-sequence 12-layer companion measurement of the default run")
     parser.add_argument("--op-microbench", choices=("ours", "reference"), default=None,
