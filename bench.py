@@ -1247,6 +1247,16 @@ def run_kernel_case(args) -> None:
                 w_packed = rn(12 * (384 + R), d) * 0.02          # the 12-layer packed projection matrix
             x = S[i % sets]
             fn = lambda: packed_projection(x, w_packed)  # noqa: E731
+        elif args.kernel_case in ("projection_rows", "second_layer_rows"):
+            if i == 0:
+                from relation_lm.kernels.packed_projection import packed_projection
+                # the packed projection of a 4096-position state build (12 layers, d 768), or the second
+                # relation-MLP layer of a whole-sequence pass (262 144 pairs, hidden 2048 -> d 512)
+                Mp, Kp, Np = (4096, 768, 6144) if args.kernel_case == "projection_rows" else (262144, 2048, 512)
+                S = [rn(Mp, Kp) for _ in range(2)]
+                w_rows = rn(Np, Kp) * 0.02
+            x = S[i % 2]
+            fn = lambda: packed_projection(x, w_rows)  # noqa: E731
         elif args.kernel_case == "tail":
             if i == 0:
                 from relation_lm.kernels.relation_reduce import relation_layer_tail
@@ -1339,7 +1349,7 @@ def main() -> None:
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
     parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router",
-                                                 "tail", "head", "select_tile", "hidden_rows"),
+                                                 "tail", "head", "select_tile", "hidden_rows", "projection_rows", "second_layer_rows"),
                         default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")

@@ -264,3 +264,34 @@ def test_decode_front_matches_embedding_norms_and_projections(B, d, n_first, n_s
     assert_rel_close(first, oracle.linear(n1.cpu(), weight[:n_first]), 1e-2, "first projection")
     assert_rel_close(second, oracle.linear(n2.cpu(), weight[n_first:]), 1e-2, "second projection")
     assert_status_clear()
+
+
+@pytest.mark.parametrize("rows,d_in,n_out,dtype,bias", [
+    (20000, 256, 512, torch.bfloat16, False),      # 157 x 2 tiles of 128 x 256: the persistent kernel
+    (20001, 192, 512, torch.float16, True),        # ragged last row tile, three K-blocks (fewer than the ring), bias
+    (4096, 768, 6144, torch.bfloat16, False),      # the packed projection of a whole-sequence state build
+    (19000, 2048, 256, torch.bfloat16, True),      # one n-tile, 32 K-blocks
+])
+def test_many_rows_projection_matches_torch_and_oracle(rows, d_in, n_out, dtype, bias):
+    """Products with at least two 128 x 256 tiles per SM run persistent CTAs with two accumulators: every
+    element against torch's fp32 product of the same 16-bit operands (1e-2 of the row's largest
+    magnitude), sampled rows against the oracle."""
+    from relation_lm.kernels.packed_projection import packed_projection
+
+    g = torch.Generator().manual_seed(rows + d_in + n_out)
+    x = torch.randn(rows, d_in, generator=g).to(dtype)
+    w = (torch.randn(n_out, d_in, generator=g) * 0.05).to(dtype)
+    b = torch.randn(n_out, generator=g) if bias else None
+    xg, wg = x.cuda(), w.cuda()
+    got = packed_projection(xg, wg, b.cuda() if bias else None)
+    assert got.shape == (rows, n_out) and got.dtype == dtype
+    want = xg.float() @ wg.float().T
+    if bias:
+        want = want + b.cuda()
+    assert_rel_close(got, want, 1e-2)
+    sample = torch.randperm(rows, generator=g)[:64]
+    ref = oracle.linear(x[sample], w) + (b if bias else 0.0)
+    assert_rel_close(got[sample.cuda()].cpu(), ref, 1e-2)
+    again = packed_projection(xg, wg, b.cuda() if bias else None)
+    assert torch.equal(got, again)
+    assert_status_clear()
