@@ -378,14 +378,24 @@ __global__ void __launch_bounds__(kSkThreads) skinny_front_kernel(const FrontArg
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             uint16_t* xk = k ? x2 : x1;
-            const float* gw = f.norm_w[k] + c0;
-            const float* gb = f.norm_b[k] + c0;
+            const float4* gw = reinterpret_cast<const float4*>(f.norm_w[k] + c0);
+            const float4* gb = reinterpret_cast<const float4*>(f.norm_b[k] + c0);
 #pragma unroll
-            for (int i = 0; i < per; ++i) xk[i] = to16<kBf16>(fmaf((v[i] - mean) * inv, gw[i], gb[i]));
-            if (store && f.norm_out[k]) {
-                uint16_t* o = static_cast<uint16_t*>(f.norm_out[k]) + static_cast<int64_t>(m) * d + c0;
+            for (int i = 0; i < per; i += 8) {
+                const float4 w0 = gw[i / 4], w1 = gw[i / 4 + 1], b0 = gb[i / 4], b1 = gb[i / 4 + 1];
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                uint32_t packed[4];
 #pragma unroll
-                for (int i = 0; i < per; i += 8) *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<const uint4*>(xk + i);
+                for (int e = 0; e < 4; ++e) {
+                    const uint16_t lo = to16<kBf16>(fmaf((v[i + 2 * e] - mean) * inv, wv[2 * e], bv[2 * e]));
+                    const uint16_t hi = to16<kBf16>(fmaf((v[i + 2 * e + 1] - mean) * inv, wv[2 * e + 1], bv[2 * e + 1]));
+                    packed[e] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                }
+                const uint4 chunk = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(xk + i) = chunk;
+                if (store && f.norm_out[k])
+                    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(f.norm_out[k]) + static_cast<int64_t>(m) * d + c0 + i) = chunk;
             }
         }
     }
