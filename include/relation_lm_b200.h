@@ -320,6 +320,22 @@ int rlm_expanded_cache_append(void* expanded_cache, const void* operand_cache,
                               int32_t* status, void* stream);
 
 /*
+ * The same with the operand rows of position t taken from the packed projection rows of that
+ * position instead of the operand cache: packed [B, row stride] in the caches' dtype, layer l's
+ * operand at columns [l * packed_layer_stride + operand_offset, + R) (384 + R and 128 for the layout
+ * of rlm_sparse_cache_append).  Same results, but independent of the state append: under
+ * programmatic dependent launch the kernel works while the launch right before it (the append) is
+ * still running and waits for it only at its end.  Rule for callers: `packed` must come from an
+ * earlier launch than the immediate predecessor on the stream.
+ */
+int rlm_expanded_cache_append_packed(void* expanded_cache, const void* packed, int64_t packed_row_stride,
+                                     int packed_layer_stride, int operand_offset,
+                                     const void* anchor_weight, const void* partner_weight,
+                                     const void* first_bias, const int64_t* position, int layers,
+                                     int batch, int max_t, int relation_dim, int hidden_dim,
+                                     int dtype, int32_t* status, void* stream);
+
+/*
  * Decode-state append for every layer of a stack in one launch (extension).  Does what a
  * reference decode step does per layer after PackedSparseCacheProjection.project
  * (src/relation_lm/inference/packed_cache.py:52-57): writes the four token features into

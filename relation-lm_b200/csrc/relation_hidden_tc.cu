@@ -62,6 +62,12 @@ struct HiddenTcArgs {
 struct RowUpdateArgs {
     void* expanded_cache;           // [layers, n_seq, max_t, 2H]
     const void* operand_cache;      // [layers, n_seq, max_t, R]
+    // alternative source of the current operand rows: the packed projection rows of this position
+    // ([n_seq, packed_stride], layer l's operand at column l * packed_layer + packed_offset), which an
+    // EARLIER launch than the immediate predecessor wrote: the kernel then works before its dependency wait
+    const void* packed;
+    int64_t packed_stride;
+    int packed_layer, packed_offset;
     const void* first_bias;         // [layers, H]
     const int64_t* position;
     int32_t* status;
@@ -576,9 +582,14 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(n_cols >> 3) << 17) |
                            (static_cast<uint32_t>(kBM >> 4) << 24);
 
+    // With the packed rows as the source nothing this kernel reads comes from the launch right before it
+    // (the state append, which it then overlaps): the dependency wait moves to the end, where it only
+    // keeps the stream's ordering chain intact.
+    const bool early = a.packed != nullptr;
     const int t = static_cast<int>(*a.position);
     if (t < 0 || t >= a.max_t) {
         if (tid == 0 && a.status) atomicOr(a.status, RLM_DEV_POSITION);
+        griddep_sync();
         return;
     }
 
@@ -606,7 +617,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
                      ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    griddep_sync();
+    if (!early) griddep_sync();
     // current operand rows of the group's sequences (zero rows up to n_cols), copied
     // asynchronously straight to their swizzled places
     const size_t op_row = static_cast<size_t>(R) * 2;
@@ -615,8 +626,10 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
         const int j = i / chunks, c = i - j * chunks;
         const uint32_t dst = smem_u32(cur_tile) + swizzled(j, c, cur_kblock);
         if (j < n_here)
-            cp_async16(dst, static_cast<const char*>(a.operand_cache) +
-                                ((static_cast<size_t>(layer) * a.n_seq + s0 + j) * a.max_t + t) * op_row + 16 * c);
+            cp_async16(dst, early ? static_cast<const char*>(a.packed) +
+                                        (static_cast<size_t>(s0 + j) * a.packed_stride + layer * a.packed_layer + a.packed_offset) * 2 + 16 * c
+                                  : static_cast<const char*>(a.operand_cache) +
+                                        ((static_cast<size_t>(layer) * a.n_seq + s0 + j) * a.max_t + t) * op_row + 16 * c);
         else
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
     }
@@ -682,6 +695,7 @@ __global__ void __launch_bounds__(kUpdThreads) expanded_row_update_kernel(
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    if (early) griddep_sync();       // every kernel waits for its predecessor before it lets its successor go
 }
 
 size_t gather_smem_bytes(int rdim, int k_out) { return 1024 + gather_plan(rdim, kBM / k_out).total; }
@@ -709,8 +723,10 @@ bool hidden_tc_applicable(bool update, int n_rows, int rdim, int hdim, int k_out
 int launch_row_update(void* expanded_cache, const void* operand_cache, const void* anchor_weight,
                       const void* partner_weight, const void* first_bias, const int64_t* position,
                       int layers, int n_seq, int max_t, int rdim, int hdim, int dtype, int32_t* status,
-                      void* stream) {
+                      void* stream, const void* packed = nullptr, int64_t packed_stride = 0, int packed_layer = 0,
+                      int packed_offset = 0) {
     RowUpdateArgs u{};
+    u.packed = packed; u.packed_stride = packed_stride; u.packed_layer = packed_layer; u.packed_offset = packed_offset;
     u.expanded_cache = expanded_cache; u.operand_cache = operand_cache; u.first_bias = first_bias;
     u.position = position; u.status = status; u.n_seq = n_seq; u.max_t = max_t; u.rdim = rdim;
     u.hdim = hdim; u.dtype = dtype;
@@ -791,6 +807,39 @@ int launch_hidden_tc(bool update, void* expanded_cache, const void* operand_cach
 }
 
 }  // namespace rlm
+
+extern "C" int rlm_expanded_cache_append_packed(void* expanded_cache, const void* packed, int64_t packed_row_stride,
+                                                int packed_layer_stride, int operand_offset,
+                                                const void* anchor_weight, const void* partner_weight,
+                                                const void* first_bias, const int64_t* position, int layers,
+                                                int batch, int max_t, int relation_dim, int hidden_dim,
+                                                int dtype, int32_t* status, void* stream) {
+    using namespace rlm;
+    if (layers == 0 || batch == 0) return RLM_OK;
+    if (!expanded_cache || !packed || !anchor_weight || !partner_weight || !first_bias || !position) {
+        set_error("expanded_cache_append_packed: NULL pointer");
+        return RLM_ERR_NULL;
+    }
+    if (layers < 0 || batch < 0 || max_t < 1 || relation_dim < kBK || relation_dim % kBK != 0 ||
+        hidden_dim < 128 || hidden_dim % 128 != 0 || operand_offset < 0 || operand_offset % 8 != 0 ||
+        packed_layer_stride < operand_offset + relation_dim || packed_layer_stride % 8 != 0 ||
+        packed_row_stride < static_cast<int64_t>(layers) * packed_layer_stride || packed_row_stride % 8 != 0) {
+        set_error("expanded_cache_append_packed: need relation_dim a multiple of 64, hidden_dim a multiple of 128 and "
+                  "packed rows whose layer stride, operand offset and row stride are multiples of 8 elements");
+        return RLM_ERR_SHAPE;
+    }
+    if (dtype != RLM_BF16 && dtype != RLM_F16) {
+        set_error("expanded_cache_append_packed: caches, packed rows and weights must be bfloat16 or float16");
+        return RLM_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(expanded_cache) || !aligned16(packed) || !aligned16(anchor_weight) || !aligned16(partner_weight)) {
+        set_error("expanded_cache_append_packed: tensors must be 16-byte aligned");
+        return RLM_ERR_ALIGN;
+    }
+    return launch_row_update(expanded_cache, nullptr, anchor_weight, partner_weight, first_bias, position, layers, batch,
+                             max_t, relation_dim, hidden_dim, dtype, status, stream, packed, packed_row_stride,
+                             packed_layer_stride, operand_offset);
+}
 
 extern "C" int rlm_expanded_cache_append(void* expanded_cache, const void* operand_cache,
                                          const void* anchor_weight, const void* partner_weight,

@@ -28,7 +28,8 @@ from relation_lm.kernels.packed_projection import (decode_embed_norm, decode_fro
                                                     packed_projection, packed_projection_slices,
                                                     skinny_argmax_scratch_bytes, skinny_projection,
                                                     skinny_projection_greedy, skinny_projection_supported)
-from relation_lm.kernels.relation_reduce import (expanded_cache_append, relation_hidden_cache_update,
+from relation_lm.kernels.relation_reduce import (expanded_cache_append, expanded_cache_append_packed,
+                                                 relation_hidden_cache_update,
                                                  relation_layer_tail, relation_layer_tail_supported,
                                                  relation_hidden_cached_out,
                                                  relation_hidden_cache_update_out,
@@ -266,8 +267,12 @@ class StatefulDecoder:
             sparse_cache_append(packed, self.anchor_keys, self.partner_keys, self.operand_cache,
                                 self.partner_anchor_cache, *self.router_caches, *self.router_stats,
                                 w["anchor_conv_weight"], w["partner_conv_weight"], pos, cfg.block_size)
-        if self.stacked_expand:
-            # every layer's operand row of this position is known: expand them all at once
+        if self.stacked_expand and self.fused_front:
+            # every layer's operand row of this position is known: expand them all at once, straight from
+            # the packed rows (written two launches back), so that this launch overlaps the append
+            expanded_cache_append_packed(self.expanded_cache, packed, w["anchor_weight"], w["partner_weight"],
+                                         w["first_bias"], pos)
+        elif self.stacked_expand:
             expanded_cache_append(self.expanded_cache, self.operand_cache, w["anchor_weight"],
                                   w["partner_weight"], w["first_bias"], pos)
         if keep_selection:

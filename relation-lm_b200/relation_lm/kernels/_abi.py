@@ -29,6 +29,7 @@ PROTOTYPES = {
     "rlm_norm_projection": [_P, _L, _P, _P, _F, _P, _P] + [_I] * 5 + [_P, _P],
     "rlm_set_programmatic_launch": [_I],
     "rlm_expanded_cache_append": [_P] * 6 + [_I] * 6 + [_P, _P],
+    "rlm_expanded_cache_append_packed": [_P, _P, _L, _I, _I] + [_P] * 4 + [_I] * 6 + [_P, _P],
     "rlm_layer_norm_cast": [_P, _L, _P, _P, _F, _P] + [_I] * 3 + [_P],
     "rlm_relation_tail": [_P] * 7 + [_F] + [_P] * 4 + [_L] + [_I] * 5 + [_P, _P],
     "rlm_relation_tail_static": [_P] * 7 + [_F] + [_P] * 3 + [_I] * 5 + [_P, _P],

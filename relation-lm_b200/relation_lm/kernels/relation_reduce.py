@@ -178,6 +178,47 @@ def _(expanded_cache, operand_cache, anchor_weight, partner_weight, first_bias, 
     return None
 
 
+@torch.library.custom_op("relation_lm::expanded_cache_append_packed", mutates_args=("expanded_cache",),
+                         device_types="cuda")
+def expanded_cache_append_packed(
+    expanded_cache: Tensor,
+    packed: Tensor,
+    anchor_weight: Tensor,
+    partner_weight: Tensor,
+    first_bias: Tensor,
+    position: Tensor,
+) -> None:
+    """``expanded_cache_append`` with the operand rows of the position read from the packed projection
+    rows ``packed [B, L * (384 + R)]`` (layout of ``sparse_cache_append``) instead of the operand cache:
+    same results, no dependence on the state append, which it overlaps under programmatic launch.
+    ``packed`` must not come from the launch right before this one on the stream."""
+    device = _abi.require_cuda_contiguous(
+        expanded_cache=expanded_cache, anchor_weight=anchor_weight, partner_weight=partner_weight,
+        first_bias=first_bias)
+    _abi.require_cuda_rows(packed=packed)
+    _abi.require_position(position, device)
+    if expanded_cache.dim() != 4 or anchor_weight.dim() != 3 or packed.dim() != 2:
+        raise ValueError("expected expanded_cache [L, B, T, 2H], packed [B, L * (384 + R)], weights [L, H, R]")
+    layers, batch, max_t, _ = expanded_cache.shape
+    hdim, rdim = anchor_weight.size(1), anchor_weight.size(2)
+    if expanded_cache.size(3) != 2 * hdim or anchor_weight.shape != (layers, hdim, rdim) \
+            or partner_weight.shape != anchor_weight.shape or first_bias.shape != (layers, hdim) \
+            or packed.shape != (batch, layers * (384 + rdim)):
+        raise ValueError("expected expanded_cache [L, B, T, 2H], packed [B, L * (384 + R)], weights [L, H, R], bias [L, H]")
+    if len({anchor_weight.dtype, partner_weight.dtype, first_bias.dtype, expanded_cache.dtype, packed.dtype}) != 1:
+        raise ValueError("cache, packed rows, weights and bias must share one 16-bit dtype")
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_expanded_cache_append_packed(
+            _abi.ptr(expanded_cache), _abi.ptr(packed), packed.stride(0), 384 + rdim, 128, _abi.ptr(anchor_weight),
+            _abi.ptr(partner_weight), _abi.ptr(first_bias), _abi.ptr(position), layers, batch, max_t, rdim, hdim,
+            _abi.code(expanded_cache), _abi.ptr(_abi.status_tensor(device)), _abi.stream_ptr(device)))
+
+
+@expanded_cache_append_packed.register_fake
+def _(expanded_cache, packed, anchor_weight, partner_weight, first_bias, position):
+    return None
+
+
 @torch.library.custom_op("relation_lm::relation_hidden_cache_update",
                          mutates_args=("expanded_cache",), device_types="cuda")
 def relation_hidden_cache_update(

@@ -150,4 +150,14 @@ def test_stacked_expanded_cache_append(layers, B, H, R, dtype):
     untouched = torch.ones(T, dtype=torch.bool)
     untouched[t] = False
     assert torch.equal(got[:, :, untouched], expanded[:, :, untouched])
+    # the same rows with the operands read from packed projection rows (layout of sparse_cache_append)
+    from relation_lm.kernels.relation_reduce import expanded_cache_append_packed
+
+    width = 384 + R
+    packed = torch.randn(B, layers * width, generator=g).to(dtype)
+    for l in range(layers):
+        packed[:, l * width + 128:l * width + 128 + R] = operand[l, :, t]
+    cache2 = expanded.cuda().clone()
+    expanded_cache_append_packed(cache2, packed.cuda(), wa.cuda(), wp.cuda(), bias.cuda(), position_tensor(t))
+    assert torch.equal(cache2, cache)
     assert_status_clear()
