@@ -524,6 +524,16 @@ int rlm_greedy_token(const void* logits, int64_t row_stride, int64_t* next_token
 int64_t rlm_skinny_argmax_scratch_bytes(void);
 
 /*
+ * L2 prefetch of up to 16 address ranges (extension; no counterpart in the reference project): one
+ * launch issues `prefetch.global.L2` for every whole 128-byte line of the ranges, in the order
+ * given.  It moves nothing into the SMs and nothing depends on it: run it on a side stream at the
+ * head of a decode step (a sibling branch of the step's CUDA graph) with the weights and caches the
+ * step's later kernels will read, so that a step that starts with a cold L2 does not fetch them
+ * from DRAM one dependent round trip at a time.  `ranges` and `bytes` are HOST arrays.
+ */
+int rlm_l2_prefetch(const void* const* ranges, const int64_t* bytes, int n_ranges, void* stream);
+
+/*
  * The front of a decode step in one launch (extension): the embedding of one position
  * (src/relation_lm/models/relation_lm.py:130-131: (token + boundary embedding) * scale + position
  * embedding), two LayerNorms of the embedded rows and one projection of each,

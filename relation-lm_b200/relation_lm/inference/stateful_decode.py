@@ -24,7 +24,7 @@ from torch import Tensor
 from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import (decode_embed_norm, decode_front, decode_front_supported,
-                                                    greedy_token, layer_norm_cast,
+                                                    greedy_token, l2_prefetch, layer_norm_cast,
                                                     packed_projection, packed_projection_slices,
                                                     skinny_argmax_scratch_bytes, skinny_projection,
                                                     skinny_projection_greedy, skinny_projection_supported)
@@ -49,7 +49,8 @@ class StatefulDecoder:
                  programmatic_launch: bool = True, second_layer_split: bool = False,
                  fused_query: bool | None = None, layer_tail: bool | None = None,
                  skinny: bool | None = None, append_in_projection: bool | None = None,
-                 whole_layer: bool | None = None, fused_front: bool | None = None) -> None:
+                 whole_layer: bool | None = None, fused_front: bool | None = None,
+                 prefetch: bool | None = None) -> None:
         cfg = model.config
         self.programmatic_launch = bool(programmatic_launch)
         self.config, self.batch, self.device, self.dtype = cfg, int(batch), torch.device(device), dtype
@@ -132,6 +133,13 @@ class StatefulDecoder:
         self.fused_front = can_front if fused_front is None else (bool(fused_front) and can_front)
         if self.fused_front:
             self.front_weight = torch.cat((self.w["w_packed"], self.w["w_query"][0]), 0).contiguous()
+        # A step of a small batch is a chain of dependent launches on a fraction of the SMs; when it
+        # starts with a cold L2 every one of them first waits for its weights and caches to come from
+        # DRAM.  One launch on a side stream at the head of the step can ask for all of them at once.
+        # Off by default: measured 3-5 us SLOWER per step (cold and warm) than letting every kernel
+        # fetch its own data under programmatic launch; the fork and join cost more than they hide.
+        self.prefetch = bool(prefetch) and self.fused
+        self._side_stream = torch.cuda.Stream(self.device) if self.prefetch else None
         self._project = skinny_projection if self.skinny else packed_projection
         if self.skinny:
             self.argmax_scratch = torch.zeros(skinny_argmax_scratch_bytes(), device=self.device, dtype=torch.uint8)
@@ -241,6 +249,14 @@ class StatefulDecoder:
         cfg, w = self.config, self.w
         pos = self.position
         tokens, boundaries = tokens.contiguous(), boundaries.contiguous()
+        if self.prefetch:
+            main = torch.cuda.current_stream(self.device)
+            self._side_stream.wait_stream(main)
+            with torch.cuda.stream(self._side_stream):
+                # in the order the step reads them
+                l2_prefetch([w["anchor_weight"], w["partner_weight"], self.anchor_keys, self.partner_keys,
+                             *self.router_stats, self.partner_anchor_cache, w["product_weight"], w["w2"],
+                             self.operand_cache, w["w_query"], self.head_weight])
         if self.fused_front:
             hidden, packed = decode_front(tokens, boundaries, w["token_embedding"], w["boundary_embedding"],
                                           w["position_embedding"], pos, self.input_scale, w["memory_norm_w"],
@@ -384,8 +400,12 @@ class StatefulDecoder:
             logits, chosen = skinny_projection_greedy(self.normalized, self.head_weight, self.head_bias,
                                                       cfg.vocab_size, self.argmax_scratch, pos)
             self.last_logits = logits
+            if self.prefetch:
+                main.wait_stream(self._side_stream)      # join the side branch (long finished) at the step's end
             return chosen
         logits = self._project(self.normalized, self.head_weight, self.head_bias)
+        if self.prefetch:
+            main.wait_stream(self._side_stream)
         self.last_logits = logits                        # [B, padded vocab + boundary vocab]
         token_logits = logits[:, :cfg.vocab_size]
         boundary_logits = logits[:, cfg.vocab_size:cfg.vocab_size + cfg.boundary_vocab_size]

@@ -198,6 +198,27 @@ def _(tokens, boundaries, token_table, boundary_table, position_table, position,
     return token_table.new_empty((tokens.numel(), token_table.size(1)), dtype=torch.float32)
 
 
+def l2_prefetch(tensors: list[Tensor]) -> None:
+    """Issue L2 prefetches for up to 16 CUDA tensors (their storage from the first element to the last), in
+    order, on the current stream (extension; see ``rlm_l2_prefetch``).  Not a registered operator: it has no
+    outputs and no effect on values."""
+    import ctypes
+
+    tensors = [t for t in tensors if t is not None and t.numel() > 0]
+    if not tensors:
+        return
+    if len(tensors) > 16:
+        raise ValueError("at most 16 tensors per call")
+    device = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda or t.device != device or not t.is_contiguous():
+            raise ValueError("l2_prefetch takes contiguous CUDA tensors of one device")
+    ranges = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    sizes = (ctypes.c_int64 * len(tensors))(*[t.numel() * t.element_size() for t in tensors])
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_l2_prefetch(ranges, sizes, len(tensors), _abi.stream_ptr(device)))
+
+
 def decode_front_supported(batch: int, d_model: int, n_first: int, dtype: torch.dtype) -> bool:
     return batch <= 16 and d_model in (256, 512) and n_first % 8 == 0 and dtype in (torch.bfloat16, torch.float16)
 

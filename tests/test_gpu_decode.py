@@ -339,3 +339,31 @@ def test_one_launch_per_layer_equals_select_then_tail_bit_for_bit():
         for (pa, pp), (sa, sp_) in zip(two.last_selection, one.last_selection):
             assert torch.equal(pa, sa) and torch.equal(pp, sp_), t
     assert_status_clear()
+
+
+def test_l2_prefetch_branch_changes_no_value():
+    """The optional side-stream L2 prefetch at the head of a step (off by default) is invisible in the
+    results, eagerly and through a captured graph."""
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+    from relation_lm.inference.stateful_decode import StatefulDecoder
+
+    cfg = RoutedRelationConfig()
+    model = RoutedRelationLM(cfg, seed=91)
+    B, steps = 3, 40
+    g = torch.Generator().manual_seed(92)
+    tokens = torch.randint(0, cfg.vocab_size, (B, steps), generator=g).cuda()
+    bounds = torch.randint(0, cfg.boundary_vocab_size, (B, steps), generator=g).cuda()
+    plain = StatefulDecoder(model, B, "cuda", torch.bfloat16)
+    eager = StatefulDecoder(model, B, "cuda", torch.bfloat16, prefetch=True)
+    graphed = StatefulDecoder(model, B, "cuda", torch.bfloat16, prefetch=True)
+    assert not plain.prefetch and eager.prefetch
+    graphed.capture()
+    for t in range(steps):
+        a = plain.step(tokens[:, t], bounds[:, t])
+        b = eager.step(tokens[:, t], bounds[:, t])
+        graphed.static_tokens.copy_(tokens[:, t])
+        graphed.static_boundaries.copy_(bounds[:, t])
+        graphed.replay()
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), t
+        assert torch.equal(a[0], graphed.static_token_logits), t
+    assert_status_clear()
