@@ -323,7 +323,8 @@ __global__ void __launch_bounds__(kTcThreads, 3) relation_hidden_tc_kernel(
 // the expanded-cache terms of tile j + 1 (cp.async) are in flight and the MMA of tile j + 1 runs
 // into the second half of the tensor memory while the warps finish tile j (tcgen05.ld, + terms,
 // GELU, 16-bit results stored straight from the registers, 64 contiguous bytes per thread).  16-bit
-// outputs only.  (32 warps with 16 columns per thread measured slower: 1.13 ms against 0.99 ms.)
+// outputs only.  (Measured slower: 32 warps with 16 columns per thread, 1.13 ms against 0.99 ms; a
+// seventeenth warp that only requests weight tiles and issues the MMAs, 0.95 ms against 0.905 ms.)
 constexpr int kRowsThreads = 512;
 
 struct RowsPlan { uint32_t a_tile, w_tile[2], terms[2], partner_rows, total; };
@@ -443,21 +444,33 @@ __global__ void __launch_bounds__(kRowsThreads, 1) relation_hidden_rows_kernel(
         }
     }
     // the expanded-cache terms of hidden tile j: row g < RPT of the staging area is the anchor term
-    // of sequence g, row RPT + r the partner term of pair r (16 threads copy a 256-byte row)
+    // of sequence g, row RPT + r the partner term of pair r (16 threads copy a 256-byte row).  The
+    // rows a thread copies are the same for every hidden tile: their source addresses are worked
+    // out once, a tile then costs one copy instruction per row.
+    constexpr int kTermRows = 2 * kBM * 16 / kRowsThreads;     // staged rows per thread, at most (RPT + pairs <= 256)
+    const char* term_src[kTermRows];
+    {
+        const int c = tid & 15, n_rows_staged = RPT + tile_pairs;
+#pragma unroll
+        for (int k = 0; k < kTermRows; ++k) {
+            const int g = (tid >> 4) + k * (kRowsThreads / 16);
+            term_src[k] = nullptr;
+            if (g >= n_rows_staged) continue;
+            const int r = g - RPT;
+            const int rb = g < RPT ? g : (r * a.inv_k16) >> 16;
+            if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
+            const int at = g < RPT ? idx_s[rb * (K + 1)] : idx_s[rb * (K + 1) + (r - rb * K) + 1];
+            term_src[k] = static_cast<const char*>(a.expanded_cache) +
+                          ((static_cast<size_t>(seq_s[rb]) * a.max_t + at) * 2 * H + (g < RPT ? 0 : H)) * 2 + 16 * c;
+        }
+    }
+    const uint32_t term_dst = static_cast<uint32_t>((tid >> 4) * kRowStride + 16 * (tid & 15));
     auto request_terms = [&](int j) {
         if (j < n_tiles) {
-            unsigned char* dst = base + plan.terms[j & 1];
-            const int c = tid & 15, n_rows_staged = RPT + tile_pairs, h0 = j * kTcBN;
-#pragma unroll 1
-            for (int g = tid >> 4; g < n_rows_staged; g += kRowsThreads / 16) {
-                const int r = g - RPT;
-                const int rb = g < RPT ? g : (r * a.inv_k16) >> 16;
-                if (row0 + rb >= a.n_rows || seq_s[rb] < 0) continue;
-                const int at = g < RPT ? idx_s[rb * (K + 1)] : idx_s[rb * (K + 1) + (r - rb * K) + 1];
-                const char* src = static_cast<const char*>(a.expanded_cache) +
-                                  ((static_cast<size_t>(seq_s[rb]) * a.max_t + at) * 2 * H + (g < RPT ? 0 : H) + h0) * 2;
-                cp_async16(smem_u32(dst) + g * kRowStride + 16 * c, src + 16 * c);
-            }
+            const uint32_t dst = smem_u32(base + plan.terms[j & 1]) + term_dst;
+#pragma unroll
+            for (int k = 0; k < kTermRows; ++k)
+                if (term_src[k]) cp_async16(dst + k * (kRowsThreads / 16) * kRowStride, term_src[k] + static_cast<size_t>(j) * kTcBN * 2);
         }
         cp_async_commit();
     };
