@@ -213,6 +213,7 @@ def test_multi_anchor_stack_configuration_at_full_shape():
     (3, 2, 512, 8, 128, 2, 8, 300, True),        # block 64, 256 candidates, queries over a prefix only, ragged last tile
     (8, 1, 192, 12, 16, 1, 2, 192, False),       # eight slots, block 16 (remote passes span blocks)
     (2, 2, 128, 4, 128, 0, 4, 128, True),        # no remote blocks: the window is the whole history
+    (2, 1, 4096, 128, 128, 4, 8, 600, True),     # 128 blocks of statistics: tiles of 8 warps instead of 16
 ])
 def test_whole_sequence_multi_anchor_selector_equals_the_per_row_selector(S, B, T, NB, L, top, K, Tq, strict):
     """The tiled whole-sequence form against the per-row multi-anchor kernel on the same rows: anchors,

@@ -309,6 +309,7 @@ def test_a_bounded_wait_that_expires_reports_timeout_and_leaves_the_context_usab
     (128, 8, 32, 0, 5, False, 128),       # no remote blocks
     (512, 8, 128, 4, 8, False, 500),      # block 64, window 128, 384 candidates; ragged last tile
     (192, 24, 16, 3, 4, True, 70),        # block 8, more than 16 blocks, queries for a prefix only
+    (4096, 128, 128, 4, 8, True, 700),    # 128 blocks of statistics: the 16-warp tile does not fit, 8 warps serve
 ])
 def test_whole_sequence_selector_equals_the_per_row_selector(context, blocks, local_window, top_blocks, k_out,
                                                              strict, query_length, dtype):
@@ -317,6 +318,8 @@ def test_whole_sequence_selector_equals_the_per_row_selector(context, blocks, lo
     from relation_lm.kernels.relation_select import relation_select_packed_prefill, relation_select_packed_rows
 
     B = 3
+    if dtype == "fp32" and blocks * 4 * 256 + 2 * (local_window + 32) * 256 > 200 * 1024:
+        pytest.skip("fp32 statistics and windows of this shape exceed the shared memory (the per-row kernel serves it)")
     case = {"kind": "select", "seed": 8800 + context + top_blocks, "batch": B, "context": context, "blocks": blocks,
             "rows": B * query_length, "local_window": local_window, "top_blocks": top_blocks, "k_out": k_out,
             "strict_valid": strict, "dtype": dtype, "quantize": dtype == "fp32"}
