@@ -251,13 +251,20 @@ class MultiAnchorPrefill:
                        w["partner_bias"])
         tiled = (self.tiled_select and self.dtype == torch.bfloat16
                  and cfg.local_window + cfg.top_blocks * cfg.block_size <= 512)
+        selected = None
         if tiled:
             # whole sequences: tiles of consecutive positions share the staged statistics and windows
-            anchor, anchor_score, anchor_active, partner, partner_score, partner_active = relation_select_multi_prefill(
-                *select_args, T, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
-        else:
-            anchor, anchor_score, anchor_active, partner, partner_score, partner_active = relation_select_multi_rows(
-                *select_args, rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+            try:
+                selected = relation_select_multi_prefill(*select_args, T, cfg.local_window, cfg.top_blocks, K,
+                                                         cfg.strict_valid)
+            except (ValueError, RuntimeError) as error:
+                if "shared memory" not in str(error):       # only "the tile's staging does not fit" falls back
+                    raise
+                self.tiled_select = False                   # rejected before anything was launched
+        if selected is None:
+            selected = relation_select_multi_rows(*select_args, rb, rp, cfg.local_window, cfg.top_blocks, K,
+                                                  cfg.strict_valid)
+        anchor, anchor_score, anchor_active, partner, partner_score, partner_active = selected
         pair_rows = rb.repeat_interleave(S)
         hidden_rel = torch.empty(N * S, K, H, device=self.device, dtype=self.dtype)
         relation_hidden_cached_rows_out(hidden_rel, state["expanded_cache"], state["operand_cache"],

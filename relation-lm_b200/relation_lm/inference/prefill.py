@@ -110,13 +110,20 @@ class RoutedPrefillLayer:
                        w["anchor_gamma"], w["anchor_bias"], q[:, 128:256], state["partner_anchor_cache"],
                        state["partner_keys"], state["partner_mean"], state["partner_std"], w["partner_gamma"],
                        w["partner_bias"])
+        selected = None
         if self.tiled_select and cfg.local_window + cfg.top_blocks * cfg.block_size <= 512:
             # all positions of every sequence: tiles of consecutive positions share their staging
-            anchor, anchor_score, partner, partner_score = relation_select_packed_prefill(
-                *select_args, T, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
-        else:
-            anchor, anchor_score, partner, partner_score = relation_select_packed_rows(
-                *select_args, rb, rp, cfg.local_window, cfg.top_blocks, K, cfg.strict_valid)
+            try:
+                selected = relation_select_packed_prefill(*select_args, T, cfg.local_window, cfg.top_blocks, K,
+                                                          cfg.strict_valid)
+            except (ValueError, RuntimeError) as error:
+                if "shared memory" not in str(error):       # only "the tile's staging does not fit" falls back
+                    raise
+                self.tiled_select = False                   # rejected before anything was launched
+        if selected is None:
+            selected = relation_select_packed_rows(*select_args, rb, rp, cfg.local_window, cfg.top_blocks, K,
+                                                   cfg.strict_valid)
+        anchor, anchor_score, partner, partner_score = selected
         hidden_rel = torch.empty(N, K, H, device=self.device, dtype=self.dtype)
         relation_hidden_cached_rows_out(hidden_rel, state["expanded_cache"], state["operand_cache"], anchor,
                                         partner, w["product_weight"], rb)
