@@ -111,6 +111,10 @@ class ClockSampler:
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        late = not self.samples
+        deadline = time.time() + 0.2                    # a region shorter than the sampling period: take the next sample
+        while not self.samples and time.time() < deadline:
+            time.sleep(0.005)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -119,9 +123,12 @@ class ClockSampler:
         sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         reasons = sorted({n for s in self.samples for n, v in zip(names, s[3:7]) if v == "Active"})
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": float(self.samples[0][1]) if self.samples else None,
-                "samples": len(self.samples), "reasons": reasons}
+        record = {"sm_mhz": statistics.median(sm) if sm else None,
+                  "sm_max_mhz": float(self.samples[0][1]) if self.samples else None,
+                  "samples": len(self.samples), "reasons": reasons}
+        if late and self.samples:
+            record["note"] = "the timed region was shorter than the 20 ms sampling period: sampled right after it"
+        return record
 
 
 # ---------------------------------------------------------------------------- CPU arm
