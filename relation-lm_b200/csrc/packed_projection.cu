@@ -198,21 +198,24 @@ __global__ void __launch_bounds__(kGemmThreads) packed_projection_kernel(
                      ::"r"(tmem_base), "r"(tmem_cols) : "memory");
 }
 
-// ------------------------------------------------------------------ many rows: persistent CTAs, 128 x 256 tiles
+// ------------------------------------------------------------------ many rows: persistent CTAs
 //
-// Products with thousands of rows (whole-sequence passes).  One CTA per SM walks output tiles of
-// 128 x 256 (n-tiles fastest, so that the CTAs running at the same time share their x rows in L2);
-// three roles, each on bounded waits:
-//   warp 0, one lane: TMA producer, a ring of four stages (x 128 x 64 | w 256 x 64 = 48 KB each);
-//   warp 1, one lane: tcgen05.mma 128 x 256 x 16 into one of TWO accumulators (2 x 256 TMEM columns);
-//   warps 2-9: epilogue of the previous tile (tcgen05.ld, bias, convert, store; two warps per
-//   quarter of the TMEM lanes, 128 columns each) while the next tile's main loop runs into the
-//   other accumulator — with four epilogue warps a K = 768 tile's epilogue outlasted its main loop.
-// Against the one-tile-per-CTA kernel above: half the weight traffic per output, no tensor-memory
-// and barrier set-up per tile, and the epilogue off the critical path.
+// Products with thousands of rows (whole-sequence passes).  One CTA per SM walks output tiles
+// (n-tiles fastest, so that the CTAs running at the same time share their x rows in L2); three
+// roles, each on bounded waits:
+//   warp 0, one lane: TMA producer, a ring of stages (x rows x 64 | w 256 x 64);
+//   warp 1, one lane: tcgen05.mma 128 x 256 x 16;
+//   warps 2-9: epilogue (tcgen05.ld, bias, convert, store; two warps per quarter of the TMEM lanes,
+//   128 columns each).
+// kRowTiles = 1: tiles of 128 x 256, two accumulators (2 x 256 TMEM columns) used by alternate
+// tiles, so that a tile's epilogue runs behind the next tile's main loop.
+// kRowTiles = 2: tiles of 256 x 256 — two row tiles share every w tile, which halves the weight
+// traffic per output: without a two-SM MMA every CTA fetches its operands through its own
+// 64-byte-per-clock L2 port, and at 85 flop per byte (128 x 256) that port, not the tensor pipe,
+// sets the pace.  Both accumulators belong to one tile; the next tile's MMAs into an accumulator
+// start as soon as the epilogue has read it out.
 constexpr int kPgThreads = 320;
 constexpr int kPgBN = 256;
-constexpr int kPgStages = 4;
 
 struct PersistentGemmArgs {
     void* out;
@@ -227,15 +230,18 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+template <int kRowTiles>
 __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
     const PersistentGemmArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * kPgStages + 4];
+    constexpr int kStages = kRowTiles == 2 ? 3 : 4;
+    __shared__ __align__(8) unsigned long long bars[2 * kStages + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
-    constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kPgBN * kBK * 2, kStageBytes = kABytes + kBBytes;
+    constexpr int kTileRows = kBM * kRowTiles;
+    constexpr uint32_t kABytes = kTileRows * kBK * 2, kBBytes = kPgBN * kBK * 2, kStageBytes = kABytes + kBBytes;
     unsigned char* ring = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const uint32_t ring_addr = smem_u32(ring);
@@ -243,14 +249,14 @@ __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_ke
     const int k_blocks = a.k / kBK;
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
-    auto empty = [&](int s) { return bar0 + 8u * (kPgStages + s); };
-    auto acc_full = [&](int b) { return bar0 + 8u * (2 * kPgStages + b); };
-    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kPgStages + 2 + b); };
+    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * kStages + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * kStages + 2 + b); };
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-        for (int i = 0; i < 2 * kPgStages; ++i) mbar_init(bar0 + 8u * i, 1);
+        for (int i = 0; i < 2 * kStages; ++i) mbar_init(bar0 + 8u * i, 1);
         mbar_init(acc_full(0), 1);
         mbar_init(acc_full(1), 1);
         mbar_init(acc_empty(0), 8);                  // one arrival per epilogue warp
@@ -274,10 +280,10 @@ __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_ke
             int it = 0;                                          // stage uses so far, across tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kPgBN;
+                const int m0 = (tile / a.tiles_n) * kTileRows, n0 = (tile % a.tiles_n) * kPgBN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kPgStages;
-                    if (it >= kPgStages && !mbar_wait(empty(s), ((it / kPgStages) - 1) & 1)) { ok = false; break; }
+                    const int s = it % kStages;
+                    if (it >= kStages && !mbar_wait(empty(s), ((it / kStages) - 1) & 1)) { ok = false; break; }
                     mbar_expect_tx(full(s), kStageBytes);
                     tma_load_2d(ring_addr + s * kStageBytes, &map_x, kb * kBK, m0, full(s));
                     tma_load_2d(ring_addr + s * kStageBytes + kABytes, &map_w, kb * kBK, n0, full(s));
@@ -291,20 +297,27 @@ __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_ke
             int it = 0, j = 0;                                   // stage uses / tiles so far
             bool ok = true;
             for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x, ++j) {
-                const int b = j & 1;
-                // the epilogue must have read this accumulator's previous tile out
-                if (j >= 2 && !mbar_wait(acc_empty(b), ((j >> 1) - 1) & 1)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t acc = tmem_base + static_cast<uint32_t>(b * kPgBN);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kPgStages;
-                    if (!mbar_wait(full(s), (it / kPgStages) & 1)) { ok = false; break; }
+                // kRowTiles == 1: accumulator j & 1, free once the epilogue of tile j - 2 has read it out.
+                // kRowTiles == 2: both accumulators, each free once the epilogue of tile j - 1 has read it out.
+                const int b = kRowTiles == 1 ? (j & 1) : 0;
+                if (kRowTiles == 1 && j >= 2 && !mbar_wait(acc_empty(b), ((j >> 1) - 1) & 1)) { ok = false; break; }
+                for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(full(s), (it / kStages) & 1)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = smem_desc_sw128(ring_addr + s * kStageBytes);
                     const uint64_t db = smem_desc_sw128(ring_addr + s * kStageBytes + kABytes);
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; ++kk)
-                        umma_f16(acc, da + 2 * kk, db + 2 * kk, a.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    for (int r = 0; r < kRowTiles; ++r) {
+                        if (kRowTiles == 2 && kb == 0 && j >= 1) {
+                            if (!mbar_wait(acc_empty(r), (j - 1) & 1)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        const uint32_t acc = tmem_base + static_cast<uint32_t>((kRowTiles == 1 ? b : r) * kPgBN);
+                        const uint64_t da = smem_desc_sw128(ring_addr + s * kStageBytes + r * (kBM * kBK * 2));
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; ++kk)
+                            umma_f16(acc, da + 2 * kk, db + 2 * kk, a.idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
                     umma_commit(empty(s));
                 }
                 umma_commit(acc_full(b));                        // tile complete (or abandoned)
@@ -319,53 +332,57 @@ __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_ke
         int j = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x, ++j) {
-            const int b = j & 1;
-            const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kPgBN;
-            ok = mbar_wait(acc_full(b), (j >> 1) & 1);
+            const int b = kRowTiles == 1 ? (j & 1) : 0;
+            const int m0 = (tile / a.tiles_n) * kTileRows, n0 = (tile % a.tiles_n) * kPgBN;
+            ok = mbar_wait(acc_full(b), kRowTiles == 1 ? ((j >> 1) & 1) : (j & 1));
             ok = __all_sync(0xffffffffu, ok) && (*reinterpret_cast<volatile int*>(&failed) == 0);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = m0 + 32 * quarter + lane;
 #pragma unroll 1
-            for (int c = col_half * (kPgBN / 2); c < (col_half + 1) * (kPgBN / 2); c += 32) {
-                uint32_t v[32];
-                tmem_ld16(tmem_base + lane_base + b * kPgBN + c, *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
-                tmem_ld16(tmem_base + lane_base + b * kPgBN + c + 16, *reinterpret_cast<uint32_t(*)[16]>(&v[16]));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c + 32 == (col_half + 1) * (kPgBN / 2)) {
-                    // the accumulator is in registers: hand it back to the MMA warp
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty(b));
-                }
-                if (a.bias) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + a.bias[n0 + c + i]);
-                }
-                if (row >= a.m) continue;
-                const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
-                if (a.out_dtype == RLM_F32) {
-                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        o[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                           __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-                } else {
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
-                        if (a.out_dtype == RLM_BF16) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&h);
-                        } else {
-                            __half2 h = __floats2half2_rn(lo, hi);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&h);
-                        }
+            for (int r = 0; r < kRowTiles; ++r) {
+                const int accn = kRowTiles == 1 ? b : r;
+                const int row = m0 + kBM * r + 32 * quarter + lane;
+#pragma unroll 1
+                for (int c = col_half * (kPgBN / 2); c < (col_half + 1) * (kPgBN / 2); c += 32) {
+                    uint32_t v[32];
+                    tmem_ld16(tmem_base + lane_base + accn * kPgBN + c, *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
+                    tmem_ld16(tmem_base + lane_base + accn * kPgBN + c + 16, *reinterpret_cast<uint32_t(*)[16]>(&v[16]));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c + 32 == (col_half + 1) * (kPgBN / 2)) {
+                        // this warp's share of the accumulator is in registers: hand it back to the MMA warp
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(accn));
                     }
-                    uint4* o = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + at);
+                    if (a.bias) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + a.bias[n0 + c + i]);
+                    }
+                    if (row >= a.m) continue;
+                    const size_t at = static_cast<size_t>(row) * a.n + n0 + c;
+                    if (a.out_dtype == RLM_F32) {
+                        float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + at);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            o[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                               __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+                            if (a.out_dtype == RLM_BF16) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                                packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                            } else {
+                                __half2 h = __floats2half2_rn(lo, hi);
+                                packed[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        }
+                        uint4* o = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + at);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    }
                 }
             }
         }
@@ -379,13 +396,15 @@ __global__ void __launch_bounds__(kPgThreads, 1) packed_projection_persistent_ke
                      ::"r"(tmem_base), "r"(2 * kPgBN) : "memory");
 }
 
+template <int kRowTiles>
 int launch_persistent_gemm(const CUtensorMap& mx, const CUtensorMap& mw, PersistentGemmArgs& a, void* stream) {
-    const int smem_bytes = kPgStages * (kBM * kBK * 2 + kPgBN * kBK * 2) + 1024;
-    auto kernel = packed_projection_persistent_kernel;
+    constexpr int kStages = kRowTiles == 2 ? 3 : 4;
+    const int smem_bytes = kStages * (kRowTiles * kBM * kBK * 2 + kPgBN * kBK * 2) + 1024;
+    auto kernel = packed_projection_persistent_kernel<kRowTiles>;
     int rc = allow_large_smem(reinterpret_cast<const void*>(kernel), kSmemPerCta);
     if (rc != RLM_OK) return rc;
     a.tiles_n = a.n / kPgBN;
-    a.tiles = a.tiles_n * ((a.m + kBM - 1) / kBM);
+    a.tiles = a.tiles_n * ((a.m + kRowTiles * kBM - 1) / (kRowTiles * kBM));
     const int ctas = a.tiles < sm_count() ? a.tiles : sm_count();
     launch_kernel(kernel, dim3(ctas), dim3(kPgThreads), smem_bytes, stream, mx, mw, a);
     count_launch();
@@ -827,9 +846,11 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
     }
     const int m_tiles = (rows + kBM - 1) / kBM;
     if (k_splits == 1 && n_out % kPgBN == 0 && d_in % kBK == 0 && m_tiles * (n_out / kPgBN) >= 2 * sm_count()) {
-        // at least two 128 x 256 tiles per SM: persistent CTAs with the epilogue behind the next tile's main loop
+        // at least two 128 x 256 tiles per SM: persistent CTAs; 256 x 256 tiles when there are two of those per SM
+        // (a 256-row tile's epilogue is not hidden behind the next main loop: it pays only with a long reduction)
+        const bool tall = d_in >= 1024 && ((rows + 2 * kBM - 1) / (2 * kBM)) * (n_out / kPgBN) >= 2 * sm_count();
         CUtensorMap px, pw;
-        if (!make_map(&px, x, rows, d_in, x_row_stride, kBM, in_dtype) ||
+        if (!make_map(&px, x, rows, d_in, x_row_stride, tall ? 2 * kBM : kBM, in_dtype) ||
             !make_map(&pw, weight, n_out, d_in, d_in, kPgBN, in_dtype)) {
             set_error("packed_projection: cuTensorMapEncodeTiled failed");
             return RLM_ERR_LAUNCH;
@@ -839,7 +860,7 @@ extern "C" int rlm_packed_projection(const void* x, int64_t x_row_stride, const 
         const uint32_t pfmt = in_dtype == RLM_BF16 ? 1u : 0u;
         p.idesc = (1u << 4) | (pfmt << 7) | (pfmt << 10) | (static_cast<uint32_t>(kPgBN >> 3) << 17) |
                   (static_cast<uint32_t>(kBM >> 4) << 24);
-        return launch_persistent_gemm(px, pw, p, stream);
+        return tall ? launch_persistent_gemm<2>(px, pw, p, stream) : launch_persistent_gemm<1>(px, pw, p, stream);
     }
     // Tile width: with few rows the weight read dominates, so pick the widest tile that still
     // gives about one CTA per SM; with many rows use wide tiles.

@@ -271,6 +271,8 @@ def test_decode_front_matches_embedding_norms_and_projections(B, d, n_first, n_s
     (20001, 192, 512, torch.float16, True),        # ragged last row tile, three K-blocks (fewer than the ring), bias
     (4096, 768, 6144, torch.bfloat16, False),      # the packed projection of a whole-sequence state build
     (19000, 2048, 256, torch.bfloat16, True),      # one n-tile, 32 K-blocks
+    (40001, 1024, 512, torch.float16, True),       # 256 x 256 tiles (two row tiles share a weight tile), ragged last tile
+    (76000, 1088, 256, torch.bfloat16, False),     # 256 x 256 tiles, one n-tile, 17 K-blocks
 ])
 def test_many_rows_projection_matches_torch_and_oracle(rows, d_in, n_out, dtype, bias):
     """Products with at least two 128 x 256 tiles per SM run persistent CTAs with two accumulators: every
