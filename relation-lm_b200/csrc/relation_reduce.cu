@@ -680,6 +680,90 @@ __global__ void __launch_bounds__(kNormThreads, kVecChunks <= 2 ? 4 : (kVecChunk
     norm_reduce_vec_row<kVecChunks, false, kPlain>(a, blockIdx.x, partial, nullptr);
 }
 
+// ---- thousands of rows (whole-sequence passes): a warp per row
+//
+// The CTA-per-row kernels above spread a row's K partners over the warps and meet in shared
+// memory: right for a decode batch, where a row's latency counts, but a pass over 10^4 .. 10^5 rows
+// is a stream of K x dim 16-bit values per row and should run at memory speed.  Here a warp owns a
+// row: it requests all its active partners' rows at once (K x dim / 16 sixteen-byte loads in
+// flight per lane), then normalises and accumulates them one after the other with warp shuffles
+// only — no shared memory, no block-wide barrier.  Plain form only: 16-bit raw rows in one slice,
+// fp32 parameters, context output.  Same formulas as relation_norm_reduce_vec_kernel
+// (src/relation_lm/kernels/relation_reduce.py:360-417 of the reference project).
+constexpr int kRowWarpK = 8;          // partners per row this form holds in registers
+
+template <int kChunks, bool kBf16>
+__global__ void __launch_bounds__(256) relation_norm_reduce_warp_kernel(const NormArgs a) {
+    griddep_sync();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= a.n_rows) return;
+    const int K = a.k_out;
+    constexpr int D = 256 * kChunks;
+    const int t = a.row_position ? a.row_position[row] : static_cast<int>(*a.position);
+    const float s = lane < K ? a.scores[static_cast<size_t>(row) * K + lane] : kNegInf;
+    int k_limit = 32 - __clz(max(t, 0) + 1);   // ceil(log2(t + 2))
+    k_limit = min(max(k_limit, 1), K);
+    const bool active = lane < K && lane < k_limit && s > -1.0e30f;
+    const unsigned live = __ballot_sync(0xffffffffu, active);
+    // every active partner's row, requested before anything is computed
+    const uint4* raw_row = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.raw) + static_cast<size_t>(row) * K * D);
+    uint4 raw[kRowWarpK][kChunks];
+#pragma unroll
+    for (int k = 0; k < kRowWarpK; ++k)
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            raw[k][i] = make_uint4(0, 0, 0, 0);
+            if ((live >> k) & 1u) raw[k][i] = raw_row[k * (D / 8) + lane + 32 * i];
+        }
+    const float f = active ? s : -1.0e4f;
+    float mx = f;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+    const float e = active ? expf(f - mx) : 0.0f;
+    const float w = e / fmaxf(warp_sum(e), 1.0e-9f);
+    float gm[kChunks][8], bt[kChunks][8], y[kChunks][8];
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+        load8(a.weight, 8 * (lane + 32 * i), RLM_F32, gm[i]);
+        load8(a.bias, 8 * (lane + 32 * i), RLM_F32, bt[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[i][j] = 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < kRowWarpK; ++k) {
+        const float wk = __shfl_sync(0xffffffffu, w, k);
+        if (!((live >> k) & 1u) || wk == 0.0f) continue;       // (warp-uniform) inactive slots contribute nothing
+        float x[kChunks][8], sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            Raw8 r8;
+            r8.lo = raw[k][i];
+            r8.hi = make_uint4(0, 0, 0, 0);
+            convert8(r8, kBf16 ? RLM_BF16 : RLM_F16, x[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += x[i][j];
+        }
+        const float mean = warp_sum(sum) / static_cast<float>(D);
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { x[i][j] -= mean; sq = fmaf(x[i][j], x[i][j], sq); }
+        const float inv = rsqrtf(warp_sum(sq) / static_cast<float>(D) + a.eps);
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[i][j] = fmaf(wk, fmaf(x[i][j] * inv, gm[i][j], bt[i][j]), y[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+        float4* dst = reinterpret_cast<float4*>(a.out + static_cast<size_t>(row) * D + 8 * (lane + 32 * i));
+        dst[0] = make_float4(y[i][0], y[i][1], y[i][2], y[i][3]);
+        dst[1] = make_float4(y[i][4], y[i][5], y[i][6], y[i][7]);
+    }
+}
+
 // ---- norm-reduce + residual + next LayerNorm + the next layer's query projection, for decode
 // batches of a few rows.  A cluster of proj_out_dim / 32 CTAs serves one row: every CTA requests
 // its 32 x dim slice of the projection weight before the dependency wait (eight lanes per output
@@ -859,6 +943,19 @@ int norm_reduce_launch(
         launch_kernel_cluster(kernel, grid, dim3(kNormThreads), slices, smem_bytes, stream, a);
         count_launch();
         return check_launch("relation_norm_reduce_project_kernel");
+    }
+    // thousands of rows in the plain form: a warp per row, all of a row's partner rows in flight at once
+    if (vec && n_rows >= 2048 && k_out <= kRowWarpK && dim % 256 == 0 && out && !residual && !next_normalized &&
+        a.raw_splits == 1 && !raw_bias && param_dtype == RLM_F32 && (raw_dtype == RLM_BF16 || raw_dtype == RLM_F16)) {
+        using Kernel = void (*)(const NormArgs);
+        const bool bf16 = raw_dtype == RLM_BF16;
+        Kernel kernel = dim == 256 ? (bf16 ? relation_norm_reduce_warp_kernel<1, true> : relation_norm_reduce_warp_kernel<1, false>)
+                      : dim == 512 ? (bf16 ? relation_norm_reduce_warp_kernel<2, true> : relation_norm_reduce_warp_kernel<2, false>)
+                      : dim == 768 ? (bf16 ? relation_norm_reduce_warp_kernel<3, true> : relation_norm_reduce_warp_kernel<3, false>)
+                                   : (bf16 ? relation_norm_reduce_warp_kernel<4, true> : relation_norm_reduce_warp_kernel<4, false>);
+        launch_kernel(kernel, dim3((n_rows + 7) / 8), dim3(256), 0, stream, a);
+        count_launch();
+        return check_launch("relation_norm_reduce_warp_kernel");
     }
     // the decode step's dtypes (bf16 rows in one slice, fp32 parameters) take builds without dtype branches
     const bool plain_rows = raw_dtype == RLM_BF16 && param_dtype == RLM_F32 && a.raw_splits == 1 && !raw_bias &&

@@ -290,3 +290,30 @@ def test_split_k_second_layer_feeds_norm_reduce(splits):
     want_norm = F.layer_norm(want_hidden, (D,), next_w, next_b, 1e-5)
     assert_rel_close(normalized, want_norm, 1e-2)
     assert_status_clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,K,D", [(4096, 8, 512), (2500, 5, 768), (3001, 4, 256), (2048, 8, 1024), (2050, 1, 512)])
+def test_many_rows_norm_reduce_matches_the_oracle(N, K, D, dtype):
+    """Launches of thousands of rows take the warp-per-row kernel (all of a row's partner rows in flight at
+    once, no shared memory): against the oracle on the same 16-bit rows (fp32 tolerance), with empty slots,
+    rows without any partner and early positions that limit the active slots; a launch just below the
+    threshold (the CTA-per-row kernel) agrees within the same tolerance."""
+    from relation_lm.kernels.relation_reduce import relation_norm_reduce_rows
+
+    g = torch.Generator().manual_seed(6500 + N + K + D)
+    raw = torch.randn(N, K, D, generator=g).to(dtype)
+    scores = torch.randn(N, K, generator=g)
+    scores[::3, -1] = -torch.inf
+    scores[5::17] = -torch.inf                      # rows without any active partner: context 0
+    gamma, beta = torch.rand(D, generator=g) + 0.5, torch.randn(D, generator=g) * 0.1
+    row_pos = torch.randint(0, 4096, (N,), generator=g, dtype=torch.int32)
+    row_pos[::5] = torch.randint(0, 6, ((N + 4) // 5,), generator=g, dtype=torch.int32)   # k_limit below K
+    got = relation_norm_reduce_rows(raw.cuda(), scores.cuda(), gamma.cuda(), beta.cuda(), row_pos.cuda(), 1e-5)
+    want = oracle.relation_norm_reduce(raw.float(), scores, gamma, beta, 0, 1e-5, row_pos=row_pos)
+    assert torch.allclose(got.cpu(), want, atol=FP32_ATOL, rtol=1e-5)
+    assert bool((got[5::17] == 0).all())
+    few = relation_norm_reduce_rows(raw[:1000].cuda(), scores[:1000].cuda(), gamma.cuda(), beta.cuda(),
+                                    row_pos[:1000].cuda(), 1e-5)
+    assert torch.allclose(few, got[:1000], atol=FP32_ATOL, rtol=1e-5)
+    assert_status_clear()
