@@ -529,11 +529,14 @@ __global__ void __launch_bounds__(kRowsThreads, 1) relation_hidden_rows_kernel(
         const unsigned char* gp = g_partner + pr * kRowStride + 64 * cg;
         // results leave straight from the registers: 64 contiguous bytes of the pair's output row per thread
         uint16_t* orow = static_cast<uint16_t*>(a.out) + (static_cast<size_t>(row0) * K + pr) * H + j * kTcBN + 32 * cg;
+        // both halves of this thread's 32 accumulator columns in one round trip to the tensor memory
+        uint32_t v2[2][16];
+        tmem_ld16(tmem_base + lane_base + b * kTcBN + 32 * cg, v2[0]);
+        tmem_ld16(tmem_base + lane_base + b * kTcBN + 32 * cg + 16, v2[1]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-            uint32_t v[16];
-            tmem_ld16(tmem_base + lane_base + b * kTcBN + 32 * cg + 16 * q, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const uint32_t (&v)[16] = v2[q];
             if (!pair_live) continue;
             float y[16];
 #pragma unroll
