@@ -49,6 +49,9 @@ UNIT = "tokens/s"
 # 12-layer decode shape (ncu capture summarised under profiles/), and its ratio to the algorithmic bytes
 NCU_SELECT_TRAFFIC_ROWS256 = 21_464_576
 NCU_SELECT_TRAFFIC_RATIO = 21_464_576 / 21_325_824
+# dram__bytes_read + write of one relation_layer_tail_kernel launch at 8 sequences x K = 8, d 512, hidden 2048
+# (ncu capture of `--kernel-case tail --rows 8`), over the algorithmic bytes of the same launch
+NCU_TAIL_TRAFFIC_RATIO = 3_298_816 / 3_251_776
 # the CPU port keeps fp32 caches on the host (58 MB per sequence at ctx 512 / d 512, 750 MB at ctx 2048 / d 768)
 CPU_MAX_BATCH = {"cfg2": 64, "cfg5": 8}
 
@@ -630,10 +633,13 @@ def roofline_of(table: dict, peak: float, peaks_found: bool) -> dict:
     return {"kernel": dominant, "bound": "hbm", "achieved": dom["gb_per_s"], "peak": peak,
             "unit": "GB/s", "frac": dom["gb_per_s"] / peak,
             "peak_source": "measured" if peaks_found else "fallback",
-            "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO)
-                        if dominant == "relation_select_kernel" else None),
-            "traffic_source": "DRAM bytes of the 256-row ncu capture of this kernel (21.46 MB per "
-                              "launch for 21.33 MB of algorithmic bytes), scaled by algorithmic bytes",
+            "traffic": (round(dom["bytes_per_launch"] * NCU_SELECT_TRAFFIC_RATIO) if dominant == "relation_select_kernel"
+                        else round(dom["bytes_per_launch"] * NCU_TAIL_TRAFFIC_RATIO) if dominant == "relation_layer_tail_kernel"
+                        else None),
+            "traffic_source": ("DRAM bytes of the ncu capture of this kernel at 8 sequences (3.30 MB per launch for 3.25 MB "
+                               "of algorithmic bytes), scaled by algorithmic bytes" if dominant == "relation_layer_tail_kernel"
+                               else "DRAM bytes of the 256-row ncu capture of this kernel (21.46 MB per launch for 21.33 MB "
+                                    "of algorithmic bytes), scaled by algorithmic bytes"),
             "us_per_launch": dom["us_per_launch"], "bytes_per_launch": dom["bytes_per_launch"],
             "share_of_library_time": dom["us_per_step"] / lib_us}
 
