@@ -57,7 +57,7 @@ typedef enum {
  * Programmatic dependent launch (extension; off by default).  When enabled, every kernel of this
  * library is launched with programmatic stream serialisation: its CTAs may start while the kernel
  * before it on the stream is still running, set up their barriers / tensor memory, request their
- * weight tiles and, for the decode form of the selectors, request the key-cache windows and block
+ * weight tiles and affine parameters and, for the decode form of the selectors, request the key-cache windows and block
  * statistics, and only then wait for the earlier kernels to complete.  Results are unchanged
  * provided the caller keeps one rule: the key caches, block statistics and the `position` scalar
  * passed to a selector must not be written by the kernel launched immediately before it on the

@@ -22,9 +22,10 @@
 // to shared memory and reduced through distributed shared memory: CTA c pulls the d / C output
 // rows it owns from all CTAs in a fixed order (deterministic sums), adds the bias and keeps
 // raw[pairs, d / C].  LayerNorm statistics over the full width are combined across the cluster
-// from per-CTA (mean, M2) pairs (Chan's parallel variance); softmax weights, context, residual
-// update and the next LayerNorm follow the same way, and the normalised rows are handed to every
-// CTA for its share of the query projection.  Four cluster barriers in total.
+// from per-CTA (mean, M2) pairs (Chan's parallel variance), which every CTA stores into the
+// shared memory of all the others before the barrier (no remote load after it); softmax weights,
+// context, residual update and the next LayerNorm follow the same way, and the normalised rows
+// are handed to every CTA for its share of the query projection.  Four cluster barriers in total.
 //
 // Semantics follow src/relation_lm/kernels/relation_reduce.py:72-146 and 360-417 of the
 // reference project with the cuBLAS second layer of benchmarks/benchmark_relation_reduce.py:55-64

@@ -83,10 +83,8 @@ __device__ __forceinline__ float4 lt_ld_peer16(uint32_t addr) {
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
     return v;
 }
-__device__ __forceinline__ float2 lt_ld_peer8(uint32_t addr) {
-    float2 v;
-    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
-    return v;
+__device__ __forceinline__ void lt_st_peer8(uint32_t addr, float x, float y) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(x), "f"(y) : "memory");
 }
 __device__ __forceinline__ void lt_st_peer2(uint32_t addr, uint16_t v) {
     asm volatile("st.shared::cluster.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
@@ -118,9 +116,7 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
     __shared__ int failed;
     __shared__ int pair_seq_s[kLtMaxPairs];
     __shared__ float weight_s[kLtMaxPairs];
-    __shared__ __align__(8) float2 stats_out[kLtMaxPairs];       // this CTA's (mean, M2) per pair
     __shared__ __align__(8) float2 ln_s[kLtMaxPairs];            // (mean, rstd) per pair over the full width
-    __shared__ __align__(8) float2 stats2_out[kLtMaxSeq];        // this CTA's (mean, M2) of the updated residual
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int dtype = kBf16 ? static_cast<int>(RLM_BF16) : static_cast<int>(RLM_F16);
@@ -147,6 +143,18 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
     unsigned char* term_a = base + plan.term_a;
     unsigned char* op_a = base + plan.op_a;
     const uint32_t p_kblock = static_cast<uint32_t>(pairs_pad) * 128u;
+    // Once every CTA has dumped its partial sums, the term rows are dead in the whole cluster: their
+    // place receives the LayerNorm statistics that the CTAs push to one another, [sender][pair]
+    // and [sender][sequence] of (mean, M2) over the sender's 32 columns.
+    float2* stats_in = reinterpret_cast<float2*>(term_p);
+    float2* stats2_in = reinterpret_cast<float2*>(term_a);
+    // LayerNorm parameters of this thread's owned column (thread = sequence x owned column at the
+    // end of the kernel): parameters, read before the dependency wait
+    const int own0 = static_cast<int>(rank) * kLtOwn;
+    const float pre_g = a.norm_w[own0 + lane], pre_bt = a.norm_b[own0 + lane];
+    const float pre_nw = a.next_w[own0 + lane], pre_nb = a.next_b[own0 + lane];
+    const int row_chunks = pairs_pad / 4;                      // 16-byte chunks per row of partial sums: 4, 8 or 16
+    const float pre_bias = tid < kLtOwn * row_chunks ? load_scalar(a.second_bias, own0 + tid / row_chunks, dtype) : 0.0f;
 
     const uint32_t bar_wm = smem_u32(&bars[0]), bar_w2 = smem_u32(&bars[1]);
     const uint32_t bar_d1 = smem_u32(&bars[2]), bar_d2 = smem_u32(&bars[3]);
@@ -178,6 +186,10 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
     } else {
         griddep_sync();
     }
+    // the residual stream was written by the previous kernel: requested now, used at the very end
+    float pre_res = 0.0f;
+    if (warp < nseq) pre_res = a.residual[static_cast<size_t>(s0 + warp) * D + own0 + lane];
+    const float pre_mix = *a.mix;
 
     // ---- gathers.  Four threads share a row to gather: they read its index themselves (one
     // broadcast load) and issue their quarter of its copies at once, so no shared-memory round
@@ -375,7 +387,6 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
 
     // ---- dump the partial raw^T [d, pairs_pad] (fp32) over the consumed W_2 slice; 16-byte chunk
     // j of row r sits at chunk j ^ (r mod chunks per row): conflict-free for writers and readers
-    const int row_chunks = pairs_pad / 4;                      // 4, 8 or 16
     const uint32_t part_row = static_cast<uint32_t>(pairs_pad) * 4u;
     {
         const int lr = 32 * (warp & 3) + lane;
@@ -401,7 +412,6 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
 
     // ---- reduce-scatter: this CTA owns output rows [own0, own0 + 32); partial sums are pulled
     // from the CTAs in rank order, so the result does not depend on timing
-    const int own0 = static_cast<int>(rank) * kLtOwn;
     float* own_raw = reinterpret_cast<float*>(p_tile);        // [pair][kLtOwnStride]
     {
         const uint32_t part_base = smem_u32(w2_tile);
@@ -417,7 +427,7 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
             float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
             for (int q = 0; q < 16; ++q) { acc.x += v[q].x; acc.y += v[q].y; acc.z += v[q].z; acc.w += v[q].w; }
-            const float bias = load_scalar(a.second_bias, row, dtype);
+            const float bias = i == tid ? pre_bias : load_scalar(a.second_bias, row, dtype);
             const int pr = 4 * j;
             own_raw[(pr + 0) * kLtOwnStride + r] = acc.x + bias;
             own_raw[(pr + 1) * kLtOwnStride + r] = acc.y + bias;
@@ -445,7 +455,12 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
         for (int i = 0; i < 8; ++i) { const float dv = x[i] - mean; m2 = fmaf(dv, dv, m2); }
         m2 += __shfl_xor_sync(0xffffffffu, m2, 1);
         m2 += __shfl_xor_sync(0xffffffffu, m2, 2);
-        if (q == 0 && pr < pairs) stats_out[pr] = make_float2(mean, m2);
+        // pushed to every CTA of the cluster (the four threads of a pair share the receivers), so that
+        // nobody waits for a remote load after the barrier
+        if (pr < pairs) {
+            const uint32_t at = smem_u32(&stats_in[rank * kLtMaxPairs + pr]);
+            for (int i = 0; i < (C >> 2); ++i) lt_st_peer8(lt_peer(at, static_cast<uint32_t>(q * (C >> 2) + i)), mean, m2);
+        }
     }
     lt_cluster_sync();                                         // (2) every CTA's pair statistics are written
     {
@@ -457,7 +472,7 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
         for (int i = 0; i < 4; ++i) {
             st[i] = make_float2(0.0f, 0.0f);
             if (i < per && pr < pairs)
-                st[i] = lt_ld_peer8(lt_peer(smem_u32(&stats_out[pr]), static_cast<uint32_t>(q * per + i)));
+                st[i] = stats_in[(q * per + i) * kLtMaxPairs + pr];
             msum += st[i].x;
         }
         msum += __shfl_xor_sync(0xffffffffu, msum, 1);
@@ -478,7 +493,7 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
     const bool live = bl < nseq && !bad_position;
     float hval = 0.0f;
     if (live) {
-        const float g = a.norm_w[col], bt = a.norm_b[col];
+        const float g = pre_g, bt = pre_bt;
         float ctx = 0.0f;
         for (int k = 0; k < K; ++k) {
             const float wk = weight_s[bl * K + k];
@@ -488,25 +503,26 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
             ctx = fmaf(wk, fmaf((x - ms.x) * ms.y, g, bt), ctx);
         }
         float* res = a.residual + static_cast<size_t>(s0 + bl) * D + col;
-        hval = fmaf(*a.mix, ctx, *res);
+        hval = fmaf(pre_mix, ctx, pre_res);
         *res = hval;
     }
     {
         const float mean = warp_sum(hval) * (1.0f / kLtOwn);
         const float dv = hval - mean;
         const float m2 = warp_sum(dv * dv);
-        if (lane == 0 && bl < kLtMaxSeq) stats2_out[bl] = make_float2(mean, m2);
+        if (lane < C && bl < kLtMaxSeq)
+            lt_st_peer8(lt_peer(smem_u32(&stats2_in[rank * kLtMaxSeq + bl]), static_cast<uint32_t>(lane)), mean, m2);
     }
     lt_cluster_sync();                                         // (3) every CTA's residual statistics are written
     {
         float2 st = make_float2(0.0f, 0.0f);
-        if (lane < C && bl < nseq) st = lt_ld_peer8(lt_peer(smem_u32(&stats2_out[bl]), static_cast<uint32_t>(lane)));
+        if (lane < C && bl < nseq) st = stats2_in[lane * kLtMaxSeq + bl];
         const float mean = warp_sum(st.x) / static_cast<float>(C);
         const float dm = st.x - mean;
         const float m2 = warp_sum(lane < C ? st.y + static_cast<float>(kLtOwn) * dm * dm : 0.0f);
         const float rstd = rsqrtf(m2 / static_cast<float>(D) + a.next_eps);
         if (live) {
-            const uint16_t nv = lt_to16(fmaf((hval - mean) * rstd, a.next_w[col], a.next_b[col]), dtype);
+            const uint16_t nv = lt_to16(fmaf((hval - mean) * rstd, pre_nw, pre_nb), dtype);
             static_cast<uint16_t*>(a.normalized)[static_cast<size_t>(s0 + bl) * D + col] = nv;
             if (nq_own > 0) {
                 // the normalised rows go to every CTA of the cluster for its share of the projection
