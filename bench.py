@@ -602,8 +602,35 @@ def measure_decode(workload: str, batch: int, args, rank: int, world: int, devic
         e2e_s += time.perf_counter() - t0
         dec.host_tokens.copy_(chosen)
     barrier()
+    # decoding past the context: the state slides by one router block whenever the position reaches
+    # max_context.  One slide timed alone with a cold L2, and 2 x block_size positions back to back with
+    # the two slides they need inside the timed region (compare with l2_warm).
+    bs = cfg.block_size
+    slide_us = []
+    for _ in range(3):
+        dec.position.fill_(T)
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        dec.slide(1)
+        e.record()
+        torch.cuda.synchronize()
+        slide_us.append(s.elapsed_time(e) * 1e3)
+    dec.position.fill_(T)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(2):
+        dec.slide(1)
+        for _ in range(bs):
+            dec.replay()
+    e.record()
+    torch.cuda.synchronize()
+    sliding_ms = s.elapsed_time(e) / (2 * bs)
+    assert int(dec.position.item()) == T
+    dec.position.fill_(prefix)
     assert _abi.read_status() == 0, "a kernel reported a device-side error"
     total_ms, e2e_ms, e2e_warm_ms, warm_ms = max_over_ranks([total_ms, e2e_s * 1e3, e2e_warm_s * 1e3, warm_ms], world, device)
+    moved = dec.state_bytes() * (T - bs) // T
     result = {
         "value": job_rate(world, B, args.steps, total_ms), "ms_per_step": total_ms / args.steps,
         "e2e": {"value": job_rate(world, B, e2e_steps, e2e_ms), "unit": UNIT,
@@ -614,6 +641,13 @@ def measure_decode(workload: str, batch: int, args, rank: int, world: int, devic
                         "l2_warm_value is the same loop back to back"},
         "l2_warm": {"ms_per_step": warm_ms, "value": world * B / (warm_ms / 1e3), "unit": UNIT,
                     "note": "same steps back to back without the L2 flush"},
+        "sliding": {"blocks_per_slide": 1, "positions_per_slide": bs, "slide_us": sorted(slide_us)[1],
+                    "moved_bytes": moved, "gb_per_s": 2 * moved / (sorted(slide_us)[1] * 1e-6) / 1e9,
+                    "ms_per_step_with_slides": sliding_ms, "value_with_slides": B / (sliding_ms / 1e3), "unit": UNIT,
+                    "note": "past max_context the state slides by one router block every block_size positions "
+                            "(state_slide_kernel: every surviving byte read and written once, cold L2 for slide_us); "
+                            "value_with_slides is this rank's rate back to back with the slides in the timed region, "
+                            "to set beside l2_warm"},
         "gpu_launches": kernels_per_step * args.steps, "launches_per_step": kernels_per_step,
         "parameters": model.parameter_count(), "state_bytes_per_gpu": dec.state_bytes(),
     }
@@ -740,7 +774,8 @@ def run_ours(args) -> None:
             "config": {**workload_config(args.workload, B, world),
                        "parameters": main["parameters"], "state_bytes_per_gpu": main["state_bytes_per_gpu"]},
             "e2e": main["e2e"], "gpu_launches": main["gpu_launches"], "launches_per_step": main["launches_per_step"],
-            "l2_warm": main["l2_warm"], "clocks": clocks, "roofline": roofline, "kernels": main["kernels"],
+            "l2_warm": main["l2_warm"], "sliding": main["sliding"], "clocks": clocks, "roofline": roofline,
+            "kernels": main["kernels"],
             "roofline_rows256": {**rows256["relation_select_kernel"], "kernel": "relation_select_kernel", "peak": peak,
                                  "note": "the selector at 256 rows of the 12-layer decode shape, the smallest launch "
                                          "whose bytes (21 MB) are bandwidth-relevant; input sets rotated so that "
@@ -1335,6 +1370,14 @@ def run_kernel_case(args) -> None:
                 pi = (torch.rand(Ns, K, device=dev) * (at[:, None] + 1)).int().clamp(max=Ts - 1)
                 hidden_out = torch.empty(Ns, K, Hs, device=dev, dtype=torch.bfloat16)      # 1.07 GB: larger than L2
             fn = lambda: relation_hidden_cached_rows_out(hidden_out, ex, op, ai, pi, wm, rows)  # noqa: E731
+        elif args.kernel_case == "slide":
+            if i == 0:
+                # the state of the 6-layer d-512 decode shape (ctx 512, block 32) for --rows sequences, two sets
+                from relation_lm.kernels.router_cache import state_slide
+                S = [[rn(6, B, 512, w) for w in (64, 64, 128, 128, 4096, 64, 64, 64, 64)] +
+                     [rn(6, B, 16, 4, 16) for _ in range(4)] for _ in range(2)]
+            state = S[i % 2]
+            fn = lambda: state_slide(state, [32] * 9 + [1] * 4, row_dim=[-2] * 9 + [-3] * 4)  # noqa: E731
         elif args.kernel_case == "norm":
             if i == 0:
                 S = [rn(B, K, d) for _ in range(sets)]
@@ -1379,7 +1422,7 @@ def main() -> None:
     parser.add_argument("--prefix", type=int, default=None,
                         help="prefix length (default: context - 64); shorter only for profiling runs")
     parser.add_argument("--kernel-case", choices=("select", "hidden", "hidden_update", "projection", "norm", "norm_project", "router",
-                                                 "tail", "head", "select_tile", "hidden_rows", "projection_rows", "second_layer_rows"),
+                                                 "tail", "head", "select_tile", "hidden_rows", "projection_rows", "second_layer_rows", "slide"),
                         default=None,
                         help="launch one library kernel a few times at --rows rows of the 12-layer "
                              "decode shape and exit (for profiler captures)")

@@ -534,6 +534,23 @@ int64_t rlm_skinny_argmax_scratch_bytes(void);
 int rlm_l2_prefetch(const void* const* ranges, const int64_t* bytes, int n_ranges, void* stream);
 
 /*
+ * Sliding decode state (extension; "persistent ring-buffer state and contexts beyond 512" is an
+ * open item of the reference's roadmap, docs/roadmap.md:8 — the reference has no code for it).
+ * Every tensor k is a contiguous [n_outer[k], rows[k], row_bytes[k]] array of position-indexed rows
+ * (the caches of src/relation_lm/inference/packed_cache.py:10-17 and of
+ * src/relation_lm/kernels/router_cache.py:256-291, or the router's block statistics with one row
+ * per block); the launch moves rows [shift, rows) to [0, rows - shift) in place and leaves the last
+ * `shift` rows as they were.  A decoder whose position has reached its context slides every cache
+ * by a whole number of router blocks (and the block statistics by that many blocks), lowers its
+ * position by the same number of rows and goes on: the candidates of later steps are the ones a
+ * ring buffer of the same capacity would still hold, with positions counted from the oldest row
+ * kept.  Up to 16 tensors per call; row_bytes a multiple of 16, bases 16-byte aligned
+ * (RLM_ERR_ALIGN); 0 <= shift < rows (RLM_ERR_SHAPE).  The four arrays are HOST arrays.
+ */
+int rlm_state_slide(void* const* tensors, const int64_t* n_outer, const int64_t* rows,
+                    const int64_t* row_bytes, const int64_t* shift_rows, int n_tensors, void* stream);
+
+/*
  * The front of a decode step in one launch (extension): the embedding of one position
  * (src/relation_lm/models/relation_lm.py:130-131: (token + boundary embedding) * scale + position
  * embedding), two LayerNorms of the embedded rows and one projection of each,

@@ -35,6 +35,17 @@ class OracleDecoder:
     def _round(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.dtype == torch.float32 else x.to(self.dtype).float()
 
+    def slide(self, blocks: int = 1) -> None:
+        """``StatefulDecoder.slide``: the oldest ``blocks`` router blocks leave, every later row (and
+        block statistic) moves to the front, the last rows keep their content, the position drops."""
+        rows = blocks * self.config.block_size
+        for c in (self.anchor_keys, self.partner_keys, self.operand_cache, self.partner_anchor_cache,
+                  self.expanded_cache, *self.router_caches):
+            c[:, :, :c.size(2) - rows] = c[:, :, rows:].clone()
+        for s in self.router_stats:
+            s[:, :, :s.size(2) - blocks] = s[:, :, blocks:].clone()
+        self.position -= rows
+
     def step(self, tokens: torch.Tensor, boundaries: torch.Tensor):
         cfg, w, t = self.config, self.w, self.position
         R = cfg.relation_dim

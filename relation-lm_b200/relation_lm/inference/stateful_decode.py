@@ -40,7 +40,7 @@ from relation_lm.kernels.relation_reduce import (expanded_cache_append, expanded
                                                  relation_norm_reduce_residual, relation_tail)
 from relation_lm.kernels.relation_select import relation_select_packed
 from relation_lm.kernels.relation_layer import relation_layer, relation_layer_supported
-from relation_lm.kernels.router_cache import packed_projection_append, sparse_cache_append
+from relation_lm.kernels.router_cache import packed_projection_append, sparse_cache_append, state_slide
 
 
 class StatefulDecoder:
@@ -161,6 +161,27 @@ class StatefulDecoder:
                   self.expanded_cache, *self.router_caches, *self.router_stats):
             t.zero_()
         self.position.zero_()
+
+    def slide(self, blocks: int = 1) -> None:
+        """Drop the oldest ``blocks`` router blocks of every sequence and lower the position by as
+        many rows (``relation_lm.kernels.router_cache.state_slide``): how a decoder goes on once its
+        position has reached ``max_context``.  Afterwards position ``p`` of the state is what position
+        ``p + blocks * block_size`` was — keys, operands, expanded rows, router caches and the
+        statistics of every block, none of them recomputed — so later steps choose among the rows a
+        ring buffer of ``max_context`` rows would still hold, and count positions (the position
+        embedding, the ``ceil(log2(t + 2))`` partner limit) from the oldest row kept.  One launch for
+        the caches and statistics and one for the position, on the current stream, between steps
+        (outside the captured graph, whose buffers it leaves where they are)."""
+        cfg = self.config
+        blocks = int(blocks)
+        if not 0 < blocks < cfg.max_context // cfg.block_size:
+            raise ValueError("slide by at least one block and fewer than the context holds")
+        rows = blocks * cfg.block_size
+        caches = [self.anchor_keys, self.partner_keys, self.operand_cache, self.partner_anchor_cache,
+                  self.expanded_cache, *self.router_caches]
+        state_slide(caches + list(self.router_stats), [rows] * len(caches) + [blocks] * 4,
+                    row_dim=[-2] * len(caches) + [-3] * 4)
+        self.position.sub_(rows)
 
     def state_bytes(self) -> int:
         tensors = (self.anchor_keys, self.partner_keys, self.operand_cache, self.partner_anchor_cache,

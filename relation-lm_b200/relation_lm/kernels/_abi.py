@@ -43,6 +43,7 @@ PROTOTYPES = {
     "rlm_skinny_projection": [_P, _L, _P, _P, _P] + [_I] * 5 + [_P] * 4,
     "rlm_packed_projection_append": [_P, _L, _P, _P, _I] + [_P] * 15 + [_I] * 7 + [_P, _P],
     "rlm_l2_prefetch": [_P, _P, _I, _P],
+    "rlm_state_slide": [_P, _P, _P, _P, _P, _I, _P],
     "rlm_decode_front": [_P] * 6 + [_F] + [_P] * 4 + [_F] + [_P] * 6 + [_I] * 8 + [_P, _P],
     "rlm_relation_layer_tail_supported": [_I] * 7,
     "rlm_relation_layer_tail": [_P] * 11 + [_F, _P, _P, _P, _P, _F, _P, _P, _P] + [_I] * 8 + [_P, _P],

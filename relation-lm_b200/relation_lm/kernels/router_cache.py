@@ -258,3 +258,45 @@ def _(x, weight, anchor_keys, partner_keys, operand_cache, partner_anchor_cache,
       partner_raw_cache, anchor_conv_cache, partner_conv_cache, anchor_mean, anchor_std, partner_mean,
       partner_std, anchor_conv_weight, partner_conv_weight, position, block_size):
     return x.new_empty((x.size(0), weight.size(0)))
+
+
+def state_slide(tensors: list[Tensor], shifts: list[int], row_dim: int | list[int] = -2) -> None:
+    """Slide position-indexed caches in place (extension; ``rlm_state_slide``): tensor ``k`` — contiguous,
+    rows along ``row_dim`` (one value, or one per tensor: the position axis -2 of a cache ``[..., T, width]``,
+    the block axis -3 of the router statistics ``[..., blocks, heads, width]``) — moves rows ``[shifts[k], rows)`` to the front and keeps its last
+    ``shifts[k]`` rows as they were.  Up to 16 tensors per launch; longer lists take several launches.
+    Not a registered operator: a decoder calls it between steps, outside its captured graph."""
+    import ctypes
+
+    if len(tensors) != len(shifts):
+        raise ValueError("one shift per tensor")
+    if not tensors:
+        return
+    device = tensors[0].device
+    entries = []
+    dims = list(row_dim) if isinstance(row_dim, (list, tuple)) else [row_dim] * len(tensors)
+    if len(dims) != len(tensors):
+        raise ValueError("one row_dim per tensor")
+    for t, shift, axis in zip(tensors, shifts, dims):
+        if t.numel() == 0:
+            continue
+        if not t.is_cuda or t.device != device or not t.is_contiguous():
+            raise ValueError("state_slide takes contiguous CUDA tensors of one device")
+        dim = int(axis) % t.dim()
+        rows = t.size(dim)
+        outer = 1
+        for d in range(dim):
+            outer *= t.size(d)
+        inner = t.element_size()
+        for d in range(dim + 1, t.dim()):
+            inner *= t.size(d)
+        if not 0 <= int(shift) < rows:
+            raise ValueError("shift must be in [0, rows)")
+        entries.append((t.data_ptr(), outer, rows, inner, int(shift)))
+    for first in range(0, len(entries), 16):
+        part = entries[first:first + 16]
+        n = len(part)
+        ptrs = (ctypes.c_void_p * n)(*[e[0] for e in part])
+        cols = [(ctypes.c_int64 * n)(*[e[i] for e in part]) for i in (1, 2, 3, 4)]
+        with _abi.device_guard(device):
+            _abi.check(_abi.LIB.rlm_state_slide(ptrs, *cols, n, _abi.stream_ptr(device)))
