@@ -637,7 +637,8 @@ def measure_decode(workload: str, batch: int, args, rank: int, world: int, devic
                 "h2d_bytes_per_step": 2 * B * 8, "d2h_bytes_per_step": B * 8, "steps": e2e_steps,
                 "l2": "flushed before every step (outside the host clock)",
                 "l2_warm_value": job_rate(world, B, e2e_steps, e2e_warm_ms),
-                "note": "host-timed: pinned ids -> device, the step's graph, chosen tokens -> pinned memory, stream sync; "
+                "note": "host-timed: pinned ids -> device (one copy node), the step's graph, chosen tokens written into pinned "
+                        "host memory by the head kernel, stream sync; "
                         "l2_warm_value is the same loop back to back"},
         "l2_warm": {"ms_per_step": warm_ms, "value": world * B / (warm_ms / 1e3), "unit": UNIT,
                     "note": "same steps back to back without the L2 flush"},

@@ -25,9 +25,10 @@ from relation_lm.inference.routed_model import RoutedRelationLM
 from relation_lm.kernels import _abi
 from relation_lm.kernels.packed_projection import (decode_embed_norm, decode_front, decode_front_supported,
                                                     greedy_token, l2_prefetch, layer_norm_cast,
-                                                    packed_projection, packed_projection_slices,
+                                                    mapped_host_view, packed_projection, packed_projection_slices,
                                                     skinny_argmax_scratch_bytes, skinny_projection,
-                                                    skinny_projection_greedy, skinny_projection_supported)
+                                                    skinny_projection_greedy, skinny_projection_greedy_into,
+                                                    skinny_projection_supported)
 from relation_lm.kernels.relation_reduce import (expanded_cache_append, expanded_cache_append_packed,
                                                  relation_hidden_cache_update,
                                                  relation_layer_tail, relation_layer_tail_supported,
@@ -202,17 +203,20 @@ class StatefulDecoder:
                 _abi.set_programmatic_launch(previous)
         return self._step_unfused(tokens, boundaries, keep_selection)
 
-    def step_greedy(self, tokens: Tensor, boundaries: Tensor) -> Tensor:
+    def step_greedy(self, tokens: Tensor, boundaries: Tensor, chosen_out: Tensor | None = None) -> Tensor:
         """One step followed by the greedy choice: returns the next token ids ``[B]`` (int64) and
         advances the position.  On the fused path the arg-max and the position increment are one
-        launch of the library."""
+        launch of the library; with ``chosen_out`` (int64 ``[B]``, skinny fused path only) the choice is
+        written there — a device view of pinned host memory included."""
+        if chosen_out is not None and not (self.fused and self.skinny):
+            raise ValueError("chosen_out needs the fused path with the head projection's greedy launch")
         if not self.fused:
             token_logits, _ = self.step(tokens, boundaries)
             return token_logits.argmax(-1)
         previous = _abi.set_programmatic_launch(self.programmatic_launch)
         try:
             if self.skinny:
-                return self._step_fused(tokens, boundaries, False, advance=False, greedy=True)
+                return self._step_fused(tokens, boundaries, False, advance=False, greedy=True, chosen_out=chosen_out)
             self._step_fused(tokens, boundaries, False, advance=False)
             return greedy_token(self.last_logits, self.config.vocab_size, self.position)
         finally:
@@ -259,7 +263,7 @@ class StatefulDecoder:
         return token_logits, boundary_logits
 
     def _step_fused(self, tokens: Tensor, boundaries: Tensor, keep_selection: bool, advance: bool = True,
-                    greedy: bool = False):
+                    greedy: bool = False, chosen_out: Tensor | None = None):
         """The same step with the elementwise glue folded into the library's kernels:
         1 launch per layer where the selector fits in front of the single-launch relation tail, 2
         (select, tail) where only the tail applies, otherwise up to 5
@@ -418,8 +422,13 @@ class StatefulDecoder:
         self.last_final = self.normalized
         if greedy:
             # head projection + greedy arg-max + position increment in one launch
-            logits, chosen = skinny_projection_greedy(self.normalized, self.head_weight, self.head_bias,
-                                                      cfg.vocab_size, self.argmax_scratch, pos)
+            if chosen_out is not None:
+                chosen = chosen_out
+                logits = skinny_projection_greedy_into(self.normalized, self.head_weight, self.head_bias,
+                                                       cfg.vocab_size, self.argmax_scratch, pos, chosen_out)
+            else:
+                logits, chosen = skinny_projection_greedy(self.normalized, self.head_weight, self.head_bias,
+                                                          cfg.vocab_size, self.argmax_scratch, pos)
             self.last_logits = logits
             if self.prefetch:
                 main.wait_stream(self._side_stream)      # join the side branch (long finished) at the step's end
@@ -466,34 +475,43 @@ class StatefulDecoder:
     def replay(self) -> None:
         self._graph.replay()
 
-    def capture_host_io(self) -> None:
-        """Capture the greedy step together with its host transfers: the token and boundary ids are
-        copied from the pinned tensors ``host_tokens`` / ``host_boundaries`` ``[B]`` (int64) at the
-        head of the graph and the chosen tokens land in the pinned ``host_next`` at its tail, so a
-        serving loop pays one graph launch and one stream synchronisation per position
-        (``step_host``).  State and position are left exactly as they were."""
+    def capture_host_io(self, mapped: bool | None = None) -> None:
+        """Capture the greedy step together with its host transfers, so that a serving loop pays one
+        graph launch and one stream synchronisation per position (``step_host``): it writes the token
+        and boundary ids into the pinned tensors ``host_tokens`` / ``host_boundaries`` ``[B]`` (int64; the
+        two rows of ``host_ids``, copied to the device by one node at the head of the graph) and finds the
+        chosen tokens in the pinned ``host_next``.  ``mapped`` (default: whenever the head projection's
+        greedy launch applies): the head kernel writes the choices into the pinned memory itself, through
+        a device view of ``host_next``, instead of a copy node at the tail of the graph.  (Reading the ids
+        through such a view was measured too: it puts a host-memory round trip at the start of the step's
+        dependency chain and is 10-20 us slower than the copy.)  State and position are left exactly as
+        they were."""
         B = self.batch
-        self.host_tokens = torch.zeros(B, dtype=torch.int64).pin_memory()
-        self.host_boundaries = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.host_ids = torch.zeros(2, B, dtype=torch.int64).pin_memory()
+        self.host_tokens, self.host_boundaries = self.host_ids[0], self.host_ids[1]
         self.host_next = torch.zeros(B, dtype=torch.int64).pin_memory()
-        tokens = torch.zeros(B, device=self.device, dtype=torch.int64)
-        boundaries = torch.zeros(B, device=self.device, dtype=torch.int64)
+        can_map = self.fused and self.skinny
+        mapped = can_map if mapped is None else (bool(mapped) and can_map)
+        ids = torch.zeros(2, B, device=self.device, dtype=torch.int64)
+        tokens, boundaries = ids[0], ids[1]
+        chosen_view = mapped_host_view(self.host_next, self.device) if mapped else None
         saved = int(self.position.item())
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):                                   # warm-up outside capture
-                self.step_greedy(tokens, boundaries)
+                self.step_greedy(tokens, boundaries, chosen_view)
                 self.position.fill_(saved)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                tokens.copy_(self.host_tokens, non_blocking=True)
-                boundaries.copy_(self.host_boundaries, non_blocking=True)
-                chosen = self.step_greedy(tokens, boundaries)
-                self.host_next.copy_(chosen, non_blocking=True)
+                ids.copy_(self.host_ids, non_blocking=True)
+                chosen = self.step_greedy(tokens, boundaries, chosen_view)
+                if not mapped:
+                    self.host_next.copy_(chosen, non_blocking=True)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         self.position.fill_(saved)
-        self._host_graph, self._host_graph_buffers = graph, (tokens, boundaries, chosen)
+        self.host_io_mapped = mapped
+        self._host_graph, self._host_graph_buffers = graph, (ids, chosen)
 
     def step_host(self) -> Tensor:
         """One position through the graph of ``capture_host_io``: reads ``host_tokens`` /

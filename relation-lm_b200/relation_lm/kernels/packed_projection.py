@@ -364,5 +364,66 @@ def _(x, weight, bias, vocab, scratch, position):
     return x.new_empty((x.size(0), weight.size(0))), x.new_empty((x.size(0),), dtype=torch.int64)
 
 
+@torch.library.custom_op("relation_lm::skinny_projection_greedy_into",
+                         mutates_args=("scratch", "position", "next_token"), device_types="cuda")
+def skinny_projection_greedy_into(x: Tensor, weight: Tensor, bias: Tensor | None, vocab: int, scratch: Tensor,
+                                  position: Tensor | None, next_token: Tensor) -> Tensor:
+    """``skinny_projection_greedy`` writing the chosen tokens into the caller's ``next_token`` ``[rows]``
+    (int64) — which may be a device view of pinned host memory (``mapped_host_view``): the choice then
+    reaches the host without a copy of its own.  Returns the logits."""
+    device = _abi.require_cuda_rows(x=x)
+    _abi.require_cuda_contiguous(weight=weight, bias=bias, scratch=scratch, next_token=next_token)
+    if weight.dim() != 2 or weight.size(1) != x.size(1) or x.dtype != weight.dtype:
+        raise ValueError("weight must be [n_out, d_in] with the dtype of x")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != weight.size(0)):
+        raise ValueError("bias must be float32 [n_out]")
+    if scratch.dtype != torch.uint8 or scratch.numel() < skinny_argmax_scratch_bytes():
+        raise ValueError("scratch must be a uint8 tensor of skinny_argmax_scratch_bytes() bytes")
+    if not 1 <= vocab <= weight.size(0):
+        raise ValueError("vocab must lie within the projection's outputs")
+    if next_token.dtype != torch.int64 or next_token.shape != (x.size(0),):
+        raise ValueError("next_token must be int64 [rows]")
+    if position is not None:
+        _abi.require_position(position, device)
+    out = torch.empty((x.size(0), weight.size(0)), device=device, dtype=x.dtype)
+    with _abi.device_guard(device):
+        _abi.check(_abi.LIB.rlm_skinny_projection(
+            _abi.ptr(x), x.stride(0), _abi.ptr(weight), _abi.ptr(bias), _abi.ptr(out), x.size(0), x.size(1),
+            weight.size(0), _abi.code(x), int(vocab), _abi.ptr(scratch), _abi.ptr(next_token), _abi.ptr(position),
+            _abi.stream_ptr(device)))
+    return out
+
+
+@skinny_projection_greedy_into.register_fake
+def _(x, weight, bias, vocab, scratch, position, next_token):
+    return x.new_empty((x.size(0), weight.size(0)))
+
+
+class _MappedHost:
+    """Pinned host memory presented through ``__cuda_array_interface__`` (with unified addressing the
+    device address of pinned memory is its host address)."""
+
+    def __init__(self, host: Tensor) -> None:
+        code = {torch.int64: "<i8", torch.int32: "<i4", torch.float32: "<f4", torch.uint8: "|u1"}[host.dtype]
+        self.__cuda_array_interface__ = {"shape": tuple(host.shape), "typestr": code,
+                                         "data": (host.data_ptr(), False), "version": 2}
+        self.host = host
+
+
+def mapped_host_view(host: Tensor, device: torch.device) -> Tensor:
+    """A CUDA tensor over the pinned, contiguous host tensor ``host``: kernels that take it read or write
+    the host memory directly (a few bytes of ids in, a few bytes of choices out: cheaper than a copy node
+    per transfer in a decode graph).  The host sees a kernel's writes once the stream is synchronised.  The
+    view keeps ``host`` alive."""
+    if host.is_cuda or not host.is_pinned() or not host.is_contiguous():
+        raise ValueError("mapped_host_view takes a pinned, contiguous host tensor")
+    holder = _MappedHost(host)
+    view = torch.as_tensor(holder, device=device)
+    if view.data_ptr() != host.data_ptr() or not view.is_cuda:
+        raise RuntimeError("the device view does not alias the host tensor")
+    view._mapped_host = holder
+    return view
+
+
 def skinny_argmax_scratch_bytes() -> int:
     return int(_abi.LIB.rlm_skinny_argmax_scratch_bytes())

@@ -203,19 +203,26 @@ def test_query_projection_inside_norm_reduce_tracks_separate_launches():
     assert_status_clear()
 
 
-def test_host_transfer_graph_equals_the_plain_greedy_step():
+@pytest.mark.parametrize("mapped", [True, False])
+def test_host_transfer_graph_equals_the_plain_greedy_step(mapped):
     """``capture_host_io`` / ``step_host``: ids from pinned host memory in, chosen tokens in pinned
-    host memory out, all inside one graph; same tokens as ``step_greedy`` on device tensors."""
+    host memory out, all inside one graph; same tokens as ``step_greedy`` on device tensors.  Mapped:
+    the head kernel writes the choices into the pinned memory itself; otherwise a copy node does."""
     from relation_lm.inference.stateful_decode import StatefulDecoder
 
-    model = _small_model(seed=19)
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+
+    # d_model 256: the head projection's greedy launch (whose output the mapped form redirects) applies
+    model = RoutedRelationLM(RoutedRelationConfig(vocab_size=500, boundary_vocab_size=16, d_model=256, layers=2,
+                                                  max_context=96, block_size=8, local_window=16, top_blocks=2), seed=19)
     B, steps = 3, 12
     g = torch.Generator().manual_seed(31)
     tokens = torch.randint(0, 500, (B, steps), generator=g)
     bounds = torch.randint(0, 16, (B, steps), generator=g)
     plain = StatefulDecoder(model, B, "cuda", torch.bfloat16)
     hosted = StatefulDecoder(model, B, "cuda", torch.bfloat16)
-    hosted.capture_host_io()
+    hosted.capture_host_io(mapped=mapped)
+    assert hosted.skinny and hosted.host_io_mapped == mapped
     assert int(hosted.position.item()) == 0
     for t in range(steps):
         want = plain.step_greedy(tokens[:, t].cuda(), bounds[:, t].cuda())
