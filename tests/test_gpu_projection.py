@@ -227,6 +227,33 @@ def test_skinny_projection_with_greedy_head(dtype):
     assert_status_clear()
 
 
+def test_greedy_head_writes_into_pinned_host_memory():
+    """``skinny_projection_greedy_into`` with a device view of a pinned host tensor as its output: the
+    host finds the same choices as ``skinny_projection_greedy`` returns, once the stream is synchronised."""
+    from relation_lm.kernels.packed_projection import (mapped_host_view, skinny_argmax_scratch_bytes,
+                                                        skinny_projection_greedy, skinny_projection_greedy_into)
+
+    g = torch.Generator().manual_seed(9191)
+    rows, d, n, vocab = 5, 256, 1024, 1000
+    x = torch.randn(rows, d, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, d, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    scratch = torch.zeros(skinny_argmax_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    want_logits, want = skinny_projection_greedy(x, w, None, vocab, scratch, None)
+    host = torch.full((rows,), -1, dtype=torch.int64).pin_memory()
+    view = mapped_host_view(host, x.device)
+    assert view.is_cuda and view.data_ptr() == host.data_ptr()
+    position = position_tensor(7)
+    logits = skinny_projection_greedy_into(x, w, None, vocab, scratch, position, view)
+    torch.cuda.synchronize()
+    assert torch.equal(host, want.cpu()) and torch.equal(logits, want_logits)
+    assert int(position.item()) == 8 and not scratch.any()
+    with pytest.raises(ValueError):
+        mapped_host_view(torch.zeros(4, dtype=torch.int64), x.device)           # not pinned
+    with pytest.raises(ValueError):
+        skinny_projection_greedy_into(x, w, None, vocab, scratch, None, view[:3])
+    assert_status_clear()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,d,n_first,n_second", [(8, 512, 3072, 256), (1, 512, 3072, 256), (16, 256, 512, 256),
                                                   (11, 256, 1000, 72)])
