@@ -494,7 +494,12 @@ class StatefulDecoder:
         mapped = can_map if mapped is None else (bool(mapped) and can_map)
         ids = torch.zeros(2, B, device=self.device, dtype=torch.int64)
         tokens, boundaries = ids[0], ids[1]
-        chosen_view = mapped_host_view(self.host_next, self.device) if mapped else None
+        chosen_view = None
+        if mapped:
+            try:
+                chosen_view = mapped_host_view(self.host_next, self.device)
+            except (RuntimeError, TypeError, ValueError):      # no device view of pinned memory here: copy node
+                mapped = False
         saved = int(self.position.item())
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
