@@ -409,6 +409,11 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     lt_cluster_sync();                                         // (1) every CTA's partial is in its shared memory
+    // every warp has read its accumulators: the tensor memory goes back now, off the kernel's exit path
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
 
     // ---- reduce-scatter: this CTA owns output rows [own0, own0 + 32); partial sums are pulled
     // from the CTAs in rank order, so the result does not depend on timing
@@ -566,10 +571,6 @@ __device__ __forceinline__ void layer_tail_body(const CUtensorMap& map_wm, const
         if (*reinterpret_cast<volatile int*>(&failed)) atomicOr(a.status, RLM_DEV_TIMEOUT);
         if (bad_position) atomicOr(a.status, RLM_DEV_POSITION);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
 int lt_validate(const LayerTailArgs& a) {
