@@ -610,6 +610,7 @@ def measure_decode(workload: str, batch: int, args, rank: int, world: int, devic
     for _ in range(3):
         dec.position.fill_(T)
         flush.zero_()
+        flush.zero_()                                   # long enough for the host to have the slide's launch queued
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         dec.slide(1)
@@ -644,6 +645,7 @@ def measure_decode(workload: str, batch: int, args, rank: int, world: int, devic
                     "note": "same steps back to back without the L2 flush"},
         "sliding": {"blocks_per_slide": 1, "positions_per_slide": bs, "slide_us": sorted(slide_us)[1],
                     "moved_bytes": moved, "gb_per_s": 2 * moved / (sorted(slide_us)[1] * 1e-6) / 1e9,
+                    "bound": "hbm", "algorithmic_bytes": 2 * moved,
                     "ms_per_step_with_slides": sliding_ms, "value_with_slides": B / (sliding_ms / 1e3), "unit": UNIT,
                     "note": "past max_context the state slides by one router block every block_size positions "
                             "(state_slide_kernel: every surviving byte read and written once, cold L2 for slide_us); "
@@ -775,7 +777,8 @@ def run_ours(args) -> None:
             "config": {**workload_config(args.workload, B, world),
                        "parameters": main["parameters"], "state_bytes_per_gpu": main["state_bytes_per_gpu"]},
             "e2e": main["e2e"], "gpu_launches": main["gpu_launches"], "launches_per_step": main["launches_per_step"],
-            "l2_warm": main["l2_warm"], "sliding": main["sliding"], "clocks": clocks, "roofline": roofline,
+            "l2_warm": main["l2_warm"], "sliding": {**main["sliding"], "peak": peak, "frac": main["sliding"]["gb_per_s"] / peak},
+            "clocks": clocks, "roofline": roofline,
             "kernels": main["kernels"],
             "roofline_rows256": {**rows256["relation_select_kernel"], "kernel": "relation_select_kernel", "peak": peak,
                                  "note": "the selector at 256 rows of the 12-layer decode shape, the smallest launch "
