@@ -183,3 +183,85 @@ def test_random_layer_tail_configurations():
         assert not n_query or torch.equal(query, again[2]), what
         done += 1
     assert_status_clear()
+
+
+def test_random_decoder_configurations_match_cpu_port(monkeypatch):
+    """fp32 decoders of random small configurations against the CPU port, position by position, sliding
+    when the context is full.  Every selection is bit-equal to the oracle's on the selector's own inputs
+    (indices and scores); the free-running port chooses the same rows at every layer and position and
+    its logits agree to 2e-3 — until a near tie, if one comes up (the two sides' GEMMs sum in different
+    orders, so their queries differ in the last bit): there the competing scores must agree to 1e-5 and
+    the comparison of that configuration ends."""
+    import relation_lm.inference.stateful_decode as decode_module
+    from oracle.decode_port import OracleDecoder
+    from relation_lm.inference.routed_model import RoutedRelationConfig, RoutedRelationLM
+
+    calls = []
+    plain_select = decode_module.relation_select_packed
+
+    def recording_select(*args):
+        out = plain_select(*args)
+        calls.append((args[:14] + (args[14].clone(),) + args[15:], out))      # the position moves on after the step
+        return out
+
+    monkeypatch.setattr(decode_module, "relation_select_packed", recording_select)
+    rng = random.Random(20264)
+    near_ties = 0
+    for _ in range(8):
+        bs = rng.choice([4, 8, 16])
+        nb = rng.choice([3, 4, 6, 8])
+        T = bs * nb
+        cfg = RoutedRelationConfig(
+            vocab_size=300, boundary_vocab_size=8, d_model=rng.choice([128, 256]), layers=rng.choice([1, 2, 3]),
+            max_context=T, block_size=bs, local_window=rng.choice([w for w in (4, 8, 16, 32) if w <= T]),
+            top_blocks=rng.choice([t for t in (0, 1, 2, 3) if t < nb]), k_max=rng.choice([2, 4, 8]),
+            relation_dim=rng.choice([64, 128]), strict_valid=rng.random() < 0.5)
+        model = RoutedRelationLM(cfg, seed=rng.randrange(1000))
+        B, steps = rng.choice([1, 2, 5]), T + 2 * bs + 3
+        gpu = decode_module.StatefulDecoder(model, B, "cuda", torch.float32)
+        cpu = OracleDecoder(model, B, torch.float32)
+        g = torch.Generator().manual_seed(rng.randrange(1 << 30))
+        tokens = torch.randint(0, 300, (B, steps), generator=g)
+        bounds = torch.randint(0, 8, (B, steps), generator=g)
+        in_step, position = True, 0
+        for t in range(steps):
+            if position == T:
+                gpu.slide(1)
+                if in_step:
+                    cpu.slide(1)
+                position -= bs
+            position += 1
+            calls.clear()
+            tl, _ = gpu.step(tokens[:, t].cuda(), bounds[:, t].cuda(), keep_selection=True)
+            assert len(calls) == cfg.layers
+            for layer, (args, out) in enumerate(calls):
+                host = [a.cpu() if isinstance(a, torch.Tensor) else a for a in args]
+                want = oracle.relation_select(*host[:14], int(host[14]), *host[15:])
+                assert _same_selection(out, want[:4]), ("selector on its own inputs", cfg, t, layer)
+            if not in_step:
+                continue
+            ctl, _ = cpu.step(tokens[:, t], bounds[:, t])
+            for layer, ((ga, gp), (ca, cp)) in enumerate(zip(gpu.last_selection, cpu.last_selection)):
+                if torch.equal(ga.cpu(), ca) and torch.equal(gp.cpu(), cp):
+                    continue
+                # a different row on the two sides: only where the rows' scores tie to rounding, judged
+                # on the selector's own inputs (gate scores are plain 64-wide dot products)
+                host = [a.cpu() if isinstance(a, torch.Tensor) else a for a in calls[layer][0]]
+                mine = [o.cpu() for o in calls[layer][1]]
+                for b in range(B):
+                    if int(ga[b]) != int(ca[b]):
+                        other = float(host[0][b].double() @ host[1][b, int(ca[b])].double()) / 8.0       # gate width 64
+                        assert abs(other - float(mine[1][b])) <= 1e-5 * max(1.0, abs(other)), (cfg, t, layer, b)
+                        continue                              # another anchor: other partner queries
+                    query = host[7][b, :64].double() + host[8][b, int(ga[b]), :64].double()
+                    kept = mine[3][b][torch.isfinite(mine[3][b])]
+                    for p in set(cp[b].tolist()) - set(gp[b].cpu().tolist()):
+                        other = float(query @ host[9][b, p].double()) / 8.0
+                        assert kept.numel() and abs(other - float(kept.min())) <= 1e-5 * max(1.0, abs(other)), (cfg, t, layer, b, p)
+                near_ties += 1
+                in_step = False
+                break
+            if in_step:
+                assert torch.allclose(tl.cpu(), ctl, atol=2e-3, rtol=1e-4), (cfg, t)
+    assert near_ties <= 2, near_ties
+    assert_status_clear()
