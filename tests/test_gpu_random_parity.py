@@ -265,3 +265,68 @@ def test_random_decoder_configurations_match_cpu_port(monkeypatch):
                 assert torch.allclose(tl.cpu(), ctl, atol=2e-3, rtol=1e-4), (cfg, t)
     assert near_ties <= 2, near_ties
     assert_status_clear()
+
+
+def test_random_multi_anchor_configurations():
+    """Routed multi-anchor selection in random shapes: the one-launch per-row form against the oracle's
+    slot-by-slot composition (anchors, activity, partner indices and scores bit-exact), and the
+    whole-sequence tile form against the per-row form, bit for bit."""
+    from relation_lm.kernels.multi_select import relation_select_multi_prefill, relation_select_multi_rows
+
+    rng = random.Random(20265)
+    done = 0
+    while done < 40:
+        S, B = rng.choice([1, 2, 3, 4, 8]), rng.choice([1, 2, 3])
+        bs, NB = rng.choice([8, 16, 32, 64]), rng.choice([2, 4, 8, 16])
+        T = bs * NB
+        L, top, K = rng.choice([8, 16, 32, 64, 128]), rng.choice([0, 1, 2, 3]), rng.choice([1, 2, 4, 8])
+        if T > 512 or L > T or top >= NB:
+            continue
+        strict = rng.random() < 0.5
+        dt = rng.choice([torch.bfloat16, torch.bfloat16, torch.float16, torch.float32])
+        what = (S, B, T, NB, L, top, K, strict, dt)
+        g = torch.Generator().manual_seed(rng.randrange(1 << 30))
+        N = B * T
+        rn = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+        x = [rn(N, S, 64).to(dt), rn(S, B, T, 64).to(dt), rn(N, S, 64).to(dt), rn(S, B, NB, 4, 16).to(dt),
+             rn(S, B, NB, 4, 16).abs().to(dt), rn(S, 4), rn(S, 4, 16), rn(N, S, 128).to(dt), rn(S, B, T, 128).to(dt),
+             rn(S, B, T, 64).to(dt), rn(S, B, NB, 4, 16).to(dt), rn(S, B, NB, 4, 16).abs().to(dt), rn(S, 4), rn(S, 4, 16)]
+        if rng.random() < 0.5:                                  # exact duplicates: ties between positions and slots
+            x[1][0, :, 5::7] = x[1][0, :, 4:5]
+            x[9][0, :, 3::5] = x[9][0, :, 2:3]
+        aq, ak, arq, am, as_, ag, ab, pb, pac, pk, pm, ps, pg, pbias = x
+        row_batch = torch.arange(B, dtype=torch.int32).repeat_interleave(T)
+        row_pos = torch.arange(T, dtype=torch.int32).repeat(B)
+        d = [v.cuda() for v in x]
+        got = relation_select_multi_rows(*d, row_batch.cuda(), row_pos.cuda(), L, top, K, strict)
+        active = torch.arange(S)[None, :] <= row_pos[:, None]
+        taken = torch.full((N, S), -1, dtype=torch.int32)
+        anchors = torch.zeros(N, S, dtype=torch.int32)
+        for s in range(S):
+            idx, score = oracle.anchor_select(aq[:, s], ak[s], arq[:, s], am[s], as_[s], ag[s], ab[s], 0, L, top, strict,
+                                              row_batch=row_batch, row_pos=row_pos, exclude_index=taken.clone())
+            live = active[:, s] & torch.isfinite(score)
+            anchors[:, s] = torch.where(live, idx, torch.zeros_like(idx))
+            taken[:, s] = torch.where(live, idx, torch.full_like(idx, -1))
+            active[:, s] = live
+        assert torch.equal(got[0].cpu(), anchors), what
+        assert torch.equal(got[2].cpu(), active), what
+        for s in range(S):
+            v = pb[:, s].float() + pac[s][row_batch.long(), anchors[:, s].long()].float()
+            idx, score = oracle.partner_topk(v[:, :64], pk[s], v[:, 64:], pm[s], ps[s], pg[s], pbias[s], 0, taken[:, s],
+                                             L, top, K, strict, row_batch=row_batch, row_pos=row_pos, exclude_index=taken)
+            live = active[:, s, None] & torch.isfinite(score)
+            assert torch.equal(got[5].cpu()[:, s], live), (what, s)
+            assert torch.equal(got[3].cpu()[:, s][live], idx[live]), (what, s)
+            assert torch.equal(got[4].cpu()[:, s][live], score[live]), (what, s)
+        if dt == torch.bfloat16 and L + top * bs <= 512:            # the tile form serves bfloat16
+            try:
+                tiled = relation_select_multi_prefill(*d, T, L, top, K, strict)
+            except (ValueError, RuntimeError) as error:
+                assert "shared memory" in str(error) or "support" in str(error), (what, error)
+            else:
+                for a, b in zip(tiled, got):
+                    same = torch.equal(a.view(torch.int32), b.view(torch.int32)) if a.dtype == torch.float32 else torch.equal(a, b)
+                    assert same, ("whole-sequence form", what)
+        done += 1
+    assert_status_clear()
